@@ -1,0 +1,382 @@
+// C ABI of the decode hot path (include/fl_b200.h): context, memory helpers,
+// single operators, the task-level entry. The decoder lives in decoder.cu.
+#include "capi_internal.h"
+
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+
+namespace flb {
+
+static thread_local char g_err[512] = "";
+
+int set_err(int code, const char *fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+int cuda_err(cudaError_t e, const char *what) {
+    if (e == cudaSuccess) return FL_B200_OK;
+    return set_err(FL_B200_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+}
+
+} // namespace flb
+
+using namespace flb;
+
+#define CK(call)                                                       \
+    do {                                                               \
+        cudaError_t e_ = (call);                                       \
+        if (e_ != cudaSuccess) return cuda_err(e_, #call);             \
+    } while (0)
+
+extern "C" {
+
+int fl_b200_abi_version(void) { return FL_B200_ABI_VERSION; }
+const char *fl_b200_last_error(void) { return g_err; }
+
+int fl_b200_create(int device, fl_b200_ctx **out) {
+    if (!out) return set_err(FL_B200_ERR_ARG, "fl_b200_create: out is null");
+    *out = nullptr;
+    int n = 0;
+    cudaError_t e = cudaGetDeviceCount(&n);
+    if (e != cudaSuccess || n == 0)
+        return set_err(FL_B200_ERR_CUDA, "fl_b200_create: no CUDA device (%s); this library has no CPU path",
+                       cudaGetErrorString(e));
+    if (device < 0 || device >= n) return set_err(FL_B200_ERR_ARG, "fl_b200_create: device %d of %d", device, n);
+    CK(cudaSetDevice(device));
+    cudaDeviceProp prop;
+    CK(cudaGetDeviceProperties(&prop, device));
+    if (prop.major != 10)
+        return set_err(FL_B200_ERR_CUDA, "fl_b200_create: device %d is sm_%d%d; kernels are built for sm_100a only",
+                       device, prop.major, prop.minor);
+    fl_b200_ctx *c = new fl_b200_ctx();
+    c->device = device;
+    c->sms = prop.multiProcessorCount;
+    CK(cudaStreamCreate(&c->stream));
+    CK(cudaEventCreate(&c->ev0));
+    CK(cudaEventCreate(&c->ev1));
+    CK(cudaMalloc(&c->status, 256));
+    CK(cudaMemset(c->status, 0, 256));
+    c->argmax_ticket = c->status + 1;
+    c->attn_tickets_cap = 1024;
+    CK(cudaMalloc(&c->attn_tickets, c->attn_tickets_cap * sizeof(uint32_t)));
+    CK(cudaMemset(c->attn_tickets, 0, c->attn_tickets_cap * sizeof(uint32_t)));
+    CK(cudaMalloc(&c->argmax_scratch, (size_t)3 * 1024 * sizeof(float)));
+    CK(cudaMalloc(&c->small, 64));
+    CK(matvec_init());
+    CK(attn_init());
+    *out = c;
+    return FL_B200_OK;
+}
+
+void fl_b200_destroy(fl_b200_ctx *c) {
+    if (!c) return;
+    cudaSetDevice(c->device);
+    cudaStreamSynchronize(c->stream);
+    cudaFree(c->attn_part);
+    cudaFree(c->attn_tickets);
+    cudaFree(c->argmax_scratch);
+    cudaFree(c->small);
+    cudaFree(c->status);
+    cudaFree(c->stage);
+    cudaEventDestroy(c->ev0);
+    cudaEventDestroy(c->ev1);
+    cudaStreamDestroy(c->stream);
+    delete c;
+}
+
+int fl_b200_sync(fl_b200_ctx *c) {
+    CK(cudaStreamSynchronize(c->stream));
+    return FL_B200_OK;
+}
+
+int fl_b200_device_status(fl_b200_ctx *c, uint32_t *out) {
+    uint32_t v = 0;
+    CK(cudaMemcpyAsync(&v, c->status, 4, cudaMemcpyDeviceToHost, c->stream));
+    CK(cudaStreamSynchronize(c->stream));
+    if (v != 0) CK(cudaMemsetAsync(c->status, 0, 4, c->stream));
+    if (out) *out = v;
+    return FL_B200_OK;
+}
+
+int fl_b200_sm_count(fl_b200_ctx *c) { return c->sms; }
+void *fl_b200_stream(fl_b200_ctx *c) { return (void *)c->stream; }
+
+int fl_b200_malloc(fl_b200_ctx *c, size_t bytes, void **out) {
+    CK(cudaSetDevice(c->device));
+    CK(cudaMalloc(out, bytes ? bytes : 1));
+    return FL_B200_OK;
+}
+int fl_b200_free(fl_b200_ctx *c, void *p) {
+    CK(cudaSetDevice(c->device));
+    CK(cudaFree(p));
+    return FL_B200_OK;
+}
+int fl_b200_upload(fl_b200_ctx *c, void *dst, const void *src, size_t bytes) {
+    CK(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, c->stream));
+    CK(cudaStreamSynchronize(c->stream));
+    return FL_B200_OK;
+}
+int fl_b200_download(fl_b200_ctx *c, void *dst, const void *src, size_t bytes) {
+    CK(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, c->stream));
+    CK(cudaStreamSynchronize(c->stream));
+    return FL_B200_OK;
+}
+int fl_b200_memset(fl_b200_ctx *c, void *dst, int value, size_t bytes) {
+    CK(cudaMemsetAsync(dst, value, bytes, c->stream));
+    return FL_B200_OK;
+}
+
+int fl_b200_timer_start(fl_b200_ctx *c) {
+    CK(cudaEventRecord(c->ev0, c->stream));
+    return FL_B200_OK;
+}
+int fl_b200_timer_stop(fl_b200_ctx *c, float *ms) {
+    CK(cudaEventRecord(c->ev1, c->stream));
+    CK(cudaEventSynchronize(c->ev1));
+    CK(cudaEventElapsedTime(ms, c->ev0, c->ev1));
+    return FL_B200_OK;
+}
+
+int fl_b200_dequant(fl_b200_ctx *c, int fmt, const void *w, uint64_t rows, uint32_t cols, float *out) {
+    if (!w || !out) return set_err(FL_B200_ERR_ARG, "dequant: null pointer");
+    if (fmt < FL_B200_F32 || fmt > FL_B200_Q6_K) return set_err(FL_B200_ERR_ARG, "dequant: format %d", fmt);
+    if (cols % blk_elems(fmt) != 0 || cols % 4 != 0)
+        return set_err(FL_B200_ERR_ARG, "dequant: cols %u not a multiple of the %u-element block", cols, blk_elems(fmt));
+    if (((uintptr_t)out & 15u) != 0) return set_err(FL_B200_ERR_ARG, "dequant: out must be 16-byte aligned");
+    if (fmt == FL_B200_Q4_K && ((uintptr_t)w & 3u) != 0) return set_err(FL_B200_ERR_ARG, "dequant: Q4_K weights must be 4-byte aligned");
+    if (((uintptr_t)w & 1u) != 0) return set_err(FL_B200_ERR_ARG, "dequant: weights must be 2-byte aligned");
+    return cuda_err(launch_dequant(fmt, w, rows, cols, out, c->sms, c->stream), "dequant launch");
+}
+
+static int check_matvec(int fmt, const void *w, uint32_t rows, uint32_t cols, const void *x, const void *y) {
+    if (!w || !x || !y) return set_err(FL_B200_ERR_ARG, "matvec: null pointer");
+    if (fmt < FL_B200_F32 || fmt > FL_B200_Q6_K) return set_err(FL_B200_ERR_ARG, "matvec: format %d", fmt);
+    if (rows == 0 || cols == 0) return set_err(FL_B200_ERR_ARG, "matvec: empty shape %u x %u", rows, cols);
+    // Graph::freeze rule (src/runtime/graph.cpp:88-89)
+    if (cols % blk_elems(fmt) != 0)
+        return set_err(FL_B200_ERR_ARG, "matvec: cols %u not a multiple of the format block size %u", cols, blk_elems(fmt));
+    if (((uintptr_t)w & 1u) != 0 || (fmt == FL_B200_F32 && ((uintptr_t)w & 3u) != 0))
+        return set_err(FL_B200_ERR_ARG, "matvec: misaligned weights");
+    return FL_B200_OK;
+}
+
+static int matvec_impl(fl_b200_ctx *c, int fmt, const void *w, uint32_t rows, uint32_t cols, const float *x,
+                       uint32_t nx, uint32_t xstride, float *y, uint32_t ystride, int accumulate) {
+    if (int rc = check_matvec(fmt, w, rows, cols, x, y)) return rc;
+    if (nx == 0) nx = 1;
+    for (uint32_t p = 0; p < nx; ++p) {
+        MatvecArgs a{};
+        a.n_tensors = 1;
+        a.t[0].w = (const uint8_t *)w;
+        a.t[0].y = y + (size_t)p * ystride;
+        a.t[0].resid = nullptr;
+        a.t[0].rows = rows;
+        a.t[0].fmt = fmt;
+        a.x = x + (size_t)p * xstride;
+        a.cols = cols;
+        a.x_mode = MV_X_PLAIN;
+        a.accumulate = accumulate;
+        a.status = c->status;
+        if (int rc = cuda_err(launch_matvec(a, c->sms, c->stream), "matvec launch")) return rc;
+    }
+    return FL_B200_OK;
+}
+
+int fl_b200_matvec(fl_b200_ctx *c, int fmt, const void *w, uint32_t rows, uint32_t cols, const float *x,
+                   uint32_t nx, uint32_t xstride, float *y, uint32_t ystride) {
+    return matvec_impl(c, fmt, w, rows, cols, x, nx, xstride, y, ystride, 1);
+}
+
+int fl_b200_matvec_assign(fl_b200_ctx *c, int fmt, const void *w, uint32_t rows, uint32_t cols,
+                          const float *x, float *y) {
+    return matvec_impl(c, fmt, w, rows, cols, x, 1, 0, y, 0, 0);
+}
+
+static int ensure_stage(fl_b200_ctx *c, size_t bytes) {
+    if (c->stage_cap >= bytes) return FL_B200_OK;
+    CK(cudaStreamSynchronize(c->stream));
+    cudaFree(c->stage);
+    c->stage = nullptr;
+    c->stage_cap = 0;
+    CK(cudaMalloc(&c->stage, bytes));
+    c->stage_cap = bytes;
+    return FL_B200_OK;
+}
+
+int fl_b200_matvec_host(fl_b200_ctx *c, int fmt, const void *w, uint32_t rows, uint32_t cols,
+                        const float *x_host, float *y_host) {
+    if (!x_host || !y_host) return set_err(FL_B200_ERR_ARG, "matvec_host: null pointer");
+    const size_t xb = ((size_t)cols * 4 + 255) & ~(size_t)255, yb = (size_t)rows * 4;
+    if (int rc = ensure_stage(c, xb + yb)) return rc;
+    float *xd = (float *)c->stage, *yd = (float *)((uint8_t *)c->stage + xb);
+    CK(cudaMemcpyAsync(xd, x_host, (size_t)cols * 4, cudaMemcpyHostToDevice, c->stream));
+    if (int rc = matvec_impl(c, fmt, w, rows, cols, xd, 1, 0, yd, 0, 0)) return rc;
+    CK(cudaMemcpyAsync(y_host, yd, yb, cudaMemcpyDeviceToHost, c->stream));
+    CK(cudaStreamSynchronize(c->stream));
+    return FL_B200_OK;
+}
+
+static int attn_impl(fl_b200_ctx *c, const float *q, const uint16_t *k, const uint16_t *v, uint32_t n_q,
+                     uint32_t n_kv, uint32_t d, uint32_t kv_len, uint32_t kv_stride, uint32_t batch, float scale,
+                     float *out, const int32_t *pos_dev) {
+    if (!q || !k || !v || !out) return set_err(FL_B200_ERR_ARG, "attn_decode: null pointer");
+    if (d != 128) return set_err(FL_B200_ERR_ARG, "attn_decode: head_dim %u (only 128 is built)", d);
+    if (n_kv == 0 || n_q != 4 * n_kv)
+        return set_err(FL_B200_ERR_ARG, "attn_decode: %u query heads over %u KV heads (only groups of 4 are built)", n_q, n_kv);
+    if (batch == 0) return set_err(FL_B200_ERR_ARG, "attn_decode: batch 0");
+    if (!pos_dev && (kv_len == 0 || kv_len > kv_stride))
+        return set_err(FL_B200_ERR_ARG, "attn_decode: kv_len %u outside 1..kv_stride %u", kv_len, kv_stride);
+    if (((uintptr_t)k & 15u) || ((uintptr_t)v & 15u) || ((uintptr_t)q & 15u))
+        return set_err(FL_B200_ERR_ARG, "attn_decode: q, k, v must be 16-byte aligned");
+    if ((uint64_t)n_kv * batch > c->attn_tickets_cap)
+        return set_err(FL_B200_ERR_ARG, "attn_decode: n_kv_head * batch = %llu exceeds %u", (unsigned long long)n_kv * batch, c->attn_tickets_cap);
+    AttnArgs a{};
+    a.q = q;
+    a.k = (const __half *)k;
+    a.v = (const __half *)v;
+    a.out = out;
+    a.pos = pos_dev;
+    a.kv_len = kv_len;
+    a.kv_stride = kv_stride;
+    a.batch_stride = (uint64_t)n_kv * kv_stride * d;
+    a.n_q_head = n_q;
+    a.n_kv_head = n_kv;
+    a.batch = batch;
+    a.n_splits = attn_pick_splits(n_kv, batch, pos_dev ? kv_stride : kv_len, c->sms);
+    a.scale = scale;
+    a.status = c->status;
+    const size_t need = attn_part_floats(n_q, batch, a.n_splits) * sizeof(float);
+    if (c->attn_part_cap < need) {
+        CK(cudaStreamSynchronize(c->stream));
+        cudaFree(c->attn_part);
+        c->attn_part = nullptr;
+        c->attn_part_cap = 0;
+        CK(cudaMalloc(&c->attn_part, need));
+        c->attn_part_cap = need;
+    }
+    a.part = c->attn_part;
+    a.tickets = c->attn_tickets;
+    return cuda_err(launch_attn_decode(a, c->stream), "attn launch");
+}
+
+int fl_b200_attn_decode(fl_b200_ctx *c, const float *q, const uint16_t *k, const uint16_t *v, uint32_t n_q,
+                        uint32_t n_kv, uint32_t d, uint32_t kv_len, uint32_t kv_stride, uint32_t batch,
+                        float scale, float *out) {
+    return attn_impl(c, q, k, v, n_q, n_kv, d, kv_len, kv_stride, batch, scale, out, nullptr);
+}
+
+int fl_b200_attn_decode_host(fl_b200_ctx *c, const float *q_host, const uint16_t *k, const uint16_t *v,
+                             uint32_t n_q, uint32_t n_kv, uint32_t d, uint32_t kv_len, uint32_t kv_stride,
+                             uint32_t batch, float scale, float *out_host) {
+    if (!q_host || !out_host) return set_err(FL_B200_ERR_ARG, "attn_decode_host: null pointer");
+    const size_t qb = (size_t)batch * n_q * d * 4;
+    if (int rc = ensure_stage(c, 2 * qb + 512)) return rc;
+    float *qd = (float *)c->stage, *od = (float *)((uint8_t *)c->stage + ((qb + 255) & ~(size_t)255));
+    CK(cudaMemcpyAsync(qd, q_host, qb, cudaMemcpyHostToDevice, c->stream));
+    if (int rc = attn_impl(c, qd, k, v, n_q, n_kv, d, kv_len, kv_stride, batch, scale, od, nullptr)) return rc;
+    CK(cudaMemcpyAsync(out_host, od, qb, cudaMemcpyDeviceToHost, c->stream));
+    CK(cudaStreamSynchronize(c->stream));
+    return FL_B200_OK;
+}
+
+int fl_b200_rmsnorm(fl_b200_ctx *c, const float *x, const float *w, float *y, float eps, uint32_t n) {
+    if (!x || !w || !y || n == 0) return set_err(FL_B200_ERR_ARG, "rmsnorm: bad argument");
+    return cuda_err(launch_rmsnorm(x, w, y, eps, n, c->stream), "rmsnorm launch");
+}
+int fl_b200_add2(fl_b200_ctx *c, const float *a, const float *b, float *y, uint32_t n) {
+    if (!a || !b || !y || n == 0) return set_err(FL_B200_ERR_ARG, "add2: bad argument");
+    return cuda_err(launch_add2(a, b, y, n, c->stream), "add2 launch");
+}
+int fl_b200_silu_mul(fl_b200_ctx *c, const float *g, const float *u, float *h, uint32_t n) {
+    if (!g || !u || !h || n == 0) return set_err(FL_B200_ERR_ARG, "silu_mul: bad argument");
+    return cuda_err(launch_silu_mul(g, u, h, n, c->stream), "silu_mul launch");
+}
+
+int fl_b200_rope_kv_append(fl_b200_ctx *c, float *q, const float *k, const float *v, uint16_t *kc,
+                           uint16_t *vc, const int32_t *pos, uint32_t n_q, uint32_t n_kv, uint32_t d,
+                           uint32_t kv_stride, float freq_base) {
+    if (!k || !v || !kc || !vc || !pos) return set_err(FL_B200_ERR_ARG, "rope_kv_append: null pointer");
+    if (d == 0 || (d & 1u)) return set_err(FL_B200_ERR_ARG, "rope_kv_append: head_dim %u must be even", d);
+    RopeAppendArgs a{};
+    a.q = q;
+    a.k = k;
+    a.v = v;
+    a.kcache = (__half *)kc;
+    a.vcache = (__half *)vc;
+    a.pos = pos;
+    a.n_q_head = n_q;
+    a.n_kv_head = n_kv;
+    a.head_dim = d;
+    a.kv_stride = kv_stride;
+    // Same expression, same libm as the reference's host path
+    // (src/runtime/decode_params.h:125).
+    a.theta_scale = powf(freq_base, -2.0f / (float)d);
+    return cuda_err(launch_rope_append(a, c->stream), "rope_append launch");
+}
+
+int fl_b200_argmax(fl_b200_ctx *c, const float *lg, uint32_t n, int32_t *idx, float *margin) {
+    if (!lg || !idx || !margin || n == 0) return set_err(FL_B200_ERR_ARG, "argmax: bad argument");
+    return cuda_err(launch_argmax(lg, n, idx, margin, c->argmax_scratch, c->argmax_ticket, c->sms, c->stream),
+                    "argmax launch");
+}
+
+int fl_b200_exec_task(fl_b200_ctx *c, const fl_b200_task *t) {
+    if (!t) return set_err(FL_B200_ERR_ARG, "exec_task: null task");
+    switch (t->kind) {
+    case FL_B200_SIGNAL: return FL_B200_OK;
+    case FL_B200_STREAM_DOT: {
+        // Graph::freeze rule (src/runtime/graph.cpp:90-91)
+        if (t->w_bytes != (uint64_t)t->rows * row_bytes(t->fmt, t->cols))
+            return set_err(FL_B200_ERR_ARG, "exec_task: STREAM_DOT w_bytes mismatch");
+        return fl_b200_matvec(c, t->fmt, t->w, t->rows, t->cols, (const float *)t->x, t->nx ? t->nx : 1, t->xstride,
+                              (float *)t->y, t->ystride);
+    }
+    case FL_B200_RMSNORM: {
+        if (!t->aux) return set_err(FL_B200_ERR_ARG, "exec_task: decode op without aux param block");
+        fl_b200_rmsnorm_p p;
+        CK(cudaMemcpyAsync(&p, t->aux, sizeof(p), cudaMemcpyDefault, c->stream));
+        CK(cudaStreamSynchronize(c->stream));
+        return fl_b200_rmsnorm(c, p.x, p.wnorm, p.y, p.eps, p.n);
+    }
+    case FL_B200_ADD2: {
+        if (!t->aux) return set_err(FL_B200_ERR_ARG, "exec_task: decode op without aux param block");
+        fl_b200_add2_p p;
+        CK(cudaMemcpyAsync(&p, t->aux, sizeof(p), cudaMemcpyDefault, c->stream));
+        CK(cudaStreamSynchronize(c->stream));
+        return fl_b200_add2(c, p.a, p.b, p.y, p.n);
+    }
+    case FL_B200_SILU_MUL: {
+        if (!t->aux) return set_err(FL_B200_ERR_ARG, "exec_task: decode op without aux param block");
+        fl_b200_silu_mul_p p;
+        CK(cudaMemcpyAsync(&p, t->aux, sizeof(p), cudaMemcpyDefault, c->stream));
+        CK(cudaStreamSynchronize(c->stream));
+        return fl_b200_silu_mul(c, p.gate, p.up, p.h, p.n);
+    }
+    case FL_B200_ATTN_GQA_F16: {
+        if (!t->aux) return set_err(FL_B200_ERR_ARG, "exec_task: decode op without aux param block");
+        fl_b200_attn_gqa_f16_p p;
+        CK(cudaMemcpyAsync(&p, t->aux, sizeof(p), cudaMemcpyDefault, c->stream));
+        CK(cudaStreamSynchronize(c->stream));
+        return attn_impl(c, p.q, p.kcache, p.vcache, p.n_q_head, p.n_kv_head, p.head_dim, 0, p.kv_stride, 1,
+                         p.scale, p.out, p.pos);
+    }
+    case FL_B200_ROPE_KV_APPEND_F16: {
+        if (!t->aux) return set_err(FL_B200_ERR_ARG, "exec_task: decode op without aux param block");
+        fl_b200_rope_kv_append_f16_p p;
+        CK(cudaMemcpyAsync(&p, t->aux, sizeof(p), cudaMemcpyDefault, c->stream));
+        CK(cudaStreamSynchronize(c->stream));
+        return fl_b200_rope_kv_append(c, p.q, p.k, p.v, p.kcache, p.vcache, p.pos, p.n_q_head, p.n_kv_head,
+                                      p.head_dim, p.kv_stride, p.freq_base);
+    }
+    default:
+        return set_err(FL_B200_ERR_ARG, "exec_task: task kind %d has no device implementation in this library", (int)t->kind);
+    }
+}
+
+} // extern "C"

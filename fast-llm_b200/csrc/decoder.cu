@@ -1,0 +1,390 @@
+// Llama-shape greedy decoder on one B200: the per-token launch sequence of the
+// decode hot path, recorded once as a CUDA graph and replayed per token. It
+// plays the role of the reference's Decoder (src/model/decoder.h:52-81): build
+// once (src/model/decoder.cpp:639-672), then per token embed -> run -> argmax
+// (src/model/decoder.cpp:1176-1264). The reference's persistent task executor
+// is replaced by a static launch plan: the graph is frozen and identical every
+// token, and the position is read from a device scalar, so one recording serves
+// every position.
+//
+// Per layer (6 launches): [RMSNorm + Q/K/V matvec] -> [RoPE + f16 KV append] ->
+// [split-KV GQA attention + combine] -> [O matvec + residual] ->
+// [RMSNorm + gate/up matvec] -> [SiLU*up + down matvec + residual];
+// then [RMSNorm + head matvec] -> [argmax] -> [advance].
+#include "capi_internal.h"
+
+#include <cmath>
+#include <vector>
+
+using namespace flb;
+
+#define CK(call)                                                       \
+    do {                                                               \
+        cudaError_t e_ = (call);                                       \
+        if (e_ != cudaSuccess) return cuda_err(e_, #call);             \
+    } while (0)
+
+namespace {
+
+struct Tensor { int fmt = -1; const uint8_t *w = nullptr; };
+
+// After a step: token <- argmax, history[count++] <- argmax, pos += 1.
+__global__ void advance_kernel(int32_t *token, const int32_t *next, int32_t *pos, int32_t *hist,
+                               uint32_t *hist_n, uint32_t hist_cap) {
+    if (threadIdx.x == 0 && blockIdx.x == 0) {
+        const int32_t t = *next;
+        *token = t;
+        const uint32_t k = *hist_n;
+        if (k < hist_cap) hist[k] = t;
+        *hist_n = k + 1;
+        *pos = *pos + 1;
+    }
+}
+
+} // namespace
+
+struct fl_b200_decoder {
+    fl_b200_ctx *ctx = nullptr;
+    fl_b200_llama_cfg c{};
+    std::vector<Tensor> lw;                 // n_layer * 7
+    std::vector<const float *> attn_norm, ffn_norm;
+    Tensor tok_embd, output;
+    const float *out_norm = nullptr;
+    std::vector<__half *> kc, vc;
+    // device state
+    int32_t *d_token = nullptr, *d_next = nullptr, *d_pos = nullptr, *d_hist = nullptr;
+    uint32_t *d_hist_n = nullptr;
+    float *d_margin = nullptr;
+    uint32_t hist_cap = 4096;
+    float *xa = nullptr, *xb = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *att = nullptr;
+    float *g = nullptr, *u = nullptr, *logits = nullptr, *xn_final = nullptr, *part = nullptr;
+    uint32_t *tickets = nullptr;
+    uint32_t n_splits = 1;
+    int32_t *h_pin = nullptr;               // pinned: [0] token, [1] pos, [2] next
+    int32_t n_past = 0;
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
+    uint32_t launches = 0;
+    bool finalized = false;
+};
+
+static int enqueue_step(fl_b200_decoder *d, cudaStream_t s, uint32_t *n_launch) {
+    const fl_b200_llama_cfg &c = d->c;
+    fl_b200_ctx *ctx = d->ctx;
+    const uint32_t E = c.n_embd, D = c.head_dim, QD = c.n_head * D, KD = c.n_kv_head * D;
+    uint32_t n = 0;
+    CK(launch_embed(d->tok_embd.fmt, d->tok_embd.w, d->d_token, E, d->xa, s)); ++n;
+    for (uint32_t l = 0; l < c.n_layer; ++l) {
+        const Tensor *w = &d->lw[(size_t)l * 7];
+        {   // RMSNorm + Q/K/V
+            MatvecArgs a{};
+            a.n_tensors = 3;
+            a.t[0] = {w[FL_B200_T_WQ].w, d->q, nullptr, QD, w[FL_B200_T_WQ].fmt};
+            a.t[1] = {w[FL_B200_T_WK].w, d->k, nullptr, KD, w[FL_B200_T_WK].fmt};
+            a.t[2] = {w[FL_B200_T_WV].w, d->v, nullptr, KD, w[FL_B200_T_WV].fmt};
+            a.x = d->xa; a.wnorm = d->attn_norm[l]; a.eps = c.eps; a.cols = E;
+            a.x_mode = MV_X_RMSNORM; a.status = ctx->status;
+            CK(launch_matvec(a, ctx->sms, s)); ++n;
+        }
+        {
+            RopeAppendArgs a{};
+            a.q = d->q; a.k = d->k; a.v = d->v; a.kcache = d->kc[l]; a.vcache = d->vc[l]; a.pos = d->d_pos;
+            a.n_q_head = c.n_head; a.n_kv_head = c.n_kv_head; a.head_dim = D; a.kv_stride = c.max_kv;
+            a.theta_scale = powf(c.rope_base, -2.0f / (float)D);
+            CK(launch_rope_append(a, s)); ++n;
+        }
+        {
+            AttnArgs a{};
+            a.q = d->q; a.k = d->kc[l]; a.v = d->vc[l]; a.out = d->att; a.part = d->part; a.tickets = d->tickets;
+            a.pos = d->d_pos; a.kv_len = 0; a.kv_stride = c.max_kv;
+            a.batch_stride = (uint64_t)c.n_kv_head * c.max_kv * D;
+            a.n_q_head = c.n_head; a.n_kv_head = c.n_kv_head; a.batch = 1; a.n_splits = d->n_splits;
+            a.scale = 1.0f / sqrtf((float)D); a.status = ctx->status;
+            CK(launch_attn_decode(a, s)); ++n;
+        }
+        {   // O projection + residual: xb = xa + Wo att
+            MatvecArgs a{};
+            a.n_tensors = 1;
+            a.t[0] = {w[FL_B200_T_WO].w, d->xb, d->xa, E, w[FL_B200_T_WO].fmt};
+            a.x = d->att; a.cols = QD; a.x_mode = MV_X_PLAIN; a.status = ctx->status;
+            CK(launch_matvec(a, ctx->sms, s)); ++n;
+        }
+        {   // RMSNorm + gate / up
+            MatvecArgs a{};
+            a.n_tensors = 2;
+            a.t[0] = {w[FL_B200_T_GATE].w, d->g, nullptr, c.n_ff, w[FL_B200_T_GATE].fmt};
+            a.t[1] = {w[FL_B200_T_UP].w, d->u, nullptr, c.n_ff, w[FL_B200_T_UP].fmt};
+            a.x = d->xb; a.wnorm = d->ffn_norm[l]; a.eps = c.eps; a.cols = E;
+            a.x_mode = MV_X_RMSNORM; a.status = ctx->status;
+            CK(launch_matvec(a, ctx->sms, s)); ++n;
+        }
+        {   // SiLU(gate) * up, down projection + residual: xa = xb + Wdown h
+            MatvecArgs a{};
+            a.n_tensors = 1;
+            a.t[0] = {w[FL_B200_T_DOWN].w, d->xa, d->xb, E, w[FL_B200_T_DOWN].fmt};
+            a.x = d->g; a.x2 = d->u; a.cols = c.n_ff; a.x_mode = MV_X_SILU_MUL; a.status = ctx->status;
+            CK(launch_matvec(a, ctx->sms, s)); ++n;
+        }
+    }
+    {   // output norm + head
+        MatvecArgs a{};
+        a.n_tensors = 1;
+        a.t[0] = {d->output.w, d->logits, nullptr, c.n_vocab, d->output.fmt};
+        a.x = d->xa; a.wnorm = d->out_norm; a.eps = c.eps; a.cols = E;
+        a.x_mode = MV_X_RMSNORM; a.status = ctx->status; a.xn_out = d->xn_final;
+        CK(launch_matvec(a, ctx->sms, s)); ++n;
+    }
+    CK(launch_argmax(d->logits, c.n_vocab, d->d_next, d->d_margin, ctx->argmax_scratch, ctx->argmax_ticket,
+                     ctx->sms, s)); ++n;
+    advance_kernel<<<1, 32, 0, s>>>(d->d_token, d->d_next, d->d_pos, d->d_hist, d->d_hist_n, d->hist_cap);
+    CK(cudaGetLastError()); ++n;
+    if (n_launch) *n_launch = n;
+    return FL_B200_OK;
+}
+
+extern "C" {
+
+int fl_b200_decoder_create(fl_b200_ctx *ctx, const fl_b200_llama_cfg *cfg, fl_b200_decoder **out) {
+    if (!ctx || !cfg || !out) return set_err(FL_B200_ERR_ARG, "decoder_create: null pointer");
+    const fl_b200_llama_cfg &c = *cfg;
+    if (c.head_dim != 128) return set_err(FL_B200_ERR_ARG, "decoder_create: head_dim %u (only 128 is built)", c.head_dim);
+    if (c.n_kv_head == 0 || c.n_head != 4 * c.n_kv_head)
+        return set_err(FL_B200_ERR_ARG, "decoder_create: %u heads over %u KV heads (only groups of 4 are built)", c.n_head, c.n_kv_head);
+    if (c.n_layer == 0 || c.n_embd == 0 || c.n_ff == 0 || c.n_vocab == 0 || c.max_kv == 0)
+        return set_err(FL_B200_ERR_ARG, "decoder_create: zero-sized dimension");
+    if (c.n_embd % 2048 || c.n_ff % 2048 || (c.n_head * c.head_dim) % 2048)
+        return set_err(FL_B200_ERR_ARG, "decoder_create: n_embd, n_ff and n_head*head_dim must be multiples of 2048");
+    fl_b200_decoder *d = new fl_b200_decoder();
+    d->ctx = ctx;
+    d->c = c;
+    d->lw.resize((size_t)c.n_layer * 7);
+    d->attn_norm.assign(c.n_layer, nullptr);
+    d->ffn_norm.assign(c.n_layer, nullptr);
+    d->kc.assign(c.n_layer, nullptr);
+    d->vc.assign(c.n_layer, nullptr);
+    CK(cudaSetDevice(ctx->device));
+    const size_t kvb = (size_t)c.n_kv_head * c.max_kv * c.head_dim * sizeof(__half);
+    for (uint32_t l = 0; l < c.n_layer; ++l) {
+        CK(cudaMalloc(&d->kc[l], kvb));
+        CK(cudaMalloc(&d->vc[l], kvb));
+        CK(cudaMemsetAsync(d->kc[l], 0, kvb, ctx->stream));
+        CK(cudaMemsetAsync(d->vc[l], 0, kvb, ctx->stream));
+    }
+    const uint32_t QD = c.n_head * c.head_dim, KD = c.n_kv_head * c.head_dim;
+    CK(cudaMalloc(&d->d_token, 64));
+    d->d_next = d->d_token + 1;
+    d->d_pos = d->d_token + 2;
+    d->d_hist_n = (uint32_t *)(d->d_token + 3);
+    d->d_margin = (float *)(d->d_token + 4);
+    CK(cudaMemsetAsync(d->d_token, 0, 64, ctx->stream));
+    CK(cudaMalloc(&d->d_hist, d->hist_cap * sizeof(int32_t)));
+    CK(cudaMalloc(&d->xa, c.n_embd * 4));
+    CK(cudaMalloc(&d->xb, c.n_embd * 4));
+    CK(cudaMalloc(&d->q, QD * 4));
+    CK(cudaMalloc(&d->k, KD * 4));
+    CK(cudaMalloc(&d->v, KD * 4));
+    CK(cudaMalloc(&d->att, QD * 4));
+    CK(cudaMalloc(&d->g, c.n_ff * 4));
+    CK(cudaMalloc(&d->u, c.n_ff * 4));
+    CK(cudaMalloc(&d->logits, (size_t)c.n_vocab * 4));
+    CK(cudaMalloc(&d->xn_final, c.n_embd * 4));
+    d->n_splits = attn_pick_splits(c.n_kv_head, 1, c.max_kv, ctx->sms);
+    CK(cudaMalloc(&d->part, attn_part_floats(c.n_head, 1, d->n_splits) * sizeof(float)));
+    CK(cudaMalloc(&d->tickets, 256 * sizeof(uint32_t)));
+    CK(cudaMemsetAsync(d->tickets, 0, 256 * sizeof(uint32_t), ctx->stream));
+    CK(cudaMallocHost(&d->h_pin, 64));
+    CK(cudaStreamSynchronize(ctx->stream));
+    *out = d;
+    return FL_B200_OK;
+}
+
+void fl_b200_decoder_destroy(fl_b200_decoder *d) {
+    if (!d) return;
+    cudaSetDevice(d->ctx->device);
+    cudaStreamSynchronize(d->ctx->stream);
+    if (d->exec) cudaGraphExecDestroy(d->exec);
+    if (d->graph) cudaGraphDestroy(d->graph);
+    for (auto p : d->kc) cudaFree(p);
+    for (auto p : d->vc) cudaFree(p);
+    cudaFree(d->d_token); cudaFree(d->d_hist); cudaFree(d->xa); cudaFree(d->xb); cudaFree(d->q);
+    cudaFree(d->k); cudaFree(d->v); cudaFree(d->att); cudaFree(d->g); cudaFree(d->u); cudaFree(d->logits);
+    cudaFree(d->xn_final); cudaFree(d->part); cudaFree(d->tickets);
+    cudaFreeHost(d->h_pin);
+    delete d;
+}
+
+static int check_weight(const fl_b200_decoder *d, int fmt, const void *w, uint32_t cols) {
+    (void)d;
+    if (!w) return set_err(FL_B200_ERR_ARG, "decoder: null weight pointer");
+    if (fmt != FL_B200_Q4_K && fmt != FL_B200_Q6_K)
+        return set_err(FL_B200_ERR_ARG, "decoder: weight format %d (the decoder streams Q4_K and Q6_K)", fmt);
+    if (((uintptr_t)w & 15u) != 0) return set_err(FL_B200_ERR_ARG, "decoder: weights must be 16-byte aligned");
+    if (cols % 2048) return set_err(FL_B200_ERR_ARG, "decoder: cols %u not a multiple of 2048", cols);
+    return FL_B200_OK;
+}
+
+int fl_b200_decoder_set_layer_tensor(fl_b200_decoder *d, uint32_t layer, int which, int fmt, const void *w) {
+    if (!d || layer >= d->c.n_layer || which < 0 || which > FL_B200_T_DOWN)
+        return set_err(FL_B200_ERR_ARG, "decoder_set_layer_tensor: bad layer / tensor id");
+    if (d->finalized) return set_err(FL_B200_ERR_STATE, "decoder_set_layer_tensor: after finalize");
+    const uint32_t cols = which == FL_B200_T_DOWN ? d->c.n_ff : which == FL_B200_T_WO ? d->c.n_head * d->c.head_dim : d->c.n_embd;
+    if (int rc = check_weight(d, fmt, w, cols)) return rc;
+    d->lw[(size_t)layer * 7 + which] = {fmt, (const uint8_t *)w};
+    return FL_B200_OK;
+}
+
+int fl_b200_decoder_set_layer_norms(fl_b200_decoder *d, uint32_t layer, const float *an, const float *fn) {
+    if (!d || layer >= d->c.n_layer || !an || !fn) return set_err(FL_B200_ERR_ARG, "decoder_set_layer_norms: bad argument");
+    if (d->finalized) return set_err(FL_B200_ERR_STATE, "decoder_set_layer_norms: after finalize");
+    d->attn_norm[layer] = an;
+    d->ffn_norm[layer] = fn;
+    return FL_B200_OK;
+}
+
+int fl_b200_decoder_set_global(fl_b200_decoder *d, int which, int fmt, const void *w) {
+    if (!d || (which != FL_B200_G_TOK_EMBD && which != FL_B200_G_OUTPUT))
+        return set_err(FL_B200_ERR_ARG, "decoder_set_global: bad tensor id");
+    if (d->finalized) return set_err(FL_B200_ERR_STATE, "decoder_set_global: after finalize");
+    if (int rc = check_weight(d, fmt, w, d->c.n_embd)) return rc;
+    (which == FL_B200_G_TOK_EMBD ? d->tok_embd : d->output) = {fmt, (const uint8_t *)w};
+    return FL_B200_OK;
+}
+
+int fl_b200_decoder_set_out_norm(fl_b200_decoder *d, const float *w) {
+    if (!d || !w) return set_err(FL_B200_ERR_ARG, "decoder_set_out_norm: null");
+    d->out_norm = w;
+    return FL_B200_OK;
+}
+
+int fl_b200_decoder_kv(fl_b200_decoder *d, uint32_t layer, uint16_t **k, uint16_t **v) {
+    if (!d || layer >= d->c.n_layer) return set_err(FL_B200_ERR_ARG, "decoder_kv: bad layer");
+    if (k) *k = (uint16_t *)d->kc[layer];
+    if (v) *v = (uint16_t *)d->vc[layer];
+    return FL_B200_OK;
+}
+
+int fl_b200_decoder_finalize(fl_b200_decoder *d) {
+    if (!d) return set_err(FL_B200_ERR_ARG, "decoder_finalize: null");
+    if (d->finalized) return FL_B200_OK;
+    for (size_t i = 0; i < d->lw.size(); ++i)
+        if (!d->lw[i].w) return set_err(FL_B200_ERR_STATE, "decoder_finalize: layer %zu tensor %zu not set", i / 7, i % 7);
+    for (uint32_t l = 0; l < d->c.n_layer; ++l)
+        if (!d->attn_norm[l] || !d->ffn_norm[l]) return set_err(FL_B200_ERR_STATE, "decoder_finalize: norms of layer %u not set", l);
+    if (!d->tok_embd.w || !d->output.w || !d->out_norm) return set_err(FL_B200_ERR_STATE, "decoder_finalize: embedding / head / output norm not set");
+    cudaStream_t s = d->ctx->stream;
+    CK(cudaSetDevice(d->ctx->device));
+    CK(cudaStreamSynchronize(s));
+    CK(cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal));
+    uint32_t n = 0;
+    int rc = enqueue_step(d, s, &n);
+    cudaGraph_t g = nullptr;
+    cudaError_t e = cudaStreamEndCapture(s, &g);
+    if (rc) { if (g) cudaGraphDestroy(g); return rc; }
+    CK(e);
+    d->graph = g;
+    CK(cudaGraphInstantiate(&d->exec, g, 0));
+    CK(cudaGraphUpload(d->exec, s));
+    d->launches = n;
+    d->finalized = true;
+    return FL_B200_OK;
+}
+
+int fl_b200_decoder_set_n_past(fl_b200_decoder *d, int32_t n_past) {
+    if (!d || n_past < 0 || (uint32_t)n_past > d->c.max_kv) return set_err(FL_B200_ERR_ARG, "decoder_set_n_past: out of range");
+    d->n_past = n_past;
+    return FL_B200_OK;
+}
+
+int fl_b200_decoder_n_past(fl_b200_decoder *d, int32_t *out) {
+    if (!d || !out) return set_err(FL_B200_ERR_ARG, "decoder_n_past: null");
+    *out = d->n_past;
+    return FL_B200_OK;
+}
+
+static int check_dev_status(fl_b200_decoder *d) {
+    uint32_t st = 0;
+    if (int rc = fl_b200_device_status(d->ctx, &st)) return rc;
+    if (st != 0) return set_err(FL_B200_ERR_DEVICE, "decoder: a kernel reported status %u (bounded wait gave up)", st);
+    return FL_B200_OK;
+}
+
+int fl_b200_decoder_step(fl_b200_decoder *d, int32_t token, int32_t *next_out) {
+    if (!d || !next_out) return set_err(FL_B200_ERR_ARG, "decoder_step: null");
+    if (!d->finalized) return set_err(FL_B200_ERR_STATE, "decoder_step: finalize first");
+    if ((uint32_t)d->n_past >= d->c.max_kv) return set_err(FL_B200_ERR_STATE, "decoder_step: kv full (%d of %u)", d->n_past, d->c.max_kv);
+    if (token < 0 || (uint32_t)token >= d->c.n_vocab) return set_err(FL_B200_ERR_ARG, "decoder_step: token %d outside the vocabulary", token);
+    cudaStream_t s = d->ctx->stream;
+    d->h_pin[0] = token;
+    d->h_pin[1] = 0;            // next (unused on the way in)
+    d->h_pin[2] = d->n_past;
+    d->h_pin[3] = 0;            // history counter
+    CK(cudaMemcpyAsync(d->d_token, d->h_pin, 16, cudaMemcpyHostToDevice, s));
+    CK(cudaGraphLaunch(d->exec, s));
+    CK(cudaMemcpyAsync(d->h_pin + 8, d->d_next, 4, cudaMemcpyDeviceToHost, s));
+    CK(cudaStreamSynchronize(s));
+    d->n_past += 1;
+    *next_out = d->h_pin[8];
+    return check_dev_status(d);
+}
+
+int fl_b200_decoder_run(fl_b200_decoder *d, int32_t first_token, uint32_t n, int32_t *tokens_host) {
+    if (!d || !tokens_host) return set_err(FL_B200_ERR_ARG, "decoder_run: null");
+    if (!d->finalized) return set_err(FL_B200_ERR_STATE, "decoder_run: finalize first");
+    if (n == 0 || n > d->hist_cap) return set_err(FL_B200_ERR_ARG, "decoder_run: n %u outside 1..%u", n, d->hist_cap);
+    if ((uint64_t)d->n_past + n > d->c.max_kv) return set_err(FL_B200_ERR_STATE, "decoder_run: kv full (%d + %u > %u)", d->n_past, n, d->c.max_kv);
+    if (first_token < 0 || (uint32_t)first_token >= d->c.n_vocab) return set_err(FL_B200_ERR_ARG, "decoder_run: token outside the vocabulary");
+    cudaStream_t s = d->ctx->stream;
+    d->h_pin[0] = first_token;
+    d->h_pin[1] = 0;
+    d->h_pin[2] = d->n_past;
+    d->h_pin[3] = 0;
+    CK(cudaMemcpyAsync(d->d_token, d->h_pin, 16, cudaMemcpyHostToDevice, s));
+    for (uint32_t i = 0; i < n; ++i) CK(cudaGraphLaunch(d->exec, s));
+    CK(cudaMemcpyAsync(tokens_host, d->d_hist, (size_t)n * 4, cudaMemcpyDeviceToHost, s));
+    CK(cudaStreamSynchronize(s));
+    d->n_past += (int32_t)n;
+    return check_dev_status(d);
+}
+
+int fl_b200_decoder_logits(fl_b200_decoder *d, float *out) {
+    if (!d || !out) return set_err(FL_B200_ERR_ARG, "decoder_logits: null");
+    return fl_b200_download(d->ctx, out, d->logits, (size_t)d->c.n_vocab * 4);
+}
+
+int fl_b200_decoder_margin(fl_b200_decoder *d, float *out) {
+    if (!d || !out) return set_err(FL_B200_ERR_ARG, "decoder_margin: null");
+    return fl_b200_download(d->ctx, out, d->d_margin, 4);
+}
+
+int fl_b200_decoder_tap(fl_b200_decoder *d, int which, float *out) {
+    if (!d || !out || which < 0 || which > 1) return set_err(FL_B200_ERR_ARG, "decoder_tap: bad argument");
+    return fl_b200_download(d->ctx, out, which == 0 ? d->xa : d->xn_final, (size_t)d->c.n_embd * 4);
+}
+
+int fl_b200_decoder_launches_per_step(fl_b200_decoder *d, uint32_t *n) {
+    if (!d || !n) return set_err(FL_B200_ERR_ARG, "decoder_launches_per_step: null");
+    if (!d->finalized) return set_err(FL_B200_ERR_STATE, "decoder_launches_per_step: finalize first");
+    *n = d->launches;
+    return FL_B200_OK;
+}
+
+int fl_b200_decoder_bytes_per_step(fl_b200_decoder *d, int32_t pos, uint64_t *wb, uint64_t *kvb) {
+    if (!d || !wb || !kvb) return set_err(FL_B200_ERR_ARG, "decoder_bytes_per_step: null");
+    const fl_b200_llama_cfg &c = d->c;
+    const uint32_t E = c.n_embd, QD = c.n_head * c.head_dim, KD = c.n_kv_head * c.head_dim;
+    uint64_t w = 0;
+    for (uint32_t l = 0; l < c.n_layer; ++l) {
+        const Tensor *t = &d->lw[(size_t)l * 7];
+        w += (uint64_t)QD * row_bytes(t[FL_B200_T_WQ].fmt, E) + (uint64_t)KD * row_bytes(t[FL_B200_T_WK].fmt, E) +
+             (uint64_t)KD * row_bytes(t[FL_B200_T_WV].fmt, E) + (uint64_t)E * row_bytes(t[FL_B200_T_WO].fmt, QD) +
+             (uint64_t)c.n_ff * row_bytes(t[FL_B200_T_GATE].fmt, E) + (uint64_t)c.n_ff * row_bytes(t[FL_B200_T_UP].fmt, E) +
+             (uint64_t)E * row_bytes(t[FL_B200_T_DOWN].fmt, c.n_ff);
+        w += 2ull * E * 4;   // the two norm vectors
+    }
+    w += (uint64_t)c.n_vocab * row_bytes(d->output.fmt, E) + (uint64_t)E * 4;
+    *wb = w;
+    *kvb = (uint64_t)c.n_layer * 2ull * (uint64_t)(pos + 1) * KD * 2ull;
+    return FL_B200_OK;
+}
+
+} // extern "C"

@@ -1,0 +1,190 @@
+// Small decode operators around the matvecs and attention. Each follows one
+// canonical operator of the reference (src/runtime/decode_params.h) and keeps
+// its rounding where that is cheap: separate multiplies / adds via __fmul_rn,
+// __fadd_rn, __fsub_rn, IEEE division and square root.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace flb {
+
+namespace {
+
+// fl_op_rmsnorm, decode_params.h:101-106. The sum of squares is a tree
+// reduction here (the reference sums sequentially); everything after it rounds
+// like the reference: 1/sqrtf(ss/n + eps), then (x*s)*w.
+__global__ void __launch_bounds__(1024) rmsnorm_kernel(const float *__restrict__ x, const float *__restrict__ w,
+                                                       float *__restrict__ y, float eps, uint32_t n) {
+    __shared__ float red[32];
+    __shared__ float inv;
+    float ss = 0.f;
+    for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) ss = fmaf(x[i], x[i], ss);
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31u) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float t = 0.f;
+        for (uint32_t k = 0; k < (blockDim.x + 31) / 32; ++k) t += red[k];
+        inv = 1.0f / sqrtf(__fadd_rn(t / (float)n, eps));
+    }
+    __syncthreads();
+    const float s = inv;
+    for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) y[i] = __fmul_rn(__fmul_rn(x[i], s), w[i]);
+}
+
+// fl_op_add2, decode_params.h:108-110
+__global__ void add2_kernel(const float *__restrict__ a, const float *__restrict__ b, float *__restrict__ y,
+                            uint32_t n) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) y[i] = __fadd_rn(a[i], b[i]);
+}
+
+// fl_op_silu_mul, decode_params.h:267-272: (g / (1 + expf(-g))) * u
+__global__ void silu_mul_kernel(const float *__restrict__ g, const float *__restrict__ u, float *__restrict__ h,
+                                uint32_t n) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) {
+        const float v = g[i];
+        h[i] = __fmul_rn(v / __fadd_rn(1.0f, expf(-v)), u[i]);
+    }
+}
+
+// fl_op_rope_ds2 (decode_params.h:124-160, plain RoPE: adjacent pairs, angle
+// pos * theta_scale^i built by repeated multiplication exactly as the reference
+// does, so the angle is bit-identical; cosf/sinf differ from the host libm by at
+// most a few ulp) followed by the f16 KV append (fl_op_kv_append,
+// decode_params.h:162-175, with the cache kept in f16, head-major).
+__global__ void __launch_bounds__(128) rope_append_kernel(const RopeAppendArgs a) {
+    const uint32_t half = a.head_dim / 2;
+    const uint32_t t = blockIdx.x * blockDim.x + threadIdx.x;
+    const uint32_t n_rot_heads = (a.q ? a.n_q_head : 0) + a.n_kv_head;
+    const uint32_t pos = (uint32_t)*a.pos;
+    if (t < n_rot_heads * half) {
+        const uint32_t h = t / half, i = t % half;
+        float theta = (float)(int32_t)pos;
+        for (uint32_t k = 0; k < i; ++k) theta = __fmul_rn(theta, a.theta_scale);
+        const float c = cosf(theta), s = sinf(theta);
+        const uint32_t nq = a.q ? a.n_q_head : 0;
+        if (h < nq) {
+            float *v = a.q + (size_t)h * a.head_dim + 2 * i;
+            const float x0 = v[0], x1 = v[1];
+            v[0] = __fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s));
+            v[1] = __fadd_rn(__fmul_rn(x0, s), __fmul_rn(x1, c));
+        } else {
+            const uint32_t hk = h - nq;
+            const float *v = a.k + (size_t)hk * a.head_dim + 2 * i;
+            const float x0 = v[0], x1 = v[1];
+            __half *dst = a.kcache + ((size_t)hk * a.kv_stride + pos) * a.head_dim + 2 * i;
+            dst[0] = __float2half_rn(__fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s)));
+            dst[1] = __float2half_rn(__fadd_rn(__fmul_rn(x0, s), __fmul_rn(x1, c)));
+        }
+    } else if (t < (n_rot_heads + a.n_kv_head) * half) {
+        const uint32_t u = t - n_rot_heads * half;
+        const uint32_t hk = u / half, i = u % half;
+        const float *v = a.v + (size_t)hk * a.head_dim + 2 * i;
+        __half *dst = a.vcache + ((size_t)hk * a.kv_stride + pos) * a.head_dim + 2 * i;
+        dst[0] = __float2half_rn(v[0]);
+        dst[1] = __float2half_rn(v[1]);
+    }
+}
+
+// Greedy argmax: strict '>' scan order of the reference (lowest index wins
+// ties) and the runner-up value for the margin (src/model/decoder.cpp:1253-1264).
+struct Top { float b; uint32_t i; float s; };
+
+__device__ __forceinline__ Top top_merge(const Top &x, const Top &y) {
+    const bool y_wins = y.b > x.b || (y.b == x.b && y.i < x.i);
+    Top r;
+    if (y_wins) { r.b = y.b; r.i = y.i; r.s = fmaxf(x.b, fmaxf(x.s, y.s)); }
+    else { r.b = x.b; r.i = x.i; r.s = fmaxf(y.b, fmaxf(x.s, y.s)); }
+    return r;
+}
+__device__ __forceinline__ Top top_warp(Top t) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        Top u;
+        u.b = __shfl_xor_sync(0xffffffffu, t.b, o);
+        u.i = __shfl_xor_sync(0xffffffffu, t.i, o);
+        u.s = __shfl_xor_sync(0xffffffffu, t.s, o);
+        t = top_merge(t, u);
+    }
+    return t;
+}
+
+__global__ void __launch_bounds__(256) argmax_kernel(const float *__restrict__ lg, uint32_t n, int32_t *out_idx,
+                                                     float *out_margin, float *scratch, uint32_t *ticket) {
+    __shared__ Top wtop[8];
+    __shared__ uint32_t last;
+    Top t{-INFINITY, 0xFFFFFFFFu, -INFINITY};
+    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+        const float v = lg[i];
+        if (v > t.b) { t.s = t.b; t.b = v; t.i = i; }   // indices ascend within a thread
+        else if (v > t.s) t.s = v;
+    }
+    t = top_warp(t);
+    if ((threadIdx.x & 31u) == 0) wtop[threadIdx.x >> 5] = t;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        Top r = wtop[0];
+        for (int w = 1; w < 8; ++w) r = top_merge(r, wtop[w]);
+        float *slot = scratch + 3 * blockIdx.x;
+        slot[0] = r.b; slot[1] = __uint_as_float(r.i); slot[2] = r.s;
+        __threadfence();
+        last = atomicAdd(ticket, 1u) == gridDim.x - 1 ? 1u : 0u;
+    }
+    __syncthreads();
+    if (!last) return;
+    __threadfence();
+    if (threadIdx.x < 32) {
+        Top r{-INFINITY, 0xFFFFFFFFu, -INFINITY};
+        for (uint32_t k = threadIdx.x; k < gridDim.x; k += 32) {
+            Top u;
+            u.b = __ldcg(scratch + 3 * k);
+            u.i = __float_as_uint(__ldcg(scratch + 3 * k + 1));
+            u.s = __ldcg(scratch + 3 * k + 2);
+            r = top_merge(r, u);
+        }
+        r = top_warp(r);
+        if (threadIdx.x == 0) {
+            *out_idx = (int32_t)r.i;
+            *out_margin = r.b - r.s;
+            *ticket = 0;
+        }
+    }
+}
+
+} // namespace
+
+cudaError_t launch_rmsnorm(const float *x, const float *wnorm, float *y, float eps, uint32_t n,
+                           cudaStream_t stream) {
+    rmsnorm_kernel<<<1, 1024, 0, stream>>>(x, wnorm, y, eps, n);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_add2(const float *a, const float *b, float *y, uint32_t n, cudaStream_t stream) {
+    add2_kernel<<<(n + 255) / 256, 256, 0, stream>>>(a, b, y, n);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_silu_mul(const float *gate, const float *up, float *h, uint32_t n, cudaStream_t stream) {
+    silu_mul_kernel<<<(n + 255) / 256, 256, 0, stream>>>(gate, up, h, n);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_rope_append(const RopeAppendArgs &a, cudaStream_t stream) {
+    if (a.head_dim == 0 || (a.head_dim & 1u)) return cudaErrorInvalidValue;
+    const uint32_t half = a.head_dim / 2;
+    const uint32_t n = ((a.q ? a.n_q_head : 0) + 2 * a.n_kv_head) * half;
+    rope_append_kernel<<<(n + 127) / 128, 128, 0, stream>>>(a);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_argmax(const float *logits, uint32_t n, int32_t *out_idx, float *out_margin,
+                          float *scratch, uint32_t *ticket, int sms, cudaStream_t stream) {
+    uint32_t grid = (n + 255) / 256;
+    if (grid > (uint32_t)sms) grid = (uint32_t)sms;
+    if (grid == 0) return cudaErrorInvalidValue;
+    argmax_kernel<<<grid, 256, 0, stream>>>(logits, n, out_idx, out_margin, scratch, ticket);
+    return cudaGetLastError();
+}
+
+} // namespace flb

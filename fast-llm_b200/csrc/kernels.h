@@ -1,0 +1,100 @@
+// Internal launch interface between the C ABI (capi.cu), the decoder
+// (decoder.cu) and the kernel translation units.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace flb {
+
+// ---- dequant.cu ---------------------------------------------------------
+cudaError_t launch_dequant(int fmt, const void *w, uint64_t rows, uint32_t cols, float *out, int sms,
+                           cudaStream_t stream);
+
+// ---- matvec.cu ----------------------------------------------------------
+// One weight tensor of a (possibly multi-tensor) matvec launch. All tensors of
+// a launch share the activation vector and the column count.
+struct MatvecTensor {
+    const uint8_t *w;     // packed rows, GGUF block layout, 16-byte aligned
+    float *y;             // rows outputs
+    const float *resid;   // optional: y[r] = resid[r] + dot   (nullptr: none)
+    uint32_t rows;
+    int fmt;
+};
+
+enum : int {
+    MV_X_PLAIN = 0,    // activation = x
+    MV_X_RMSNORM = 1,  // activation = x * rsqrt(mean(x^2)+eps) * wnorm
+    MV_X_SILU_MUL = 2, // activation = silu(x) * x2
+};
+
+struct MatvecArgs {
+    MatvecTensor t[4];
+    int n_tensors;
+    const float *x;
+    const float *x2;      // MV_X_SILU_MUL: the "up" vector
+    const float *wnorm;   // MV_X_RMSNORM
+    float eps;
+    uint32_t cols;
+    int x_mode;
+    int accumulate;       // 1: y[r] += dot (STREAM_DOT semantics); 0: y[r] = dot (+ resid)
+    uint32_t *status;     // device status word
+    float *xn_out;        // optional: CTA 0 also writes the activation it built (nullptr: no)
+};
+
+// Streaming kernel (Q4_K / Q6_K, cols a multiple of 2048) or the generic
+// kernel (every other supported shape). Returns cudaErrorInvalidValue for
+// unsupported arguments.
+cudaError_t launch_matvec(const MatvecArgs &a, int sms, cudaStream_t stream);
+// True when launch_matvec would take the streaming kernel for this shape.
+bool matvec_is_streaming(int fmt, uint32_t cols);
+// Dynamic shared memory the streaming kernel needs for (cols, formats used).
+size_t matvec_smem_bytes(uint32_t cols, bool use_q4k, bool use_q6k, int *stages_out);
+cudaError_t matvec_init(void);   // sets the dynamic shared memory attribute once
+
+// ---- attn.cu ------------------------------------------------------------
+struct AttnArgs {
+    const float *q;        // [batch][n_q_head][128] f32 (post-RoPE unless rope fused)
+    const __half *k;       // [batch][n_kv_head][kv_stride][128] f16
+    const __half *v;       // same layout
+    float *out;            // [batch][n_q_head][128]
+    float *part;           // scratch: [batch][n_q_head][n_splits][130]
+    uint32_t *tickets;     // scratch: [batch][n_kv_head], zero before first use; self-resetting
+    const int32_t *pos;    // device scalar: last valid position (kv_len = *pos + 1); nullptr -> kv_len
+    uint32_t kv_len;       // used when pos == nullptr
+    uint32_t kv_stride;    // positions allocated per head
+    uint64_t batch_stride; // elements between sequences in k / v
+    uint32_t n_q_head, n_kv_head, batch, n_splits;
+    float scale;
+    uint32_t *status;
+};
+cudaError_t launch_attn_decode(const AttnArgs &a, cudaStream_t stream);
+cudaError_t attn_init(void);
+uint32_t attn_pick_splits(uint32_t n_kv_head, uint32_t batch, uint32_t kv_len, int sms);
+size_t attn_part_floats(uint32_t n_q_head, uint32_t batch, uint32_t n_splits);
+
+// ---- glue.cu ------------------------------------------------------------
+cudaError_t launch_rmsnorm(const float *x, const float *wnorm, float *y, float eps, uint32_t n,
+                           cudaStream_t stream);
+cudaError_t launch_add2(const float *a, const float *b, float *y, uint32_t n, cudaStream_t stream);
+cudaError_t launch_silu_mul(const float *gate, const float *up, float *h, uint32_t n, cudaStream_t stream);
+// RoPE (adjacent pairs) on q in place and on k, then store k and v as f16 at
+// row *pos of a cache laid out [n_kv_head][kv_stride][head_dim].
+struct RopeAppendArgs {
+    float *q;              // [n_q_head][head_dim], rotated in place (nullptr: skip)
+    const float *k;        // [n_kv_head][head_dim] (pre-RoPE)
+    const float *v;        // [n_kv_head][head_dim]
+    __half *kcache, *vcache;
+    const int32_t *pos;
+    uint32_t n_q_head, n_kv_head, head_dim, kv_stride;
+    float theta_scale;     // freq_base^(-2/head_dim), computed on the host
+};
+cudaError_t launch_rope_append(const RopeAppendArgs &a, cudaStream_t stream);
+// Greedy argmax with the reference's tie rule (lowest index) and the
+// top1 - top2 margin. out_idx: int32, out_margin: float; scratch: 2*blocks*2 floats.
+cudaError_t launch_argmax(const float *logits, uint32_t n, int32_t *out_idx, float *out_margin,
+                          float *scratch, uint32_t *ticket, int sms, cudaStream_t stream);
+// Embedding row gather + dequant: out[0..cols) = dequant(table row *token).
+cudaError_t launch_embed(int fmt, const void *table, const int32_t *token, uint32_t cols, float *out,
+                         cudaStream_t stream);
+
+} // namespace flb

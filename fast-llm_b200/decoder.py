@@ -1,0 +1,107 @@
+"""Host-side mirror of the reference's ``Decoder`` interface
+(src/model/decoder.h:52-81) for the Llama shape, over the C ABI decoder
+(``fl_b200_decoder_*``): ``step``, ``n_past``, ``rewind_to``, ``logits``,
+``last_margin``. All arithmetic happens in the CUDA library."""
+import ctypes as C
+
+import numpy as np
+
+from . import capi
+
+
+class Decoder:
+    def __init__(self, ctx, cfg):
+        """cfg: dict with n_layer, n_embd, n_head, n_kv_head, head_dim, n_ff,
+        n_vocab, max_kv, rope_base, eps."""
+        self.ctx = ctx
+        self.lib = ctx.lib
+        self.cfg = dict(cfg)
+        c = capi.LlamaCfg(**{k: cfg[k] for k in ("n_layer", "n_embd", "n_head", "n_kv_head", "head_dim",
+                                                  "n_ff", "n_vocab", "max_kv", "rope_base", "eps")})
+        self._h = C.c_void_p()
+        capi._ck(self.lib.fl_b200_decoder_create(ctx._h, C.byref(c), C.byref(self._h)))
+        self._keep = []   # device tensors the decoder points into
+
+    def close(self):
+        if self._h:
+            self.lib.fl_b200_decoder_destroy(self._h)
+            self._h = C.c_void_p()
+            self._keep = []
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # -- model set-up --
+    def set_layer_tensor(self, layer, which, fmt, w):
+        self._keep.append(w)
+        capi._ck(self.lib.fl_b200_decoder_set_layer_tensor(self._h, C.c_uint32(layer), which, fmt, capi._p(w)))
+
+    def set_layer_norms(self, layer, attn_norm, ffn_norm):
+        self._keep += [attn_norm, ffn_norm]
+        capi._ck(self.lib.fl_b200_decoder_set_layer_norms(self._h, C.c_uint32(layer), capi._p(attn_norm),
+                                                          capi._p(ffn_norm)))
+
+    def set_global(self, which, fmt, w):
+        self._keep.append(w)
+        capi._ck(self.lib.fl_b200_decoder_set_global(self._h, which, fmt, capi._p(w)))
+
+    def set_out_norm(self, w):
+        self._keep.append(w)
+        capi._ck(self.lib.fl_b200_decoder_set_out_norm(self._h, capi._p(w)))
+
+    def kv_ptrs(self, layer):
+        k, v = C.c_void_p(), C.c_void_p()
+        capi._ck(self.lib.fl_b200_decoder_kv(self._h, C.c_uint32(layer), C.byref(k), C.byref(v)))
+        return k.value, v.value
+
+    def finalize(self):
+        capi._ck(self.lib.fl_b200_decoder_finalize(self._h))
+
+    # -- Decoder interface --
+    def step(self, token):
+        out = C.c_int32()
+        capi._ck(self.lib.fl_b200_decoder_step(self._h, C.c_int32(int(token)), C.byref(out)))
+        return out.value
+
+    def run(self, first_token, n):
+        """n greedy steps with the argmax fed back on the device."""
+        toks = np.zeros(n, dtype=np.int32)
+        capi._ck(self.lib.fl_b200_decoder_run(self._h, C.c_int32(int(first_token)), C.c_uint32(n),
+                                              C.c_void_p(toks.ctypes.data)))
+        return toks
+
+    def n_past(self):
+        v = C.c_int32()
+        capi._ck(self.lib.fl_b200_decoder_n_past(self._h, C.byref(v)))
+        return v.value
+
+    def rewind_to(self, pos):
+        capi._ck(self.lib.fl_b200_decoder_set_n_past(self._h, C.c_int32(int(pos))))
+
+    def logits(self):
+        out = np.empty(self.cfg["n_vocab"], dtype=np.float32)
+        capi._ck(self.lib.fl_b200_decoder_logits(self._h, C.c_void_p(out.ctypes.data)))
+        return out
+
+    def last_margin(self):
+        v = C.c_float()
+        capi._ck(self.lib.fl_b200_decoder_margin(self._h, C.byref(v)))
+        return v.value
+
+    def tap(self, which):
+        out = np.empty(self.cfg["n_embd"], dtype=np.float32)
+        capi._ck(self.lib.fl_b200_decoder_tap(self._h, which, C.c_void_p(out.ctypes.data)))
+        return out
+
+    def launches_per_step(self):
+        v = C.c_uint32()
+        capi._ck(self.lib.fl_b200_decoder_launches_per_step(self._h, C.byref(v)))
+        return v.value
+
+    def bytes_per_step(self, pos):
+        w, kv = C.c_uint64(), C.c_uint64()
+        capi._ck(self.lib.fl_b200_decoder_bytes_per_step(self._h, C.c_int32(int(pos)), C.byref(w), C.byref(kv)))
+        return w.value, kv.value

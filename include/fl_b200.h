@@ -1,0 +1,240 @@
+/* fl_b200 — C ABI of the B200 (sm_100a) decode hot path.
+ *
+ * Drop-in boundary for the CUDA execution backend of the reference runtime:
+ * what its task executor calls per task (exec_task_block,
+ * src/runtime/gpu_exec.cu:64-140), what its decoder does per token
+ * (Decoder::step / step_batch, src/model/decoder.h:52-81,
+ * src/model/decoder.cpp:1176-1301) and the device bring-up it performs
+ * (gpu_make_stream / gpu_start / gpu_stop_sync,
+ * src/runtime/runtime_internal.h:288-301) are exported here as plain C
+ * functions over plain pointers and sizes.
+ *
+ * Conventions
+ *   - Every function returns 0 on success and a non-zero code on failure;
+ *     fl_b200_last_error() then returns a message for the calling thread. The
+ *     reference prints and abort()s at the same places (FL_CUCHECK,
+ *     src/runtime/gpu_exec.cu:15-17; graph die, src/runtime/graph.cpp:100-103);
+ *     a C++ wrapper that wants that behaviour aborts on non-zero.
+ *   - Pointers named *_dev are device pointers valid on the context's device;
+ *     *_host are host pointers. The caller owns every buffer.
+ *   - All work is enqueued on the context's stream, in call order. Functions
+ *     with "_host" in the name copy in, run and copy out, and return after the
+ *     result is in host memory; the others return without synchronising.
+ *   - One context = one device = one stream; calls on a context are serialised
+ *     by the caller (as Runtime::run, include/fastllm/fastllm.h:226-229).
+ *   - There is no CPU fallback: without a CUDA device fl_b200_create fails.
+ */
+#ifndef FL_B200_H
+#define FL_B200_H
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FL_B200_ABI_VERSION 1
+
+/* Weight formats: numeric values of fastllm::Fmt
+ * (include/fastllm/fastllm.h:56-57). */
+enum { FL_B200_F32 = 0, FL_B200_Q8_0 = 1, FL_B200_Q5_0 = 2, FL_B200_Q4_K = 3, FL_B200_Q6_K = 4 };
+
+/* Error codes. */
+enum {
+    FL_B200_OK = 0,
+    FL_B200_ERR_ARG = 1,      /* rejected at the boundary (shape, alignment, null) */
+    FL_B200_ERR_CUDA = 2,     /* a CUDA runtime call failed */
+    FL_B200_ERR_DEVICE = 3,   /* a kernel reported a status (bounded wait gave up) */
+    FL_B200_ERR_STATE = 4     /* call order (e.g. step before finalize) */
+};
+
+typedef struct fl_b200_ctx fl_b200_ctx;
+typedef struct fl_b200_decoder fl_b200_decoder;
+
+int fl_b200_abi_version(void);
+const char *fl_b200_last_error(void);
+
+/* ---- context: replaces gpu_make_stream / gpu_start / gpu_stop_sync
+ *      (src/runtime/gpu_exec.cu:384-502). No persistent kernel is started. ---- */
+int fl_b200_create(int device, fl_b200_ctx **out);
+void fl_b200_destroy(fl_b200_ctx *ctx);
+int fl_b200_sync(fl_b200_ctx *ctx);
+/* Reads and clears the device status word (0 = no kernel reported a problem). */
+int fl_b200_device_status(fl_b200_ctx *ctx, uint32_t *status_out);
+int fl_b200_sm_count(fl_b200_ctx *ctx);
+/* cudaStream_t of the context, for callers that enqueue their own work. */
+void *fl_b200_stream(fl_b200_ctx *ctx);
+
+/* Device memory for callers without a CUDA runtime of their own (replaces the
+ * unified-memory Arena, src/runtime/arena.cpp:54-74, for the GPU side). */
+int fl_b200_malloc(fl_b200_ctx *ctx, size_t bytes, void **dev_out);
+int fl_b200_free(fl_b200_ctx *ctx, void *dev);
+int fl_b200_upload(fl_b200_ctx *ctx, void *dst_dev, const void *src_host, size_t bytes);
+int fl_b200_download(fl_b200_ctx *ctx, void *dst_host, const void *src_dev, size_t bytes);
+int fl_b200_memset(fl_b200_ctx *ctx, void *dst_dev, int value, size_t bytes);
+
+/* CUDA-event stopwatch on the context's stream. */
+int fl_b200_timer_start(fl_b200_ctx *ctx);
+int fl_b200_timer_stop(fl_b200_ctx *ctx, float *ms_out);   /* synchronises */
+
+/* ---- single operators (device pointers) ---- */
+
+/* Bulk dequantise rows x cols packed weights to f32, bit-exact with
+ * dequant_chunk (src/runtime/kernels.h:162-242). */
+int fl_b200_dequant(fl_b200_ctx *ctx, int fmt, const void *w_dev, uint64_t rows, uint32_t cols,
+                    float *out_dev);
+
+/* STREAM_DOT (exec_task_scalar, src/runtime/runtime_internal.h:240-257):
+ *   y[p*ystride + r] += dot(W[r], x + p*xstride), r < rows, p < nx.
+ * Accumulates into y like the reference (its slots are zeroed per run,
+ * src/model/decoder.cpp:1206-1208). w_dev must be 16-byte aligned. */
+int fl_b200_matvec(fl_b200_ctx *ctx, int fmt, const void *w_dev, uint32_t rows, uint32_t cols,
+                   const float *x_dev, uint32_t nx, uint32_t xstride, float *y_dev, uint32_t ystride);
+/* Same with y = dot (no read of y). */
+int fl_b200_matvec_assign(fl_b200_ctx *ctx, int fmt, const void *w_dev, uint32_t rows, uint32_t cols,
+                          const float *x_dev, float *y_dev);
+/* End-to-end form: x and y in host memory (y_host receives W x). */
+int fl_b200_matvec_host(fl_b200_ctx *ctx, int fmt, const void *w_dev, uint32_t rows, uint32_t cols,
+                        const float *x_host, float *y_host);
+
+/* Decode attention for all query heads (fl_op_attn_head applied per head,
+ * src/runtime/decode_params.h:183-232, extended to grouped-query heads and an
+ * f16 cache). q, out: [batch][n_q_head][head_dim] f32; k, v:
+ * [batch][n_kv_head][kv_stride][head_dim] f16; keys 0..kv_len-1 are attended.
+ * head_dim must be 128 and n_q_head == 4 * n_kv_head. */
+int fl_b200_attn_decode(fl_b200_ctx *ctx, const float *q_dev, const uint16_t *k_dev, const uint16_t *v_dev,
+                        uint32_t n_q_head, uint32_t n_kv_head, uint32_t head_dim, uint32_t kv_len,
+                        uint32_t kv_stride, uint32_t batch, float scale, float *out_dev);
+int fl_b200_attn_decode_host(fl_b200_ctx *ctx, const float *q_host, const uint16_t *k_dev,
+                             const uint16_t *v_dev, uint32_t n_q_head, uint32_t n_kv_head, uint32_t head_dim,
+                             uint32_t kv_len, uint32_t kv_stride, uint32_t batch, float scale,
+                             float *out_host);
+
+/* fl_op_rmsnorm / fl_op_add2 / fl_op_silu_mul (decode_params.h:101-110, :267-272) */
+int fl_b200_rmsnorm(fl_b200_ctx *ctx, const float *x_dev, const float *wnorm_dev, float *y_dev, float eps,
+                    uint32_t n);
+int fl_b200_add2(fl_b200_ctx *ctx, const float *a_dev, const float *b_dev, float *y_dev, uint32_t n);
+int fl_b200_silu_mul(fl_b200_ctx *ctx, const float *gate_dev, const float *up_dev, float *h_dev, uint32_t n);
+/* fl_op_rope_ds2 (plain RoPE, adjacent pairs, decode_params.h:124-160) on q in
+ * place and on k, then fl_op_kv_append (decode_params.h:162-175) of k and v
+ * into an f16 cache [n_kv_head][kv_stride][head_dim] at row *pos_dev. */
+int fl_b200_rope_kv_append(fl_b200_ctx *ctx, float *q_dev, const float *k_dev, const float *v_dev,
+                           uint16_t *kcache_dev, uint16_t *vcache_dev, const int32_t *pos_dev,
+                           uint32_t n_q_head, uint32_t n_kv_head, uint32_t head_dim, uint32_t kv_stride,
+                           float freq_base);
+/* Greedy argmax, lowest index on ties, and top1 - top2 margin
+ * (src/model/decoder.cpp:1253-1264). */
+int fl_b200_argmax(fl_b200_ctx *ctx, const float *logits_dev, uint32_t n, int32_t *idx_dev,
+                   float *margin_dev);
+
+/* ---- task-level entry: one reference Task on the device ------------------
+ * Field-for-field image of fastllm::Task (include/fastllm/fastllm.h:65-97);
+ * oracle/abi_check.cpp asserts the offsets against the reference header. All
+ * pointers inside (and inside the aux parameter block) must be device
+ * pointers. Kinds 0..12 keep the reference's numbers; 13 and 14 are appended
+ * for the shapes the reference cannot express (grouped-query heads, f16
+ * cache). */
+enum {
+    FL_B200_STREAM_DOT = 0, FL_B200_MERGE = 1, FL_B200_SIGNAL = 2, FL_B200_ACT_Q8 = 3,
+    FL_B200_STREAM_DOT_IDX = 4, FL_B200_RMSNORM = 5, FL_B200_ADD2 = 6, FL_B200_ROPE_DS2 = 7,
+    FL_B200_KV_APPEND = 8, FL_B200_ATTN_HEAD = 9, FL_B200_ROUTER_SEL = 10, FL_B200_SILU_MUL = 11,
+    FL_B200_WMERGE = 12,
+    FL_B200_ATTN_GQA_F16 = 13, FL_B200_ROPE_KV_APPEND_F16 = 14
+};
+
+typedef struct
+#if defined(__GNUC__)
+    __attribute__((aligned(128)))
+#endif
+    fl_b200_task {
+    uint32_t id;
+    uint8_t kind, affinity, fmt;
+    uint16_t n_consumers;
+    uint32_t consumers[6];
+    const void *w;
+    uint64_t w_bytes;
+    const void *x;
+    void *y;
+    uint32_t rows, cols;
+    int32_t dep_init, dep_count;
+    uint32_t epoch;
+    uint64_t handoff_ts;
+    const void *aux;
+    uint64_t aux2;
+    uint32_t nx, xstride, ystride;
+} fl_b200_task;
+
+/* Parameter blocks of the reference operators (src/runtime/decode_params.h:23-97),
+ * same field order, so a block built for the reference can be passed as is
+ * once its pointers are device pointers. */
+typedef struct { const float *wnorm, *x; float *y; float eps; uint32_t n; } fl_b200_rmsnorm_p;
+typedef struct { const float *a, *b; float *y; uint32_t n; } fl_b200_add2_p;
+typedef struct { const float *gate, *up; float *h; uint32_t n; } fl_b200_silu_mul_p;
+/* Appended kinds. */
+typedef struct {
+    const float *q; const uint16_t *kcache, *vcache; float *out; const int32_t *pos;
+    float scale; uint32_t n_q_head, n_kv_head, head_dim, kv_stride;
+} fl_b200_attn_gqa_f16_p;
+typedef struct {
+    float *q; const float *k, *v; uint16_t *kcache, *vcache; const int32_t *pos;
+    uint32_t n_q_head, n_kv_head, head_dim, kv_stride; float freq_base;
+} fl_b200_rope_kv_append_f16_p;
+
+/* Executes one task (what exec_task_block does for the whole block,
+ * src/runtime/gpu_exec.cu:64-140). SIGNAL is a no-op. Kinds without a device
+ * implementation here (MERGE, ACT_Q8, STREAM_DOT_IDX, ROPE_DS2, KV_APPEND,
+ * ATTN_HEAD, ROUTER_SEL, WMERGE) return FL_B200_ERR_ARG. */
+int fl_b200_exec_task(fl_b200_ctx *ctx, const fl_b200_task *task);
+
+/* ---- Llama-shape greedy decoder: Decoder::step for the GQA / f16-cache
+ *      shape (src/model/decoder.h:52-81). ---- */
+typedef struct {
+    uint32_t n_layer, n_embd, n_head, n_kv_head, head_dim, n_ff, n_vocab, max_kv;
+    float rope_base, eps;
+} fl_b200_llama_cfg;
+
+enum { FL_B200_T_WQ = 0, FL_B200_T_WK, FL_B200_T_WV, FL_B200_T_WO, FL_B200_T_GATE, FL_B200_T_UP,
+       FL_B200_T_DOWN };
+enum { FL_B200_G_TOK_EMBD = 0, FL_B200_G_OUTPUT = 1 };
+
+int fl_b200_decoder_create(fl_b200_ctx *ctx, const fl_b200_llama_cfg *cfg, fl_b200_decoder **out);
+void fl_b200_decoder_destroy(fl_b200_decoder *dec);
+/* Weights stay where the caller put them (device memory, GGUF block layout,
+ * 16-byte aligned); the decoder keeps the pointers. */
+int fl_b200_decoder_set_layer_tensor(fl_b200_decoder *dec, uint32_t layer, int which, int fmt,
+                                     const void *w_dev);
+int fl_b200_decoder_set_layer_norms(fl_b200_decoder *dec, uint32_t layer, const float *attn_norm_dev,
+                                    const float *ffn_norm_dev);
+int fl_b200_decoder_set_global(fl_b200_decoder *dec, int which, int fmt, const void *w_dev);
+int fl_b200_decoder_set_out_norm(fl_b200_decoder *dec, const float *w_dev);
+/* The decoder owns the KV cache: per layer K and V, each
+ * [n_kv_head][max_kv][head_dim] f16. Returns the device pointers so a caller
+ * can prefill it. */
+int fl_b200_decoder_kv(fl_b200_decoder *dec, uint32_t layer, uint16_t **k_dev_out, uint16_t **v_dev_out);
+/* Freezes the configuration and records the per-token launch sequence as a
+ * CUDA graph (the counterpart of Graph::freeze, src/runtime/graph.cpp:48-93). */
+int fl_b200_decoder_finalize(fl_b200_decoder *dec);
+int fl_b200_decoder_set_n_past(fl_b200_decoder *dec, int32_t n_past);   /* rewind_to */
+int fl_b200_decoder_n_past(fl_b200_decoder *dec, int32_t *n_past_out);
+/* Feed one token at position n_past; returns the greedy next token. The token
+ * goes host -> device and the result device -> host inside the call. */
+int fl_b200_decoder_step(fl_b200_decoder *dec, int32_t token, int32_t *next_out);
+/* Runs `n` steps feeding each step's argmax back on the device (no host round
+ * trip between steps); writes the n produced tokens to tokens_host. */
+int fl_b200_decoder_run(fl_b200_decoder *dec, int32_t first_token, uint32_t n, int32_t *tokens_host);
+/* After a step: logits (n_vocab floats) and the top1 - top2 margin. */
+int fl_b200_decoder_logits(fl_b200_decoder *dec, float *logits_host);
+int fl_b200_decoder_margin(fl_b200_decoder *dec, float *margin_out);
+/* Device pointers of activations of the last step, for layer-level parity:
+ * which = 0 hidden state after the last layer, 1 final normed vector. */
+int fl_b200_decoder_tap(fl_b200_decoder *dec, int which, float *host_out);
+/* Number of kernels this library launches per decoder step. */
+int fl_b200_decoder_launches_per_step(fl_b200_decoder *dec, uint32_t *n_out);
+/* Weight + KV bytes one step at position `pos` must read (the roofline numerator). */
+int fl_b200_decoder_bytes_per_step(fl_b200_decoder *dec, int32_t pos, uint64_t *weight_bytes,
+                                   uint64_t *kv_bytes);
+
+#ifdef __cplusplus
+}
+#endif
+#endif
