@@ -34,7 +34,7 @@ constexpr int kTile = 64;            // positions per stage
 constexpr int kStages = 3;
 constexpr int kAttnThreads = 128;
 constexpr uint32_t kTileBytes = kTile * kD * 2;   // 16 KB
-constexpr int kPartStride = kD + 2;  // m, l, o[128]
+constexpr int kPartStride = kD + 4;  // o[128], m, l, pad (keeps o 16-byte aligned)
 
 struct AttnSmem {
     __half k[kStages][kTile][kD];
@@ -204,9 +204,9 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnArg
             float t = 0.f;
 #pragma unroll
             for (int g = 0; g < 8; ++g) t += red[(g * kGroup + h) * kD + d];
-            part[2 + d] = t;
+            part[d] = t;
         }
-        if (lane == 0) { part[0] = m_run; part[1] = l_run; }
+        if (lane == 0) { part[kD] = m_run; part[kD + 1] = l_run; }
     }
     __threadfence();
     __syncthreads();
@@ -218,27 +218,40 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnArg
     if (!sm.is_last) return;
     __threadfence();
 
-    // ---- combine: warp h <-> head h, splits in ascending order ----
+    // ---- combine: warp h <-> head h. Lane s owns the weights of splits s and
+    // s + 32; the context is summed over splits in ascending order, each lane
+    // holding 4 dims, with the loads of 8 splits in flight. ----
     {
         const uint32_t h = warp;
         const uint64_t hq = (uint64_t)b * a.n_q_head + (uint64_t)hkv * group + h;
         const float *part = a.part + hq * a.n_splits * kPartStride;
-        float mx = -INFINITY;
-        for (uint32_t s = 0; s < a.n_splits; ++s) mx = fmaxf(mx, __ldcg(part + (uint64_t)s * kPartStride));
-        float L = 0.f, acc[kD / 32] = {0.f, 0.f, 0.f, 0.f};
-        for (uint32_t s = 0; s < a.n_splits; ++s) {
-            const float *ps = part + (uint64_t)s * kPartStride;
-            const float ms = __ldcg(ps);
-            if (ms == -INFINITY) continue;   // empty split
-            const float w = expf(ms - mx);
-            L += __ldcg(ps + 1) * w;
+        const uint32_t S = a.n_splits;
+        const float m0 = lane < S ? __ldcg(part + (uint64_t)lane * kPartStride + kD) : -INFINITY;
+        const float m1 = lane + 32 < S ? __ldcg(part + (uint64_t)(lane + 32) * kPartStride + kD) : -INFINITY;
+        const float l0 = lane < S ? __ldcg(part + (uint64_t)lane * kPartStride + kD + 1) : 0.f;
+        const float l1 = lane + 32 < S ? __ldcg(part + (uint64_t)(lane + 32) * kPartStride + kD + 1) : 0.f;
+        const float mx = warp_max(fmaxf(m0, m1));
+        const float w0 = m0 == -INFINITY ? 0.f : expf(m0 - mx);
+        const float w1 = m1 == -INFINITY ? 0.f : expf(m1 - mx);
+        const float L = warp_sum(l0 * w0 + l1 * w1);
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (uint32_t s0 = 0; s0 < S; s0 += 8) {
+            float4 o[8];
 #pragma unroll
-            for (int k = 0; k < kD / 32; ++k) acc[k] = fmaf(__ldcg(ps + 2 + lane + 32 * k), w, acc[k]);
+            for (int j = 0; j < 8; ++j)
+                o[j] = s0 + j < S ? __ldcg(reinterpret_cast<const float4 *>(part + (uint64_t)(s0 + j) * kPartStride) + lane)
+                                  : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const uint32_t s = s0 + j;
+                const float w = __shfl_sync(0xffffffffu, s < 32 ? w0 : w1, s & 31u);
+                acc.x = fmaf(o[j].x, w, acc.x); acc.y = fmaf(o[j].y, w, acc.y);
+                acc.z = fmaf(o[j].z, w, acc.z); acc.w = fmaf(o[j].w, w, acc.w);
+            }
         }
         const float inv = 1.0f / L;
-        float *out = a.out + hq * kD;
-#pragma unroll
-        for (int k = 0; k < kD / 32; ++k) out[lane + 32 * k] = acc[k] * inv;
+        acc.x *= inv; acc.y *= inv; acc.z *= inv; acc.w *= inv;
+        reinterpret_cast<float4 *>(a.out + hq * kD)[lane] = acc;
     }
     if (tid == 0) a.tickets[b * a.n_kv_head + hkv] = 0;   // ready for the next launch
 }
@@ -254,7 +267,7 @@ uint32_t attn_pick_splits(uint32_t n_kv_head, uint32_t batch, uint32_t kv_len, i
     const uint32_t heads = n_kv_head * batch;
     uint32_t s = (2u * (uint32_t)sms + heads - 1) / heads;   // two resident CTAs per SM
     if (s > tiles) s = tiles;
-    if (s > 64) s = 64;
+    if (s > 64) s = 64;   // the combine gives each lane two splits
     if (s < 1) s = 1;
     return s;
 }

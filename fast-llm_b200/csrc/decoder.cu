@@ -68,12 +68,15 @@ struct fl_b200_decoder {
     bool finalized = false;
 };
 
-static int enqueue_step(fl_b200_decoder *d, cudaStream_t s, uint32_t *n_launch) {
+// Kernel classes, for timing one class of the step in isolation.
+enum : uint32_t { K_MATVEC = 1u, K_ATTN = 2u, K_OTHER = 4u, K_ALL = 7u };
+
+static int enqueue_step(fl_b200_decoder *d, cudaStream_t s, uint32_t *n_launch, uint32_t mask = K_ALL) {
     const fl_b200_llama_cfg &c = d->c;
     fl_b200_ctx *ctx = d->ctx;
     const uint32_t E = c.n_embd, D = c.head_dim, QD = c.n_head * D, KD = c.n_kv_head * D;
     uint32_t n = 0;
-    CK(launch_embed(d->tok_embd.fmt, d->tok_embd.w, d->d_token, E, d->xa, s)); ++n;
+    if (mask & K_OTHER) { CK(launch_embed(d->tok_embd.fmt, d->tok_embd.w, d->d_token, E, d->xa, s)); ++n; }
     for (uint32_t l = 0; l < c.n_layer; ++l) {
         const Tensor *w = &d->lw[(size_t)l * 7];
         {   // RMSNorm + Q/K/V
@@ -84,14 +87,14 @@ static int enqueue_step(fl_b200_decoder *d, cudaStream_t s, uint32_t *n_launch) 
             a.t[2] = {w[FL_B200_T_WV].w, d->v, nullptr, KD, w[FL_B200_T_WV].fmt};
             a.x = d->xa; a.wnorm = d->attn_norm[l]; a.eps = c.eps; a.cols = E;
             a.x_mode = MV_X_RMSNORM; a.status = ctx->status;
-            CK(launch_matvec(a, ctx->sms, s)); ++n;
+            if (mask & K_MATVEC) { CK(launch_matvec(a, ctx->sms, s)); ++n; }
         }
         {
             RopeAppendArgs a{};
             a.q = d->q; a.k = d->k; a.v = d->v; a.kcache = d->kc[l]; a.vcache = d->vc[l]; a.pos = d->d_pos;
             a.n_q_head = c.n_head; a.n_kv_head = c.n_kv_head; a.head_dim = D; a.kv_stride = c.max_kv;
             a.theta_scale = powf(c.rope_base, -2.0f / (float)D);
-            CK(launch_rope_append(a, s)); ++n;
+            if (mask & K_OTHER) { CK(launch_rope_append(a, s)); ++n; }
         }
         {
             AttnArgs a{};
@@ -100,14 +103,14 @@ static int enqueue_step(fl_b200_decoder *d, cudaStream_t s, uint32_t *n_launch) 
             a.batch_stride = (uint64_t)c.n_kv_head * c.max_kv * D;
             a.n_q_head = c.n_head; a.n_kv_head = c.n_kv_head; a.batch = 1; a.n_splits = d->n_splits;
             a.scale = 1.0f / sqrtf((float)D); a.status = ctx->status;
-            CK(launch_attn_decode(a, s)); ++n;
+            if (mask & K_ATTN) { CK(launch_attn_decode(a, s)); ++n; }
         }
         {   // O projection + residual: xb = xa + Wo att
             MatvecArgs a{};
             a.n_tensors = 1;
             a.t[0] = {w[FL_B200_T_WO].w, d->xb, d->xa, E, w[FL_B200_T_WO].fmt};
             a.x = d->att; a.cols = QD; a.x_mode = MV_X_PLAIN; a.status = ctx->status;
-            CK(launch_matvec(a, ctx->sms, s)); ++n;
+            if (mask & K_MATVEC) { CK(launch_matvec(a, ctx->sms, s)); ++n; }
         }
         {   // RMSNorm + gate / up
             MatvecArgs a{};
@@ -116,14 +119,14 @@ static int enqueue_step(fl_b200_decoder *d, cudaStream_t s, uint32_t *n_launch) 
             a.t[1] = {w[FL_B200_T_UP].w, d->u, nullptr, c.n_ff, w[FL_B200_T_UP].fmt};
             a.x = d->xb; a.wnorm = d->ffn_norm[l]; a.eps = c.eps; a.cols = E;
             a.x_mode = MV_X_RMSNORM; a.status = ctx->status;
-            CK(launch_matvec(a, ctx->sms, s)); ++n;
+            if (mask & K_MATVEC) { CK(launch_matvec(a, ctx->sms, s)); ++n; }
         }
         {   // SiLU(gate) * up, down projection + residual: xa = xb + Wdown h
             MatvecArgs a{};
             a.n_tensors = 1;
             a.t[0] = {w[FL_B200_T_DOWN].w, d->xa, d->xb, E, w[FL_B200_T_DOWN].fmt};
             a.x = d->g; a.x2 = d->u; a.cols = c.n_ff; a.x_mode = MV_X_SILU_MUL; a.status = ctx->status;
-            CK(launch_matvec(a, ctx->sms, s)); ++n;
+            if (mask & K_MATVEC) { CK(launch_matvec(a, ctx->sms, s)); ++n; }
         }
     }
     {   // output norm + head
@@ -132,12 +135,16 @@ static int enqueue_step(fl_b200_decoder *d, cudaStream_t s, uint32_t *n_launch) 
         a.t[0] = {d->output.w, d->logits, nullptr, c.n_vocab, d->output.fmt};
         a.x = d->xa; a.wnorm = d->out_norm; a.eps = c.eps; a.cols = E;
         a.x_mode = MV_X_RMSNORM; a.status = ctx->status; a.xn_out = d->xn_final;
-        CK(launch_matvec(a, ctx->sms, s)); ++n;
+        if (mask & K_MATVEC) { CK(launch_matvec(a, ctx->sms, s)); ++n; }
     }
-    CK(launch_argmax(d->logits, c.n_vocab, d->d_next, d->d_margin, ctx->argmax_scratch, ctx->argmax_ticket,
-                     ctx->sms, s)); ++n;
-    advance_kernel<<<1, 32, 0, s>>>(d->d_token, d->d_next, d->d_pos, d->d_hist, d->d_hist_n, d->hist_cap);
-    CK(cudaGetLastError()); ++n;
+    if (mask & K_OTHER) {
+        CK(launch_argmax(d->logits, c.n_vocab, d->d_next, d->d_margin, ctx->argmax_scratch, ctx->argmax_ticket,
+                         ctx->sms, s)); ++n;
+    }
+    if (mask == K_ALL) {   // state only advances in the real step
+        advance_kernel<<<1, 32, 0, s>>>(d->d_token, d->d_next, d->d_pos, d->d_hist, d->d_hist_n, d->hist_cap);
+        CK(cudaGetLastError()); ++n;
+    }
     if (n_launch) *n_launch = n;
     return FL_B200_OK;
 }
@@ -357,8 +364,63 @@ int fl_b200_decoder_margin(fl_b200_decoder *d, float *out) {
 }
 
 int fl_b200_decoder_tap(fl_b200_decoder *d, int which, float *out) {
-    if (!d || !out || which < 0 || which > 1) return set_err(FL_B200_ERR_ARG, "decoder_tap: bad argument");
-    return fl_b200_download(d->ctx, out, which == 0 ? d->xa : d->xn_final, (size_t)d->c.n_embd * 4);
+    if (!d || !out) return set_err(FL_B200_ERR_ARG, "decoder_tap: null");
+    const fl_b200_llama_cfg &c = d->c;
+    const uint32_t QD = c.n_head * c.head_dim, KD = c.n_kv_head * c.head_dim;
+    const float *src = nullptr;
+    size_t n = 0;
+    switch (which) {
+    case 0: src = d->xa; n = c.n_embd; break;        // hidden state after the last layer
+    case 1: src = d->xn_final; n = c.n_embd; break;  // final normed vector
+    case 2: src = d->q; n = QD; break;               // last layer: q after RoPE
+    case 3: src = d->v; n = KD; break;               // last layer: v
+    case 4: src = d->att; n = QD; break;             // last layer: attention output
+    case 5: src = d->xb; n = c.n_embd; break;        // last layer: residual after attention
+    case 6: src = d->g; n = c.n_ff; break;           // last layer: gate
+    case 7: src = d->u; n = c.n_ff; break;           // last layer: up
+    default: return set_err(FL_B200_ERR_ARG, "decoder_tap: unknown tap %d", which);
+    }
+    return fl_b200_download(d->ctx, out, src, n * 4);
+}
+
+// Times `reps` replays of one kernel class of the step (the same launches, in
+// step order, with the decoder's real weights and buffers; the other classes
+// are left out, so the activations are stale and the results meaningless) with
+// CUDA events on the context's stream. The position used is the current n_past.
+int fl_b200_decoder_time_class(fl_b200_decoder *d, uint32_t kernel_class, uint32_t reps, float *ms_per_step,
+                               uint32_t *launches_per_step) {
+    if (!d || !ms_per_step || !launches_per_step) return set_err(FL_B200_ERR_ARG, "decoder_time_class: null");
+    if (!d->finalized) return set_err(FL_B200_ERR_STATE, "decoder_time_class: finalize first");
+    if (kernel_class == 0 || kernel_class > K_ALL || reps == 0) return set_err(FL_B200_ERR_ARG, "decoder_time_class: bad class / reps");
+    if ((uint32_t)d->n_past >= d->c.max_kv) return set_err(FL_B200_ERR_STATE, "decoder_time_class: kv full");
+    cudaStream_t s = d->ctx->stream;
+    d->h_pin[0] = 0; d->h_pin[1] = 0; d->h_pin[2] = d->n_past; d->h_pin[3] = 0;
+    CK(cudaMemcpyAsync(d->d_token, d->h_pin, 16, cudaMemcpyHostToDevice, s));
+    // Bit 3 keeps the mask different from K_ALL, so the advance kernel is left
+    // out and the position stays put over the replays.
+    const uint32_t m = kernel_class | 8u;
+    cudaGraph_t g = nullptr;
+    cudaGraphExec_t ge = nullptr;
+    CK(cudaStreamSynchronize(s));
+    CK(cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal));
+    uint32_t n = 0;
+    int rc = enqueue_step(d, s, &n, m);
+    cudaError_t e = cudaStreamEndCapture(s, &g);
+    if (rc) { if (g) cudaGraphDestroy(g); return rc; }
+    CK(e);
+    CK(cudaGraphInstantiate(&ge, g, 0));
+    CK(cudaGraphLaunch(ge, s));   // warm-up
+    CK(cudaEventRecord(d->ctx->ev0, s));
+    for (uint32_t i = 0; i < reps; ++i) CK(cudaGraphLaunch(ge, s));
+    CK(cudaEventRecord(d->ctx->ev1, s));
+    CK(cudaEventSynchronize(d->ctx->ev1));
+    float ms = 0.f;
+    CK(cudaEventElapsedTime(&ms, d->ctx->ev0, d->ctx->ev1));
+    cudaGraphExecDestroy(ge);
+    cudaGraphDestroy(g);
+    *ms_per_step = ms / (float)reps;
+    *launches_per_step = n;
+    return check_dev_status(d);
 }
 
 int fl_b200_decoder_launches_per_step(fl_b200_decoder *d, uint32_t *n) {

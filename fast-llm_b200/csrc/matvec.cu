@@ -42,20 +42,33 @@ constexpr int kThreads = kWarps * 32;
 constexpr int kRowsPerStage = 4;
 constexpr uint32_t kSeg4 = 8 * 144;   // bytes of one Q4_K segment (8 super-blocks)
 constexpr uint32_t kSeg6 = 8 * 210;   // bytes of one Q6_K segment
-constexpr uint32_t kStageBytes = kRowsPerStage * kSeg6;   // ring slot size (fits both)
+constexpr uint32_t kStage4 = kRowsPerStage * kSeg4;       // ring slot size, Q4_K only
+constexpr uint32_t kStage6 = kRowsPerStage * kSeg6;       // ring slot size when Q6_K is present
 
-// ---- u8 -> f32 ------------------------------------------------------------
+// ---- u8 -> f32 without the conversion pipe --------------------------------
+// Integer-to-float conversion instructions issue at a fraction of the FMA rate,
+// so bytes are turned into floats with a byte permute instead: placing byte k
+// of w under the constant 0x4B000000 gives the float 2^23 + byte exactly; a
+// packed f32x2 add of -2^23 removes the offset for two values at once.
+constexpr float kMagic = 8388608.0f;   // 2^23
+
 template <int K>
-__device__ __forceinline__ float u8f(uint32_t w) {
-    return (float)((w >> (8 * K)) & 0xFFu);
+__device__ __forceinline__ float u8_biased(uint32_t w) {   // 2^23 + byte K of w
+    return __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7650u | K));
 }
+template <int K>
+__device__ __forceinline__ float u8f(uint32_t w) { return u8_biased<K>(w) - kMagic; }
 
 __device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) { return __ffma2_rn(a, b, c); }
+__device__ __forceinline__ float2 add2(float2 a, float2 b) { return __fadd2_rn(a, b); }
 
 // acc += (bytes of w as floats) . x4
 __device__ __forceinline__ void dot4_u8(uint32_t w, const float4 &x, float2 &acc) {
-    acc = fma2(make_float2(u8f<0>(w), u8f<1>(w)), make_float2(x.x, x.y), acc);
-    acc = fma2(make_float2(u8f<2>(w), u8f<3>(w)), make_float2(x.z, x.w), acc);
+    const float2 nm = make_float2(-kMagic, -kMagic);
+    const float2 q01 = add2(make_float2(u8_biased<0>(w), u8_biased<1>(w)), nm);
+    const float2 q23 = add2(make_float2(u8_biased<2>(w), u8_biased<3>(w)), nm);
+    acc = fma2(q01, make_float2(x.x, x.y), acc);
+    acc = fma2(q23, make_float2(x.z, x.w), acc);
 }
 
 // ---- permuted activation layouts -------------------------------------------
@@ -82,7 +95,7 @@ struct Smem {
     float *x4, *s4;   // Q4_K: permuted x, per-lane sums of its two 32-element sub-blocks
     float *x6, *s6;   // Q6_K: permuted x, per-lane sums of its four 16-element groups
     uint64_t *bars;   // [kWarps][stages]
-    uint8_t *ring;    // [kWarps][stages][kStageBytes]
+    uint8_t *ring;    // [kWarps][stages][stage bytes]
 };
 
 __device__ __forceinline__ Smem carve(uint8_t *base, uint32_t cols, bool q4, bool q6, int stages) {
@@ -109,7 +122,7 @@ __device__ __forceinline__ float q4k_quarter(const uint8_t *blk, uint32_t c, con
     float2 pa = make_float2(0.f, 0.f), pb = make_float2(0.f, 0.f);
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-        const uint32_t lo = qw[i] & 0x0F0F0F0Fu, hi = (qw[i] >> 4) & 0x0F0F0F0Fu;
+        const uint32_t lo = qw[i] & 0x0F0F0F0Fu, hi = qw[i] & 0xF0F0F0F0u;   // hi holds 16 * q
         dot4_u8(lo, xs[i * 32], pa);
         dot4_u8(hi, xs[(8 + i) * 32], pb);
     }
@@ -122,7 +135,7 @@ __device__ __forceinline__ float q4k_quarter(const uint8_t *blk, uint32_t c, con
     const uint32_t mn_hi = ((e >> 4) & 0x0F0Fu) | ((b >> 2) & 0x3030u);
     const uint32_t sc = c >= 2 ? sc_hi : sc_lo, mn = c >= 2 ? mn_hi : mn_lo;
     const float d = h2f_bits((uint16_t)(hdr.x & 0xFFFFu)), dmin = h2f_bits((uint16_t)(hdr.x >> 16));
-    const float t = u8f<0>(sc) * (pa.x + pa.y) + u8f<1>(sc) * (pb.x + pb.y);
+    const float t = u8f<0>(sc) * (pa.x + pa.y) + u8f<1>(sc) * (0.0625f * (pb.x + pb.y));
     const float m = u8f<0>(mn) * sx.x + u8f<1>(mn) * sx.y;
     return d * t - dmin * m;
 }
@@ -155,13 +168,16 @@ __device__ __forceinline__ float q6k_quarter(const uint8_t *stage_row, uint32_t 
         dot4_u8(g2, xs[(8 + j) * 32], p2);
         dot4_u8(g3, xs[(12 + j) * 32], p3);
     }
-    const int8_t *sc = reinterpret_cast<const int8_t *>(stage_row + ob + 192 + 8 * hf + hq);
+    const uint8_t *scp = stage_row + ob + 192 + 8 * hf + hq;
+    // int8 scales -> f32 through the same trick: (s ^ 0x80) = s + 128 as an unsigned byte
+    const uint32_t sw = ((uint32_t)scp[0] | ((uint32_t)scp[2] << 8) | ((uint32_t)scp[4] << 16) | ((uint32_t)scp[6] << 24)) ^ 0x80808080u;
+    const float kOff = kMagic + 128.0f;
     const float d = h2f_bits(*reinterpret_cast<const uint16_t *>(stage_row + ob + 208));
     // value = d * sc * (q - 32): sum q*x minus 32 * sum x per 16-element group
-    float t = (float)sc[0] * ((p0.x + p0.y) - 32.f * sx.x);
-    t += (float)sc[2] * ((p1.x + p1.y) - 32.f * sx.y);
-    t += (float)sc[4] * ((p2.x + p2.y) - 32.f * sx.z);
-    t += (float)sc[6] * ((p3.x + p3.y) - 32.f * sx.w);
+    float t = (u8_biased<0>(sw) - kOff) * ((p0.x + p0.y) - 32.f * sx.x);
+    t += (u8_biased<1>(sw) - kOff) * ((p1.x + p1.y) - 32.f * sx.y);
+    t += (u8_biased<2>(sw) - kOff) * ((p2.x + p2.y) - 32.f * sx.z);
+    t += (u8_biased<3>(sw) - kOff) * ((p3.x + p3.y) - 32.f * sx.w);
     return d * t;
 }
 
@@ -207,6 +223,7 @@ matvec_stream_kernel(const MatvecArgs a, const uint32_t total_quads, const int s
     const Smem sm = carve(smem_raw, a.cols, use_q4 != 0, use_q6 != 0, stages);
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
     const uint32_t nseg = a.cols / 2048u;
+    const uint32_t kStageBytes = use_q6 ? kStage6 : kStage4;
     __shared__ float red[kWarps];
     __shared__ float inv_rms;
 
@@ -399,9 +416,10 @@ size_t matvec_smem_bytes(uint32_t cols, bool q4, bool q6, int *stages_out) {
     fixed += 128;   // ring alignment slack
     const size_t limit = 227 * 1024 - 1024;   // leave room for static shared memory
     int stages = 4;
-    while (stages > 1 && fixed + (size_t)kWarps * stages * (8 + kStageBytes) > limit) --stages;
+    const size_t slot = q6 ? kStage6 : kStage4;
+    while (stages > 1 && fixed + (size_t)kWarps * stages * (8 + slot) > limit) --stages;
     if (stages_out) *stages_out = stages;
-    return fixed + (size_t)kWarps * stages * (8 + kStageBytes);
+    return fixed + (size_t)kWarps * stages * (8 + slot);
 }
 
 cudaError_t matvec_init(void) {

@@ -92,9 +92,20 @@ class Decoder:
         return v.value
 
     def tap(self, which):
-        out = np.empty(self.cfg["n_embd"], dtype=np.float32)
+        c = self.cfg
+        n = {0: c["n_embd"], 1: c["n_embd"], 2: c["n_head"] * c["head_dim"], 3: c["n_kv_head"] * c["head_dim"],
+             4: c["n_head"] * c["head_dim"], 5: c["n_embd"], 6: c["n_ff"], 7: c["n_ff"]}[which]
+        out = np.empty(n, dtype=np.float32)
         capi._ck(self.lib.fl_b200_decoder_tap(self._h, which, C.c_void_p(out.ctypes.data)))
         return out
+
+    def time_class(self, kernel_class, reps):
+        """(ms per step, launches per step) of one kernel class replayed alone:
+        1 matvec, 2 attention, 4 small operators, 7 all."""
+        ms, n = C.c_float(), C.c_uint32()
+        capi._ck(self.lib.fl_b200_decoder_time_class(self._h, C.c_uint32(kernel_class), C.c_uint32(reps),
+                                                     C.byref(ms), C.byref(n)))
+        return ms.value, n.value
 
     def launches_per_step(self):
         v = C.c_uint32()

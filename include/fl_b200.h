@@ -225,9 +225,18 @@ int fl_b200_decoder_run(fl_b200_decoder *dec, int32_t first_token, uint32_t n, i
 /* After a step: logits (n_vocab floats) and the top1 - top2 margin. */
 int fl_b200_decoder_logits(fl_b200_decoder *dec, float *logits_host);
 int fl_b200_decoder_margin(fl_b200_decoder *dec, float *margin_out);
-/* Device pointers of activations of the last step, for layer-level parity:
- * which = 0 hidden state after the last layer, 1 final normed vector. */
+/* Activations of the last step, for layer-level parity. which: 0 hidden state
+ * after the last layer (n_embd), 1 final normed vector (n_embd); of the last
+ * layer: 2 q after RoPE (n_head*head_dim), 3 v (n_kv_head*head_dim), 4 attention
+ * output (n_head*head_dim), 5 residual after attention (n_embd), 6 gate (n_ff),
+ * 7 up (n_ff). */
 int fl_b200_decoder_tap(fl_b200_decoder *dec, int which, float *host_out);
+/* Times `reps` replays of one class of the step's kernels in isolation (same
+ * launches, real weights and buffers, CUDA events on the context's stream).
+ * kernel_class: 1 matvec launches, 2 attention launches, 4 the small
+ * operators, 7 all of them. Results of the replays are not meaningful. */
+int fl_b200_decoder_time_class(fl_b200_decoder *dec, uint32_t kernel_class, uint32_t reps,
+                               float *ms_per_step_out, uint32_t *launches_per_step_out);
 /* Number of kernels this library launches per decoder step. */
 int fl_b200_decoder_launches_per_step(fl_b200_decoder *dec, uint32_t *n_out);
 /* Weight + KV bytes one step at position `pos` must read (the roofline numerator). */

@@ -257,6 +257,22 @@ int32_t flo_llama_step(flo_llama *m, const flo_ops_t *ops, int32_t token) {
  * the final normed vector of the last step. */
 const float *flo_llama_hidden(const flo_llama *m) { return m->x; }
 const float *flo_llama_normed(const flo_llama *m) { return m->xn; }
+/* Last-layer activations of the last step, same numbering as the GPU decoder's
+ * taps: 2 q after RoPE, 3 v, 4 attention output, 5 residual after attention,
+ * 6 gate, 7 up. */
+const float *flo_llama_tap(const flo_llama *m, int which) {
+    switch (which) {
+    case 0: return m->x;
+    case 1: return m->xn;
+    case 2: return m->q;
+    case 3: return m->v;
+    case 4: return m->att;
+    case 5: return m->x1;
+    case 6: return m->g;
+    case 7: return m->u;
+    default: return 0;
+    }
+}
 
 /* Plain multi-threaded matvec (y = W x) on an operator table, for parity tests
  * and the timed CPU baseline. */

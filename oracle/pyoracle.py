@@ -117,6 +117,7 @@ class Oracle:
         p.flo_llama_hidden.restype = C.POINTER(C.c_float)
         p.flo_llama_normed.restype = C.POINTER(C.c_float)
         p.flo_llama_margin.restype = C.c_float
+        p.flo_llama_tap.restype = C.POINTER(C.c_float)
 
     @staticmethod
     def available(kind):
@@ -299,6 +300,12 @@ class LlamaOracle:
 
     def margin(self):
         return self.p.flo_llama_margin(self.h)
+
+    def tap(self, which):
+        c = self.cfg
+        n = {0: c["n_embd"], 1: c["n_embd"], 2: c["n_head"] * c["head_dim"], 3: c["n_kv_head"] * c["head_dim"],
+             4: c["n_head"] * c["head_dim"], 5: c["n_embd"], 6: c["n_ff"], 7: c["n_ff"]}[which]
+        return np.ctypeslib.as_array(self.p.flo_llama_tap(self.h, which), shape=(n,)).copy()
 
     def kv_row(self, layer, pos):
         n = self.cfg["n_kv_head"] * self.cfg["head_dim"]

@@ -1,0 +1,126 @@
+"""GPU parity tests of the Llama-shape decoder (the per-token launch plan)
+against the CPU oracle's decode step on identical seeded weights and KV."""
+import os
+
+import numpy as np
+import pytest
+
+from fast_llm_b200 import capi, synth
+from fast_llm_b200.decoder import Decoder
+
+pytestmark = pytest.mark.gpu
+torch = pytest.importorskip("torch")
+
+SMALL = dict(n_layer=2, n_embd=2048, n_head=16, n_kv_head=4, head_dim=128, n_ff=4096, n_vocab=1000, max_kv=96,
+             rope_base=500000.0, eps=1e-5)
+
+
+def build_pair(ctx, checker, cfg, seed, n_prefill, kv_std=0.1):
+    """The same synthetic model on the GPU decoder and on the CPU oracle."""
+    from oracle import pyoracle
+    dec = Decoder(ctx, cfg)
+    orc = pyoracle.LlamaOracle(checker, cfg)
+    for l in range(cfg["n_layer"]):
+        for i, name in enumerate(synth.LAYER_TENSORS):
+            w = synth.llama_tensor(cfg, seed, name, l)
+            dec.set_layer_tensor(l, i, synth.Q4_K_M[name], torch.from_numpy(w).cuda())
+            orc.set_layer_tensor(l, i, synth.Q4_K_M[name], w)
+        an, fn = synth.llama_norm(cfg, seed, "attn_norm", l), synth.llama_norm(cfg, seed, "ffn_norm", l)
+        dec.set_layer_norms(l, torch.from_numpy(an).cuda(), torch.from_numpy(fn).cuda())
+        orc.set_layer_norms(l, an, fn)
+        if n_prefill:
+            k, v = synth.llama_kv(cfg, seed, l, n_prefill, std=kv_std)
+            orc.seed_kv(l, k, v)
+            kp, vp = dec.kv_ptrs(l)
+            for src, dst in ((k, kp), (v, vp)):
+                full = np.zeros((cfg["n_kv_head"], cfg["max_kv"], cfg["head_dim"]), dtype=np.float16)
+                full[:, :n_prefill] = src
+                capi._ck(ctx.lib.fl_b200_upload(ctx._h, capi.C.c_void_p(dst), capi.C.c_void_p(full.ctypes.data),
+                                                capi.C.c_size_t(full.nbytes)))
+    for which, name in ((capi.G_TOK_EMBD, "tok_embd"), (capi.G_OUTPUT, "output")):
+        w = synth.llama_tensor(cfg, seed, name)
+        dec.set_global(which, synth.Q4_K_M[name], torch.from_numpy(w).cuda())
+        orc.set_global(which, synth.Q4_K_M[name], w)
+    on = synth.llama_norm(cfg, seed, "out_norm")
+    dec.set_out_norm(torch.from_numpy(on).cuda())
+    orc.set_out_norm(on)
+    torch.cuda.synchronize()
+    dec.finalize()
+    dec.rewind_to(n_prefill)
+    orc.set_n_past(n_prefill)
+    return dec, orc
+
+
+def logits_close(got, want):
+    """Relative to the logit scale: max |diff| / RMS(want)."""
+    return float(np.max(np.abs(got - want)) / (np.sqrt(np.mean(want.astype(np.float64) ** 2)) + 1e-30))
+
+
+def test_small_model_teacher_forced(ctx, checker):
+    dec, orc = build_pair(ctx, checker, SMALL, seed=3, n_prefill=40)
+    tok = 11
+    for step in range(8):
+        want_tok = orc.step(tok)
+        got_tok = dec.step(tok)
+        got, want = dec.logits(), orc.logits()
+        assert np.all(np.isfinite(got))
+        err = logits_close(got, want)
+        assert err < 1e-3, (step, err)
+        # identical greedy token unless the oracle's own top1-top2 margin is inside the observed error
+        if got_tok != want_tok:
+            assert orc.margin() <= 2 * np.max(np.abs(got - want)), (step, got_tok, want_tok, orc.margin())
+        assert abs(dec.last_margin() - orc.margin()) <= 4 * np.max(np.abs(got - want)) + 1e-6
+        hid = dec.tap(0)
+        assert logits_close(hid, orc.hidden()) < 1e-3
+        tok = want_tok          # teacher forcing: both sides see the oracle's token
+    assert dec.n_past() == 48 and orc.n_past() == 48
+    dec.close(); orc.close()
+
+
+def test_run_equals_stepwise_and_rewind(ctx, checker):
+    dec, orc = build_pair(ctx, checker, SMALL, seed=5, n_prefill=10)
+    toks = dec.run(3, 6)                 # device feedback
+    dec.rewind_to(10)
+    t, seq = 3, []
+    for _ in range(6):
+        t = dec.step(t)
+        seq.append(t)
+    assert list(toks) == seq             # same kernels, same order: identical tokens
+    assert dec.n_past() == 16
+    with pytest.raises(capi.Fl200Error):
+        dec.rewind_to(10 ** 6)
+    with pytest.raises(capi.Fl200Error):
+        dec.step(SMALL["n_vocab"])       # token outside the vocabulary
+    dec.close(); orc.close()
+
+
+def test_kv_full_is_reported(ctx, checker):
+    cfg = dict(SMALL, max_kv=12)
+    dec, orc = build_pair(ctx, checker, cfg, seed=6, n_prefill=11)
+    dec.step(1)
+    with pytest.raises(capi.Fl200Error):
+        dec.step(1)                      # the reference aborts with "kv full" (decoder.cpp:1182-1186)
+    dec.close(); orc.close()
+
+
+def test_llama8b_shape_greedy(ctx, checker):
+    """Synthetic Llama-3-8B-shape Q4_K_M model, 8192 prefilled positions: greedy
+    next-token identity, teacher-forced, for FLB_8B_STEPS steps (default 2; the
+    oracle needs ~8e9 multiply-adds per step on the host cores)."""
+    steps = int(os.environ.get("FLB_8B_STEPS", "2"))
+    cfg = dict(synth.LLAMA3_8B)
+    dec, orc = build_pair(ctx, checker, cfg, seed=0, n_prefill=8192)
+    w_bytes, kv_bytes = dec.bytes_per_step(8192 + 127)
+    assert w_bytes == 4876918784 and kv_bytes == 131072 * 8320
+    tok, mism = 1, []
+    for step in range(steps):
+        want_tok = orc.step(tok)
+        got_tok = dec.step(tok)
+        got, want = dec.logits(), orc.logits()
+        err = logits_close(got, want)
+        assert err < 1e-3, (step, err)
+        if got_tok != want_tok:
+            mism.append((step, got_tok, want_tok, orc.margin(), float(np.max(np.abs(got - want)))))
+        tok = want_tok
+    assert not mism, mism
+    dec.close(); orc.close()

@@ -1,0 +1,335 @@
+"""GPU parity tests of the single operators, through the C ABI, against the CPU
+oracle (the reference's own code where its build travelled, else the pinned
+port) on identical seeded inputs.
+
+Gates:
+  dequantised weights    bit-exact
+  matvec                 <= 1e-3 relative, error normalised by max(|ref|, 0.1 * RMS(ref))
+                         (the reference's own GPU gate, tools/membench.cu:524-530)
+  attention              <= 2e-3 max-abs
+"""
+import os
+
+import numpy as np
+import pytest
+
+from fast_llm_b200 import capi, synth
+
+pytestmark = pytest.mark.gpu
+torch = pytest.importorskip("torch")
+
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "decode_ops_golden.npz")
+MATVEC_RTOL = 1e-3
+ATTN_ATOL = 2e-3
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def bits(a):
+    return np.ascontiguousarray(a, dtype=np.float32).view(np.uint32)
+
+
+def rel_err(y, ref):
+    ref = ref.astype(np.float64)
+    floor = 0.1 * np.sqrt(np.mean(ref ** 2)) + 1e-30
+    return float(np.max(np.abs(y.astype(np.float64) - ref) / np.maximum(np.abs(ref), floor)))
+
+
+def gpu_dequant(ctx, fmt, w, rows, cols):
+    wd = dev(w)
+    out = torch.empty((rows, cols), dtype=torch.float32, device="cuda")
+    torch.cuda.synchronize()
+    ctx.dequant(fmt, wd, rows, cols, out)
+    ctx.sync()
+    return out.cpu().numpy()
+
+
+def gpu_matvec(ctx, fmt, w, rows, cols, x):
+    wd, xd = dev(w), dev(x)
+    y = torch.full((rows + 8,), 7.0, dtype=torch.float32, device="cuda")   # canary tail
+    torch.cuda.synchronize()
+    ctx.matvec_assign(fmt, wd, rows, cols, xd, y)
+    ctx.sync()
+    assert ctx.status() == 0
+    y = y.cpu().numpy()
+    assert np.all(y[rows:] == 7.0), "matvec wrote past its output"
+    return y[:rows]
+
+
+@pytest.mark.parametrize("fmt,rows,cols", [
+    (capi.Q4_K, 4096, 4096),       # configuration 0
+    (capi.Q6_K, 1024, 4096),       # attn_v shape
+    (capi.Q6_K, 64, 14336),        # ffn_down rows
+    (capi.Q4_K, 3, 256), (capi.Q6_K, 3, 256), (capi.Q4_K, 5, 768), (capi.Q6_K, 5, 768),
+    (capi.Q8_0, 7, 1408), (capi.Q5_0, 7, 1408), (capi.Q8_0, 1, 32), (capi.F32, 4, 64),
+])
+def test_dequant_bitexact(ctx, checker, fmt, rows, cols):
+    w = synth.quant_tensor(fmt, np.random.default_rng(rows * 7 + cols + fmt), rows, cols)
+    got = gpu_dequant(ctx, fmt, w, rows, cols)
+    want = checker.dequant(fmt, w, rows, cols)
+    assert np.array_equal(bits(got), bits(want))
+
+
+def test_dequant_extreme_scales(ctx, checker):
+    """Largest / smallest finite f16 scales, zero and subnormal scales, extreme quants."""
+    rng = np.random.default_rng(1)
+    w = synth.q4k_tensor(rng, 8, 512)
+    blk = w.reshape(-1, 144)
+    blk[0, 0:2] = np.array([0x7BFF], dtype=np.uint16).view(np.uint8)   # d = 65504
+    blk[1, 0:2] = np.array([0x0001], dtype=np.uint16).view(np.uint8)   # d = smallest subnormal
+    blk[2, 0:4] = 0                                                    # d = dmin = 0
+    blk[3, 4:16] = 0xFF                                                # all scales / mins 63
+    blk[4, 16:] = 0xFF                                                 # all quants 15
+    blk[5, 2:4] = np.array([0x8400], dtype=np.uint16).view(np.uint8)   # negative dmin
+    assert np.array_equal(bits(gpu_dequant(ctx, capi.Q4_K, w, 8, 512)), bits(checker.dequant(capi.Q4_K, w, 8, 512)))
+    w = synth.q6k_tensor(rng, 8, 512)
+    blk = w.reshape(-1, 210)
+    blk[0, 208:210] = np.array([0x7BFF], dtype=np.uint16).view(np.uint8)
+    blk[1, 208:210] = np.array([0x0001], dtype=np.uint16).view(np.uint8)
+    blk[2, 192:208] = np.array([-128] * 16, dtype=np.int8).view(np.uint8)
+    blk[3, 0:192] = 0xFF
+    blk[4, 0:192] = 0
+    assert np.array_equal(bits(gpu_dequant(ctx, capi.Q6_K, w, 8, 512)), bits(checker.dequant(capi.Q6_K, w, 8, 512)))
+
+
+@pytest.mark.parametrize("fmt,rows,cols", [
+    (capi.Q4_K, 4096, 4096),       # configuration 0 (streaming kernel)
+    (capi.Q4_K, 1024, 4096),       # wk
+    (capi.Q6_K, 1024, 4096),       # wv
+    (capi.Q6_K, 512, 14336),       # rows of ffn_down
+    (capi.Q4_K, 1026, 2048), (capi.Q6_K, 1029, 2048), (capi.Q4_K, 1, 2048), (capi.Q6_K, 3, 6144),   # ragged row counts
+    (capi.Q4_K, 37, 768), (capi.Q6_K, 37, 1280), (capi.Q8_0, 100, 1408), (capi.Q5_0, 33, 1408), (capi.F32, 50, 200),
+])
+def test_matvec_vs_oracle(ctx, checker, fmt, rows, cols):
+    rng = np.random.default_rng(rows + 31 * cols + fmt)
+    w = synth.quant_tensor(fmt, rng, rows, cols)
+    x = rng.standard_normal(cols).astype(np.float32)
+    got = gpu_matvec(ctx, fmt, w, rows, cols, x)
+    want = checker.matvec(fmt, w, rows, cols, x)
+    assert rel_err(got, want) <= MATVEC_RTOL
+    # run-to-run reproducible (fixed summation order)
+    assert np.array_equal(bits(got), bits(gpu_matvec(ctx, fmt, w, rows, cols, x)))
+
+
+def test_matvec_config0_vs_f64_and_golden(ctx, checker):
+    c0 = synth.config0(0)
+    got = gpu_matvec(ctx, capi.Q4_K, c0["w"], 4096, 4096, c0["x"])
+    deq = checker.dequant(capi.Q4_K, c0["w"], 4096, 4096).astype(np.float64)
+    y64 = deq @ c0["x"].astype(np.float64)
+    S = np.sqrt((deq ** 2) @ (c0["x"].astype(np.float64) ** 2))
+    # error normalised by S = ||w o x||_2 (tests/test_runtime.cpp:489-512): the canonical CPU dot itself is ~8e-6
+    assert np.max(np.abs(got - y64) / S) < 2e-5
+    g = np.load(GOLDEN)
+    for name, fmt in (("q4_k", capi.Q4_K), ("q6_k", capi.Q6_K), ("q8_0", capi.Q8_0), ("q5_0", capi.Q5_0)):
+        w, x = g[name + "_w"], g[name + "_x"]
+        assert rel_err(gpu_matvec(ctx, fmt, w, w.shape[0], x.size, x), g[name + "_y"]) <= MATVEC_RTOL
+        assert np.array_equal(bits(gpu_dequant(ctx, fmt, w, w.shape[0], x.size)), bits(g[name + "_deq"]))
+
+
+def test_matvec_linearity_full_size(ctx):
+    """Size-independent property at the head's full size: W(a x1 + x2) = a W x1 + W x2."""
+    rows, cols = 128256, 4096
+    rng = np.random.default_rng(5)
+    w = synth.q6k_tensor(rng, rows, cols)
+    x1 = rng.standard_normal(cols).astype(np.float32)
+    x2 = rng.standard_normal(cols).astype(np.float32)
+    y1, y2 = gpu_matvec(ctx, capi.Q6_K, w, rows, cols, x1), gpu_matvec(ctx, capi.Q6_K, w, rows, cols, x2)
+    y3 = gpu_matvec(ctx, capi.Q6_K, w, rows, cols, (2.0 * x1 + x2).astype(np.float32))
+    assert rel_err(y3, 2.0 * y1.astype(np.float64) + y2) <= 1e-4
+
+
+def test_stream_dot_semantics(ctx, checker):
+    """fl_b200_matvec accumulates into y and handles nx columns like the reference's STREAM_DOT."""
+    rng = np.random.default_rng(8)
+    rows, cols, nx = 300, 2048, 3
+    w = synth.q4k_tensor(rng, rows, cols)
+    x = rng.standard_normal((nx, cols)).astype(np.float32)
+    y0 = rng.standard_normal((nx, rows)).astype(np.float32)
+    want = y0.copy()
+    checker.stream_dot(capi.Q4_K, w, rows, cols, x, want, nx=nx, xstride=cols, ystride=rows)
+    wd, xd, yd = dev(w), dev(x), dev(y0)
+    torch.cuda.synchronize()
+    ctx.matvec(capi.Q4_K, wd, rows, cols, xd, yd, nx=nx, xstride=cols, ystride=rows)
+    ctx.sync()
+    assert rel_err(yd.cpu().numpy().ravel(), want.ravel()) <= MATVEC_RTOL
+
+
+def test_matvec_host_entry(ctx, checker):
+    rng = np.random.default_rng(4)
+    rows, cols = 2048, 4096
+    w = synth.q4k_tensor(rng, rows, cols)
+    x = rng.standard_normal(cols).astype(np.float32)
+    y = np.zeros(rows, dtype=np.float32)
+    wd = dev(w)
+    torch.cuda.synchronize()
+    ctx.matvec_host(capi.Q4_K, wd, rows, cols, x, y)
+    assert rel_err(y, checker.matvec(capi.Q4_K, w, rows, cols, x)) <= MATVEC_RTOL
+
+
+def test_boundary_rejects_bad_arguments(ctx):
+    w = torch.zeros(4096, dtype=torch.uint8, device="cuda")
+    x = torch.zeros(4096, dtype=torch.float32, device="cuda")
+    with pytest.raises(capi.Fl200Error):
+        ctx.matvec_assign(capi.Q4_K, w, 1, 100, x, x)            # cols not a multiple of the block
+    with pytest.raises(capi.Fl200Error):
+        ctx.matvec_assign(9, w, 1, 256, x, x)                    # unknown format
+    with pytest.raises(capi.Fl200Error):
+        ctx.matvec_assign(capi.Q4_K, None, 1, 256, x, x)         # null weights
+    with pytest.raises(capi.Fl200Error):
+        ctx.attn_decode(x, w, w, 32, 8, 64, 10, 16, 1, 1.0, x)   # head_dim 64 is not built
+    with pytest.raises(capi.Fl200Error):
+        ctx.attn_decode(x, w, w, 32, 8, 128, 0, 16, 1, 1.0, x)   # empty KV
+    t = capi.Task()
+    t.kind = 9                                                   # ATTN_HEAD (f32 MHA): not implemented on the device
+    with pytest.raises(capi.Fl200Error):
+        ctx.exec_task(t)
+
+
+def gpu_attn(ctx, q, k, v, kv_len, scale, batch=1):
+    n_q, d = q.shape[-2], q.shape[-1]
+    n_kv, stride = k.shape[-3], k.shape[-2]
+    qd, kd, vd = dev(q), dev(k.view(np.uint16)), dev(v.view(np.uint16))
+    out = torch.zeros(q.shape, dtype=torch.float32, device="cuda")
+    torch.cuda.synchronize()
+    ctx.attn_decode(qd, kd, vd, n_q, n_kv, d, kv_len, stride, batch, scale, out)
+    ctx.sync()
+    assert ctx.status() == 0
+    return out.cpu().numpy()
+
+
+@pytest.mark.parametrize("kv_len", [1, 7, 63, 64, 65, 191, 400, 1024, 3000])
+def test_attn_vs_oracle(ctx, checker, kv_len):
+    rng = np.random.default_rng(23 + kv_len)
+    n_q, n_kv, d = 32, 8, 128
+    stride = kv_len + 3
+    q = rng.standard_normal((n_q, d)).astype(np.float32)
+    k = (rng.standard_normal((n_kv, stride, d)) / np.sqrt(d)).astype(np.float16)
+    v = (rng.standard_normal((n_kv, stride, d)) / np.sqrt(d)).astype(np.float16)
+    scale = float(1.0 / np.sqrt(np.float32(d)))
+    got = gpu_attn(ctx, q, k, v, kv_len, scale)
+    want = checker.attn_gqa_f16(q, k, v, kv_len, scale)
+    assert np.max(np.abs(got - want)) <= ATTN_ATOL
+    assert np.array_equal(bits(got), bits(gpu_attn(ctx, q, k, v, kv_len, scale)))   # reproducible
+
+
+def test_attn_config0_and_golden(ctx, checker):
+    c0 = synth.config0(0)
+    got = gpu_attn(ctx, c0["q"], c0["k"], c0["v"], 1024, c0["scale"])
+    want = checker.attn_gqa_f16(c0["q"], c0["k"], c0["v"], 1024, c0["scale"])
+    assert np.max(np.abs(got - want)) <= ATTN_ATOL
+    g = np.load(GOLDEN)
+    got = gpu_attn(ctx, g["attn_q"], g["attn_k"], g["attn_v"], int(g["attn_kv_len"]), float(g["attn_scale"]))
+    assert np.max(np.abs(got - g["attn_out"])) <= ATTN_ATOL
+
+
+def test_attn_peaked_and_batched(ctx, checker):
+    """Large score range (softmax close to one-hot) and batch > 1 with separate caches."""
+    rng = np.random.default_rng(77)
+    n_q, n_kv, d, kv, batch = 32, 8, 128, 333, 3
+    q = (rng.standard_normal((batch, n_q, d)) * 8).astype(np.float32)
+    k = rng.standard_normal((batch, n_kv, kv, d)).astype(np.float16)
+    v = rng.standard_normal((batch, n_kv, kv, d)).astype(np.float16)
+    scale = float(1.0 / np.sqrt(np.float32(d)))
+    got = gpu_attn(ctx, q, k, v, kv, scale, batch=batch)
+    for b in range(batch):
+        want = checker.attn_gqa_f16(q[b], k[b], v[b], kv, scale)
+        assert np.max(np.abs(got[b] - want)) <= ATTN_ATOL
+
+
+def test_attn_long_context_property(ctx):
+    """At 32K keys (too slow for the scalar oracle): attention over identical
+    value rows returns that row, and splitting invariance holds for a cache whose
+    second half is masked out by a very negative score."""
+    rng = np.random.default_rng(3)
+    n_q, n_kv, d, kv = 32, 8, 128, 32768
+    q = rng.standard_normal((n_q, d)).astype(np.float32)
+    k = (rng.standard_normal((n_kv, kv, d)) / np.sqrt(d)).astype(np.float16)
+    row = rng.standard_normal((n_kv, 1, d)).astype(np.float16)
+    v = np.broadcast_to(row, (n_kv, kv, d)).copy()
+    got = gpu_attn(ctx, q, k, v, kv, 0.088)
+    for h in range(n_q):
+        assert np.max(np.abs(got[h] - row[h // 4, 0].astype(np.float32))) <= ATTN_ATOL
+
+
+def test_glue_ops_vs_oracle(ctx, checker):
+    rng = np.random.default_rng(12)
+    n = 4096
+    x = (rng.standard_normal(n) * 3).astype(np.float32)
+    u = rng.standard_normal(n).astype(np.float32)
+    wn = rng.uniform(0.9, 1.1, n).astype(np.float32)
+    xd, ud, wd = dev(x), dev(u), dev(wn)
+    y = torch.empty(n, dtype=torch.float32, device="cuda")
+    torch.cuda.synchronize()
+    ctx.rmsnorm(xd, wd, y, 1e-5, n); ctx.sync()
+    want = checker.rmsnorm(wn, x, 1e-5)
+    assert np.max(np.abs(y.cpu().numpy() - want) / (np.abs(want) + 1e-6)) < 1e-5   # tests/test_decode_ops.cpp:20-35
+    ctx.add2(xd, ud, y, n); ctx.sync()
+    assert np.array_equal(bits(y.cpu().numpy()), bits(checker.add2(x, u)))
+    ctx.silu_mul(xd, ud, y, n); ctx.sync()
+    want = checker.silu_mul(x, u)
+    assert np.max(np.abs(y.cpu().numpy() - want)) <= 1e-5 * (1 + np.max(np.abs(want)))
+
+
+@pytest.mark.parametrize("pos", [0, 1, 100, 8191])
+def test_rope_kv_append_vs_oracle(ctx, checker, pos):
+    rng = np.random.default_rng(pos + 1)
+    n_q, n_kv, d, stride = 32, 8, 128, 8200
+    q = rng.standard_normal(n_q * d).astype(np.float32)
+    k = rng.standard_normal(n_kv * d).astype(np.float32)
+    v = rng.standard_normal(n_kv * d).astype(np.float32)
+    qd, kd, vd = dev(q), dev(k), dev(v)
+    kc = torch.zeros((n_kv, stride, d), dtype=torch.float16, device="cuda")
+    vc = torch.zeros((n_kv, stride, d), dtype=torch.float16, device="cuda")
+    pd = torch.tensor([pos], dtype=torch.int32, device="cuda")
+    torch.cuda.synchronize()
+    ctx.rope_kv_append(qd, kd, vd, kc, vc, pd, n_q, n_kv, d, stride, 500000.0); ctx.sync()
+    want_q = checker.rope(q, pos, n_q, d, 0, d, 500000.0)
+    want_k = checker.rope(k, pos, n_kv, d, 0, d, 500000.0)
+    # angles are bit-identical; cosf/sinf may differ from the host libm by a few ulp
+    assert np.max(np.abs(qd.cpu().numpy() - want_q)) <= 2e-6 * np.max(np.abs(q)) + 1e-6
+    got_k = kc[:, pos, :].cpu().numpy().astype(np.float32).ravel()
+    assert np.max(np.abs(got_k - want_k.astype(np.float16).astype(np.float32))) <= 2e-3   # one f16 ulp at |k| < 4
+    assert np.array_equal(vc[:, pos, :].cpu().numpy().ravel().view(np.uint16), v.astype(np.float16).view(np.uint16))
+    # nothing else was touched
+    assert int(torch.count_nonzero(kc).item()) <= n_kv * d and int(torch.count_nonzero(vc).item()) <= n_kv * d
+
+
+def test_argmax_tie_rule_and_margin(ctx):
+    rng = np.random.default_rng(6)
+    n = 128256
+    lg = rng.standard_normal(n).astype(np.float32)
+    lg[777] = 9.0
+    lg[90000] = 9.0            # tie: the lower index wins, margin 0
+    ld = dev(lg)
+    idx = torch.zeros(1, dtype=torch.int32, device="cuda")
+    mg = torch.zeros(1, dtype=torch.float32, device="cuda")
+    torch.cuda.synchronize()
+    ctx.argmax(ld, n, idx, mg); ctx.sync()
+    assert int(idx.item()) == 777 and float(mg.item()) == 0.0
+    lg[90000] = 8.5
+    ld = dev(lg)
+    torch.cuda.synchronize()
+    ctx.argmax(ld, n, idx, mg); ctx.sync()
+    assert int(idx.item()) == 777 and abs(float(mg.item()) - 0.5) < 1e-6
+
+
+def test_exec_task_stream_dot(ctx, checker):
+    """The task-level entry with a reference-layout Task record."""
+    rng = np.random.default_rng(10)
+    rows, cols = 192, 4096            # one tile as the reference's builder emits (decoder.cpp:713-716)
+    w = synth.q4k_tensor(rng, rows, cols)
+    x = rng.standard_normal(cols).astype(np.float32)
+    wd, xd = dev(w), dev(x)
+    yd = torch.zeros(rows, dtype=torch.float32, device="cuda")
+    t = capi.Task()
+    t.kind, t.fmt = 0, capi.Q4_K
+    t.w, t.w_bytes, t.x, t.y = wd.data_ptr(), rows * capi.row_bytes(capi.Q4_K, cols), xd.data_ptr(), yd.data_ptr()
+    t.rows, t.cols, t.nx = rows, cols, 1
+    torch.cuda.synchronize()
+    ctx.exec_task(t); ctx.sync()
+    assert rel_err(yd.cpu().numpy(), checker.matvec(capi.Q4_K, w, rows, cols, x)) <= MATVEC_RTOL
+    t.w_bytes += 1                    # freeze() rule: w_bytes must equal rows * row_bytes
+    with pytest.raises(capi.Fl200Error):
+        ctx.exec_task(t)
