@@ -1,0 +1,280 @@
+"""Benchmark of the decode hot path: greedy decode tokens/s of the synthetic
+Llama-3-8B-shape Q4_K_M model (32 layers, hidden 4096, 32/8 heads of 128, FFN
+14336, vocab 128256) with an 8192-token prefilled f16 KV cache, batch 1.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+A step is one decoded token: every packed weight and every cached K/V row is
+read once. Prints ONE JSON line (rank 0).
+
+  value      tokens/s with the token fed back on the device (CUDA-graph replays,
+             inputs resident in HBM), device-timed with CUDA events
+  e2e        tokens/s through the public per-token call: token host->device,
+             graph, next token device->host, every step
+  roofline   the streaming matvec kernel (dominant): packed weight bytes of one
+             step / time of that step's matvec launches replayed alone
+  cpu_baseline  the reference's CPU operators on this box's host cores, on a
+             bounded sample (2 of the 32 layers + the output head), N=1 only
+
+With --gpus N > 1 (torchrun, one rank per GPU) every rank decodes its own
+sequence on its own replica of the model ("weak": per-GPU work fixed); value is
+the sum over ranks / the slowest rank's time.
+--impl reference times only the CPU arm (rank 0), same metric and config.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+N_PREFILL = 8192
+METRIC = "decode tokens/s at 8B Q4_K_M shape, 1/2/4/8 B200; HBM GB/s % of roofline"
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons, sampled while the timed region runs."""
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device):
+        self.device = device
+        self.proc = None
+        self.path = os.path.join(ROOT, "gpurun_out", "clocks_rank%d.csv" % device)
+
+    def start(self):
+        os.makedirs(os.path.dirname(self.path), exist_ok=True)
+        try:
+            self.out = open(self.path, "w")
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.device), "--query-gpu=" + self.QUERY,
+                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=self.out,
+                                         stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        self.out.close()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in open(self.path):
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def cpu_reference_arm(steps, warmup, threads=None):
+    """Times the reference's CPU operators (oracle/_ref when it travelled, else
+    the pinned port) on a bounded sample of the workload: one decode step of a
+    2-layer slice of the model plus the output head, at position 8192, on all
+    host cores. tokens/s = 1 / (t_head + 16 * (t_2layers+head - t_head))."""
+    import numpy as np
+    from fast_llm_b200 import synth
+    from oracle import pyoracle
+    kind = "reference" if pyoracle.Oracle.available("reference") else "port"
+    orc = pyoracle.Oracle(kind)
+    cores = threads or os.cpu_count() or 1
+    os.environ.setdefault("OMP_NUM_THREADS", str(cores))
+    full = dict(synth.LLAMA3_8B)
+
+    def build(n_layer):
+        cfg = dict(full, n_layer=n_layer)
+        m = pyoracle.LlamaOracle(orc, cfg)
+        for l in range(n_layer):
+            for i, name in enumerate(synth.LAYER_TENSORS):
+                m.set_layer_tensor(l, i, synth.Q4_K_M[name], synth.llama_tensor(cfg, 0, name, l))
+            m.set_layer_norms(l, synth.llama_norm(cfg, 0, "attn_norm", l), synth.llama_norm(cfg, 0, "ffn_norm", l))
+            k, v = synth.llama_kv(cfg, 0, l, N_PREFILL)
+            m.seed_kv(l, k, v)
+        return m
+
+    head_w = synth.llama_tensor(full, 0, "output")
+    on = synth.llama_norm(full, 0, "out_norm")
+    models = []
+    for n_layer in (0, 2):
+        m = build(n_layer)
+        m.set_global(0, synth.Q4_K_M["tok_embd"], head_w)   # same bytes serve as embedding table
+        m.set_global(1, synth.Q4_K_M["output"], head_w)
+        m.set_out_norm(on)
+        models.append(m)
+
+    def one(m):
+        m.set_n_past(N_PREFILL)
+        t0 = time.perf_counter()
+        m.step(1)
+        return time.perf_counter() - t0
+
+    times = []
+    for it in range(warmup + steps):
+        t_head, t_two = one(models[0]), one(models[1])
+        if it >= warmup:
+            times.append(t_head + 16.0 * max(t_two - t_head, 0.0))
+    for m in models:
+        m.close()
+    t_tok = sum(times) / len(times)
+    return {"value": 1.0 / t_tok, "unit": "tokens/s", "cores": cores, "kind": kind,
+            "sample": "one decode step of 2 of the 32 layers + output head at position 8192, scaled to 32 layers; "
+                      "reference STREAM_DOT tiles of 192 rows and one attention head per task on %d threads" % cores,
+            "ms_per_token": t_tok * 1e3}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    steps, warmup = max(1, args.steps), max(3, args.warmup)
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    config = {"workload": "synthetic Llama-3-8B-shape Q4_K_M greedy decode, batch 1, 8192-token prefilled f16 KV",
+              "n_layer": 32, "hidden": 4096, "heads": "32/8 x 128", "ffn": 14336, "vocab": 128256,
+              "kv_prefill": N_PREFILL, "parallelism": "replicas x%d" % world if world > 1 else "single GPU",
+              "l2": "each step reads 6.0 GB of distinct weights and KV, far larger than L2; no flush needed"}
+
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        cpu_steps = min(steps, 3)
+        r = cpu_reference_arm(cpu_steps, 1)
+        print(json.dumps({
+            "impl": "reference", "metric": METRIC, "value": r["value"], "unit": "tokens/s", "n_gpus": args.gpus,
+            "steps": cpu_steps, "warmup": 1, "ms_per_step": r["ms_per_token"], "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config,
+            "cpu_baseline": {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")},
+            "e2e": {"value": r["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        }))
+        return
+
+    import torch
+    from fast_llm_b200 import capi, synth
+    from fast_llm_b200.decoder import Decoder
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU path); use --impl reference for the CPU arm")
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    ctx = capi.Context(local_rank)
+    cfg = dict(synth.LLAMA3_8B)
+    if steps + warmup + 8 > cfg["max_kv"] - N_PREFILL:
+        cfg["max_kv"] = N_PREFILL + steps + warmup + 8
+    dec = Decoder(ctx, cfg)
+    synth.device_llama(dec, cfg, seed=1234 + rank, n_prefill=N_PREFILL)
+    dec.finalize()
+
+    def barrier():
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(ms):
+        if dist is None:
+            return ms
+        t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    sampler = ClockSampler(local_rank)
+    # ---- value: device-resident feedback loop ----
+    dec.rewind_to(N_PREFILL)
+    dec.run(1, warmup)
+    barrier()
+    sampler.start()
+    ctx.timer_start()
+    toks = dec.run(1, steps)
+    ms_dev = ctx.timer_stop()
+    barrier()
+    ms_dev = max_over_ranks(ms_dev)
+    # ---- e2e: public per-token call with host token in / out ----
+    dec.rewind_to(N_PREFILL)
+    t = 1
+    for _ in range(warmup):
+        t = dec.step(t)
+    barrier()
+    ctx.timer_start()
+    for _ in range(steps):
+        t = dec.step(t)
+    ms_e2e = ctx.timer_stop()
+    barrier()
+    clocks = sampler.stop()
+    ms_e2e = max_over_ranks(ms_e2e)
+    assert ctx.status() == 0, "a kernel reported a status"
+
+    # ---- roofline of the dominant kernel: the step's matvec launches alone ----
+    pos_mid = N_PREFILL + warmup + steps // 2
+    w_bytes, kv_bytes = dec.bytes_per_step(pos_mid)
+    dec.rewind_to(pos_mid)
+    mv_ms, mv_n = dec.time_class(1, 20)
+    at_ms, at_n = dec.time_class(2, 20)
+    ot_ms, ot_n = dec.time_class(4, 20)
+    peak, peak_kind = measured_peaks()
+    achieved = w_bytes / (mv_ms * 1e-3) / 1e9
+    launches = dec.launches_per_step()
+    out = {
+        "metric": METRIC, "value": world * steps / (ms_dev * 1e-3), "unit": "tokens/s", "n_gpus": world,
+        "steps": steps, "warmup": warmup, "ms_per_step": ms_dev / steps, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32 activations / accumulation over Q4_K,Q6_K weights and f16 KV",
+        "data": "synthetic", "config": config,
+        "roofline": {"bound": "hbm", "kernel": "matvec_stream_kernel", "achieved": achieved, "peak": peak,
+                     "peak_source": "MEASURED_PEAKS.json hbm_gbs" if peak_kind == "measured" else "fallback 6.65 TB/s",
+                     "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+                     "bytes_per_launch": w_bytes / mv_n, "launches_per_step": mv_n, "avg_launch_us": mv_ms * 1e3 / mv_n,
+                     "step": {"bytes": w_bytes + kv_bytes, "achieved": (w_bytes + kv_bytes) / (ms_dev / steps * 1e-3) / 1e9,
+                              "frac": (w_bytes + kv_bytes) / (ms_dev / steps * 1e-3) / 1e9 / peak,
+                              "frac_of_8TBs": (w_bytes + kv_bytes) / (ms_dev / steps * 1e-3) / 1e9 / 8000.0},
+                     "attention": {"achieved": kv_bytes / (at_ms * 1e-3) / 1e9, "frac": kv_bytes / (at_ms * 1e-3) / 1e9 / peak,
+                                   "launches_per_step": at_n, "avg_launch_us": at_ms * 1e3 / at_n},
+                     "other_ms_per_step": ot_ms, "other_launches_per_step": ot_n},
+        "e2e": {"value": world * steps / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": 16,
+                "d2h_bytes_per_step": 4},
+        "gpu_launches": launches * steps, "clocks": clocks, "last_token": int(toks[-1]),
+    }
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        r = cpu_reference_arm(1, 1)
+        out["cpu_baseline"] = {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")}
+    dec.close()
+    ctx.close()
+    if dist is not None:
+        dist.destroy_process_group()
+    if rank == 0:
+        print(json.dumps(out))
+
+
+if __name__ == "__main__":
+    main()

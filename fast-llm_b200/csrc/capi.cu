@@ -118,7 +118,7 @@ int fl_b200_free(fl_b200_ctx *c, void *p) {
     return FL_B200_OK;
 }
 int fl_b200_upload(fl_b200_ctx *c, void *dst, const void *src, size_t bytes) {
-    CK(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, c->stream));
+    CK(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDefault, c->stream));   // src: host or device
     CK(cudaStreamSynchronize(c->stream));
     return FL_B200_OK;
 }

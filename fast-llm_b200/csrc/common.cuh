@@ -100,6 +100,14 @@ __device__ __forceinline__ void bulk_g2s(void *dst_smem, const void *src, uint32
         : "memory");
 }
 
+// Same, with the destination given as a 32-bit shared address.
+__device__ __forceinline__ void bulk_g2s_addr(uint32_t dst_smem_addr, const void *src, uint32_t bytes, uint64_t *bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst_smem_addr),
+        "l"(src), "r"(bytes), "r"(smem_u32(bar))
+        : "memory");
+}
+
 // Hint: pull [src, src+bytes) into L2 (16-byte aligned, multiple of 16).
 __device__ __forceinline__ void bulk_prefetch_l2(const void *src, uint32_t bytes) {
     asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");

@@ -4,32 +4,40 @@
 //
 // Streaming kernel (Q4_K and Q6_K, cols a multiple of 2048)
 // ---------------------------------------------------------
-// HBM-bound: every packed weight byte is read exactly once. Each warp owns a
-// private ring of shared-memory stages that its lane 0 keeps filled with 1-D
-// bulk copies (TMA engine, completion on an mbarrier), so the bytes in flight
-// per SM do not depend on registers and no warp ever synchronises with another.
+// HBM-bound by design: every packed weight byte is read exactly once. Each warp
+// owns a private ring of shared-memory stages that its lane 0 keeps filled with
+// 1-D bulk copies (TMA engine, completion on an mbarrier), so the bytes in
+// flight per SM do not depend on registers and no warp synchronises with
+// another one.
 //   stage  = the same 8-super-block column segment (2048 weights) of 4
 //            consecutive rows (a "row quad"): 4 x 1152 B (Q4_K) or 4 x 1680 B
 //            (Q6_K), each a contiguous, 16-byte aligned slice of a packed row;
 //   lane   = one quarter of a super-block (64 weights) of each of the 4 rows:
 //            block = lane/4, quarter = lane%4. The activation slice a lane
-//            needs is the same for all 4 rows, so it is read from shared memory
-//            once per stage (float4, conflict-free thanks to a per-format
-//            permuted copy of x built once per CTA) and reused 4 times;
-//   math   = quants are converted to f32 in registers and multiplied with f32
-//            activations (packed f32x2 FMA), accumulated per 32- or 16-element
-//            sub-block; the sub-block scale (and, for Q4_K, the min times the
-//            precomputed sum of the activations of that sub-block) is applied
-//            once per sub-block, the super-block scale d / dmin once per
-//            quarter. All accumulation is f32 in a fixed order, so results
-//            are reproducible run to run.
+//            needs is the same for the 4 rows: it is read from shared memory
+//            once per stage and reused 4 times.
+//   math   = a first version converted every quant to f32 and used f32 FMAs; ncu
+//            showed it issue-bound at 4.5 instructions per weight (the byte ->
+//            float conversions dominate). The activation is therefore kept in
+//            21-bit fixed point per 256-column block: x = s * (a0*2^14 + a1*2^7
+//            + a2) with balanced base-128 digits a_i in [-64, 63] stored as
+//            int8. The 4/6-bit quants, masked four to a word, are multiplied
+//            with the three digit planes by dp4a (exact int32 sums over a 32- or
+//            16-element sub-block); one int->float conversion per sub-block,
+//            then f32: times the sub-block scale, minus min * (sum of the
+//            sub-block's activations) for Q4_K, times d / dmin and the block's
+//            activation scale. The fixed-point step is amax * 2^-20 of each
+//            256-column block, i.e. about 1e-6 of the row dot in the
+//            S-normalised metric (the canonical f32 sequential dot is itself
+//            8e-6 from the f64 value), far inside the 1e-3 gate; all sums are
+//            in a fixed order, so results are reproducible run to run.
 // A row's 32-lane partials are reduced with shuffles when its last segment is
 // done; lane 0 writes y. Several tensors that share x (Q/K/V, gate/up) run in
 // one launch. The activation can be built on the fly from the residual stream
 // (RMSNorm) or from gate/up (SiLU * up), which removes those launches.
 //
 // Generic kernel: any other shape / format (Q8_0, Q5_0, F32, cols not a
-// multiple of 2048): warp per row, element-wise, same f32 accumulation.
+// multiple of 2048): warp per row, element-wise f32.
 #include "common.cuh"
 #include "kernels.h"
 
@@ -37,94 +45,147 @@ namespace flb {
 
 namespace {
 
-constexpr int kWarps = 12;            // warps per CTA (all are consumers + self-producers)
+constexpr int kWarps = 12;            // warps per CTA (each consumes and feeds its own ring)
 constexpr int kThreads = kWarps * 32;
 constexpr int kRowsPerStage = 4;
 constexpr uint32_t kSeg4 = 8 * 144;   // bytes of one Q4_K segment (8 super-blocks)
 constexpr uint32_t kSeg6 = 8 * 210;   // bytes of one Q6_K segment
 constexpr uint32_t kStage4 = kRowsPerStage * kSeg4;       // ring slot size, Q4_K only
 constexpr uint32_t kStage6 = kRowsPerStage * kSeg6;       // ring slot size when Q6_K is present
+constexpr float kFixMax = 1040000.0f; // largest fixed-point magnitude (63*2^14 + 63*2^7 + 63 = 1040447)
 
-// ---- u8 -> f32 without the conversion pipe --------------------------------
-// Integer-to-float conversion instructions issue at a fraction of the FMA rate,
-// so bytes are turned into floats with a byte permute instead: placing byte k
-// of w under the constant 0x4B000000 gives the float 2^23 + byte exactly; a
-// packed f32x2 add of -2^23 removes the offset for two values at once.
-constexpr float kMagic = 8388608.0f;   // 2^23
-
+// byte K of w as a float, without the integer->float conversion pipe: the byte
+// placed under 0x4B000000 is the float 2^23 + byte.
 template <int K>
-__device__ __forceinline__ float u8_biased(uint32_t w) {   // 2^23 + byte K of w
-    return __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7650u | K));
-}
-template <int K>
-__device__ __forceinline__ float u8f(uint32_t w) { return u8_biased<K>(w) - kMagic; }
-
-__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) { return __ffma2_rn(a, b, c); }
-__device__ __forceinline__ float2 add2(float2 a, float2 b) { return __fadd2_rn(a, b); }
-
-// acc += (bytes of w as floats) . x4
-__device__ __forceinline__ void dot4_u8(uint32_t w, const float4 &x, float2 &acc) {
-    const float2 nm = make_float2(-kMagic, -kMagic);
-    const float2 q01 = add2(make_float2(u8_biased<0>(w), u8_biased<1>(w)), nm);
-    const float2 q23 = add2(make_float2(u8_biased<2>(w), u8_biased<3>(w)), nm);
-    acc = fma2(q01, make_float2(x.x, x.y), acc);
-    acc = fma2(q23, make_float2(x.z, x.w), acc);
+__device__ __forceinline__ float u8f(uint32_t w) {
+    return __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7650u | K)) - 8388608.0f;
 }
 
-// ---- permuted activation layouts -------------------------------------------
-// Both layouts store, for segment s and float4 slot f (0..15), the 32 lanes'
-// float4 contiguously: index ((s*16 + f)*32 + lane)*4 + i.
-// Q4_K: lane = blk*4 + chunk(64); f = (element within chunk)/4: f 0..7 are the
-//       low-nibble sub-block, 8..15 the high-nibble sub-block.
-// Q6_K: lane = blk*4 + half*2 + hq where the quarter covers, in each of the 4
-//       32-element groups g of the half, elements 16*hq .. 16*hq+15;
-//       f = g*4 + (element within the 16)/4.
-__device__ __forceinline__ uint32_t perm4(uint32_t col) {
+// 4 x (u8 * s8) + c
+__device__ __forceinline__ int dp4a_us(uint32_t a_u8x4, uint32_t b_s8x4, int c) {
+    int d;
+    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a_u8x4), "r"(b_s8x4), "r"(c));
+    return d;
+}
+
+// ---- activation layouts in shared memory --------------------------------------
+// For segment s (2048 columns), 16-byte slot f (0..11) and lane l the slot sits at
+// byte ((s*12 + f)*32 + l)*16, so a warp's 16-byte loads are contiguous.
+// slot f = digit*4 + part, digit 0 = most significant.
+// Q4_K: lane = blk*4 + chunk(64 columns); parts 0,1 = the 32 columns of the
+//       low-nibble sub-block (16 each), parts 2,3 = the high-nibble sub-block.
+// Q6_K: lane = blk*4 + half*2 + hq; the quarter covers columns 16*hq..16*hq+15
+//       of each 32-column group g of the half; part = g.
+__device__ __forceinline__ uint32_t pos4(uint32_t col, uint32_t digit) {
     const uint32_t blk = col >> 8, seg = blk >> 3, sbi = blk & 7u;
     const uint32_t c = (col >> 6) & 3u, k = col & 63u;
-    return ((seg * 16 + (k >> 2)) * 32 + sbi * 4 + c) * 4 + (k & 3u);
+    return (((seg * 12 + digit * 4 + (k >> 4)) * 32) + sbi * 4 + c) * 16 + (k & 15u);
 }
-__device__ __forceinline__ uint32_t perm6(uint32_t col) {
+__device__ __forceinline__ uint32_t pos6(uint32_t col, uint32_t digit) {
     const uint32_t blk = col >> 8, seg = blk >> 3, sbi = blk & 7u;
     const uint32_t e = col & 255u;
-    const uint32_t hf = e >> 7, g = (e >> 5) & 3u, hq = (e >> 4) & 1u, j = (e >> 2) & 3u;
-    return ((seg * 16 + g * 4 + j) * 32 + sbi * 4 + hf * 2 + hq) * 4 + (e & 3u);
+    const uint32_t hf = e >> 7, g = (e >> 5) & 3u, hq = (e >> 4) & 1u;
+    return (((seg * 12 + digit * 4 + g) * 32) + sbi * 4 + hf * 2 + hq) * 16 + (e & 15u);
 }
 
 struct Smem {
-    float *x4, *s4;   // Q4_K: permuted x, per-lane sums of its two 32-element sub-blocks
-    float *x6, *s6;   // Q6_K: permuted x, per-lane sums of its four 16-element groups
-    uint64_t *bars;   // [kWarps][stages]
-    uint8_t *ring;    // [kWarps][stages][stage bytes]
+    int8_t *q4;      // Q4_K layout of the digit planes: cols * 3 bytes
+    float *s4;       // per lane: sums of its two 32-column sub-blocks (in units of the block scale)
+    int8_t *q6;      // Q6_K layout: cols * 3 bytes
+    float *s6;       // per lane: sums of its four 16-column groups
+    float *xs;       // activation scale of each 256-column block
+    uint64_t *bars;  // [kWarps][stages]
+    uint8_t *ring;   // [kWarps][stages][stage bytes]
 };
+
+__host__ __device__ inline size_t smem_fixed_bytes(uint32_t cols, bool q4, bool q6) {
+    size_t n = (size_t)cols / 256 * 4;                               // xs
+    if (q4) n += (size_t)cols * 3 + (size_t)cols / 32 * 4;
+    if (q6) n += (size_t)cols * 3 + (size_t)cols / 16 * 4;
+    return n;
+}
 
 __device__ __forceinline__ Smem carve(uint8_t *base, uint32_t cols, bool q4, bool q6, int stages) {
     Smem s;
     uint8_t *p = base;
-    s.x4 = s.s4 = s.x6 = s.s6 = nullptr;
-    if (q4) { s.x4 = (float *)p; p += (size_t)cols * 4; s.s4 = (float *)p; p += (size_t)cols / 32 * 4; }
-    if (q6) { s.x6 = (float *)p; p += (size_t)cols * 4; s.s6 = (float *)p; p += (size_t)cols / 16 * 4; }
+    s.q4 = s.q6 = nullptr;
+    s.s4 = s.s6 = nullptr;
+    if (q4) { s.q4 = (int8_t *)p; p += (size_t)cols * 3; }     // cols*3 is a multiple of 16
+    if (q6) { s.q6 = (int8_t *)p; p += (size_t)cols * 3; }
+    if (q4) { s.s4 = (float *)p; p += (size_t)cols / 32 * 4; }
+    if (q6) { s.s6 = (float *)p; p += (size_t)cols / 16 * 4; }
+    s.xs = (float *)p; p += (size_t)cols / 256 * 4;
+    p = (uint8_t *)(((uintptr_t)p + 7) & ~(uintptr_t)7);
     s.bars = (uint64_t *)p; p += (size_t)kWarps * stages * 8;
     p = (uint8_t *)(((uintptr_t)p + 127) & ~(uintptr_t)127);
     s.ring = p;
     return s;
 }
 
+// ---- shared-memory loads by 32-bit shared address ------------------------------
+// (explicit .shared loads: ring pointers derived from the dynamic shared base
+// would otherwise compile to generic loads)
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint2 lds64(uint32_t addr) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds16(uint32_t addr) {
+    uint16_t v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
+    return v;
+}
+
 // ---- per-stage math ----------------------------------------------------------
 
-// Q4_K quarter (64 weights) of one row: returns its contribution to the dot.
-__device__ __forceinline__ float q4k_quarter(const uint8_t *blk, uint32_t c, const float4 *xs,
-                                             float2 sx) {
-    const uint4 hdr = *reinterpret_cast<const uint4 *>(blk);
-    const uint4 qa = *reinterpret_cast<const uint4 *>(blk + 16 + 32 * c);
-    const uint4 qb = *reinterpret_cast<const uint4 *>(blk + 32 + 32 * c);
-    const uint32_t qw[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
-    float2 pa = make_float2(0.f, 0.f), pb = make_float2(0.f, 0.f);
+// The 12 activation slots of one lane for one segment: v[digit*4 + part].
+struct XSlots { uint4 v[12]; };
+
+__device__ __forceinline__ XSlots load_slots(uint32_t base_addr, uint32_t seg, uint32_t lane) {
+    XSlots s;
+    const uint32_t p = base_addr + ((seg * 12 * 32) + lane) * 16;
+#pragma unroll
+    for (int f = 0; f < 12; ++f) s.v[f] = lds128(p + f * 32 * 16);
+    return s;
+}
+
+__device__ __forceinline__ uint32_t word_of(const uint4 &v, int i) {
+    return i == 0 ? v.x : i == 1 ? v.y : i == 2 ? v.z : v.w;
+}
+
+// digits -> one integer: a0*2^14 + a1*2^7 + a2 (fits int32 for a sub-block)
+__device__ __forceinline__ float fix_to_float(int i0, int i1, int i2) {
+    return (float)((i0 << 14) + (i1 << 7) + i2);
+}
+
+// Q4_K quarter (64 weights) of one row: its contribution to the dot, in units
+// of the block's activation scale. blk: shared address of the super-block.
+__device__ __forceinline__ float q4k_quarter(uint32_t blk, uint32_t c, const XSlots &xq, float2 sx) {
+    const uint4 hdr = lds128(blk);
+    const uint4 qa = lds128(blk + 16 + 32 * c);
+    const uint4 qb = lds128(blk + 32 + 32 * c);
+    int a0 = 0, a1 = 0, a2 = 0, b0 = 0, b1 = 0, b2 = 0;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-        const uint32_t lo = qw[i] & 0x0F0F0F0Fu, hi = qw[i] & 0xF0F0F0F0u;   // hi holds 16 * q
-        dot4_u8(lo, xs[i * 32], pa);
-        dot4_u8(hi, xs[(8 + i) * 32], pb);
+        const uint32_t w = i < 4 ? word_of(qa, i) : word_of(qb, i - 4);
+        const uint32_t lo = w & 0x0F0F0F0Fu, hi = (w >> 4) & 0x0F0F0F0Fu;
+        const int part = i >> 2, wi = i & 3;
+        a0 = dp4a_us(lo, word_of(xq.v[0 + part], wi), a0);
+        a1 = dp4a_us(lo, word_of(xq.v[4 + part], wi), a1);
+        a2 = dp4a_us(lo, word_of(xq.v[8 + part], wi), a2);
+        b0 = dp4a_us(hi, word_of(xq.v[2 + part], wi), b0);
+        b1 = dp4a_us(hi, word_of(xq.v[6 + part], wi), b1);
+        b2 = dp4a_us(hi, word_of(xq.v[10 + part], wi), b2);
     }
     // 6-bit scales / mins of sub-blocks 2c and 2c+1 (packing: fl_q4k_scale_min,
     // src/runtime/quants.h:121-129), both pairs decoded byte-parallel.
@@ -135,59 +196,72 @@ __device__ __forceinline__ float q4k_quarter(const uint8_t *blk, uint32_t c, con
     const uint32_t mn_hi = ((e >> 4) & 0x0F0Fu) | ((b >> 2) & 0x3030u);
     const uint32_t sc = c >= 2 ? sc_hi : sc_lo, mn = c >= 2 ? mn_hi : mn_lo;
     const float d = h2f_bits((uint16_t)(hdr.x & 0xFFFFu)), dmin = h2f_bits((uint16_t)(hdr.x >> 16));
-    const float t = u8f<0>(sc) * (pa.x + pa.y) + u8f<1>(sc) * (0.0625f * (pb.x + pb.y));
+    const float t = u8f<0>(sc) * fix_to_float(a0, a1, a2) + u8f<1>(sc) * fix_to_float(b0, b1, b2);
     const float m = u8f<0>(mn) * sx.x + u8f<1>(mn) * sx.y;
     return d * t - dmin * m;
 }
 
-// Aligned-word fetch from a 2-byte aligned position inside a stage.
-__device__ __forceinline__ uint32_t ldw2(const uint32_t *w, uint32_t sel) {
-    return __byte_perm(w[0], w[1], sel);
-}
-
-// Q6_K quarter (64 weights: 16 elements of each of the 4 groups of one half).
-__device__ __forceinline__ float q6k_quarter(const uint8_t *stage_row, uint32_t sbi, uint32_t qt,
-                                             const float4 *xs, float4 sx) {
+// Q6_K quarter (64 weights: 16 columns of each of the 4 groups of one half).
+// row: shared address of this row's segment in the stage. Blocks are 210 bytes,
+// so odd blocks start 2 bytes past a word boundary: every field is read as the
+// two aligned words around it and realigned with a byte permute.
+__device__ __forceinline__ float q6k_quarter(uint32_t row, uint32_t sbi, uint32_t qt, const XSlots &xq, float4 sx) {
     const uint32_t hf = qt >> 1, hq = qt & 1u;
-    const uint32_t ob = sbi * 210u;                  // block offset: 2 mod 4 for odd blocks
+    const uint32_t ob = sbi * 210u;
     const uint32_t sel = (ob & 2u) ? 0x5432u : 0x3210u;
-    const uint32_t *wbase = reinterpret_cast<const uint32_t *>(stage_row + (ob & ~3u));
-    const uint32_t *wa = wbase + (64 * hf + 16 * hq) / 4;          // ql: groups 0 (low) / 2 (high)
-    const uint32_t *wb = wa + 8;                                   // ql + 32: groups 1 / 3
-    const uint32_t *wh = wbase + (128 + 32 * hf + 16 * hq) / 4;    // qh
-    float2 p0 = make_float2(0.f, 0.f), p1 = p0, p2 = p0, p3 = p0;
+    const uint32_t wbase = row + (ob & ~3u);
+    const uint32_t pa = wbase + 64 * hf + 16 * hq;          // ql: groups 0 (low nibbles) / 2 (high)
+    const uint32_t ph = wbase + 128 + 32 * hf + 16 * hq;    // qh
+    uint32_t wa[5], wb[5], wh[5];
+#pragma unroll
+    for (int j = 0; j < 5; ++j) {
+        wa[j] = lds32(pa + 4 * j);
+        wb[j] = lds32(pa + 32 + 4 * j);                    // ql + 32: groups 1 / 3
+        wh[j] = lds32(ph + 4 * j);
+    }
+    int acc[4][3];
+#pragma unroll
+    for (int g = 0; g < 4; ++g) acc[g][0] = acc[g][1] = acc[g][2] = 0;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-        const uint32_t a = ldw2(wa + j, sel), b = ldw2(wb + j, sel), h = ldw2(wh + j, sel);
-        const uint32_t g0 = (a & 0x0F0F0F0Fu) | ((h << 4) & 0x30303030u);
-        const uint32_t g1 = (b & 0x0F0F0F0Fu) | ((h << 2) & 0x30303030u);
-        const uint32_t g2 = ((a >> 4) & 0x0F0F0F0Fu) | (h & 0x30303030u);
-        const uint32_t g3 = ((b >> 4) & 0x0F0F0F0Fu) | ((h >> 2) & 0x30303030u);
-        dot4_u8(g0, xs[(0 + j) * 32], p0);
-        dot4_u8(g1, xs[(4 + j) * 32], p1);
-        dot4_u8(g2, xs[(8 + j) * 32], p2);
-        dot4_u8(g3, xs[(12 + j) * 32], p3);
+        const uint32_t a = __byte_perm(wa[j], wa[j + 1], sel), b = __byte_perm(wb[j], wb[j + 1], sel);
+        const uint32_t h = __byte_perm(wh[j], wh[j + 1], sel);
+        uint32_t q[4];
+        q[0] = (a & 0x0F0F0F0Fu) | ((h << 4) & 0x30303030u);
+        q[1] = (b & 0x0F0F0F0Fu) | ((h << 2) & 0x30303030u);
+        q[2] = ((a >> 4) & 0x0F0F0F0Fu) | (h & 0x30303030u);
+        q[3] = ((b >> 4) & 0x0F0F0F0Fu) | ((h >> 2) & 0x30303030u);
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+            acc[g][0] = dp4a_us(q[g], word_of(xq.v[0 + g], j), acc[g][0]);
+            acc[g][1] = dp4a_us(q[g], word_of(xq.v[4 + g], j), acc[g][1]);
+            acc[g][2] = dp4a_us(q[g], word_of(xq.v[8 + g], j), acc[g][2]);
+        }
     }
-    const uint8_t *scp = stage_row + ob + 192 + 8 * hf + hq;
-    // int8 scales -> f32 through the same trick: (s ^ 0x80) = s + 128 as an unsigned byte
-    const uint32_t sw = ((uint32_t)scp[0] | ((uint32_t)scp[2] << 8) | ((uint32_t)scp[4] << 16) | ((uint32_t)scp[6] << 24)) ^ 0x80808080u;
-    const float kOff = kMagic + 128.0f;
-    const float d = h2f_bits(*reinterpret_cast<const uint16_t *>(stage_row + ob + 208));
-    // value = d * sc * (q - 32): sum q*x minus 32 * sum x per 16-element group
-    float t = (u8_biased<0>(sw) - kOff) * ((p0.x + p0.y) - 32.f * sx.x);
-    t += (u8_biased<1>(sw) - kOff) * ((p1.x + p1.y) - 32.f * sx.y);
-    t += (u8_biased<2>(sw) - kOff) * ((p2.x + p2.y) - 32.f * sx.z);
-    t += (u8_biased<3>(sw) - kOff) * ((p3.x + p3.y) - 32.f * sx.w);
+    // the 8 int8 scales of this half: bytes hq, hq+2, hq+4, hq+6 are this quarter's
+    const uint32_t ps = wbase + 192 + 8 * hf;
+    const uint32_t s0 = lds32(ps), s1 = lds32(ps + 4), s2 = lds32(ps + 8);
+    const uint32_t lo = __byte_perm(s0, s1, sel), hi = __byte_perm(s1, s2, sel);
+    // (s ^ 0x80) is s + 128 as an unsigned byte
+    const uint32_t sw = __byte_perm(lo, hi, hq ? 0x7531u : 0x6420u) ^ 0x80808080u;
+    const float d = h2f_bits((uint16_t)lds16(row + ob + 208));
+    // value = d * sc * (q - 32): sum q*x minus 32 * sum x per 16-column group
+    float t = (u8f<0>(sw) - 128.f) * (fix_to_float(acc[0][0], acc[0][1], acc[0][2]) - 32.f * sx.x);
+    t += (u8f<1>(sw) - 128.f) * (fix_to_float(acc[1][0], acc[1][1], acc[1][2]) - 32.f * sx.y);
+    t += (u8f<2>(sw) - 128.f) * (fix_to_float(acc[2][0], acc[2][1], acc[2][2]) - 32.f * sx.z);
+    t += (u8f<3>(sw) - 128.f) * (fix_to_float(acc[3][0], acc[3][1], acc[3][2]) - 32.f * sx.w);
     return d * t;
 }
 
 // ---- the streaming kernel ---------------------------------------------------
 
+// A row quad of one of the launch's tensors.
 struct QuadRef {
-    const uint8_t *row[kRowsPerStage];
+    const uint8_t *row0;   // first row of the quad
     float *y;
     const float *resid;
-    uint32_t r0, rows;
+    uint32_t r0, rows;     // first row index, rows in the tensor
+    uint32_t rb;           // bytes per row
     int fmt;
 };
 
@@ -202,18 +276,22 @@ __device__ __forceinline__ QuadRef locate_quad(const MatvecArgs &a, uint32_t qua
         base += nq;
     }
     const MatvecTensor &t = a.t[ti];
-    const uint64_t rb = row_bytes(t.fmt, a.cols);
+    q.rb = (uint32_t)row_bytes(t.fmt, a.cols);
     q.r0 = (quad - base) * kRowsPerStage;
     q.rows = t.rows;
     q.fmt = t.fmt;
     q.y = t.y;
     q.resid = t.resid;
-#pragma unroll
-    for (int r = 0; r < kRowsPerStage; ++r) {
-        const uint32_t rr = q.r0 + r < t.rows ? q.r0 + r : t.rows - 1;   // clamp: tail rows re-read the last row
-        q.row[r] = t.w + (uint64_t)rr * rb;
-    }
+    q.row0 = t.w + (uint64_t)q.r0 * q.rb;
     return q;
+}
+
+// One activation value (column c) as the selected prologue defines it.
+__device__ __forceinline__ float act_value(const MatvecArgs &a, uint32_t c, float inv_rms) {
+    float v = a.x[c];
+    if (a.x_mode == MV_X_RMSNORM) v = v * inv_rms * a.wnorm[c];
+    else if (a.x_mode == MV_X_SILU_MUL) v = (v / (1.0f + expf(-v))) * a.x2[c];
+    return v;
 }
 
 __global__ void __launch_bounds__(kThreads, 1)
@@ -223,36 +301,47 @@ matvec_stream_kernel(const MatvecArgs a, const uint32_t total_quads, const int s
     const Smem sm = carve(smem_raw, a.cols, use_q4 != 0, use_q6 != 0, stages);
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
     const uint32_t nseg = a.cols / 2048u;
-    const uint32_t kStageBytes = use_q6 ? kStage6 : kStage4;
+    const uint32_t stage_bytes = use_q6 ? kStage6 : kStage4;
     __shared__ float red[kWarps];
-    __shared__ float inv_rms;
+    __shared__ float inv_rms_s;
 
     uint64_t *bars = sm.bars + warp * stages;
-    uint8_t *ring = sm.ring + (size_t)warp * stages * kStageBytes;
+    const uint32_t ring = smem_u32(sm.ring) + warp * stages * stage_bytes;   // shared address
     if (lane == 0)
         for (int s = 0; s < stages; ++s) mbar_init(&bars[s], 1);
     fence_barrier_init();
     __syncwarp();
 
-    // This warp's quads: gw, gw + W, ... ; its stage i is (quad i / nseg, segment i % nseg).
+    // This warp's quads: gw, gw + W, ... ; per quad nseg stages (one per column segment).
     const uint32_t gw = blockIdx.x * kWarps + warp, W = gridDim.x * kWarps;
     const uint32_t my_quads = gw < total_quads ? (total_quads - gw + W - 1) / W : 0;
     const uint32_t my_stages = my_quads * nseg;
 
-    auto issue = [&](uint32_t i) {   // lane 0 only
-        const QuadRef q = locate_quad(a, gw + (i / nseg) * W);
-        const uint32_t seg = i % nseg, slot = i % stages;
-        const uint32_t sb = q.fmt == FMT_Q4_K ? kSeg4 : kSeg6;
-        mbar_arrive_expect_tx(&bars[slot], kRowsPerStage * sb);
+    // Producer state (meaningful in lane 0): next stage to request.
+    uint32_t p_i = 0, p_seg = 0, p_slot = 0, p_quad = gw;
+    QuadRef pq;
+    auto issue = [&]() {   // lane 0 only; requests stage p_i and advances
+        if (p_seg == 0) pq = locate_quad(a, p_quad);
+        const uint32_t sb = pq.fmt == FMT_Q4_K ? kSeg4 : kSeg6;
+        const uint32_t dst = ring + p_slot * stage_bytes;
+        const uint8_t *src = pq.row0 + (size_t)p_seg * sb;
+        mbar_arrive_expect_tx(&bars[p_slot], kRowsPerStage * sb);
 #pragma unroll
-        for (int r = 0; r < kRowsPerStage; ++r)
-            bulk_g2s(ring + (size_t)slot * kStageBytes + r * sb, q.row[r] + (size_t)seg * sb, sb, &bars[slot]);
+        for (int r = 0; r < kRowsPerStage; ++r) {
+            // rows past the end of the tensor re-read its last row (their results are dropped)
+            const uint32_t rr = pq.r0 + r < pq.rows ? r : pq.rows - 1 - pq.r0;
+            bulk_g2s_addr(dst + r * sb, src + (size_t)rr * pq.rb, sb, &bars[p_slot]);
+        }
+        ++p_i;
+        if (++p_slot == (uint32_t)stages) p_slot = 0;
+        if (++p_seg == nseg) { p_seg = 0; p_quad += W; }
     };
     // Weights do not depend on the activation: start streaming before x is built.
     if (lane == 0)
-        for (uint32_t i = 0; i < (uint32_t)stages && i < my_stages; ++i) issue(i);
+        while (p_i < (uint32_t)stages && p_i < my_stages) issue();
 
-    // ---- build the activation in shared memory (permuted, per format) ----
+    // ---- build the fixed-point activation in shared memory ----
+    float inv_rms = 1.f;
     if (a.x_mode == MV_X_RMSNORM) {
         float ss = 0.f;
         for (uint32_t c = tid; c < a.cols; c += kThreads) { const float v = a.x[c]; ss += v * v; }
@@ -262,67 +351,97 @@ matvec_stream_kernel(const MatvecArgs a, const uint32_t total_quads, const int s
         if (tid == 0) {
             float t = 0.f;
             for (int w = 0; w < kWarps; ++w) t += red[w];
-            inv_rms = 1.0f / sqrtf(t / (float)a.cols + a.eps);
+            inv_rms_s = 1.0f / sqrtf(t / (float)a.cols + a.eps);
         }
         __syncthreads();
+        inv_rms = inv_rms_s;
     }
-    for (uint32_t c = tid; c < a.cols; c += kThreads) {
-        float v = a.x[c];
-        if (a.x_mode == MV_X_RMSNORM) v = v * inv_rms * a.wnorm[c];
-        else if (a.x_mode == MV_X_SILU_MUL) v = (v / (1.0f + expf(-v))) * a.x2[c];
-        if (use_q4) sm.x4[perm4(c)] = v;
-        if (use_q6) sm.x6[perm6(c)] = v;
-        if (a.xn_out != nullptr && blockIdx.x == 0) a.xn_out[c] = v;
-    }
-    __syncthreads();
-    if (use_q4) {   // sums of each lane's two 32-element sub-blocks
-        for (uint32_t i = tid; i < a.cols / 32; i += kThreads) {
-            const uint32_t seg = i >> 6, ln = (i >> 1) & 31u, which = i & 1u;
-            const float *p = sm.x4 + ((size_t)(seg * 16 + which * 8) * 32 + ln) * 4;
-            float s = 0.f;
-            for (int f = 0; f < 8; ++f) { const float4 v = *(const float4 *)(p + f * 128); s += (v.x + v.y) + (v.z + v.w); }
-            sm.s4[i] = s;
+    // One warp per 256-column block; lane l holds columns 8l .. 8l+7 of the block.
+    for (uint32_t blk = warp; blk < a.cols / 256; blk += kWarps) {
+        const uint32_t c0 = blk * 256 + lane * 8;
+        float v[8];
+        float amax = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            v[i] = act_value(a, c0 + i, inv_rms);
+            amax = fmaxf(amax, fabsf(v[i]));
         }
-    }
-    if (use_q6) {   // sums of each lane's four 16-element groups
-        for (uint32_t i = tid; i < a.cols / 16; i += kThreads) {
-            const uint32_t seg = i >> 7, ln = (i >> 2) & 31u, g = i & 3u;
-            const float *p = sm.x6 + ((size_t)(seg * 16 + g * 4) * 32 + ln) * 4;
-            float s = 0.f;
-            for (int f = 0; f < 4; ++f) { const float4 v = *(const float4 *)(p + f * 128); s += (v.x + v.y) + (v.z + v.w); }
-            sm.s6[i] = s;
+        if (a.xn_out != nullptr && blockIdx.x == 0) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) a.xn_out[c0 + i] = v[i];
         }
+        amax = warp_max(amax);
+        const float s = amax > 0.f ? amax / kFixMax : 1.0f;
+        const float inv_s = 1.0f / s;
+        int sum = 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int X = __float2int_rn(v[i] * inv_s);          // |X| <= 1040000
+            const int d2 = ((X + 64) & 127) - 64;                // balanced base-128 digits
+            const int X1 = (X - d2) >> 7;
+            const int d1 = ((X1 + 64) & 127) - 64;
+            const int d0 = (X1 - d1) >> 7;
+            sum += X;
+            const uint32_t c = c0 + i;
+            if (use_q4) {
+                sm.q4[pos4(c, 0)] = (int8_t)d0; sm.q4[pos4(c, 1)] = (int8_t)d1; sm.q4[pos4(c, 2)] = (int8_t)d2;
+            }
+            if (use_q6) {
+                sm.q6[pos6(c, 0)] = (int8_t)d0; sm.q6[pos6(c, 1)] = (int8_t)d1; sm.q6[pos6(c, 2)] = (int8_t)d2;
+            }
+        }
+        // sums over 16 columns (lane pairs) and 32 columns (lane quads), exact in int32
+        const int s16 = sum + __shfl_xor_sync(0xffffffffu, sum, 1);
+        const int s32 = s16 + __shfl_xor_sync(0xffffffffu, s16, 2);
+        const uint32_t seg = blk >> 3, sbi = blk & 7u;
+        if (use_q4 && (lane & 3u) == 0) {
+            // 32-column sub-block j = lane / 4 -> consumer lane sbi*4 + j/2, component j & 1
+            const uint32_t j = lane >> 2;
+            sm.s4[((seg * 32 + sbi * 4 + (j >> 1)) << 1) + (j & 1u)] = (float)s32;
+        }
+        if (use_q6 && (lane & 1u) == 0) {
+            // 16-column run r = lane / 2 (0..15): half = r/8, group g = (r/2)%4, hq = r%2
+            const uint32_t r = lane >> 1, hf = r >> 3, g = (r >> 1) & 3u, hq = r & 1u;
+            sm.s6[((seg * 32 + sbi * 4 + hf * 2 + hq) << 2) + g] = (float)s16;
+        }
+        if (lane == 0) sm.xs[blk] = s;
     }
     __syncthreads();
 
     // ---- consume ----
+    const uint32_t q4_addr = use_q4 ? smem_u32(sm.q4) : 0, q6_addr = use_q6 ? smem_u32(sm.q6) : 0;
     float acc[kRowsPerStage] = {0.f, 0.f, 0.f, 0.f};
     const uint32_t sbi = lane >> 2, qt = lane & 3u;
+    uint32_t seg = 0, slot = 0, parity = 0, quad = gw;
     QuadRef cur;
     for (uint32_t i = 0; i < my_stages; ++i) {
-        const uint32_t seg = i % nseg, slot = i % stages;
-        if (seg == 0) cur = locate_quad(a, gw + (i / nseg) * W);
-        if (!mbar_wait_bounded(&bars[slot], (i / stages) & 1u, a.status)) return;
-        const uint8_t *st = ring + (size_t)slot * kStageBytes;
+        if (seg == 0) cur = locate_quad(a, quad);
+        const float xs = sm.xs[seg * 8 + sbi];
+        const uint32_t st = ring + slot * stage_bytes;
         if (cur.fmt == FMT_Q4_K) {
-            const float4 *xs = reinterpret_cast<const float4 *>(sm.x4) + (size_t)seg * 16 * 32 + lane;
+            const XSlots xq = load_slots(q4_addr, seg, lane);
             const float2 sx = reinterpret_cast<const float2 *>(sm.s4)[seg * 32 + lane];
+            if (!mbar_wait_bounded(&bars[slot], parity, a.status)) return;
 #pragma unroll
             for (int r = 0; r < kRowsPerStage; ++r)
-                acc[r] += q4k_quarter(st + r * kSeg4 + sbi * 144, qt, xs, sx);
+                acc[r] = fmaf(xs, q4k_quarter(st + r * kSeg4 + sbi * 144, qt, xq, sx), acc[r]);
         } else {
-            const float4 *xs = reinterpret_cast<const float4 *>(sm.x6) + (size_t)seg * 16 * 32 + lane;
+            const XSlots xq = load_slots(q6_addr, seg, lane);
             const float4 sx = reinterpret_cast<const float4 *>(sm.s6)[seg * 32 + lane];
+            if (!mbar_wait_bounded(&bars[slot], parity, a.status)) return;
 #pragma unroll
             for (int r = 0; r < kRowsPerStage; ++r)
-                acc[r] += q6k_quarter(st + r * kSeg6, sbi, qt, xs, sx);
+                acc[r] = fmaf(xs, q6k_quarter(st + r * kSeg6, sbi, qt, xq, sx), acc[r]);
         }
         __syncwarp();
-        if (lane == 0 && i + stages < my_stages) {
+        if (lane == 0 && p_i < my_stages) {
             fence_proxy_async_smem();
-            issue(i + stages);
+            issue();
         }
-        if (seg == nseg - 1) {
+        if (++slot == (uint32_t)stages) { slot = 0; parity ^= 1u; }
+        if (++seg == nseg) {
+            seg = 0;
+            quad += W;
 #pragma unroll
             for (int r = 0; r < kRowsPerStage; ++r) {
                 const float v = warp_sum(acc[r]);
@@ -410,13 +529,10 @@ bool matvec_is_streaming(int fmt, uint32_t cols) {
 }
 
 size_t matvec_smem_bytes(uint32_t cols, bool q4, bool q6, int *stages_out) {
-    size_t fixed = 0;
-    if (q4) fixed += (size_t)cols * 4 + (size_t)cols / 32 * 4;
-    if (q6) fixed += (size_t)cols * 4 + (size_t)cols / 16 * 4;
-    fixed += 128;   // ring alignment slack
+    const size_t fixed = smem_fixed_bytes(cols, q4, q6) + 8 + 128;   // + alignment slack
     const size_t limit = 227 * 1024 - 1024;   // leave room for static shared memory
-    int stages = 4;
     const size_t slot = q6 ? kStage6 : kStage4;
+    int stages = 4;
     while (stages > 1 && fixed + (size_t)kWarps * stages * (8 + slot) > limit) --stages;
     if (stages_out) *stages_out = stages;
     return fixed + (size_t)kWarps * stages * (8 + slot);

@@ -142,3 +142,71 @@ def model_weight_bytes(cfg, recipe=Q4_K_M):
     total = cfg["n_layer"] * (total + 2 * cfg["n_embd"] * 4)
     total += cfg["n_vocab"] * capi.row_bytes(recipe["output"], cfg["n_embd"]) + cfg["n_embd"] * 4
     return total
+
+
+# ---- device-side generators (benchmark set-up) --------------------------------
+# Same layouts and value distributions as above, drawn with torch on the GPU so
+# that the 4.9 GB model of the benchmark is ready in about a second instead of
+# half a minute of host generation + upload. (Different random stream than the
+# numpy generators: use those whenever the CPU oracle must see the same bytes.)
+
+def device_quant_tensor(fmt, rows, cols, gen):
+    import torch
+    nb = rows * (cols // capi.BLK_ELEMS[fmt])
+    bb = capi.BLK_BYTES[fmt]
+    dev = gen.device
+    w = torch.randint(0, 256, (nb, bb), dtype=torch.uint8, device=dev, generator=gen)
+
+    def f16_uniform(lo, hi):
+        return (torch.rand(nb, device=dev, generator=gen) * (hi - lo) + lo).half().view(torch.uint8).reshape(nb, 2)
+
+    if fmt == capi.Q4_K:
+        w[:, 0:2] = f16_uniform(0.001, 0.02)
+        w[:, 2:4] = f16_uniform(0.0, 0.01)
+    elif fmt == capi.Q6_K:
+        w[:, 192:208] = torch.randint(-63, 64, (nb, 16), dtype=torch.int8, device=dev, generator=gen).view(torch.uint8)
+        w[:, 208:210] = f16_uniform(0.001, 0.02)
+    elif fmt == capi.Q8_0:
+        w[:, 0:2] = f16_uniform(0.001, 0.02)
+    else:
+        raise ValueError(fmt)
+    return w.reshape(rows, -1)
+
+
+def device_llama(dec, cfg, seed, n_prefill, kv_std=0.1, recipe=Q4_K_M):
+    """Fills a fast_llm_b200.decoder.Decoder with a synthetic model generated on
+    its device and prefills n_prefill KV positions ~ N(0, kv_std). Returns the
+    list of tensors kept alive."""
+    import ctypes as C
+    import torch
+    dev = torch.device("cuda", dec.ctx.device)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(seed)
+    keep = []
+    shapes = layer_shapes(cfg)
+    for l in range(cfg["n_layer"]):
+        for i, name in enumerate(LAYER_TENSORS):
+            rows, cols = shapes[name]
+            w = device_quant_tensor(recipe[name], rows, cols, gen)
+            dec.set_layer_tensor(l, i, recipe[name], w)
+        an = torch.rand(cfg["n_embd"], device=dev, generator=gen) * 0.2 + 0.9
+        fn = torch.rand(cfg["n_embd"], device=dev, generator=gen) * 0.2 + 0.9
+        dec.set_layer_norms(l, an, fn)
+        if n_prefill:
+            kp, vp = dec.kv_ptrs(l)
+            for ptr in (kp, vp):
+                t = (torch.randn((cfg["n_kv_head"], n_prefill, cfg["head_dim"]), device=dev, generator=gen)
+                     * kv_std).half()
+                full = torch.zeros((cfg["n_kv_head"], cfg["max_kv"], cfg["head_dim"]), dtype=torch.float16, device=dev)
+                full[:, :n_prefill] = t
+                torch.cuda.synchronize(dev)
+                # copy into the decoder's cache (the source may be a device pointer)
+                capi._ck(dec.lib.fl_b200_upload(dec.ctx._h, C.c_void_p(ptr), C.c_void_p(full.data_ptr()),
+                                                C.c_size_t(full.numel() * 2)))
+    for which, name in ((capi.G_TOK_EMBD, "tok_embd"), (capi.G_OUTPUT, "output")):
+        w = device_quant_tensor(recipe[name], cfg["n_vocab"], cfg["n_embd"], gen)
+        dec.set_global(which, recipe[name], w)
+    on = torch.rand(cfg["n_embd"], device=dev, generator=gen) * 0.2 + 0.9
+    dec.set_out_norm(on)
+    torch.cuda.synchronize(dev)
+    return keep

@@ -69,6 +69,7 @@ void *fl_b200_stream(fl_b200_ctx *ctx);
  * unified-memory Arena, src/runtime/arena.cpp:54-74, for the GPU side). */
 int fl_b200_malloc(fl_b200_ctx *ctx, size_t bytes, void **dev_out);
 int fl_b200_free(fl_b200_ctx *ctx, void *dev);
+/* src may be a host pointer or a device pointer (unified addressing). */
 int fl_b200_upload(fl_b200_ctx *ctx, void *dst_dev, const void *src_host, size_t bytes);
 int fl_b200_download(fl_b200_ctx *ctx, void *dst_host, const void *src_dev, size_t bytes);
 int fl_b200_memset(fl_b200_ctx *ctx, void *dst_dev, int value, size_t bytes);
