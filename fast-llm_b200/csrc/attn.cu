@@ -52,6 +52,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnArg
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
     const uint32_t split = blockIdx.x, hkv = blockIdx.y, b = blockIdx.z;
     const uint32_t group = a.n_q_head / a.n_kv_head;   // == kGroup (checked on the host)
+    griddep_wait();   // *pos, q and the appended K/V row come from the previous kernels
     const uint32_t kv_len = a.pos ? (uint32_t)(*a.pos) + 1u : a.kv_len;
 
     const uint32_t tiles_total = (kv_len + kTile - 1) / kTile;
@@ -68,6 +69,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnArg
         sm.is_last = 0;
     }
     fence_barrier_init();
+    griddep_launch_dependents();
     __syncthreads();
 
     auto issue = [&](uint32_t i) {   // thread 0 only: tile t0 + i into slot i % kStages
@@ -281,8 +283,7 @@ cudaError_t launch_attn_decode(const AttnArgs &a, cudaStream_t stream) {
         return cudaErrorInvalidValue;
     if (a.pos == nullptr && a.kv_len == 0) return cudaErrorInvalidValue;
     const dim3 grid(a.n_splits, a.n_kv_head, a.batch);
-    attn_decode_kernel<<<grid, kAttnThreads, sizeof(AttnSmem), stream>>>(a);
-    return cudaGetLastError();
+    return launch_kernel(attn_decode_kernel, grid, dim3(kAttnThreads), sizeof(AttnSmem), stream, a.pdl != 0, a);
 }
 
 } // namespace flb

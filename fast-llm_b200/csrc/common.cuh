@@ -113,6 +113,18 @@ __device__ __forceinline__ void bulk_prefetch_l2(const void *src, uint32_t bytes
     asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
 }
 
+// Programmatic dependent launch. launch_dependents lets the next kernel of the
+// stream start its independent preamble (barrier set-up, weight prefetch) while
+// this one is still running; wait blocks until the previous kernel has completed
+// and its writes are visible. Both are no-ops for a kernel launched without the
+// programmatic-serialization attribute.
+__device__ __forceinline__ void griddep_launch_dependents() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void griddep_wait() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
@@ -129,5 +141,23 @@ __device__ __forceinline__ float h2f_bits(uint16_t h) {
 }
 
 #endif // __CUDACC__
+
+// Launch helper: optional programmatic dependent launch (the kernel must call
+// griddep_wait() before it touches anything the previous kernel wrote).
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                 bool pdl, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = pdl ? 1 : 0;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
 
 } // namespace flb

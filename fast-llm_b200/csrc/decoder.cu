@@ -31,6 +31,8 @@ struct Tensor { int fmt = -1; const uint8_t *w = nullptr; };
 // After a step: token <- argmax, history[count++] <- argmax, pos += 1.
 __global__ void advance_kernel(int32_t *token, const int32_t *next, int32_t *pos, int32_t *hist,
                                uint32_t *hist_n, uint32_t hist_cap) {
+    griddep_launch_dependents();
+    griddep_wait();
     if (threadIdx.x == 0 && blockIdx.x == 0) {
         const int32_t t = *next;
         *token = t;
@@ -68,6 +70,11 @@ struct fl_b200_decoder {
     bool finalized = false;
 };
 
+// Every kernel of the step after the embedding lookup is launched with
+// programmatic dependent launch: its preamble (barrier set-up, weight prefetch
+// into shared memory) overlaps the tail of the kernel before it.
+static int kPdl = 1;
+
 // Kernel classes, for timing one class of the step in isolation.
 enum : uint32_t { K_MATVEC = 1u, K_ATTN = 2u, K_OTHER = 4u, K_ALL = 7u };
 
@@ -76,7 +83,7 @@ static int enqueue_step(fl_b200_decoder *d, cudaStream_t s, uint32_t *n_launch, 
     fl_b200_ctx *ctx = d->ctx;
     const uint32_t E = c.n_embd, D = c.head_dim, QD = c.n_head * D, KD = c.n_kv_head * D;
     uint32_t n = 0;
-    if (mask & K_OTHER) { CK(launch_embed(d->tok_embd.fmt, d->tok_embd.w, d->d_token, E, d->xa, s)); ++n; }
+    if (mask & K_OTHER) { CK(launch_embed(d->tok_embd.fmt, d->tok_embd.w, d->d_token, E, d->xa, s, false)); ++n; }
     for (uint32_t l = 0; l < c.n_layer; ++l) {
         const Tensor *w = &d->lw[(size_t)l * 7];
         {   // RMSNorm + Q/K/V
@@ -86,14 +93,14 @@ static int enqueue_step(fl_b200_decoder *d, cudaStream_t s, uint32_t *n_launch, 
             a.t[1] = {w[FL_B200_T_WK].w, d->k, nullptr, KD, w[FL_B200_T_WK].fmt};
             a.t[2] = {w[FL_B200_T_WV].w, d->v, nullptr, KD, w[FL_B200_T_WV].fmt};
             a.x = d->xa; a.wnorm = d->attn_norm[l]; a.eps = c.eps; a.cols = E;
-            a.x_mode = MV_X_RMSNORM; a.status = ctx->status;
+            a.x_mode = MV_X_RMSNORM; a.status = ctx->status; a.pdl = kPdl;
             if (mask & K_MATVEC) { CK(launch_matvec(a, ctx->sms, s)); ++n; }
         }
         {
             RopeAppendArgs a{};
             a.q = d->q; a.k = d->k; a.v = d->v; a.kcache = d->kc[l]; a.vcache = d->vc[l]; a.pos = d->d_pos;
             a.n_q_head = c.n_head; a.n_kv_head = c.n_kv_head; a.head_dim = D; a.kv_stride = c.max_kv;
-            a.theta_scale = powf(c.rope_base, -2.0f / (float)D);
+            a.theta_scale = powf(c.rope_base, -2.0f / (float)D); a.pdl = kPdl;
             if (mask & K_OTHER) { CK(launch_rope_append(a, s)); ++n; }
         }
         {
@@ -102,14 +109,14 @@ static int enqueue_step(fl_b200_decoder *d, cudaStream_t s, uint32_t *n_launch, 
             a.pos = d->d_pos; a.kv_len = 0; a.kv_stride = c.max_kv;
             a.batch_stride = (uint64_t)c.n_kv_head * c.max_kv * D;
             a.n_q_head = c.n_head; a.n_kv_head = c.n_kv_head; a.batch = 1; a.n_splits = d->n_splits;
-            a.scale = 1.0f / sqrtf((float)D); a.status = ctx->status;
+            a.scale = 1.0f / sqrtf((float)D); a.status = ctx->status; a.pdl = kPdl;
             if (mask & K_ATTN) { CK(launch_attn_decode(a, s)); ++n; }
         }
         {   // O projection + residual: xb = xa + Wo att
             MatvecArgs a{};
             a.n_tensors = 1;
             a.t[0] = {w[FL_B200_T_WO].w, d->xb, d->xa, E, w[FL_B200_T_WO].fmt};
-            a.x = d->att; a.cols = QD; a.x_mode = MV_X_PLAIN; a.status = ctx->status;
+            a.x = d->att; a.cols = QD; a.x_mode = MV_X_PLAIN; a.status = ctx->status; a.pdl = kPdl;
             if (mask & K_MATVEC) { CK(launch_matvec(a, ctx->sms, s)); ++n; }
         }
         {   // RMSNorm + gate / up
@@ -118,14 +125,14 @@ static int enqueue_step(fl_b200_decoder *d, cudaStream_t s, uint32_t *n_launch, 
             a.t[0] = {w[FL_B200_T_GATE].w, d->g, nullptr, c.n_ff, w[FL_B200_T_GATE].fmt};
             a.t[1] = {w[FL_B200_T_UP].w, d->u, nullptr, c.n_ff, w[FL_B200_T_UP].fmt};
             a.x = d->xb; a.wnorm = d->ffn_norm[l]; a.eps = c.eps; a.cols = E;
-            a.x_mode = MV_X_RMSNORM; a.status = ctx->status;
+            a.x_mode = MV_X_RMSNORM; a.status = ctx->status; a.pdl = kPdl;
             if (mask & K_MATVEC) { CK(launch_matvec(a, ctx->sms, s)); ++n; }
         }
         {   // SiLU(gate) * up, down projection + residual: xa = xb + Wdown h
             MatvecArgs a{};
             a.n_tensors = 1;
             a.t[0] = {w[FL_B200_T_DOWN].w, d->xa, d->xb, E, w[FL_B200_T_DOWN].fmt};
-            a.x = d->g; a.x2 = d->u; a.cols = c.n_ff; a.x_mode = MV_X_SILU_MUL; a.status = ctx->status;
+            a.x = d->g; a.x2 = d->u; a.cols = c.n_ff; a.x_mode = MV_X_SILU_MUL; a.status = ctx->status; a.pdl = kPdl;
             if (mask & K_MATVEC) { CK(launch_matvec(a, ctx->sms, s)); ++n; }
         }
     }
@@ -134,16 +141,16 @@ static int enqueue_step(fl_b200_decoder *d, cudaStream_t s, uint32_t *n_launch, 
         a.n_tensors = 1;
         a.t[0] = {d->output.w, d->logits, nullptr, c.n_vocab, d->output.fmt};
         a.x = d->xa; a.wnorm = d->out_norm; a.eps = c.eps; a.cols = E;
-        a.x_mode = MV_X_RMSNORM; a.status = ctx->status; a.xn_out = d->xn_final;
+        a.x_mode = MV_X_RMSNORM; a.status = ctx->status; a.pdl = kPdl; a.xn_out = d->xn_final;
         if (mask & K_MATVEC) { CK(launch_matvec(a, ctx->sms, s)); ++n; }
     }
     if (mask & K_OTHER) {
         CK(launch_argmax(d->logits, c.n_vocab, d->d_next, d->d_margin, ctx->argmax_scratch, ctx->argmax_ticket,
-                         ctx->sms, s)); ++n;
+                         ctx->sms, s, kPdl != 0)); ++n;
     }
     if (mask == K_ALL) {   // state only advances in the real step
-        advance_kernel<<<1, 32, 0, s>>>(d->d_token, d->d_next, d->d_pos, d->d_hist, d->d_hist_n, d->hist_cap);
-        CK(cudaGetLastError()); ++n;
+        CK(launch_kernel(advance_kernel, dim3(1), dim3(32), 0, s, kPdl != 0, d->d_token, d->d_next, d->d_pos, d->d_hist,
+                         d->d_hist_n, d->hist_cap)); ++n;
     }
     if (n_launch) *n_launch = n;
     return FL_B200_OK;

@@ -31,6 +31,8 @@ template <int FMT>
 __global__ void __launch_bounds__(256) dequant_kernel(const uint8_t *__restrict__ w, float *__restrict__ out,
                                                       uint64_t n4, const int32_t *__restrict__ sel,
                                                       uint64_t sel_stride) {
+    griddep_launch_dependents();
+    griddep_wait();
     // Row gather (embedding lookup): start at row *sel of a table whose rows are
     // sel_stride bytes apart.
     if (sel != nullptr) w += (uint64_t)(*sel) * sel_stride;
@@ -121,17 +123,17 @@ cudaError_t launch_dequant(int fmt, const void *w, uint64_t rows, uint32_t cols,
 // Embedding lookup: out[0..cols) = dequant(row *token of the table), the device
 // version of the host step in Decoder::step_batch (src/model/decoder.cpp:1194-1201).
 cudaError_t launch_embed(int fmt, const void *table, const int32_t *token, uint32_t cols, float *out,
-                         cudaStream_t stream) {
+                         cudaStream_t stream, bool pdl) {
     const uint64_t n4 = cols / 4;
     const int grid = (int)((n4 + 255) / 256);
     const uint8_t *wp = static_cast<const uint8_t *>(table);
     const uint64_t rb = row_bytes(fmt, cols);
     switch (fmt) {
-    case FMT_F32: dequant_kernel<FMT_F32><<<grid, 256, 0, stream>>>(wp, out, n4, token, rb); break;
-    case FMT_Q8_0: dequant_kernel<FMT_Q8_0><<<grid, 256, 0, stream>>>(wp, out, n4, token, rb); break;
-    case FMT_Q5_0: dequant_kernel<FMT_Q5_0><<<grid, 256, 0, stream>>>(wp, out, n4, token, rb); break;
-    case FMT_Q4_K: dequant_kernel<FMT_Q4_K><<<grid, 256, 0, stream>>>(wp, out, n4, token, rb); break;
-    case FMT_Q6_K: dequant_kernel<FMT_Q6_K><<<grid, 256, 0, stream>>>(wp, out, n4, token, rb); break;
+    case FMT_F32: return launch_kernel(dequant_kernel<FMT_F32>, dim3(grid), dim3(256), 0, stream, pdl, wp, out, n4, token, rb);
+    case FMT_Q8_0: return launch_kernel(dequant_kernel<FMT_Q8_0>, dim3(grid), dim3(256), 0, stream, pdl, wp, out, n4, token, rb);
+    case FMT_Q5_0: return launch_kernel(dequant_kernel<FMT_Q5_0>, dim3(grid), dim3(256), 0, stream, pdl, wp, out, n4, token, rb);
+    case FMT_Q4_K: return launch_kernel(dequant_kernel<FMT_Q4_K>, dim3(grid), dim3(256), 0, stream, pdl, wp, out, n4, token, rb);
+    case FMT_Q6_K: return launch_kernel(dequant_kernel<FMT_Q6_K>, dim3(grid), dim3(256), 0, stream, pdl, wp, out, n4, token, rb);
     default: return cudaErrorInvalidValue;
     }
     return cudaGetLastError();

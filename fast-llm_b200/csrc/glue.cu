@@ -54,6 +54,8 @@ __global__ void silu_mul_kernel(const float *__restrict__ g, const float *__rest
 // most a few ulp) followed by the f16 KV append (fl_op_kv_append,
 // decode_params.h:162-175, with the cache kept in f16, head-major).
 __global__ void __launch_bounds__(128) rope_append_kernel(const RopeAppendArgs a) {
+    griddep_launch_dependents();
+    griddep_wait();
     const uint32_t half = a.head_dim / 2;
     const uint32_t t = blockIdx.x * blockDim.x + threadIdx.x;
     const uint32_t n_rot_heads = (a.q ? a.n_q_head : 0) + a.n_kv_head;
@@ -112,6 +114,8 @@ __device__ __forceinline__ Top top_warp(Top t) {
 
 __global__ void __launch_bounds__(256) argmax_kernel(const float *__restrict__ lg, uint32_t n, int32_t *out_idx,
                                                      float *out_margin, float *scratch, uint32_t *ticket) {
+    griddep_launch_dependents();
+    griddep_wait();
     __shared__ Top wtop[8];
     __shared__ uint32_t last;
     Top t{-INFINITY, 0xFFFFFFFFu, -INFINITY};
@@ -174,17 +178,16 @@ cudaError_t launch_rope_append(const RopeAppendArgs &a, cudaStream_t stream) {
     if (a.head_dim == 0 || (a.head_dim & 1u)) return cudaErrorInvalidValue;
     const uint32_t half = a.head_dim / 2;
     const uint32_t n = ((a.q ? a.n_q_head : 0) + 2 * a.n_kv_head) * half;
-    rope_append_kernel<<<(n + 127) / 128, 128, 0, stream>>>(a);
-    return cudaGetLastError();
+    return launch_kernel(rope_append_kernel, dim3((n + 127) / 128), dim3(128), 0, stream, a.pdl != 0, a);
 }
 
 cudaError_t launch_argmax(const float *logits, uint32_t n, int32_t *out_idx, float *out_margin,
-                          float *scratch, uint32_t *ticket, int sms, cudaStream_t stream) {
+                          float *scratch, uint32_t *ticket, int sms, cudaStream_t stream, bool pdl) {
     uint32_t grid = (n + 255) / 256;
     if (grid > (uint32_t)sms) grid = (uint32_t)sms;
     if (grid == 0) return cudaErrorInvalidValue;
-    argmax_kernel<<<grid, 256, 0, stream>>>(logits, n, out_idx, out_margin, scratch, ticket);
-    return cudaGetLastError();
+    return launch_kernel(argmax_kernel, dim3(grid), dim3(256), 0, stream, pdl, logits, n, out_idx, out_margin, scratch,
+                         ticket);
 }
 
 } // namespace flb

@@ -39,6 +39,7 @@ struct MatvecArgs {
     int accumulate;       // 1: y[r] += dot (STREAM_DOT semantics); 0: y[r] = dot (+ resid)
     uint32_t *status;     // device status word
     float *xn_out;        // optional: CTA 0 also writes the activation it built (nullptr: no)
+    int pdl;              // launch with programmatic dependent launch (inside the decoder's step)
 };
 
 // Streaming kernel (Q4_K / Q6_K, cols a multiple of 2048) or the generic
@@ -66,6 +67,7 @@ struct AttnArgs {
     uint32_t n_q_head, n_kv_head, batch, n_splits;
     float scale;
     uint32_t *status;
+    int pdl;
 };
 cudaError_t launch_attn_decode(const AttnArgs &a, cudaStream_t stream);
 cudaError_t attn_init(void);
@@ -87,14 +89,15 @@ struct RopeAppendArgs {
     const int32_t *pos;
     uint32_t n_q_head, n_kv_head, head_dim, kv_stride;
     float theta_scale;     // freq_base^(-2/head_dim), computed on the host
+    int pdl;
 };
 cudaError_t launch_rope_append(const RopeAppendArgs &a, cudaStream_t stream);
 // Greedy argmax with the reference's tie rule (lowest index) and the
 // top1 - top2 margin. out_idx: int32, out_margin: float; scratch: 2*blocks*2 floats.
 cudaError_t launch_argmax(const float *logits, uint32_t n, int32_t *out_idx, float *out_margin,
-                          float *scratch, uint32_t *ticket, int sms, cudaStream_t stream);
+                          float *scratch, uint32_t *ticket, int sms, cudaStream_t stream, bool pdl = false);
 // Embedding row gather + dequant: out[0..cols) = dequant(table row *token).
 cudaError_t launch_embed(int fmt, const void *table, const int32_t *token, uint32_t cols, float *out,
-                         cudaStream_t stream);
+                         cudaStream_t stream, bool pdl = false);
 
 } // namespace flb

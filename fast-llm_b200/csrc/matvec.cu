@@ -41,6 +41,9 @@
 #include "common.cuh"
 #include "kernels.h"
 
+#include <cuda.h>
+#include <cstring>
+
 namespace flb {
 
 namespace {
@@ -51,7 +54,7 @@ constexpr int kRowsPerStage = 4;
 constexpr uint32_t kSeg4 = 8 * 144;   // bytes of one Q4_K segment (8 super-blocks)
 constexpr uint32_t kSeg6 = 8 * 210;   // bytes of one Q6_K segment
 constexpr uint32_t kStage4 = kRowsPerStage * kSeg4;       // ring slot size, Q4_K only
-constexpr uint32_t kStage6 = kRowsPerStage * kSeg6;       // ring slot size when Q6_K is present
+constexpr uint32_t kStage6 = (kRowsPerStage * kSeg6 + 127u) & ~127u;   // ring slot size when Q6_K is present (128-byte aligned for TMA)
 constexpr float kFixMax = 1040000.0f; // largest fixed-point magnitude (63*2^14 + 63*2^7 + 63 = 1040447)
 
 // byte K of w as a float, without the integer->float conversion pipe: the byte
@@ -178,7 +181,7 @@ __device__ __forceinline__ float q4k_quarter(uint32_t blk, uint32_t c, const XSl
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
         const uint32_t w = i < 4 ? word_of(qa, i) : word_of(qb, i - 4);
-        const uint32_t lo = w & 0x0F0F0F0Fu, hi = (w >> 4) & 0x0F0F0F0Fu;
+        const uint32_t lo = w & 0x0F0F0F0Fu, hi = w & 0xF0F0F0F0u;   // hi holds 16 * q
         const int part = i >> 2, wi = i & 3;
         a0 = dp4a_us(lo, word_of(xq.v[0 + part], wi), a0);
         a1 = dp4a_us(lo, word_of(xq.v[4 + part], wi), a1);
@@ -196,7 +199,9 @@ __device__ __forceinline__ float q4k_quarter(uint32_t blk, uint32_t c, const XSl
     const uint32_t mn_hi = ((e >> 4) & 0x0F0Fu) | ((b >> 2) & 0x3030u);
     const uint32_t sc = c >= 2 ? sc_hi : sc_lo, mn = c >= 2 ? mn_hi : mn_lo;
     const float d = h2f_bits((uint16_t)(hdr.x & 0xFFFFu)), dmin = h2f_bits((uint16_t)(hdr.x >> 16));
-    const float t = u8f<0>(sc) * fix_to_float(a0, a1, a2) + u8f<1>(sc) * fix_to_float(b0, b1, b2);
+    // the high-nibble sums are exact multiples of 16: fold the 1/16 into the digit shifts
+    const float fb = (float)((b0 << 10) + (b1 << 3) + (b2 >> 4));
+    const float t = u8f<0>(sc) * fix_to_float(a0, a1, a2) + u8f<1>(sc) * fb;
     const float m = u8f<0>(mn) * sx.x + u8f<1>(mn) * sx.y;
     return d * t - dmin * m;
 }
@@ -255,15 +260,26 @@ __device__ __forceinline__ float q6k_quarter(uint32_t row, uint32_t sbi, uint32_
 
 // ---- the streaming kernel ---------------------------------------------------
 
+// One TMA descriptor per tensor of the launch: the packed tensor as a 2-D array
+// of 8-byte elements [rows][row_bytes / 8]; a box is 4 rows x one column segment.
+struct TensorMaps { CUtensorMap m[4]; };
+
 // A row quad of one of the launch's tensors.
 struct QuadRef {
-    const uint8_t *row0;   // first row of the quad
     float *y;
     const float *resid;
     uint32_t r0, rows;     // first row index, rows in the tensor
-    uint32_t rb;           // bytes per row
-    int fmt;
+    int fmt, ti;           // format, tensor index
 };
+
+// 2-D tiled TMA load (box = 4 rows x one segment) into shared memory; x counts
+// 8-byte elements (always a multiple of 2, so the copy starts 16-byte aligned).
+__device__ __forceinline__ void tma_load_box(uint32_t dst, const CUtensorMap *map, uint32_t x, uint32_t y, uint64_t *bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+        "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
+        : "memory");
+}
 
 __device__ __forceinline__ QuadRef locate_quad(const MatvecArgs &a, uint32_t quad) {
     QuadRef q;
@@ -276,27 +292,18 @@ __device__ __forceinline__ QuadRef locate_quad(const MatvecArgs &a, uint32_t qua
         base += nq;
     }
     const MatvecTensor &t = a.t[ti];
-    q.rb = (uint32_t)row_bytes(t.fmt, a.cols);
     q.r0 = (quad - base) * kRowsPerStage;
     q.rows = t.rows;
     q.fmt = t.fmt;
+    q.ti = ti;
     q.y = t.y;
     q.resid = t.resid;
-    q.row0 = t.w + (uint64_t)q.r0 * q.rb;
     return q;
 }
 
-// One activation value (column c) as the selected prologue defines it.
-__device__ __forceinline__ float act_value(const MatvecArgs &a, uint32_t c, float inv_rms) {
-    float v = a.x[c];
-    if (a.x_mode == MV_X_RMSNORM) v = v * inv_rms * a.wnorm[c];
-    else if (a.x_mode == MV_X_SILU_MUL) v = (v / (1.0f + expf(-v))) * a.x2[c];
-    return v;
-}
-
 __global__ void __launch_bounds__(kThreads, 1)
-matvec_stream_kernel(const MatvecArgs a, const uint32_t total_quads, const int stages, const int use_q4,
-                     const int use_q6) {
+matvec_stream_kernel(const MatvecArgs a, const __grid_constant__ TensorMaps maps, const uint32_t total_quads,
+                     const int stages, const int use_q4, const int use_q6) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     const Smem sm = carve(smem_raw, a.cols, use_q4 != 0, use_q6 != 0, stages);
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
@@ -323,28 +330,50 @@ matvec_stream_kernel(const MatvecArgs a, const uint32_t total_quads, const int s
     auto issue = [&]() {   // lane 0 only; requests stage p_i and advances
         if (p_seg == 0) pq = locate_quad(a, p_quad);
         const uint32_t sb = pq.fmt == FMT_Q4_K ? kSeg4 : kSeg6;
-        const uint32_t dst = ring + p_slot * stage_bytes;
-        const uint8_t *src = pq.row0 + (size_t)p_seg * sb;
         mbar_arrive_expect_tx(&bars[p_slot], kRowsPerStage * sb);
-#pragma unroll
-        for (int r = 0; r < kRowsPerStage; ++r) {
-            // rows past the end of the tensor re-read its last row (their results are dropped)
-            const uint32_t rr = pq.r0 + r < pq.rows ? r : pq.rows - 1 - pq.r0;
-            bulk_g2s_addr(dst + r * sb, src + (size_t)rr * pq.rb, sb, &bars[p_slot]);
-        }
+        // rows past the end of the tensor are filled with zeros by the TMA unit (their results are dropped)
+        tma_load_box(ring + p_slot * stage_bytes, &maps.m[pq.ti], p_seg * (sb / 8), pq.r0, &bars[p_slot]);
         ++p_i;
         if (++p_slot == (uint32_t)stages) p_slot = 0;
         if (++p_seg == nseg) { p_seg = 0; p_quad += W; }
     };
     // Weights do not depend on the activation: start streaming before x is built.
+    griddep_launch_dependents();
     if (lane == 0)
         while (p_i < (uint32_t)stages && p_i < my_stages) issue();
+    griddep_wait();   // the activation (and y, resid) come from the previous kernel
 
     // ---- build the fixed-point activation in shared memory ----
+    // One warp per 256-column block (blocks warp, warp + kWarps, ...); lane l holds
+    // columns 8l .. 8l+7 of the block. All global loads of all the warp's blocks
+    // are issued first, so the prologue costs one memory round trip.
+    constexpr int kMaxBlk = 6;   // blocks per warp: cols <= 6 * 256 * kWarps = 18432
+    const uint32_t nblk = a.cols / 256;
+    float4 ra[kMaxBlk][2], rb2[kMaxBlk][2];
+#pragma unroll
+    for (int b = 0; b < kMaxBlk; ++b) {
+        const uint32_t blk = warp + b * kWarps;
+        if (blk < nblk) {
+            const uint32_t c0 = blk * 256 + lane * 8;
+            ra[b][0] = *reinterpret_cast<const float4 *>(a.x + c0);
+            ra[b][1] = *reinterpret_cast<const float4 *>(a.x + c0 + 4);
+            if (a.x_mode != MV_X_PLAIN) {
+                const float *p2 = a.x_mode == MV_X_RMSNORM ? a.wnorm : a.x2;
+                rb2[b][0] = *reinterpret_cast<const float4 *>(p2 + c0);
+                rb2[b][1] = *reinterpret_cast<const float4 *>(p2 + c0 + 4);
+            }
+        }
+    }
     float inv_rms = 1.f;
     if (a.x_mode == MV_X_RMSNORM) {
         float ss = 0.f;
-        for (uint32_t c = tid; c < a.cols; c += kThreads) { const float v = a.x[c]; ss += v * v; }
+#pragma unroll
+        for (int b = 0; b < kMaxBlk; ++b)
+            if (warp + b * kWarps < nblk) {
+                const float4 u0 = ra[b][0], u1 = ra[b][1];
+                ss += (u0.x * u0.x + u0.y * u0.y) + (u0.z * u0.z + u0.w * u0.w);
+                ss += (u1.x * u1.x + u1.y * u1.y) + (u1.z * u1.z + u1.w * u1.w);
+            }
         ss = warp_sum(ss);
         if (lane == 0) red[warp] = ss;
         __syncthreads();
@@ -356,14 +385,19 @@ matvec_stream_kernel(const MatvecArgs a, const uint32_t total_quads, const int s
         __syncthreads();
         inv_rms = inv_rms_s;
     }
-    // One warp per 256-column block; lane l holds columns 8l .. 8l+7 of the block.
-    for (uint32_t blk = warp; blk < a.cols / 256; blk += kWarps) {
+#pragma unroll
+    for (int b = 0; b < kMaxBlk; ++b) {
+        const uint32_t blk = warp + b * kWarps;
+        if (blk >= nblk) break;
         const uint32_t c0 = blk * 256 + lane * 8;
-        float v[8];
+        float v[8] = {ra[b][0].x, ra[b][0].y, ra[b][0].z, ra[b][0].w, ra[b][1].x, ra[b][1].y, ra[b][1].z, ra[b][1].w};
+        const float w2[8] = {rb2[b][0].x, rb2[b][0].y, rb2[b][0].z, rb2[b][0].w,
+                             rb2[b][1].x, rb2[b][1].y, rb2[b][1].z, rb2[b][1].w};
         float amax = 0.f;
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-            v[i] = act_value(a, c0 + i, inv_rms);
+            if (a.x_mode == MV_X_RMSNORM) v[i] = v[i] * inv_rms * w2[i];
+            else if (a.x_mode == MV_X_SILU_MUL) v[i] = (v[i] / (1.0f + expf(-v[i]))) * w2[i];
             amax = fmaxf(amax, fabsf(v[i]));
         }
         if (a.xn_out != nullptr && blockIdx.x == 0) {
@@ -442,17 +476,26 @@ matvec_stream_kernel(const MatvecArgs a, const uint32_t total_quads, const int s
         if (++seg == nseg) {
             seg = 0;
             quad += W;
-#pragma unroll
-            for (int r = 0; r < kRowsPerStage; ++r) {
-                const float v = warp_sum(acc[r]);
-                acc[r] = 0.f;
-                const uint32_t row = cur.r0 + r;
-                if (lane == 0 && row < cur.rows) {
-                    float o = v;
-                    if (cur.resid) o = cur.resid[row] + v;
-                    if (a.accumulate) o = cur.y[row] + o;
-                    cur.y[row] = o;
-                }
+            // 4 row sums over 32 lanes in 6 shuffles: halve the number of live
+            // values at each of the first two steps, then a 3-step butterfly.
+            // Afterwards lanes 0, 8, 16, 24 hold the totals of rows 0, 2, 1, 3.
+            const bool up16 = (lane & 16u) != 0, up8 = (lane & 8u) != 0;
+            float k0 = up16 ? acc[1] : acc[0], g0 = up16 ? acc[0] : acc[1];
+            float k1 = up16 ? acc[3] : acc[2], g1 = up16 ? acc[2] : acc[3];
+            k0 += __shfl_xor_sync(0xffffffffu, g0, 16);   // lanes <16: row 0, lanes >=16: row 1
+            k1 += __shfl_xor_sync(0xffffffffu, g1, 16);   // lanes <16: row 2, lanes >=16: row 3
+            float k = up8 ? k1 : k0, g = up8 ? k0 : k1;
+            k += __shfl_xor_sync(0xffffffffu, g, 8);      // row = (lane>>4 & 1) + 2*(lane>>3 & 1)
+            k += __shfl_xor_sync(0xffffffffu, k, 4);
+            k += __shfl_xor_sync(0xffffffffu, k, 2);
+            k += __shfl_xor_sync(0xffffffffu, k, 1);
+            acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
+            const uint32_t row = cur.r0 + ((lane >> 4) & 1u) + 2u * ((lane >> 3) & 1u);
+            if ((lane & 7u) == 0 && row < cur.rows) {
+                float o = k;
+                if (cur.resid) o = cur.resid[row] + k;
+                if (a.accumulate) o = cur.y[row] + o;
+                cur.y[row] = o;
             }
         }
     }
@@ -498,6 +541,8 @@ __device__ __forceinline__ float dequant_elem(int fmt, const uint8_t *row, uint3
 }
 
 __global__ void __launch_bounds__(256) matvec_generic_kernel(const MatvecArgs a, const uint32_t total_rows) {
+    griddep_launch_dependents();
+    griddep_wait();
     const uint32_t lane = threadIdx.x & 31u;
     const uint32_t gw = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, W = (gridDim.x * blockDim.x) >> 5;
     for (uint32_t vr = gw; vr < total_rows; vr += W) {
@@ -538,8 +583,36 @@ size_t matvec_smem_bytes(uint32_t cols, bool q4, bool q6, int *stages_out) {
     return fixed + (size_t)kWarps * stages * (8 + slot);
 }
 
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn g_encode = nullptr;
+
 cudaError_t matvec_init(void) {
+    if (!g_encode) {
+        void *fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+        if (e != cudaSuccess) return e;
+        if (qres != cudaDriverEntryPointSuccess || !fn) return cudaErrorNotSupported;
+        g_encode = (EncodeTiledFn)fn;
+    }
     return cudaFuncSetAttribute(matvec_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024 - 1024);
+}
+
+// The packed tensor as [rows][row_bytes / 8] 8-byte elements, box = 4 rows x one segment.
+static cudaError_t encode_map(CUtensorMap *m, const MatvecTensor &t, uint32_t cols) {
+    if (!g_encode) return cudaErrorNotSupported;
+    const uint64_t rb = row_bytes(t.fmt, cols);
+    const uint32_t seg = t.fmt == FMT_Q4_K ? kSeg4 : kSeg6;
+    const cuuint64_t gdim[2] = {rb / 8, t.rows};
+    const cuuint64_t gstride[1] = {rb};
+    const cuuint32_t box[2] = {seg / 8, (cuuint32_t)kRowsPerStage};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = g_encode(m, CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, (void *)t.w, gdim, gstride, box, estr,
+                                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
 }
 
 cudaError_t launch_matvec(const MatvecArgs &a, int sms, cudaStream_t stream) {
@@ -551,6 +624,8 @@ cudaError_t launch_matvec(const MatvecArgs &a, int sms, cudaStream_t stream) {
         if (t.rows == 0 || a.cols % blk_elems(t.fmt) != 0) return cudaErrorInvalidValue;
         if (t.fmt < FMT_F32 || t.fmt > FMT_Q6_K) return cudaErrorInvalidValue;
         streaming = streaming && matvec_is_streaming(t.fmt, a.cols) && (((uintptr_t)t.w) & 15u) == 0;
+        streaming = streaming && a.cols <= 6u * 256u * kWarps && (((uintptr_t)a.x) & 15u) == 0 &&
+                    (((uintptr_t)a.x2) & 15u) == 0 && (((uintptr_t)a.wnorm) & 15u) == 0;
         q4 = q4 || t.fmt == FMT_Q4_K;
         q6 = q6 || t.fmt == FMT_Q6_K;
         total_rows += t.rows;
@@ -562,15 +637,20 @@ cudaError_t launch_matvec(const MatvecArgs &a, int sms, cudaStream_t stream) {
         if (smem <= 227 * 1024 - 1024 && stages >= 2) {
             uint32_t grid = (total_quads + kWarps - 1) / kWarps;
             if (grid > (uint32_t)sms) grid = (uint32_t)sms;
-            matvec_stream_kernel<<<grid, kThreads, smem, stream>>>(a, total_quads, stages, q4 ? 1 : 0, q6 ? 1 : 0);
-            return cudaGetLastError();
+            TensorMaps maps;
+            memset(&maps, 0, sizeof(maps));
+            for (int i = 0; i < a.n_tensors; ++i) {
+                const cudaError_t e = encode_map(&maps.m[i], a.t[i], a.cols);
+                if (e != cudaSuccess) return e;
+            }
+            return launch_kernel(matvec_stream_kernel, dim3(grid), dim3(kThreads), smem, stream, a.pdl != 0, a, maps,
+                                 total_quads, stages, q4 ? 1 : 0, q6 ? 1 : 0);
         }
     }
     if (a.x_mode != MV_X_PLAIN) return cudaErrorInvalidValue;   // prologues exist only in the streaming kernel
     uint32_t grid = (total_rows + 7) / 8;
     if (grid > (uint32_t)sms * 8) grid = (uint32_t)sms * 8;
-    matvec_generic_kernel<<<grid, 256, 0, stream>>>(a, total_rows);
-    return cudaGetLastError();
+    return launch_kernel(matvec_generic_kernel, dim3(grid), dim3(256), 0, stream, a.pdl != 0, a, total_rows);
 }
 
 } // namespace flb
