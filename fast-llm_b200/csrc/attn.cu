@@ -52,7 +52,9 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnArg
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
     const uint32_t split = blockIdx.x, hkv = blockIdx.y, b = blockIdx.z;
     const uint32_t group = a.n_q_head / a.n_kv_head;   // == kGroup (checked on the host)
+    if (tid == 0) trace_min(a.trace, 0);
     griddep_wait();   // *pos, q and the appended K/V row come from the previous kernels
+    if (tid == 0) trace_min(a.trace, 1);
     const uint32_t kv_len = a.pos ? (uint32_t)(*a.pos) + 1u : a.kv_len;
 
     const uint32_t tiles_total = (kv_len + kTile - 1) / kTile;
@@ -213,6 +215,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnArg
     __threadfence();
     __syncthreads();
     if (tid == 0) {
+        trace_max(a.trace, 2);
         const uint32_t tk = atomicAdd(&a.tickets[b * a.n_kv_head + hkv], 1u);
         sm.is_last = (tk == a.n_splits - 1) ? 1u : 0u;
     }
@@ -255,7 +258,10 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnArg
         acc.x *= inv; acc.y *= inv; acc.z *= inv; acc.w *= inv;
         reinterpret_cast<float4 *>(a.out + hq * kD)[lane] = acc;
     }
-    if (tid == 0) a.tickets[b * a.n_kv_head + hkv] = 0;   // ready for the next launch
+    if (tid == 0) {
+        a.tickets[b * a.n_kv_head + hkv] = 0;   // ready for the next launch
+        trace_max(a.trace, 3);
+    }
 }
 
 } // namespace

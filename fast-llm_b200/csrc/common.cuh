@@ -125,6 +125,23 @@ __device__ __forceinline__ void griddep_wait() {
     asm volatile("griddepcontrol.wait;" ::: "memory");
 }
 
+// Optional per-launch timeline (diagnostics): rec[0] = earliest kernel entry,
+// rec[1] = earliest point after the dependency wait, rec[2] = latest end of the
+// prologue, rec[3] = latest exit, as %globaltimer nanoseconds. rec[0..1] must be
+// pre-set to all ones, rec[2..3] to zero. One thread per CTA calls these.
+__device__ __forceinline__ void trace_min(unsigned long long *rec, int i) {
+    if (rec) atomicMin(rec + i, (unsigned long long)globaltimer_ns());
+}
+__device__ __forceinline__ void trace_max(unsigned long long *rec, int i) {
+    if (rec) atomicMax(rec + i, (unsigned long long)globaltimer_ns());
+}
+
+// Release / acquire fences at GPU scope (cheaper than the sequentially
+// consistent __threadfence()).
+__device__ __forceinline__ void fence_acq_rel_gpu() {
+    asm volatile("fence.acq_rel.gpu;" ::: "memory");
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -14,6 +14,7 @@
 #include "capi_internal.h"
 
 #include <cmath>
+#include <cstdlib>
 #include <vector>
 
 using namespace flb;
@@ -27,6 +28,12 @@ using namespace flb;
 namespace {
 
 struct Tensor { int fmt = -1; const uint8_t *w = nullptr; };
+
+// Timeline records start as {~0, ~0, 0, 0} (two minima, two maxima).
+__global__ void trace_init_kernel(unsigned long long *t, uint32_t n) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n * 4) t[i] = (i & 2u) ? 0ull : ~0ull;
+}
 
 // After a step: token <- argmax, history[count++] <- argmax, pos += 1.
 __global__ void advance_kernel(int32_t *token, const int32_t *next, int32_t *pos, int32_t *hist,
@@ -61,6 +68,10 @@ struct fl_b200_decoder {
     float *xa = nullptr, *xb = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *att = nullptr;
     float *g = nullptr, *u = nullptr, *logits = nullptr, *xn_final = nullptr, *part = nullptr;
     uint32_t *tickets = nullptr;
+    MatvecScratch mv;                       // scratch of the step's matvec launches (sized before capture)
+    bool fused_swiglu = false;              // the gate/up launch writes silu(gate)*up into g
+    unsigned long long *trace = nullptr;    // FLB_TRACE=1: 4 device timestamps per launch of the step
+    uint32_t trace_n = 0;
     uint32_t n_splits = 1;
     int32_t *h_pin = nullptr;               // pinned: [0] token, [1] pos, [2] next
     int32_t n_past = 0;
@@ -78,11 +89,21 @@ static int kPdl = 1;
 // Kernel classes, for timing one class of the step in isolation.
 enum : uint32_t { K_MATVEC = 1u, K_ATTN = 2u, K_OTHER = 4u, K_ALL = 7u };
 
-static int enqueue_step(fl_b200_decoder *d, cudaStream_t s, uint32_t *n_launch, uint32_t mask = K_ALL) {
+// dry = true: no launches, only grows the context's matvec scratch to what the
+// step's launches need (must run before the step is captured).
+static int enqueue_step(fl_b200_decoder *d, cudaStream_t s, uint32_t *n_launch, uint32_t mask = K_ALL,
+                        bool dry = false) {
+    uint32_t n = 0;   // launches so far
+    auto do_matvec = [&](MatvecArgs &a) -> int {
+        if (d->trace && mask == K_ALL) a.trace = d->trace + 4 * (size_t)n;
+        if (int rc = ensure_matvec_scratch(d->ctx, d->mv, a)) return rc;
+        if (dry) return FL_B200_OK;
+        return cuda_err(launch_matvec(a, d->ctx->sms, s), "matvec launch");
+    };
+    if (dry) mask = K_MATVEC;
     const fl_b200_llama_cfg &c = d->c;
     fl_b200_ctx *ctx = d->ctx;
     const uint32_t E = c.n_embd, D = c.head_dim, QD = c.n_head * D, KD = c.n_kv_head * D;
-    uint32_t n = 0;
     if (mask & K_OTHER) { CK(launch_embed(d->tok_embd.fmt, d->tok_embd.w, d->d_token, E, d->xa, s, false)); ++n; }
     for (uint32_t l = 0; l < c.n_layer; ++l) {
         const Tensor *w = &d->lw[(size_t)l * 7];
@@ -94,7 +115,7 @@ static int enqueue_step(fl_b200_decoder *d, cudaStream_t s, uint32_t *n_launch, 
             a.t[2] = {w[FL_B200_T_WV].w, d->v, nullptr, KD, w[FL_B200_T_WV].fmt};
             a.x = d->xa; a.wnorm = d->attn_norm[l]; a.eps = c.eps; a.cols = E;
             a.x_mode = MV_X_RMSNORM; a.status = ctx->status; a.pdl = kPdl;
-            if (mask & K_MATVEC) { CK(launch_matvec(a, ctx->sms, s)); ++n; }
+            if (mask & K_MATVEC) { if (int rc = do_matvec(a)) return rc; ++n; }
         }
         {
             RopeAppendArgs a{};
@@ -110,6 +131,7 @@ static int enqueue_step(fl_b200_decoder *d, cudaStream_t s, uint32_t *n_launch, 
             a.batch_stride = (uint64_t)c.n_kv_head * c.max_kv * D;
             a.n_q_head = c.n_head; a.n_kv_head = c.n_kv_head; a.batch = 1; a.n_splits = d->n_splits;
             a.scale = 1.0f / sqrtf((float)D); a.status = ctx->status; a.pdl = kPdl;
+            if (d->trace && mask == K_ALL) a.trace = d->trace + 4 * (size_t)n;
             if (mask & K_ATTN) { CK(launch_attn_decode(a, s)); ++n; }
         }
         {   // O projection + residual: xb = xa + Wo att
@@ -117,23 +139,26 @@ static int enqueue_step(fl_b200_decoder *d, cudaStream_t s, uint32_t *n_launch, 
             a.n_tensors = 1;
             a.t[0] = {w[FL_B200_T_WO].w, d->xb, d->xa, E, w[FL_B200_T_WO].fmt};
             a.x = d->att; a.cols = QD; a.x_mode = MV_X_PLAIN; a.status = ctx->status; a.pdl = kPdl;
-            if (mask & K_MATVEC) { CK(launch_matvec(a, ctx->sms, s)); ++n; }
+            if (mask & K_MATVEC) { if (int rc = do_matvec(a)) return rc; ++n; }
         }
-        {   // RMSNorm + gate / up
+        {   // RMSNorm + gate / up with the SwiGLU product in the epilogue: g <- silu(gate x) * (up x)
             MatvecArgs a{};
             a.n_tensors = 2;
             a.t[0] = {w[FL_B200_T_GATE].w, d->g, nullptr, c.n_ff, w[FL_B200_T_GATE].fmt};
             a.t[1] = {w[FL_B200_T_UP].w, d->u, nullptr, c.n_ff, w[FL_B200_T_UP].fmt};
             a.x = d->xb; a.wnorm = d->ffn_norm[l]; a.eps = c.eps; a.cols = E;
             a.x_mode = MV_X_RMSNORM; a.status = ctx->status; a.pdl = kPdl;
-            if (mask & K_MATVEC) { CK(launch_matvec(a, ctx->sms, s)); ++n; }
+            a.swiglu = w[FL_B200_T_GATE].fmt == w[FL_B200_T_UP].fmt ? 1 : 0;
+            if (mask & K_MATVEC) { if (int rc = do_matvec(a)) return rc; ++n; }
+            d->fused_swiglu = a.swiglu != 0;
         }
-        {   // SiLU(gate) * up, down projection + residual: xa = xb + Wdown h
+        {   // down projection + residual: xa = xb + Wdown h
             MatvecArgs a{};
             a.n_tensors = 1;
             a.t[0] = {w[FL_B200_T_DOWN].w, d->xa, d->xb, E, w[FL_B200_T_DOWN].fmt};
-            a.x = d->g; a.x2 = d->u; a.cols = c.n_ff; a.x_mode = MV_X_SILU_MUL; a.status = ctx->status; a.pdl = kPdl;
-            if (mask & K_MATVEC) { CK(launch_matvec(a, ctx->sms, s)); ++n; }
+            a.x = d->g; a.x2 = d->u; a.cols = c.n_ff; a.status = ctx->status; a.pdl = kPdl;
+            a.x_mode = d->fused_swiglu ? MV_X_PLAIN : MV_X_SILU_MUL;
+            if (mask & K_MATVEC) { if (int rc = do_matvec(a)) return rc; ++n; }
         }
     }
     {   // output norm + head
@@ -142,7 +167,7 @@ static int enqueue_step(fl_b200_decoder *d, cudaStream_t s, uint32_t *n_launch, 
         a.t[0] = {d->output.w, d->logits, nullptr, c.n_vocab, d->output.fmt};
         a.x = d->xa; a.wnorm = d->out_norm; a.eps = c.eps; a.cols = E;
         a.x_mode = MV_X_RMSNORM; a.status = ctx->status; a.pdl = kPdl; a.xn_out = d->xn_final;
-        if (mask & K_MATVEC) { CK(launch_matvec(a, ctx->sms, s)); ++n; }
+        if (mask & K_MATVEC) { if (int rc = do_matvec(a)) return rc; ++n; }
     }
     if (mask & K_OTHER) {
         CK(launch_argmax(d->logits, c.n_vocab, d->d_next, d->d_margin, ctx->argmax_scratch, ctx->argmax_ticket,
@@ -223,6 +248,8 @@ void fl_b200_decoder_destroy(fl_b200_decoder *d) {
     cudaFree(d->d_token); cudaFree(d->d_hist); cudaFree(d->xa); cudaFree(d->xb); cudaFree(d->q);
     cudaFree(d->k); cudaFree(d->v); cudaFree(d->att); cudaFree(d->g); cudaFree(d->u); cudaFree(d->logits);
     cudaFree(d->xn_final); cudaFree(d->part); cudaFree(d->tickets);
+    free_matvec_scratch(d->mv);
+    cudaFree(d->trace);
     cudaFreeHost(d->h_pin);
     delete d;
 }
@@ -288,6 +315,13 @@ int fl_b200_decoder_finalize(fl_b200_decoder *d) {
     cudaStream_t s = d->ctx->stream;
     CK(cudaSetDevice(d->ctx->device));
     CK(cudaStreamSynchronize(s));
+    if (const char *e = getenv("FLB_TRACE")) {
+        if (e[0] == '1' && !d->trace) {
+            d->trace_n = 8 + 6 * d->c.n_layer;
+            CK(cudaMalloc(&d->trace, (size_t)d->trace_n * 4 * sizeof(unsigned long long)));
+        }
+    }
+    if (int rc0 = enqueue_step(d, s, nullptr, K_MATVEC, true)) return rc0;   // size the scratch before capturing
     CK(cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal));
     uint32_t n = 0;
     int rc = enqueue_step(d, s, &n);
@@ -333,6 +367,7 @@ int fl_b200_decoder_step(fl_b200_decoder *d, int32_t token, int32_t *next_out) {
     d->h_pin[2] = d->n_past;
     d->h_pin[3] = 0;            // history counter
     CK(cudaMemcpyAsync(d->d_token, d->h_pin, 16, cudaMemcpyHostToDevice, s));
+    if (d->trace) trace_init_kernel<<<(d->trace_n * 4 + 255) / 256, 256, 0, s>>>(d->trace, d->trace_n);
     CK(cudaGraphLaunch(d->exec, s));
     CK(cudaMemcpyAsync(d->h_pin + 8, d->d_next, 4, cudaMemcpyDeviceToHost, s));
     CK(cudaStreamSynchronize(s));
@@ -383,8 +418,8 @@ int fl_b200_decoder_tap(fl_b200_decoder *d, int which, float *out) {
     case 3: src = d->v; n = KD; break;               // last layer: v
     case 4: src = d->att; n = QD; break;             // last layer: attention output
     case 5: src = d->xb; n = c.n_embd; break;        // last layer: residual after attention
-    case 6: src = d->g; n = c.n_ff; break;           // last layer: gate
-    case 7: src = d->u; n = c.n_ff; break;           // last layer: up
+    case 6: src = d->g; n = c.n_ff; break;           // last layer: silu(gate) * up (gate alone if the formats of gate and up differ)
+    case 7: src = d->u; n = c.n_ff; break;           // last layer: up (only written if the formats of gate and up differ)
     default: return set_err(FL_B200_ERR_ARG, "decoder_tap: unknown tap %d", which);
     }
     return fl_b200_download(d->ctx, out, src, n * 4);
@@ -428,6 +463,22 @@ int fl_b200_decoder_time_class(fl_b200_decoder *d, uint32_t kernel_class, uint32
     *ms_per_step = ms / (float)reps;
     *launches_per_step = n;
     return check_dev_status(d);
+}
+
+// Diagnostics (FLB_TRACE=1 in the environment at finalize): per launch of the
+// last fl_b200_decoder_step, four %globaltimer values in ns: earliest kernel
+// entry, earliest point after the dependency wait, latest end of the prologue,
+// latest exit. Only the matvec and attention kernels record; the other entries
+// stay {~0, ~0, 0, 0}. Returns the number of records through n_out (0 when
+// tracing is off).
+int fl_b200_decoder_trace(fl_b200_decoder *d, uint64_t *host_out, uint32_t cap_records, uint32_t *n_out) {
+    if (!d || !n_out) return set_err(FL_B200_ERR_ARG, "decoder_trace: null");
+    *n_out = 0;
+    if (!d->trace) return FL_B200_OK;
+    const uint32_t n = d->launches < d->trace_n ? d->launches : d->trace_n;
+    if (!host_out || cap_records < n) return set_err(FL_B200_ERR_ARG, "decoder_trace: need room for %u records", n);
+    *n_out = n;
+    return fl_b200_download(d->ctx, host_out, d->trace, (size_t)n * 4 * sizeof(uint64_t));
 }
 
 int fl_b200_decoder_launches_per_step(fl_b200_decoder *d, uint32_t *n) {

@@ -37,9 +37,17 @@ struct MatvecArgs {
     uint32_t cols;
     int x_mode;
     int accumulate;       // 1: y[r] += dot (STREAM_DOT semantics); 0: y[r] = dot (+ resid)
+    int swiglu;           // 1: t[0] = gate, t[1] = up (same shape and format): t[0].y[r] = silu(gate_r . x) * (up_r . x)
     uint32_t *status;     // device status word
     float *xn_out;        // optional: CTA 0 also writes the activation it built (nullptr: no)
     int pdl;              // launch with programmatic dependent launch (inside the decoder's step)
+    // Streaming kernel only: partial row sums of units shared between warps and
+    // their arrival counters (zero before the first launch; the kernel resets
+    // them). Sized with matvec_scratch_need().
+    float *scratch;
+    uint32_t *tickets;
+    size_t scratch_floats, tickets_n;
+    unsigned long long *trace;   // optional 4-entry timeline record of this launch (diagnostics)
 };
 
 // Streaming kernel (Q4_K / Q6_K, cols a multiple of 2048) or the generic
@@ -51,6 +59,7 @@ bool matvec_is_streaming(int fmt, uint32_t cols);
 // Dynamic shared memory the streaming kernel needs for (cols, formats used).
 size_t matvec_smem_bytes(uint32_t cols, bool use_q4k, bool use_q6k, int *stages_out);
 cudaError_t matvec_init(void);   // sets the dynamic shared memory attribute once
+void matvec_scratch_need(const MatvecArgs &a, int sms, size_t *scratch_floats, size_t *tickets);
 
 // ---- attn.cu ------------------------------------------------------------
 struct AttnArgs {
@@ -68,6 +77,7 @@ struct AttnArgs {
     float scale;
     uint32_t *status;
     int pdl;
+    unsigned long long *trace;   // optional 4-entry timeline record (diagnostics)
 };
 cudaError_t launch_attn_decode(const AttnArgs &a, cudaStream_t stream);
 cudaError_t attn_init(void);

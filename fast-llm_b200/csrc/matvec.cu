@@ -283,6 +283,15 @@ __device__ __forceinline__ void tma_load_box(uint32_t dst, const CUtensorMap *ma
 
 __device__ __forceinline__ QuadRef locate_quad(const MatvecArgs &a, uint32_t quad) {
     QuadRef q;
+    if (a.swiglu) {   // quad = rows 2q, 2q+1 of the gate tensor and the same rows of the up tensor
+        q.r0 = quad * 2;
+        q.rows = a.t[0].rows;
+        q.fmt = a.t[0].fmt;
+        q.ti = 0;
+        q.y = a.t[0].y;
+        q.resid = nullptr;
+        return q;
+    }
     int ti = 0;
     uint32_t base = 0;
 #pragma unroll 1
@@ -310,7 +319,6 @@ matvec_stream_kernel(const MatvecArgs a, const __grid_constant__ TensorMaps maps
     const uint32_t nseg = a.cols / 2048u;
     const uint32_t stage_bytes = use_q6 ? kStage6 : kStage4;
     __shared__ float red[kWarps];
-    __shared__ float inv_rms_s;
 
     uint64_t *bars = sm.bars + warp * stages;
     const uint32_t ring = smem_u32(sm.ring) + warp * stages * stage_bytes;   // shared address
@@ -320,7 +328,9 @@ matvec_stream_kernel(const MatvecArgs a, const __grid_constant__ TensorMaps maps
     __syncwarp();
 
     // This warp's quads: gw, gw + W, ... ; per quad nseg stages (one per column segment).
-    const uint32_t gw = blockIdx.x * kWarps + warp, W = gridDim.x * kWarps;
+    // Warps are numbered CTA-fastest, so a launch with few quads spreads them over
+    // all SMs instead of filling the first CTAs.
+    const uint32_t gw = warp * gridDim.x + blockIdx.x, W = gridDim.x * kWarps;
     const uint32_t my_quads = gw < total_quads ? (total_quads - gw + W - 1) / W : 0;
     const uint32_t my_stages = my_quads * nseg;
 
@@ -332,16 +342,23 @@ matvec_stream_kernel(const MatvecArgs a, const __grid_constant__ TensorMaps maps
         const uint32_t sb = pq.fmt == FMT_Q4_K ? kSeg4 : kSeg6;
         mbar_arrive_expect_tx(&bars[p_slot], kRowsPerStage * sb);
         // rows past the end of the tensor are filled with zeros by the TMA unit (their results are dropped)
-        tma_load_box(ring + p_slot * stage_bytes, &maps.m[pq.ti], p_seg * (sb / 8), pq.r0, &bars[p_slot]);
+        if (a.swiglu) {   // two boxes of 2 rows: gate rows, then up rows
+            tma_load_box(ring + p_slot * stage_bytes, &maps.m[0], p_seg * (sb / 8), pq.r0, &bars[p_slot]);
+            tma_load_box(ring + p_slot * stage_bytes + 2 * sb, &maps.m[1], p_seg * (sb / 8), pq.r0, &bars[p_slot]);
+        } else {
+            tma_load_box(ring + p_slot * stage_bytes, &maps.m[pq.ti], p_seg * (sb / 8), pq.r0, &bars[p_slot]);
+        }
         ++p_i;
         if (++p_slot == (uint32_t)stages) p_slot = 0;
         if (++p_seg == nseg) { p_seg = 0; p_quad += W; }
     };
     // Weights do not depend on the activation: start streaming before x is built.
+    if (tid == 0) trace_min(a.trace, 0);
     griddep_launch_dependents();
     if (lane == 0)
         while (p_i < (uint32_t)stages && p_i < my_stages) issue();
     griddep_wait();   // the activation (and y, resid) come from the previous kernel
+    if (tid == 0) trace_min(a.trace, 1);
 
     // ---- build the fixed-point activation in shared memory ----
     // One warp per 256-column block (blocks warp, warp + kWarps, ...); lane l holds
@@ -364,9 +381,11 @@ matvec_stream_kernel(const MatvecArgs a, const __grid_constant__ TensorMaps maps
             }
         }
     }
-    float inv_rms = 1.f;
+    // RMSNorm: the digits are those of x*w (the common factor 1/rms is applied to
+    // the row sums at the end), so the sum of squares and the quantisation need
+    // only one block-wide barrier between them and the consumers.
+    float ss = 0.f;
     if (a.x_mode == MV_X_RMSNORM) {
-        float ss = 0.f;
 #pragma unroll
         for (int b = 0; b < kMaxBlk; ++b)
             if (warp + b * kWarps < nblk) {
@@ -376,14 +395,6 @@ matvec_stream_kernel(const MatvecArgs a, const __grid_constant__ TensorMaps maps
             }
         ss = warp_sum(ss);
         if (lane == 0) red[warp] = ss;
-        __syncthreads();
-        if (tid == 0) {
-            float t = 0.f;
-            for (int w = 0; w < kWarps; ++w) t += red[w];
-            inv_rms_s = 1.0f / sqrtf(t / (float)a.cols + a.eps);
-        }
-        __syncthreads();
-        inv_rms = inv_rms_s;
     }
 #pragma unroll
     for (int b = 0; b < kMaxBlk; ++b) {
@@ -396,18 +407,15 @@ matvec_stream_kernel(const MatvecArgs a, const __grid_constant__ TensorMaps maps
         float amax = 0.f;
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-            if (a.x_mode == MV_X_RMSNORM) v[i] = v[i] * inv_rms * w2[i];
+            if (a.x_mode == MV_X_RMSNORM) v[i] = v[i] * w2[i];
             else if (a.x_mode == MV_X_SILU_MUL) v[i] = (v[i] / (1.0f + expf(-v[i]))) * w2[i];
             amax = fmaxf(amax, fabsf(v[i]));
-        }
-        if (a.xn_out != nullptr && blockIdx.x == 0) {
-#pragma unroll
-            for (int i = 0; i < 8; ++i) a.xn_out[c0 + i] = v[i];
         }
         amax = warp_max(amax);
         const float s = amax > 0.f ? amax / kFixMax : 1.0f;
         const float inv_s = 1.0f / s;
         int sum = 0;
+        uint32_t pk[3][2] = {{0u, 0u}, {0u, 0u}, {0u, 0u}};   // this lane's 8 columns of each digit plane
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
             const int X = __float2int_rn(v[i] * inv_s);          // |X| <= 1040000
@@ -416,13 +424,15 @@ matvec_stream_kernel(const MatvecArgs a, const __grid_constant__ TensorMaps maps
             const int d1 = ((X1 + 64) & 127) - 64;
             const int d0 = (X1 - d1) >> 7;
             sum += X;
-            const uint32_t c = c0 + i;
-            if (use_q4) {
-                sm.q4[pos4(c, 0)] = (int8_t)d0; sm.q4[pos4(c, 1)] = (int8_t)d1; sm.q4[pos4(c, 2)] = (int8_t)d2;
-            }
-            if (use_q6) {
-                sm.q6[pos6(c, 0)] = (int8_t)d0; sm.q6[pos6(c, 1)] = (int8_t)d1; sm.q6[pos6(c, 2)] = (int8_t)d2;
-            }
+            pk[0][i >> 2] |= (uint32_t)(d0 & 0xFF) << (8 * (i & 3));
+            pk[1][i >> 2] |= (uint32_t)(d1 & 0xFF) << (8 * (i & 3));
+            pk[2][i >> 2] |= (uint32_t)(d2 & 0xFF) << (8 * (i & 3));
+        }
+        // the lane's 8 columns are 8 consecutive bytes of one 16-byte slot in both layouts
+#pragma unroll
+        for (int d = 0; d < 3; ++d) {
+            if (use_q4) *reinterpret_cast<uint2 *>(sm.q4 + pos4(c0, d)) = make_uint2(pk[d][0], pk[d][1]);
+            if (use_q6) *reinterpret_cast<uint2 *>(sm.q6 + pos6(c0, d)) = make_uint2(pk[d][0], pk[d][1]);
         }
         // sums over 16 columns (lane pairs) and 32 columns (lane quads), exact in int32
         const int s16 = sum + __shfl_xor_sync(0xffffffffu, sum, 1);
@@ -441,6 +451,22 @@ matvec_stream_kernel(const MatvecArgs a, const __grid_constant__ TensorMaps maps
         if (lane == 0) sm.xs[blk] = s;
     }
     __syncthreads();
+    float inv_rms = 1.f;
+    if (a.x_mode == MV_X_RMSNORM) {
+        float t = 0.f;
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) t += red[w];   // same order in every thread
+        inv_rms = 1.0f / sqrtf(t / (float)a.cols + a.eps);
+    }
+    if (a.xn_out != nullptr && blockIdx.x == 0) {   // the activation as f32, for layer-level checks
+        for (uint32_t c = tid; c < a.cols; c += kThreads) {
+            float v = a.x[c];
+            if (a.x_mode == MV_X_RMSNORM) v = v * inv_rms * a.wnorm[c];
+            else if (a.x_mode == MV_X_SILU_MUL) v = (v / (1.0f + expf(-v))) * a.x2[c];
+            a.xn_out[c] = v;
+        }
+    }
+    if (tid == 0) trace_max(a.trace, 2);
 
     // ---- consume ----
     const uint32_t q4_addr = use_q4 ? smem_u32(sm.q4) : 0, q6_addr = use_q6 ? smem_u32(sm.q6) : 0;
@@ -490,8 +516,18 @@ matvec_stream_kernel(const MatvecArgs a, const __grid_constant__ TensorMaps maps
             k += __shfl_xor_sync(0xffffffffu, k, 2);
             k += __shfl_xor_sync(0xffffffffu, k, 1);
             acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
+            if (a.swiglu) {
+                // stage rows 0,1 = gate rows r0, r0+1 (lanes 0, 16), rows 2,3 = up rows (lanes 8, 24):
+                // h = silu(gate) * up (fl_op_silu_mul, src/runtime/decode_params.h:267-272)
+                k *= inv_rms;
+                const float up = __shfl_xor_sync(0xffffffffu, k, 8);
+                const uint32_t row = cur.r0 + ((lane >> 4) & 1u);
+                if ((lane & 15u) == 0 && row < cur.rows) cur.y[row] = (k / (1.0f + expf(-k))) * up;
+                continue;
+            }
             const uint32_t row = cur.r0 + ((lane >> 4) & 1u) + 2u * ((lane >> 3) & 1u);
             if ((lane & 7u) == 0 && row < cur.rows) {
+                k *= inv_rms;
                 float o = k;
                 if (cur.resid) o = cur.resid[row] + k;
                 if (a.accumulate) o = cur.y[row] + o;
@@ -499,6 +535,7 @@ matvec_stream_kernel(const MatvecArgs a, const __grid_constant__ TensorMaps maps
             }
         }
     }
+    if (lane == 0) trace_max(a.trace, 3);
 }
 
 // ---- generic kernel: warp per row, element-wise -------------------------------
@@ -601,18 +638,24 @@ cudaError_t matvec_init(void) {
 }
 
 // The packed tensor as [rows][row_bytes / 8] 8-byte elements, box = 4 rows x one segment.
-static cudaError_t encode_map(CUtensorMap *m, const MatvecTensor &t, uint32_t cols) {
+static cudaError_t encode_map(CUtensorMap *m, const MatvecTensor &t, uint32_t cols, uint32_t box_rows) {
     if (!g_encode) return cudaErrorNotSupported;
     const uint64_t rb = row_bytes(t.fmt, cols);
     const uint32_t seg = t.fmt == FMT_Q4_K ? kSeg4 : kSeg6;
     const cuuint64_t gdim[2] = {rb / 8, t.rows};
     const cuuint64_t gstride[1] = {rb};
-    const cuuint32_t box[2] = {seg / 8, (cuuint32_t)kRowsPerStage};
+    const cuuint32_t box[2] = {seg / 8, (cuuint32_t)box_rows};
     const cuuint32_t estr[2] = {1, 1};
     const CUresult r = g_encode(m, CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, (void *)t.w, gdim, gstride, box, estr,
                                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
                                 CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
+}
+
+// The streaming kernel assigns whole row quads to warps and needs no scratch.
+void matvec_scratch_need(const MatvecArgs &, int, size_t *scratch_floats, size_t *tickets) {
+    *scratch_floats = 0;
+    *tickets = 0;
 }
 
 cudaError_t launch_matvec(const MatvecArgs &a, int sms, cudaStream_t stream) {
@@ -631,16 +674,20 @@ cudaError_t launch_matvec(const MatvecArgs &a, int sms, cudaStream_t stream) {
         total_rows += t.rows;
         total_quads += (t.rows + kRowsPerStage - 1) / kRowsPerStage;
     }
+    if (a.swiglu) {
+        if (a.n_tensors != 2 || a.t[0].rows != a.t[1].rows || a.t[0].fmt != a.t[1].fmt || a.accumulate || !streaming)
+            return cudaErrorInvalidValue;
+        total_quads = (a.t[0].rows + 1) / 2;
+    }
     if (streaming) {
         int stages = 0;
         const size_t smem = matvec_smem_bytes(a.cols, q4, q6, &stages);
         if (smem <= 227 * 1024 - 1024 && stages >= 2) {
-            uint32_t grid = (total_quads + kWarps - 1) / kWarps;
-            if (grid > (uint32_t)sms) grid = (uint32_t)sms;
+            uint32_t grid = total_quads < (uint32_t)sms ? total_quads : (uint32_t)sms;
             TensorMaps maps;
             memset(&maps, 0, sizeof(maps));
             for (int i = 0; i < a.n_tensors; ++i) {
-                const cudaError_t e = encode_map(&maps.m[i], a.t[i], a.cols);
+                const cudaError_t e = encode_map(&maps.m[i], a.t[i], a.cols, a.swiglu ? 2 : kRowsPerStage);
                 if (e != cudaSuccess) return e;
             }
             return launch_kernel(matvec_stream_kernel, dim3(grid), dim3(kThreads), smem, stream, a.pdl != 0, a, maps,

@@ -107,6 +107,14 @@ class Decoder:
                                                      C.byref(ms), C.byref(n)))
         return ms.value, n.value
 
+    def trace(self):
+        """Per-launch device timestamps of the last step (FLB_TRACE=1): array [n, 4] of ns."""
+        cap = 16 + 8 * self.cfg["n_layer"]
+        buf = np.zeros((cap, 4), dtype=np.uint64)
+        n = C.c_uint32()
+        capi._ck(self.lib.fl_b200_decoder_trace(self._h, C.c_void_p(buf.ctypes.data), C.c_uint32(cap), C.byref(n)))
+        return buf[:n.value]
+
     def launches_per_step(self):
         v = C.c_uint32()
         capi._ck(self.lib.fl_b200_decoder_launches_per_step(self._h, C.byref(v)))

@@ -148,7 +148,7 @@ def model_weight_bytes(cfg, recipe=Q4_K_M):
 # Same layouts and value distributions as above, drawn with torch on the GPU so
 # that the 4.9 GB model of the benchmark is ready in about a second instead of
 # half a minute of host generation + upload. (Different random stream than the
-# numpy generators: use those whenever the CPU oracle must see the same bytes.)
+# numpy generators: use those whenever a host-side checker must see the same bytes.)
 
 def device_quant_tensor(fmt, rows, cols, gen):
     import torch

@@ -229,8 +229,8 @@ int fl_b200_decoder_margin(fl_b200_decoder *dec, float *margin_out);
 /* Activations of the last step, for layer-level parity. which: 0 hidden state
  * after the last layer (n_embd), 1 final normed vector (n_embd); of the last
  * layer: 2 q after RoPE (n_head*head_dim), 3 v (n_kv_head*head_dim), 4 attention
- * output (n_head*head_dim), 5 residual after attention (n_embd), 6 gate (n_ff),
- * 7 up (n_ff). */
+ * output (n_head*head_dim), 5 residual after attention (n_embd), 6 the FFN
+ * hidden vector silu(gate)*up (n_ff). */
 int fl_b200_decoder_tap(fl_b200_decoder *dec, int which, float *host_out);
 /* Times `reps` replays of one class of the step's kernels in isolation (same
  * launches, real weights and buffers, CUDA events on the context's stream).
@@ -238,6 +238,12 @@ int fl_b200_decoder_tap(fl_b200_decoder *dec, int which, float *host_out);
  * operators, 7 all of them. Results of the replays are not meaningful. */
 int fl_b200_decoder_time_class(fl_b200_decoder *dec, uint32_t kernel_class, uint32_t reps,
                                float *ms_per_step_out, uint32_t *launches_per_step_out);
+/* Diagnostics. With FLB_TRACE=1 in the environment when the decoder is
+ * finalized, every matvec and attention launch of a step records four device
+ * timestamps (ns): earliest kernel entry, earliest point after its dependency
+ * wait, latest end of its prologue, latest exit. Copies the records of the last
+ * fl_b200_decoder_step (4 values per launch, launch order) to host_out. */
+int fl_b200_decoder_trace(fl_b200_decoder *dec, uint64_t *host_out, uint32_t cap_records, uint32_t *n_out);
 /* Number of kernels this library launches per decoder step. */
 int fl_b200_decoder_launches_per_step(fl_b200_decoder *dec, uint32_t *n_out);
 /* Weight + KV bytes one step at position `pos` must read (the roofline numerator). */

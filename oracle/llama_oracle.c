@@ -259,7 +259,7 @@ const float *flo_llama_hidden(const flo_llama *m) { return m->x; }
 const float *flo_llama_normed(const flo_llama *m) { return m->xn; }
 /* Last-layer activations of the last step, same numbering as the GPU decoder's
  * taps: 2 q after RoPE, 3 v, 4 attention output, 5 residual after attention,
- * 6 gate, 7 up. */
+ * 6 the FFN hidden vector silu(gate) * up, 7 up. */
 const float *flo_llama_tap(const flo_llama *m, int which) {
     switch (which) {
     case 0: return m->x;
@@ -268,7 +268,7 @@ const float *flo_llama_tap(const flo_llama *m, int which) {
     case 3: return m->v;
     case 4: return m->att;
     case 5: return m->x1;
-    case 6: return m->g;
+    case 6: return m->h;
     case 7: return m->u;
     default: return 0;
     }
