@@ -11,12 +11,12 @@
 // the 64-position tile a CTA needs is one contiguous 16 KB range, fetched with a
 // 1-D bulk copy (TMA engine) into a 3-stage shared-memory ring.
 //
-// Grid = (n_splits, n_kv_head, batch), 128 threads. A CTA serves the 4 query
+// Grid = (n_splits, n_kv_head, batch), 256 threads. A CTA serves the 4 query
 // heads of its KV head, so every K/V byte is read from HBM once per group.
-//   scores : 8 lanes per position x 16 dims each, 4 heads per lane, shuffle
-//            reduce over the 8 lanes;
+//   scores : 8 lanes per position x 16 dims each (32 positions per pass), 4 heads
+//            per lane, shuffle reduce over the 8 lanes;
 //   softmax: warp h owns head h; online (running max / sum), exp in f32;
-//   context: 16 lanes per position x 8 dims, 8 positions in flight, 4 heads;
+//   context: 16 lanes per position x 8 dims, 16 positions in flight, 4 heads;
 // Each CTA writes (max, sum, context[128]) per head to scratch and takes a
 // ticket; the CTA that draws the last ticket of its (batch, kv head) rescales
 // and sums the partials in split order (deterministic) and writes the output.
@@ -32,7 +32,9 @@ constexpr int kD = 128;              // head dimension
 constexpr int kGroup = 4;            // query heads per KV head handled by one CTA
 constexpr int kTile = 64;            // positions per stage
 constexpr int kStages = 3;
-constexpr int kAttnThreads = 128;
+constexpr int kAttnThreads = 256;
+constexpr int kPosPerPass = kAttnThreads / 8;    // scores: 8 lanes per position
+constexpr int kPosGroups = kAttnThreads / 16;    // context: 16 lanes per position
 constexpr uint32_t kTileBytes = kTile * kD * 2;   // 16 KB
 constexpr int kPartStride = kD + 4;  // o[128], m, l, pad (keeps o 16-byte aligned)
 
@@ -46,7 +48,7 @@ struct AttnSmem {
     uint32_t is_last;
 };
 
-__global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnArgs a) {
+__global__ void __launch_bounds__(kAttnThreads, 2) attn_decode_kernel(const AttnArgs a) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     AttnSmem &sm = *reinterpret_cast<AttnSmem *>(smem_raw);
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
@@ -84,15 +86,17 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnArg
     if (tid == 0)
         for (uint32_t i = 0; i < (uint32_t)kStages && i < n_tiles; ++i) issue(i);
 
-    // q: this thread's 16 dims of the 4 heads
+    // q: this thread's 16 dims of the 4 heads: dims 8*ds .. 8*ds+7 and 64+8*ds ..
+    // 64+8*ds+7, so that the 8 lanes of a position read 128 contiguous bytes of its
+    // K row per load (no shared-memory bank conflicts).
     const uint32_t pp = tid >> 3, ds = tid & 7u;
-    const float *qg = a.q + ((uint64_t)b * a.n_q_head + (uint64_t)hkv * group) * kD + ds * 16;
+    const float *qg = a.q + ((uint64_t)b * a.n_q_head + (uint64_t)hkv * group) * kD + ds * 8;
     float q[kGroup][16];
 #pragma unroll
     for (int h = 0; h < kGroup; ++h)
 #pragma unroll
         for (int i = 0; i < 16; i += 4) {
-            const float4 t = *reinterpret_cast<const float4 *>(qg + h * kD + i);
+            const float4 t = *reinterpret_cast<const float4 *>(qg + h * kD + (i & 7) + (i >> 3) * 64);
             q[h][i] = t.x; q[h][i + 1] = t.y; q[h][i + 2] = t.z; q[h][i + 3] = t.w;
         }
 
@@ -113,12 +117,12 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnArg
 
         // ---- scores ----
 #pragma unroll
-        for (int pass = 0; pass < kTile / 16; ++pass) {
-            const uint32_t p = pass * 16 + pp;
+        for (int pass = 0; pass < kTile / kPosPerPass; ++pass) {
+            const uint32_t p = pass * kPosPerPass + pp;
             float acc[kGroup] = {0.f, 0.f, 0.f, 0.f};
             if (p < n) {
-                const uint4 r0 = *reinterpret_cast<const uint4 *>(&sm.k[slot][p][ds * 16]);
-                const uint4 r1 = *reinterpret_cast<const uint4 *>(&sm.k[slot][p][ds * 16 + 8]);
+                const uint4 r0 = *reinterpret_cast<const uint4 *>(&sm.k[slot][p][ds * 8]);
+                const uint4 r1 = *reinterpret_cast<const uint4 *>(&sm.k[slot][p][64 + ds * 8]);
                 const uint32_t rw[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
@@ -143,8 +147,8 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnArg
         }
         __syncthreads();
 
-        // ---- online softmax: warp h <-> head h ----
-        {
+        // ---- online softmax: warp h <-> head h (warps 0..3) ----
+        if (warp < kGroup) {
             const float s0 = sm.s[warp][lane], s1 = sm.s[warp][lane + 32];
             const float m_new = fmaxf(m_run, warp_max(fmaxf(s0, s1)));
             const float e0 = expf(s0 - m_new), e1 = expf(s1 - m_new);
@@ -166,8 +170,8 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnArg
 #pragma unroll
                 for (int i = 0; i < 8; ++i) o[h][i] *= alv[h];
 #pragma unroll
-            for (int j = 0; j < kTile / 8; ++j) {
-                const uint32_t p = j * 8 + pg;
+            for (int j = 0; j < kTile / kPosGroups; ++j) {
+                const uint32_t p = j * kPosGroups + pg;
                 if (p < n) {
                     const uint4 r = *reinterpret_cast<const uint4 *>(&sm.v[slot][p][dseg * 8]);
                     const float4 w = *reinterpret_cast<const float4 *>(&sm.p[p][0]);
@@ -193,13 +197,13 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnArg
     }
 
     // ---- reduce the 8 position groups, write this split's partial ----
-    float *red = reinterpret_cast<float *>(&sm.k[0][0][0]);   // [8][kGroup][kD] floats = 16 KB, ring is idle now
+    float *red = reinterpret_cast<float *>(&sm.k[0][0][0]);   // [kPosGroups][kGroup][kD] floats = 32 KB, ring is idle now
 #pragma unroll
     for (int h = 0; h < kGroup; ++h)
 #pragma unroll
         for (int i = 0; i < 8; ++i) red[(pg * kGroup + h) * kD + dseg * 8 + i] = o[h][i];
     __syncthreads();
-    {
+    if (warp < kGroup) {
         const uint32_t h = warp;   // head within the group
         float *part = a.part + (((uint64_t)b * a.n_q_head + (uint64_t)hkv * group + h) * a.n_splits + split) * kPartStride;
 #pragma unroll
@@ -207,7 +211,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnArg
             const uint32_t d = lane + 32 * k;
             float t = 0.f;
 #pragma unroll
-            for (int g = 0; g < 8; ++g) t += red[(g * kGroup + h) * kD + d];
+            for (int g = 0; g < kPosGroups; ++g) t += red[(g * kGroup + h) * kD + d];
             part[d] = t;
         }
         if (lane == 0) { part[kD] = m_run; part[kD + 1] = l_run; }
@@ -223,11 +227,12 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnArg
     if (!sm.is_last) return;
     __threadfence();
 
-    // ---- combine: warp h <-> head h. Lane s owns the weights of splits s and
-    // s + 32; the context is summed over splits in ascending order, each lane
-    // holding 4 dims, with the loads of 8 splits in flight. ----
+    // ---- combine: warps h and h+4 <-> head h. Every lane first derives the global
+    // maximum and the rescaled sum from all splits' (m, l); warp h then accumulates
+    // the context of the even splits and warp h+4 of the odd ones (each lane 4
+    // dims, 16 loads in flight), and the two halves are added in a fixed order. ----
     {
-        const uint32_t h = warp;
+        const uint32_t h = warp & 3u, half = warp >> 2;
         const uint64_t hq = (uint64_t)b * a.n_q_head + (uint64_t)hkv * group + h;
         const float *part = a.part + hq * a.n_splits * kPartStride;
         const uint32_t S = a.n_splits;
@@ -240,23 +245,30 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnArg
         const float w1 = m1 == -INFINITY ? 0.f : expf(m1 - mx);
         const float L = warp_sum(l0 * w0 + l1 * w1);
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (uint32_t s0 = 0; s0 < S; s0 += 8) {
-            float4 o[8];
+        for (uint32_t s0 = half; s0 < S; s0 += 32) {
+            float4 o[16];
 #pragma unroll
-            for (int j = 0; j < 8; ++j)
-                o[j] = s0 + j < S ? __ldcg(reinterpret_cast<const float4 *>(part + (uint64_t)(s0 + j) * kPartStride) + lane)
-                                  : make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int j = 0; j < 16; ++j)
+                o[j] = s0 + 2 * j < S ? __ldcg(reinterpret_cast<const float4 *>(part + (uint64_t)(s0 + 2 * j) * kPartStride) + lane)
+                                      : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const uint32_t s = s0 + j;
+            for (int j = 0; j < 16; ++j) {
+                const uint32_t s = s0 + 2 * j;
                 const float w = __shfl_sync(0xffffffffu, s < 32 ? w0 : w1, s & 31u);
                 acc.x = fmaf(o[j].x, w, acc.x); acc.y = fmaf(o[j].y, w, acc.y);
                 acc.z = fmaf(o[j].z, w, acc.z); acc.w = fmaf(o[j].w, w, acc.w);
             }
         }
-        const float inv = 1.0f / L;
-        acc.x *= inv; acc.y *= inv; acc.z *= inv; acc.w *= inv;
-        reinterpret_cast<float4 *>(a.out + hq * kD)[lane] = acc;
+        float4 *xch = reinterpret_cast<float4 *>(&sm.v[0][0][0]);   // the V ring is idle now
+        if (half == 1) xch[h * 32 + lane] = acc;
+        __syncthreads();
+        if (half == 0) {
+            const float4 other = xch[h * 32 + lane];
+            const float inv = 1.0f / L;
+            acc.x = (acc.x + other.x) * inv; acc.y = (acc.y + other.y) * inv;
+            acc.z = (acc.z + other.z) * inv; acc.w = (acc.w + other.w) * inv;
+            reinterpret_cast<float4 *>(a.out + hq * kD)[lane] = acc;
+        }
     }
     if (tid == 0) {
         a.tickets[b * a.n_kv_head + hkv] = 0;   // ready for the next launch

@@ -357,16 +357,28 @@ matvec_stream_kernel(const MatvecArgs a, const __grid_constant__ TensorMaps maps
     griddep_launch_dependents();
     if (lane == 0)
         while (p_i < (uint32_t)stages && p_i < my_stages) issue();
-    griddep_wait();   // the activation (and y, resid) come from the previous kernel
-    if (tid == 0) trace_min(a.trace, 1);
 
     // ---- build the fixed-point activation in shared memory ----
     // One warp per 256-column block (blocks warp, warp + kWarps, ...); lane l holds
     // columns 8l .. 8l+7 of the block. All global loads of all the warp's blocks
-    // are issued first, so the prologue costs one memory round trip.
+    // are issued first, so the prologue costs one memory round trip; the norm
+    // weights are constants and are fetched before the dependency wait.
     constexpr int kMaxBlk = 6;   // blocks per warp: cols <= 6 * 256 * kWarps = 18432
     const uint32_t nblk = a.cols / 256;
     float4 ra[kMaxBlk][2], rb2[kMaxBlk][2];
+    if (a.x_mode == MV_X_RMSNORM) {
+#pragma unroll
+        for (int b = 0; b < kMaxBlk; ++b) {
+            const uint32_t blk = warp + b * kWarps;
+            if (blk < nblk) {
+                const uint32_t c0 = blk * 256 + lane * 8;
+                rb2[b][0] = __ldg(reinterpret_cast<const float4 *>(a.wnorm + c0));
+                rb2[b][1] = __ldg(reinterpret_cast<const float4 *>(a.wnorm + c0 + 4));
+            }
+        }
+    }
+    griddep_wait();   // the activation (and y, resid) come from the previous kernel
+    if (tid == 0) trace_min(a.trace, 1);
 #pragma unroll
     for (int b = 0; b < kMaxBlk; ++b) {
         const uint32_t blk = warp + b * kWarps;
@@ -374,10 +386,9 @@ matvec_stream_kernel(const MatvecArgs a, const __grid_constant__ TensorMaps maps
             const uint32_t c0 = blk * 256 + lane * 8;
             ra[b][0] = *reinterpret_cast<const float4 *>(a.x + c0);
             ra[b][1] = *reinterpret_cast<const float4 *>(a.x + c0 + 4);
-            if (a.x_mode != MV_X_PLAIN) {
-                const float *p2 = a.x_mode == MV_X_RMSNORM ? a.wnorm : a.x2;
-                rb2[b][0] = *reinterpret_cast<const float4 *>(p2 + c0);
-                rb2[b][1] = *reinterpret_cast<const float4 *>(p2 + c0 + 4);
+            if (a.x_mode == MV_X_SILU_MUL) {
+                rb2[b][0] = *reinterpret_cast<const float4 *>(a.x2 + c0);
+                rb2[b][1] = *reinterpret_cast<const float4 *>(a.x2 + c0 + 4);
             }
         }
     }
