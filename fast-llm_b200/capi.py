@@ -24,7 +24,7 @@ SYMBOLS = [
     "fl_b200_device_status", "fl_b200_sm_count", "fl_b200_stream", "fl_b200_malloc", "fl_b200_free",
     "fl_b200_upload", "fl_b200_download", "fl_b200_memset", "fl_b200_timer_start", "fl_b200_timer_stop",
     "fl_b200_dequant", "fl_b200_matvec", "fl_b200_matvec_assign", "fl_b200_matvec_host",
-    "fl_b200_attn_decode", "fl_b200_attn_decode_host", "fl_b200_rmsnorm", "fl_b200_add2",
+    "fl_b200_attn_decode", "fl_b200_attn_decode_static", "fl_b200_attn_decode_host", "fl_b200_rmsnorm", "fl_b200_add2",
     "fl_b200_silu_mul", "fl_b200_rope_kv_append", "fl_b200_argmax", "fl_b200_exec_task",
     "fl_b200_decoder_create", "fl_b200_decoder_destroy", "fl_b200_decoder_set_layer_tensor",
     "fl_b200_decoder_set_layer_norms", "fl_b200_decoder_set_global", "fl_b200_decoder_set_out_norm",
@@ -165,6 +165,12 @@ class Context:
         _ck(self.lib.fl_b200_attn_decode(self._h, _p(q), _p(k), _p(v), C.c_uint32(n_q_head),
                                          C.c_uint32(n_kv_head), C.c_uint32(head_dim), C.c_uint32(kv_len),
                                          C.c_uint32(kv_stride), C.c_uint32(batch), C.c_float(scale), _p(out)))
+
+    def attn_decode_static(self, q, k, v, n_q_head, n_kv_head, head_dim, kv_len, kv_stride, batch, scale, out):
+        """attn_decode with its scratch in a fixed array of the library (no allocation at call time)."""
+        _ck(self.lib.fl_b200_attn_decode_static(self._h, _p(q), _p(k), _p(v), C.c_uint32(n_q_head),
+                                                C.c_uint32(n_kv_head), C.c_uint32(head_dim), C.c_uint32(kv_len),
+                                                C.c_uint32(kv_stride), C.c_uint32(batch), C.c_float(scale), _p(out)))
 
     def attn_decode_host(self, q_host, k, v, n_q_head, n_kv_head, head_dim, kv_len, kv_stride, batch, scale,
                          out_host):

@@ -296,6 +296,57 @@ size_t attn_part_floats(uint32_t n_q_head, uint32_t batch, uint32_t n_splits) {
     return (size_t)n_q_head * batch * n_splits * kPartStride;
 }
 
+// ---- Split-KV scratch that lives in the module image instead of the heap ----
+//
+// Some callers may not allocate device memory at call time at all: a serving
+// loop that promised its embedder a fixed memory footprint after start-up, or a
+// host thread that runs between two points where cudaMalloc's implicit
+// device-wide synchronisation would stall other streams. For them the partial
+// results of the split-KV kernel (one 132-float record per query head and split)
+// and the per-KV-head arrival counters sit in this fixed array. Its size is the
+// limit of the variant: kStaticMaxRecords records (4096 x 528 B = 2.1 MB, e.g.
+// 64 query heads x 64 splits) and kStaticMaxTickets (KV head, sequence) pairs.
+// Every call on a device shares the one array, so two calls that overlap in
+// time (different streams or host threads) race on it; calls on one stream are
+// ordered and safe.
+constexpr size_t kStaticMaxRecords = 4096;
+constexpr uint32_t kStaticMaxTickets = 256;
+constexpr size_t kStaticPartFloats = kStaticMaxRecords * kPartStride;
+static __device__ __align__(256) float g_attn_static_scratch[kStaticPartFloats + kStaticMaxTickets];
+
+constexpr int kMaxDevices = 64;
+static float *g_static_ptr[kMaxDevices];   // device address of the array, per device; nullptr = not asked yet
+
+// Launches the split-KV kernel with its scratch in the static array. a.part and
+// a.tickets are ignored. The first call on a device resolves the array's device
+// address (cudaGetSymbolAddress; that first call may initialise the module, so
+// make it before any stream capture). The counters have to be zero when the
+// kernel starts: the kernel leaves them at zero, but a launch that gave up on a
+// bounded wait may not, so they are cleared on the stream in front of every
+// launch (a memset node: no allocation).
+cudaError_t launch_attn_decode_static(AttnArgs a, int device, cudaStream_t stream, size_t *records_needed) {
+    const size_t records = (size_t)a.n_q_head * a.batch * a.n_splits;
+    if (records_needed) *records_needed = records;
+    if (device < 0 || device >= kMaxDevices) return cudaErrorInvalidDevice;
+    if (records > kStaticMaxRecords || (uint64_t)a.n_kv_head * a.batch > kStaticMaxTickets)
+        return cudaErrorMemoryAllocation;   // the caller turns this into its size message
+    if (!g_static_ptr[device]) {
+        float *ptr = nullptr;
+        const cudaError_t e = cudaGetSymbolAddress((void **)&ptr, g_attn_static_scratch);
+        if (e != cudaSuccess) return e;
+        g_static_ptr[device] = ptr;
+    }
+    float *ptr = g_static_ptr[device];
+    a.part = ptr;
+    a.tickets = reinterpret_cast<uint32_t *>(ptr + kStaticPartFloats);
+    const cudaError_t e = cudaMemsetAsync(a.tickets, 0, (size_t)a.n_kv_head * a.batch * sizeof(uint32_t), stream);
+    if (e != cudaSuccess) return e;
+    return launch_attn_decode(a, stream);
+}
+
+size_t attn_static_max_records(void) { return kStaticMaxRecords; }
+uint32_t attn_static_max_tickets(void) { return kStaticMaxTickets; }
+
 cudaError_t launch_attn_decode(const AttnArgs &a, cudaStream_t stream) {
     if (a.n_kv_head == 0 || a.n_q_head != a.n_kv_head * kGroup || a.n_splits == 0 || a.batch == 0)
         return cudaErrorInvalidValue;

@@ -312,6 +312,47 @@ int fl_b200_attn_decode(fl_b200_ctx *c, const float *q, const uint16_t *k, const
     return attn_impl(c, q, k, v, n_q, n_kv, d, kv_len, kv_stride, batch, scale, out, nullptr);
 }
 
+// fl_b200_attn_decode without any allocation at call time: the split-KV scratch
+// is a fixed array in the library image (attn.cu). Same arguments, same kernel,
+// same results as fl_b200_attn_decode.
+int fl_b200_attn_decode_static(fl_b200_ctx *c, const float *q, const uint16_t *k, const uint16_t *v, uint32_t n_q,
+                               uint32_t n_kv, uint32_t d, uint32_t kv_len, uint32_t kv_stride, uint32_t batch,
+                               float scale, float *out) {
+    if (!c) return set_err(FL_B200_ERR_ARG, "attn_decode_static: null context");
+    if (!q || !k || !v || !out) return set_err(FL_B200_ERR_ARG, "attn_decode_static: null pointer");
+    if (d != 128) return set_err(FL_B200_ERR_ARG, "attn_decode_static: head_dim %u (only 128 is built)", d);
+    if (n_kv == 0 || n_q != 4 * n_kv)
+        return set_err(FL_B200_ERR_ARG, "attn_decode_static: %u query heads over %u KV heads (only groups of 4 are built)", n_q, n_kv);
+    if (batch == 0) return set_err(FL_B200_ERR_ARG, "attn_decode_static: batch 0");
+    if (kv_len == 0 || kv_len > kv_stride)
+        return set_err(FL_B200_ERR_ARG, "attn_decode_static: kv_len %u outside 1..kv_stride %u", kv_len, kv_stride);
+    if (((uintptr_t)k & 15u) || ((uintptr_t)v & 15u) || ((uintptr_t)q & 15u))
+        return set_err(FL_B200_ERR_ARG, "attn_decode_static: q, k, v must be 16-byte aligned");
+    AttnArgs a{};
+    a.q = q;
+    a.k = (const __half *)k;
+    a.v = (const __half *)v;
+    a.out = out;
+    a.pos = nullptr;
+    a.kv_len = kv_len;
+    a.kv_stride = kv_stride;
+    a.batch_stride = (uint64_t)n_kv * kv_stride * d;
+    a.n_q_head = n_q;
+    a.n_kv_head = n_kv;
+    a.batch = batch;
+    a.n_splits = attn_pick_splits(n_kv, batch, kv_len, c->sms);
+    a.scale = scale;
+    a.status = c->status;
+    size_t records = 0;
+    const cudaError_t e = launch_attn_decode_static(a, c->device, c->stream, &records);
+    if (e == cudaErrorMemoryAllocation)
+        return set_err(FL_B200_ERR_ARG,
+                       "attn_decode_static: needs %zu scratch records (n_q_head * batch * splits) and %llu counters; "
+                       "the fixed scratch holds %zu records and %u counters - use fl_b200_attn_decode",
+                       records, (unsigned long long)n_kv * batch, attn_static_max_records(), attn_static_max_tickets());
+    return cuda_err(e, "attn_decode_static launch");
+}
+
 int fl_b200_attn_decode_host(fl_b200_ctx *c, const float *q_host, const uint16_t *k, const uint16_t *v,
                              uint32_t n_q, uint32_t n_kv, uint32_t d, uint32_t kv_len, uint32_t kv_stride,
                              uint32_t batch, float scale, float *out_host) {

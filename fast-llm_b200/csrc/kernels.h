@@ -80,6 +80,13 @@ struct AttnArgs {
     unsigned long long *trace;   // optional 4-entry timeline record (diagnostics)
 };
 cudaError_t launch_attn_decode(const AttnArgs &a, cudaStream_t stream);
+// Same kernel with the split-KV scratch in a fixed file-scope device array
+// (no allocation at call time); cudaErrorMemoryAllocation when the launch needs
+// more than attn_static_max_records() records or attn_static_max_tickets()
+// (KV head, sequence) pairs.
+cudaError_t launch_attn_decode_static(AttnArgs a, int device, cudaStream_t stream, size_t *records_needed);
+size_t attn_static_max_records(void);
+uint32_t attn_static_max_tickets(void);
 cudaError_t attn_init(void);
 uint32_t attn_pick_splits(uint32_t n_kv_head, uint32_t batch, uint32_t kv_len, int sms);
 size_t attn_part_floats(uint32_t n_q_head, uint32_t batch, uint32_t n_splits);

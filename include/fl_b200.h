@@ -106,6 +106,18 @@ int fl_b200_matvec_host(fl_b200_ctx *ctx, int fmt, const void *w_dev, uint32_t r
 int fl_b200_attn_decode(fl_b200_ctx *ctx, const float *q_dev, const uint16_t *k_dev, const uint16_t *v_dev,
                         uint32_t n_q_head, uint32_t n_kv_head, uint32_t head_dim, uint32_t kv_len,
                         uint32_t kv_stride, uint32_t batch, float scale, float *out_dev);
+/* fl_b200_attn_decode for callers that must not allocate device memory at call
+ * time. It has no counterpart in the reference, whose operators keep their
+ * temporaries in the caller's buffers. The split-KV scratch is a fixed array in
+ * the library image: at most 4096 records of n_q_head * batch * splits (splits
+ * <= 64, chosen from the SM count and kv_len) and n_kv_head * batch <= 256;
+ * larger calls return FL_B200_ERR_ARG and leave `out` untouched. Arguments and
+ * results are those of fl_b200_attn_decode. The first call on a device looks up
+ * the array's address and should be made before any stream capture. All calls
+ * on a device share the array: calls that overlap in time race on it. */
+int fl_b200_attn_decode_static(fl_b200_ctx *ctx, const float *q_dev, const uint16_t *k_dev,
+                               const uint16_t *v_dev, uint32_t n_q_head, uint32_t n_kv_head, uint32_t head_dim,
+                               uint32_t kv_len, uint32_t kv_stride, uint32_t batch, float scale, float *out_dev);
 int fl_b200_attn_decode_host(fl_b200_ctx *ctx, const float *q_host, const uint16_t *k_dev,
                              const uint16_t *v_dev, uint32_t n_q_head, uint32_t n_kv_head, uint32_t head_dim,
                              uint32_t kv_len, uint32_t kv_stride, uint32_t batch, float scale,
