@@ -155,13 +155,15 @@ def main():
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--layers", type=int, default=32,
+                    help="number of layers (32 = the benchmark; fewer = a small case of the same kernels for profiler captures, not a benchmark number)")
     args = ap.parse_args()
     steps, warmup = max(1, args.steps), max(3, args.warmup)
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     config = {"workload": "synthetic Llama-3-8B-shape Q4_K_M greedy decode, batch 1, 8192-token prefilled f16 KV",
-              "n_layer": 32, "hidden": 4096, "heads": "32/8 x 128", "ffn": 14336, "vocab": 128256,
+              "n_layer": args.layers, "hidden": 4096, "heads": "32/8 x 128", "ffn": 14336, "vocab": 128256,
               "kv_prefill": N_PREFILL, "parallelism": "replicas x%d" % world if world > 1 else "single GPU",
               "l2": "each step reads 6.0 GB of distinct weights and KV, far larger than L2; no flush needed"}
 
@@ -190,7 +192,9 @@ def main():
         torch.cuda.set_device(local_rank)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     ctx = capi.Context(local_rank)
-    cfg = dict(synth.LLAMA3_8B)
+    cfg = dict(synth.LLAMA3_8B, n_layer=args.layers)
+    if args.layers != 32:
+        config["workload"] += " (REDUCED to %d layers: profiler case, not the benchmark)" % args.layers
     if steps + warmup + 8 > cfg["max_kv"] - N_PREFILL:
         cfg["max_kv"] = N_PREFILL + steps + warmup + 8
     dec = Decoder(ctx, cfg)
