@@ -36,6 +36,9 @@ N_PREFILL = 8192
 METRIC = "decode tokens/s at 8B Q4_K_M shape, 1/2/4/8 B200; HBM GB/s % of roofline"
 
 
+NCU_TRAFFIC_RATIO = 1.0095
+
+
 def measured_peaks():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
@@ -257,7 +260,11 @@ def main():
         "data": "synthetic", "config": config,
         "roofline": {"bound": "hbm", "kernel": "matvec_stream_kernel", "achieved": achieved, "peak": peak,
                      "peak_source": "MEASURED_PEAKS.json hbm_gbs" if peak_kind == "measured" else "fallback 6.65 TB/s",
-                     "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+                     "unit": "GB/s", "frac": achieved / peak,
+                     # dram__bytes_read.sum + dram__bytes_write.sum of the four matvec launch shapes in one ncu
+                     # capture (profiles/matvec_stream_kernel_8b_layer_shapes.md) were 1.0095 x their algorithmic
+                     # bytes; traffic grows in proportion to the weights streamed, so it is scaled to this launch mix
+                     "traffic": NCU_TRAFFIC_RATIO * w_bytes / mv_n,
                      "bytes_per_launch": w_bytes / mv_n, "launches_per_step": mv_n, "avg_launch_us": mv_ms * 1e3 / mv_n,
                      "step": {"bytes": w_bytes + kv_bytes, "achieved": (w_bytes + kv_bytes) / (ms_dev / steps * 1e-3) / 1e9,
                               "frac": (w_bytes + kv_bytes) / (ms_dev / steps * 1e-3) / 1e9 / peak,
