@@ -22,11 +22,12 @@ G_TOK_EMBD, G_OUTPUT = 0, 1
 SYMBOLS = [
     "fl_b200_abi_version", "fl_b200_last_error", "fl_b200_create", "fl_b200_destroy", "fl_b200_sync",
     "fl_b200_device_status", "fl_b200_sm_count", "fl_b200_stream", "fl_b200_malloc", "fl_b200_free",
-    "fl_b200_upload", "fl_b200_download", "fl_b200_memset", "fl_b200_timer_start", "fl_b200_timer_stop",
-    "fl_b200_dequant", "fl_b200_matvec", "fl_b200_matvec_assign", "fl_b200_matvec_host",
+    "fl_b200_upload", "fl_b200_download", "fl_b200_memset", "fl_b200_ipc_export", "fl_b200_ipc_open", "fl_b200_ipc_close", "fl_b200_timer_start", "fl_b200_timer_stop",
+    "fl_b200_dequant", "fl_b200_matvec", "fl_b200_matvec_assign", "fl_b200_matvec_pitched", "fl_b200_matvec_host",
     "fl_b200_attn_decode", "fl_b200_attn_decode_static", "fl_b200_attn_decode_host", "fl_b200_rmsnorm", "fl_b200_add2",
     "fl_b200_silu_mul", "fl_b200_rope_kv_append", "fl_b200_argmax", "fl_b200_exec_task",
-    "fl_b200_decoder_create", "fl_b200_decoder_destroy", "fl_b200_decoder_set_layer_tensor",
+    "fl_b200_decoder_create", "fl_b200_decoder_create_tp", "fl_b200_decoder_comm", "fl_b200_decoder_set_peers",
+    "fl_b200_decoder_destroy", "fl_b200_decoder_set_layer_tensor",
     "fl_b200_decoder_set_layer_norms", "fl_b200_decoder_set_global", "fl_b200_decoder_set_out_norm",
     "fl_b200_decoder_kv", "fl_b200_decoder_finalize", "fl_b200_decoder_set_n_past",
     "fl_b200_decoder_n_past", "fl_b200_decoder_step", "fl_b200_decoder_run", "fl_b200_decoder_logits",
@@ -155,6 +156,10 @@ class Context:
 
     def matvec_assign(self, fmt, w, rows, cols, x, y):
         _ck(self.lib.fl_b200_matvec_assign(self._h, fmt, _p(w), C.c_uint32(rows), C.c_uint32(cols), _p(x), _p(y)))
+
+    def matvec_pitched(self, fmt, w, rows, cols, pitch, x, y):
+        _ck(self.lib.fl_b200_matvec_pitched(self._h, fmt, _p(w), C.c_uint32(rows), C.c_uint32(cols), C.c_uint32(pitch),
+                                            _p(x), _p(y)))
 
     def matvec_host(self, fmt, w, rows, cols, x_host, y_host):
         """x_host / y_host: numpy float32 arrays (or pinned torch CPU tensors)."""

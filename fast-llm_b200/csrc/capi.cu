@@ -167,6 +167,34 @@ int fl_b200_download(fl_b200_ctx *c, void *dst, const void *src, size_t bytes) {
     CK(cudaStreamSynchronize(c->stream));
     return FL_B200_OK;
 }
+// CUDA IPC: lets the ranks of a tensor-parallel group (one process per GPU) map
+// each other's exchange buffers. The handle is the 64-byte cudaIpcMemHandle_t.
+int fl_b200_ipc_export(fl_b200_ctx *c, const void *dev_ptr, uint8_t handle_out[64]) {
+    if (!c || !dev_ptr || !handle_out) return set_err(FL_B200_ERR_ARG, "ipc_export: null");
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    CK(cudaSetDevice(c->device));
+    cudaIpcMemHandle_t h;
+    CK(cudaIpcGetMemHandle(&h, const_cast<void *>(dev_ptr)));
+    memcpy(handle_out, &h, 64);
+    return FL_B200_OK;
+}
+
+int fl_b200_ipc_open(fl_b200_ctx *c, const uint8_t handle[64], void **dev_ptr_out) {
+    if (!c || !handle || !dev_ptr_out) return set_err(FL_B200_ERR_ARG, "ipc_open: null");
+    CK(cudaSetDevice(c->device));
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, 64);
+    CK(cudaIpcOpenMemHandle(dev_ptr_out, h, cudaIpcMemLazyEnablePeerAccess));
+    return FL_B200_OK;
+}
+
+int fl_b200_ipc_close(fl_b200_ctx *c, void *dev_ptr) {
+    if (!c || !dev_ptr) return set_err(FL_B200_ERR_ARG, "ipc_close: null");
+    CK(cudaSetDevice(c->device));
+    CK(cudaIpcCloseMemHandle(dev_ptr));
+    return FL_B200_OK;
+}
+
 int fl_b200_memset(fl_b200_ctx *c, void *dst, int value, size_t bytes) {
     CK(cudaMemsetAsync(dst, value, bytes, c->stream));
     return FL_B200_OK;
@@ -207,8 +235,11 @@ static int check_matvec(int fmt, const void *w, uint32_t rows, uint32_t cols, co
 }
 
 static int matvec_impl(fl_b200_ctx *c, int fmt, const void *w, uint32_t rows, uint32_t cols, const float *x,
-                       uint32_t nx, uint32_t xstride, float *y, uint32_t ystride, int accumulate) {
+                       uint32_t nx, uint32_t xstride, float *y, uint32_t ystride, int accumulate, uint32_t pitch = 0) {
     if (int rc = check_matvec(fmt, w, rows, cols, x, y)) return rc;
+    if (pitch != 0 && pitch < row_bytes(fmt, cols))
+        return set_err(FL_B200_ERR_ARG, "matvec: row pitch %u smaller than the packed row (%llu bytes)", pitch,
+                       (unsigned long long)row_bytes(fmt, cols));
     if (nx == 0) nx = 1;
     for (uint32_t p = 0; p < nx; ++p) {
         MatvecArgs a{};
@@ -218,6 +249,7 @@ static int matvec_impl(fl_b200_ctx *c, int fmt, const void *w, uint32_t rows, ui
         a.t[0].resid = nullptr;
         a.t[0].rows = rows;
         a.t[0].fmt = fmt;
+        a.t[0].pitch = pitch;
         a.x = x + (size_t)p * xstride;
         a.cols = cols;
         a.x_mode = MV_X_PLAIN;
@@ -227,6 +259,11 @@ static int matvec_impl(fl_b200_ctx *c, int fmt, const void *w, uint32_t rows, ui
         if (int rc = cuda_err(launch_matvec(a, c->sms, c->stream), "matvec launch")) return rc;
     }
     return FL_B200_OK;
+}
+
+int fl_b200_matvec_pitched(fl_b200_ctx *c, int fmt, const void *w, uint32_t rows, uint32_t cols, uint32_t pitch,
+                           const float *x, float *y) {
+    return matvec_impl(c, fmt, w, rows, cols, x, 1, 0, y, 0, 0, pitch);
 }
 
 int fl_b200_matvec(fl_b200_ctx *c, int fmt, const void *w, uint32_t rows, uint32_t cols, const float *x,

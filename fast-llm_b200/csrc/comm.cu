@@ -1,0 +1,179 @@
+// Exchange steps of the tensor-parallel decode step (one process per GPU, up to
+// 8 GPUs of one NVSwitch domain). The reference has no multi-GPU path; the
+// partition follows the decode graph: Q/K/V, gate/up and the head are split by
+// output rows (KV heads), O and down by input columns, so a layer needs two
+// sums of a hidden-size vector over the ranks and the step one exchange of the
+// per-rank (best, index, runner-up) of the logits.
+//
+// One-shot push all-reduce over peer memory. Every rank owns a communication
+// buffer that all ranks map (CUDA IPC):
+//     recv [2 slots][kMaxRanks][kMaxVec] f32    partial vectors, written by the owners of the rows
+//     flags[2 slots][kMaxRanks][kChunks] u32    "chunk c of rank r has landed", holds the epoch
+//     top  [2 slots][kMaxRanks][4] f32          per-rank argmax records
+//     tflag[2 slots][kMaxRanks] u32
+// A launch with epoch e (a per-rank counter that every exchange launch bumps,
+// identical on all ranks because they run the same launch sequence) uses slot
+// e & 1. CTA c pushes chunk c of its partial vector into every rank's recv
+// (plain stores over NVLink), makes them visible (fence.acq_rel.sys after a CTA
+// barrier) and publishes flag = e at each destination; then it waits until the
+// flags of all ranks for its chunk in its OWN buffer equal e, and adds the G
+// partials in rank order (so every rank computes bit-identical sums) plus the
+// residual. Two slots are enough: a rank can only push epoch e+2 after it has
+// seen every rank's flag of epoch e+1, which a rank publishes after it has
+// finished reading epoch e.
+//
+// Waits are bounded (about one second of %globaltimer); on expiry the kernel
+// records ST_PEER_TIMEOUT in the status word and returns without writing its
+// output. No multimem / NVLS and no TMA are used here: plain peer stores and
+// local loads only, so a rank that dies leaves the others with a time-out, not
+// a fault.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace flb {
+
+namespace {
+
+__device__ __forceinline__ void fence_acq_rel_sys() { asm volatile("fence.acq_rel.sys;" ::: "memory"); }
+__device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// Spins until *flag == want; false (and the status word set) after about a second.
+__device__ __forceinline__ bool wait_flag(const uint32_t *flag, uint32_t want, uint32_t *status) {
+    if (ld_acquire_sys(flag) == want) return true;
+    const uint64_t t0 = globaltimer_ns();
+    for (;;) {
+        for (int i = 0; i < 32; ++i)
+            if (ld_acquire_sys(flag) == want) return true;
+        if (globaltimer_ns() - t0 > 1000000000ull) {
+            atomicCAS(status, ST_OK, ST_PEER_TIMEOUT);
+            return false;
+        }
+    }
+}
+
+__device__ __forceinline__ float *recv_of(uint8_t *base, uint32_t slot, uint32_t rank) {
+    return reinterpret_cast<float *>(base) + ((size_t)slot * kCommMaxRanks + rank) * kCommMaxVec;
+}
+__device__ __forceinline__ uint32_t *flag_of(uint8_t *base, uint32_t slot, uint32_t rank, uint32_t chunk) {
+    return reinterpret_cast<uint32_t *>(base + kCommFlagsOff) + ((size_t)slot * kCommMaxRanks + rank) * kCommChunks + chunk;
+}
+__device__ __forceinline__ float *top_of(uint8_t *base, uint32_t slot, uint32_t rank) {
+    return reinterpret_cast<float *>(base + kCommTopOff) + ((size_t)slot * kCommMaxRanks + rank) * 4;
+}
+__device__ __forceinline__ uint32_t *tflag_of(uint8_t *base, uint32_t slot, uint32_t rank) {
+    return reinterpret_cast<uint32_t *>(base + kCommTFlagOff) + (size_t)slot * kCommMaxRanks + rank;
+}
+
+// The last CTA of an exchange launch stores the epoch it used.
+__device__ __forceinline__ void finish_epoch(CommState st, uint32_t e) {
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        if (atomicAdd(st.done, 1u) == gridDim.x - 1) {
+            *st.done = 0;
+            *st.epoch = e;
+        }
+    }
+}
+
+// out[i] = resid[i] + sum over ranks of their `in`[i], i < n (n a multiple of 4 * kCommChunks).
+// grid = kCommChunks, block = n / (4 * kCommChunks) threads.
+__global__ void __launch_bounds__(1024) allreduce_resid_kernel(const AllReduceArgs a) {
+    griddep_launch_dependents();
+    griddep_wait();
+    __shared__ uint32_t ok_s;
+    const uint32_t tid = threadIdx.x, chunk = blockIdx.x;
+    const uint32_t e = *a.st.epoch + 1u, slot = e & 1u;
+    const uint32_t i = (chunk * blockDim.x + tid) * 4;
+    if (tid == 0) ok_s = 1u;
+    const float4 mine = *reinterpret_cast<const float4 *>(a.in + i);
+    for (uint32_t k = 0; k < a.world; ++k) {
+        const uint32_t p = (a.rank + k) % a.world;   // own buffer first, then the ring of peers
+        *reinterpret_cast<float4 *>(recv_of(a.peers[p], slot, a.rank) + i) = mine;
+    }
+    __syncthreads();
+    if (tid < a.world) {
+        fence_acq_rel_sys();
+        st_release_sys(flag_of(a.peers[tid], slot, a.rank, chunk), e);
+        if (!wait_flag(flag_of(a.peers[a.rank], slot, tid, chunk), e, a.status)) ok_s = 0u;
+    }
+    __syncthreads();
+    if (ok_s) {
+        float4 acc = a.resid ? *reinterpret_cast<const float4 *>(a.resid + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+        for (uint32_t r = 0; r < a.world; ++r) {
+            const float4 v = __ldcg(reinterpret_cast<const float4 *>(recv_of(a.peers[a.rank], slot, r) + i));
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+        *reinterpret_cast<float4 *>(a.out + i) = acc;
+    }
+    finish_epoch(a.st, e);
+}
+
+struct Top { float b; uint32_t i; float s; };
+__device__ __forceinline__ Top top_merge(const Top &x, const Top &y) {
+    const bool y_wins = y.b > x.b || (y.b == x.b && y.i < x.i);
+    Top r;
+    if (y_wins) { r.b = y.b; r.i = y.i; r.s = fmaxf(x.b, fmaxf(x.s, y.s)); }
+    else { r.b = x.b; r.i = x.i; r.s = fmaxf(y.b, fmaxf(x.s, y.s)); }
+    return r;
+}
+
+// Every rank holds the (best, index, runner-up) of its slice of the logits
+// (top3 = {best, index bits, runner-up}; index local to the slice). All ranks
+// exchange them and merge in rank order with the reference's tie rule (lowest
+// global index wins, src/model/decoder.cpp:1253-1264): identical token on all ranks.
+__global__ void __launch_bounds__(32) argmax_exchange_kernel(const TopExchangeArgs a) {
+    griddep_launch_dependents();
+    griddep_wait();
+    const uint32_t tid = threadIdx.x;
+    const uint32_t e = *a.st.epoch + 1u, slot = e & 1u;
+    bool ok = true;
+    if (tid < a.world) {
+        float4 rec;
+        rec.x = a.top3[0];
+        rec.y = __uint_as_float(__float_as_uint(a.top3[1]) + a.index_base);
+        rec.z = a.top3[2];
+        rec.w = 0.f;
+        *reinterpret_cast<float4 *>(top_of(a.peers[tid], slot, a.rank)) = rec;
+        fence_acq_rel_sys();
+        st_release_sys(tflag_of(a.peers[tid], slot, a.rank), e);
+        ok = wait_flag(tflag_of(a.peers[a.rank], slot, tid), e, a.status);
+    }
+    ok = __all_sync(0xffffffffu, ok);
+    if (ok && tid == 0) {
+        Top r{-INFINITY, 0xFFFFFFFFu, -INFINITY};
+        for (uint32_t k = 0; k < a.world; ++k) {
+            const float4 v = __ldcg(reinterpret_cast<const float4 *>(top_of(a.peers[a.rank], slot, k)));
+            Top u{v.x, __float_as_uint(v.y), v.z};
+            r = top_merge(r, u);
+        }
+        *a.out_idx = (int32_t)r.i;
+        *a.out_margin = r.b - r.s;
+    }
+    finish_epoch(a.st, e);
+}
+
+} // namespace
+
+size_t comm_buffer_bytes(void) { return kCommBytes; }
+
+cudaError_t launch_allreduce_resid(const AllReduceArgs &a, cudaStream_t stream, bool pdl) {
+    if (a.world < 1 || a.world > kCommMaxRanks || a.rank >= a.world || a.n == 0 || a.n > kCommMaxVec ||
+        a.n % (4 * kCommChunks) != 0 || a.n / (4 * kCommChunks) > 1024)
+        return cudaErrorInvalidValue;
+    return launch_kernel(allreduce_resid_kernel, dim3(kCommChunks), dim3(a.n / (4 * kCommChunks)), 0, stream, pdl, a);
+}
+
+cudaError_t launch_argmax_exchange(const TopExchangeArgs &a, cudaStream_t stream, bool pdl) {
+    if (a.world < 1 || a.world > kCommMaxRanks || a.rank >= a.world) return cudaErrorInvalidValue;
+    return launch_kernel(argmax_exchange_kernel, dim3(1), dim3(32), 0, stream, pdl, a);
+}
+
+} // namespace flb

@@ -15,6 +15,7 @@ enum : int { FMT_F32 = 0, FMT_Q8_0 = 1, FMT_Q5_0 = 2, FMT_Q4_K = 3, FMT_Q6_K = 4
 enum : uint32_t {
     ST_OK = 0,
     ST_WAIT_TIMEOUT = 1,   // a bounded mbarrier wait gave up
+    ST_PEER_TIMEOUT = 2,   // a bounded wait for another rank's flag gave up
 };
 
 __host__ __device__ inline uint32_t blk_elems(int fmt) {

@@ -27,7 +27,7 @@ using namespace flb;
 
 namespace {
 
-struct Tensor { int fmt = -1; const uint8_t *w = nullptr; };
+struct Tensor { int fmt = -1; const uint8_t *w = nullptr; uint32_t pitch = 0; };
 
 // Timeline records start as {~0, ~0, 0, 0} (two minima, two maxima).
 __global__ void trace_init_kernel(unsigned long long *t, uint32_t n) {
@@ -54,7 +54,17 @@ __global__ void advance_kernel(int32_t *token, const int32_t *next, int32_t *pos
 
 struct fl_b200_decoder {
     fl_b200_ctx *ctx = nullptr;
-    fl_b200_llama_cfg c{};
+    fl_b200_llama_cfg c{};                  // the whole model
+    // Tensor parallelism: this rank's share. Q/K/V, gate/up and the head are split
+    // by output rows (whole KV heads with their 4 query heads), O and down by
+    // input columns; the hidden state is replicated.
+    uint32_t tp_rank = 0, tp_size = 1;
+    uint32_t Hq = 0, Hkv = 0, F = 0, V = 0;  // local query heads, KV heads, FFN rows, vocabulary rows
+    uint8_t *comm = nullptr;                // this rank's exchange buffer (mapped by the peers)
+    uint8_t *peers[kCommMaxRanks] = {};     // all ranks' buffers as mapped here
+    bool peers_set = false;
+    uint32_t *comm_state = nullptr;         // [0] epoch, [1] CTA counter
+    float *partial = nullptr, *top3 = nullptr;
     std::vector<Tensor> lw;                 // n_layer * 7
     std::vector<const float *> attn_norm, ffn_norm;
     Tensor tok_embd, output;
@@ -87,7 +97,7 @@ struct fl_b200_decoder {
 static int kPdl = 1;
 
 // Kernel classes, for timing one class of the step in isolation.
-enum : uint32_t { K_MATVEC = 1u, K_ATTN = 2u, K_OTHER = 4u, K_ALL = 7u };
+enum : uint32_t { K_MATVEC = 1u, K_ATTN = 2u, K_OTHER = 4u, K_COMM = 8u, K_ALL = 15u };
 
 // dry = true: no launches, only grows the context's matvec scratch to what the
 // step's launches need (must run before the step is captured).
@@ -103,16 +113,26 @@ static int enqueue_step(fl_b200_decoder *d, cudaStream_t s, uint32_t *n_launch, 
     if (dry) mask = K_MATVEC;
     const fl_b200_llama_cfg &c = d->c;
     fl_b200_ctx *ctx = d->ctx;
-    const uint32_t E = c.n_embd, D = c.head_dim, QD = c.n_head * D, KD = c.n_kv_head * D;
+    const uint32_t E = c.n_embd, D = c.head_dim, QD = d->Hq * D, KD = d->Hkv * D;
+    const bool tp = d->tp_size > 1;
+    const CommState cst{d->comm_state, d->comm_state ? d->comm_state + 1 : nullptr};
+    // sum of the ranks' partial vectors + residual (the exchange step after O and after down)
+    auto do_allreduce = [&](const float *resid, float *out) -> int {
+        AllReduceArgs r{};
+        for (uint32_t p = 0; p < d->tp_size; ++p) r.peers[p] = d->peers[p];
+        r.in = d->partial; r.resid = resid; r.out = out; r.n = E; r.rank = d->tp_rank; r.world = d->tp_size;
+        r.st = cst; r.status = ctx->status;
+        return cuda_err(launch_allreduce_resid(r, s, kPdl != 0), "all-reduce launch");
+    };
     if (mask & K_OTHER) { CK(launch_embed(d->tok_embd.fmt, d->tok_embd.w, d->d_token, E, d->xa, s, false)); ++n; }
     for (uint32_t l = 0; l < c.n_layer; ++l) {
         const Tensor *w = &d->lw[(size_t)l * 7];
         {   // RMSNorm + Q/K/V
             MatvecArgs a{};
             a.n_tensors = 3;
-            a.t[0] = {w[FL_B200_T_WQ].w, d->q, nullptr, QD, w[FL_B200_T_WQ].fmt};
-            a.t[1] = {w[FL_B200_T_WK].w, d->k, nullptr, KD, w[FL_B200_T_WK].fmt};
-            a.t[2] = {w[FL_B200_T_WV].w, d->v, nullptr, KD, w[FL_B200_T_WV].fmt};
+            a.t[0] = {w[FL_B200_T_WQ].w, d->q, nullptr, QD, w[FL_B200_T_WQ].fmt, 0};
+            a.t[1] = {w[FL_B200_T_WK].w, d->k, nullptr, KD, w[FL_B200_T_WK].fmt, 0};
+            a.t[2] = {w[FL_B200_T_WV].w, d->v, nullptr, KD, w[FL_B200_T_WV].fmt, 0};
             a.x = d->xa; a.wnorm = d->attn_norm[l]; a.eps = c.eps; a.cols = E;
             a.x_mode = MV_X_RMSNORM; a.status = ctx->status; a.pdl = kPdl;
             if (mask & K_MATVEC) { if (int rc = do_matvec(a)) return rc; ++n; }
@@ -120,7 +140,7 @@ static int enqueue_step(fl_b200_decoder *d, cudaStream_t s, uint32_t *n_launch, 
         {
             RopeAppendArgs a{};
             a.q = d->q; a.k = d->k; a.v = d->v; a.kcache = d->kc[l]; a.vcache = d->vc[l]; a.pos = d->d_pos;
-            a.n_q_head = c.n_head; a.n_kv_head = c.n_kv_head; a.head_dim = D; a.kv_stride = c.max_kv;
+            a.n_q_head = d->Hq; a.n_kv_head = d->Hkv; a.head_dim = D; a.kv_stride = c.max_kv;
             a.theta_scale = powf(c.rope_base, -2.0f / (float)D); a.pdl = kPdl;
             if (mask & K_OTHER) { CK(launch_rope_append(a, s)); ++n; }
         }
@@ -128,24 +148,27 @@ static int enqueue_step(fl_b200_decoder *d, cudaStream_t s, uint32_t *n_launch, 
             AttnArgs a{};
             a.q = d->q; a.k = d->kc[l]; a.v = d->vc[l]; a.out = d->att; a.part = d->part; a.tickets = d->tickets;
             a.pos = d->d_pos; a.kv_len = 0; a.kv_stride = c.max_kv;
-            a.batch_stride = (uint64_t)c.n_kv_head * c.max_kv * D;
-            a.n_q_head = c.n_head; a.n_kv_head = c.n_kv_head; a.batch = 1; a.n_splits = d->n_splits;
+            a.batch_stride = (uint64_t)d->Hkv * c.max_kv * D;
+            a.n_q_head = d->Hq; a.n_kv_head = d->Hkv; a.batch = 1; a.n_splits = d->n_splits;
             a.scale = 1.0f / sqrtf((float)D); a.status = ctx->status; a.pdl = kPdl;
             if (d->trace && mask == K_ALL) a.trace = d->trace + 4 * (size_t)n;
             if (mask & K_ATTN) { CK(launch_attn_decode(a, s)); ++n; }
         }
-        {   // O projection + residual: xb = xa + Wo att
+        {   // O projection + residual: xb = xa + Wo att (tensor parallel: partial sums over this rank's
+            // columns, then the exchange adds the ranks' partials and the residual)
             MatvecArgs a{};
             a.n_tensors = 1;
-            a.t[0] = {w[FL_B200_T_WO].w, d->xb, d->xa, E, w[FL_B200_T_WO].fmt};
+            a.t[0] = {w[FL_B200_T_WO].w, tp ? d->partial : d->xb, tp ? nullptr : d->xa, E, w[FL_B200_T_WO].fmt,
+                      w[FL_B200_T_WO].pitch};
             a.x = d->att; a.cols = QD; a.x_mode = MV_X_PLAIN; a.status = ctx->status; a.pdl = kPdl;
             if (mask & K_MATVEC) { if (int rc = do_matvec(a)) return rc; ++n; }
+            if (tp && (mask & K_COMM)) { if (int rc = do_allreduce(d->xa, d->xb)) return rc; ++n; }
         }
         {   // RMSNorm + gate / up with the SwiGLU product in the epilogue: g <- silu(gate x) * (up x)
             MatvecArgs a{};
             a.n_tensors = 2;
-            a.t[0] = {w[FL_B200_T_GATE].w, d->g, nullptr, c.n_ff, w[FL_B200_T_GATE].fmt};
-            a.t[1] = {w[FL_B200_T_UP].w, d->u, nullptr, c.n_ff, w[FL_B200_T_UP].fmt};
+            a.t[0] = {w[FL_B200_T_GATE].w, d->g, nullptr, d->F, w[FL_B200_T_GATE].fmt, 0};
+            a.t[1] = {w[FL_B200_T_UP].w, d->u, nullptr, d->F, w[FL_B200_T_UP].fmt, 0};
             a.x = d->xb; a.wnorm = d->ffn_norm[l]; a.eps = c.eps; a.cols = E;
             a.x_mode = MV_X_RMSNORM; a.status = ctx->status; a.pdl = kPdl;
             a.swiglu = w[FL_B200_T_GATE].fmt == w[FL_B200_T_UP].fmt ? 1 : 0;
@@ -155,23 +178,32 @@ static int enqueue_step(fl_b200_decoder *d, cudaStream_t s, uint32_t *n_launch, 
         {   // down projection + residual: xa = xb + Wdown h
             MatvecArgs a{};
             a.n_tensors = 1;
-            a.t[0] = {w[FL_B200_T_DOWN].w, d->xa, d->xb, E, w[FL_B200_T_DOWN].fmt};
-            a.x = d->g; a.x2 = d->u; a.cols = c.n_ff; a.status = ctx->status; a.pdl = kPdl;
+            a.t[0] = {w[FL_B200_T_DOWN].w, tp ? d->partial : d->xa, tp ? nullptr : d->xb, E, w[FL_B200_T_DOWN].fmt,
+                      w[FL_B200_T_DOWN].pitch};
+            a.x = d->g; a.x2 = d->u; a.cols = d->F; a.status = ctx->status; a.pdl = kPdl;
             a.x_mode = d->fused_swiglu ? MV_X_PLAIN : MV_X_SILU_MUL;
             if (mask & K_MATVEC) { if (int rc = do_matvec(a)) return rc; ++n; }
+            if (tp && (mask & K_COMM)) { if (int rc = do_allreduce(d->xb, d->xa)) return rc; ++n; }
         }
     }
     {   // output norm + head
         MatvecArgs a{};
         a.n_tensors = 1;
-        a.t[0] = {d->output.w, d->logits, nullptr, c.n_vocab, d->output.fmt};
+        a.t[0] = {d->output.w, d->logits, nullptr, d->V, d->output.fmt, 0};
         a.x = d->xa; a.wnorm = d->out_norm; a.eps = c.eps; a.cols = E;
         a.x_mode = MV_X_RMSNORM; a.status = ctx->status; a.pdl = kPdl; a.xn_out = d->xn_final;
         if (mask & K_MATVEC) { if (int rc = do_matvec(a)) return rc; ++n; }
     }
     if (mask & K_OTHER) {
-        CK(launch_argmax(d->logits, c.n_vocab, d->d_next, d->d_margin, ctx->argmax_scratch, ctx->argmax_ticket,
-                         ctx->sms, s, kPdl != 0)); ++n;
+        CK(launch_argmax(d->logits, d->V, d->d_next, d->d_margin, ctx->argmax_scratch, ctx->argmax_ticket,
+                         ctx->sms, s, kPdl != 0, d->top3)); ++n;
+    }
+    if (tp && (mask & K_COMM)) {   // merge the ranks' (best, index, runner-up): the same token on every rank
+        TopExchangeArgs x{};
+        for (uint32_t p = 0; p < d->tp_size; ++p) x.peers[p] = d->peers[p];
+        x.top3 = d->top3; x.index_base = d->tp_rank * d->V; x.out_idx = d->d_next; x.out_margin = d->d_margin;
+        x.rank = d->tp_rank; x.world = d->tp_size; x.st = cst; x.status = ctx->status;
+        CK(launch_argmax_exchange(x, s, kPdl != 0)); ++n;
     }
     if (mask == K_ALL) {   // state only advances in the real step
         CK(launch_kernel(advance_kernel, dim3(1), dim3(32), 0, s, kPdl != 0, d->d_token, d->d_next, d->d_pos, d->d_hist,
@@ -184,8 +216,23 @@ static int enqueue_step(fl_b200_decoder *d, cudaStream_t s, uint32_t *n_launch, 
 extern "C" {
 
 int fl_b200_decoder_create(fl_b200_ctx *ctx, const fl_b200_llama_cfg *cfg, fl_b200_decoder **out) {
+    return fl_b200_decoder_create_tp(ctx, cfg, 0, 1, out);
+}
+
+int fl_b200_decoder_create_tp(fl_b200_ctx *ctx, const fl_b200_llama_cfg *cfg, uint32_t rank, uint32_t world,
+                              fl_b200_decoder **out) {
     if (!ctx || !cfg || !out) return set_err(FL_B200_ERR_ARG, "decoder_create: null pointer");
     const fl_b200_llama_cfg &c = *cfg;
+    if (world == 0 || world > kCommMaxRanks || rank >= world)
+        return set_err(FL_B200_ERR_ARG, "decoder_create: rank %u of %u (at most %u ranks)", rank, world, kCommMaxRanks);
+    if (world > 1) {
+        if (c.n_kv_head % world || c.n_ff % (256 * world) || c.n_vocab % world)
+            return set_err(FL_B200_ERR_ARG, "decoder_create: %u ranks do not divide n_kv_head %u, n_ff %u / 256 and n_vocab %u",
+                           world, c.n_kv_head, c.n_ff, c.n_vocab);
+        if (c.n_embd > kCommMaxVec || c.n_embd % (4 * kCommChunks) || (c.n_ff / world) < 512 ||
+            (c.n_head / world) * c.head_dim < 512)
+            return set_err(FL_B200_ERR_ARG, "decoder_create: shape too small or too large for %u ranks", world);
+    }
     if (c.head_dim != 128) return set_err(FL_B200_ERR_ARG, "decoder_create: head_dim %u (only 128 is built)", c.head_dim);
     if (c.n_kv_head == 0 || c.n_head != 4 * c.n_kv_head)
         return set_err(FL_B200_ERR_ARG, "decoder_create: %u heads over %u KV heads (only groups of 4 are built)", c.n_head, c.n_kv_head);
@@ -196,20 +243,26 @@ int fl_b200_decoder_create(fl_b200_ctx *ctx, const fl_b200_llama_cfg *cfg, fl_b2
     fl_b200_decoder *d = new fl_b200_decoder();
     d->ctx = ctx;
     d->c = c;
+    d->tp_rank = rank;
+    d->tp_size = world;
+    d->Hq = c.n_head / world;
+    d->Hkv = c.n_kv_head / world;
+    d->F = c.n_ff / world;
+    d->V = c.n_vocab / world;
     d->lw.resize((size_t)c.n_layer * 7);
     d->attn_norm.assign(c.n_layer, nullptr);
     d->ffn_norm.assign(c.n_layer, nullptr);
     d->kc.assign(c.n_layer, nullptr);
     d->vc.assign(c.n_layer, nullptr);
     CK(cudaSetDevice(ctx->device));
-    const size_t kvb = (size_t)c.n_kv_head * c.max_kv * c.head_dim * sizeof(__half);
+    const size_t kvb = (size_t)d->Hkv * c.max_kv * c.head_dim * sizeof(__half);
     for (uint32_t l = 0; l < c.n_layer; ++l) {
         CK(cudaMalloc(&d->kc[l], kvb));
         CK(cudaMalloc(&d->vc[l], kvb));
         CK(cudaMemsetAsync(d->kc[l], 0, kvb, ctx->stream));
         CK(cudaMemsetAsync(d->vc[l], 0, kvb, ctx->stream));
     }
-    const uint32_t QD = c.n_head * c.head_dim, KD = c.n_kv_head * c.head_dim;
+    const uint32_t QD = d->Hq * c.head_dim, KD = d->Hkv * c.head_dim;
     CK(cudaMalloc(&d->d_token, 64));
     d->d_next = d->d_token + 1;
     d->d_pos = d->d_token + 2;
@@ -223,12 +276,20 @@ int fl_b200_decoder_create(fl_b200_ctx *ctx, const fl_b200_llama_cfg *cfg, fl_b2
     CK(cudaMalloc(&d->k, KD * 4));
     CK(cudaMalloc(&d->v, KD * 4));
     CK(cudaMalloc(&d->att, QD * 4));
-    CK(cudaMalloc(&d->g, c.n_ff * 4));
-    CK(cudaMalloc(&d->u, c.n_ff * 4));
-    CK(cudaMalloc(&d->logits, (size_t)c.n_vocab * 4));
+    CK(cudaMalloc(&d->g, d->F * 4));
+    CK(cudaMalloc(&d->u, d->F * 4));
+    CK(cudaMalloc(&d->logits, (size_t)d->V * 4));
+    CK(cudaMalloc(&d->top3, 16));
+    if (world > 1) {
+        CK(cudaMalloc(&d->comm, comm_buffer_bytes()));
+        CK(cudaMemsetAsync(d->comm, 0, comm_buffer_bytes(), ctx->stream));
+        CK(cudaMalloc(&d->comm_state, 16));
+        CK(cudaMemsetAsync(d->comm_state, 0, 16, ctx->stream));
+        CK(cudaMalloc(&d->partial, c.n_embd * 4));
+    }
     CK(cudaMalloc(&d->xn_final, c.n_embd * 4));
-    d->n_splits = attn_pick_splits(c.n_kv_head, 1, c.max_kv, ctx->sms);
-    CK(cudaMalloc(&d->part, attn_part_floats(c.n_head, 1, d->n_splits) * sizeof(float)));
+    d->n_splits = attn_pick_splits(d->Hkv, 1, c.max_kv, ctx->sms);
+    CK(cudaMalloc(&d->part, attn_part_floats(d->Hq, 1, d->n_splits) * sizeof(float)));
     CK(cudaMalloc(&d->tickets, 256 * sizeof(uint32_t)));
     CK(cudaMemsetAsync(d->tickets, 0, 256 * sizeof(uint32_t), ctx->stream));
     CK(cudaMallocHost(&d->h_pin, 64));
@@ -248,6 +309,7 @@ void fl_b200_decoder_destroy(fl_b200_decoder *d) {
     cudaFree(d->d_token); cudaFree(d->d_hist); cudaFree(d->xa); cudaFree(d->xb); cudaFree(d->q);
     cudaFree(d->k); cudaFree(d->v); cudaFree(d->att); cudaFree(d->g); cudaFree(d->u); cudaFree(d->logits);
     cudaFree(d->xn_final); cudaFree(d->part); cudaFree(d->tickets);
+    cudaFree(d->top3); cudaFree(d->comm); cudaFree(d->comm_state); cudaFree(d->partial);
     free_matvec_scratch(d->mv);
     cudaFree(d->trace);
     cudaFreeHost(d->h_pin);
@@ -260,7 +322,7 @@ static int check_weight(const fl_b200_decoder *d, int fmt, const void *w, uint32
     if (fmt != FL_B200_Q4_K && fmt != FL_B200_Q6_K)
         return set_err(FL_B200_ERR_ARG, "decoder: weight format %d (the decoder streams Q4_K and Q6_K)", fmt);
     if (((uintptr_t)w & 15u) != 0) return set_err(FL_B200_ERR_ARG, "decoder: weights must be 16-byte aligned");
-    if (cols % 2048) return set_err(FL_B200_ERR_ARG, "decoder: cols %u not a multiple of 2048", cols);
+    if (cols % 256 || cols < 512) return set_err(FL_B200_ERR_ARG, "decoder: cols %u not a multiple of 256 (>= 512)", cols);
     return FL_B200_OK;
 }
 
@@ -268,9 +330,11 @@ int fl_b200_decoder_set_layer_tensor(fl_b200_decoder *d, uint32_t layer, int whi
     if (!d || layer >= d->c.n_layer || which < 0 || which > FL_B200_T_DOWN)
         return set_err(FL_B200_ERR_ARG, "decoder_set_layer_tensor: bad layer / tensor id");
     if (d->finalized) return set_err(FL_B200_ERR_STATE, "decoder_set_layer_tensor: after finalize");
-    const uint32_t cols = which == FL_B200_T_DOWN ? d->c.n_ff : which == FL_B200_T_WO ? d->c.n_head * d->c.head_dim : d->c.n_embd;
+    const uint32_t cols = which == FL_B200_T_DOWN ? d->F : which == FL_B200_T_WO ? d->Hq * d->c.head_dim : d->c.n_embd;
     if (int rc = check_weight(d, fmt, w, cols)) return rc;
-    d->lw[(size_t)layer * 7 + which] = {fmt, (const uint8_t *)w};
+    // Column slices (O, down) are stored with their rows zero-padded to a multiple of 16 bytes.
+    const uint32_t pitch = (uint32_t)((row_bytes(fmt, cols) + 15u) & ~(uint64_t)15u);
+    d->lw[(size_t)layer * 7 + which] = {fmt, (const uint8_t *)w, pitch};
     return FL_B200_OK;
 }
 
@@ -287,7 +351,7 @@ int fl_b200_decoder_set_global(fl_b200_decoder *d, int which, int fmt, const voi
         return set_err(FL_B200_ERR_ARG, "decoder_set_global: bad tensor id");
     if (d->finalized) return set_err(FL_B200_ERR_STATE, "decoder_set_global: after finalize");
     if (int rc = check_weight(d, fmt, w, d->c.n_embd)) return rc;
-    (which == FL_B200_G_TOK_EMBD ? d->tok_embd : d->output) = {fmt, (const uint8_t *)w};
+    (which == FL_B200_G_TOK_EMBD ? d->tok_embd : d->output) = {fmt, (const uint8_t *)w, 0};
     return FL_B200_OK;
 }
 
@@ -304,6 +368,27 @@ int fl_b200_decoder_kv(fl_b200_decoder *d, uint32_t layer, uint16_t **k, uint16_
     return FL_B200_OK;
 }
 
+int fl_b200_decoder_comm(fl_b200_decoder *d, void **buf, size_t *bytes) {
+    if (!d || !buf || !bytes) return set_err(FL_B200_ERR_ARG, "decoder_comm: null");
+    *buf = d->comm;
+    *bytes = d->comm ? comm_buffer_bytes() : 0;
+    return FL_B200_OK;
+}
+
+int fl_b200_decoder_set_peers(fl_b200_decoder *d, void *const *bufs, uint32_t n) {
+    if (!d || !bufs) return set_err(FL_B200_ERR_ARG, "decoder_set_peers: null");
+    if (d->finalized) return set_err(FL_B200_ERR_STATE, "decoder_set_peers: after finalize");
+    if (n != d->tp_size) return set_err(FL_B200_ERR_ARG, "decoder_set_peers: %u buffers for %u ranks", n, d->tp_size);
+    for (uint32_t p = 0; p < n; ++p) {
+        if (!bufs[p]) return set_err(FL_B200_ERR_ARG, "decoder_set_peers: buffer of rank %u is null", p);
+        d->peers[p] = (uint8_t *)bufs[p];
+    }
+    if (d->tp_size > 1 && d->peers[d->tp_rank] != d->comm)
+        return set_err(FL_B200_ERR_ARG, "decoder_set_peers: entry %u must be this rank's own buffer", d->tp_rank);
+    d->peers_set = true;
+    return FL_B200_OK;
+}
+
 int fl_b200_decoder_finalize(fl_b200_decoder *d) {
     if (!d) return set_err(FL_B200_ERR_ARG, "decoder_finalize: null");
     if (d->finalized) return FL_B200_OK;
@@ -312,6 +397,7 @@ int fl_b200_decoder_finalize(fl_b200_decoder *d) {
     for (uint32_t l = 0; l < d->c.n_layer; ++l)
         if (!d->attn_norm[l] || !d->ffn_norm[l]) return set_err(FL_B200_ERR_STATE, "decoder_finalize: norms of layer %u not set", l);
     if (!d->tok_embd.w || !d->output.w || !d->out_norm) return set_err(FL_B200_ERR_STATE, "decoder_finalize: embedding / head / output norm not set");
+    if (d->tp_size > 1 && !d->peers_set) return set_err(FL_B200_ERR_STATE, "decoder_finalize: set the peers' exchange buffers first");
     cudaStream_t s = d->ctx->stream;
     CK(cudaSetDevice(d->ctx->device));
     CK(cudaStreamSynchronize(s));
@@ -397,7 +483,7 @@ int fl_b200_decoder_run(fl_b200_decoder *d, int32_t first_token, uint32_t n, int
 
 int fl_b200_decoder_logits(fl_b200_decoder *d, float *out) {
     if (!d || !out) return set_err(FL_B200_ERR_ARG, "decoder_logits: null");
-    return fl_b200_download(d->ctx, out, d->logits, (size_t)d->c.n_vocab * 4);
+    return fl_b200_download(d->ctx, out, d->logits, (size_t)d->V * 4);   // this rank's slice of the vocabulary
 }
 
 int fl_b200_decoder_margin(fl_b200_decoder *d, float *out) {
@@ -408,7 +494,7 @@ int fl_b200_decoder_margin(fl_b200_decoder *d, float *out) {
 int fl_b200_decoder_tap(fl_b200_decoder *d, int which, float *out) {
     if (!d || !out) return set_err(FL_B200_ERR_ARG, "decoder_tap: null");
     const fl_b200_llama_cfg &c = d->c;
-    const uint32_t QD = c.n_head * c.head_dim, KD = c.n_kv_head * c.head_dim;
+    const uint32_t QD = d->Hq * c.head_dim, KD = d->Hkv * c.head_dim;
     const float *src = nullptr;
     size_t n = 0;
     switch (which) {
@@ -418,8 +504,8 @@ int fl_b200_decoder_tap(fl_b200_decoder *d, int which, float *out) {
     case 3: src = d->v; n = KD; break;               // last layer: v
     case 4: src = d->att; n = QD; break;             // last layer: attention output
     case 5: src = d->xb; n = c.n_embd; break;        // last layer: residual after attention
-    case 6: src = d->g; n = c.n_ff; break;           // last layer: silu(gate) * up (gate alone if the formats of gate and up differ)
-    case 7: src = d->u; n = c.n_ff; break;           // last layer: up (only written if the formats of gate and up differ)
+    case 6: src = d->g; n = d->F; break;           // last layer: silu(gate) * up (gate alone if the formats of gate and up differ)
+    case 7: src = d->u; n = d->F; break;           // last layer: up (only written if the formats of gate and up differ)
     default: return set_err(FL_B200_ERR_ARG, "decoder_tap: unknown tap %d", which);
     }
     return fl_b200_download(d->ctx, out, src, n * 4);
@@ -438,9 +524,9 @@ int fl_b200_decoder_time_class(fl_b200_decoder *d, uint32_t kernel_class, uint32
     cudaStream_t s = d->ctx->stream;
     d->h_pin[0] = 0; d->h_pin[1] = 0; d->h_pin[2] = d->n_past; d->h_pin[3] = 0;
     CK(cudaMemcpyAsync(d->d_token, d->h_pin, 16, cudaMemcpyHostToDevice, s));
-    // Bit 3 keeps the mask different from K_ALL, so the advance kernel is left
+    // Bit 4 keeps the mask different from K_ALL, so the advance kernel is left
     // out and the position stays put over the replays.
-    const uint32_t m = kernel_class | 8u;
+    const uint32_t m = kernel_class | 16u;
     cudaGraph_t g = nullptr;
     cudaGraphExec_t ge = nullptr;
     CK(cudaStreamSynchronize(s));
@@ -491,17 +577,18 @@ int fl_b200_decoder_launches_per_step(fl_b200_decoder *d, uint32_t *n) {
 int fl_b200_decoder_bytes_per_step(fl_b200_decoder *d, int32_t pos, uint64_t *wb, uint64_t *kvb) {
     if (!d || !wb || !kvb) return set_err(FL_B200_ERR_ARG, "decoder_bytes_per_step: null");
     const fl_b200_llama_cfg &c = d->c;
-    const uint32_t E = c.n_embd, QD = c.n_head * c.head_dim, KD = c.n_kv_head * c.head_dim;
+    // this rank's share (the whole model on one GPU)
+    const uint32_t E = c.n_embd, QD = d->Hq * c.head_dim, KD = d->Hkv * c.head_dim;
     uint64_t w = 0;
     for (uint32_t l = 0; l < c.n_layer; ++l) {
         const Tensor *t = &d->lw[(size_t)l * 7];
         w += (uint64_t)QD * row_bytes(t[FL_B200_T_WQ].fmt, E) + (uint64_t)KD * row_bytes(t[FL_B200_T_WK].fmt, E) +
              (uint64_t)KD * row_bytes(t[FL_B200_T_WV].fmt, E) + (uint64_t)E * row_bytes(t[FL_B200_T_WO].fmt, QD) +
-             (uint64_t)c.n_ff * row_bytes(t[FL_B200_T_GATE].fmt, E) + (uint64_t)c.n_ff * row_bytes(t[FL_B200_T_UP].fmt, E) +
-             (uint64_t)E * row_bytes(t[FL_B200_T_DOWN].fmt, c.n_ff);
+             (uint64_t)d->F * row_bytes(t[FL_B200_T_GATE].fmt, E) + (uint64_t)d->F * row_bytes(t[FL_B200_T_UP].fmt, E) +
+             (uint64_t)E * row_bytes(t[FL_B200_T_DOWN].fmt, d->F);
         w += 2ull * E * 4;   // the two norm vectors
     }
-    w += (uint64_t)c.n_vocab * row_bytes(d->output.fmt, E) + (uint64_t)E * 4;
+    w += (uint64_t)d->V * row_bytes(d->output.fmt, E) + (uint64_t)E * 4;
     *wb = w;
     *kvb = (uint64_t)c.n_layer * 2ull * (uint64_t)(pos + 1) * KD * 2ull;
     return FL_B200_OK;

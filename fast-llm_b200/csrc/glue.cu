@@ -113,7 +113,7 @@ __device__ __forceinline__ Top top_warp(Top t) {
 }
 
 __global__ void __launch_bounds__(256) argmax_kernel(const float *__restrict__ lg, uint32_t n, int32_t *out_idx,
-                                                     float *out_margin, float *scratch, uint32_t *ticket) {
+                                                     float *out_margin, float *scratch, uint32_t *ticket, float *top3) {
     griddep_launch_dependents();
     griddep_wait();
     __shared__ Top wtop[8];
@@ -151,6 +151,7 @@ __global__ void __launch_bounds__(256) argmax_kernel(const float *__restrict__ l
         if (threadIdx.x == 0) {
             *out_idx = (int32_t)r.i;
             *out_margin = r.b - r.s;
+            if (top3) { top3[0] = r.b; top3[1] = __uint_as_float(r.i); top3[2] = r.s; }   // for the cross-rank merge
             *ticket = 0;
         }
     }
@@ -182,12 +183,12 @@ cudaError_t launch_rope_append(const RopeAppendArgs &a, cudaStream_t stream) {
 }
 
 cudaError_t launch_argmax(const float *logits, uint32_t n, int32_t *out_idx, float *out_margin,
-                          float *scratch, uint32_t *ticket, int sms, cudaStream_t stream, bool pdl) {
+                          float *scratch, uint32_t *ticket, int sms, cudaStream_t stream, bool pdl, float *top3) {
     uint32_t grid = (n + 255) / 256;
     if (grid > (uint32_t)sms) grid = (uint32_t)sms;
     if (grid == 0) return cudaErrorInvalidValue;
     return launch_kernel(argmax_kernel, dim3(grid), dim3(256), 0, stream, pdl, logits, n, out_idx, out_margin, scratch,
-                         ticket);
+                         ticket, top3);
 }
 
 } // namespace flb

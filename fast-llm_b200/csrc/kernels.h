@@ -19,6 +19,8 @@ struct MatvecTensor {
     const float *resid;   // optional: y[r] = resid[r] + dot   (nullptr: none)
     uint32_t rows;
     int fmt;
+    uint32_t pitch;       // bytes between rows; 0 = packed (row_bytes(fmt, cols)). A column slice of a Q6_K
+                          // tensor is stored with its rows zero-padded to a multiple of 16 bytes.
 };
 
 enum : int {
@@ -91,6 +93,41 @@ cudaError_t attn_init(void);
 uint32_t attn_pick_splits(uint32_t n_kv_head, uint32_t batch, uint32_t kv_len, int sms);
 size_t attn_part_floats(uint32_t n_q_head, uint32_t batch, uint32_t n_splits);
 
+// ---- comm.cu: exchange steps of the tensor-parallel step ----------------------
+constexpr uint32_t kCommMaxRanks = 8;
+constexpr uint32_t kCommMaxVec = 8192;     // floats per partial vector (hidden size)
+constexpr uint32_t kCommChunks = 8;        // CTAs (and flags) per all-reduce
+constexpr size_t kCommFlagsOff = (size_t)2 * kCommMaxRanks * kCommMaxVec * 4;
+constexpr size_t kCommTopOff = kCommFlagsOff + (size_t)2 * kCommMaxRanks * kCommChunks * 4;
+constexpr size_t kCommTFlagOff = kCommTopOff + (size_t)2 * kCommMaxRanks * 16;
+constexpr size_t kCommBytes = kCommTFlagOff + (size_t)2 * kCommMaxRanks * 4;
+struct CommState {
+    uint32_t *epoch;   // device scalar: epoch of the last finished exchange on this rank
+    uint32_t *done;    // device scalar: CTA arrival counter (zero between launches)
+};
+struct AllReduceArgs {
+    uint8_t *peers[kCommMaxRanks];   // every rank's communication buffer as mapped here; peers[rank] is local
+    const float *in;                 // this rank's partial vector
+    const float *resid;              // optional, added once (local)
+    float *out;
+    uint32_t n, rank, world;
+    CommState st;
+    uint32_t *status;
+};
+struct TopExchangeArgs {
+    uint8_t *peers[kCommMaxRanks];
+    const float *top3;               // {best, index bits, runner-up} of this rank's slice
+    uint32_t index_base;             // first global index of the slice
+    int32_t *out_idx;
+    float *out_margin;
+    uint32_t rank, world;
+    CommState st;
+    uint32_t *status;
+};
+size_t comm_buffer_bytes(void);
+cudaError_t launch_allreduce_resid(const AllReduceArgs &a, cudaStream_t stream, bool pdl);
+cudaError_t launch_argmax_exchange(const TopExchangeArgs &a, cudaStream_t stream, bool pdl);
+
 // ---- glue.cu ------------------------------------------------------------
 cudaError_t launch_rmsnorm(const float *x, const float *wnorm, float *y, float eps, uint32_t n,
                            cudaStream_t stream);
@@ -112,7 +149,8 @@ cudaError_t launch_rope_append(const RopeAppendArgs &a, cudaStream_t stream);
 // Greedy argmax with the reference's tie rule (lowest index) and the
 // top1 - top2 margin. out_idx: int32, out_margin: float; scratch: 2*blocks*2 floats.
 cudaError_t launch_argmax(const float *logits, uint32_t n, int32_t *out_idx, float *out_margin,
-                          float *scratch, uint32_t *ticket, int sms, cudaStream_t stream, bool pdl = false);
+                          float *scratch, uint32_t *ticket, int sms, cudaStream_t stream, bool pdl = false,
+                          float *top3 = nullptr);   // top3: optional {best, index bits, runner-up}
 // Embedding row gather + dequant: out[0..cols) = dequant(table row *token).
 cudaError_t launch_embed(int fmt, const void *table, const int32_t *token, uint32_t cols, float *out,
                          cudaStream_t stream, bool pdl = false);

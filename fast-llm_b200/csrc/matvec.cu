@@ -101,7 +101,12 @@ struct Smem {
     uint8_t *ring;   // [kWarps][stages][stage bytes]
 };
 
+// Columns rounded up to whole 2048-column segments: the shared-memory layouts are
+// per segment, and the blocks past the end of a shorter row hold zeros.
+__host__ __device__ inline uint32_t padded_cols(uint32_t cols) { return (cols + 2047u) & ~2047u; }
+
 __host__ __device__ inline size_t smem_fixed_bytes(uint32_t cols, bool q4, bool q6) {
+    cols = padded_cols(cols);
     size_t n = (size_t)cols / 256 * 4;                               // xs
     if (q4) n += (size_t)cols * 3 + (size_t)cols / 32 * 4;
     if (q6) n += (size_t)cols * 3 + (size_t)cols / 16 * 4;
@@ -111,6 +116,7 @@ __host__ __device__ inline size_t smem_fixed_bytes(uint32_t cols, bool q4, bool 
 __device__ __forceinline__ Smem carve(uint8_t *base, uint32_t cols, bool q4, bool q6, int stages) {
     Smem s;
     uint8_t *p = base;
+    cols = padded_cols(cols);
     s.q4 = s.q6 = nullptr;
     s.s4 = s.s6 = nullptr;
     if (q4) { s.q4 = (int8_t *)p; p += (size_t)cols * 3; }     // cols*3 is a multiple of 16
@@ -316,7 +322,7 @@ matvec_stream_kernel(const MatvecArgs a, const __grid_constant__ TensorMaps maps
     extern __shared__ __align__(128) uint8_t smem_raw[];
     const Smem sm = carve(smem_raw, a.cols, use_q4 != 0, use_q6 != 0, stages);
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
-    const uint32_t nseg = a.cols / 2048u;
+    const uint32_t nseg = (a.cols + 2047u) / 2048u;   // the last segment may be partial: the TMA unit fills the rest with zeros
     const uint32_t stage_bytes = use_q6 ? kStage6 : kStage4;
     __shared__ float red[kWarps];
 
@@ -364,8 +370,13 @@ matvec_stream_kernel(const MatvecArgs a, const __grid_constant__ TensorMaps maps
     // are issued first, so the prologue costs one memory round trip; the norm
     // weights are constants and are fetched before the dependency wait.
     constexpr int kMaxBlk = 6;   // blocks per warp: cols <= 6 * 256 * kWarps = 18432
-    const uint32_t nblk = a.cols / 256;
+    const uint32_t nblk = a.cols / 256, nblk_pad = nseg * 8;   // blocks nblk .. nblk_pad-1 are zeros
     float4 ra[kMaxBlk][2], rb2[kMaxBlk][2];
+#pragma unroll
+    for (int b = 0; b < kMaxBlk; ++b) {
+        ra[b][0] = ra[b][1] = make_float4(0.f, 0.f, 0.f, 0.f);
+        rb2[b][0] = rb2[b][1] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
     if (a.x_mode == MV_X_RMSNORM) {
 #pragma unroll
         for (int b = 0; b < kMaxBlk; ++b) {
@@ -410,7 +421,7 @@ matvec_stream_kernel(const MatvecArgs a, const __grid_constant__ TensorMaps maps
 #pragma unroll
     for (int b = 0; b < kMaxBlk; ++b) {
         const uint32_t blk = warp + b * kWarps;
-        if (blk >= nblk) break;
+        if (blk >= nblk_pad) break;
         const uint32_t c0 = blk * 256 + lane * 8;
         float v[8] = {ra[b][0].x, ra[b][0].y, ra[b][0].z, ra[b][0].w, ra[b][1].x, ra[b][1].y, ra[b][1].z, ra[b][1].w};
         const float w2[8] = {rb2[b][0].x, rb2[b][0].y, rb2[b][0].z, rb2[b][0].w,
@@ -419,7 +430,7 @@ matvec_stream_kernel(const MatvecArgs a, const __grid_constant__ TensorMaps maps
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
             if (a.x_mode == MV_X_RMSNORM) v[i] = v[i] * w2[i];
-            else if (a.x_mode == MV_X_SILU_MUL) v[i] = (v[i] / (1.0f + expf(-v[i]))) * w2[i];
+            else if (a.x_mode == MV_X_SILU_MUL) v[i] = (v[i] / (1.0f + expf(-v[i]))) * w2[i];   // 0 for padding: silu(0) = 0
             amax = fmaxf(amax, fabsf(v[i]));
         }
         amax = warp_max(amax);
@@ -602,7 +613,7 @@ __global__ void __launch_bounds__(256) matvec_generic_kernel(const MatvecArgs a,
         }
         const MatvecTensor &t = a.t[ti];
         const uint32_t r = vr - base;
-        const uint8_t *row = t.w + (uint64_t)r * row_bytes(t.fmt, a.cols);
+        const uint8_t *row = t.w + (uint64_t)r * (t.pitch ? t.pitch : row_bytes(t.fmt, a.cols));
         float acc = 0.f;
         for (uint32_t e = lane; e < a.cols; e += 32) acc += dequant_elem(t.fmt, row, e) * a.x[e];
         acc = warp_sum(acc);
@@ -618,7 +629,7 @@ __global__ void __launch_bounds__(256) matvec_generic_kernel(const MatvecArgs a,
 } // namespace
 
 bool matvec_is_streaming(int fmt, uint32_t cols) {
-    return (fmt == FMT_Q4_K || fmt == FMT_Q6_K) && cols >= 2048 && cols % 2048 == 0;
+    return (fmt == FMT_Q4_K || fmt == FMT_Q6_K) && cols >= 512 && cols % 256 == 0;
 }
 
 size_t matvec_smem_bytes(uint32_t cols, bool q4, bool q6, int *stages_out) {
@@ -651,7 +662,7 @@ cudaError_t matvec_init(void) {
 // The packed tensor as [rows][row_bytes / 8] 8-byte elements, box = 4 rows x one segment.
 static cudaError_t encode_map(CUtensorMap *m, const MatvecTensor &t, uint32_t cols, uint32_t box_rows) {
     if (!g_encode) return cudaErrorNotSupported;
-    const uint64_t rb = row_bytes(t.fmt, cols);
+    const uint64_t rb = t.pitch ? t.pitch : row_bytes(t.fmt, cols);   // a multiple of 16 (checked by the caller)
     const uint32_t seg = t.fmt == FMT_Q4_K ? kSeg4 : kSeg6;
     const cuuint64_t gdim[2] = {rb / 8, t.rows};
     const cuuint64_t gstride[1] = {rb};
@@ -677,7 +688,9 @@ cudaError_t launch_matvec(const MatvecArgs &a, int sms, cudaStream_t stream) {
         const MatvecTensor &t = a.t[i];
         if (t.rows == 0 || a.cols % blk_elems(t.fmt) != 0) return cudaErrorInvalidValue;
         if (t.fmt < FMT_F32 || t.fmt > FMT_Q6_K) return cudaErrorInvalidValue;
-        streaming = streaming && matvec_is_streaming(t.fmt, a.cols) && (((uintptr_t)t.w) & 15u) == 0;
+        const uint64_t pitch = t.pitch ? t.pitch : row_bytes(t.fmt, a.cols);
+        if (pitch < row_bytes(t.fmt, a.cols)) return cudaErrorInvalidValue;
+        streaming = streaming && matvec_is_streaming(t.fmt, a.cols) && (((uintptr_t)t.w) & 15u) == 0 && (pitch & 15u) == 0;
         streaming = streaming && a.cols <= 6u * 256u * kWarps && (((uintptr_t)a.x) & 15u) == 0 &&
                     (((uintptr_t)a.x2) & 15u) == 0 && (((uintptr_t)a.wnorm) & 15u) == 0;
         q4 = q4 || t.fmt == FMT_Q4_K;

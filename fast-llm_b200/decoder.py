@@ -10,23 +10,36 @@ from . import capi
 
 
 class Decoder:
-    def __init__(self, ctx, cfg):
+    def __init__(self, ctx, cfg, tp=None):
         """cfg: dict with n_layer, n_embd, n_head, n_kv_head, head_dim, n_ff,
-        n_vocab, max_kv, rope_base, eps."""
+        n_vocab, max_kv, rope_base, eps (the whole model). tp = (rank, world)
+        makes this the decoder of one rank of a tensor-parallel group: tensors are
+        then handed over sliced (fast_llm_b200.tp) and fast_llm_b200.tp.connect
+        must run before finalize."""
         self.ctx = ctx
         self.lib = ctx.lib
         self.cfg = dict(cfg)
+        self.rank, self.world = tp if tp else (0, 1)
         c = capi.LlamaCfg(**{k: cfg[k] for k in ("n_layer", "n_embd", "n_head", "n_kv_head", "head_dim",
                                                   "n_ff", "n_vocab", "max_kv", "rope_base", "eps")})
         self._h = C.c_void_p()
-        capi._ck(self.lib.fl_b200_decoder_create(ctx._h, C.byref(c), C.byref(self._h)))
+        capi._ck(self.lib.fl_b200_decoder_create_tp(ctx._h, C.byref(c), C.c_uint32(self.rank), C.c_uint32(self.world),
+                                                    C.byref(self._h)))
+        # this rank's share of the sizes that are split
+        self.loc = dict(self.cfg)
+        for k in ("n_head", "n_kv_head", "n_ff", "n_vocab"):
+            self.loc[k] = cfg[k] // self.world
         self._keep = []   # device tensors the decoder points into
+        self._peer_maps = []
 
     def close(self):
         if self._h:
             self.lib.fl_b200_decoder_destroy(self._h)
             self._h = C.c_void_p()
             self._keep = []
+            for p in self._peer_maps:
+                self.lib.fl_b200_ipc_close(self.ctx._h, C.c_void_p(p))
+            self._peer_maps = []
 
     def __del__(self):
         try:
@@ -82,7 +95,7 @@ class Decoder:
         capi._ck(self.lib.fl_b200_decoder_set_n_past(self._h, C.c_int32(int(pos))))
 
     def logits(self):
-        out = np.empty(self.cfg["n_vocab"], dtype=np.float32)
+        out = np.empty(self.loc["n_vocab"], dtype=np.float32)   # this rank's slice of the vocabulary
         capi._ck(self.lib.fl_b200_decoder_logits(self._h, C.c_void_p(out.ctypes.data)))
         return out
 
@@ -92,7 +105,7 @@ class Decoder:
         return v.value
 
     def tap(self, which):
-        c = self.cfg
+        c = self.loc
         n = {0: c["n_embd"], 1: c["n_embd"], 2: c["n_head"] * c["head_dim"], 3: c["n_kv_head"] * c["head_dim"],
              4: c["n_head"] * c["head_dim"], 5: c["n_embd"], 6: c["n_ff"], 7: c["n_ff"]}[which]
         out = np.empty(n, dtype=np.float32)
@@ -101,7 +114,7 @@ class Decoder:
 
     def time_class(self, kernel_class, reps):
         """(ms per step, launches per step) of one kernel class replayed alone:
-        1 matvec, 2 attention, 4 small operators, 7 all."""
+        1 matvec, 2 attention, 4 small operators, 8 exchange steps (tensor parallel), 15 all."""
         ms, n = C.c_float(), C.c_uint32()
         capi._ck(self.lib.fl_b200_decoder_time_class(self._h, C.c_uint32(kernel_class), C.c_uint32(reps),
                                                      C.byref(ms), C.byref(n)))

@@ -175,19 +175,24 @@ def device_quant_tensor(fmt, rows, cols, gen):
 
 def device_llama(dec, cfg, seed, n_prefill, kv_std=0.1, recipe=Q4_K_M):
     """Fills a fast_llm_b200.decoder.Decoder with a synthetic model generated on
-    its device and prefills n_prefill KV positions ~ N(0, kv_std). Returns the
-    list of tensors kept alive."""
+    its device and prefills n_prefill KV positions ~ N(0, kv_std). A
+    tensor-parallel decoder gets tensors of its share's shapes (drawn directly,
+    not sliced from a whole model: the values are synthetic either way). Returns
+    the list of tensors kept alive."""
     import ctypes as C
     import torch
+    from . import tp
     dev = torch.device("cuda", dec.ctx.device)
     gen = torch.Generator(device=dev)
     gen.manual_seed(seed)
     keep = []
-    shapes = layer_shapes(cfg)
+    shapes = layer_shapes(dec.loc)
     for l in range(cfg["n_layer"]):
         for i, name in enumerate(LAYER_TENSORS):
             rows, cols = shapes[name]
             w = device_quant_tensor(recipe[name], rows, cols, gen)
+            if name in tp.COL_SPLIT and w.shape[1] % 16:
+                w = torch.nn.functional.pad(w, (0, 16 - w.shape[1] % 16)).contiguous()
             dec.set_layer_tensor(l, i, recipe[name], w)
         an = torch.rand(cfg["n_embd"], device=dev, generator=gen) * 0.2 + 0.9
         fn = torch.rand(cfg["n_embd"], device=dev, generator=gen) * 0.2 + 0.9
@@ -195,16 +200,17 @@ def device_llama(dec, cfg, seed, n_prefill, kv_std=0.1, recipe=Q4_K_M):
         if n_prefill:
             kp, vp = dec.kv_ptrs(l)
             for ptr in (kp, vp):
-                t = (torch.randn((cfg["n_kv_head"], n_prefill, cfg["head_dim"]), device=dev, generator=gen)
-                     * kv_std).half()
-                full = torch.zeros((cfg["n_kv_head"], cfg["max_kv"], cfg["head_dim"]), dtype=torch.float16, device=dev)
+                nkv = dec.loc["n_kv_head"]
+                t = (torch.randn((nkv, n_prefill, cfg["head_dim"]), device=dev, generator=gen) * kv_std).half()
+                full = torch.zeros((nkv, cfg["max_kv"], cfg["head_dim"]), dtype=torch.float16, device=dev)
                 full[:, :n_prefill] = t
                 torch.cuda.synchronize(dev)
                 # copy into the decoder's cache (the source may be a device pointer)
                 capi._ck(dec.lib.fl_b200_upload(dec.ctx._h, C.c_void_p(ptr), C.c_void_p(full.data_ptr()),
                                                 C.c_size_t(full.numel() * 2)))
     for which, name in ((capi.G_TOK_EMBD, "tok_embd"), (capi.G_OUTPUT, "output")):
-        w = device_quant_tensor(recipe[name], cfg["n_vocab"], cfg["n_embd"], gen)
+        rows = cfg["n_vocab"] if name == "tok_embd" else dec.loc["n_vocab"]   # the embedding table is whole on every rank
+        w = device_quant_tensor(recipe[name], rows, cfg["n_embd"], gen)
         dec.set_global(which, recipe[name], w)
     on = torch.rand(cfg["n_embd"], device=dev, generator=gen) * 0.2 + 0.9
     dec.set_out_norm(on)

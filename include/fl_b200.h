@@ -72,6 +72,10 @@ int fl_b200_free(fl_b200_ctx *ctx, void *dev);
 /* src may be a host pointer or a device pointer (unified addressing). */
 int fl_b200_upload(fl_b200_ctx *ctx, void *dst_dev, const void *src_host, size_t bytes);
 int fl_b200_download(fl_b200_ctx *ctx, void *dst_host, const void *src_dev, size_t bytes);
+/* CUDA IPC handles (64 bytes) for mapping another rank's buffer into this process. */
+int fl_b200_ipc_export(fl_b200_ctx *ctx, const void *dev_ptr, uint8_t handle_out[64]);
+int fl_b200_ipc_open(fl_b200_ctx *ctx, const uint8_t handle[64], void **dev_ptr_out);
+int fl_b200_ipc_close(fl_b200_ctx *ctx, void *dev_ptr);
 int fl_b200_memset(fl_b200_ctx *ctx, void *dst_dev, int value, size_t bytes);
 
 /* CUDA-event stopwatch on the context's stream. */
@@ -95,6 +99,11 @@ int fl_b200_matvec(fl_b200_ctx *ctx, int fmt, const void *w_dev, uint32_t rows, 
 int fl_b200_matvec_assign(fl_b200_ctx *ctx, int fmt, const void *w_dev, uint32_t rows, uint32_t cols,
                           const float *x_dev, float *y_dev);
 /* End-to-end form: x and y in host memory (y_host receives W x). */
+/* y = W x (assigns) for a tensor whose rows are `pitch` bytes apart (pitch >=
+ * the packed row size): the layout of a column slice of a k-quant tensor, whose
+ * rows are zero-padded to a multiple of 16 bytes (tensor-parallel O and down). */
+int fl_b200_matvec_pitched(fl_b200_ctx *ctx, int fmt, const void *w_dev, uint32_t rows, uint32_t cols,
+                           uint32_t pitch, const float *x_dev, float *y_dev);
 int fl_b200_matvec_host(fl_b200_ctx *ctx, int fmt, const void *w_dev, uint32_t rows, uint32_t cols,
                         const float *x_host, float *y_host);
 
@@ -211,6 +220,28 @@ enum { FL_B200_T_WQ = 0, FL_B200_T_WK, FL_B200_T_WV, FL_B200_T_WO, FL_B200_T_GAT
 enum { FL_B200_G_TOK_EMBD = 0, FL_B200_G_OUTPUT = 1 };
 
 int fl_b200_decoder_create(fl_b200_ctx *ctx, const fl_b200_llama_cfg *cfg, fl_b200_decoder **out);
+/* Tensor-parallel decoder: rank `rank` of `world` (<= 8) ranks, one process and
+ * one GPU per rank (the reference has no multi-GPU path). cfg describes the
+ * WHOLE model; this rank holds n_kv_head / world KV heads with their query heads
+ * (rows of wq, wk, wv; its slice of the KV cache), the matching columns of wo,
+ * n_ff / world rows of gate and up and the matching columns of down, and
+ * n_vocab / world rows of the head; the hidden state is replicated. Tensors are
+ * handed over already sliced: row slices are plain row ranges; a column slice
+ * keeps every row's blocks [first, first + n) and stores each row zero-padded to
+ * a multiple of 16 bytes. The embedding table is whole on every rank. After O
+ * and after down the ranks' partial vectors are summed (in rank order, so all
+ * ranks hold identical bits) by a one-shot exchange through peer memory, and the
+ * per-rank argmax records are merged likewise: every rank returns the same
+ * token. fl_b200_decoder_logits returns this rank's slice. Set-up: create on
+ * every rank, export fl_b200_decoder_comm's buffer (fl_b200_ipc_export), open
+ * the other ranks' handles (fl_b200_ipc_open), pass all `world` pointers in
+ * rank order to fl_b200_decoder_set_peers (own buffer at index `rank`), then
+ * finalize. All ranks must issue the same sequence of step / run / time_class
+ * calls. */
+int fl_b200_decoder_create_tp(fl_b200_ctx *ctx, const fl_b200_llama_cfg *cfg, uint32_t rank, uint32_t world,
+                              fl_b200_decoder **out);
+int fl_b200_decoder_comm(fl_b200_decoder *dec, void **buf_dev_out, size_t *bytes_out);
+int fl_b200_decoder_set_peers(fl_b200_decoder *dec, void *const *bufs_dev, uint32_t n);
 void fl_b200_decoder_destroy(fl_b200_decoder *dec);
 /* Weights stay where the caller put them (device memory, GGUF block layout,
  * 16-byte aligned); the decoder keeps the pointers. */

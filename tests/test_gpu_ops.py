@@ -100,7 +100,9 @@ def test_dequant_extreme_scales(ctx, checker):
     (capi.Q6_K, 1024, 4096),       # wv
     (capi.Q6_K, 512, 14336),       # rows of ffn_down
     (capi.Q4_K, 1026, 2048), (capi.Q6_K, 1029, 2048), (capi.Q4_K, 1, 2048), (capi.Q6_K, 3, 6144),   # ragged row counts
-    (capi.Q4_K, 37, 768), (capi.Q6_K, 37, 1280), (capi.Q8_0, 100, 1408), (capi.Q5_0, 33, 1408), (capi.F32, 50, 200),
+    (capi.Q4_K, 37, 768), (capi.Q6_K, 37, 1280),
+    (capi.Q4_K, 64, 512), (capi.Q4_K, 101, 1792), (capi.Q4_K, 256, 7168), (capi.Q6_K, 64, 6144 + 2048),   # partial last segment
+ (capi.Q8_0, 100, 1408), (capi.Q5_0, 33, 1408), (capi.F32, 50, 200),
 ])
 def test_matvec_vs_oracle(ctx, checker, fmt, rows, cols):
     rng = np.random.default_rng(rows + 31 * cols + fmt)
@@ -111,6 +113,49 @@ def test_matvec_vs_oracle(ctx, checker, fmt, rows, cols):
     assert rel_err(got, want) <= MATVEC_RTOL
     # run-to-run reproducible (fixed summation order)
     assert np.array_equal(bits(got), bits(gpu_matvec(ctx, fmt, w, rows, cols, x)))
+
+
+@pytest.mark.parametrize("fmt,rows,cols,c0,n", [
+    (capi.Q6_K, 4096, 14336, 7168, 7168),    # down, rank 1 of 2
+    (capi.Q6_K, 512, 14336, 3584 * 3, 3584), # down, rank 3 of 4
+    (capi.Q6_K, 300, 14336, 1792 * 5, 1792), # down, rank 5 of 8 (7 blocks: 1470-byte rows padded to 1472)
+    (capi.Q4_K, 4096, 4096, 512 * 7, 512),   # O, rank 7 of 8
+    (capi.Q4_K, 130, 4096, 1024, 1024),      # O, rank 1 of 4
+])
+def test_matvec_column_slice_with_pitch(ctx, checker, fmt, rows, cols, c0, n):
+    """The tensor-parallel column slices of O / down: blocks [c0, c0+n) of every row,
+    rows zero-padded to a multiple of 16 bytes, against the oracle on the packed slice."""
+    from fast_llm_b200 import tp
+    rng = np.random.default_rng(rows + cols + c0)
+    w = synth.quant_tensor(fmt, rng, rows, cols)
+    x = rng.standard_normal(n).astype(np.float32)
+    ws = tp.slice_cols(w, fmt, c0, n)
+    pitch = tp.pitch_of(fmt, n)
+    assert ws.shape == (rows, pitch) and pitch % 16 == 0
+    packed = np.ascontiguousarray(ws[:, :capi.row_bytes(fmt, n)])
+    want = checker.matvec(fmt, packed, rows, n, x)
+    wd, xd = dev(ws), dev(x)
+    y = torch.full((rows + 8,), 7.0, dtype=torch.float32, device="cuda")
+    torch.cuda.synchronize()
+    ctx.matvec_pitched(fmt, wd, rows, n, pitch, xd, y)
+    ctx.sync()
+    assert ctx.status() == 0
+    y = y.cpu().numpy()
+    assert np.all(y[rows:] == 7.0)
+    assert rel_err(y[:rows], want) <= MATVEC_RTOL
+    # the slices of all ranks add up to the whole product (linearity across the split)
+    if c0 == 0 or rows > 1000:
+        return
+    xf = rng.standard_normal(cols).astype(np.float32)
+    full = checker.matvec(fmt, w, rows, cols, xf)
+    acc = np.zeros(rows, dtype=np.float64)
+    for r in range(cols // n):
+        wr = dev(tp.slice_cols(w, fmt, r * n, n)); xr = dev(xf[r * n:(r + 1) * n]); yr = torch.zeros(rows, device="cuda")
+        torch.cuda.synchronize()
+        ctx.matvec_pitched(fmt, wr, rows, n, pitch, xr, yr)
+        ctx.sync()
+        acc += yr.cpu().numpy()
+    assert rel_err(acc.astype(np.float32), full) <= MATVEC_RTOL
 
 
 def test_matvec_config0_vs_f64_and_golden(ctx, checker):

@@ -1,0 +1,141 @@
+"""Tensor-parallel decoder on 2 GPUs (one process per GPU) against the same
+model on one GPU: identical greedy tokens, logits within the whole-step
+tolerance. Skipped on boxes with fewer than 2 GPUs."""
+import os
+import socket
+
+import numpy as np
+import pytest
+
+torch = pytest.importorskip("torch")
+pytestmark = pytest.mark.gpu
+
+SMALL = dict(n_layer=2, n_embd=2048, n_head=16, n_kv_head=4, head_dim=128, n_ff=4096, n_vocab=1000, max_kv=96,
+             rope_base=500000.0, eps=1e-5)
+N_PREFILL, STEPS, SEED = 40, 6, 3
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _fill(dec, ctx, cfg, rank, world):
+    """The seeded synthetic model, sliced for (rank, world)."""
+    from fast_llm_b200 import capi, synth, tp
+    for l in range(cfg["n_layer"]):
+        for i, name in enumerate(synth.LAYER_TENSORS):
+            fmt = synth.Q4_K_M[name]
+            w = synth.llama_tensor(cfg, SEED, name, l)
+            if world > 1:
+                w = np.ascontiguousarray(tp.shard_tensor(name, w, fmt, cfg, rank, world))
+            dec.set_layer_tensor(l, i, fmt, torch.from_numpy(w).cuda())
+        an, fn = synth.llama_norm(cfg, SEED, "attn_norm", l), synth.llama_norm(cfg, SEED, "ffn_norm", l)
+        dec.set_layer_norms(l, torch.from_numpy(an).cuda(), torch.from_numpy(fn).cuda())
+        k, v = synth.llama_kv(cfg, SEED, l, N_PREFILL)
+        nkv = cfg["n_kv_head"] // world
+        kp, vp = dec.kv_ptrs(l)
+        for src, dst in ((k, kp), (v, vp)):
+            full = np.zeros((nkv, cfg["max_kv"], cfg["head_dim"]), dtype=np.float16)
+            full[:, :N_PREFILL] = src[rank * nkv:(rank + 1) * nkv]
+            capi._ck(ctx.lib.fl_b200_upload(ctx._h, capi.C.c_void_p(dst), capi.C.c_void_p(full.ctypes.data),
+                                            capi.C.c_size_t(full.nbytes)))
+    emb = synth.llama_tensor(cfg, SEED, "tok_embd")
+    dec.set_global(capi.G_TOK_EMBD, synth.Q4_K_M["tok_embd"], torch.from_numpy(emb).cuda())
+    head = synth.llama_tensor(cfg, SEED, "output")
+    if world > 1:
+        head = np.ascontiguousarray(tp.shard_tensor("output", head, synth.Q4_K_M["output"], cfg, rank, world))
+    dec.set_global(capi.G_OUTPUT, synth.Q4_K_M["output"], torch.from_numpy(head).cuda())
+    dec.set_out_norm(torch.from_numpy(synth.llama_norm(cfg, SEED, "out_norm")).cuda())
+    torch.cuda.synchronize()
+
+
+def _worker(rank, world, port, q):
+    try:
+        import torch.distributed as dist
+        os.environ["MASTER_ADDR"] = "127.0.0.1"
+        os.environ["MASTER_PORT"] = str(port)
+        torch.cuda.set_device(rank)
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+        from fast_llm_b200 import capi, tp
+        from fast_llm_b200.decoder import Decoder
+        ctx = capi.Context(rank)
+        dec = Decoder(ctx, SMALL, tp=(rank, world))
+        _fill(dec, ctx, SMALL, rank, world)
+        tp.connect(dec, dist)
+        dec.finalize()
+        dec.rewind_to(N_PREFILL)
+        dist.barrier()
+        res = {"tokens": [], "logits": [], "margin": []}
+        tok = 11
+        for _ in range(STEPS):
+            tok = dec.step(tok)
+            res["tokens"].append(tok)
+            sl = torch.from_numpy(dec.logits())
+            parts = [torch.zeros_like(sl) for _ in range(world)]
+            dist.all_gather(parts, sl)
+            res["logits"].append(torch.cat(parts).numpy())
+            res["margin"].append(dec.last_margin())
+        # device feedback loop: same tokens again from the same start
+        dec.rewind_to(N_PREFILL)
+        dist.barrier()
+        res["run"] = [int(t) for t in dec.run(11, STEPS)]
+        res["status"] = ctx.status()
+        dist.barrier()
+        if rank == 0:   # the same model on one GPU
+            one = Decoder(ctx, SMALL)
+            _fill(one, ctx, SMALL, 0, 1)
+            one.finalize()
+            one.rewind_to(N_PREFILL)
+            ref = {"tokens": [], "logits": [], "margin": []}
+            tok = 11
+            for _ in range(STEPS):
+                tok = one.step(tok)
+                ref["tokens"].append(tok)
+                ref["logits"].append(one.logits())
+                ref["margin"].append(one.last_margin())
+            res["ref"] = ref
+            one.close()
+        dist.barrier()
+        dec.close()
+        ctx.close()
+        dist.destroy_process_group()
+        q.put((rank, res))
+    except Exception:
+        import traceback
+        q.put((rank, "ERROR " + traceback.format_exc()))
+
+
+def test_two_rank_decoder_matches_single_gpu():
+    if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    import torch.multiprocessing as mp
+    mpc = mp.get_context("spawn")
+    q = mpc.Queue()
+    port = _free_port()
+    procs = [mpc.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = dict(q.get(timeout=600) for _ in procs)
+    for p in procs:
+        p.join(timeout=120)
+    for r in (0, 1):
+        assert not isinstance(res[r], str), res[r]
+        assert res[r]["status"] == 0
+    a, b, ref = res[0], res[1], res[0]["ref"]
+    # every rank holds the same token, margin and (gathered) logits, bit for bit
+    assert a["tokens"] == b["tokens"] and a["run"] == b["run"] and a["margin"] == b["margin"]
+    assert a["run"] == a["tokens"]
+    for la, lb in zip(a["logits"], b["logits"]):
+        assert np.array_equal(la.view(np.uint32), lb.view(np.uint32))
+    # against one GPU: only the summation order of O and down changes
+    for s in range(STEPS):
+        want, got = ref["logits"][s], a["logits"][s]
+        err = float(np.max(np.abs(got - want)) / np.sqrt(np.mean(want.astype(np.float64) ** 2)))
+        assert err < 3e-3, (s, err)
+        if a["tokens"][s] != ref["tokens"][s]:
+            assert ref["margin"][s] <= 2 * float(np.max(np.abs(got - want))), (s, a["tokens"][s], ref["tokens"][s])
+            break   # the sequences differ from here on
