@@ -158,6 +158,11 @@ def main():
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--parallelism", default="both", choices=["both", "tp", "replicas"],
+                    help="N > 1: replicas = one independent sequence per GPU (weak scaling, the headline value); "
+                         "tp = one sequence, the step split over the GPUs (KV heads, matvec rows / columns, exchange "
+                         "through peer memory; strong scaling); both = replicas as the headline and the tp "
+                         "measurement of the same run under the key \"tp\"")
     ap.add_argument("--layers", type=int, default=32,
                     help="number of layers (32 = the benchmark; fewer = a small case of the same kernels for profiler captures, not a benchmark number)")
     args = ap.parse_args()
@@ -167,7 +172,10 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     config = {"workload": "synthetic Llama-3-8B-shape Q4_K_M greedy decode, batch 1, 8192-token prefilled f16 KV",
               "n_layer": args.layers, "hidden": 4096, "heads": "32/8 x 128", "ffn": 14336, "vocab": 128256,
-              "kv_prefill": N_PREFILL, "parallelism": "replicas x%d" % world if world > 1 else "single GPU",
+              "kv_prefill": N_PREFILL,
+              "parallelism": "single GPU" if world == 1 else
+                             ("tp%d (KV heads + matvec rows/columns per GPU, 2 all-reduces per layer through peer memory)" % world
+                              if args.parallelism == "tp" else "replicas x%d (independent sequences, no data-path collective)" % world),
               "l2": "each step reads 6.0 GB of distinct weights and KV, far larger than L2; no flush needed"}
 
     if args.impl == "reference":
@@ -200,9 +208,45 @@ def main():
         config["workload"] += " (REDUCED to %d layers: profiler case, not the benchmark)" % args.layers
     if steps + warmup + 8 > cfg["max_kv"] - N_PREFILL:
         cfg["max_kv"] = N_PREFILL + steps + warmup + 8
-    dec = Decoder(ctx, cfg)
-    synth.device_llama(dec, cfg, seed=1234 + rank, n_prefill=N_PREFILL)
+    gloo = dist.new_group(backend="gloo") if world > 1 else None   # IPC handles travel as Python objects
+    modes = ["replicas"] if world == 1 else {"both": ["replicas", "tp"], "tp": ["tp"], "replicas": ["replicas"]}[args.parallelism]
+    out = None
+    for mode in modes:
+        r = measure(mode == "tp", args, ctx, cfg, config, dist, gloo, rank, local_rank, world, steps, warmup)
+        if out is None:
+            out = r
+        else:   # the tensor-parallel measurement of the same run, beside the headline
+            out["tp"] = {"value": r["value"], "unit": r["unit"], "ms_per_step": r["ms_per_step"], "scaling": "strong",
+                         "parallelism": "tp%d: one sequence; KV heads + matvec rows/columns per GPU, 2 all-reduces per "
+                                        "layer + 1 argmax exchange per step through peer memory" % world,
+                         "e2e": r["e2e"], "roofline": r["roofline"], "gpu_launches": r["gpu_launches"]}
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        r = cpu_reference_arm(1, 1)
+        out["cpu_baseline"] = {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")}
+    ctx.close()
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank == 0:
+        print(json.dumps(out))
+
+
+def measure(tp_mode, args, ctx, cfg, config, dist, gloo, rank, local_rank, world, steps, warmup):
+    """One decoder (this rank's replica, or its share of the tensor-parallel group), timed."""
+    import torch
+    from fast_llm_b200 import synth
+    from fast_llm_b200.decoder import Decoder
+    config = dict(config)
+    if world > 1:
+        config["parallelism"] = ("tp%d (one sequence; KV heads + matvec rows/columns per GPU, 2 all-reduces per layer through "
+                                 "peer memory)" % world) if tp_mode else "replicas x%d (independent sequences, no data-path collective)" % world
+    dec = Decoder(ctx, cfg, tp=(rank, world) if tp_mode else None)
+    synth.device_llama(dec, cfg, seed=1234 if tp_mode else 1234 + rank, n_prefill=N_PREFILL)
+    if tp_mode:
+        from fast_llm_b200 import tp
+        tp.connect(dec, dist, group=gloo)
     dec.finalize()
+    seqs = 1 if tp_mode else world   # sequences decoded at once
 
     def barrier():
         torch.cuda.synchronize()
@@ -250,13 +294,17 @@ def main():
     mv_ms, mv_n = dec.time_class(1, 20)
     at_ms, at_n = dec.time_class(2, 20)
     ot_ms, ot_n = dec.time_class(4, 20)
+    if tp_mode:
+        barrier()
+        cm_ms, cm_n = dec.time_class(8, 20)   # the exchange steps alone (all ranks together)
+        barrier()
     peak, peak_kind = measured_peaks()
     achieved = w_bytes / (mv_ms * 1e-3) / 1e9
     launches = dec.launches_per_step()
     out = {
-        "metric": METRIC, "value": world * steps / (ms_dev * 1e-3), "unit": "tokens/s", "n_gpus": world,
+        "metric": METRIC, "value": seqs * steps / (ms_dev * 1e-3), "unit": "tokens/s", "n_gpus": world,
         "steps": steps, "warmup": warmup, "ms_per_step": ms_dev / steps, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f32 activations / accumulation over Q4_K,Q6_K weights and f16 KV",
+        "scaling": "strong" if tp_mode else "weak", "vs_baseline": None, "dtype": "f32 activations / accumulation over Q4_K,Q6_K weights and f16 KV",
         "data": "synthetic", "config": config,
         "roofline": {"bound": "hbm", "kernel": "matvec_stream_kernel", "achieved": achieved, "peak": peak,
                      "peak_source": "MEASURED_PEAKS.json hbm_gbs" if peak_kind == "measured" else "fallback 6.65 TB/s",
@@ -272,19 +320,16 @@ def main():
                      "attention": {"achieved": kv_bytes / (at_ms * 1e-3) / 1e9, "frac": kv_bytes / (at_ms * 1e-3) / 1e9 / peak,
                                    "launches_per_step": at_n, "avg_launch_us": at_ms * 1e3 / at_n},
                      "other_ms_per_step": ot_ms, "other_launches_per_step": ot_n},
-        "e2e": {"value": world * steps / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": 16,
+        "e2e": {"value": seqs * steps / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": 16,
                 "d2h_bytes_per_step": 4},
         "gpu_launches": launches * steps, "clocks": clocks, "last_token": int(toks[-1]),
     }
-    if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        r = cpu_reference_arm(1, 1)
-        out["cpu_baseline"] = {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")}
+    if tp_mode:
+        out["roofline"]["per_gpu"] = "bytes are this rank's share (1/%d of the weights and KV); fractions are per GPU" % world
+        out["roofline"]["exchange"] = {"launches_per_step": cm_n, "ms_per_step": cm_ms, "avg_launch_us": cm_ms * 1e3 / max(cm_n, 1)}
+    barrier()
     dec.close()
-    ctx.close()
-    if dist is not None:
-        dist.destroy_process_group()
-    if rank == 0:
-        print(json.dumps(out))
+    return out
 
 
 if __name__ == "__main__":

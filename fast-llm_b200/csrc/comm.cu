@@ -11,11 +11,12 @@
 //     flags[2 slots][kMaxRanks][kChunks] u32    "chunk c of rank r has landed", holds the epoch
 //     top  [2 slots][kMaxRanks][4] f32          per-rank argmax records
 //     tflag[2 slots][kMaxRanks] u32
-// A launch with epoch e (a per-rank counter that every exchange launch bumps,
-// identical on all ranks because they run the same launch sequence) uses slot
-// e & 1. CTA c pushes chunk c of its partial vector into every rank's recv
-// (plain stores over NVLink), makes them visible (fence.acq_rel.sys after a CTA
-// barrier) and publishes flag = e at each destination; then it waits until the
+// A launch with epoch e (per rank one counter per chunk, bumped by the CTA that
+// owns the chunk in every exchange launch, so identical on all ranks because they
+// run the same launch sequence) uses slot e & 1. CTA c pushes chunk c of its partial vector into every rank's recv
+// (plain stores over NVLink) and, after a CTA barrier, publishes flag = e at each
+// destination with a system-scope release store (which orders the CTA's data
+// stores before the flag); then it waits until the
 // flags of all ranks for its chunk in its OWN buffer equal e, and adds the G
 // partials in rank order (so every rank computes bit-identical sums) plus the
 // residual. Two slots are enough: a rank can only push epoch e+2 after it has
@@ -34,7 +35,6 @@ namespace flb {
 
 namespace {
 
-__device__ __forceinline__ void fence_acq_rel_sys() { asm volatile("fence.acq_rel.sys;" ::: "memory"); }
 __device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v) {
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
@@ -71,16 +71,16 @@ __device__ __forceinline__ uint32_t *tflag_of(uint8_t *base, uint32_t slot, uint
     return reinterpret_cast<uint32_t *>(base + kCommTFlagOff) + (size_t)slot * kCommMaxRanks + rank;
 }
 
-// The last CTA of an exchange launch stores the epoch it used.
-__device__ __forceinline__ void finish_epoch(CommState st, uint32_t e) {
-    __syncthreads();
+// Epoch of this launch for the calling CTA: its own counter + 1, stored back at once
+// (only this CTA of this stream's exchange launches ever touches the counter).
+__device__ __forceinline__ uint32_t next_epoch(uint32_t *ctr) {
+    __shared__ uint32_t e_s;
     if (threadIdx.x == 0) {
-        __threadfence();
-        if (atomicAdd(st.done, 1u) == gridDim.x - 1) {
-            *st.done = 0;
-            *st.epoch = e;
-        }
+        e_s = *ctr + 1u;
+        *ctr = e_s;
     }
+    __syncthreads();
+    return e_s;
 }
 
 // out[i] = resid[i] + sum over ranks of their `in`[i], i < n (n a multiple of 4 * kCommChunks).
@@ -90,17 +90,16 @@ __global__ void __launch_bounds__(1024) allreduce_resid_kernel(const AllReduceAr
     griddep_wait();
     __shared__ uint32_t ok_s;
     const uint32_t tid = threadIdx.x, chunk = blockIdx.x;
-    const uint32_t e = *a.st.epoch + 1u, slot = e & 1u;
     const uint32_t i = (chunk * blockDim.x + tid) * 4;
-    if (tid == 0) ok_s = 1u;
     const float4 mine = *reinterpret_cast<const float4 *>(a.in + i);
+    if (tid == 0) ok_s = 1u;
+    const uint32_t e = next_epoch(a.st.epoch + chunk), slot = e & 1u;
     for (uint32_t k = 0; k < a.world; ++k) {
         const uint32_t p = (a.rank + k) % a.world;   // own buffer first, then the ring of peers
         *reinterpret_cast<float4 *>(recv_of(a.peers[p], slot, a.rank) + i) = mine;
     }
     __syncthreads();
     if (tid < a.world) {
-        fence_acq_rel_sys();
         st_release_sys(flag_of(a.peers[tid], slot, a.rank, chunk), e);
         if (!wait_flag(flag_of(a.peers[a.rank], slot, tid, chunk), e, a.status)) ok_s = 0u;
     }
@@ -113,7 +112,6 @@ __global__ void __launch_bounds__(1024) allreduce_resid_kernel(const AllReduceAr
         }
         *reinterpret_cast<float4 *>(a.out + i) = acc;
     }
-    finish_epoch(a.st, e);
 }
 
 struct Top { float b; uint32_t i; float s; };
@@ -133,7 +131,7 @@ __global__ void __launch_bounds__(32) argmax_exchange_kernel(const TopExchangeAr
     griddep_launch_dependents();
     griddep_wait();
     const uint32_t tid = threadIdx.x;
-    const uint32_t e = *a.st.epoch + 1u, slot = e & 1u;
+    const uint32_t e = next_epoch(a.st.epoch + kCommChunks), slot = e & 1u;   // its own counter, after the chunks'
     bool ok = true;
     if (tid < a.world) {
         float4 rec;
@@ -142,7 +140,6 @@ __global__ void __launch_bounds__(32) argmax_exchange_kernel(const TopExchangeAr
         rec.z = a.top3[2];
         rec.w = 0.f;
         *reinterpret_cast<float4 *>(top_of(a.peers[tid], slot, a.rank)) = rec;
-        fence_acq_rel_sys();
         st_release_sys(tflag_of(a.peers[tid], slot, a.rank), e);
         ok = wait_flag(tflag_of(a.peers[a.rank], slot, tid), e, a.status);
     }
@@ -157,7 +154,6 @@ __global__ void __launch_bounds__(32) argmax_exchange_kernel(const TopExchangeAr
         *a.out_idx = (int32_t)r.i;
         *a.out_margin = r.b - r.s;
     }
-    finish_epoch(a.st, e);
 }
 
 } // namespace

@@ -63,7 +63,7 @@ struct fl_b200_decoder {
     uint8_t *comm = nullptr;                // this rank's exchange buffer (mapped by the peers)
     uint8_t *peers[kCommMaxRanks] = {};     // all ranks' buffers as mapped here
     bool peers_set = false;
-    uint32_t *comm_state = nullptr;         // [0] epoch, [1] CTA counter
+    uint32_t *comm_state = nullptr;         // epoch counters of the exchange kernels
     float *partial = nullptr, *top3 = nullptr;
     std::vector<Tensor> lw;                 // n_layer * 7
     std::vector<const float *> attn_norm, ffn_norm;
@@ -115,7 +115,7 @@ static int enqueue_step(fl_b200_decoder *d, cudaStream_t s, uint32_t *n_launch, 
     fl_b200_ctx *ctx = d->ctx;
     const uint32_t E = c.n_embd, D = c.head_dim, QD = d->Hq * D, KD = d->Hkv * D;
     const bool tp = d->tp_size > 1;
-    const CommState cst{d->comm_state, d->comm_state ? d->comm_state + 1 : nullptr};
+    const CommState cst{d->comm_state};
     // sum of the ranks' partial vectors + residual (the exchange step after O and after down)
     auto do_allreduce = [&](const float *resid, float *out) -> int {
         AllReduceArgs r{};
@@ -283,8 +283,8 @@ int fl_b200_decoder_create_tp(fl_b200_ctx *ctx, const fl_b200_llama_cfg *cfg, ui
     if (world > 1) {
         CK(cudaMalloc(&d->comm, comm_buffer_bytes()));
         CK(cudaMemsetAsync(d->comm, 0, comm_buffer_bytes(), ctx->stream));
-        CK(cudaMalloc(&d->comm_state, 16));
-        CK(cudaMemsetAsync(d->comm_state, 0, 16, ctx->stream));
+        CK(cudaMalloc(&d->comm_state, 64));
+        CK(cudaMemsetAsync(d->comm_state, 0, 64, ctx->stream));
         CK(cudaMalloc(&d->partial, c.n_embd * 4));
     }
     CK(cudaMalloc(&d->xn_final, c.n_embd * 4));

@@ -102,8 +102,7 @@ constexpr size_t kCommTopOff = kCommFlagsOff + (size_t)2 * kCommMaxRanks * kComm
 constexpr size_t kCommTFlagOff = kCommTopOff + (size_t)2 * kCommMaxRanks * 16;
 constexpr size_t kCommBytes = kCommTFlagOff + (size_t)2 * kCommMaxRanks * 4;
 struct CommState {
-    uint32_t *epoch;   // device scalar: epoch of the last finished exchange on this rank
-    uint32_t *done;    // device scalar: CTA arrival counter (zero between launches)
+    uint32_t *epoch;   // kCommChunks + 1 device counters: epoch of the last exchange per chunk, then of the argmax exchange
 };
 struct AllReduceArgs {
     uint8_t *peers[kCommMaxRanks];   // every rank's communication buffer as mapped here; peers[rank] is local

@@ -184,7 +184,9 @@ def device_llama(dec, cfg, seed, n_prefill, kv_std=0.1, recipe=Q4_K_M):
     from . import tp
     dev = torch.device("cuda", dec.ctx.device)
     gen = torch.Generator(device=dev)
-    gen.manual_seed(seed)
+    gen.manual_seed(seed * 64 + dec.rank)   # this rank's slices
+    rep = torch.Generator(device=dev)
+    rep.manual_seed(seed * 64 + 63)         # tensors every rank holds whole: norms, embedding table
     keep = []
     shapes = layer_shapes(dec.loc)
     for l in range(cfg["n_layer"]):
@@ -194,8 +196,8 @@ def device_llama(dec, cfg, seed, n_prefill, kv_std=0.1, recipe=Q4_K_M):
             if name in tp.COL_SPLIT and w.shape[1] % 16:
                 w = torch.nn.functional.pad(w, (0, 16 - w.shape[1] % 16)).contiguous()
             dec.set_layer_tensor(l, i, recipe[name], w)
-        an = torch.rand(cfg["n_embd"], device=dev, generator=gen) * 0.2 + 0.9
-        fn = torch.rand(cfg["n_embd"], device=dev, generator=gen) * 0.2 + 0.9
+        an = torch.rand(cfg["n_embd"], device=dev, generator=rep) * 0.2 + 0.9
+        fn = torch.rand(cfg["n_embd"], device=dev, generator=rep) * 0.2 + 0.9
         dec.set_layer_norms(l, an, fn)
         if n_prefill:
             kp, vp = dec.kv_ptrs(l)
@@ -210,9 +212,9 @@ def device_llama(dec, cfg, seed, n_prefill, kv_std=0.1, recipe=Q4_K_M):
                                                 C.c_size_t(full.numel() * 2)))
     for which, name in ((capi.G_TOK_EMBD, "tok_embd"), (capi.G_OUTPUT, "output")):
         rows = cfg["n_vocab"] if name == "tok_embd" else dec.loc["n_vocab"]   # the embedding table is whole on every rank
-        w = device_quant_tensor(recipe[name], rows, cfg["n_embd"], gen)
+        w = device_quant_tensor(recipe[name], rows, cfg["n_embd"], rep if name == "tok_embd" else gen)
         dec.set_global(which, recipe[name], w)
-    on = torch.rand(cfg["n_embd"], device=dev, generator=gen) * 0.2 + 0.9
+    on = torch.rand(cfg["n_embd"], device=dev, generator=rep) * 0.2 + 0.9
     dec.set_out_norm(on)
     torch.cuda.synchronize(dev)
     return keep
