@@ -23,9 +23,9 @@ SYMBOLS = [
     "fl_b200_abi_version", "fl_b200_last_error", "fl_b200_create", "fl_b200_destroy", "fl_b200_sync",
     "fl_b200_device_status", "fl_b200_sm_count", "fl_b200_stream", "fl_b200_malloc", "fl_b200_free",
     "fl_b200_upload", "fl_b200_download", "fl_b200_memset", "fl_b200_ipc_export", "fl_b200_ipc_open", "fl_b200_ipc_close", "fl_b200_timer_start", "fl_b200_timer_stop",
-    "fl_b200_dequant", "fl_b200_matvec", "fl_b200_matvec_assign", "fl_b200_matvec_pitched", "fl_b200_matvec_host",
+    "fl_b200_dequant", "fl_b200_matvec", "fl_b200_matvec_assign", "fl_b200_matvec_expert", "fl_b200_matvec_pitched", "fl_b200_matvec_host",
     "fl_b200_attn_decode", "fl_b200_attn_decode_static", "fl_b200_attn_decode_host", "fl_b200_rmsnorm", "fl_b200_add2",
-    "fl_b200_silu_mul", "fl_b200_rope_kv_append", "fl_b200_argmax", "fl_b200_exec_task",
+    "fl_b200_silu_mul", "fl_b200_router_sel", "fl_b200_wmerge", "fl_b200_rope_kv_append", "fl_b200_argmax", "fl_b200_exec_task",
     "fl_b200_decoder_create", "fl_b200_decoder_create_tp", "fl_b200_decoder_comm", "fl_b200_decoder_set_peers",
     "fl_b200_decoder_destroy", "fl_b200_decoder_set_layer_tensor",
     "fl_b200_decoder_set_layer_norms", "fl_b200_decoder_set_global", "fl_b200_decoder_set_out_norm",
@@ -156,6 +156,20 @@ class Context:
 
     def matvec_assign(self, fmt, w, rows, cols, x, y):
         _ck(self.lib.fl_b200_matvec_assign(self._h, fmt, _p(w), C.c_uint32(rows), C.c_uint32(cols), _p(x), _p(y)))
+
+    def matvec_expert(self, fmt, w, rows, cols, expert_id, expert_stride, x, y, nx=1, xstride=0, ystride=0):
+        """STREAM_DOT_IDX: accumulates W[expert] x into y; expert_id is a device uint32."""
+        _ck(self.lib.fl_b200_matvec_expert(self._h, fmt, _p(w), C.c_uint32(rows), C.c_uint32(cols), _p(expert_id),
+                                           C.c_uint64(expert_stride), _p(x), C.c_uint32(nx), C.c_uint32(xstride),
+                                           _p(y), C.c_uint32(ystride)))
+
+    def router_sel(self, logits, ids, gates, n_expert, top_k, norm, scale):
+        _ck(self.lib.fl_b200_router_sel(self._h, _p(logits), _p(ids), _p(gates), C.c_uint32(n_expert),
+                                        C.c_uint32(top_k), C.c_uint32(norm), C.c_float(scale)))
+
+    def wmerge(self, parts, gates, add1, add2, y, scale, n_parts, n, n_full=0):
+        _ck(self.lib.fl_b200_wmerge(self._h, _p(parts), _p(gates), _p(add1), _p(add2), _p(y), C.c_float(scale),
+                                    C.c_uint32(n_parts), C.c_uint32(n), C.c_uint32(n_full)))
 
     def matvec_pitched(self, fmt, w, rows, cols, pitch, x, y):
         _ck(self.lib.fl_b200_matvec_pitched(self._h, fmt, _p(w), C.c_uint32(rows), C.c_uint32(cols), C.c_uint32(pitch),

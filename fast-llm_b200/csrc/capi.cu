@@ -235,7 +235,8 @@ static int check_matvec(int fmt, const void *w, uint32_t rows, uint32_t cols, co
 }
 
 static int matvec_impl(fl_b200_ctx *c, int fmt, const void *w, uint32_t rows, uint32_t cols, const float *x,
-                       uint32_t nx, uint32_t xstride, float *y, uint32_t ystride, int accumulate, uint32_t pitch = 0) {
+                       uint32_t nx, uint32_t xstride, float *y, uint32_t ystride, int accumulate, uint32_t pitch = 0,
+                       const uint32_t *expert_id = nullptr, uint64_t expert_stride = 0) {
     if (int rc = check_matvec(fmt, w, rows, cols, x, y)) return rc;
     if (pitch != 0 && pitch < row_bytes(fmt, cols))
         return set_err(FL_B200_ERR_ARG, "matvec: row pitch %u smaller than the packed row (%llu bytes)", pitch,
@@ -250,6 +251,14 @@ static int matvec_impl(fl_b200_ctx *c, int fmt, const void *w, uint32_t rows, ui
         a.t[0].rows = rows;
         a.t[0].fmt = fmt;
         a.t[0].pitch = pitch;
+        if (expert_id) {
+            const uint64_t rb = pitch ? pitch : row_bytes(fmt, cols);
+            if (expert_stride == 0 || expert_stride % rb != 0)
+                return set_err(FL_B200_ERR_ARG, "matvec: expert stride %llu is not a whole number of %llu-byte rows",
+                               (unsigned long long)expert_stride, (unsigned long long)rb);
+            a.t[0].expert_id = expert_id;
+            a.t[0].expert_rows = (uint32_t)(expert_stride / rb);
+        }
         a.x = x + (size_t)p * xstride;
         a.cols = cols;
         a.x_mode = MV_X_PLAIN;
@@ -259,6 +268,13 @@ static int matvec_impl(fl_b200_ctx *c, int fmt, const void *w, uint32_t rows, ui
         if (int rc = cuda_err(launch_matvec(a, c->sms, c->stream), "matvec launch")) return rc;
     }
     return FL_B200_OK;
+}
+
+int fl_b200_matvec_expert(fl_b200_ctx *c, int fmt, const void *w, uint32_t rows, uint32_t cols,
+                          const uint32_t *expert_id, uint64_t expert_stride, const float *x, uint32_t nx, uint32_t xstride,
+                          float *y, uint32_t ystride) {
+    if (!expert_id) return set_err(FL_B200_ERR_ARG, "matvec_expert: null expert id pointer");
+    return matvec_impl(c, fmt, w, rows, cols, x, nx, xstride, y, ystride, 1, 0, expert_id, expert_stride);
 }
 
 int fl_b200_matvec_pitched(fl_b200_ctx *c, int fmt, const void *w, uint32_t rows, uint32_t cols, uint32_t pitch,
@@ -417,6 +433,20 @@ int fl_b200_silu_mul(fl_b200_ctx *c, const float *g, const float *u, float *h, u
     return cuda_err(launch_silu_mul(g, u, h, n, c->stream), "silu_mul launch");
 }
 
+int fl_b200_router_sel(fl_b200_ctx *c, const float *logits, uint32_t *ids, float *gates, uint32_t n_expert,
+                       uint32_t top_k, uint32_t norm, float scale) {
+    if (!c || !logits || !ids || !gates) return set_err(FL_B200_ERR_ARG, "router_sel: null pointer");
+    if (n_expert == 0 || n_expert > 256 || top_k == 0 || top_k > n_expert)
+        return set_err(FL_B200_ERR_ARG, "router_sel: %u experts (1..256), top_k %u", n_expert, top_k);
+    return cuda_err(launch_router_sel(logits, ids, gates, n_expert, top_k, norm, scale, c->stream), "router_sel launch");
+}
+
+int fl_b200_wmerge(fl_b200_ctx *c, const float *parts, const float *gates, const float *add1, const float *add2,
+                   float *y, float scale, uint32_t n_parts, uint32_t n, uint32_t n_full) {
+    if (!c || !parts || !y || n == 0 || n_parts == 0) return set_err(FL_B200_ERR_ARG, "wmerge: bad argument");
+    return cuda_err(launch_wmerge(parts, gates, add1, add2, y, scale, n_parts, n, n_full, c->stream), "wmerge launch");
+}
+
 int fl_b200_rope_kv_append(fl_b200_ctx *c, float *q, const float *k, const float *v, uint16_t *kc,
                            uint16_t *vc, const int32_t *pos, uint32_t n_q, uint32_t n_kv, uint32_t d,
                            uint32_t kv_stride, float freq_base) {
@@ -455,6 +485,28 @@ int fl_b200_exec_task(fl_b200_ctx *c, const fl_b200_task *t) {
             return set_err(FL_B200_ERR_ARG, "exec_task: STREAM_DOT w_bytes mismatch");
         return fl_b200_matvec(c, t->fmt, t->w, t->rows, t->cols, (const float *)t->x, t->nx ? t->nx : 1, t->xstride,
                               (float *)t->y, t->ystride);
+    }
+    case FL_B200_STREAM_DOT_IDX: {
+        // aux -> router-written expert id (read on the device at run time), aux2 = expert stride in bytes
+        if (!t->aux) return set_err(FL_B200_ERR_ARG, "exec_task: STREAM_DOT_IDX without the expert id pointer");
+        if (t->w_bytes != (uint64_t)t->rows * row_bytes(t->fmt, t->cols))
+            return set_err(FL_B200_ERR_ARG, "exec_task: STREAM_DOT_IDX w_bytes mismatch");
+        return fl_b200_matvec_expert(c, t->fmt, t->w, t->rows, t->cols, (const uint32_t *)t->aux, t->aux2,
+                                     (const float *)t->x, t->nx ? t->nx : 1, t->xstride, (float *)t->y, t->ystride);
+    }
+    case FL_B200_ROUTER_SEL: {
+        if (!t->aux) return set_err(FL_B200_ERR_ARG, "exec_task: decode op without aux param block");
+        fl_b200_router_p p;
+        CK(cudaMemcpyAsync(&p, t->aux, sizeof(p), cudaMemcpyDefault, c->stream));
+        CK(cudaStreamSynchronize(c->stream));
+        return fl_b200_router_sel(c, p.logits, p.ids, p.gates, p.n_expert, p.top_k, p.norm, p.scale);
+    }
+    case FL_B200_WMERGE: {
+        if (!t->aux) return set_err(FL_B200_ERR_ARG, "exec_task: decode op without aux param block");
+        fl_b200_wmerge_p p;
+        CK(cudaMemcpyAsync(&p, t->aux, sizeof(p), cudaMemcpyDefault, c->stream));
+        CK(cudaStreamSynchronize(c->stream));
+        return fl_b200_wmerge(c, p.parts, p.gates, p.add1, p.add2, p.y, p.scale, p.n_parts, p.n, p.n_full);
     }
     case FL_B200_RMSNORM: {
         if (!t->aux) return set_err(FL_B200_ERR_ARG, "exec_task: decode op without aux param block");

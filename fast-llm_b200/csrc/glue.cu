@@ -38,6 +38,68 @@ __global__ void add2_kernel(const float *__restrict__ a, const float *__restrict
     if (i < n) y[i] = __fadd_rn(a[i], b[i]);
 }
 
+// fl_op_router_sel, decode_params.h:234-265: one thread follows the reference's
+// sequential algorithm literally (same order of sums, IEEE divisions, ties to
+// the lower index); n_expert <= 256 like the reference's stack array.
+__global__ void router_sel_kernel(const float *__restrict__ logits, uint32_t *ids, float *gates, uint32_t n_expert,
+                                  uint32_t top_k, uint32_t norm, float scale) {
+    if (threadIdx.x != 0 || blockIdx.x != 0) return;
+    float mx = -1e30f;
+    for (uint32_t i = 0; i < n_expert; ++i)
+        if (logits[i] > mx) mx = logits[i];
+    float w[256];
+    float sum = 0.f;
+    for (uint32_t i = 0; i < n_expert; ++i) {
+        w[i] = expf(__fsub_rn(logits[i], mx));
+        sum = __fadd_rn(sum, w[i]);
+    }
+    for (uint32_t i = 0; i < n_expert; ++i) w[i] = __fdiv_rn(w[i], sum);
+    float tsum = 0.f;
+    for (uint32_t k = 0; k < top_k; ++k) {
+        uint32_t best = 0;
+        float bw = -1.f;
+        for (uint32_t i = 0; i < n_expert; ++i) {
+            bool taken = false;
+            for (uint32_t k2 = 0; k2 < k; ++k2)
+                if (ids[k2] == i) { taken = true; break; }
+            if (!taken && w[i] > bw) { bw = w[i]; best = i; }
+        }
+        ids[k] = best;
+        gates[k] = bw;
+        tsum = __fadd_rn(tsum, bw);
+    }
+    for (uint32_t k = 0; k < top_k; ++k) {
+        float g = gates[k];
+        if (norm) g = __fdiv_rn(g, tsum);
+        gates[k] = __fmul_rn(g, scale);
+    }
+}
+
+// fl_op_wmerge, decode_params.h:274-295: y = add1 + add2 + scale * sum_q gate_q * part_q,
+// products and sums rounded separately and in the reference's order.
+__global__ void wmerge_kernel(const float *__restrict__ parts, const float *__restrict__ gates,
+                              const float *__restrict__ add1, const float *__restrict__ add2, float *__restrict__ y,
+                              float scale, uint32_t n_parts, uint32_t n, uint32_t n_full) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    float gsc = 1.0f;
+    if (gates && n_full > n_parts) {
+        float s = 0.f, sf = 0.f;
+        for (uint32_t q = 0; q < n_parts; ++q) s = __fadd_rn(s, gates[q]);
+        for (uint32_t q = 0; q < n_full; ++q) sf = __fadd_rn(sf, gates[q]);
+        if (s > 0.f) gsc = __fdiv_rn(sf, s);
+    }
+    float acc = 0.f;
+    for (uint32_t q = 0; q < n_parts; ++q) {
+        const float g = gates ? __fmul_rn(gsc, gates[q]) : 1.0f;
+        acc = __fadd_rn(acc, __fmul_rn(g, parts[(size_t)q * n + i]));
+    }
+    acc = __fmul_rn(acc, scale);
+    if (add1) acc = __fadd_rn(acc, add1[i]);
+    if (add2) acc = __fadd_rn(acc, add2[i]);
+    y[i] = acc;
+}
+
 // fl_op_silu_mul, decode_params.h:267-272: (g / (1 + expf(-g))) * u
 __global__ void silu_mul_kernel(const float *__restrict__ g, const float *__restrict__ u, float *__restrict__ h,
                                 uint32_t n) {
@@ -167,6 +229,20 @@ cudaError_t launch_rmsnorm(const float *x, const float *wnorm, float *y, float e
 
 cudaError_t launch_add2(const float *a, const float *b, float *y, uint32_t n, cudaStream_t stream) {
     add2_kernel<<<(n + 255) / 256, 256, 0, stream>>>(a, b, y, n);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_router_sel(const float *logits, uint32_t *ids, float *gates, uint32_t n_expert, uint32_t top_k,
+                              uint32_t norm, float scale, cudaStream_t stream) {
+    if (n_expert == 0 || n_expert > 256 || top_k == 0 || top_k > n_expert) return cudaErrorInvalidValue;
+    router_sel_kernel<<<1, 32, 0, stream>>>(logits, ids, gates, n_expert, top_k, norm, scale);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_wmerge(const float *parts, const float *gates, const float *add1, const float *add2, float *y,
+                          float scale, uint32_t n_parts, uint32_t n, uint32_t n_full, cudaStream_t stream) {
+    if (n == 0 || n_parts == 0) return cudaErrorInvalidValue;
+    wmerge_kernel<<<(n + 255) / 256, 256, 0, stream>>>(parts, gates, add1, add2, y, scale, n_parts, n, n_full);
     return cudaGetLastError();
 }
 

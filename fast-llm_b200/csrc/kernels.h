@@ -21,6 +21,10 @@ struct MatvecTensor {
     int fmt;
     uint32_t pitch;       // bytes between rows; 0 = packed (row_bytes(fmt, cols)). A column slice of a Q6_K
                           // tensor is stored with its rows zero-padded to a multiple of 16 bytes.
+    // Expert indirection (STREAM_DOT_IDX, fl_idx_w, src/runtime/runtime_internal.h:149-152): the rows used
+    // are those of expert *expert_id, expert_rows rows further down per expert (nullptr: none).
+    const uint32_t *expert_id;
+    uint32_t expert_rows;
 };
 
 enum : int {
@@ -131,6 +135,12 @@ cudaError_t launch_argmax_exchange(const TopExchangeArgs &a, cudaStream_t stream
 cudaError_t launch_rmsnorm(const float *x, const float *wnorm, float *y, float eps, uint32_t n,
                            cudaStream_t stream);
 cudaError_t launch_add2(const float *a, const float *b, float *y, uint32_t n, cudaStream_t stream);
+// fl_op_router_sel (src/runtime/decode_params.h:234-265): softmax over n_expert logits, top_k by weight.
+cudaError_t launch_router_sel(const float *logits, uint32_t *ids, float *gates, uint32_t n_expert, uint32_t top_k,
+                              uint32_t norm, float scale, cudaStream_t stream);
+// fl_op_wmerge (src/runtime/decode_params.h:274-295).
+cudaError_t launch_wmerge(const float *parts, const float *gates, const float *add1, const float *add2, float *y,
+                          float scale, uint32_t n_parts, uint32_t n, uint32_t n_full, cudaStream_t stream);
 cudaError_t launch_silu_mul(const float *gate, const float *up, float *h, uint32_t n, cudaStream_t stream);
 // RoPE (adjacent pairs) on q in place and on k, then store k and v as f16 at
 // row *pos of a cache laid out [n_kv_head][kv_stride][head_dim].

@@ -275,6 +275,7 @@ struct QuadRef {
     float *y;
     const float *resid;
     uint32_t r0, rows;     // first row index, rows in the tensor
+    uint32_t row_off;      // rows to skip in the weight array (expert indirection)
     int fmt, ti;           // format, tensor index
 };
 
@@ -296,6 +297,7 @@ __device__ __forceinline__ QuadRef locate_quad(const MatvecArgs &a, uint32_t qua
         q.ti = 0;
         q.y = a.t[0].y;
         q.resid = nullptr;
+        q.row_off = 0;
         return q;
     }
     int ti = 0;
@@ -313,6 +315,7 @@ __device__ __forceinline__ QuadRef locate_quad(const MatvecArgs &a, uint32_t qua
     q.ti = ti;
     q.y = t.y;
     q.resid = t.resid;
+    q.row_off = t.expert_id ? *t.expert_id * t.expert_rows : 0u;
     return q;
 }
 
@@ -326,6 +329,8 @@ matvec_stream_kernel(const MatvecArgs a, const __grid_constant__ TensorMaps maps
     const uint32_t stage_bytes = use_q6 ? kStage6 : kStage4;
     __shared__ float red[kWarps];
 
+    bool indirect = false;
+    for (int i = 0; i < a.n_tensors; ++i) indirect = indirect || a.t[i].expert_id != nullptr;
     uint64_t *bars = sm.bars + warp * stages;
     const uint32_t ring = smem_u32(sm.ring) + warp * stages * stage_bytes;   // shared address
     if (lane == 0)
@@ -352,16 +357,17 @@ matvec_stream_kernel(const MatvecArgs a, const __grid_constant__ TensorMaps maps
             tma_load_box(ring + p_slot * stage_bytes, &maps.m[0], p_seg * (sb / 8), pq.r0, &bars[p_slot]);
             tma_load_box(ring + p_slot * stage_bytes + 2 * sb, &maps.m[1], p_seg * (sb / 8), pq.r0, &bars[p_slot]);
         } else {
-            tma_load_box(ring + p_slot * stage_bytes, &maps.m[pq.ti], p_seg * (sb / 8), pq.r0, &bars[p_slot]);
+            tma_load_box(ring + p_slot * stage_bytes, &maps.m[pq.ti], p_seg * (sb / 8), pq.r0 + pq.row_off, &bars[p_slot]);
         }
         ++p_i;
         if (++p_slot == (uint32_t)stages) p_slot = 0;
         if (++p_seg == nseg) { p_seg = 0; p_quad += W; }
     };
-    // Weights do not depend on the activation: start streaming before x is built.
+    // Weights do not depend on the activation: start streaming before x is built
+    // (unless the expert to stream is itself a result of the previous kernel).
     if (tid == 0) trace_min(a.trace, 0);
     griddep_launch_dependents();
-    if (lane == 0)
+    if (lane == 0 && !indirect)
         while (p_i < (uint32_t)stages && p_i < my_stages) issue();
 
     // ---- build the fixed-point activation in shared memory ----
@@ -390,6 +396,8 @@ matvec_stream_kernel(const MatvecArgs a, const __grid_constant__ TensorMaps maps
     }
     griddep_wait();   // the activation (and y, resid) come from the previous kernel
     if (tid == 0) trace_min(a.trace, 1);
+    if (lane == 0 && indirect)
+        while (p_i < (uint32_t)stages && p_i < my_stages) issue();
 #pragma unroll
     for (int b = 0; b < kMaxBlk; ++b) {
         const uint32_t blk = warp + b * kWarps;
@@ -613,7 +621,8 @@ __global__ void __launch_bounds__(256) matvec_generic_kernel(const MatvecArgs a,
         }
         const MatvecTensor &t = a.t[ti];
         const uint32_t r = vr - base;
-        const uint8_t *row = t.w + (uint64_t)r * (t.pitch ? t.pitch : row_bytes(t.fmt, a.cols));
+        const uint64_t pitch = t.pitch ? t.pitch : row_bytes(t.fmt, a.cols);
+        const uint8_t *row = t.w + ((uint64_t)r + (t.expert_id ? (uint64_t)*t.expert_id * t.expert_rows : 0ull)) * pitch;
         float acc = 0.f;
         for (uint32_t e = lane; e < a.cols; e += 32) acc += dequant_elem(t.fmt, row, e) * a.x[e];
         acc = warp_sum(acc);
@@ -664,7 +673,9 @@ static cudaError_t encode_map(CUtensorMap *m, const MatvecTensor &t, uint32_t co
     if (!g_encode) return cudaErrorNotSupported;
     const uint64_t rb = t.pitch ? t.pitch : row_bytes(t.fmt, cols);   // a multiple of 16 (checked by the caller)
     const uint32_t seg = t.fmt == FMT_Q4_K ? kSeg4 : kSeg6;
-    const cuuint64_t gdim[2] = {rb / 8, t.rows};
+    // With expert indirection the rows of all experts are one array; its end is not known here, and
+    // no box reaches past an expert (rows % 4 == 0 is required), so the row bound is left open.
+    const cuuint64_t gdim[2] = {rb / 8, t.expert_id ? (cuuint64_t)0x7fffffffu : (cuuint64_t)t.rows};
     const cuuint64_t gstride[1] = {rb};
     const cuuint32_t box[2] = {seg / 8, (cuuint32_t)box_rows};
     const cuuint32_t estr[2] = {1, 1};
@@ -691,6 +702,7 @@ cudaError_t launch_matvec(const MatvecArgs &a, int sms, cudaStream_t stream) {
         const uint64_t pitch = t.pitch ? t.pitch : row_bytes(t.fmt, a.cols);
         if (pitch < row_bytes(t.fmt, a.cols)) return cudaErrorInvalidValue;
         streaming = streaming && matvec_is_streaming(t.fmt, a.cols) && (((uintptr_t)t.w) & 15u) == 0 && (pitch & 15u) == 0;
+        if (t.expert_id && (t.rows % kRowsPerStage != 0 || a.swiglu)) streaming = false;
         streaming = streaming && a.cols <= 6u * 256u * kWarps && (((uintptr_t)a.x) & 15u) == 0 &&
                     (((uintptr_t)a.x2) & 15u) == 0 && (((uintptr_t)a.wnorm) & 15u) == 0;
         q4 = q4 || t.fmt == FMT_Q4_K;

@@ -99,6 +99,14 @@ int fl_b200_matvec(fl_b200_ctx *ctx, int fmt, const void *w_dev, uint32_t rows, 
 int fl_b200_matvec_assign(fl_b200_ctx *ctx, int fmt, const void *w_dev, uint32_t rows, uint32_t cols,
                           const float *x_dev, float *y_dev);
 /* End-to-end form: x and y in host memory (y_host receives W x). */
+/* Task{STREAM_DOT_IDX} (include/fastllm/fastllm.h:33-36, fl_idx_w,
+ * src/runtime/runtime_internal.h:149-152): STREAM_DOT over the rows of expert
+ * *expert_id_dev (read on the device when the kernel runs, so a router kernel
+ * earlier on the stream may write it): W = w_dev + *expert_id_dev *
+ * expert_stride_bytes. Accumulates into y like STREAM_DOT. */
+int fl_b200_matvec_expert(fl_b200_ctx *ctx, int fmt, const void *w_dev, uint32_t rows, uint32_t cols,
+                          const uint32_t *expert_id_dev, uint64_t expert_stride_bytes, const float *x_dev,
+                          uint32_t nx, uint32_t xstride, float *y_dev, uint32_t ystride);
 /* y = W x (assigns) for a tensor whose rows are `pitch` bytes apart (pitch >=
  * the packed row size): the layout of a column slice of a k-quant tensor, whose
  * rows are zero-padded to a multiple of 16 bytes (tensor-parallel O and down). */
@@ -137,6 +145,15 @@ int fl_b200_rmsnorm(fl_b200_ctx *ctx, const float *x_dev, const float *wnorm_dev
                     uint32_t n);
 int fl_b200_add2(fl_b200_ctx *ctx, const float *a_dev, const float *b_dev, float *y_dev, uint32_t n);
 int fl_b200_silu_mul(fl_b200_ctx *ctx, const float *gate_dev, const float *up_dev, float *h_dev, uint32_t n);
+/* fl_op_router_sel (decode_params.h:234-265): softmax over n_expert (<= 256)
+ * logits, top_k by weight, ties to the lower index, optional renormalisation,
+ * times scale. fl_op_wmerge (decode_params.h:274-295): y = add1 + add2 + scale *
+ * sum_q gates[q] * parts[q*n + i] (gates, add1, add2 may be null; n_full > n_parts
+ * rescales the gates to carry the truncated tail's mass). */
+int fl_b200_router_sel(fl_b200_ctx *ctx, const float *logits_dev, uint32_t *ids_dev, float *gates_dev,
+                       uint32_t n_expert, uint32_t top_k, uint32_t norm, float scale);
+int fl_b200_wmerge(fl_b200_ctx *ctx, const float *parts_dev, const float *gates_dev, const float *add1_dev,
+                   const float *add2_dev, float *y_dev, float scale, uint32_t n_parts, uint32_t n, uint32_t n_full);
 /* fl_op_rope_ds2 (plain RoPE, adjacent pairs, decode_params.h:124-160) on q in
  * place and on k, then fl_op_kv_append (decode_params.h:162-175) of k and v
  * into an f16 cache [n_kv_head][kv_stride][head_dim] at row *pos_dev. */
@@ -192,6 +209,10 @@ typedef struct
 typedef struct { const float *wnorm, *x; float *y; float eps; uint32_t n; } fl_b200_rmsnorm_p;
 typedef struct { const float *a, *b; float *y; uint32_t n; } fl_b200_add2_p;
 typedef struct { const float *gate, *up; float *h; uint32_t n; } fl_b200_silu_mul_p;
+typedef struct { const float *logits; uint32_t *ids; float *gates; uint32_t n_expert, top_k, norm; float scale; } fl_b200_router_p;
+typedef struct {
+    const float *parts, *gates, *add1, *add2; float *y; float scale; uint32_t n_parts, n, n_full;
+} fl_b200_wmerge_p;
 /* Appended kinds. */
 typedef struct {
     const float *q; const uint16_t *kcache, *vcache; float *out; const int32_t *pos;
@@ -204,8 +225,8 @@ typedef struct {
 
 /* Executes one task (what exec_task_block does for the whole block,
  * src/runtime/gpu_exec.cu:64-140). SIGNAL is a no-op. Kinds without a device
- * implementation here (MERGE, ACT_Q8, STREAM_DOT_IDX, ROPE_DS2, KV_APPEND,
- * ATTN_HEAD, ROUTER_SEL, WMERGE) return FL_B200_ERR_ARG. */
+ * implementation here (MERGE, ACT_Q8, ROPE_DS2, KV_APPEND, ATTN_HEAD: the
+ * DeepSeek-specific forms) return FL_B200_ERR_ARG. */
 int fl_b200_exec_task(fl_b200_ctx *ctx, const fl_b200_task *task);
 
 /* ---- Llama-shape greedy decoder: Decoder::step for the GQA / f16-cache

@@ -34,6 +34,16 @@ static_assert(offsetof(fastllm::RmsNormP, eps) == offsetof(fl_b200_rmsnorm_p, ep
 static_assert(offsetof(fastllm::RmsNormP, n) == offsetof(fl_b200_rmsnorm_p, n), "RmsNormP::n");
 static_assert(sizeof(fastllm::Add2P) == sizeof(fl_b200_add2_p), "Add2P");
 static_assert(offsetof(fastllm::Add2P, n) == offsetof(fl_b200_add2_p, n), "Add2P::n");
+static_assert(sizeof(fastllm::RouterP) == sizeof(fl_b200_router_p), "RouterP");
+static_assert(offsetof(fastllm::RouterP, ids) == offsetof(fl_b200_router_p, ids), "RouterP::ids");
+static_assert(offsetof(fastllm::RouterP, top_k) == offsetof(fl_b200_router_p, top_k), "RouterP::top_k");
+static_assert(offsetof(fastllm::RouterP, scale) == offsetof(fl_b200_router_p, scale), "RouterP::scale");
+static_assert(sizeof(fastllm::WmergeP) == sizeof(fl_b200_wmerge_p), "WmergeP");
+static_assert(offsetof(fastllm::WmergeP, y) == offsetof(fl_b200_wmerge_p, y), "WmergeP::y");
+static_assert(offsetof(fastllm::WmergeP, scale) == offsetof(fl_b200_wmerge_p, scale), "WmergeP::scale");
+static_assert(offsetof(fastllm::WmergeP, n_full) == offsetof(fl_b200_wmerge_p, n_full), "WmergeP::n_full");
+static_assert((int)fastllm::TaskKind::STREAM_DOT_IDX == FL_B200_STREAM_DOT_IDX, "kind");
+static_assert((int)fastllm::TaskKind::ROUTER_SEL == FL_B200_ROUTER_SEL, "kind");
 static_assert(sizeof(fastllm::SiluMulP) == sizeof(fl_b200_silu_mul_p), "SiluMulP");
 static_assert(offsetof(fastllm::SiluMulP, n) == offsetof(fl_b200_silu_mul_p, n), "SiluMulP::n");
 
