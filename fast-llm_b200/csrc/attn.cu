@@ -7,20 +7,37 @@
 // src/runtime/gpu_exec.cu:84-88), no GQA and no f16 cache, so layout and
 // parallelisation here are new.
 //
-// Cache layout in HBM: [batch][n_kv_head][kv_stride][128] f16 for K and for V:
-// the 64-position tile a CTA needs is one contiguous 16 KB range, fetched with a
-// 1-D bulk copy (TMA engine) into a 3-stage shared-memory ring.
+// Cache layout in HBM: [batch][n_kv_head][kv_stride][128] f16 for K and for V,
+// described to the TMA unit as a 2-D tensor [rows][128]. A tile is 64 positions:
+// four boxes of 64 rows x 64 columns (K and V, low and high half of the head
+// dimension), written to shared memory with the 128-byte swizzle so that the
+// 8 x 8 matrix loads below are free of bank conflicts. 3-stage ring per CTA.
 //
-// Grid = (n_splits, n_kv_head, batch), 256 threads. A CTA serves the 4 query
-// heads of its KV head, so every K/V byte is read from HBM once per group.
-//   scores : 8 lanes per position x 16 dims each (32 positions per pass), 4 heads
-//            per lane, shuffle reduce over the 8 lanes;
-//   softmax: warp h owns head h; online (running max / sum), exp in f32;
-//   context: 16 lanes per position x 8 dims, 16 positions in flight, 4 heads;
-// Each CTA writes (max, sum, context[128]) per head to scratch and takes a
-// ticket; the CTA that draws the last ticket of its (batch, kv head) rescales
-// and sums the partials in split order (deterministic) and writes the output.
-// No CTA ever waits for another one.
+// Grid = (n_splits, n_kv_head, batch), 128 threads, two or more CTAs per SM. A
+// CTA serves the 4 query heads of its KV head, so every K/V byte is read from HBM
+// once per group. Warp w owns positions 16w .. 16w+15 of every tile and runs an
+// independent online softmax over them (no block barrier between scores,
+// softmax and context):
+//   scores : mma.sync m16n8k16 (f16 x f16 -> f32), A = K rows (ldmatrix), B = q.
+//            The 8 columns are the 4 heads, each as (hi, lo) with q = hi + lo in
+//            f16, so the product is exact to 2^-22 although the multiplier is f16;
+//   softmax: lane (g, t) holds head t for positions g and g + 8; max / sum over
+//            the 8 lanes of a head by shuffles;
+//   context: mma.sync with A = V^T (ldmatrix.trans), B = probabilities as
+//            (hi, lo) f16 pairs, accumulators 128 dims x 4 heads in registers.
+// The warps' (max, sum, context) are merged through shared memory, each CTA
+// writes one record per head to scratch and takes a ticket; the CTA that draws
+// the last ticket of its (batch, kv head) rescales and sums the partials in split
+// order (deterministic) and writes the output. No CTA ever waits for another one.
+//
+// Fused mode of the decoder (rope_k != nullptr): q arrives un-rotated, and this
+// token's K and V rows are not in the cache yet. Every CTA rotates q itself
+// (fl_op_rope_ds2, plain RoPE on adjacent pairs, angle built by repeated
+// multiplication like the reference, src/runtime/decode_params.h:124-160); the CTA
+// whose range holds the current position also rotates k, rounds k and v to f16,
+// appends them to the cache (fl_op_kv_append, decode_params.h:162-175) and patches
+// the rows into its shared-memory tile. Tiles are requested before the dependency
+// wait: older rows cannot change.
 #include "common.cuh"
 #include "kernels.h"
 
@@ -32,189 +49,255 @@ constexpr int kD = 128;              // head dimension
 constexpr int kGroup = 4;            // query heads per KV head handled by one CTA
 constexpr int kTile = 64;            // positions per stage
 constexpr int kStages = 3;
-constexpr int kAttnThreads = 256;
-constexpr int kPosPerPass = kAttnThreads / 8;    // scores: 8 lanes per position
-constexpr int kPosGroups = kAttnThreads / 16;    // context: 16 lanes per position
-constexpr uint32_t kTileBytes = kTile * kD * 2;   // 16 KB
+constexpr int kAttnWarps = 4;        // warp w <-> positions 16w .. 16w+15 of a tile
+constexpr int kAttnThreads = kAttnWarps * 32;
+constexpr uint32_t kHalfBytes = kTile * 128;        // one box: 64 rows x 64 f16 (128 bytes), swizzled
+constexpr uint32_t kStageBytes = 4 * kHalfBytes;    // K lo, K hi, V lo, V hi = 32 KB
 constexpr int kPartStride = kD + 4;  // o[128], m, l, pad (keeps o 16-byte aligned)
 
 struct AttnSmem {
-    __half k[kStages][kTile][kD];
-    __half v[kStages][kTile][kD];
-    float s[kGroup][kTile];          // scaled scores of the current tile
-    float p[kTile][kGroup];          // exp(s - m) of the current tile
-    float alpha[kGroup];
+    uint8_t ring[kStages][kStageBytes];   // 1024-byte aligned (swizzle atom)
+    float wo[kAttnWarps][kGroup][kD];     // per-warp context, for the merge
+    float wm[kAttnWarps][kGroup], wl[kAttnWarps][kGroup];
+    float2 cs[kD / 2];                    // cos / sin of this position's rotation angles (fused mode)
     uint64_t full[kStages];
     uint32_t is_last;
 };
 
-__global__ void __launch_bounds__(kAttnThreads, 2) attn_decode_kernel(const AttnArgs a) {
-    extern __shared__ __align__(128) uint8_t smem_raw[];
-    AttnSmem &sm = *reinterpret_cast<AttnSmem *>(smem_raw);
+// Byte offset of (row r, 16-byte chunk c of the 128-byte row) inside a swizzled box.
+__device__ __forceinline__ uint32_t swz(uint32_t r, uint32_t c) { return r * 128u + ((c ^ (r & 7u)) << 4); }
+
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t (&r)[4]) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t addr, uint32_t (&r)[4]) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+// D(16x8, f32) += A(16x16, f16, row) * B(16x8, f16, col)
+__device__ __forceinline__ void mma_f16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void tma_box(uint32_t dst, const CUtensorMap *map, uint32_t x, uint32_t y, uint64_t *bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+        "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
+        : "memory");
+}
+// x as an f16 pair: part 0 = the nearest f16, part 1 = the f16 nearest to the remainder.
+__device__ __forceinline__ __half split_part(float x, uint32_t part) {
+    const __half hi = __float2half_rn(x);
+    return part ? __float2half_rn(x - __half2float(hi)) : hi;
+}
+__device__ __forceinline__ uint32_t pack_h2(__half lo, __half hi) {
+    return (uint32_t)__half_as_ushort(lo) | ((uint32_t)__half_as_ushort(hi) << 16);
+}
+
+__global__ void __launch_bounds__(kAttnThreads, 2) attn_decode_kernel(const __grid_constant__ AttnArgs a) {
+    extern __shared__ uint8_t smem_dyn[];
+    AttnSmem &sm = *reinterpret_cast<AttnSmem *>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    const uint32_t g = lane >> 2, t = lane & 3u;
     const uint32_t split = blockIdx.x, hkv = blockIdx.y, b = blockIdx.z;
     const uint32_t group = a.n_q_head / a.n_kv_head;   // == kGroup (checked on the host)
+    const bool fused = a.rope_k != nullptr;
     if (tid == 0) trace_min(a.trace, 0);
-    griddep_wait();   // *pos, q and the appended K/V row come from the previous kernels
-    if (tid == 0) trace_min(a.trace, 1);
+    griddep_launch_dependents();
+    // *pos was written at the end of the previous step (or is kv_len - 1 of a single call): stable here.
     const uint32_t kv_len = a.pos ? (uint32_t)(*a.pos) + 1u : a.kv_len;
-
     const uint32_t tiles_total = (kv_len + kTile - 1) / kTile;
     const uint32_t tps = (tiles_total + a.n_splits - 1) / a.n_splits;
     const uint32_t t0 = split * tps;
     const uint32_t t1 = min(t0 + tps, tiles_total);
     const uint32_t n_tiles = t1 > t0 ? t1 - t0 : 0;
-
-    const __half *kbase = a.k + (uint64_t)b * a.batch_stride + (uint64_t)hkv * a.kv_stride * kD;
-    const __half *vbase = a.v + (uint64_t)b * a.batch_stride + (uint64_t)hkv * a.kv_stride * kD;
+    const uint32_t row0 = (b * a.n_kv_head + hkv) * a.kv_stride;   // first row of this head in the 2-D view
 
     if (tid == 0) {
         for (int s = 0; s < kStages; ++s) mbar_init(&sm.full[s], 1);
         sm.is_last = 0;
+        fence_barrier_init();
     }
-    fence_barrier_init();
-    griddep_launch_dependents();
+    if (fused && tid < kD / 2) {
+        // angle of pair i: pos * theta_scale^i by repeated multiplication (bit-identical to the reference)
+        float theta = (float)(int32_t)(kv_len - 1u);
+        for (uint32_t k = 0; k < tid; ++k) theta = __fmul_rn(theta, a.theta_scale);
+        sm.cs[tid] = make_float2(cosf(theta), sinf(theta));
+    }
     __syncthreads();
 
+    const uint32_t ring = smem_u32(&sm.ring[0][0]);
     auto issue = [&](uint32_t i) {   // thread 0 only: tile t0 + i into slot i % kStages
-        const uint32_t slot = i % kStages, p0 = (t0 + i) * kTile;
-        const uint32_t n = min((uint32_t)kTile, kv_len - p0);
-        mbar_arrive_expect_tx(&sm.full[slot], 2 * n * kD * 2);
-        bulk_g2s(&sm.k[slot][0][0], kbase + (uint64_t)p0 * kD, n * kD * 2, &sm.full[slot]);
-        bulk_g2s(&sm.v[slot][0][0], vbase + (uint64_t)p0 * kD, n * kD * 2, &sm.full[slot]);
+        const uint32_t slot = i % kStages, r = row0 + (t0 + i) * kTile;
+        const uint32_t dst = ring + slot * kStageBytes;
+        mbar_arrive_expect_tx(&sm.full[slot], kStageBytes);
+        // rows past the end of the whole cache are filled with zeros; rows past kv_len are masked below
+        tma_box(dst, &a.kmap, 0, r, &sm.full[slot]);
+        tma_box(dst + kHalfBytes, &a.kmap, 64, r, &sm.full[slot]);
+        tma_box(dst + 2 * kHalfBytes, &a.vmap, 0, r, &sm.full[slot]);
+        tma_box(dst + 3 * kHalfBytes, &a.vmap, 64, r, &sm.full[slot]);
     };
+    // Older cache rows never change: request the first tiles while the previous kernel still runs.
     if (tid == 0)
         for (uint32_t i = 0; i < (uint32_t)kStages && i < n_tiles; ++i) issue(i);
 
-    // q: this thread's 16 dims of the 4 heads: dims 8*ds .. 8*ds+7 and 64+8*ds ..
-    // 64+8*ds+7, so that the 8 lanes of a position read 128 contiguous bytes of its
-    // K row per load (no shared-memory bank conflicts).
-    const uint32_t pp = tid >> 3, ds = tid & 7u;
-    const float *qg = a.q + ((uint64_t)b * a.n_q_head + (uint64_t)hkv * group) * kD + ds * 8;
-    float q[kGroup][16];
-#pragma unroll
-    for (int h = 0; h < kGroup; ++h)
-#pragma unroll
-        for (int i = 0; i < 16; i += 4) {
-            const float4 t = *reinterpret_cast<const float4 *>(qg + h * kD + (i & 7) + (i >> 3) * 64);
-            q[h][i] = t.x; q[h][i + 1] = t.y; q[h][i + 2] = t.z; q[h][i + 3] = t.w;
-        }
+    griddep_wait();   // q (and, fused, this token's k and v) come from the previous kernel
+    if (tid == 0) trace_min(a.trace, 1);
 
-    // context accumulators: 8 dims x 4 heads; positions pg, pg+8, ...
-    const uint32_t pg = tid >> 4, dseg = tid & 15u;
-    float o[kGroup][8];
+    // ---- q as the B operand of the score MMAs: column n = g is head g/2, part g&1 (hi / lo);
+    //      for k-step kb this lane holds dims 16kb + {2t, 2t+1} and 16kb + {2t+8, 2t+9}. ----
+    uint32_t qb[8][2];
+    {
+        const uint32_t h = g >> 1, part = g & 1u;
+        const float *qg = a.q + ((uint64_t)b * a.n_q_head + (uint64_t)hkv * group + h) * kD;
 #pragma unroll
-    for (int h = 0; h < kGroup; ++h)
+        for (int kb = 0; kb < 8; ++kb)
 #pragma unroll
-        for (int i = 0; i < 8; ++i) o[h][i] = 0.f;
-    float m_run = -INFINITY, l_run = 0.f;   // warp `warp` tracks head `warp`
+            for (int j = 0; j < 2; ++j) {
+                const uint32_t d = kb * 16 + 2 * t + 8 * j;
+                float2 v = *reinterpret_cast<const float2 *>(qg + d);
+                if (fused) {
+                    const float2 cs = sm.cs[d >> 1];
+                    const float x0 = v.x, x1 = v.y;
+                    v.x = __fsub_rn(__fmul_rn(x0, cs.x), __fmul_rn(x1, cs.y));
+                    v.y = __fadd_rn(__fmul_rn(x0, cs.y), __fmul_rn(x1, cs.x));
+                }
+                qb[kb][j] = pack_h2(split_part(v.x * a.scale, part), split_part(v.y * a.scale, part));
+            }
+    }
+
+    // ---- fused mode: the CTA whose tiles hold the current position appends this token's K / V ----
+    const uint32_t pos = kv_len - 1u;
+    const bool owner = fused && n_tiles > 0 && pos / kTile >= t0 && pos / kTile < t1;
+    if (owner) {
+        // thread i < 64: pair i of k (rotated) ; thread 64 + i: elements 2i, 2i+1 of v
+        const uint32_t i = tid & 63u;
+        const float *src = (tid < 64 ? a.rope_k : a.rope_v) + ((uint64_t)b * a.n_kv_head + hkv) * kD + 2 * i;
+        float x0 = src[0], x1 = src[1];
+        if (tid < 64) {
+            const float2 cs = sm.cs[i];
+            const float y0 = __fsub_rn(__fmul_rn(x0, cs.x), __fmul_rn(x1, cs.y));
+            const float y1 = __fadd_rn(__fmul_rn(x0, cs.y), __fmul_rn(x1, cs.x));
+            x0 = y0; x1 = y1;
+        }
+        const uint32_t packed = pack_h2(__float2half_rn(x0), __float2half_rn(x1));
+        __half *cache = (tid < 64 ? a.k_append : a.v_append) + ((uint64_t)row0 + pos) * kD + 2 * i;
+        *reinterpret_cast<uint32_t *>(cache) = packed;
+        sm.wo[0][0][tid] = __uint_as_float(packed);   // staged: patched into the tile once it has landed
+    }
+
+    // ---- main loop ----
+    float o[8][4];                       // context^T: dim tile dt, {(dim g, hi), (dim g, lo), (dim g+8, hi), (dim g+8, lo)} of head t
+#pragma unroll
+    for (int dt = 0; dt < 8; ++dt) o[dt][0] = o[dt][1] = o[dt][2] = o[dt][3] = 0.f;
+    float m_run = -INFINITY, l_run = 0.f;   // of head t over this warp's positions (replicated over g)
 
     for (uint32_t it = 0; it < n_tiles; ++it) {
         const uint32_t slot = it % kStages;
         const uint32_t p0 = (t0 + it) * kTile;
-        const uint32_t n = min((uint32_t)kTile, kv_len - p0);
+        const uint32_t n = min((uint32_t)kTile, kv_len - p0);   // valid positions of this tile
+        const uint32_t st = ring + slot * kStageBytes;
         if (!mbar_wait_bounded(&sm.full[slot], (it / kStages) & 1u, a.status)) return;
-
-        // ---- scores ----
+        if (owner && pos >= p0 && pos < p0 + kTile) {
+            // overwrite the (stale) row of the current position with the values staged above
+            __syncthreads();   // staging complete (all warps pass here: `owner` and the tile are CTA-uniform)
+            const uint32_t r = pos - p0, i = tid & 63u;
+            const uint32_t off = (tid < 64 ? 0u : 2u * kHalfBytes) + (i >= 32 ? kHalfBytes : 0u) + swz(r, (i & 31u) >> 2) + (i & 3u) * 4u;
+            *reinterpret_cast<uint32_t *>(&sm.ring[slot][off]) = __float_as_uint(sm.wo[0][0][tid]);
+            __syncthreads();
+        }
+        const uint32_t wrow = warp * 16;       // this warp's rows of the tile
+        if (wrow < n) {
+            if (n < wrow + 16) {
+                // ragged end: rows >= n may hold anything (even NaN): clear them in V so that 0 * V stays 0
+                for (uint32_t k = lane; k < 16 * 16; k += 32) {
+                    const uint32_t r = wrow + (k >> 4), c = k & 15u;
+                    if (r >= n)
+                        *reinterpret_cast<uint4 *>(&sm.ring[slot][2 * kHalfBytes + (c >> 3) * kHalfBytes + swz(r, c & 7u)]) = make_uint4(0, 0, 0, 0);
+                }
+                __syncwarp();
+            }
+            // ---- scores: S[16 positions][8 columns] ----
+            float sc[4] = {0.f, 0.f, 0.f, 0.f};
+            {
+                const uint32_t r = wrow + ((lane >> 3) & 1u) * 8 + (lane & 7u);   // row this lane addresses
 #pragma unroll
-        for (int pass = 0; pass < kTile / kPosPerPass; ++pass) {
-            const uint32_t p = pass * kPosPerPass + pp;
-            float acc[kGroup] = {0.f, 0.f, 0.f, 0.f};
-            if (p < n) {
-                const uint4 r0 = *reinterpret_cast<const uint4 *>(&sm.k[slot][p][ds * 8]);
-                const uint4 r1 = *reinterpret_cast<const uint4 *>(&sm.k[slot][p][64 + ds * 8]);
-                const uint32_t rw[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const float2 kf = __half22float2(*reinterpret_cast<const __half2 *>(&rw[i]));
-#pragma unroll
-                    for (int h = 0; h < kGroup; ++h) {
-                        acc[h] = fmaf(q[h][2 * i], kf.x, acc[h]);
-                        acc[h] = fmaf(q[h][2 * i + 1], kf.y, acc[h]);
-                    }
+                for (int kb = 0; kb < 8; ++kb) {
+                    uint32_t ka[4];
+                    ldsm_x4(st + (kb >> 2) * kHalfBytes + swz(r, 2 * (kb & 3) + (lane >> 4)), ka);
+                    mma_f16(sc, ka, qb[kb][0], qb[kb][1]);
                 }
             }
-#pragma unroll
-            for (int h = 0; h < kGroup; ++h) {
-                acc[h] += __shfl_xor_sync(0xffffffffu, acc[h], 1);
-                acc[h] += __shfl_xor_sync(0xffffffffu, acc[h], 2);
-                acc[h] += __shfl_xor_sync(0xffffffffu, acc[h], 4);
-            }
-            if (ds < kGroup) {
-                const float v = ds == 0 ? acc[0] : ds == 1 ? acc[1] : ds == 2 ? acc[2] : acc[3];
-                sm.s[ds][p] = p < n ? v * a.scale : -INFINITY;
-            }
-        }
-        __syncthreads();
-
-        // ---- online softmax: warp h <-> head h (warps 0..3) ----
-        if (warp < kGroup) {
-            const float s0 = sm.s[warp][lane], s1 = sm.s[warp][lane + 32];
-            const float m_new = fmaxf(m_run, warp_max(fmaxf(s0, s1)));
-            const float e0 = expf(s0 - m_new), e1 = expf(s1 - m_new);
-            const float al = expf(m_run - m_new);
-            sm.p[lane][warp] = e0;
-            sm.p[lane + 32][warp] = e1;
-            l_run = l_run * al + warp_sum(e0 + e1);
+            // lane (g, t): head t, positions wrow + g and wrow + g + 8 (hi + lo columns)
+            float s0 = sc[0] + sc[1], s1 = sc[2] + sc[3];
+            if (wrow + g >= n) s0 = -INFINITY;
+            if (wrow + g + 8 >= n) s1 = -INFINITY;
+            float mt = fmaxf(s0, s1);
+            mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, 4));
+            mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, 8));
+            mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, 16));
+            const float m_new = fmaxf(m_run, mt);   // finite: row wrow < n is valid
+            const float p0v = expf(s0 - m_new), p1v = expf(s1 - m_new);
+            const float al = expf(m_run - m_new);   // 0 on the first tile (m_run = -inf)
+            float ps = p0v + p1v;
+            ps += __shfl_xor_sync(0xffffffffu, ps, 4);
+            ps += __shfl_xor_sync(0xffffffffu, ps, 8);
+            ps += __shfl_xor_sync(0xffffffffu, ps, 16);
+            l_run = l_run * al + ps;
             m_run = m_new;
-            if (lane == 0) sm.alpha[warp] = al;
-        }
-        __syncthreads();
-
-        // ---- context ----
-        {
-            const float4 al = *reinterpret_cast<const float4 *>(sm.alpha);
-            const float alv[kGroup] = {al.x, al.y, al.z, al.w};
+            // ---- probabilities as the B operand: column g = head g/2, part g&1; k = positions 2t, 2t+1, 2t+8, 2t+9 ----
+            const uint32_t srcA = (2 * t) * 4 + (g >> 1), srcB = srcA + 4;
+            const float a0 = __shfl_sync(0xffffffffu, p0v, srcA), b0 = __shfl_sync(0xffffffffu, p0v, srcB);
+            const float a1 = __shfl_sync(0xffffffffu, p1v, srcA), b1 = __shfl_sync(0xffffffffu, p1v, srcB);
+            const uint32_t part = g & 1u;
+            const uint32_t pb0 = pack_h2(split_part(a0, part), split_part(b0, part));
+            const uint32_t pb1 = pack_h2(split_part(a1, part), split_part(b1, part));
+            // ---- context: O^T[128 dims][8 columns] = alpha * O^T + V^T P ----
+            {
+                const uint32_t mi = lane >> 3;
+                const uint32_t r = wrow + (mi >> 1) * 8 + (lane & 7u);
 #pragma unroll
-            for (int h = 0; h < kGroup; ++h)
-#pragma unroll
-                for (int i = 0; i < 8; ++i) o[h][i] *= alv[h];
-#pragma unroll
-            for (int j = 0; j < kTile / kPosGroups; ++j) {
-                const uint32_t p = j * kPosGroups + pg;
-                if (p < n) {
-                    const uint4 r = *reinterpret_cast<const uint4 *>(&sm.v[slot][p][dseg * 8]);
-                    const float4 w = *reinterpret_cast<const float4 *>(&sm.p[p][0]);
-                    const float wv[kGroup] = {w.x, w.y, w.z, w.w};
-                    const uint32_t rw[4] = {r.x, r.y, r.z, r.w};
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const float2 vf = __half22float2(*reinterpret_cast<const __half2 *>(&rw[i]));
-#pragma unroll
-                        for (int h = 0; h < kGroup; ++h) {
-                            o[h][2 * i] = fmaf(wv[h], vf.x, o[h][2 * i]);
-                            o[h][2 * i + 1] = fmaf(wv[h], vf.y, o[h][2 * i + 1]);
-                        }
-                    }
+                for (int dt = 0; dt < 8; ++dt) {
+                    uint32_t va[4];
+                    ldsm_x4_trans(st + 2 * kHalfBytes + (dt >> 2) * kHalfBytes + swz(r, 2 * (dt & 3) + (mi & 1u)), va);
+                    o[dt][0] *= al; o[dt][1] *= al; o[dt][2] *= al; o[dt][3] *= al;
+                    mma_f16(o[dt], va, pb0, pb1);
                 }
             }
         }
-        __syncthreads();   // tile fully consumed: s/p reusable, slot reusable
-        if (tid == 0 && it + kStages < n_tiles) {
-            fence_proxy_async_smem();
-            issue(it + kStages);
-        }
+        __syncthreads();   // tile fully consumed by all warps: the slot can be refilled
+        if (tid == 0 && it + kStages < n_tiles) issue(it + kStages);
     }
 
-    // ---- reduce the 8 position groups, write this split's partial ----
-    float *red = reinterpret_cast<float *>(&sm.k[0][0][0]);   // [kPosGroups][kGroup][kD] floats = 32 KB, ring is idle now
+    // ---- merge the 4 warps' (max, sum, context) and write this split's partial ----
+    // o[dt][0] + o[dt][1] = context of head t at dim 16dt + g; o[dt][2] + o[dt][3] at dim 16dt + g + 8.
 #pragma unroll
-    for (int h = 0; h < kGroup; ++h)
-#pragma unroll
-        for (int i = 0; i < 8; ++i) red[(pg * kGroup + h) * kD + dseg * 8 + i] = o[h][i];
+    for (int dt = 0; dt < 8; ++dt) {
+        sm.wo[warp][t][16 * dt + g] = o[dt][0] + o[dt][1];
+        sm.wo[warp][t][16 * dt + g + 8] = o[dt][2] + o[dt][3];
+    }
+    if (g == 0) { sm.wm[warp][t] = m_run; sm.wl[warp][t] = l_run; }
     __syncthreads();
-    if (warp < kGroup) {
-        const uint32_t h = warp;   // head within the group
-        float *part = a.part + (((uint64_t)b * a.n_q_head + (uint64_t)hkv * group + h) * a.n_splits + split) * kPartStride;
+    {
+        const uint32_t h = warp;   // warp h <-> head h of the group, lane <-> 4 dims
+        float mw[kAttnWarps], M = -INFINITY;
 #pragma unroll
-        for (int k = 0; k < kD / 32; ++k) {
-            const uint32_t d = lane + 32 * k;
-            float t = 0.f;
+        for (int w = 0; w < kAttnWarps; ++w) { mw[w] = sm.wm[w][h]; M = fmaxf(M, mw[w]); }
+        float L = 0.f;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-            for (int g = 0; g < kPosGroups; ++g) t += red[(g * kGroup + h) * kD + d];
-            part[d] = t;
+        for (int w = 0; w < kAttnWarps; ++w) {
+            const float sc = mw[w] == -INFINITY ? 0.f : expf(mw[w] - M);
+            L = fmaf(sm.wl[w][h], sc, L);
+            const float4 v = *reinterpret_cast<const float4 *>(&sm.wo[w][h][lane * 4]);
+            acc.x = fmaf(v.x, sc, acc.x); acc.y = fmaf(v.y, sc, acc.y);
+            acc.z = fmaf(v.z, sc, acc.z); acc.w = fmaf(v.w, sc, acc.w);
         }
-        if (lane == 0) { part[kD] = m_run; part[kD + 1] = l_run; }
+        float *part = a.part + (((uint64_t)b * a.n_q_head + (uint64_t)hkv * group + h) * a.n_splits + split) * kPartStride;
+        *reinterpret_cast<float4 *>(part + lane * 4) = acc;
+        if (lane == 0) { part[kD] = M; part[kD + 1] = L; }
     }
     __threadfence();
     __syncthreads();
@@ -227,12 +310,11 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_decode_kernel(const Attn
     if (!sm.is_last) return;
     __threadfence();
 
-    // ---- combine: warps h and h+4 <-> head h. Every lane first derives the global
-    // maximum and the rescaled sum from all splits' (m, l); warp h then accumulates
-    // the context of the even splits and warp h+4 of the odd ones (each lane 4
-    // dims, 16 loads in flight), and the two halves are added in a fixed order. ----
+    // ---- combine (last CTA of this batch / KV head): warp h <-> head h. Every lane derives the
+    // global maximum and the rescaled sum from all splits' (m, l), then accumulates the contexts
+    // in split order, 4 dims per lane, 16 loads in flight. ----
     {
-        const uint32_t h = warp & 3u, half = warp >> 2;
+        const uint32_t h = warp;
         const uint64_t hq = (uint64_t)b * a.n_q_head + (uint64_t)hkv * group + h;
         const float *part = a.part + hq * a.n_splits * kPartStride;
         const uint32_t S = a.n_splits;
@@ -245,30 +327,23 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_decode_kernel(const Attn
         const float w1 = m1 == -INFINITY ? 0.f : expf(m1 - mx);
         const float L = warp_sum(l0 * w0 + l1 * w1);
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (uint32_t s0 = half; s0 < S; s0 += 32) {
-            float4 o[16];
+        for (uint32_t s0 = 0; s0 < S; s0 += 16) {
+            float4 ov[16];
 #pragma unroll
             for (int j = 0; j < 16; ++j)
-                o[j] = s0 + 2 * j < S ? __ldcg(reinterpret_cast<const float4 *>(part + (uint64_t)(s0 + 2 * j) * kPartStride) + lane)
-                                      : make_float4(0.f, 0.f, 0.f, 0.f);
+                ov[j] = s0 + j < S ? __ldcg(reinterpret_cast<const float4 *>(part + (uint64_t)(s0 + j) * kPartStride) + lane)
+                                   : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
-                const uint32_t s = s0 + 2 * j;
+                const uint32_t s = s0 + j;
                 const float w = __shfl_sync(0xffffffffu, s < 32 ? w0 : w1, s & 31u);
-                acc.x = fmaf(o[j].x, w, acc.x); acc.y = fmaf(o[j].y, w, acc.y);
-                acc.z = fmaf(o[j].z, w, acc.z); acc.w = fmaf(o[j].w, w, acc.w);
+                acc.x = fmaf(ov[j].x, w, acc.x); acc.y = fmaf(ov[j].y, w, acc.y);
+                acc.z = fmaf(ov[j].z, w, acc.z); acc.w = fmaf(ov[j].w, w, acc.w);
             }
         }
-        float4 *xch = reinterpret_cast<float4 *>(&sm.v[0][0][0]);   // the V ring is idle now
-        if (half == 1) xch[h * 32 + lane] = acc;
-        __syncthreads();
-        if (half == 0) {
-            const float4 other = xch[h * 32 + lane];
-            const float inv = 1.0f / L;
-            acc.x = (acc.x + other.x) * inv; acc.y = (acc.y + other.y) * inv;
-            acc.z = (acc.z + other.z) * inv; acc.w = (acc.w + other.w) * inv;
-            reinterpret_cast<float4 *>(a.out + hq * kD)[lane] = acc;
-        }
+        const float inv = 1.0f / L;
+        acc.x *= inv; acc.y *= inv; acc.z *= inv; acc.w *= inv;
+        reinterpret_cast<float4 *>(a.out + hq * kD)[lane] = acc;
     }
     if (tid == 0) {
         a.tickets[b * a.n_kv_head + hkv] = 0;   // ready for the next launch
@@ -276,10 +351,21 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_decode_kernel(const Attn
     }
 }
 
+constexpr size_t kAttnSmemBytes = sizeof(AttnSmem) + 1024;   // + slack to align the ring to the swizzle atom
+
 } // namespace
 
+// K and V as 2-D f16 tensors [rows][128] for the TMA unit: box = 64 rows x 64 columns, 128-byte swizzle.
+cudaError_t attn_make_maps(AttnArgs &a) {
+    const uint64_t rows = (uint64_t)a.batch * a.n_kv_head * a.kv_stride;
+    if (a.batch_stride != (uint64_t)a.n_kv_head * a.kv_stride * kD) return cudaErrorInvalidValue;   // sequences are contiguous
+    cudaError_t e = tensor_map_2d(&a.kmap, /*elem_bytes=*/2, a.k, kD, rows, kD * 2, 64, kTile, /*swizzle128=*/true);
+    if (e != cudaSuccess) return e;
+    return tensor_map_2d(&a.vmap, 2, a.v, kD, rows, kD * 2, 64, kTile, true);
+}
+
 cudaError_t attn_init(void) {
-    return cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(AttnSmem));
+    return cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kAttnSmemBytes);
 }
 
 uint32_t attn_pick_splits(uint32_t n_kv_head, uint32_t batch, uint32_t kv_len, int sms) {
@@ -339,7 +425,9 @@ cudaError_t launch_attn_decode_static(AttnArgs a, int device, cudaStream_t strea
     float *ptr = g_static_ptr[device];
     a.part = ptr;
     a.tickets = reinterpret_cast<uint32_t *>(ptr + kStaticPartFloats);
-    const cudaError_t e = cudaMemsetAsync(a.tickets, 0, (size_t)a.n_kv_head * a.batch * sizeof(uint32_t), stream);
+    cudaError_t e = cudaMemsetAsync(a.tickets, 0, (size_t)a.n_kv_head * a.batch * sizeof(uint32_t), stream);
+    if (e != cudaSuccess) return e;
+    e = attn_make_maps(a);   // host-side descriptors only
     if (e != cudaSuccess) return e;
     return launch_attn_decode(a, stream);
 }
@@ -351,8 +439,9 @@ cudaError_t launch_attn_decode(const AttnArgs &a, cudaStream_t stream) {
     if (a.n_kv_head == 0 || a.n_q_head != a.n_kv_head * kGroup || a.n_splits == 0 || a.batch == 0)
         return cudaErrorInvalidValue;
     if (a.pos == nullptr && a.kv_len == 0) return cudaErrorInvalidValue;
+    if (a.rope_k && (!a.rope_v || !a.k_append || !a.v_append || !a.pos)) return cudaErrorInvalidValue;
     const dim3 grid(a.n_splits, a.n_kv_head, a.batch);
-    return launch_kernel(attn_decode_kernel, grid, dim3(kAttnThreads), sizeof(AttnSmem), stream, a.pdl != 0, a);
+    return launch_kernel(attn_decode_kernel, grid, dim3(kAttnThreads), kAttnSmemBytes, stream, a.pdl != 0, a);
 }
 
 } // namespace flb

@@ -356,6 +356,7 @@ static int attn_impl(fl_b200_ctx *c, const float *q, const uint16_t *k, const ui
     }
     a.part = c->attn_part;
     a.tickets = c->attn_tickets;
+    if (int rc = cuda_err(attn_make_maps(a), "attn tensor maps")) return rc;
     return cuda_err(launch_attn_decode(a, c->stream), "attn launch");
 }
 

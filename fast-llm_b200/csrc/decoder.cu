@@ -7,8 +7,8 @@
 // token, and the position is read from a device scalar, so one recording serves
 // every position.
 //
-// Per layer (6 launches): [RMSNorm + Q/K/V matvec] -> [RoPE + f16 KV append] ->
-// [split-KV GQA attention + combine] -> [O matvec + residual] ->
+// Per layer (5 launches): [RMSNorm + Q/K/V matvec] ->
+// [RoPE + f16 KV append + split-KV GQA attention + combine] -> [O matvec + residual] ->
 // [RMSNorm + gate/up matvec] -> [SiLU*up + down matvec + residual];
 // then [RMSNorm + head matvec] -> [argmax] -> [advance].
 #include "capi_internal.h"
@@ -137,22 +137,17 @@ static int enqueue_step(fl_b200_decoder *d, cudaStream_t s, uint32_t *n_launch, 
             a.x_mode = MV_X_RMSNORM; a.status = ctx->status; a.pdl = kPdl;
             if (mask & K_MATVEC) { if (int rc = do_matvec(a)) return rc; ++n; }
         }
-        {
-            RopeAppendArgs a{};
-            a.q = d->q; a.k = d->k; a.v = d->v; a.kcache = d->kc[l]; a.vcache = d->vc[l]; a.pos = d->d_pos;
-            a.n_q_head = d->Hq; a.n_kv_head = d->Hkv; a.head_dim = D; a.kv_stride = c.max_kv;
-            a.theta_scale = powf(c.rope_base, -2.0f / (float)D); a.pdl = kPdl;
-            if (mask & K_OTHER) { CK(launch_rope_append(a, s)); ++n; }
-        }
-        {
+        {   // RoPE on q and k, the f16 append of k and v, and the attention itself: one kernel
             AttnArgs a{};
+            a.rope_k = d->k; a.rope_v = d->v; a.k_append = d->kc[l]; a.v_append = d->vc[l];
+            a.theta_scale = powf(c.rope_base, -2.0f / (float)D);
             a.q = d->q; a.k = d->kc[l]; a.v = d->vc[l]; a.out = d->att; a.part = d->part; a.tickets = d->tickets;
             a.pos = d->d_pos; a.kv_len = 0; a.kv_stride = c.max_kv;
             a.batch_stride = (uint64_t)d->Hkv * c.max_kv * D;
             a.n_q_head = d->Hq; a.n_kv_head = d->Hkv; a.batch = 1; a.n_splits = d->n_splits;
             a.scale = 1.0f / sqrtf((float)D); a.status = ctx->status; a.pdl = kPdl;
             if (d->trace && mask == K_ALL) a.trace = d->trace + 4 * (size_t)n;
-            if (mask & K_ATTN) { CK(launch_attn_decode(a, s)); ++n; }
+            if (mask & K_ATTN) { CK(attn_make_maps(a)); CK(launch_attn_decode(a, s)); ++n; }
         }
         {   // O projection + residual: xb = xa + Wo att (tensor parallel: partial sums over this rank's
             // columns, then the exchange adds the ranks' partials and the residual)
@@ -500,7 +495,7 @@ int fl_b200_decoder_tap(fl_b200_decoder *d, int which, float *out) {
     switch (which) {
     case 0: src = d->xa; n = c.n_embd; break;        // hidden state after the last layer
     case 1: src = d->xn_final; n = c.n_embd; break;  // final normed vector
-    case 2: src = d->q; n = QD; break;               // last layer: q after RoPE
+    case 2: src = d->q; n = QD; break;               // last layer: q (before RoPE: the attention kernel rotates it)
     case 3: src = d->v; n = KD; break;               // last layer: v
     case 4: src = d->att; n = QD; break;             // last layer: attention output
     case 5: src = d->xb; n = c.n_embd; break;        // last layer: residual after attention

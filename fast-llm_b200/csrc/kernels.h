@@ -1,6 +1,7 @@
 // Internal launch interface between the C ABI (capi.cu), the decoder
 // (decoder.cu) and the kernel translation units.
 #pragma once
+#include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -59,11 +60,14 @@ struct MatvecArgs {
 // Streaming kernel (Q4_K / Q6_K, cols a multiple of 2048) or the generic
 // kernel (every other supported shape). Returns cudaErrorInvalidValue for
 // unsupported arguments.
+// 2-D tiled TMA descriptor over a row-major array (rows x dim0 elements, row pitch stride_bytes).
+cudaError_t tensor_map_2d(CUtensorMap *m, uint32_t elem_bytes, const void *base, uint64_t dim0, uint64_t rows,
+                          uint64_t stride_bytes, uint32_t box0, uint32_t box_rows, bool swizzle128);
 cudaError_t launch_matvec(const MatvecArgs &a, int sms, cudaStream_t stream);
 // True when launch_matvec would take the streaming kernel for this shape.
 bool matvec_is_streaming(int fmt, uint32_t cols);
 // Dynamic shared memory the streaming kernel needs for (cols, formats used).
-size_t matvec_smem_bytes(uint32_t cols, bool use_q4k, bool use_q6k, int *stages_out);
+size_t matvec_smem_bytes(uint32_t cols, bool use_q4k, bool use_q6k, int *stages_out, int *warps_out);
 cudaError_t matvec_init(void);   // sets the dynamic shared memory attribute once
 void matvec_scratch_need(const MatvecArgs &a, int sms, size_t *scratch_floats, size_t *tickets);
 
@@ -84,7 +88,15 @@ struct AttnArgs {
     uint32_t *status;
     int pdl;
     unsigned long long *trace;   // optional 4-entry timeline record (diagnostics)
+    // Fused RoPE + KV append (the decoder's launch plan): q arrives un-rotated; rope_k / rope_v are this
+    // token's k and v ([batch][n_kv_head][128] f32, k un-rotated); the kernel rotates q and k by the angle
+    // of position *pos and appends k, v (f16) at row *pos of k_append / v_append (the same arrays as k, v).
+    const float *rope_k, *rope_v;   // nullptr: q is already rotated and the cache is complete
+    __half *k_append, *v_append;
+    float theta_scale;              // freq_base^(-2/128)
+    CUtensorMap kmap, vmap;         // filled by attn_make_maps
 };
+cudaError_t attn_make_maps(AttnArgs &a);
 cudaError_t launch_attn_decode(const AttnArgs &a, cudaStream_t stream);
 // Same kernel with the split-KV scratch in a fixed file-scope device array
 // (no allocation at call time); cudaErrorMemoryAllocation when the launch needs

@@ -42,14 +42,16 @@
 #include "kernels.h"
 
 #include <cuda.h>
+#include <cstdlib>
 #include <cstring>
 
 namespace flb {
 
 namespace {
 
-constexpr int kWarps = 12;            // warps per CTA (each consumes and feeds its own ring)
-constexpr int kThreads = kWarps * 32;
+constexpr int kMaxWarps = 12;         // warps per CTA (each consumes and feeds its own ring). 16 warps with two ring
+constexpr int kMinWarps = 12;         // stages each were measured slower (128-register cap), so the range is one value.
+constexpr int kMaxThreads = kMaxWarps * 32;
 constexpr int kRowsPerStage = 4;
 constexpr uint32_t kSeg4 = 8 * 144;   // bytes of one Q4_K segment (8 super-blocks)
 constexpr uint32_t kSeg6 = 8 * 210;   // bytes of one Q6_K segment
@@ -97,8 +99,8 @@ struct Smem {
     int8_t *q6;      // Q6_K layout: cols * 3 bytes
     float *s6;       // per lane: sums of its four 16-column groups
     float *xs;       // activation scale of each 256-column block
-    uint64_t *bars;  // [kWarps][stages]
-    uint8_t *ring;   // [kWarps][stages][stage bytes]
+    uint64_t *bars;  // [warps][stages]
+    uint8_t *ring;   // [warps][stages][stage bytes]
 };
 
 // Columns rounded up to whole 2048-column segments: the shared-memory layouts are
@@ -113,7 +115,7 @@ __host__ __device__ inline size_t smem_fixed_bytes(uint32_t cols, bool q4, bool 
     return n;
 }
 
-__device__ __forceinline__ Smem carve(uint8_t *base, uint32_t cols, bool q4, bool q6, int stages) {
+__device__ __forceinline__ Smem carve(uint8_t *base, uint32_t cols, bool q4, bool q6, int stages, uint32_t nw) {
     Smem s;
     uint8_t *p = base;
     cols = padded_cols(cols);
@@ -125,7 +127,7 @@ __device__ __forceinline__ Smem carve(uint8_t *base, uint32_t cols, bool q4, boo
     if (q6) { s.s6 = (float *)p; p += (size_t)cols / 16 * 4; }
     s.xs = (float *)p; p += (size_t)cols / 256 * 4;
     p = (uint8_t *)(((uintptr_t)p + 7) & ~(uintptr_t)7);
-    s.bars = (uint64_t *)p; p += (size_t)kWarps * stages * 8;
+    s.bars = (uint64_t *)p; p += (size_t)nw * stages * 8;
     p = (uint8_t *)(((uintptr_t)p + 127) & ~(uintptr_t)127);
     s.ring = p;
     return s;
@@ -319,15 +321,16 @@ __device__ __forceinline__ QuadRef locate_quad(const MatvecArgs &a, uint32_t qua
     return q;
 }
 
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kMaxThreads, 1)
 matvec_stream_kernel(const MatvecArgs a, const __grid_constant__ TensorMaps maps, const uint32_t total_quads,
                      const int stages, const int use_q4, const int use_q6) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
-    const Smem sm = carve(smem_raw, a.cols, use_q4 != 0, use_q6 != 0, stages);
+    const uint32_t nw = blockDim.x >> 5;   // warps of this launch
+    const Smem sm = carve(smem_raw, a.cols, use_q4 != 0, use_q6 != 0, stages, nw);
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
     const uint32_t nseg = (a.cols + 2047u) / 2048u;   // the last segment may be partial: the TMA unit fills the rest with zeros
     const uint32_t stage_bytes = use_q6 ? kStage6 : kStage4;
-    __shared__ float red[kWarps];
+    __shared__ float red[kMaxWarps];
 
     bool indirect = false;
     for (int i = 0; i < a.n_tensors; ++i) indirect = indirect || a.t[i].expert_id != nullptr;
@@ -341,7 +344,7 @@ matvec_stream_kernel(const MatvecArgs a, const __grid_constant__ TensorMaps maps
     // This warp's quads: gw, gw + W, ... ; per quad nseg stages (one per column segment).
     // Warps are numbered CTA-fastest, so a launch with few quads spreads them over
     // all SMs instead of filling the first CTAs.
-    const uint32_t gw = warp * gridDim.x + blockIdx.x, W = gridDim.x * kWarps;
+    const uint32_t gw = warp * gridDim.x + blockIdx.x, W = gridDim.x * nw;
     const uint32_t my_quads = gw < total_quads ? (total_quads - gw + W - 1) / W : 0;
     const uint32_t my_stages = my_quads * nseg;
 
@@ -371,11 +374,11 @@ matvec_stream_kernel(const MatvecArgs a, const __grid_constant__ TensorMaps maps
         while (p_i < (uint32_t)stages && p_i < my_stages) issue();
 
     // ---- build the fixed-point activation in shared memory ----
-    // One warp per 256-column block (blocks warp, warp + kWarps, ...); lane l holds
+    // One warp per 256-column block (blocks warp, warp + nw, ...); lane l holds
     // columns 8l .. 8l+7 of the block. All global loads of all the warp's blocks
     // are issued first, so the prologue costs one memory round trip; the norm
     // weights are constants and are fetched before the dependency wait.
-    constexpr int kMaxBlk = 6;   // blocks per warp: cols <= 6 * 256 * kWarps = 18432
+    constexpr int kMaxBlk = 6;   // blocks per warp: cols <= 6 * 256 * kMinWarps = 18432
     const uint32_t nblk = a.cols / 256, nblk_pad = nseg * 8;   // blocks nblk .. nblk_pad-1 are zeros
     float4 ra[kMaxBlk][2], rb2[kMaxBlk][2];
 #pragma unroll
@@ -386,7 +389,7 @@ matvec_stream_kernel(const MatvecArgs a, const __grid_constant__ TensorMaps maps
     if (a.x_mode == MV_X_RMSNORM) {
 #pragma unroll
         for (int b = 0; b < kMaxBlk; ++b) {
-            const uint32_t blk = warp + b * kWarps;
+            const uint32_t blk = warp + b * nw;
             if (blk < nblk) {
                 const uint32_t c0 = blk * 256 + lane * 8;
                 rb2[b][0] = __ldg(reinterpret_cast<const float4 *>(a.wnorm + c0));
@@ -400,7 +403,7 @@ matvec_stream_kernel(const MatvecArgs a, const __grid_constant__ TensorMaps maps
         while (p_i < (uint32_t)stages && p_i < my_stages) issue();
 #pragma unroll
     for (int b = 0; b < kMaxBlk; ++b) {
-        const uint32_t blk = warp + b * kWarps;
+        const uint32_t blk = warp + b * nw;
         if (blk < nblk) {
             const uint32_t c0 = blk * 256 + lane * 8;
             ra[b][0] = *reinterpret_cast<const float4 *>(a.x + c0);
@@ -418,7 +421,7 @@ matvec_stream_kernel(const MatvecArgs a, const __grid_constant__ TensorMaps maps
     if (a.x_mode == MV_X_RMSNORM) {
 #pragma unroll
         for (int b = 0; b < kMaxBlk; ++b)
-            if (warp + b * kWarps < nblk) {
+            if (warp + b * nw < nblk) {
                 const float4 u0 = ra[b][0], u1 = ra[b][1];
                 ss += (u0.x * u0.x + u0.y * u0.y) + (u0.z * u0.z + u0.w * u0.w);
                 ss += (u1.x * u1.x + u1.y * u1.y) + (u1.z * u1.z + u1.w * u1.w);
@@ -428,7 +431,7 @@ matvec_stream_kernel(const MatvecArgs a, const __grid_constant__ TensorMaps maps
     }
 #pragma unroll
     for (int b = 0; b < kMaxBlk; ++b) {
-        const uint32_t blk = warp + b * kWarps;
+        const uint32_t blk = warp + b * nw;
         if (blk >= nblk_pad) break;
         const uint32_t c0 = blk * 256 + lane * 8;
         float v[8] = {ra[b][0].x, ra[b][0].y, ra[b][0].z, ra[b][0].w, ra[b][1].x, ra[b][1].y, ra[b][1].z, ra[b][1].w};
@@ -485,11 +488,11 @@ matvec_stream_kernel(const MatvecArgs a, const __grid_constant__ TensorMaps maps
     if (a.x_mode == MV_X_RMSNORM) {
         float t = 0.f;
 #pragma unroll
-        for (int w = 0; w < kWarps; ++w) t += red[w];   // same order in every thread
+        for (uint32_t w = 0; w < nw; ++w) t += red[w];   // same order in every thread
         inv_rms = 1.0f / sqrtf(t / (float)a.cols + a.eps);
     }
     if (a.xn_out != nullptr && blockIdx.x == 0) {   // the activation as f32, for layer-level checks
-        for (uint32_t c = tid; c < a.cols; c += kThreads) {
+        for (uint32_t c = tid; c < a.cols; c += blockDim.x) {
             float v = a.x[c];
             if (a.x_mode == MV_X_RMSNORM) v = v * inv_rms * a.wnorm[c];
             else if (a.x_mode == MV_X_SILU_MUL) v = (v / (1.0f + expf(-v))) * a.x2[c];
@@ -641,14 +644,21 @@ bool matvec_is_streaming(int fmt, uint32_t cols) {
     return (fmt == FMT_Q4_K || fmt == FMT_Q6_K) && cols >= 512 && cols % 256 == 0;
 }
 
-size_t matvec_smem_bytes(uint32_t cols, bool q4, bool q6, int *stages_out) {
+// Shared memory of a launch and its shape: as many warps as fit with two ring
+// stages each (more warps hide more latency of the issue-bound unpack loop than
+// a third stage does), then as many stages as still fit.
+size_t matvec_smem_bytes(uint32_t cols, bool q4, bool q6, int *stages_out, int *warps_out) {
     const size_t fixed = smem_fixed_bytes(cols, q4, q6) + 8 + 128;   // + alignment slack
     const size_t limit = 227 * 1024 - 1024;   // leave room for static shared memory
     const size_t slot = q6 ? kStage6 : kStage4;
+    int warps = kMaxWarps;
+    if (const char *e = getenv("FLB_MV_WARPS")) { const int w = atoi(e); if (w >= 1 && w <= kMaxWarps) warps = w; }
+    while (warps > kMinWarps && fixed + (size_t)warps * 2 * (8 + slot) > limit) --warps;
     int stages = 4;
-    while (stages > 1 && fixed + (size_t)kWarps * stages * (8 + slot) > limit) --stages;
+    while (stages > 1 && fixed + (size_t)warps * stages * (8 + slot) > limit) --stages;
     if (stages_out) *stages_out = stages;
-    return fixed + (size_t)kWarps * stages * (8 + slot);
+    if (warps_out) *warps_out = warps;
+    return fixed + (size_t)warps * stages * (8 + slot);
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
@@ -685,6 +695,24 @@ static cudaError_t encode_map(CUtensorMap *m, const MatvecTensor &t, uint32_t co
     return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
 }
 
+cudaError_t tensor_map_2d(CUtensorMap *m, uint32_t elem_bytes, const void *base, uint64_t dim0, uint64_t rows,
+                          uint64_t stride_bytes, uint32_t box0, uint32_t box_rows, bool swizzle128) {
+    if (!g_encode) {
+        const cudaError_t e = matvec_init();
+        if (e != cudaSuccess) return e;
+    }
+    const CUtensorMapDataType dt = elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_UINT16
+                                 : elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_UINT32 : CU_TENSOR_MAP_DATA_TYPE_UINT64;
+    const cuuint64_t gdim[2] = {dim0, rows};
+    const cuuint64_t gstride[1] = {stride_bytes};
+    const cuuint32_t box[2] = {box0, box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = g_encode(m, dt, 2, const_cast<void *>(base), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
+}
+
 // The streaming kernel assigns whole row quads to warps and needs no scratch.
 void matvec_scratch_need(const MatvecArgs &, int, size_t *scratch_floats, size_t *tickets) {
     *scratch_floats = 0;
@@ -703,7 +731,7 @@ cudaError_t launch_matvec(const MatvecArgs &a, int sms, cudaStream_t stream) {
         if (pitch < row_bytes(t.fmt, a.cols)) return cudaErrorInvalidValue;
         streaming = streaming && matvec_is_streaming(t.fmt, a.cols) && (((uintptr_t)t.w) & 15u) == 0 && (pitch & 15u) == 0;
         if (t.expert_id && (t.rows % kRowsPerStage != 0 || a.swiglu)) streaming = false;
-        streaming = streaming && a.cols <= 6u * 256u * kWarps && (((uintptr_t)a.x) & 15u) == 0 &&
+        streaming = streaming && a.cols <= 6u * 256u * kMinWarps && (((uintptr_t)a.x) & 15u) == 0 &&
                     (((uintptr_t)a.x2) & 15u) == 0 && (((uintptr_t)a.wnorm) & 15u) == 0;
         q4 = q4 || t.fmt == FMT_Q4_K;
         q6 = q6 || t.fmt == FMT_Q6_K;
@@ -716,8 +744,8 @@ cudaError_t launch_matvec(const MatvecArgs &a, int sms, cudaStream_t stream) {
         total_quads = (a.t[0].rows + 1) / 2;
     }
     if (streaming) {
-        int stages = 0;
-        const size_t smem = matvec_smem_bytes(a.cols, q4, q6, &stages);
+        int stages = 0, warps = 0;
+        const size_t smem = matvec_smem_bytes(a.cols, q4, q6, &stages, &warps);
         if (smem <= 227 * 1024 - 1024 && stages >= 2) {
             uint32_t grid = total_quads < (uint32_t)sms ? total_quads : (uint32_t)sms;
             TensorMaps maps;
@@ -726,7 +754,7 @@ cudaError_t launch_matvec(const MatvecArgs &a, int sms, cudaStream_t stream) {
                 const cudaError_t e = encode_map(&maps.m[i], a.t[i], a.cols, a.swiglu ? 2 : kRowsPerStage);
                 if (e != cudaSuccess) return e;
             }
-            return launch_kernel(matvec_stream_kernel, dim3(grid), dim3(kThreads), smem, stream, a.pdl != 0, a, maps,
+            return launch_kernel(matvec_stream_kernel, dim3(grid), dim3(warps * 32), smem, stream, a.pdl != 0, a, maps,
                                  total_quads, stages, q4 ? 1 : 0, q6 ? 1 : 0);
         }
     }
