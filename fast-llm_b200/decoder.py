@@ -33,6 +33,8 @@ class Decoder:
         self._peer_maps = []
 
     def close(self):
+        if self._h and not self.ctx._h:
+            self._h = C.c_void_p()   # the context is gone already (teardown order): nothing left to free safely
         if self._h:
             self.lib.fl_b200_decoder_destroy(self._h)
             self._h = C.c_void_p()
