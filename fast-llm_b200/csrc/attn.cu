@@ -107,13 +107,13 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_decode_kernel(const __gr
     if (tid == 0) trace_min(a.trace, 0);
     griddep_launch_dependents();
     // *pos was written at the end of the previous step (or is kv_len - 1 of a single call): stable here.
-    const uint32_t kv_len = a.pos ? (uint32_t)(*a.pos) + 1u : a.kv_len;
+    const uint32_t kv_len = a.pos ? (uint32_t)(*a.pos) + 1u : a.kv_len + b * a.kv_len_step;
     const uint32_t tiles_total = (kv_len + kTile - 1) / kTile;
     const uint32_t tps = (tiles_total + a.n_splits - 1) / a.n_splits;
     const uint32_t t0 = split * tps;
     const uint32_t t1 = min(t0 + tps, tiles_total);
     const uint32_t n_tiles = t1 > t0 ? t1 - t0 : 0;
-    const uint32_t row0 = (b * a.n_kv_head + hkv) * a.kv_stride;   // first row of this head in the 2-D view
+    const uint32_t row0 = ((a.shared_kv ? 0u : b) * a.n_kv_head + hkv) * a.kv_stride;   // first row of this head in the 2-D view
 
     if (tid == 0) {
         for (int s = 0; s < kStages; ++s) mbar_init(&sm.full[s], 1);
@@ -357,8 +357,8 @@ constexpr size_t kAttnSmemBytes = sizeof(AttnSmem) + 1024;   // + slack to align
 
 // K and V as 2-D f16 tensors [rows][128] for the TMA unit: box = 64 rows x 64 columns, 128-byte swizzle.
 cudaError_t attn_make_maps(AttnArgs &a) {
-    const uint64_t rows = (uint64_t)a.batch * a.n_kv_head * a.kv_stride;
-    if (a.batch_stride != (uint64_t)a.n_kv_head * a.kv_stride * kD) return cudaErrorInvalidValue;   // sequences are contiguous
+    const uint64_t rows = (uint64_t)(a.shared_kv ? 1u : a.batch) * a.n_kv_head * a.kv_stride;
+    if (!a.shared_kv && a.batch_stride != (uint64_t)a.n_kv_head * a.kv_stride * kD) return cudaErrorInvalidValue;   // sequences are contiguous
     cudaError_t e = tensor_map_2d(&a.kmap, /*elem_bytes=*/2, a.k, kD, rows, kD * 2, 64, kTile, /*swizzle128=*/true);
     if (e != cudaSuccess) return e;
     return tensor_map_2d(&a.vmap, 2, a.v, kD, rows, kD * 2, 64, kTile, true);

@@ -318,13 +318,13 @@ int fl_b200_matvec_host(fl_b200_ctx *c, int fmt, const void *w, uint32_t rows, u
 
 static int attn_impl(fl_b200_ctx *c, const float *q, const uint16_t *k, const uint16_t *v, uint32_t n_q,
                      uint32_t n_kv, uint32_t d, uint32_t kv_len, uint32_t kv_stride, uint32_t batch, float scale,
-                     float *out, const int32_t *pos_dev) {
+                     float *out, const int32_t *pos_dev, bool verify = false) {
     if (!q || !k || !v || !out) return set_err(FL_B200_ERR_ARG, "attn_decode: null pointer");
     if (d != 128) return set_err(FL_B200_ERR_ARG, "attn_decode: head_dim %u (only 128 is built)", d);
     if (n_kv == 0 || n_q != 4 * n_kv)
         return set_err(FL_B200_ERR_ARG, "attn_decode: %u query heads over %u KV heads (only groups of 4 are built)", n_q, n_kv);
     if (batch == 0) return set_err(FL_B200_ERR_ARG, "attn_decode: batch 0");
-    if (!pos_dev && (kv_len == 0 || kv_len > kv_stride))
+    if (!pos_dev && (kv_len == 0 || kv_len + (verify ? batch - 1 : 0) > kv_stride))
         return set_err(FL_B200_ERR_ARG, "attn_decode: kv_len %u outside 1..kv_stride %u", kv_len, kv_stride);
     if (((uintptr_t)k & 15u) || ((uintptr_t)v & 15u) || ((uintptr_t)q & 15u))
         return set_err(FL_B200_ERR_ARG, "attn_decode: q, k, v must be 16-byte aligned");
@@ -342,7 +342,9 @@ static int attn_impl(fl_b200_ctx *c, const float *q, const uint16_t *k, const ui
     a.n_q_head = n_q;
     a.n_kv_head = n_kv;
     a.batch = batch;
-    a.n_splits = attn_pick_splits(n_kv, batch, pos_dev ? kv_stride : kv_len, c->sms);
+    a.n_splits = attn_pick_splits(n_kv, batch, pos_dev ? kv_stride : kv_len + (verify ? batch - 1 : 0), c->sms);
+    a.kv_len_step = verify ? 1u : 0u;
+    a.shared_kv = verify ? 1u : 0u;
     a.scale = scale;
     a.status = c->status;
     const size_t need = attn_part_floats(n_q, batch, a.n_splits) * sizeof(float);
@@ -405,6 +407,15 @@ int fl_b200_attn_decode_static(fl_b200_ctx *c, const float *q, const uint16_t *k
                        "the fixed scratch holds %zu records and %u counters - use fl_b200_attn_decode",
                        records, (unsigned long long)n_kv * batch, attn_static_max_records(), attn_static_max_tickets());
     return cuda_err(e, "attn_decode_static launch");
+}
+
+// Draft verification (causal within the draft): query b of `n_draft` attends keys 0 .. base_len + b - 1 of
+// ONE shared cache, i.e. fl_op_attn_head called once per draft position with pos = base_len - 1 + b.
+int fl_b200_attn_verify(fl_b200_ctx *c, const float *q, const uint16_t *k, const uint16_t *v, uint32_t n_q,
+                        uint32_t n_kv, uint32_t d, uint32_t base_len, uint32_t kv_stride, uint32_t n_draft,
+                        float scale, float *out) {
+    if (!c) return set_err(FL_B200_ERR_ARG, "attn_verify: null context");
+    return attn_impl(c, q, k, v, n_q, n_kv, d, base_len, kv_stride, n_draft, scale, out, nullptr, true);
 }
 
 int fl_b200_attn_decode_host(fl_b200_ctx *c, const float *q_host, const uint16_t *k, const uint16_t *v,

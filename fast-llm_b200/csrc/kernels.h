@@ -81,6 +81,8 @@ struct AttnArgs {
     uint32_t *tickets;     // scratch: [batch][n_kv_head], zero before first use; self-resetting
     const int32_t *pos;    // device scalar: last valid position (kv_len = *pos + 1); nullptr -> kv_len
     uint32_t kv_len;       // used when pos == nullptr
+    uint32_t kv_len_step;  // sequence b attends kv_len + b * kv_len_step keys (draft verification: step 1)
+    uint32_t shared_kv;    // 1: all sequences read the same cache (batch_stride ignored)
     uint32_t kv_stride;    // positions allocated per head
     uint64_t batch_stride; // elements between sequences in k / v
     uint32_t n_q_head, n_kv_head, batch, n_splits;

@@ -123,6 +123,13 @@ int fl_b200_matvec_host(fl_b200_ctx *ctx, int fmt, const void *w_dev, uint32_t r
 int fl_b200_attn_decode(fl_b200_ctx *ctx, const float *q_dev, const uint16_t *k_dev, const uint16_t *v_dev,
                         uint32_t n_q_head, uint32_t n_kv_head, uint32_t head_dim, uint32_t kv_len,
                         uint32_t kv_stride, uint32_t batch, float scale, float *out_dev);
+/* Draft verification, causal within the draft (the speculative-verify step):
+ * n_draft queries q[b][n_q_head][128] against ONE cache [n_kv_head][kv_stride][128];
+ * query b attends keys 0 .. base_len + b - 1 (the draft's own K/V rows are in
+ * the cache already), i.e. fl_op_attn_head with pos = base_len - 1 + b per query. */
+int fl_b200_attn_verify(fl_b200_ctx *ctx, const float *q_dev, const uint16_t *k_dev, const uint16_t *v_dev,
+                        uint32_t n_q_head, uint32_t n_kv_head, uint32_t head_dim, uint32_t base_len,
+                        uint32_t kv_stride, uint32_t n_draft, float scale, float *out_dev);
 /* fl_b200_attn_decode for callers that must not allocate device memory at call
  * time. It has no counterpart in the reference, whose operators keep their
  * temporaries in the caller's buffers. The split-KV scratch is a fixed array in
