@@ -35,16 +35,17 @@ __global__ void trace_init_kernel(unsigned long long *t, uint32_t n) {
     if (i < n * 4) t[i] = (i & 2u) ? 0ull : ~0ull;
 }
 
-// After a step: token <- argmax, history[count++] <- argmax, pos += 1.
+// After a step: history[count++] <- argmax, pos += 1, and the next input token: the argmax (greedy
+// decoding) or, while a draft is being verified (*use_forced != 0), the draft's token forced[count].
 __global__ void advance_kernel(int32_t *token, const int32_t *next, int32_t *pos, int32_t *hist,
-                               uint32_t *hist_n, uint32_t hist_cap) {
+                               uint32_t *hist_n, uint32_t hist_cap, const uint32_t *use_forced, const int32_t *forced) {
     griddep_launch_dependents();
     griddep_wait();
     if (threadIdx.x == 0 && blockIdx.x == 0) {
         const int32_t t = *next;
-        *token = t;
         const uint32_t k = *hist_n;
         if (k < hist_cap) hist[k] = t;
+        *token = (*use_forced && k < hist_cap) ? forced[k] : t;
         *hist_n = k + 1;
         *pos = *pos + 1;
     }
@@ -71,7 +72,8 @@ struct fl_b200_decoder {
     const float *out_norm = nullptr;
     std::vector<__half *> kc, vc;
     // device state
-    int32_t *d_token = nullptr, *d_next = nullptr, *d_pos = nullptr, *d_hist = nullptr;
+    int32_t *d_token = nullptr, *d_next = nullptr, *d_pos = nullptr, *d_hist = nullptr, *d_forced = nullptr;
+    uint32_t *d_use_forced = nullptr;
     uint32_t *d_hist_n = nullptr;
     float *d_margin = nullptr;
     uint32_t hist_cap = 4096;
@@ -202,7 +204,7 @@ static int enqueue_step(fl_b200_decoder *d, cudaStream_t s, uint32_t *n_launch, 
     }
     if (mask == K_ALL) {   // state only advances in the real step
         CK(launch_kernel(advance_kernel, dim3(1), dim3(32), 0, s, kPdl != 0, d->d_token, d->d_next, d->d_pos, d->d_hist,
-                         d->d_hist_n, d->hist_cap)); ++n;
+                         d->d_hist_n, d->hist_cap, (const uint32_t *)d->d_use_forced, (const int32_t *)d->d_forced)); ++n;
     }
     if (n_launch) *n_launch = n;
     return FL_B200_OK;
@@ -263,8 +265,10 @@ int fl_b200_decoder_create_tp(fl_b200_ctx *ctx, const fl_b200_llama_cfg *cfg, ui
     d->d_pos = d->d_token + 2;
     d->d_hist_n = (uint32_t *)(d->d_token + 3);
     d->d_margin = (float *)(d->d_token + 4);
+    d->d_use_forced = (uint32_t *)(d->d_token + 5);
     CK(cudaMemsetAsync(d->d_token, 0, 64, ctx->stream));
     CK(cudaMalloc(&d->d_hist, d->hist_cap * sizeof(int32_t)));
+    CK(cudaMalloc(&d->d_forced, d->hist_cap * sizeof(int32_t)));
     CK(cudaMalloc(&d->xa, c.n_embd * 4));
     CK(cudaMalloc(&d->xb, c.n_embd * 4));
     CK(cudaMalloc(&d->q, QD * 4));
@@ -301,7 +305,7 @@ void fl_b200_decoder_destroy(fl_b200_decoder *d) {
     if (d->graph) cudaGraphDestroy(d->graph);
     for (auto p : d->kc) cudaFree(p);
     for (auto p : d->vc) cudaFree(p);
-    cudaFree(d->d_token); cudaFree(d->d_hist); cudaFree(d->xa); cudaFree(d->xb); cudaFree(d->q);
+    cudaFree(d->d_token); cudaFree(d->d_hist); cudaFree(d->d_forced); cudaFree(d->xa); cudaFree(d->xb); cudaFree(d->q);
     cudaFree(d->k); cudaFree(d->v); cudaFree(d->att); cudaFree(d->g); cudaFree(d->u); cudaFree(d->logits);
     cudaFree(d->xn_final); cudaFree(d->part); cudaFree(d->tickets);
     cudaFree(d->top3); cudaFree(d->comm); cudaFree(d->comm_state); cudaFree(d->partial);
@@ -473,6 +477,40 @@ int fl_b200_decoder_run(fl_b200_decoder *d, int32_t first_token, uint32_t n, int
     CK(cudaMemcpyAsync(tokens_host, d->d_hist, (size_t)n * 4, cudaMemcpyDeviceToHost, s));
     CK(cudaStreamSynchronize(s));
     d->n_past += (int32_t)n;
+    return check_dev_status(d);
+}
+
+// Greedy verification of a draft (the speculative-decoding verify step, tools/decode_main.cpp:329-400
+// of the reference): the model is run on first_token, draft[0], ..., draft[n_draft-1] teacher-forced
+// from position n_past; draft[i] is accepted while it equals the model's greedy token after the
+// previous input. Returns the number of accepted draft tokens and the model's own next token after
+// the last accepted one; n_past moves past the accepted tokens only (the cache rows of rejected
+// positions are overwritten by later steps). The positions are computed one after the other with
+// the single-token launch plan (no host round trip in between).
+int fl_b200_decoder_verify(fl_b200_decoder *d, int32_t first_token, const int32_t *draft, uint32_t n_draft,
+                           uint32_t *n_accepted_out, int32_t *next_token_out) {
+    if (!d || !draft || !n_accepted_out || !next_token_out) return set_err(FL_B200_ERR_ARG, "decoder_verify: null");
+    if (!d->finalized) return set_err(FL_B200_ERR_STATE, "decoder_verify: finalize first");
+    const uint32_t n = n_draft + 1;   // inputs: the last accepted token and the draft
+    if (n_draft == 0 || n > d->hist_cap) return set_err(FL_B200_ERR_ARG, "decoder_verify: draft length %u outside 1..%u", n_draft, d->hist_cap - 1);
+    if ((uint64_t)d->n_past + n > d->c.max_kv) return set_err(FL_B200_ERR_STATE, "decoder_verify: kv full (%d + %u > %u)", d->n_past, n, d->c.max_kv);
+    if (first_token < 0 || (uint32_t)first_token >= d->c.n_vocab) return set_err(FL_B200_ERR_ARG, "decoder_verify: token outside the vocabulary");
+    for (uint32_t i = 0; i < n_draft; ++i)
+        if (draft[i] < 0 || (uint32_t)draft[i] >= d->c.n_vocab) return set_err(FL_B200_ERR_ARG, "decoder_verify: draft token %u outside the vocabulary", i);
+    cudaStream_t s = d->ctx->stream;
+    std::vector<int32_t> got(n);
+    CK(cudaMemcpyAsync(d->d_forced, draft, (size_t)n_draft * 4, cudaMemcpyHostToDevice, s));   // forced[k] follows input k
+    d->h_pin[0] = first_token; d->h_pin[1] = 0; d->h_pin[2] = d->n_past; d->h_pin[3] = 0; d->h_pin[4] = 0; d->h_pin[5] = 1;
+    CK(cudaMemcpyAsync(d->d_token, d->h_pin, 24, cudaMemcpyHostToDevice, s));
+    for (uint32_t i = 0; i < n; ++i) CK(cudaGraphLaunch(d->exec, s));
+    CK(cudaMemcpyAsync(got.data(), d->d_hist, (size_t)n * 4, cudaMemcpyDeviceToHost, s));
+    CK(cudaMemsetAsync(d->d_use_forced, 0, 4, s));
+    CK(cudaStreamSynchronize(s));
+    uint32_t acc = 0;
+    while (acc < n_draft && got[acc] == draft[acc]) ++acc;
+    *n_accepted_out = acc;
+    *next_token_out = got[acc];
+    d->n_past += (int32_t)acc + 1;
     return check_dev_status(d);
 }
 

@@ -88,6 +88,14 @@ class Decoder:
                                               C.c_void_p(toks.ctypes.data)))
         return toks
 
+    def verify(self, first_token, draft):
+        """Greedy verification of a draft: (number of accepted draft tokens, the model's next token)."""
+        arr = (C.c_int32 * len(draft))(*[int(t) for t in draft])
+        acc, nxt = C.c_uint32(), C.c_int32()
+        capi._ck(self.lib.fl_b200_decoder_verify(self._h, C.c_int32(int(first_token)), arr, C.c_uint32(len(draft)),
+                                                 C.byref(acc), C.byref(nxt)))
+        return acc.value, nxt.value
+
     def n_past(self):
         v = C.c_int32()
         capi._ck(self.lib.fl_b200_decoder_n_past(self._h, C.byref(v)))

@@ -294,6 +294,13 @@ int fl_b200_decoder_step(fl_b200_decoder *dec, int32_t token, int32_t *next_out)
 /* Runs `n` steps feeding each step's argmax back on the device (no host round
  * trip between steps); writes the n produced tokens to tokens_host. */
 int fl_b200_decoder_run(fl_b200_decoder *dec, int32_t first_token, uint32_t n, int32_t *tokens_host);
+/* Greedy verification of a draft (speculative decoding): runs the model on
+ * first_token, draft[0..n_draft-1] teacher-forced from position n_past and
+ * accepts draft[i] while it equals the model's greedy token; returns how many
+ * were accepted and the model's own token after the last accepted one. n_past
+ * advances by n_accepted + 1. */
+int fl_b200_decoder_verify(fl_b200_decoder *dec, int32_t first_token, const int32_t *draft_host, uint32_t n_draft,
+                           uint32_t *n_accepted_out, int32_t *next_token_out);
 /* After a step: logits (n_vocab floats) and the top1 - top2 margin. */
 int fl_b200_decoder_logits(fl_b200_decoder *dec, float *logits_host);
 int fl_b200_decoder_margin(fl_b200_decoder *dec, float *margin_out);

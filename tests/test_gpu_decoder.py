@@ -131,6 +131,41 @@ def test_run_equals_stepwise_and_rewind(ctx, checker):
     dec.close(); orc.close()
 
 
+def test_verify_draft_greedy_acceptance(ctx, checker):
+    """Draft verification (configuration 3's acceptance rule: greedy-argmax equality): the accepted
+    prefix and the corrected token equal what token-by-token decoding gives, on the device and on the oracle."""
+    dec, orc = build_pair(ctx, checker, SMALL, seed=7, n_prefill=20)
+    first = 5
+    greedy = [int(t) for t in dec.run(first, 7)]                 # a0 .. a6 after inputs first, a0, .., a5
+    # all of the draft accepted: next token is the model's continuation
+    dec.rewind_to(20)
+    acc, nxt = dec.verify(first, greedy[:5])
+    assert (acc, nxt) == (5, greedy[5]) and dec.n_past() == 26
+    # a wrong token in the middle: the prefix before it is accepted, the model's own token is returned
+    dec.rewind_to(20)
+    wrong = (greedy[3] + 1) % SMALL["n_vocab"]
+    acc, nxt = dec.verify(first, greedy[:3] + [wrong, greedy[4]])
+    assert (acc, nxt) == (3, greedy[3]) and dec.n_past() == 24
+    # decoding goes on from there as if nothing had been drafted
+    assert dec.step(nxt) == greedy[4]
+    # first draft token wrong: nothing accepted
+    dec.rewind_to(20)
+    acc, nxt = dec.verify(first, [wrong if wrong != greedy[0] else (wrong + 1) % SMALL["n_vocab"]] * 2)
+    assert (acc, nxt) == (0, greedy[0]) and dec.n_past() == 21
+    # the oracle accepts the same prefix (teacher-forced greedy tokens)
+    tok, want = first, []
+    for _ in range(4):
+        tok = orc.step(tok)
+        want.append(tok)
+    if want == greedy[:4]:
+        dec.rewind_to(20)
+        acc, nxt = dec.verify(first, want[:3])
+        assert (acc, nxt) == (3, want[3])
+    with pytest.raises(capi.Fl200Error):
+        dec.verify(first, [])
+    dec.close(); orc.close()
+
+
 def test_kv_full_is_reported(ctx, checker):
     cfg = dict(SMALL, max_kv=12)
     dec, orc = build_pair(ctx, checker, cfg, seed=6, n_prefill=11)
