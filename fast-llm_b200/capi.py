@@ -24,7 +24,8 @@ SYMBOLS = [
     "fl_b200_device_status", "fl_b200_sm_count", "fl_b200_stream", "fl_b200_malloc", "fl_b200_free",
     "fl_b200_upload", "fl_b200_download", "fl_b200_memset", "fl_b200_ipc_export", "fl_b200_ipc_open", "fl_b200_ipc_close", "fl_b200_timer_start", "fl_b200_timer_stop",
     "fl_b200_dequant", "fl_b200_matvec", "fl_b200_matvec_assign", "fl_b200_matvec_expert", "fl_b200_matvec_pitched", "fl_b200_matvec_host",
-    "fl_b200_attn_decode", "fl_b200_attn_verify", "fl_b200_attn_decode_static", "fl_b200_attn_decode_host", "fl_b200_rmsnorm", "fl_b200_add2",
+    "fl_b200_attn_decode", "fl_b200_attn_decode_lse", "fl_b200_seqpar_create", "fl_b200_seqpar_destroy",
+    "fl_b200_seqpar_comm", "fl_b200_seqpar_set_peers", "fl_b200_seqpar_combine", "fl_b200_attn_verify", "fl_b200_attn_decode_static", "fl_b200_attn_decode_host", "fl_b200_rmsnorm", "fl_b200_add2",
     "fl_b200_silu_mul", "fl_b200_router_sel", "fl_b200_wmerge", "fl_b200_rope_kv_append", "fl_b200_argmax", "fl_b200_exec_task",
     "fl_b200_decoder_create", "fl_b200_decoder_create_tp", "fl_b200_decoder_comm", "fl_b200_decoder_set_peers",
     "fl_b200_decoder_destroy", "fl_b200_decoder_set_layer_tensor",
@@ -83,6 +84,7 @@ def load():
     lib.fl_b200_stream.restype = C.c_void_p
     lib.fl_b200_destroy.restype = None
     lib.fl_b200_decoder_destroy.restype = None
+    lib.fl_b200_seqpar_destroy.restype = None
     _lib = lib
     return lib
 
@@ -184,6 +186,11 @@ class Context:
         _ck(self.lib.fl_b200_attn_decode(self._h, _p(q), _p(k), _p(v), C.c_uint32(n_q_head),
                                          C.c_uint32(n_kv_head), C.c_uint32(head_dim), C.c_uint32(kv_len),
                                          C.c_uint32(kv_stride), C.c_uint32(batch), C.c_float(scale), _p(out)))
+
+    def attn_decode_lse(self, q, k, v, n_q_head, n_kv_head, head_dim, kv_len, kv_stride, batch, scale, out, lse):
+        _ck(self.lib.fl_b200_attn_decode_lse(self._h, _p(q), _p(k), _p(v), C.c_uint32(n_q_head), C.c_uint32(n_kv_head),
+                                             C.c_uint32(head_dim), C.c_uint32(kv_len), C.c_uint32(kv_stride),
+                                             C.c_uint32(batch), C.c_float(scale), _p(out), _p(lse)))
 
     def attn_verify(self, q, k, v, n_q_head, n_kv_head, head_dim, base_len, kv_stride, n_draft, scale, out):
         """Causal-within-draft attention: query b sees keys 0 .. base_len + b - 1 of one shared cache."""

@@ -344,6 +344,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_decode_kernel(const __gr
         const float inv = 1.0f / L;
         acc.x *= inv; acc.y *= inv; acc.z *= inv; acc.w *= inv;
         reinterpret_cast<float4 *>(a.out + hq * kD)[lane] = acc;
+        if (a.lse_out && lane == 0) a.lse_out[hq] = make_float2(mx, L);
     }
     if (tid == 0) {
         a.tickets[b * a.n_kv_head + hkv] = 0;   // ready for the next launch

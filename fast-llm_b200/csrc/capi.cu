@@ -318,7 +318,7 @@ int fl_b200_matvec_host(fl_b200_ctx *c, int fmt, const void *w, uint32_t rows, u
 
 static int attn_impl(fl_b200_ctx *c, const float *q, const uint16_t *k, const uint16_t *v, uint32_t n_q,
                      uint32_t n_kv, uint32_t d, uint32_t kv_len, uint32_t kv_stride, uint32_t batch, float scale,
-                     float *out, const int32_t *pos_dev, bool verify = false) {
+                     float *out, const int32_t *pos_dev, bool verify = false, float *lse_out = nullptr) {
     if (!q || !k || !v || !out) return set_err(FL_B200_ERR_ARG, "attn_decode: null pointer");
     if (d != 128) return set_err(FL_B200_ERR_ARG, "attn_decode: head_dim %u (only 128 is built)", d);
     if (n_kv == 0 || n_q != 4 * n_kv)
@@ -343,6 +343,7 @@ static int attn_impl(fl_b200_ctx *c, const float *q, const uint16_t *k, const ui
     a.n_kv_head = n_kv;
     a.batch = batch;
     a.n_splits = attn_pick_splits(n_kv, batch, pos_dev ? kv_stride : kv_len + (verify ? batch - 1 : 0), c->sms);
+    a.lse_out = reinterpret_cast<float2 *>(lse_out);
     a.kv_len_step = verify ? 1u : 0u;
     a.shared_kv = verify ? 1u : 0u;
     a.scale = scale;
@@ -416,6 +417,79 @@ int fl_b200_attn_verify(fl_b200_ctx *c, const float *q, const uint16_t *k, const
                         float scale, float *out) {
     if (!c) return set_err(FL_B200_ERR_ARG, "attn_verify: null context");
     return attn_impl(c, q, k, v, n_q, n_kv, d, base_len, kv_stride, n_draft, scale, out, nullptr, true);
+}
+
+// ---- sequence-parallel attention: every rank attends its slice of the keys, then the ranks' records merge ----
+int fl_b200_attn_decode_lse(fl_b200_ctx *c, const float *q, const uint16_t *k, const uint16_t *v, uint32_t n_q,
+                            uint32_t n_kv, uint32_t d, uint32_t kv_len, uint32_t kv_stride, uint32_t batch,
+                            float scale, float *out, float *lse_out) {
+    if (!c || !lse_out) return set_err(FL_B200_ERR_ARG, "attn_decode_lse: null");
+    if (((uintptr_t)lse_out & 7u) != 0) return set_err(FL_B200_ERR_ARG, "attn_decode_lse: lse_out must be 8-byte aligned");
+    return attn_impl(c, q, k, v, n_q, n_kv, d, kv_len, kv_stride, batch, scale, out, nullptr, false, lse_out);
+}
+
+struct fl_b200_seqpar {
+    fl_b200_ctx *ctx = nullptr;
+    uint32_t rank = 0, world = 1, max_records = 0;
+    uint8_t *buf = nullptr;
+    uint8_t *peers[kCommMaxRanks] = {};
+    bool peers_set = false;
+    uint32_t *epoch = nullptr;
+};
+
+int fl_b200_seqpar_create(fl_b200_ctx *c, uint32_t rank, uint32_t world, uint32_t max_records, fl_b200_seqpar **out) {
+    if (!c || !out) return set_err(FL_B200_ERR_ARG, "seqpar_create: null");
+    if (world == 0 || world > kCommMaxRanks || rank >= world || max_records == 0 || max_records > (1u << 16))
+        return set_err(FL_B200_ERR_ARG, "seqpar_create: rank %u of %u, %u records", rank, world, max_records);
+    fl_b200_seqpar *h = new fl_b200_seqpar();
+    h->ctx = c; h->rank = rank; h->world = world; h->max_records = max_records;
+    CK(cudaSetDevice(c->device));
+    CK(cudaMalloc(&h->buf, lse_buffer_bytes(max_records)));
+    CK(cudaMemsetAsync(h->buf, 0, lse_buffer_bytes(max_records), c->stream));
+    CK(cudaMalloc(&h->epoch, kLseChunks * 4));
+    CK(cudaMemsetAsync(h->epoch, 0, kLseChunks * 4, c->stream));
+    CK(cudaStreamSynchronize(c->stream));
+    *out = h;
+    return FL_B200_OK;
+}
+
+void fl_b200_seqpar_destroy(fl_b200_seqpar *h) {
+    if (!h) return;
+    cudaSetDevice(h->ctx->device);
+    cudaStreamSynchronize(h->ctx->stream);
+    cudaFree(h->buf);
+    cudaFree(h->epoch);
+    delete h;
+}
+
+int fl_b200_seqpar_comm(fl_b200_seqpar *h, void **buf, size_t *bytes) {
+    if (!h || !buf || !bytes) return set_err(FL_B200_ERR_ARG, "seqpar_comm: null");
+    *buf = h->buf;
+    *bytes = lse_buffer_bytes(h->max_records);
+    return FL_B200_OK;
+}
+
+int fl_b200_seqpar_set_peers(fl_b200_seqpar *h, void *const *bufs, uint32_t n) {
+    if (!h || !bufs || n != h->world) return set_err(FL_B200_ERR_ARG, "seqpar_set_peers: need %u buffers", h ? h->world : 0);
+    for (uint32_t p = 0; p < n; ++p) {
+        if (!bufs[p]) return set_err(FL_B200_ERR_ARG, "seqpar_set_peers: buffer of rank %u is null", p);
+        h->peers[p] = (uint8_t *)bufs[p];
+    }
+    if (h->peers[h->rank] != h->buf) return set_err(FL_B200_ERR_ARG, "seqpar_set_peers: entry %u must be this rank's own buffer", h->rank);
+    h->peers_set = true;
+    return FL_B200_OK;
+}
+
+int fl_b200_seqpar_combine(fl_b200_seqpar *h, const float *out_local, const float *lse_local, uint32_t n, float *out) {
+    if (!h || !out_local || !lse_local || !out) return set_err(FL_B200_ERR_ARG, "seqpar_combine: null");
+    if (!h->peers_set) return set_err(FL_B200_ERR_STATE, "seqpar_combine: set the peers first");
+    if (n == 0 || n > h->max_records) return set_err(FL_B200_ERR_ARG, "seqpar_combine: %u records (at most %u)", n, h->max_records);
+    LseCombineArgs a{};
+    for (uint32_t p = 0; p < h->world; ++p) a.peers[p] = h->peers[p];
+    a.out_local = out_local; a.lse_local = reinterpret_cast<const float2 *>(lse_local); a.out = out;
+    a.n = n; a.max_records = h->max_records; a.rank = h->rank; a.world = h->world;
+    a.epoch = h->epoch; a.status = h->ctx->status;
+    return cuda_err(launch_lse_combine(a, h->ctx->stream), "lse combine launch");
 }
 
 int fl_b200_attn_decode_host(fl_b200_ctx *c, const float *q_host, const uint16_t *k, const uint16_t *v,

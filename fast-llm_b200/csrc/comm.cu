@@ -156,7 +156,74 @@ __global__ void __launch_bounds__(32) argmax_exchange_kernel(const TopExchangeAr
     }
 }
 
+// Merge of the ranks' attention records (sequence-parallel attention). Record i of rank r: context
+// o_r[128] normalised over the rank's own keys, m_r = max score, l_r = sum exp(score - m_r). With
+// M = max_r m_r and w_r = l_r * exp(m_r - M): out = sum_r w_r o_r / sum_r w_r, ranks in ascending
+// order (identical bits on every rank). CTA c handles records c, c + kLseChunks, ...; one warp per
+// record, lane <-> 4 dims. Same push / flag / bounded wait protocol as the all-reduce above.
+__global__ void __launch_bounds__(128) lse_combine_kernel(const LseCombineArgs a) {
+    __shared__ uint32_t ok_s;
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5, chunk = blockIdx.x;
+    if (tid == 0) ok_s = 1u;
+    const uint32_t e = next_epoch(a.epoch + chunk), slot = e & 1u;
+    const size_t rec_floats = 132;
+    const size_t slot_floats = (size_t)a.world * a.max_records * rec_floats;
+    auto rec_of = [&](uint8_t *base, uint32_t r, uint32_t i) {
+        return reinterpret_cast<float *>(base) + (size_t)slot * slot_floats + ((size_t)r * a.max_records + i) * rec_floats;
+    };
+    auto flag_of2 = [&](uint8_t *base, uint32_t r) {
+        return reinterpret_cast<uint32_t *>(base + 2 * slot_floats * 4) + ((size_t)slot * a.world + r) * kLseChunks + chunk;
+    };
+    for (uint32_t i = chunk + warp * kLseChunks; i < a.n; i += kLseChunks * 4) {
+        const float4 o = *reinterpret_cast<const float4 *>(a.out_local + (size_t)i * 128 + lane * 4);
+        const float2 ml = a.lse_local[i];
+        for (uint32_t k = 0; k < a.world; ++k) {
+            const uint32_t p = (a.rank + k) % a.world;
+            float *dst = rec_of(a.peers[p], a.rank, i);
+            *reinterpret_cast<float4 *>(dst + lane * 4) = o;
+            if (lane == 0) *reinterpret_cast<float2 *>(dst + 128) = ml;
+        }
+    }
+    __syncthreads();
+    if (tid < a.world) {
+        st_release_sys(flag_of2(a.peers[tid], a.rank), e);
+        if (!wait_flag(flag_of2(a.peers[a.rank], tid), e, a.status)) ok_s = 0u;
+    }
+    __syncthreads();
+    if (!ok_s) return;
+    for (uint32_t i = chunk + warp * kLseChunks; i < a.n; i += kLseChunks * 4) {
+        float M = -INFINITY;
+        for (uint32_t r = 0; r < a.world; ++r) M = fmaxf(M, __ldcg(rec_of(a.peers[a.rank], r, i) + 128));
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        float W = 0.f;
+        for (uint32_t r = 0; r < a.world; ++r) {
+            const float *rec = rec_of(a.peers[a.rank], r, i);
+            const float m = __ldcg(rec + 128), l = __ldcg(rec + 129);
+            const float w = (m == -INFINITY || l == 0.f) ? 0.f : l * expf(m - M);
+            const float4 o = __ldcg(reinterpret_cast<const float4 *>(rec) + lane);
+            if (w != 0.f) {   // a rank without keys contributes nothing (its context may be undefined)
+                acc.x = fmaf(o.x, w, acc.x); acc.y = fmaf(o.y, w, acc.y);
+                acc.z = fmaf(o.z, w, acc.z); acc.w = fmaf(o.w, w, acc.w);
+            }
+            W += w;
+        }
+        const float inv = 1.0f / W;
+        *reinterpret_cast<float4 *>(a.out + (size_t)i * 128 + lane * 4) = make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
+    }
+}
+
 } // namespace
+
+size_t lse_buffer_bytes(uint32_t max_records) {
+    return (size_t)2 * kCommMaxRanks * max_records * 132 * 4 + (size_t)2 * kCommMaxRanks * kLseChunks * 4;
+}
+
+cudaError_t launch_lse_combine(const LseCombineArgs &a, cudaStream_t stream) {
+    if (a.world < 1 || a.world > kCommMaxRanks || a.rank >= a.world || a.n == 0 || a.n > a.max_records)
+        return cudaErrorInvalidValue;
+    lse_combine_kernel<<<kLseChunks, 128, 0, stream>>>(a);
+    return cudaGetLastError();
+}
 
 size_t comm_buffer_bytes(void) { return kCommBytes; }
 

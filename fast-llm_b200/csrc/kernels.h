@@ -93,6 +93,7 @@ struct AttnArgs {
     // Fused RoPE + KV append (the decoder's launch plan): q arrives un-rotated; rope_k / rope_v are this
     // token's k and v ([batch][n_kv_head][128] f32, k un-rotated); the kernel rotates q and k by the angle
     // of position *pos and appends k, v (f16) at row *pos of k_append / v_append (the same arrays as k, v).
+    float2 *lse_out;                // optional [batch][n_q_head]: (max score, sum of exp(score - max)) of each head
     const float *rope_k, *rope_v;   // nullptr: q is already rotated and the cache is complete
     __half *k_append, *v_append;
     float theta_scale;              // freq_base^(-2/128)
@@ -141,6 +142,20 @@ struct TopExchangeArgs {
     CommState st;
     uint32_t *status;
 };
+// Sequence-parallel attention: every rank attended its slice of the keys and holds, per (sequence,
+// query head) record, the normalised context and (max, sum); the exchange merges the ranks' records.
+struct LseCombineArgs {
+    uint8_t *peers[kCommMaxRanks];   // exchange buffers: [2 slots][world][max_records][132] f32, then flags [2][world][kLseChunks]
+    const float *out_local;          // [n][128]
+    const float2 *lse_local;         // [n]
+    float *out;                      // [n][128]
+    uint32_t n, max_records, rank, world;
+    uint32_t *epoch;                 // kLseChunks device counters
+    uint32_t *status;
+};
+constexpr uint32_t kLseChunks = 32;
+size_t lse_buffer_bytes(uint32_t max_records);
+cudaError_t launch_lse_combine(const LseCombineArgs &a, cudaStream_t stream);
 size_t comm_buffer_bytes(void);
 cudaError_t launch_allreduce_resid(const AllReduceArgs &a, cudaStream_t stream, bool pdl);
 cudaError_t launch_argmax_exchange(const TopExchangeArgs &a, cudaStream_t stream, bool pdl);

@@ -85,6 +85,20 @@ def merge_top(records):
     return i, b - s
 
 
+def merge_lse(records):
+    """Host restatement of the cross-rank attention merge: records in rank order, each
+    (context[128] normalised over the rank's keys, max score, sum of exp(score - max));
+    returns the context over all keys."""
+    import numpy as np
+    M = max(m for _, m, _ in records)
+    acc, W = np.zeros_like(np.asarray(records[0][0], dtype=np.float64)), 0.0
+    for o, m, l in records:
+        w = 0.0 if (l == 0 or m == float("-inf")) else l * np.exp(m - M)
+        acc += w * np.asarray(o, dtype=np.float64)
+        W += w
+    return acc / W
+
+
 def connect(dec, dist, group=None):
     """Maps every rank's exchange buffer into this process and hands the pointers
     to the decoder. `dist` is torch.distributed with an initialised process group
@@ -111,3 +125,46 @@ def connect(dec, dist, group=None):
     capi._ck(lib.fl_b200_decoder_set_peers(dec._h, ptrs, C.c_uint32(world)))
     dec._peer_maps = opened
     return opened
+
+
+class SeqParallel:
+    """Cross-GPU merge of sequence-parallel decode attention (the long-context
+    configuration): every rank attends its contiguous slice of the keys with
+    Context.attn_decode_lse, then combine() merges the ranks' (context, max, sum)
+    records through peer memory; all ranks get identical results."""
+
+    def __init__(self, ctx, dist, max_records, group=None):
+        self.ctx, self.lib = ctx, ctx.lib
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self._h = C.c_void_p()
+        capi._ck(self.lib.fl_b200_seqpar_create(ctx._h, C.c_uint32(self.rank), C.c_uint32(self.world),
+                                                C.c_uint32(max_records), C.byref(self._h)))
+        buf, nbytes = C.c_void_p(), C.c_size_t()
+        capi._ck(self.lib.fl_b200_seqpar_comm(self._h, C.byref(buf), C.byref(nbytes)))
+        handle = (C.c_uint8 * 64)()
+        capi._ck(self.lib.fl_b200_ipc_export(ctx._h, buf, handle))
+        handles = [None] * self.world
+        dist.all_gather_object(handles, bytes(handle), group=group)
+        ptrs = (C.c_void_p * self.world)()
+        self._maps = []
+        for r in range(self.world):
+            if r == self.rank:
+                ptrs[r] = buf.value
+            else:
+                p = C.c_void_p()
+                capi._ck(self.lib.fl_b200_ipc_open(ctx._h, (C.c_uint8 * 64).from_buffer_copy(handles[r]), C.byref(p)))
+                ptrs[r] = p.value
+                self._maps.append(p.value)
+        capi._ck(self.lib.fl_b200_seqpar_set_peers(self._h, ptrs, C.c_uint32(self.world)))
+
+    def combine(self, out_local, lse_local, n_records, out):
+        capi._ck(self.lib.fl_b200_seqpar_combine(self._h, capi._p(out_local), capi._p(lse_local),
+                                                 C.c_uint32(n_records), capi._p(out)))
+
+    def close(self):
+        if self._h and self.ctx._h:
+            for p in self._maps:
+                self.lib.fl_b200_ipc_close(self.ctx._h, C.c_void_p(p))
+            self.lib.fl_b200_seqpar_destroy(self._h)
+        self._h = C.c_void_p()
+        self._maps = []

@@ -50,6 +50,7 @@ enum {
 
 typedef struct fl_b200_ctx fl_b200_ctx;
 typedef struct fl_b200_decoder fl_b200_decoder;
+typedef struct fl_b200_seqpar fl_b200_seqpar;
 
 int fl_b200_abi_version(void);
 const char *fl_b200_last_error(void);
@@ -130,6 +131,24 @@ int fl_b200_attn_decode(fl_b200_ctx *ctx, const float *q_dev, const uint16_t *k_
 int fl_b200_attn_verify(fl_b200_ctx *ctx, const float *q_dev, const uint16_t *k_dev, const uint16_t *v_dev,
                         uint32_t n_q_head, uint32_t n_kv_head, uint32_t head_dim, uint32_t base_len,
                         uint32_t kv_stride, uint32_t n_draft, float scale, float *out_dev);
+/* Sequence-parallel decode attention over the GPUs of one box (the long-context
+ * configuration: every rank holds a contiguous slice of the keys; the reference
+ * has no counterpart). fl_b200_attn_decode_lse is fl_b200_attn_decode over the
+ * rank's own keys that also returns, per (sequence, query head), lse_out = (max
+ * score, sum of exp(score - max)) [batch][n_q_head][2]. fl_b200_seqpar_combine
+ * merges the ranks' (context, max, sum) records through peer memory (same
+ * protocol as the tensor-parallel all-reduce: push, release flag, bounded wait)
+ * in rank order, so every rank gets identical bits. Set-up like the decoder's:
+ * create, export fl_b200_seqpar_comm's buffer, open the peers', set_peers. */
+int fl_b200_attn_decode_lse(fl_b200_ctx *ctx, const float *q_dev, const uint16_t *k_dev, const uint16_t *v_dev,
+                            uint32_t n_q_head, uint32_t n_kv_head, uint32_t head_dim, uint32_t kv_len,
+                            uint32_t kv_stride, uint32_t batch, float scale, float *out_dev, float *lse_out_dev);
+int fl_b200_seqpar_create(fl_b200_ctx *ctx, uint32_t rank, uint32_t world, uint32_t max_records, fl_b200_seqpar **out);
+void fl_b200_seqpar_destroy(fl_b200_seqpar *h);
+int fl_b200_seqpar_comm(fl_b200_seqpar *h, void **buf_dev_out, size_t *bytes_out);
+int fl_b200_seqpar_set_peers(fl_b200_seqpar *h, void *const *bufs_dev, uint32_t n);
+int fl_b200_seqpar_combine(fl_b200_seqpar *h, const float *out_local_dev, const float *lse_local_dev,
+                           uint32_t n_records, float *out_dev);
 /* fl_b200_attn_decode for callers that must not allocate device memory at call
  * time. It has no counterpart in the reference, whose operators keep their
  * temporaries in the caller's buffers. The split-KV scratch is a fixed array in

@@ -139,3 +139,70 @@ def test_two_rank_decoder_matches_single_gpu():
         if a["tokens"][s] != ref["tokens"][s]:
             assert ref["margin"][s] <= 2 * float(np.max(np.abs(got - want))), (s, a["tokens"][s], ref["tokens"][s])
             break   # the sequences differ from here on
+
+
+# ---- sequence-parallel long-context attention (2 GPUs) ------------------------------------------
+
+def _seq_worker(rank, world, port, q_out):
+    try:
+        import torch.distributed as dist
+        os.environ["MASTER_ADDR"] = "127.0.0.1"
+        os.environ["MASTER_PORT"] = str(port)
+        torch.cuda.set_device(rank)
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+        from fast_llm_b200 import capi, tp
+        ctx = capi.Context(rank)
+        scale = float(1.0 / np.sqrt(128.0))
+        res = {}
+        sp = tp.SeqParallel(ctx, dist, max_records=32 * 4)
+        for kv, batch in ((32768, 1), (4096 + 333, 4)):
+            g = torch.Generator(device="cuda").manual_seed(kv + batch)      # same stream on both ranks
+            q = torch.randn((batch, 32, 128), generator=g, device="cuda")
+            k = (torch.randn((batch, 8, kv, 128), generator=g, device="cuda") * scale).half()
+            v = (torch.randn((batch, 8, kv, 128), generator=g, device="cuda") * scale).half()
+            # this rank's contiguous slice of the keys (uneven when kv is odd)
+            lo, hi = kv * rank // world, kv * (rank + 1) // world
+            ks = k[:, :, lo:hi].contiguous().view(torch.int16)
+            vs = v[:, :, lo:hi].contiguous().view(torch.int16)
+            out_l = torch.zeros_like(q); lse = torch.zeros((batch, 32, 2), device="cuda"); out = torch.zeros_like(q)
+            torch.cuda.synchronize()
+            dist.barrier()
+            ctx.attn_decode_lse(q, ks, vs, 32, 8, 128, hi - lo, hi - lo, batch, scale, out_l, lse)
+            sp.combine(out_l, lse, batch * 32, out)
+            ctx.sync()
+            full = torch.zeros_like(q)
+            ctx.attn_decode(q, k.view(torch.int16), v.view(torch.int16), 32, 8, 128, kv, kv, batch, scale, full)
+            ctx.sync()
+            res[(kv, batch)] = (out.cpu().numpy(), float((out - full).abs().max()))
+        res["status"] = ctx.status()
+        dist.barrier()
+        sp.close()
+        ctx.close()
+        dist.destroy_process_group()
+        q_out.put((rank, res))
+    except Exception:
+        import traceback
+        q_out.put((rank, "ERROR " + traceback.format_exc()))
+
+
+def test_sequence_parallel_attention_two_ranks():
+    if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    import torch.multiprocessing as mp
+    mpc = mp.get_context("spawn")
+    q = mpc.Queue()
+    port = _free_port()
+    procs = [mpc.Process(target=_seq_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = dict(q.get(timeout=600) for _ in procs)
+    for p in procs:
+        p.join(timeout=120)
+    for r in (0, 1):
+        assert not isinstance(res[r], str), res[r]
+        assert res[r]["status"] == 0
+    for key in ((32768, 1), (4096 + 333, 4)):
+        a, err_a = res[0][key]
+        b, err_b = res[1][key]
+        assert np.array_equal(a.view(np.uint32), b.view(np.uint32))     # both ranks: identical bits
+        assert err_a <= 1e-5 and err_b <= 1e-5, (key, err_a, err_b)      # = one GPU over all keys (f32 reassociation)

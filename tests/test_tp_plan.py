@@ -126,3 +126,21 @@ def test_merge_top_tie_rule():
         idx, margin = tp.merge_top(recs)
         assert idx == int(np.argmax(lg))
         assert margin == float(lg[idx] - np.delete(lg, idx).max())
+
+
+def test_merge_lse_equals_softmax_over_all_keys():
+    from fast_llm_b200 import tp
+    rng = np.random.default_rng(3)
+    for world in (1, 2, 3, 8):
+        n = 97 * world + 5
+        s = rng.standard_normal(n) * 4.0
+        v = rng.standard_normal((n, 128))
+        p = np.exp(s - s.max()); p /= p.sum()
+        want = p @ v
+        bounds = [n * r // world for r in range(world + 1)]
+        recs = []
+        for r in range(world):
+            sl = slice(bounds[r], bounds[r + 1])
+            m = s[sl].max(); e = np.exp(s[sl] - m)
+            recs.append((e @ v[sl] / e.sum(), m, e.sum()))
+        assert np.allclose(tp.merge_lse(recs), want, rtol=1e-12, atol=1e-12)
