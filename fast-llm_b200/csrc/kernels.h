@@ -64,6 +64,9 @@ struct MatvecArgs {
 cudaError_t tensor_map_2d(CUtensorMap *m, uint32_t elem_bytes, const void *base, uint64_t dim0, uint64_t rows,
                           uint64_t stride_bytes, uint32_t box0, uint32_t box_rows, bool swizzle128);
 cudaError_t launch_matvec(const MatvecArgs &a, int sms, cudaStream_t stream);
+// Q4_K launches that qualify run on the integer tensor-core kernel (matvec_mma.cu).
+bool matvec_mma_eligible(const MatvecArgs &a);
+cudaError_t launch_matvec_mma(const MatvecArgs &a, int sms, cudaStream_t stream);
 // True when launch_matvec would take the streaming kernel for this shape.
 bool matvec_is_streaming(int fmt, uint32_t cols);
 // Dynamic shared memory the streaming kernel needs for (cols, formats used).

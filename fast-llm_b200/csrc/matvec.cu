@@ -374,26 +374,28 @@ matvec_stream_kernel(const MatvecArgs a, const __grid_constant__ TensorMaps maps
         while (p_i < (uint32_t)stages && p_i < my_stages) issue();
 
     // ---- build the fixed-point activation in shared memory ----
-    // One warp per 256-column block (blocks warp, warp + nw, ...); lane l holds
-    // columns 8l .. 8l+7 of the block. All global loads of all the warp's blocks
-    // are issued first, so the prologue costs one memory round trip; the norm
-    // weights are constants and are fetched before the dependency wait.
-    constexpr int kMaxBlk = 6;   // blocks per warp: cols <= 6 * 256 * kMinWarps = 18432
+    // Half a warp per 256-column block (blocks h, h + 2 nw, ... with h = 2 warp + lane / 16); lane l of
+    // the half holds columns 16 l .. 16 l + 15 of the block, so the 16 blocks of a 4096-column
+    // activation are one round for 12 warps (a block's chain of reduce -> scale -> digits is latency
+    // bound; a second round would double it). All global loads of all the blocks are issued first, so
+    // the prologue costs one memory round trip; the norm weights are constants and are fetched before
+    // the dependency wait.
+    constexpr int kMaxBlk = 3;   // blocks per half-warp: cols <= 3 * 256 * 2 * kMinWarps = 18432
     const uint32_t nblk = a.cols / 256, nblk_pad = nseg * 8;   // blocks nblk .. nblk_pad-1 are zeros
-    float4 ra[kMaxBlk][2], rb2[kMaxBlk][2];
+    const uint32_t hw = 2 * warp + (lane >> 4), hl = lane & 15u, nhw = 2 * nw;
+    float4 ra[kMaxBlk][4], rb2[kMaxBlk][4];
 #pragma unroll
-    for (int b = 0; b < kMaxBlk; ++b) {
-        ra[b][0] = ra[b][1] = make_float4(0.f, 0.f, 0.f, 0.f);
-        rb2[b][0] = rb2[b][1] = make_float4(0.f, 0.f, 0.f, 0.f);
-    }
+    for (int b = 0; b < kMaxBlk; ++b)
+#pragma unroll
+        for (int k = 0; k < 4; ++k) ra[b][k] = rb2[b][k] = make_float4(0.f, 0.f, 0.f, 0.f);
     if (a.x_mode == MV_X_RMSNORM) {
 #pragma unroll
         for (int b = 0; b < kMaxBlk; ++b) {
-            const uint32_t blk = warp + b * nw;
+            const uint32_t blk = hw + b * nhw;
             if (blk < nblk) {
-                const uint32_t c0 = blk * 256 + lane * 8;
-                rb2[b][0] = __ldg(reinterpret_cast<const float4 *>(a.wnorm + c0));
-                rb2[b][1] = __ldg(reinterpret_cast<const float4 *>(a.wnorm + c0 + 4));
+                const float4 *src = reinterpret_cast<const float4 *>(a.wnorm + blk * 256 + hl * 16);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) rb2[b][k] = __ldg(src + k);
             }
         }
     }
@@ -403,14 +405,15 @@ matvec_stream_kernel(const MatvecArgs a, const __grid_constant__ TensorMaps maps
         while (p_i < (uint32_t)stages && p_i < my_stages) issue();
 #pragma unroll
     for (int b = 0; b < kMaxBlk; ++b) {
-        const uint32_t blk = warp + b * nw;
+        const uint32_t blk = hw + b * nhw;
         if (blk < nblk) {
-            const uint32_t c0 = blk * 256 + lane * 8;
-            ra[b][0] = *reinterpret_cast<const float4 *>(a.x + c0);
-            ra[b][1] = *reinterpret_cast<const float4 *>(a.x + c0 + 4);
+            const float4 *src = reinterpret_cast<const float4 *>(a.x + blk * 256 + hl * 16);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) ra[b][k] = src[k];
             if (a.x_mode == MV_X_SILU_MUL) {
-                rb2[b][0] = *reinterpret_cast<const float4 *>(a.x2 + c0);
-                rb2[b][1] = *reinterpret_cast<const float4 *>(a.x2 + c0 + 4);
+                const float4 *src2 = reinterpret_cast<const float4 *>(a.x2 + blk * 256 + hl * 16);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) rb2[b][k] = src2[k];
             }
         }
     }
@@ -420,37 +423,42 @@ matvec_stream_kernel(const MatvecArgs a, const __grid_constant__ TensorMaps maps
     float ss = 0.f;
     if (a.x_mode == MV_X_RMSNORM) {
 #pragma unroll
-        for (int b = 0; b < kMaxBlk; ++b)
-            if (warp + b * nw < nblk) {
-                const float4 u0 = ra[b][0], u1 = ra[b][1];
-                ss += (u0.x * u0.x + u0.y * u0.y) + (u0.z * u0.z + u0.w * u0.w);
-                ss += (u1.x * u1.x + u1.y * u1.y) + (u1.z * u1.z + u1.w * u1.w);
+        for (int b = 0; b < kMaxBlk; ++b)   // blocks that were not loaded hold zeros
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const float4 u = ra[b][k];
+                ss += (u.x * u.x + u.y * u.y) + (u.z * u.z + u.w * u.w);
             }
         ss = warp_sum(ss);
         if (lane == 0) red[warp] = ss;
     }
 #pragma unroll
     for (int b = 0; b < kMaxBlk; ++b) {
-        const uint32_t blk = warp + b * nw;
-        if (blk >= nblk_pad) break;
-        const uint32_t c0 = blk * 256 + lane * 8;
-        float v[8] = {ra[b][0].x, ra[b][0].y, ra[b][0].z, ra[b][0].w, ra[b][1].x, ra[b][1].y, ra[b][1].z, ra[b][1].w};
-        const float w2[8] = {rb2[b][0].x, rb2[b][0].y, rb2[b][0].z, rb2[b][0].w,
-                             rb2[b][1].x, rb2[b][1].y, rb2[b][1].z, rb2[b][1].w};
+        // nblk_pad is even and the warp's two blocks are 2 warp + b nhw (+1): both halves leave together
+        if (2 * warp + b * nhw >= nblk_pad) break;
+        const uint32_t blk = hw + b * nhw;
+        const uint32_t c0 = blk * 256 + hl * 16;
+        float v[16], w2[16];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            v[4 * k] = ra[b][k].x; v[4 * k + 1] = ra[b][k].y; v[4 * k + 2] = ra[b][k].z; v[4 * k + 3] = ra[b][k].w;
+            w2[4 * k] = rb2[b][k].x; w2[4 * k + 1] = rb2[b][k].y; w2[4 * k + 2] = rb2[b][k].z; w2[4 * k + 3] = rb2[b][k].w;
+        }
         float amax = 0.f;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
+        for (int i = 0; i < 16; ++i) {
             if (a.x_mode == MV_X_RMSNORM) v[i] = v[i] * w2[i];
             else if (a.x_mode == MV_X_SILU_MUL) v[i] = (v[i] / (1.0f + expf(-v[i]))) * w2[i];   // 0 for padding: silu(0) = 0
             amax = fmaxf(amax, fabsf(v[i]));
         }
-        amax = warp_max(amax);
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));   // over the half-warp
         const float s = amax > 0.f ? amax / kFixMax : 1.0f;
         const float inv_s = 1.0f / s;
         int sum = 0;
-        uint32_t pk[3][2] = {{0u, 0u}, {0u, 0u}, {0u, 0u}};   // this lane's 8 columns of each digit plane
+        uint32_t pk[3][4] = {{0u, 0u, 0u, 0u}, {0u, 0u, 0u, 0u}, {0u, 0u, 0u, 0u}};   // this lane's 16 columns of each digit plane
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
+        for (int i = 0; i < 16; ++i) {
             const int X = __float2int_rn(v[i] * inv_s);          // |X| <= 1040000
             const int d2 = ((X + 64) & 127) - 64;                // balanced base-128 digits
             const int X1 = (X - d2) >> 7;
@@ -461,27 +469,28 @@ matvec_stream_kernel(const MatvecArgs a, const __grid_constant__ TensorMaps maps
             pk[1][i >> 2] |= (uint32_t)(d1 & 0xFF) << (8 * (i & 3));
             pk[2][i >> 2] |= (uint32_t)(d2 & 0xFF) << (8 * (i & 3));
         }
-        // the lane's 8 columns are 8 consecutive bytes of one 16-byte slot in both layouts
+        // the lane's 16 columns are exactly one 16-byte slot in both layouts
 #pragma unroll
         for (int d = 0; d < 3; ++d) {
-            if (use_q4) *reinterpret_cast<uint2 *>(sm.q4 + pos4(c0, d)) = make_uint2(pk[d][0], pk[d][1]);
-            if (use_q6) *reinterpret_cast<uint2 *>(sm.q6 + pos6(c0, d)) = make_uint2(pk[d][0], pk[d][1]);
+            const uint4 w4 = make_uint4(pk[d][0], pk[d][1], pk[d][2], pk[d][3]);
+            if (use_q4) *reinterpret_cast<uint4 *>(sm.q4 + pos4(c0, d)) = w4;
+            if (use_q6) *reinterpret_cast<uint4 *>(sm.q6 + pos6(c0, d)) = w4;
         }
-        // sums over 16 columns (lane pairs) and 32 columns (lane quads), exact in int32
-        const int s16 = sum + __shfl_xor_sync(0xffffffffu, sum, 1);
-        const int s32 = s16 + __shfl_xor_sync(0xffffffffu, s16, 2);
+        // sums over 16 columns (this lane) and 32 columns (lane pairs), exact in int32
+        const int s16 = sum;
+        const int s32 = s16 + __shfl_xor_sync(0xffffffffu, s16, 1);
         const uint32_t seg = blk >> 3, sbi = blk & 7u;
-        if (use_q4 && (lane & 3u) == 0) {
-            // 32-column sub-block j = lane / 4 -> consumer lane sbi*4 + j/2, component j & 1
-            const uint32_t j = lane >> 2;
+        if (use_q4 && (hl & 1u) == 0) {
+            // 32-column sub-block j = hl / 2 -> consumer lane sbi*4 + j/2, component j & 1
+            const uint32_t j = hl >> 1;
             sm.s4[((seg * 32 + sbi * 4 + (j >> 1)) << 1) + (j & 1u)] = (float)s32;
         }
-        if (use_q6 && (lane & 1u) == 0) {
-            // 16-column run r = lane / 2 (0..15): half = r/8, group g = (r/2)%4, hq = r%2
-            const uint32_t r = lane >> 1, hf = r >> 3, g = (r >> 1) & 3u, hq = r & 1u;
+        if (use_q6) {
+            // 16-column run r = hl (0..15): half = r/8, group g = (r/2)%4, hq = r%2
+            const uint32_t r = hl, hf = r >> 3, g = (r >> 1) & 3u, hq = r & 1u;
             sm.s6[((seg * 32 + sbi * 4 + hf * 2 + hq) << 2) + g] = (float)s16;
         }
-        if (lane == 0) sm.xs[blk] = s;
+        if (hl == 0) sm.xs[blk] = s;
     }
     __syncthreads();
     float inv_rms = 1.f;
@@ -721,6 +730,7 @@ void matvec_scratch_need(const MatvecArgs &, int, size_t *scratch_floats, size_t
 
 cudaError_t launch_matvec(const MatvecArgs &a, int sms, cudaStream_t stream) {
     if (a.n_tensors < 1 || a.n_tensors > 4 || a.cols == 0) return cudaErrorInvalidValue;
+    if (matvec_mma_eligible(a)) return launch_matvec_mma(a, sms, stream);
     bool streaming = true, q4 = false, q6 = false;
     uint32_t total_rows = 0, total_quads = 0;
     for (int i = 0; i < a.n_tensors; ++i) {
