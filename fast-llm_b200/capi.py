@@ -11,6 +11,9 @@ LIB_PATH = os.path.join(_HERE, "libfl_b200.so")
 
 F32, Q8_0, Q5_0, Q4_K, Q6_K = 0, 1, 2, 3, 4
 FMT_NAMES = {F32: "F32", Q8_0: "Q8_0", Q5_0: "Q5_0", Q4_K: "Q4_K", Q6_K: "Q6_K"}
+# TaskKind values (include/fastllm/fastllm.h:17-45 of the reference; 13 and 14 are appended here)
+K_STREAM_DOT, K_MERGE, K_SIGNAL, K_ACT_Q8, K_STREAM_DOT_IDX, K_RMSNORM, K_ADD2, K_ROPE_DS2, K_KV_APPEND = range(9)
+K_ATTN_HEAD, K_ROUTER_SEL, K_SILU_MUL, K_WMERGE, K_ATTN_GQA_F16, K_ROPE_KV_APPEND_F16 = range(9, 15)
 BLK_ELEMS = {F32: 1, Q8_0: 32, Q5_0: 32, Q4_K: 256, Q6_K: 256}
 BLK_BYTES = {F32: 4, Q8_0: 34, Q5_0: 22, Q4_K: 144, Q6_K: 210}
 
@@ -26,7 +29,7 @@ SYMBOLS = [
     "fl_b200_dequant", "fl_b200_matvec", "fl_b200_matvec_assign", "fl_b200_matvec_expert", "fl_b200_matvec_pitched", "fl_b200_matvec_host",
     "fl_b200_attn_decode", "fl_b200_attn_decode_lse", "fl_b200_seqpar_create", "fl_b200_seqpar_destroy",
     "fl_b200_seqpar_comm", "fl_b200_seqpar_set_peers", "fl_b200_seqpar_combine", "fl_b200_attn_verify", "fl_b200_attn_decode_static", "fl_b200_attn_decode_host", "fl_b200_rmsnorm", "fl_b200_add2",
-    "fl_b200_silu_mul", "fl_b200_router_sel", "fl_b200_wmerge", "fl_b200_rope_kv_append", "fl_b200_argmax", "fl_b200_exec_task",
+    "fl_b200_silu_mul", "fl_b200_router_sel", "fl_b200_wmerge", "fl_b200_rope_kv_append", "fl_b200_argmax", "fl_b200_exec_task", "fl_b200_plan_create", "fl_b200_plan_run", "fl_b200_plan_info", "fl_b200_plan_destroy",
     "fl_b200_decoder_create", "fl_b200_decoder_create_tp", "fl_b200_decoder_comm", "fl_b200_decoder_set_peers",
     "fl_b200_decoder_destroy", "fl_b200_decoder_set_layer_tensor",
     "fl_b200_decoder_set_layer_norms", "fl_b200_decoder_set_global", "fl_b200_decoder_set_out_norm",
@@ -85,6 +88,7 @@ def load():
     lib.fl_b200_destroy.restype = None
     lib.fl_b200_decoder_destroy.restype = None
     lib.fl_b200_seqpar_destroy.restype = None
+    lib.fl_b200_plan_destroy.restype = None
     _lib = lib
     return lib
 

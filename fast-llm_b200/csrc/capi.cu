@@ -6,6 +6,9 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <algorithm>
+#include <array>
+#include <vector>
 
 namespace flb {
 
@@ -561,8 +564,34 @@ int fl_b200_argmax(fl_b200_ctx *c, const float *lg, uint32_t n, int32_t *idx, fl
                     "argmax launch");
 }
 
-int fl_b200_exec_task(fl_b200_ctx *c, const fl_b200_task *t) {
+// Size of the parameter block behind Task::aux for a kind (0: none / not a parameter block).
+static size_t aux_bytes(int kind) {
+    switch (kind) {
+    case FL_B200_ROUTER_SEL: return sizeof(fl_b200_router_p);
+    case FL_B200_WMERGE: return sizeof(fl_b200_wmerge_p);
+    case FL_B200_RMSNORM: return sizeof(fl_b200_rmsnorm_p);
+    case FL_B200_ADD2: return sizeof(fl_b200_add2_p);
+    case FL_B200_SILU_MUL: return sizeof(fl_b200_silu_mul_p);
+    case FL_B200_ATTN_GQA_F16: return sizeof(fl_b200_attn_gqa_f16_p);
+    case FL_B200_ROPE_KV_APPEND_F16: return sizeof(fl_b200_rope_kv_append_f16_p);
+    default: return 0;
+    }
+}
+
+// Launches one task on the context's stream. aux_host: host copy of the task's parameter block
+// (fetched here, with a stream synchronisation, when null).
+static int launch_task(fl_b200_ctx *c, const fl_b200_task *t, const void *aux_host) {
     if (!t) return set_err(FL_B200_ERR_ARG, "exec_task: null task");
+    uint8_t local[64];
+    const size_t ab = aux_bytes(t->kind);
+    if (ab) {
+        if (!t->aux) return set_err(FL_B200_ERR_ARG, "exec_task: decode op without aux param block");
+        if (!aux_host) {
+            CK(cudaMemcpyAsync(local, t->aux, ab, cudaMemcpyDefault, c->stream));
+            CK(cudaStreamSynchronize(c->stream));
+            aux_host = local;
+        }
+    }
     switch (t->kind) {
     case FL_B200_SIGNAL: return FL_B200_OK;
     case FL_B200_STREAM_DOT: {
@@ -581,59 +610,202 @@ int fl_b200_exec_task(fl_b200_ctx *c, const fl_b200_task *t) {
                                      (const float *)t->x, t->nx ? t->nx : 1, t->xstride, (float *)t->y, t->ystride);
     }
     case FL_B200_ROUTER_SEL: {
-        if (!t->aux) return set_err(FL_B200_ERR_ARG, "exec_task: decode op without aux param block");
-        fl_b200_router_p p;
-        CK(cudaMemcpyAsync(&p, t->aux, sizeof(p), cudaMemcpyDefault, c->stream));
-        CK(cudaStreamSynchronize(c->stream));
+        const fl_b200_router_p &p = *(const fl_b200_router_p *)aux_host;
         return fl_b200_router_sel(c, p.logits, p.ids, p.gates, p.n_expert, p.top_k, p.norm, p.scale);
     }
     case FL_B200_WMERGE: {
-        if (!t->aux) return set_err(FL_B200_ERR_ARG, "exec_task: decode op without aux param block");
-        fl_b200_wmerge_p p;
-        CK(cudaMemcpyAsync(&p, t->aux, sizeof(p), cudaMemcpyDefault, c->stream));
-        CK(cudaStreamSynchronize(c->stream));
+        const fl_b200_wmerge_p &p = *(const fl_b200_wmerge_p *)aux_host;
         return fl_b200_wmerge(c, p.parts, p.gates, p.add1, p.add2, p.y, p.scale, p.n_parts, p.n, p.n_full);
     }
     case FL_B200_RMSNORM: {
-        if (!t->aux) return set_err(FL_B200_ERR_ARG, "exec_task: decode op without aux param block");
-        fl_b200_rmsnorm_p p;
-        CK(cudaMemcpyAsync(&p, t->aux, sizeof(p), cudaMemcpyDefault, c->stream));
-        CK(cudaStreamSynchronize(c->stream));
+        const fl_b200_rmsnorm_p &p = *(const fl_b200_rmsnorm_p *)aux_host;
         return fl_b200_rmsnorm(c, p.x, p.wnorm, p.y, p.eps, p.n);
     }
     case FL_B200_ADD2: {
-        if (!t->aux) return set_err(FL_B200_ERR_ARG, "exec_task: decode op without aux param block");
-        fl_b200_add2_p p;
-        CK(cudaMemcpyAsync(&p, t->aux, sizeof(p), cudaMemcpyDefault, c->stream));
-        CK(cudaStreamSynchronize(c->stream));
+        const fl_b200_add2_p &p = *(const fl_b200_add2_p *)aux_host;
         return fl_b200_add2(c, p.a, p.b, p.y, p.n);
     }
     case FL_B200_SILU_MUL: {
-        if (!t->aux) return set_err(FL_B200_ERR_ARG, "exec_task: decode op without aux param block");
-        fl_b200_silu_mul_p p;
-        CK(cudaMemcpyAsync(&p, t->aux, sizeof(p), cudaMemcpyDefault, c->stream));
-        CK(cudaStreamSynchronize(c->stream));
+        const fl_b200_silu_mul_p &p = *(const fl_b200_silu_mul_p *)aux_host;
         return fl_b200_silu_mul(c, p.gate, p.up, p.h, p.n);
     }
     case FL_B200_ATTN_GQA_F16: {
-        if (!t->aux) return set_err(FL_B200_ERR_ARG, "exec_task: decode op without aux param block");
-        fl_b200_attn_gqa_f16_p p;
-        CK(cudaMemcpyAsync(&p, t->aux, sizeof(p), cudaMemcpyDefault, c->stream));
-        CK(cudaStreamSynchronize(c->stream));
+        const fl_b200_attn_gqa_f16_p &p = *(const fl_b200_attn_gqa_f16_p *)aux_host;
         return attn_impl(c, p.q, p.kcache, p.vcache, p.n_q_head, p.n_kv_head, p.head_dim, 0, p.kv_stride, 1,
                          p.scale, p.out, p.pos);
     }
     case FL_B200_ROPE_KV_APPEND_F16: {
-        if (!t->aux) return set_err(FL_B200_ERR_ARG, "exec_task: decode op without aux param block");
-        fl_b200_rope_kv_append_f16_p p;
-        CK(cudaMemcpyAsync(&p, t->aux, sizeof(p), cudaMemcpyDefault, c->stream));
-        CK(cudaStreamSynchronize(c->stream));
+        const fl_b200_rope_kv_append_f16_p &p = *(const fl_b200_rope_kv_append_f16_p *)aux_host;
         return fl_b200_rope_kv_append(c, p.q, p.k, p.v, p.kcache, p.vcache, p.pos, p.n_q_head, p.n_kv_head,
                                       p.head_dim, p.kv_stride, p.freq_base);
     }
     default:
         return set_err(FL_B200_ERR_ARG, "exec_task: task kind %d has no device implementation in this library", (int)t->kind);
     }
+}
+
+int fl_b200_exec_task(fl_b200_ctx *c, const fl_b200_task *t) { return launch_task(c, t, nullptr); }
+
+// ---- a frozen task table as one CUDA graph -------------------------------------------------------
+// The counterpart of Graph::freeze + Runtime::run for the GPU side (src/runtime/graph.cpp:48-148,
+// src/runtime/runtime.cpp:178-292): the table is validated with the reference's rules, ordered by
+// dependency level, row tiles of one weight tensor are merged back into one matvec launch (the
+// reference cuts a tensor into 192..1024-row tiles for its CPU/GPU work queues,
+// src/model/decoder.cpp:713-717; here a launch covers the GPU whatever its size), and the launches
+// are recorded once as a CUDA graph that fl_b200_plan_run replays.
+struct fl_b200_plan {
+    fl_b200_ctx *ctx = nullptr;
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
+    uint32_t n_tasks = 0, n_launches = 0, n_merged = 0;
+};
+
+int fl_b200_plan_create(fl_b200_ctx *c, const fl_b200_task *tasks, uint32_t n, fl_b200_plan **out) {
+    if (!c || !tasks || !out || n == 0) return set_err(FL_B200_ERR_ARG, "plan_create: null / empty");
+    *out = nullptr;
+    // --- Graph::freeze: Kahn's algorithm (cycle check), exactly one sink, which must be SIGNAL ---
+    std::vector<int32_t> deps(n);
+    std::vector<uint32_t> level(n, 0), order;
+    std::vector<uint32_t> ready;
+    for (uint32_t i = 0; i < n; ++i) {
+        if (tasks[i].n_consumers > 6) return set_err(FL_B200_ERR_ARG, "plan_create: task %u: consumer fan-out exceeded", i);
+        deps[i] = tasks[i].dep_init;
+        if (deps[i] == 0) ready.push_back(i);
+    }
+    uint32_t seen = 0, sinks = 0, terminal = 0;
+    while (!ready.empty()) {
+        const uint32_t id = ready.back();
+        ready.pop_back();
+        ++seen;
+        order.push_back(id);
+        const fl_b200_task &t = tasks[id];
+        if (t.n_consumers == 0) { ++sinks; terminal = id; }
+        for (uint16_t k = 0; k < t.n_consumers; ++k) {
+            const uint32_t cns = t.consumers[k];
+            if (cns >= n || cns == id) return set_err(FL_B200_ERR_ARG, "plan_create: task %u: bad edge to %u", id, cns);
+            if (level[cns] < level[id] + 1) level[cns] = level[id] + 1;
+            if (--deps[cns] == 0) ready.push_back(cns);
+        }
+    }
+    if (seen != n) return set_err(FL_B200_ERR_ARG, "plan_create: cycle in graph (or dep_init does not match the edges)");
+    if (sinks != 1) return set_err(FL_B200_ERR_ARG, "plan_create: graph must have exactly one sink (terminal SIGNAL), found %u", sinks);
+    if (tasks[terminal].kind != FL_B200_SIGNAL) return set_err(FL_B200_ERR_ARG, "plan_create: terminal must be SIGNAL");
+    for (uint32_t i = 0; i < n; ++i) {
+        const fl_b200_task &t = tasks[i];
+        if (t.kind != FL_B200_STREAM_DOT && t.kind != FL_B200_STREAM_DOT_IDX) {
+            if (t.kind > FL_B200_ROPE_KV_APPEND_F16) return set_err(FL_B200_ERR_ARG, "plan_create: task %u: unknown task kind %d", i, (int)t.kind);
+            if (t.kind >= FL_B200_RMSNORM && t.aux == nullptr) return set_err(FL_B200_ERR_ARG, "plan_create: task %u: decode op without aux param block", i);
+            continue;
+        }
+        if (t.kind == FL_B200_STREAM_DOT_IDX && (t.aux == nullptr || t.aux2 == 0))
+            return set_err(FL_B200_ERR_ARG, "plan_create: task %u: STREAM_DOT_IDX without id slot / stride", i);
+        if (t.fmt > FL_B200_Q6_K) return set_err(FL_B200_ERR_ARG, "plan_create: task %u: weight format %d has no device kernel", i, (int)t.fmt);
+        if (t.cols % blk_elems(t.fmt) != 0) return set_err(FL_B200_ERR_ARG, "plan_create: task %u: STREAM_DOT cols not a multiple of the format block size", i);
+        if (t.w_bytes != (uint64_t)t.rows * row_bytes(t.fmt, t.cols)) return set_err(FL_B200_ERR_ARG, "plan_create: task %u: STREAM_DOT w_bytes mismatch", i);
+    }
+    // --- parameter blocks to the host (one synchronisation), attention scratch sized before the capture ---
+    std::vector<std::array<uint8_t, 64>> aux(n);
+    CK(cudaSetDevice(c->device));
+    for (uint32_t i = 0; i < n; ++i) {
+        const size_t ab = aux_bytes(tasks[i].kind);
+        if (ab) CK(cudaMemcpyAsync(aux[i].data(), tasks[i].aux, ab, cudaMemcpyDefault, c->stream));
+    }
+    CK(cudaStreamSynchronize(c->stream));
+    for (uint32_t i = 0; i < n; ++i)
+        if (tasks[i].kind == FL_B200_ATTN_GQA_F16) {
+            const fl_b200_attn_gqa_f16_p &p = *(const fl_b200_attn_gqa_f16_p *)aux[i].data();
+            if (p.n_kv_head == 0 || p.n_q_head != 4 * p.n_kv_head || p.head_dim != 128)
+                return set_err(FL_B200_ERR_ARG, "plan_create: task %u: attention shape %u/%u x %u is not built", i, p.n_q_head, p.n_kv_head, p.head_dim);
+            const uint32_t splits = attn_pick_splits(p.n_kv_head, 1, p.kv_stride, c->sms);
+            const size_t need = attn_part_floats(p.n_q_head, 1, splits) * sizeof(float);
+            if (c->attn_part_cap < need) {
+                cudaFree(c->attn_part);
+                c->attn_part = nullptr;
+                c->attn_part_cap = 0;
+                CK(cudaMalloc(&c->attn_part, need));
+                c->attn_part_cap = need;
+            }
+        }
+    // --- launch list: by dependency level; within a level, STREAM_DOT tiles of one tensor merge ---
+    std::vector<uint32_t> by_level(order);
+    std::stable_sort(by_level.begin(), by_level.end(), [&](uint32_t a, uint32_t b) {
+        if (level[a] != level[b]) return level[a] < level[b];
+        const fl_b200_task &x = tasks[a], &y = tasks[b];
+        const bool dx = x.kind == FL_B200_STREAM_DOT, dy = y.kind == FL_B200_STREAM_DOT;
+        if (dx != dy) return dx;                      // dots first
+        if (!dx) return false;
+        if (x.x != y.x) return x.x < y.x;
+        return x.w < y.w;                             // tiles of one tensor next to each other, ascending
+    });
+    std::vector<fl_b200_task> launches;
+    std::vector<uint32_t> src;                        // the task a launch takes its parameter block from
+    uint32_t merged = 0;
+    for (uint32_t id : by_level) {
+        const fl_b200_task &t = tasks[id];
+        if (t.kind == FL_B200_SIGNAL) continue;
+        if (t.kind == FL_B200_STREAM_DOT && !launches.empty()) {
+            fl_b200_task &p = launches.back();
+            const uint32_t pnx = p.nx ? p.nx : 1, tnx = t.nx ? t.nx : 1;
+            if (p.kind == FL_B200_STREAM_DOT && level[src.back()] == level[id] && p.fmt == t.fmt && p.cols == t.cols &&
+                p.x == t.x && pnx == tnx && p.xstride == t.xstride && p.ystride == t.ystride &&
+                (const uint8_t *)p.w + p.w_bytes == (const uint8_t *)t.w && (const float *)p.y + p.rows == (const float *)t.y &&
+                (pnx == 1 || p.ystride >= p.rows + t.rows)) {
+                p.rows += t.rows;
+                p.w_bytes += t.w_bytes;
+                ++merged;
+                continue;
+            }
+        }
+        launches.push_back(t);
+        src.push_back(id);
+    }
+    // --- record ---
+    fl_b200_plan *pl = new fl_b200_plan();
+    pl->ctx = c;
+    pl->n_tasks = n;
+    pl->n_launches = (uint32_t)launches.size();
+    pl->n_merged = merged;
+    cudaStream_t s = c->stream;
+    cudaError_t e = cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal);
+    if (e != cudaSuccess) { delete pl; return cuda_err(e, "cudaStreamBeginCapture"); }
+    int rc = FL_B200_OK;
+    for (size_t i = 0; i < launches.size() && rc == FL_B200_OK; ++i) rc = launch_task(c, &launches[i], aux[src[i]].data());
+    cudaGraph_t g = nullptr;
+    e = cudaStreamEndCapture(s, &g);
+    if (rc != FL_B200_OK || e != cudaSuccess) {
+        if (g) cudaGraphDestroy(g);
+        delete pl;
+        return rc != FL_B200_OK ? rc : cuda_err(e, "cudaStreamEndCapture");
+    }
+    pl->graph = g;
+    e = cudaGraphInstantiate(&pl->exec, g, 0);
+    if (e != cudaSuccess) { cudaGraphDestroy(g); delete pl; return cuda_err(e, "cudaGraphInstantiate"); }
+    *out = pl;
+    return FL_B200_OK;
+}
+
+// One run of the table (asynchronous on the context's stream; fl_b200_sync waits). STREAM_DOT accumulates:
+// the caller zeroes the y slots per run like the reference does (src/model/decoder.cpp:1206-1208).
+int fl_b200_plan_run(fl_b200_plan *p) {
+    if (!p) return set_err(FL_B200_ERR_ARG, "plan_run: null");
+    return cuda_err(cudaGraphLaunch(p->exec, p->ctx->stream), "cudaGraphLaunch");
+}
+
+int fl_b200_plan_info(fl_b200_plan *p, uint32_t *n_tasks, uint32_t *n_launches, uint32_t *n_merged) {
+    if (!p) return set_err(FL_B200_ERR_ARG, "plan_info: null");
+    if (n_tasks) *n_tasks = p->n_tasks;
+    if (n_launches) *n_launches = p->n_launches;
+    if (n_merged) *n_merged = p->n_merged;
+    return FL_B200_OK;
+}
+
+void fl_b200_plan_destroy(fl_b200_plan *p) {
+    if (!p) return;
+    cudaSetDevice(p->ctx->device);
+    cudaStreamSynchronize(p->ctx->stream);
+    if (p->exec) cudaGraphExecDestroy(p->exec);
+    if (p->graph) cudaGraphDestroy(p->graph);
+    delete p;
 }
 
 } // extern "C"

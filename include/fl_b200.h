@@ -255,6 +255,23 @@ typedef struct {
  * DeepSeek-specific forms) return FL_B200_ERR_ARG. */
 int fl_b200_exec_task(fl_b200_ctx *ctx, const fl_b200_task *task);
 
+/* ---- a frozen task table as one CUDA graph: Graph::freeze + Runtime::run for
+ *      the GPU side (src/runtime/graph.cpp:48-148, src/runtime/runtime.cpp:178-292).
+ * `tasks` is the host copy of the table (ids 0..n-1, consumers / dep_init as
+ * Graph::edge leaves them; every pointer inside is a device pointer). The table
+ * is validated with the reference's freeze rules (no cycle, exactly one sink,
+ * which is a SIGNAL, aux blocks present, STREAM_DOT shapes consistent), ordered
+ * by dependency level, row tiles of one weight tensor are merged into one matvec
+ * launch, and the launches are recorded once. fl_b200_plan_run replays them
+ * (asynchronous; fl_b200_sync waits). Parameter blocks are read at plan time:
+ * they are immutable after freeze in the reference too. STREAM_DOT accumulates
+ * into y: zero the slots per run as the reference does. ---- */
+typedef struct fl_b200_plan fl_b200_plan;
+int fl_b200_plan_create(fl_b200_ctx *ctx, const fl_b200_task *tasks_host, uint32_t n, fl_b200_plan **out);
+int fl_b200_plan_run(fl_b200_plan *plan);
+int fl_b200_plan_info(fl_b200_plan *plan, uint32_t *n_tasks, uint32_t *n_launches, uint32_t *n_merged_tiles);
+void fl_b200_plan_destroy(fl_b200_plan *plan);
+
 /* ---- Llama-shape greedy decoder: Decoder::step for the GQA / f16-cache
  *      shape (src/model/decoder.h:52-81). ---- */
 typedef struct {
