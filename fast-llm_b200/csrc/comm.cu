@@ -35,29 +35,6 @@ namespace flb {
 
 namespace {
 
-__device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p) {
-    uint32_t v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
-
-// Spins until *flag == want; false (and the status word set) after about a second.
-__device__ __forceinline__ bool wait_flag(const uint32_t *flag, uint32_t want, uint32_t *status) {
-    if (ld_acquire_sys(flag) == want) return true;
-    const uint64_t t0 = globaltimer_ns();
-    for (;;) {
-        for (int i = 0; i < 32; ++i)
-            if (ld_acquire_sys(flag) == want) return true;
-        if (globaltimer_ns() - t0 > 1000000000ull) {
-            atomicCAS(status, ST_OK, ST_PEER_TIMEOUT);
-            return false;
-        }
-    }
-}
-
 __device__ __forceinline__ float *recv_of(uint8_t *base, uint32_t slot, uint32_t rank) {
     return reinterpret_cast<float *>(base) + ((size_t)slot * kCommMaxRanks + rank) * kCommMaxVec;
 }
@@ -112,6 +89,23 @@ __global__ void __launch_bounds__(1024) allreduce_resid_kernel(const AllReduceAr
         }
         *reinterpret_cast<float4 *>(a.out + i) = acc;
     }
+}
+
+// The first half of the all-reduce alone: push this rank's chunk to every rank and publish the flags.
+// The kernel that consumes the sum (the next matvec's prologue) waits for the flags and adds.
+__global__ void __launch_bounds__(1024) allreduce_push_kernel(const AllReduceArgs a) {
+    griddep_launch_dependents();
+    griddep_wait();
+    const uint32_t tid = threadIdx.x, chunk = blockIdx.x;
+    const uint32_t i = (chunk * blockDim.x + tid) * 4;
+    const float4 mine = *reinterpret_cast<const float4 *>(a.in + i);
+    const uint32_t e = next_epoch(a.st.epoch + chunk), slot = e & 1u;
+    for (uint32_t k = 0; k < a.world; ++k) {
+        const uint32_t p = (a.rank + k) % a.world;
+        *reinterpret_cast<float4 *>(recv_of(a.peers[p], slot, a.rank) + i) = mine;
+    }
+    __syncthreads();
+    if (tid < a.world) st_release_sys(flag_of(a.peers[tid], slot, a.rank, chunk), e);
 }
 
 struct Top { float b; uint32_t i; float s; };
@@ -232,6 +226,13 @@ cudaError_t launch_allreduce_resid(const AllReduceArgs &a, cudaStream_t stream, 
         a.n % (4 * kCommChunks) != 0 || a.n / (4 * kCommChunks) > 1024)
         return cudaErrorInvalidValue;
     return launch_kernel(allreduce_resid_kernel, dim3(kCommChunks), dim3(a.n / (4 * kCommChunks)), 0, stream, pdl, a);
+}
+
+cudaError_t launch_allreduce_push(const AllReduceArgs &a, cudaStream_t stream, bool pdl) {
+    if (a.world < 1 || a.world > kCommMaxRanks || a.rank >= a.world || a.n == 0 || a.n > kCommMaxVec ||
+        a.n % (4 * kCommChunks) != 0 || a.n / (4 * kCommChunks) > 1024)
+        return cudaErrorInvalidValue;
+    return launch_kernel(allreduce_push_kernel, dim3(kCommChunks), dim3(a.n / (4 * kCommChunks)), 0, stream, pdl, a);
 }
 
 cudaError_t launch_argmax_exchange(const TopExchangeArgs &a, cudaStream_t stream, bool pdl) {

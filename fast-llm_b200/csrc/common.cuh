@@ -143,6 +143,29 @@ __device__ __forceinline__ void fence_acq_rel_gpu() {
     asm volatile("fence.acq_rel.gpu;" ::: "memory");
 }
 
+// System-scope release store / acquire load (flags that another GPU reads or writes).
+__device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+// Spins until *flag == want; false (and ST_PEER_TIMEOUT in the status word) after about a second.
+__device__ __forceinline__ bool wait_flag(const uint32_t *flag, uint32_t want, uint32_t *status) {
+    if (ld_acquire_sys(flag) == want) return true;
+    const uint64_t t0 = globaltimer_ns();
+    for (;;) {
+        for (int i = 0; i < 32; ++i)
+            if (ld_acquire_sys(flag) == want) return true;
+        if (globaltimer_ns() - t0 > 1000000000ull) {
+            atomicCAS(status, ST_OK, ST_PEER_TIMEOUT);
+            return false;
+        }
+    }
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

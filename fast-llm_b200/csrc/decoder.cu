@@ -119,12 +119,25 @@ static int enqueue_step(fl_b200_decoder *d, cudaStream_t s, uint32_t *n_launch, 
     const bool tp = d->tp_size > 1;
     const CommState cst{d->comm_state};
     // sum of the ranks' partial vectors + residual (the exchange step after O and after down)
+    // Two forms: one kernel that pushes, waits and adds (the default), or (FLB_TP_FUSED=1) a push-only
+    // kernel whose sum is taken by the prologue of the matvec that consumes it (one launch and one pass
+    // through memory less; the consumer's CTAs start while the pushes are still crossing NVLink).
+    static const bool fused = getenv("FLB_TP_FUSED") && getenv("FLB_TP_FUSED")[0] == '1';
+    struct { const float *resid; float *out; bool on; } pend = {nullptr, nullptr, false};
     auto do_allreduce = [&](const float *resid, float *out) -> int {
         AllReduceArgs r{};
         for (uint32_t p = 0; p < d->tp_size; ++p) r.peers[p] = d->peers[p];
         r.in = d->partial; r.resid = resid; r.out = out; r.n = E; r.rank = d->tp_rank; r.world = d->tp_size;
         r.st = cst; r.status = ctx->status;
-        return cuda_err(launch_allreduce_resid(r, s, kPdl != 0), "all-reduce launch");
+        if (!fused) return cuda_err(launch_allreduce_resid(r, s, kPdl != 0), "all-reduce launch");
+        pend.resid = resid; pend.out = out; pend.on = true;
+        return cuda_err(launch_allreduce_push(r, s, kPdl != 0), "all-reduce push launch");
+    };
+    auto take_pending = [&](MatvecArgs &a) {   // the matvec whose activation is the pending sum
+        if (!pend.on) return;
+        a.xr_buf = d->peers[d->tp_rank]; a.xr_epoch = d->comm_state; a.xr_resid = pend.resid; a.xr_out = pend.out;
+        a.xr_world = d->tp_size; a.x = pend.out;
+        pend.on = false;
     };
     if (mask & K_OTHER) { CK(launch_embed(d->tok_embd.fmt, d->tok_embd.w, d->d_token, E, d->xa, s, false)); ++n; }
     for (uint32_t l = 0; l < c.n_layer; ++l) {
@@ -137,6 +150,7 @@ static int enqueue_step(fl_b200_decoder *d, cudaStream_t s, uint32_t *n_launch, 
             a.t[2] = {w[FL_B200_T_WV].w, d->v, nullptr, KD, w[FL_B200_T_WV].fmt, 0};
             a.x = d->xa; a.wnorm = d->attn_norm[l]; a.eps = c.eps; a.cols = E;
             a.x_mode = MV_X_RMSNORM; a.status = ctx->status; a.pdl = kPdl;
+            take_pending(a);
             if (mask & K_MATVEC) { if (int rc = do_matvec(a)) return rc; ++n; }
         }
         {   // RoPE on q and k, the f16 append of k and v, and the attention itself: one kernel
@@ -169,6 +183,7 @@ static int enqueue_step(fl_b200_decoder *d, cudaStream_t s, uint32_t *n_launch, 
             a.x = d->xb; a.wnorm = d->ffn_norm[l]; a.eps = c.eps; a.cols = E;
             a.x_mode = MV_X_RMSNORM; a.status = ctx->status; a.pdl = kPdl;
             a.swiglu = w[FL_B200_T_GATE].fmt == w[FL_B200_T_UP].fmt ? 1 : 0;
+            take_pending(a);
             if (mask & K_MATVEC) { if (int rc = do_matvec(a)) return rc; ++n; }
             d->fused_swiglu = a.swiglu != 0;
         }
@@ -189,6 +204,7 @@ static int enqueue_step(fl_b200_decoder *d, cudaStream_t s, uint32_t *n_launch, 
         a.t[0] = {d->output.w, d->logits, nullptr, d->V, d->output.fmt, 0};
         a.x = d->xa; a.wnorm = d->out_norm; a.eps = c.eps; a.cols = E;
         a.x_mode = MV_X_RMSNORM; a.status = ctx->status; a.pdl = kPdl; a.xn_out = d->xn_final;
+        take_pending(a);
         if (mask & K_MATVEC) { if (int rc = do_matvec(a)) return rc; ++n; }
     }
     if (mask & K_OTHER) {

@@ -55,6 +55,16 @@ struct MatvecArgs {
     uint32_t *tickets;
     size_t scratch_floats, tickets_n;
     unsigned long long *trace;   // optional 4-entry timeline record of this launch (diagnostics)
+    // Tensor parallel: the activation is the sum of the ranks' partial vectors that an exchange launch
+    // (launch_allreduce_push) is delivering into this rank's exchange buffer, plus a residual:
+    // x = xr_resid + sum_r recv[r]. The kernel waits (bounded) for the ranks' flags of the epoch the
+    // push launch recorded, adds in rank order (identical bits on all ranks) and CTA 0 also stores the
+    // sum to xr_out (the new residual stream). nullptr: x is read as usual.
+    const uint8_t *xr_buf;
+    const uint32_t *xr_epoch;    // kCommChunks epoch counters of this rank's push launches
+    const float *xr_resid;
+    float *xr_out;
+    uint32_t xr_world;
 };
 
 // Streaming kernel (Q4_K / Q6_K, cols a multiple of 2048) or the generic
@@ -161,6 +171,8 @@ size_t lse_buffer_bytes(uint32_t max_records);
 cudaError_t launch_lse_combine(const LseCombineArgs &a, cudaStream_t stream);
 size_t comm_buffer_bytes(void);
 cudaError_t launch_allreduce_resid(const AllReduceArgs &a, cudaStream_t stream, bool pdl);
+// The push half alone (stores + flags; resid / out unused): the consumer matvec waits and adds.
+cudaError_t launch_allreduce_push(const AllReduceArgs &a, cudaStream_t stream, bool pdl);
 cudaError_t launch_argmax_exchange(const TopExchangeArgs &a, cudaStream_t stream, bool pdl);
 
 // ---- glue.cu ------------------------------------------------------------

@@ -321,6 +321,9 @@ __device__ __forceinline__ QuadRef locate_quad(const MatvecArgs &a, uint32_t qua
     return q;
 }
 
+// XR: the activation is the sum of the ranks' partial vectors arriving in the exchange buffer (tensor
+// parallel); a separate instantiation so that the single-GPU kernel does not pay for it in registers.
+template <bool XR>
 __global__ void __launch_bounds__(kMaxThreads, 1)
 matvec_stream_kernel(const MatvecArgs a, const __grid_constant__ TensorMaps maps, const uint32_t total_quads,
                      const int stages, const int use_q4, const int use_q6) {
@@ -406,7 +409,32 @@ matvec_stream_kernel(const MatvecArgs a, const __grid_constant__ TensorMaps maps
 #pragma unroll
     for (int b = 0; b < kMaxBlk; ++b) {
         const uint32_t blk = hw + b * nhw;
-        if (blk < nblk) {
+        if (XR && blk < nblk) {
+            // x = residual + the ranks' partial vectors, as they land in this rank's exchange buffer
+            const uint32_t c0 = blk * 256 + hl * 16;
+            const uint32_t chunk = c0 / (a.cols / kCommChunks);        // the lane's 16 columns lie in one chunk
+            const uint32_t e = __ldcg(a.xr_epoch + chunk), slot = e & 1u;
+            const float *recv = reinterpret_cast<const float *>(a.xr_buf) + (size_t)slot * kCommMaxRanks * kCommMaxVec;
+            const uint32_t *flags = reinterpret_cast<const uint32_t *>(a.xr_buf + kCommFlagsOff) +
+                                    (size_t)slot * kCommMaxRanks * kCommChunks + chunk;
+            const float4 *rs = reinterpret_cast<const float4 *>(a.xr_resid + c0);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) ra[b][k] = rs[k];
+            for (uint32_t r = 0; r < a.xr_world; ++r) {
+                if (!wait_flag(flags + r * kCommChunks, e, a.status)) break;   // status word set; the result is void
+                const float4 *pv = reinterpret_cast<const float4 *>(recv + (size_t)r * kCommMaxVec + c0);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const float4 v = __ldcg(pv + k);
+                    ra[b][k].x += v.x; ra[b][k].y += v.y; ra[b][k].z += v.z; ra[b][k].w += v.w;
+                }
+            }
+            if (blockIdx.x == 0) {
+                float4 *dst = reinterpret_cast<float4 *>(a.xr_out + c0);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) dst[k] = ra[b][k];
+            }
+        } else if (blk < nblk) {
             const float4 *src = reinterpret_cast<const float4 *>(a.x + blk * 256 + hl * 16);
 #pragma unroll
             for (int k = 0; k < 4; ++k) ra[b][k] = src[k];
@@ -684,7 +712,9 @@ cudaError_t matvec_init(void) {
         if (qres != cudaDriverEntryPointSuccess || !fn) return cudaErrorNotSupported;
         g_encode = (EncodeTiledFn)fn;
     }
-    return cudaFuncSetAttribute(matvec_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024 - 1024);
+    cudaError_t e = cudaFuncSetAttribute(matvec_stream_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024 - 1024);
+    if (e != cudaSuccess) return e;
+    return cudaFuncSetAttribute(matvec_stream_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024 - 1024);
 }
 
 // The packed tensor as [rows][row_bytes / 8] 8-byte elements, box = 4 rows x one segment.
@@ -764,11 +794,14 @@ cudaError_t launch_matvec(const MatvecArgs &a, int sms, cudaStream_t stream) {
                 const cudaError_t e = encode_map(&maps.m[i], a.t[i], a.cols, a.swiglu ? 2 : kRowsPerStage);
                 if (e != cudaSuccess) return e;
             }
-            return launch_kernel(matvec_stream_kernel, dim3(grid), dim3(warps * 32), smem, stream, a.pdl != 0, a, maps,
+            if (a.xr_buf)
+                return launch_kernel(matvec_stream_kernel<true>, dim3(grid), dim3(warps * 32), smem, stream, a.pdl != 0, a, maps,
+                                     total_quads, stages, q4 ? 1 : 0, q6 ? 1 : 0);
+            return launch_kernel(matvec_stream_kernel<false>, dim3(grid), dim3(warps * 32), smem, stream, a.pdl != 0, a, maps,
                                  total_quads, stages, q4 ? 1 : 0, q6 ? 1 : 0);
         }
     }
-    if (a.x_mode != MV_X_PLAIN) return cudaErrorInvalidValue;   // prologues exist only in the streaming kernel
+    if (a.x_mode != MV_X_PLAIN || a.xr_buf) return cudaErrorInvalidValue;   // prologues exist only in the streaming kernel
     uint32_t grid = (total_rows + 7) / 8;
     if (grid > (uint32_t)sms * 8) grid = (uint32_t)sms * 8;
     return launch_kernel(matvec_generic_kernel, dim3(grid), dim3(256), 0, stream, a.pdl != 0, a, total_rows);
