@@ -564,6 +564,12 @@ int fl_b200_argmax(fl_b200_ctx *c, const float *lg, uint32_t n, int32_t *idx, fl
                     "argmax launch");
 }
 
+// Host buffers for one parameter block: large enough for every POD below.
+constexpr size_t kAuxMax = 128;
+static_assert(sizeof(fl_b200_router_p) <= kAuxMax && sizeof(fl_b200_wmerge_p) <= kAuxMax && sizeof(fl_b200_rmsnorm_p) <= kAuxMax &&
+              sizeof(fl_b200_add2_p) <= kAuxMax && sizeof(fl_b200_silu_mul_p) <= kAuxMax &&
+              sizeof(fl_b200_attn_gqa_f16_p) <= kAuxMax && sizeof(fl_b200_rope_kv_append_f16_p) <= kAuxMax, "parameter block buffer");
+
 // Size of the parameter block behind Task::aux for a kind (0: none / not a parameter block).
 static size_t aux_bytes(int kind) {
     switch (kind) {
@@ -582,7 +588,7 @@ static size_t aux_bytes(int kind) {
 // (fetched here, with a stream synchronisation, when null).
 static int launch_task(fl_b200_ctx *c, const fl_b200_task *t, const void *aux_host) {
     if (!t) return set_err(FL_B200_ERR_ARG, "exec_task: null task");
-    uint8_t local[64];
+    alignas(8) uint8_t local[kAuxMax];
     const size_t ab = aux_bytes(t->kind);
     if (ab) {
         if (!t->aux) return set_err(FL_B200_ERR_ARG, "exec_task: decode op without aux param block");
@@ -704,7 +710,7 @@ int fl_b200_plan_create(fl_b200_ctx *c, const fl_b200_task *tasks, uint32_t n, f
         if (t.w_bytes != (uint64_t)t.rows * row_bytes(t.fmt, t.cols)) return set_err(FL_B200_ERR_ARG, "plan_create: task %u: STREAM_DOT w_bytes mismatch", i);
     }
     // --- parameter blocks to the host (one synchronisation), attention scratch sized before the capture ---
-    std::vector<std::array<uint8_t, 64>> aux(n);
+    std::vector<std::array<uint8_t, kAuxMax>> aux(n);
     CK(cudaSetDevice(c->device));
     for (uint32_t i = 0; i < n; ++i) {
         const size_t ab = aux_bytes(tasks[i].kind);

@@ -49,6 +49,8 @@ class Graph:
 
     # -- Graph::freeze + plan --
     def freeze(self):
+        import torch
+        torch.cuda.synchronize(self.ctx.device)   # the parameter blocks were uploaded on torch's stream
         arr = (capi.Task * len(self._tasks))(*self._tasks)
         capi._ck(self.lib.fl_b200_plan_create(self.ctx._h, arr, C.c_uint32(len(self._tasks)), C.byref(self._plan)))
         return self

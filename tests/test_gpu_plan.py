@@ -131,7 +131,7 @@ def test_layer_as_task_table(ctx, checker):
     t_end = g.add(capi.K_SIGNAL)
     g.edge(t_add2, t_end)
     g.freeze()
-    info = g.info()
+    info = g.info(); print("PLANINFO", info, "adj", d["wq"].data_ptr() + d["wq"].numel() == d["wk"].data_ptr(), q_d.data_ptr() + QD * 4 == k_d.data_ptr(), d["gate"].data_ptr() + d["gate"].numel() == d["up"].data_ptr(), g_d.data_ptr() + F * 4 == u_d.data_ptr(), k_d.data_ptr() + KD*4 == v_d.data_ptr())
     n_tiles = len(tq + tk + tv + to + tg + tu + td)
     assert info["tasks"] == len(g._tasks)
     # every tensor's tiles collapse into one launch: 7 matvecs + 2 norms + rope + attn + 2 adds + silu (two tensors
@@ -147,9 +147,6 @@ def test_layer_as_task_table(ctx, checker):
     kc2[:, POS] = kr.reshape(NKV, D).astype(np.float16); vc2[:, POS] = v.reshape(NKV, D).astype(np.float16)
     att = checker.attn_gqa_f16(qr.reshape(NH, D), kc2, vc2, POS + 1, scale).reshape(-1)
     x1 = checker.add2(x0, checker.matvec(fm["wo"], w["wo"], E, QD, att))
-    xn2 = checker.rmsnorm(fn, x1, 1e-5)
-    h = checker.silu_mul(checker.matvec(fm["gate"], w["gate"], F, E, xn2), checker.matvec(fm["up"], w["up"], F, E, xn2))
-    x2 = checker.add2(x1, checker.matvec(fm["down"], w["down"], E, F, h))
 
     for run in range(2):   # replay: the accumulate slots are zeroed per run, like the reference does
         for t_ in (q_d, k_d, v_d, o_d, g_d, u_d, dn_d):
@@ -160,8 +157,13 @@ def test_layer_as_task_table(ctx, checker):
         assert ctx.status() == 0
         assert rel(xn_d.cpu().numpy(), xn) < 1e-5
         assert rel(v_d.cpu().numpy(), v) < 1e-4
-        assert rel(x1_d.cpu().numpy(), x1) < 5e-3      # through the f16 append of this token's K / V
-        assert rel(x2_d.cpu().numpy(), x2) < 1e-2
+        x1g = x1_d.cpu().numpy()
+        assert rel(x1g, x1) < 5e-3      # through the f16 append of this token's K / V
+        # the FFN half from the device's own x1 (these synthetic weights amplify a 1e-3 input difference a hundredfold)
+        xn2g = checker.rmsnorm(fn, x1g, 1e-5)
+        hg = checker.silu_mul(checker.matvec(fm["gate"], w["gate"], F, E, xn2g), checker.matvec(fm["up"], w["up"], F, E, xn2g))
+        x2g = checker.add2(x1g, checker.matvec(fm["down"], w["down"], E, F, hg))
+        assert rel(x2_d.cpu().numpy(), x2g) < 2e-3
     g.close()
 
 
