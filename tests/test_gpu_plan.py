@@ -131,7 +131,7 @@ def test_layer_as_task_table(ctx, checker):
     t_end = g.add(capi.K_SIGNAL)
     g.edge(t_add2, t_end)
     g.freeze()
-    info = g.info(); print("PLANINFO", info, "adj", d["wq"].data_ptr() + d["wq"].numel() == d["wk"].data_ptr(), q_d.data_ptr() + QD * 4 == k_d.data_ptr(), d["gate"].data_ptr() + d["gate"].numel() == d["up"].data_ptr(), g_d.data_ptr() + F * 4 == u_d.data_ptr(), k_d.data_ptr() + KD*4 == v_d.data_ptr())
+    info = g.info()
     n_tiles = len(tq + tk + tv + to + tg + tu + td)
     assert info["tasks"] == len(g._tasks)
     # every tensor's tiles collapse into one launch: 7 matvecs + 2 norms + rope + attn + 2 adds + silu (two tensors
