@@ -48,6 +48,9 @@ struct MatvecArgs {
     uint32_t *status;     // device status word
     float *xn_out;        // optional: CTA 0 also writes the activation it built (nullptr: no)
     int pdl;              // launch with programmatic dependent launch (inside the decoder's step)
+    int issue_late;       // 1: request the first weight stages after the activation loads are in flight instead of
+                          // before the dependency wait (for launches whose CTAs only become resident when the previous
+                          // kernel's CTAs leave, so that nothing is gained by requesting early)
     // Streaming kernel only: partial row sums of units shared between warps and
     // their arrival counters (zero before the first launch; the kernel resets
     // them). Sized with matvec_scratch_need().

@@ -373,7 +373,7 @@ matvec_stream_kernel(const MatvecArgs a, const __grid_constant__ TensorMaps maps
     // (unless the expert to stream is itself a result of the previous kernel).
     if (tid == 0) trace_min(a.trace, 0);
     griddep_launch_dependents();
-    if (lane == 0 && !indirect)
+    if (lane == 0 && !indirect && !a.issue_late)
         while (p_i < (uint32_t)stages && p_i < my_stages) issue();
 
     // ---- build the fixed-point activation in shared memory ----
@@ -445,6 +445,8 @@ matvec_stream_kernel(const MatvecArgs a, const __grid_constant__ TensorMaps maps
             }
         }
     }
+    if (lane == 0 && a.issue_late && !indirect)
+        while (p_i < (uint32_t)stages && p_i < my_stages) issue();   // the activation loads are in flight meanwhile
     // RMSNorm: the digits are those of x*w (the common factor 1/rms is applied to
     // the row sums at the end), so the sum of squares and the quantisation need
     // only one block-wide barrier between them and the consumers.
