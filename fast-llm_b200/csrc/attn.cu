@@ -121,10 +121,14 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_decode_kernel(const __gr
         fence_barrier_init();
     }
     if (fused && tid < kD / 2) {
-        // angle of pair i: pos * theta_scale^i by repeated multiplication (bit-identical to the reference)
-        float theta = (float)(int32_t)(kv_len - 1u);
-        for (uint32_t k = 0; k < tid; ++k) theta = __fmul_rn(theta, a.theta_scale);
-        sm.cs[tid] = make_float2(cosf(theta), sinf(theta));
+        if (a.rope_table) {
+            sm.cs[tid] = a.rope_table[tid];   // computed once per step, before this launch's predecessors
+        } else {
+            // angle of pair i: pos * theta_scale^i by repeated multiplication (bit-identical to the reference)
+            float theta = (float)(int32_t)(kv_len - 1u);
+            for (uint32_t k = 0; k < tid; ++k) theta = __fmul_rn(theta, a.theta_scale);
+            sm.cs[tid] = make_float2(cosf(theta), sinf(theta));
+        }
     }
     __syncthreads();
 

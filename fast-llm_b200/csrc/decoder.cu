@@ -66,6 +66,7 @@ struct fl_b200_decoder {
     bool peers_set = false;
     uint32_t *comm_state = nullptr;         // epoch counters of the exchange kernels
     float *partial = nullptr, *top3 = nullptr;
+    float2 *rope_table = nullptr;           // (cos, sin) of this step's position, shared by all layers
     std::vector<Tensor> lw;                 // n_layer * 7
     std::vector<const float *> attn_norm, ffn_norm;
     Tensor tok_embd, output;
@@ -142,6 +143,8 @@ static int enqueue_step(fl_b200_decoder *d, cudaStream_t s, uint32_t *n_launch, 
         a.xr_world = d->tp_size; a.x = pend.out;
         pend.on = false;
     };
+    const float theta_scale = powf(c.rope_base, -2.0f / (float)D);
+    if (mask & K_OTHER) { CK(launch_rope_table(d->d_pos, theta_scale, D, d->rope_table, s)); ++n; }
     if (mask & K_OTHER) { CK(launch_embed(d->tok_embd.fmt, d->tok_embd.w, d->d_token, E, d->xa, s, false)); ++n; }
     for (uint32_t l = 0; l < c.n_layer; ++l) {
         const Tensor *w = &d->lw[(size_t)l * 7];
@@ -159,7 +162,7 @@ static int enqueue_step(fl_b200_decoder *d, cudaStream_t s, uint32_t *n_launch, 
         {   // RoPE on q and k, the f16 append of k and v, and the attention itself: one kernel
             AttnArgs a{};
             a.rope_k = d->k; a.rope_v = d->v; a.k_append = d->kc[l]; a.v_append = d->vc[l];
-            a.theta_scale = powf(c.rope_base, -2.0f / (float)D);
+            a.theta_scale = theta_scale; a.rope_table = d->rope_table;
             a.q = d->q; a.k = d->kc[l]; a.v = d->vc[l]; a.out = d->att; a.part = d->part; a.tickets = d->tickets;
             a.pos = d->d_pos; a.kv_len = 0; a.kv_stride = c.max_kv;
             a.batch_stride = (uint64_t)d->Hkv * c.max_kv * D;
@@ -302,6 +305,7 @@ int fl_b200_decoder_create_tp(fl_b200_ctx *ctx, const fl_b200_llama_cfg *cfg, ui
     CK(cudaMalloc(&d->u, d->F * 4));
     CK(cudaMalloc(&d->logits, (size_t)d->V * 4));
     CK(cudaMalloc(&d->top3, 16));
+    CK(cudaMalloc(&d->rope_table, (c.head_dim / 2) * sizeof(float2)));
     if (world > 1) {
         CK(cudaMalloc(&d->comm, comm_buffer_bytes()));
         CK(cudaMemsetAsync(d->comm, 0, comm_buffer_bytes(), ctx->stream));
@@ -331,7 +335,7 @@ void fl_b200_decoder_destroy(fl_b200_decoder *d) {
     cudaFree(d->d_token); cudaFree(d->d_hist); cudaFree(d->d_forced); cudaFree(d->xa); cudaFree(d->xb); cudaFree(d->q);
     cudaFree(d->k); cudaFree(d->v); cudaFree(d->att); cudaFree(d->g); cudaFree(d->u); cudaFree(d->logits);
     cudaFree(d->xn_final); cudaFree(d->part); cudaFree(d->tickets);
-    cudaFree(d->top3); cudaFree(d->comm); cudaFree(d->comm_state); cudaFree(d->partial);
+    cudaFree(d->top3); cudaFree(d->rope_table); cudaFree(d->comm); cudaFree(d->comm_state); cudaFree(d->partial);
     free_matvec_scratch(d->mv);
     cudaFree(d->trace);
     cudaFreeHost(d->h_pin);

@@ -151,6 +151,14 @@ __global__ void __launch_bounds__(128) rope_append_kernel(const RopeAppendArgs a
     }
 }
 
+__global__ void rope_table_kernel(const int32_t *pos, float theta_scale, uint32_t half, float2 *table) {
+    const uint32_t i = threadIdx.x;
+    if (i >= half) return;
+    float theta = (float)*pos;
+    for (uint32_t k = 0; k < i; ++k) theta = __fmul_rn(theta, theta_scale);
+    table[i] = make_float2(cosf(theta), sinf(theta));
+}
+
 // Greedy argmax: strict '>' scan order of the reference (lowest index wins
 // ties) and the runner-up value for the margin (src/model/decoder.cpp:1253-1264).
 struct Top { float b; uint32_t i; float s; };
@@ -256,6 +264,12 @@ cudaError_t launch_rope_append(const RopeAppendArgs &a, cudaStream_t stream) {
     const uint32_t half = a.head_dim / 2;
     const uint32_t n = ((a.q ? a.n_q_head : 0) + 2 * a.n_kv_head) * half;
     return launch_kernel(rope_append_kernel, dim3((n + 127) / 128), dim3(128), 0, stream, a.pdl != 0, a);
+}
+
+cudaError_t launch_rope_table(const int32_t *pos, float theta_scale, uint32_t head_dim, float2 *table, cudaStream_t stream) {
+    if (head_dim == 0 || (head_dim & 1u) || head_dim > 2048) return cudaErrorInvalidValue;
+    rope_table_kernel<<<1, head_dim / 2, 0, stream>>>(pos, theta_scale, head_dim / 2, table);
+    return cudaGetLastError();
 }
 
 cudaError_t launch_argmax(const float *logits, uint32_t n, int32_t *out_idx, float *out_margin,

@@ -113,6 +113,8 @@ struct AttnArgs {
     const float *rope_k, *rope_v;   // nullptr: q is already rotated and the cache is complete
     __half *k_append, *v_append;
     float theta_scale;              // freq_base^(-2/128)
+    const float2 *rope_table;       // optional: (cos, sin) of the 64 angles of position *pos, computed once per step
+                                    // (launch_rope_table); nullptr: every CTA computes them itself
     CUtensorMap kmap, vmap;         // filled by attn_make_maps
 };
 cudaError_t attn_make_maps(AttnArgs &a);
@@ -202,6 +204,9 @@ struct RopeAppendArgs {
     int pdl;
 };
 cudaError_t launch_rope_append(const RopeAppendArgs &a, cudaStream_t stream);
+// (cos, sin) of pos * theta_scale^i, i < head_dim / 2, with the angle built by repeated multiplication exactly as
+// fl_op_rope_ds2 does (src/runtime/decode_params.h:124-160); table: head_dim / 2 float2.
+cudaError_t launch_rope_table(const int32_t *pos, float theta_scale, uint32_t head_dim, float2 *table, cudaStream_t stream);
 // Greedy argmax with the reference's tie rule (lowest index) and the
 // top1 - top2 margin. out_idx: int32, out_margin: float; scratch: 2*blocks*2 floats.
 cudaError_t launch_argmax(const float *logits, uint32_t n, int32_t *out_idx, float *out_margin,
