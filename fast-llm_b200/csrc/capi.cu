@@ -27,44 +27,6 @@ int cuda_err(cudaError_t e, const char *what) {
     return set_err(FL_B200_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
 }
 
-int ensure_matvec_scratch(fl_b200_ctx *c, MatvecScratch &s, MatvecArgs &a) {
-    size_t nf = 0, nt = 0;
-    matvec_scratch_need(a, c->sms, &nf, &nt);
-    if (nf > s.cap || nt > s.tickets_cap) {
-        cudaError_t e = cudaStreamSynchronize(c->stream);
-        if (e != cudaSuccess) return cuda_err(e, "sync before growing matvec scratch");
-        if (nf > s.cap) {
-            cudaFree(s.buf);
-            s.buf = nullptr;
-            s.cap = 0;
-            e = cudaMalloc(&s.buf, nf * sizeof(float));
-            if (e != cudaSuccess) return cuda_err(e, "cudaMalloc matvec scratch");
-            s.cap = nf;
-        }
-        if (nt > s.tickets_cap) {
-            cudaFree(s.tickets);
-            s.tickets = nullptr;
-            s.tickets_cap = 0;
-            e = cudaMalloc(&s.tickets, nt * sizeof(uint32_t));
-            if (e != cudaSuccess) return cuda_err(e, "cudaMalloc matvec tickets");
-            e = cudaMemset(s.tickets, 0, nt * sizeof(uint32_t));
-            if (e != cudaSuccess) return cuda_err(e, "cudaMemset matvec tickets");
-            s.tickets_cap = nt;
-        }
-    }
-    a.scratch = s.buf;
-    a.tickets = s.tickets;
-    a.scratch_floats = s.cap;
-    a.tickets_n = s.tickets_cap;
-    return FL_B200_OK;
-}
-
-void free_matvec_scratch(MatvecScratch &s) {
-    cudaFree(s.buf);
-    cudaFree(s.tickets);
-    s = MatvecScratch();
-}
-
 } // namespace flb
 
 using namespace flb;
@@ -109,7 +71,6 @@ int fl_b200_create(int device, fl_b200_ctx **out) {
     CK(cudaMemset(c->attn_tickets, 0, c->attn_tickets_cap * sizeof(uint32_t)));
     CK(cudaMalloc(&c->argmax_scratch, (size_t)3 * 1024 * sizeof(float)));
     CK(cudaMalloc(&c->small, 64));
-    c->mv = reinterpret_cast<MatvecScratchFwd *>(new MatvecScratch());
     CK(matvec_init());
     CK(attn_init());
     *out = c;
@@ -126,7 +87,6 @@ void fl_b200_destroy(fl_b200_ctx *c) {
     cudaFree(c->small);
     cudaFree(c->status);
     cudaFree(c->stage);
-    if (c->mv) { free_matvec_scratch(*reinterpret_cast<MatvecScratch *>(c->mv)); delete reinterpret_cast<MatvecScratch *>(c->mv); }
     cudaEventDestroy(c->ev0);
     cudaEventDestroy(c->ev1);
     cudaStreamDestroy(c->stream);
@@ -267,7 +227,6 @@ static int matvec_impl(fl_b200_ctx *c, int fmt, const void *w, uint32_t rows, ui
         a.x_mode = MV_X_PLAIN;
         a.accumulate = accumulate;
         a.status = c->status;
-        if (int rc = ensure_matvec_scratch(c, *reinterpret_cast<MatvecScratch *>(c->mv), a)) return rc;
         if (int rc = cuda_err(launch_matvec(a, c->sms, c->stream), "matvec launch")) return rc;
     }
     return FL_B200_OK;

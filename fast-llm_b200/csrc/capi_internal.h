@@ -17,7 +17,6 @@ struct fl_b200_ctx {
     size_t attn_part_cap = 0;
     float *argmax_scratch = nullptr;
     void *small = nullptr;
-    struct MatvecScratchFwd *mv = nullptr;   // scratch of ad-hoc matvec calls (MatvecScratch)
     void *stage = nullptr;               // device staging for the *_host entry points
     size_t stage_cap = 0;
 };
@@ -25,16 +24,4 @@ struct fl_b200_ctx {
 namespace flb {
 int set_err(int code, const char *fmt, ...);
 int cuda_err(cudaError_t e, const char *what);
-// Scratch of the streaming matvec: partial row sums of units shared between
-// warps and their arrival counters (zero between launches).
-struct MatvecScratch {
-    float *buf = nullptr;
-    size_t cap = 0;          // floats
-    uint32_t *tickets = nullptr;
-    size_t tickets_cap = 0;
-};
-// Grows the scratch for this launch if needed (synchronises; not allowed during
-// stream capture) and points the arguments at it.
-int ensure_matvec_scratch(fl_b200_ctx *c, MatvecScratch &s, MatvecArgs &a);
-void free_matvec_scratch(MatvecScratch &s);
 } // namespace flb

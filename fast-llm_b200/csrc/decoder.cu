@@ -81,7 +81,6 @@ struct fl_b200_decoder {
     float *xa = nullptr, *xb = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *att = nullptr;
     float *g = nullptr, *u = nullptr, *logits = nullptr, *xn_final = nullptr, *part = nullptr;
     uint32_t *tickets = nullptr;
-    MatvecScratch mv;                       // scratch of the step's matvec launches (sized before capture)
     bool fused_swiglu = false;              // the gate/up launch writes silu(gate)*up into g
     unsigned long long *trace = nullptr;    // FLB_TRACE=1: 4 device timestamps per launch of the step
     uint32_t trace_n = 0;
@@ -105,18 +104,12 @@ static int issue_late() { static const int v = getenv("FLB_ISSUE_LATE") ? atoi(g
 // Kernel classes, for timing one class of the step in isolation.
 enum : uint32_t { K_MATVEC = 1u, K_ATTN = 2u, K_OTHER = 4u, K_COMM = 8u, K_ALL = 15u };
 
-// dry = true: no launches, only grows the context's matvec scratch to what the
-// step's launches need (must run before the step is captured).
-static int enqueue_step(fl_b200_decoder *d, cudaStream_t s, uint32_t *n_launch, uint32_t mask = K_ALL,
-                        bool dry = false) {
+static int enqueue_step(fl_b200_decoder *d, cudaStream_t s, uint32_t *n_launch, uint32_t mask = K_ALL) {
     uint32_t n = 0;   // launches so far
     auto do_matvec = [&](MatvecArgs &a) -> int {
         if (d->trace && mask == K_ALL) a.trace = d->trace + 4 * (size_t)n;
-        if (int rc = ensure_matvec_scratch(d->ctx, d->mv, a)) return rc;
-        if (dry) return FL_B200_OK;
         return cuda_err(launch_matvec(a, d->ctx->sms, s), "matvec launch");
     };
-    if (dry) mask = K_MATVEC;
     const fl_b200_llama_cfg &c = d->c;
     fl_b200_ctx *ctx = d->ctx;
     const uint32_t E = c.n_embd, D = c.head_dim, QD = d->Hq * D, KD = d->Hkv * D;
@@ -261,8 +254,8 @@ int fl_b200_decoder_create_tp(fl_b200_ctx *ctx, const fl_b200_llama_cfg *cfg, ui
         return set_err(FL_B200_ERR_ARG, "decoder_create: %u heads over %u KV heads (only groups of 4 are built)", c.n_head, c.n_kv_head);
     if (c.n_layer == 0 || c.n_embd == 0 || c.n_ff == 0 || c.n_vocab == 0 || c.max_kv == 0)
         return set_err(FL_B200_ERR_ARG, "decoder_create: zero-sized dimension");
-    if (c.n_embd % 2048 || c.n_ff % 2048 || (c.n_head * c.head_dim) % 2048)
-        return set_err(FL_B200_ERR_ARG, "decoder_create: n_embd, n_ff and n_head*head_dim must be multiples of 2048");
+    if (c.n_embd % 256 || c.n_ff % 256 || c.n_embd < 512 || c.n_ff < 512)
+        return set_err(FL_B200_ERR_ARG, "decoder_create: n_embd and n_ff must be multiples of 256 (>= 512)");
     fl_b200_decoder *d = new fl_b200_decoder();
     d->ctx = ctx;
     d->c = c;
@@ -336,7 +329,6 @@ void fl_b200_decoder_destroy(fl_b200_decoder *d) {
     cudaFree(d->k); cudaFree(d->v); cudaFree(d->att); cudaFree(d->g); cudaFree(d->u); cudaFree(d->logits);
     cudaFree(d->xn_final); cudaFree(d->part); cudaFree(d->tickets);
     cudaFree(d->top3); cudaFree(d->rope_table); cudaFree(d->comm); cudaFree(d->comm_state); cudaFree(d->partial);
-    free_matvec_scratch(d->mv);
     cudaFree(d->trace);
     cudaFreeHost(d->h_pin);
     delete d;
@@ -433,7 +425,6 @@ int fl_b200_decoder_finalize(fl_b200_decoder *d) {
             CK(cudaMalloc(&d->trace, (size_t)d->trace_n * 4 * sizeof(unsigned long long)));
         }
     }
-    if (int rc0 = enqueue_step(d, s, nullptr, K_MATVEC, true)) return rc0;   // size the scratch before capturing
     CK(cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal));
     uint32_t n = 0;
     int rc = enqueue_step(d, s, &n);

@@ -51,12 +51,6 @@ struct MatvecArgs {
     int issue_late;       // 1: request the first weight stages after the activation loads are in flight instead of
                           // before the dependency wait (for launches whose CTAs only become resident when the previous
                           // kernel's CTAs leave, so that nothing is gained by requesting early)
-    // Streaming kernel only: partial row sums of units shared between warps and
-    // their arrival counters (zero before the first launch; the kernel resets
-    // them). Sized with matvec_scratch_need().
-    float *scratch;
-    uint32_t *tickets;
-    size_t scratch_floats, tickets_n;
     unsigned long long *trace;   // optional 4-entry timeline record of this launch (diagnostics)
     // Tensor parallel: the activation is the sum of the ranks' partial vectors that an exchange launch
     // (launch_allreduce_push) is delivering into this rank's exchange buffer, plus a residual:
@@ -70,7 +64,7 @@ struct MatvecArgs {
     uint32_t xr_world;
 };
 
-// Streaming kernel (Q4_K / Q6_K, cols a multiple of 2048) or the generic
+// Streaming kernel (Q4_K / Q6_K, cols a multiple of 256 and >= 512, rows 16-byte pitched) or the generic
 // kernel (every other supported shape). Returns cudaErrorInvalidValue for
 // unsupported arguments.
 // 2-D tiled TMA descriptor over a row-major array (rows x dim0 elements, row pitch stride_bytes).
@@ -85,7 +79,6 @@ bool matvec_is_streaming(int fmt, uint32_t cols);
 // Dynamic shared memory the streaming kernel needs for (cols, formats used).
 size_t matvec_smem_bytes(uint32_t cols, bool use_q4k, bool use_q6k, int *stages_out, int *warps_out);
 cudaError_t matvec_init(void);   // sets the dynamic shared memory attribute once
-void matvec_scratch_need(const MatvecArgs &a, int sms, size_t *scratch_floats, size_t *tickets);
 
 // ---- attn.cu ------------------------------------------------------------
 struct AttnArgs {
@@ -93,7 +86,7 @@ struct AttnArgs {
     const __half *k;       // [batch][n_kv_head][kv_stride][128] f16
     const __half *v;       // same layout
     float *out;            // [batch][n_q_head][128]
-    float *part;           // scratch: [batch][n_q_head][n_splits][130]
+    float *part;           // scratch: [batch][n_q_head][n_splits][132] (context[128], max, sum, pad)
     uint32_t *tickets;     // scratch: [batch][n_kv_head], zero before first use; self-resetting
     const int32_t *pos;    // device scalar: last valid position (kv_len = *pos + 1); nullptr -> kv_len
     uint32_t kv_len;       // used when pos == nullptr

@@ -2,16 +2,17 @@
 // warp-per-row gdot_q4_K / gdot_q6_K / gdot_q8_0, src/runtime/kernels_gpu.h:65-205,
 // and the STREAM_DOT branch of exec_task_block, src/runtime/gpu_exec.cu:64-140).
 //
-// Streaming kernel (Q4_K and Q6_K, cols a multiple of 2048)
+// Streaming kernel (Q4_K and Q6_K, cols a multiple of 256)
 // ---------------------------------------------------------
 // HBM-bound by design: every packed weight byte is read exactly once. Each warp
 // owns a private ring of shared-memory stages that its lane 0 keeps filled with
-// 1-D bulk copies (TMA engine, completion on an mbarrier), so the bytes in
-// flight per SM do not depend on registers and no warp synchronises with
-// another one.
+// 2-D TMA box loads (cp.async.bulk.tensor.2d over a [rows][row bytes / 8]
+// view of the packed tensor, completion on an mbarrier), so the bytes in flight
+// per SM do not depend on registers and no warp synchronises with another one.
 //   stage  = the same 8-super-block column segment (2048 weights) of 4
-//            consecutive rows (a "row quad"): 4 x 1152 B (Q4_K) or 4 x 1680 B
-//            (Q6_K), each a contiguous, 16-byte aligned slice of a packed row;
+//            consecutive rows (a "row quad"): one box of 4 x 1152 B (Q4_K) or
+//            4 x 1680 B (Q6_K); a last partial segment and rows past the end
+//            of the tensor are filled with zeros by the TMA unit;
 //   lane   = one quarter of a super-block (64 weights) of each of the 4 rows:
 //            block = lane/4, quarter = lane%4. The activation slice a lane
 //            needs is the same for the 4 rows: it is read from shared memory
@@ -37,7 +38,7 @@
 // (RMSNorm) or from gate/up (SiLU * up), which removes those launches.
 //
 // Generic kernel: any other shape / format (Q8_0, Q5_0, F32, cols not a
-// multiple of 2048): warp per row, element-wise f32.
+// multiple of 256, rows not 16-byte pitched): warp per row, element-wise f32.
 #include "common.cuh"
 #include "kernels.h"
 
@@ -139,11 +140,6 @@ __device__ __forceinline__ Smem carve(uint8_t *base, uint32_t cols, bool q4, boo
 __device__ __forceinline__ uint4 lds128(uint32_t addr) {
     uint4 v;
     asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
-    return v;
-}
-__device__ __forceinline__ uint2 lds64(uint32_t addr) {
-    uint2 v;
-    asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
     return v;
 }
 __device__ __forceinline__ uint32_t lds32(uint32_t addr) {
@@ -691,7 +687,6 @@ size_t matvec_smem_bytes(uint32_t cols, bool q4, bool q6, int *stages_out, int *
     const size_t limit = 227 * 1024 - 1024;   // leave room for static shared memory
     const size_t slot = q6 ? kStage6 : kStage4;
     int warps = kMaxWarps;
-    if (const char *e = getenv("FLB_MV_WARPS")) { const int w = atoi(e); if (w >= 1 && w <= kMaxWarps) warps = w; }
     while (warps > kMinWarps && fixed + (size_t)warps * 2 * (8 + slot) > limit) --warps;
     int stages = 4;
     while (stages > 1 && fixed + (size_t)warps * stages * (8 + slot) > limit) --stages;
@@ -752,12 +747,6 @@ cudaError_t tensor_map_2d(CUtensorMap *m, uint32_t elem_bytes, const void *base,
                                 swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
                                 CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
-}
-
-// The streaming kernel assigns whole row quads to warps and needs no scratch.
-void matvec_scratch_need(const MatvecArgs &, int, size_t *scratch_floats, size_t *tickets) {
-    *scratch_floats = 0;
-    *tickets = 0;
 }
 
 cudaError_t launch_matvec(const MatvecArgs &a, int sms, cudaStream_t stream) {
