@@ -77,7 +77,7 @@ cudaError_t launch_matvec_mma(const MatvecArgs &a, int sms, cudaStream_t stream)
 // True when launch_matvec would take the streaming kernel for this shape.
 bool matvec_is_streaming(int fmt, uint32_t cols);
 // Dynamic shared memory the streaming kernel needs for (cols, formats used).
-size_t matvec_smem_bytes(uint32_t cols, bool use_q4k, bool use_q6k, int *stages_out, int *warps_out);
+size_t matvec_smem_bytes(uint32_t cols, bool use_q4k, bool use_q6k, int *stages_out, int *warps_out, bool use_q8_0 = false);
 cudaError_t matvec_init(void);   // sets the dynamic shared memory attribute once
 
 // ---- attn.cu ------------------------------------------------------------

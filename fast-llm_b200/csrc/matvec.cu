@@ -58,6 +58,9 @@ constexpr uint32_t kSeg4 = 8 * 144;   // bytes of one Q4_K segment (8 super-bloc
 constexpr uint32_t kSeg6 = 8 * 210;   // bytes of one Q6_K segment
 constexpr uint32_t kStage4 = kRowsPerStage * kSeg4;       // ring slot size, Q4_K only
 constexpr uint32_t kStage6 = (kRowsPerStage * kSeg6 + 127u) & ~127u;   // ring slot size when Q6_K is present (128-byte aligned for TMA)
+constexpr uint32_t kSeg8 = 64 * 34;   // bytes of one Q8_0 segment (64 blocks of 32 weights = 2048 columns)
+constexpr uint32_t kHalf8 = kSeg8 / 2;                    // a TMA box is at most 256 eight-byte elements wide: two boxes per segment
+constexpr uint32_t kStage8 = kRowsPerStage * kSeg8;       // ring slot size, Q8_0 only: [half][row][1088 bytes]
 constexpr float kFixMax = 1040000.0f; // largest fixed-point magnitude (63*2^14 + 63*2^7 + 63 = 1040447)
 
 // byte K of w as a float, without the integer->float conversion pipe: the byte
@@ -262,6 +265,30 @@ __device__ __forceinline__ float q6k_quarter(uint32_t row, uint32_t sbi, uint32_
     return d * t;
 }
 
+// Q8_0: the lane's 64 columns are two blocks of 34 bytes (f16 d + 32 int8), 68 bytes from `blk` (4-byte
+// aligned). The first block's quants start 2 bytes into a word and are realigned with byte permutes.
+// Value in units of the block's activation scale. Same digit-plane layout as Q4_K (16 columns per slot).
+__device__ __forceinline__ float q8_0_pair(uint32_t blk, const XSlots &xq) {
+    uint32_t w[17];
+#pragma unroll
+    for (int i = 0; i < 17; ++i) w[i] = lds32(blk + 4 * i);
+    int a0 = 0, a1 = 0, a2 = 0, b0 = 0, b1 = 0, b2 = 0;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        const int qa = (int)__byte_perm(w[k], w[k + 1], 0x5432u);   // bytes 2, 3 of word k, then 0, 1 of word k + 1
+        const int qb = (int)w[9 + k];
+        const int part = k >> 2, wi = k & 3;
+        a0 = __dp4a(qa, (int)word_of(xq.v[0 + part], wi), a0);
+        a1 = __dp4a(qa, (int)word_of(xq.v[4 + part], wi), a1);
+        a2 = __dp4a(qa, (int)word_of(xq.v[8 + part], wi), a2);
+        b0 = __dp4a(qb, (int)word_of(xq.v[2 + part], wi), b0);
+        b1 = __dp4a(qb, (int)word_of(xq.v[6 + part], wi), b1);
+        b2 = __dp4a(qb, (int)word_of(xq.v[10 + part], wi), b2);
+    }
+    const float d0 = h2f_bits((uint16_t)(w[0] & 0xFFFFu)), d1 = h2f_bits((uint16_t)(w[8] >> 16));
+    return d0 * fix_to_float(a0, a1, a2) + d1 * fix_to_float(b0, b1, b2);
+}
+
 // ---- the streaming kernel ---------------------------------------------------
 
 // One TMA descriptor per tensor of the launch: the packed tensor as a 2-D array
@@ -322,13 +349,13 @@ __device__ __forceinline__ QuadRef locate_quad(const MatvecArgs &a, uint32_t qua
 template <bool XR>
 __global__ void __launch_bounds__(kMaxThreads, 1)
 matvec_stream_kernel(const MatvecArgs a, const __grid_constant__ TensorMaps maps, const uint32_t total_quads,
-                     const int stages, const int use_q4, const int use_q6) {
+                     const int stages, const int use_q4, const int use_q6, const int use_q8) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     const uint32_t nw = blockDim.x >> 5;   // warps of this launch
-    const Smem sm = carve(smem_raw, a.cols, use_q4 != 0, use_q6 != 0, stages, nw);
+    const Smem sm = carve(smem_raw, a.cols, use_q4 != 0, use_q6 != 0, stages, nw);   // Q8_0 uses the Q4_K plane layout (use_q4 is set)
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
     const uint32_t nseg = (a.cols + 2047u) / 2048u;   // the last segment may be partial: the TMA unit fills the rest with zeros
-    const uint32_t stage_bytes = use_q6 ? kStage6 : kStage4;
+    const uint32_t stage_bytes = use_q8 ? kStage8 : use_q6 ? kStage6 : kStage4;
     __shared__ float red[kMaxWarps];
 
     bool indirect = false;
@@ -352,6 +379,16 @@ matvec_stream_kernel(const MatvecArgs a, const __grid_constant__ TensorMaps maps
     QuadRef pq;
     auto issue = [&]() {   // lane 0 only; requests stage p_i and advances
         if (p_seg == 0) pq = locate_quad(a, p_quad);
+        if (use_q8) {   // two boxes of 4 rows x 1088 bytes: the halves of the segment
+            mbar_arrive_expect_tx(&bars[p_slot], kStage8);
+            tma_load_box(ring + p_slot * stage_bytes, &maps.m[pq.ti], p_seg * (kSeg8 / 8), pq.r0, &bars[p_slot]);
+            tma_load_box(ring + p_slot * stage_bytes + kRowsPerStage * kHalf8, &maps.m[pq.ti], p_seg * (kSeg8 / 8) + kHalf8 / 8, pq.r0,
+                         &bars[p_slot]);
+            ++p_i;
+            if (++p_slot == (uint32_t)stages) p_slot = 0;
+            if (++p_seg == nseg) { p_seg = 0; p_quad += W; }
+            return;
+        }
         const uint32_t sb = pq.fmt == FMT_Q4_K ? kSeg4 : kSeg6;
         mbar_arrive_expect_tx(&bars[p_slot], kRowsPerStage * sb);
         // rows past the end of the tensor are filled with zeros by the TMA unit (their results are dropped)
@@ -546,7 +583,13 @@ matvec_stream_kernel(const MatvecArgs a, const __grid_constant__ TensorMaps maps
         if (seg == 0) cur = locate_quad(a, quad);
         const float xs = sm.xs[seg * 8 + sbi];
         const uint32_t st = ring + slot * stage_bytes;
-        if (cur.fmt == FMT_Q4_K) {
+        if (use_q8) {
+            const XSlots xq = load_slots(q4_addr, seg, lane);
+            if (!mbar_wait_bounded(&bars[slot], parity, a.status)) return;
+            const uint32_t base = st + (lane >> 4) * (kRowsPerStage * kHalf8) + (lane & 15u) * 68u;
+#pragma unroll
+            for (int r = 0; r < kRowsPerStage; ++r) acc[r] = fmaf(xs, q8_0_pair(base + r * kHalf8, xq), acc[r]);
+        } else if (cur.fmt == FMT_Q4_K) {
             const XSlots xq = load_slots(q4_addr, seg, lane);
             const float2 sx = reinterpret_cast<const float2 *>(sm.s4)[seg * 32 + lane];
             if (!mbar_wait_bounded(&bars[slot], parity, a.status)) return;
@@ -676,16 +719,16 @@ __global__ void __launch_bounds__(256) matvec_generic_kernel(const MatvecArgs a,
 } // namespace
 
 bool matvec_is_streaming(int fmt, uint32_t cols) {
-    return (fmt == FMT_Q4_K || fmt == FMT_Q6_K) && cols >= 512 && cols % 256 == 0;
+    return (fmt == FMT_Q4_K || fmt == FMT_Q6_K || fmt == FMT_Q8_0) && cols >= 512 && cols % 256 == 0;
 }
 
 // Shared memory of a launch and its shape: as many warps as fit with two ring
 // stages each (more warps hide more latency of the issue-bound unpack loop than
 // a third stage does), then as many stages as still fit.
-size_t matvec_smem_bytes(uint32_t cols, bool q4, bool q6, int *stages_out, int *warps_out) {
-    const size_t fixed = smem_fixed_bytes(cols, q4, q6) + 8 + 128;   // + alignment slack
+size_t matvec_smem_bytes(uint32_t cols, bool q4, bool q6, int *stages_out, int *warps_out, bool q8) {
+    const size_t fixed = smem_fixed_bytes(cols, q4 || q8, q6) + 8 + 128;   // + alignment slack
     const size_t limit = 227 * 1024 - 1024;   // leave room for static shared memory
-    const size_t slot = q6 ? kStage6 : kStage4;
+    const size_t slot = q8 ? kStage8 : q6 ? kStage6 : kStage4;
     int warps = kMaxWarps;
     while (warps > kMinWarps && fixed + (size_t)warps * 2 * (8 + slot) > limit) --warps;
     int stages = 4;
@@ -718,7 +761,7 @@ cudaError_t matvec_init(void) {
 static cudaError_t encode_map(CUtensorMap *m, const MatvecTensor &t, uint32_t cols, uint32_t box_rows) {
     if (!g_encode) return cudaErrorNotSupported;
     const uint64_t rb = t.pitch ? t.pitch : row_bytes(t.fmt, cols);   // a multiple of 16 (checked by the caller)
-    const uint32_t seg = t.fmt == FMT_Q4_K ? kSeg4 : kSeg6;
+    const uint32_t seg = t.fmt == FMT_Q4_K ? kSeg4 : t.fmt == FMT_Q8_0 ? kHalf8 : kSeg6;
     // With expert indirection the rows of all experts are one array; its end is not known here, and
     // no box reaches past an expert (rows % 4 == 0 is required), so the row bound is left open.
     const cuuint64_t gdim[2] = {rb / 8, t.expert_id ? (cuuint64_t)0x7fffffffu : (cuuint64_t)t.rows};
@@ -752,7 +795,7 @@ cudaError_t tensor_map_2d(CUtensorMap *m, uint32_t elem_bytes, const void *base,
 cudaError_t launch_matvec(const MatvecArgs &a, int sms, cudaStream_t stream) {
     if (a.n_tensors < 1 || a.n_tensors > 4 || a.cols == 0) return cudaErrorInvalidValue;
     if (matvec_mma_eligible(a)) return launch_matvec_mma(a, sms, stream);
-    bool streaming = true, q4 = false, q6 = false;
+    bool streaming = true, q4 = false, q6 = false, q8 = false;
     uint32_t total_rows = 0, total_quads = 0;
     for (int i = 0; i < a.n_tensors; ++i) {
         const MatvecTensor &t = a.t[i];
@@ -766,6 +809,8 @@ cudaError_t launch_matvec(const MatvecArgs &a, int sms, cudaStream_t stream) {
                     (((uintptr_t)a.x2) & 15u) == 0 && (((uintptr_t)a.wnorm) & 15u) == 0;
         q4 = q4 || t.fmt == FMT_Q4_K;
         q6 = q6 || t.fmt == FMT_Q6_K;
+        q8 = q8 || t.fmt == FMT_Q8_0;
+        if (t.fmt == FMT_Q8_0 && (t.expert_id || a.swiglu)) streaming = false;
         total_rows += t.rows;
         total_quads += (t.rows + kRowsPerStage - 1) / kRowsPerStage;
     }
@@ -774,9 +819,10 @@ cudaError_t launch_matvec(const MatvecArgs &a, int sms, cudaStream_t stream) {
             return cudaErrorInvalidValue;
         total_quads = (a.t[0].rows + 1) / 2;
     }
+    if (q8 && (q4 || q6)) streaming = false;   // Q8_0 streams only in launches of its own (another stage layout)
     if (streaming) {
         int stages = 0, warps = 0;
-        const size_t smem = matvec_smem_bytes(a.cols, q4, q6, &stages, &warps);
+        const size_t smem = matvec_smem_bytes(a.cols, q4, q6, &stages, &warps, q8);
         if (smem <= 227 * 1024 - 1024 && stages >= 2) {
             uint32_t grid = total_quads < (uint32_t)sms ? total_quads : (uint32_t)sms;
             TensorMaps maps;
@@ -787,9 +833,9 @@ cudaError_t launch_matvec(const MatvecArgs &a, int sms, cudaStream_t stream) {
             }
             if (a.xr_buf)
                 return launch_kernel(matvec_stream_kernel<true>, dim3(grid), dim3(warps * 32), smem, stream, a.pdl != 0, a, maps,
-                                     total_quads, stages, q4 ? 1 : 0, q6 ? 1 : 0);
+                                     total_quads, stages, (q4 || q8) ? 1 : 0, q6 ? 1 : 0, q8 ? 1 : 0);
             return launch_kernel(matvec_stream_kernel<false>, dim3(grid), dim3(warps * 32), smem, stream, a.pdl != 0, a, maps,
-                                 total_quads, stages, q4 ? 1 : 0, q6 ? 1 : 0);
+                                 total_quads, stages, (q4 || q8) ? 1 : 0, q6 ? 1 : 0, q8 ? 1 : 0);
         }
     }
     if (a.x_mode != MV_X_PLAIN || a.xr_buf) return cudaErrorInvalidValue;   // prologues exist only in the streaming kernel

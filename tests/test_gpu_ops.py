@@ -101,6 +101,7 @@ def test_dequant_extreme_scales(ctx, checker):
     (capi.Q6_K, 512, 14336),       # rows of ffn_down
     (capi.Q4_K, 1026, 2048), (capi.Q6_K, 1029, 2048), (capi.Q4_K, 1, 2048), (capi.Q6_K, 3, 6144),   # ragged row counts
     (capi.Q4_K, 37, 768), (capi.Q6_K, 37, 1280),
+    (capi.Q8_0, 1024, 4096), (capi.Q8_0, 37, 2048), (capi.Q8_0, 130, 768), (capi.Q8_0, 66, 6144),   # Q8_0 streaming path
     (capi.Q4_K, 64, 512), (capi.Q4_K, 101, 1792), (capi.Q4_K, 256, 7168), (capi.Q6_K, 64, 6144 + 2048),   # partial last segment
  (capi.Q8_0, 100, 1408), (capi.Q5_0, 33, 1408), (capi.F32, 50, 200),
 ])
