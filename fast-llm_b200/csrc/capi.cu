@@ -205,7 +205,20 @@ static int matvec_impl(fl_b200_ctx *c, int fmt, const void *w, uint32_t rows, ui
         return set_err(FL_B200_ERR_ARG, "matvec: row pitch %u smaller than the packed row (%llu bytes)", pitch,
                        (unsigned long long)row_bytes(fmt, cols));
     if (nx == 0) nx = 1;
-    for (uint32_t p = 0; p < nx; ++p) {
+    uint32_t first_single = 0;   // columns from here on go through the one-column kernel
+    if (nx >= 2 && fmt == FL_B200_Q4_K && pitch == 0 && !expert_id) {
+        // verify batches: up to 8 columns per pass over the weights on the tensor-core kernel; a last
+        // chunk of one column is left to the one-column kernel
+        for (uint32_t p0 = 0; p0 + 2 <= nx; p0 += 8) {
+            const uint32_t nt = nx - p0 < 8 ? nx - p0 : 8;
+            const cudaError_t e = launch_matmul_q4k_nx(w, rows, cols, x + (size_t)p0 * xstride, nt, xstride, y + (size_t)p0 * ystride,
+                                                       ystride, accumulate, c->status, c->sms, c->stream);
+            if (e == cudaErrorNotSupported) break;   // the shape does not qualify (same answer for every chunk)
+            if (e != cudaSuccess) return cuda_err(e, "multi-column matmul launch");
+            first_single = p0 + nt;
+        }
+    }
+    for (uint32_t p = first_single; p < nx; ++p) {
         MatvecArgs a{};
         a.n_tensors = 1;
         a.t[0].w = (const uint8_t *)w;

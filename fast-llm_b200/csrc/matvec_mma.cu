@@ -59,6 +59,12 @@ __device__ __forceinline__ void mma_u8s8(int (&d)[4], uint32_t a0, uint32_t a1, 
                  : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
 }
+// D += A * B
+__device__ __forceinline__ void mma_u8s8_acc(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
 // byte K of w as a float (no integer->float conversion instruction): 2^23 + byte under 0x4B000000
 template <int K>
 __device__ __forceinline__ float u8f(uint32_t w) {
@@ -337,6 +343,232 @@ matvec_q4k_mma_kernel(const MatvecArgs a, const __grid_constant__ Maps maps, con
     if (lane == 0) trace_max(a.trace, 3);
 }
 
+
+// ---- several activation columns at once (draft verification: Task::nx > 1) ---------------------
+//
+// y[p][r] (+)= dot(W[r], x[p]) for p < nt <= 8 columns in ONE pass over the weights
+// (include/fastllm/fastllm.h:87-96: "the weight row is read ONCE for all nx columns"). Same stage
+// geometry as above. What makes several columns cheap is that the per-sub-block scale moves into the
+// A operand: sc = 8 sh + sl with sh, sl in 0..7, and q * sh, q * sl (<= 105) are still bytes, one
+// integer multiply on the packed word. The MMAs then accumulate over the 8 sub-blocks of a super-block,
+// and the scalar epilogue runs once per super-block instead of once per sub-block. The min term goes the
+// same way (A = the 6-bit min broadcast to the 32 weights). B holds two columns per MMA: columns
+// n = 3 * (p & 1) + plane of the 8, for the column pair p / 2. Per super-block, lane t of a quad then
+// owns accumulator columns 2t, 2t + 1 of each pair and applies d, dmin, the plane weight and the
+// column's activation scale in f32.
+constexpr int kNxMaxCols = 8;
+constexpr int kNxStages = 3;
+
+struct NxArgs {
+    const uint8_t *w;      // packed Q4_K rows
+    const float *x;        // nt activation columns, xstride floats apart
+    float *y;              // nt output columns, ystride floats apart
+    uint32_t rows, cols, nt, xstride, ystride;
+    int accumulate;
+    uint32_t *status;
+};
+
+struct NxSmem {
+    int8_t *planes;   // [nt_pad][3][cols + kPlanePad], nt_pad = nt rounded up to even (a zero column pads)
+    float *xs;        // [nt_pad][cols / 256]
+    float *part;      // [kWarps][16 rows][kNxMaxCols]
+    uint64_t *bars;
+    uint8_t *ring;
+};
+__host__ __device__ inline size_t nx_fixed_bytes(uint32_t cols, uint32_t nt_pad) {
+    return (size_t)nt_pad * 3 * (cols + kPlanePad) + (size_t)nt_pad * (cols / 256) * 4 + (size_t)kWarps * 16 * kNxMaxCols * 4 +
+           (size_t)kWarps * kNxStages * 8;
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+matvec_q4k_mma_nx_kernel(const NxArgs a, const __grid_constant__ CUtensorMap map, const uint32_t n_units) {
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    const uint32_t g = lane >> 2, t = lane & 3u;
+    const uint32_t nblk = a.cols / 256, spu = nblk / kWarps;
+    const uint32_t nt_pad = (a.nt + 1u) & ~1u, npair = nt_pad / 2;
+    const uint32_t pstride = a.cols + kPlanePad;
+    NxSmem sm;
+    {
+        uint8_t *p = smem_raw;
+        sm.planes = (int8_t *)p; p += (size_t)nt_pad * 3 * pstride;
+        sm.xs = (float *)p; p += (size_t)nt_pad * nblk * 4;
+        sm.part = (float *)p; p += (size_t)kWarps * 16 * kNxMaxCols * 4;
+        p = (uint8_t *)(((uintptr_t)p + 7) & ~(uintptr_t)7);
+        sm.bars = (uint64_t *)p; p += (size_t)kWarps * kNxStages * 8;
+        p = (uint8_t *)(((uintptr_t)p + 127) & ~(uintptr_t)127);
+        sm.ring = p;
+    }
+    uint64_t *bars = sm.bars + warp * kNxStages;
+    const uint32_t ring = smem_u32(sm.ring) + warp * kNxStages * kStageBytes;
+    if (lane == 0)
+        for (int s = 0; s < kNxStages; ++s) mbar_init(&bars[s], 1);
+    fence_barrier_init();
+    __syncwarp();
+
+    const uint32_t my_units = blockIdx.x < n_units ? (n_units - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    const uint32_t my_stages = my_units * spu;
+    uint32_t p_i = 0, p_slot = 0, p_unit = blockIdx.x, p_s = 0;
+    auto issue = [&]() {
+        mbar_arrive_expect_tx(&bars[p_slot], kStageBytes);
+        tma_load_box(ring + p_slot * kStageBytes, &map, (warp + p_s * kWarps) * 18, p_unit * 16, &bars[p_slot]);
+        ++p_i;
+        if (++p_slot == (uint32_t)kNxStages) p_slot = 0;
+        if (++p_s == spu) { p_s = 0; p_unit += gridDim.x; }
+    };
+    if (lane == 0)
+        while (p_i < (uint32_t)kNxStages && p_i < my_stages) issue();
+
+    // ---- fixed-point planes of every column: warp w takes blocks w, w + 16, ... of each column in turn ----
+    for (uint32_t p = 0; p < nt_pad; ++p) {
+        for (uint32_t blk = warp; blk < nblk; blk += kWarps) {
+            float v[8];
+            if (p < a.nt) {
+                const float4 u0 = *reinterpret_cast<const float4 *>(a.x + (size_t)p * a.xstride + blk * 256 + lane * 8);
+                const float4 u1 = *reinterpret_cast<const float4 *>(a.x + (size_t)p * a.xstride + blk * 256 + lane * 8 + 4);
+                v[0] = u0.x; v[1] = u0.y; v[2] = u0.z; v[3] = u0.w; v[4] = u1.x; v[5] = u1.y; v[6] = u1.z; v[7] = u1.w;
+            } else {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[i] = 0.f;
+            }
+            float amax = 0.f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+            amax = warp_max(amax);
+            const float s = amax > 0.f ? amax / kFixMax : 1.0f;
+            const float inv_s = 1.0f / s;
+            uint32_t pk[3][2] = {{0u, 0u}, {0u, 0u}, {0u, 0u}};
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int X = __float2int_rn(v[i] * inv_s);
+                const int d2 = ((X + 64) & 127) - 64;
+                const int X1 = (X - d2) >> 7;
+                const int d1 = ((X1 + 64) & 127) - 64;
+                const int d0 = (X1 - d1) >> 7;
+                pk[0][i >> 2] |= (uint32_t)(d0 & 0xFF) << (8 * (i & 3));
+                pk[1][i >> 2] |= (uint32_t)(d1 & 0xFF) << (8 * (i & 3));
+                pk[2][i >> 2] |= (uint32_t)(d2 & 0xFF) << (8 * (i & 3));
+            }
+#pragma unroll
+            for (int d = 0; d < 3; ++d)
+                *reinterpret_cast<uint2 *>(sm.planes + ((size_t)p * 3 + d) * pstride + blk * 256 + lane * 8) = make_uint2(pk[d][0], pk[d][1]);
+            if (lane == 0) sm.xs[p * nblk + blk] = s;
+        }
+    }
+    __syncthreads();
+
+    // B operand: MMA column n = g holds column 2 * pair + n / 3 of the activation, plane n % 3 (n < 6).
+    const bool feeds = g < 6;
+    const uint32_t bcol = g < 3 ? 0u : 1u, bplane = g < 3 ? g : g - 3u;
+    // accumulator columns of this lane: n = 2t and 2t + 1
+    const uint32_t n0 = 2 * t, n1 = 2 * t + 1;
+    const float pwt[3] = {16384.f, 128.f, 1.f};
+    const float pw0 = n0 < 6 ? pwt[n0 % 3] : 0.f, pw1 = n1 < 6 ? pwt[n1 % 3] : 0.f;
+    const uint32_t c0 = n0 < 6 ? n0 / 3 : 0u, c1 = n1 < 6 ? n1 / 3 : 0u;   // which column of the pair
+
+    float acc[kNxMaxCols / 2][2][2];   // [pair][row g / g + 8][accumulator column]
+#pragma unroll
+    for (int q = 0; q < kNxMaxCols / 2; ++q) acc[q][0][0] = acc[q][0][1] = acc[q][1][0] = acc[q][1][1] = 0.f;
+    uint32_t slot = 0, parity = 0, unit = blockIdx.x, s_in = 0;
+    bool dead = false;
+    for (uint32_t i = 0; i < my_stages; ++i) {
+        const uint32_t st = ring + slot * kStageBytes;
+        const uint32_t blk = warp + s_in * kWarps;
+        if (!dead && !mbar_wait_bounded(&bars[slot], parity, a.status)) dead = true;
+        if (!dead) {
+            const uint32_t rg = st + g * 144, rh = st + (g + 8) * 144;
+            const uint4 hg = lds128(rg), hh = lds128(rh);
+            const uint32_t scg_lo = hg.y & 0x3F3F3F3Fu, mng_lo = hg.z & 0x3F3F3F3Fu;
+            const uint32_t scg_hi = (hg.w & 0x0F0F0F0Fu) | ((hg.y >> 2) & 0x30303030u);
+            const uint32_t mng_hi = ((hg.w >> 4) & 0x0F0F0F0Fu) | ((hg.z >> 2) & 0x30303030u);
+            const uint32_t sch_lo = hh.y & 0x3F3F3F3Fu, mnh_lo = hh.z & 0x3F3F3F3Fu;
+            const uint32_t sch_hi = (hh.w & 0x0F0F0F0Fu) | ((hh.y >> 2) & 0x30303030u);
+            const uint32_t mnh_hi = ((hh.w >> 4) & 0x0F0F0F0Fu) | ((hh.z >> 2) & 0x30303030u);
+            int chi[kNxMaxCols / 2][4], clo[kNxMaxCols / 2][4], cmn[kNxMaxCols / 2][4];
+#pragma unroll
+            for (int q = 0; q < kNxMaxCols / 2; ++q)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) chi[q][e] = clo[q][e] = cmn[q][e] = 0;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const uint32_t wg0 = lds32(rg + 16 + 32 * c + 4 * t), wg1 = lds32(rg + 32 + 32 * c + 4 * t);
+                const uint32_t wh0 = lds32(rh + 16 + 32 * c + 4 * t), wh1 = lds32(rh + 32 + 32 * c + 4 * t);
+#pragma unroll
+                for (int hn = 0; hn < 2; ++hn) {   // sub-block j = 2c + hn: low / high nibbles
+                    const int j = 2 * c + hn;
+                    const uint32_t qg0 = (hn ? wg0 >> 4 : wg0) & 0x0F0F0F0Fu, qg1 = (hn ? wg1 >> 4 : wg1) & 0x0F0F0F0Fu;
+                    const uint32_t qh0 = (hn ? wh0 >> 4 : wh0) & 0x0F0F0F0Fu, qh1 = (hn ? wh1 >> 4 : wh1) & 0x0F0F0F0Fu;
+                    const uint32_t scg = ((j < 4 ? scg_lo : scg_hi) >> (8 * (j & 3))) & 0xFFu;
+                    const uint32_t sch = ((j < 4 ? sch_lo : sch_hi) >> (8 * (j & 3))) & 0xFFu;
+                    const uint32_t mg = (((j < 4 ? mng_lo : mng_hi) >> (8 * (j & 3))) & 0xFFu) * 0x01010101u;
+                    const uint32_t mh = (((j < 4 ? mnh_lo : mnh_hi) >> (8 * (j & 3))) & 0xFFu) * 0x01010101u;
+                    const uint32_t shg = scg >> 3, slg = scg & 7u, shh = sch >> 3, slh = sch & 7u;
+                    const uint32_t adr = smem_u32(sm.planes) + (blk * 256 + j * 32) + 4 * t;
+#pragma unroll
+                    for (int q = 0; q < kNxMaxCols / 2; ++q) {
+                        if (q < (int)npair) {
+                            const uint32_t pa = adr + ((2 * q + bcol) * 3 + bplane) * pstride;
+                            const uint32_t v0 = lds32(pa), v1 = lds32(pa + 16);
+                            const uint32_t b0 = feeds ? v0 : 0u, b1 = feeds ? v1 : 0u;
+                            mma_u8s8_acc(chi[q], qg0 * shg, qh0 * shh, qg1 * shg, qh1 * shh, b0, b1);
+                            mma_u8s8_acc(clo[q], qg0 * slg, qh0 * slh, qg1 * slg, qh1 * slh, b0, b1);
+                            mma_u8s8_acc(cmn[q], mg, mh, mg, mh, b0, b1);
+                        }
+                    }
+                }
+            }
+            const float dg = h2f_bits((uint16_t)(hg.x & 0xFFFFu)), dming = h2f_bits((uint16_t)(hg.x >> 16));
+            const float dh = h2f_bits((uint16_t)(hh.x & 0xFFFFu)), dminh = h2f_bits((uint16_t)(hh.x >> 16));
+#pragma unroll
+            for (int q = 0; q < kNxMaxCols / 2; ++q) {
+                if (q < (int)npair) {
+                    const float xs0 = sm.xs[(2 * q + c0) * nblk + blk] * pw0, xs1 = sm.xs[(2 * q + c1) * nblk + blk] * pw1;
+                    // accumulator entries: [0] (row g, col n0), [1] (row g, col n1), [2] (row g + 8, n0), [3] (row g + 8, n1)
+                    acc[q][0][0] = fmaf(xs0, dg * (float)(8 * chi[q][0] + clo[q][0]) - dming * (float)cmn[q][0], acc[q][0][0]);
+                    acc[q][0][1] = fmaf(xs1, dg * (float)(8 * chi[q][1] + clo[q][1]) - dming * (float)cmn[q][1], acc[q][0][1]);
+                    acc[q][1][0] = fmaf(xs0, dh * (float)(8 * chi[q][2] + clo[q][2]) - dminh * (float)cmn[q][2], acc[q][1][0]);
+                    acc[q][1][1] = fmaf(xs1, dh * (float)(8 * chi[q][3] + clo[q][3]) - dminh * (float)cmn[q][3], acc[q][1][1]);
+                }
+            }
+        }
+        __syncwarp();
+        if (lane == 0 && p_i < my_stages && !dead) issue();
+        if (++slot == (uint32_t)kNxStages) { slot = 0; parity ^= 1u; }
+        if (++s_in == spu) {
+            s_in = 0;
+            // per (row, column) totals of this warp: columns n = 0..2 of a pair are its even column, 3..5 its odd one
+#pragma unroll
+            for (int q = 0; q < kNxMaxCols / 2; ++q) {
+#pragma unroll
+                for (int r = 0; r < 2; ++r) {
+                    float ev = t == 0 ? acc[q][r][0] + acc[q][r][1] : t == 1 ? acc[q][r][0] : 0.f;
+                    float od = t == 2 ? acc[q][r][0] + acc[q][r][1] : t == 1 ? acc[q][r][1] : 0.f;
+                    ev += __shfl_xor_sync(0xffffffffu, ev, 1); od += __shfl_xor_sync(0xffffffffu, od, 1);
+                    ev += __shfl_xor_sync(0xffffffffu, ev, 2); od += __shfl_xor_sync(0xffffffffu, od, 2);
+                    if (t == 0) {
+                        sm.part[(warp * 16 + g + 8 * r) * kNxMaxCols + 2 * q] = ev;
+                        sm.part[(warp * 16 + g + 8 * r) * kNxMaxCols + 2 * q + 1] = od;
+                    }
+                    acc[q][r][0] = acc[q][r][1] = 0.f;
+                }
+            }
+            __syncthreads();
+            if (tid < 16 * kNxMaxCols) {
+                const uint32_t row = tid / kNxMaxCols, col = tid % kNxMaxCols;
+                if (col < a.nt) {
+                    float v = 0.f;
+#pragma unroll
+                    for (int w = 0; w < kWarps; ++w) v += sm.part[(w * 16 + row) * kNxMaxCols + col];   // fixed order
+                    float *dst = a.y + (size_t)col * a.ystride + unit * 16 + row;
+                    *dst = a.accumulate ? *dst + v : v;
+                }
+            }
+            __syncthreads();
+            unit += gridDim.x;
+        }
+    }
+}
+
 } // namespace
 
 static bool g_mma_init = false;
@@ -366,6 +598,34 @@ bool matvec_mma_eligible(const MatvecArgs &a) {
     if ((((uintptr_t)a.x) & 15u) != 0 || (((uintptr_t)a.wnorm) & 15u) != 0) return false;
     if (a.xn_out) return false;
     return true;
+}
+
+// y[p * ystride + r] (+)= dot(W[r], x + p * xstride), p < nt, in one pass over a Q4_K tensor. Returns
+// cudaErrorNotSupported when the shape does not qualify (the caller then runs the columns one by one).
+cudaError_t launch_matmul_q4k_nx(const void *w, uint32_t rows, uint32_t cols, const float *x, uint32_t nt, uint32_t xstride,
+                                 float *y, uint32_t ystride, int accumulate, uint32_t *status, int sms, cudaStream_t stream) {
+    static bool init = false;
+    if (nt < 2 || nt > kNxMaxCols || rows % 16 != 0 || cols % (256u * kWarps) != 0) return cudaErrorNotSupported;
+    if ((((uintptr_t)w) & 15u) != 0 || (((uintptr_t)x) & 15u) != 0 || (xstride & 3u) != 0 || ystride < rows) return cudaErrorNotSupported;
+    const uint32_t nt_pad = (nt + 1u) & ~1u;
+    const size_t smem = nx_fixed_bytes(cols, nt_pad) + 8 + 128 + (size_t)kWarps * kNxStages * kStageBytes;
+    if (smem > 227 * 1024 - 1024) return cudaErrorNotSupported;
+    if (!init) {
+        const cudaError_t e = cudaFuncSetAttribute(matvec_q4k_mma_nx_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024 - 1024);
+        if (e != cudaSuccess) return e;
+        init = true;
+    }
+    CUtensorMap map;
+    memset(&map, 0, sizeof(map));
+    const uint64_t rb = row_bytes(FMT_Q4_K, cols);
+    cudaError_t e = tensor_map_2d(&map, 8, w, rb / 8, rows, rb, 18, 16, false);
+    if (e != cudaSuccess) return e;
+    NxArgs a{};
+    a.w = (const uint8_t *)w; a.x = x; a.y = y; a.rows = rows; a.cols = cols; a.nt = nt; a.xstride = xstride; a.ystride = ystride;
+    a.accumulate = accumulate; a.status = status;
+    const uint32_t n_units = rows / 16;
+    const uint32_t grid = n_units < (uint32_t)sms ? n_units : (uint32_t)sms;
+    return launch_kernel(matvec_q4k_mma_nx_kernel, dim3(grid), dim3(kThreads), smem, stream, false, a, map, n_units);
 }
 
 cudaError_t launch_matvec_mma(const MatvecArgs &a, int sms, cudaStream_t stream) {

@@ -224,6 +224,31 @@ def test_stream_dot_semantics(ctx, checker):
     assert rel_err(yd.cpu().numpy().ravel(), want.ravel()) <= MATVEC_RTOL
 
 
+@pytest.mark.parametrize("rows,cols,nx", [(320, 4096, 2), (64, 4096, 3), (1024, 4096, 8), (48, 8192, 4), (160, 4096, 9), (32, 4096, 17)])
+def test_stream_dot_multi_column_tensor_core(ctx, checker, rows, cols, nx):
+    """Task::nx > 1 (draft verification): the columns go through the tensor-core kernel in one pass
+    over the weights (up to 8 at a time); results equal the reference's STREAM_DOT column by column."""
+    rng = np.random.default_rng(rows + cols + nx)
+    w = synth.q4k_tensor(rng, rows, cols)
+    xstride, ystride = cols + 64, rows + 16
+    x = rng.standard_normal((nx, xstride)).astype(np.float32)
+    x[:, cols:] = np.nan                                   # the gap between columns is never read
+    x[1] *= 1000.0                                         # columns with very different scales
+    y0 = rng.standard_normal((nx, ystride)).astype(np.float32)
+    want = y0.copy()
+    for p in range(nx):
+        want[p, :rows] += checker.matvec(capi.Q4_K, w, rows, cols, x[p, :cols].copy())
+    wd, xd, yd = dev(w), dev(x), dev(y0)
+    torch.cuda.synchronize()
+    ctx.matvec(capi.Q4_K, wd, rows, cols, xd, yd, nx=nx, xstride=xstride, ystride=ystride)
+    ctx.sync()
+    assert ctx.status() == 0
+    got = yd.cpu().numpy()
+    assert np.array_equal(got[:, rows:], y0[:, rows:])     # nothing outside the rows is touched
+    for p in range(nx):
+        assert rel_err(got[p, :rows], want[p, :rows]) <= MATVEC_RTOL, p
+
+
 def test_matvec_host_entry(ctx, checker):
     rng = np.random.default_rng(4)
     rows, cols = 2048, 4096
