@@ -37,6 +37,9 @@ SYMBOLS = [
     "fl_b200_decoder_n_past", "fl_b200_decoder_step", "fl_b200_decoder_run", "fl_b200_decoder_verify", "fl_b200_decoder_logits",
     "fl_b200_decoder_margin", "fl_b200_decoder_tap", "fl_b200_decoder_time_class", "fl_b200_decoder_trace", "fl_b200_decoder_launches_per_step",
     "fl_b200_decoder_bytes_per_step",
+    "fl_b200_gguf_open", "fl_b200_gguf_close", "fl_b200_gguf_counts", "fl_b200_gguf_tensor_at", "fl_b200_gguf_find",
+    "fl_b200_gguf_has", "fl_b200_gguf_kv_i", "fl_b200_gguf_kv_f", "fl_b200_gguf_kv_s", "fl_b200_gguf_kv_sarr_count",
+    "fl_b200_gguf_kv_sarr_at", "fl_b200_gguf_llama_cfg", "fl_b200_decoder_create_gguf",
 ]
 
 
@@ -89,6 +92,10 @@ def load():
     lib.fl_b200_decoder_destroy.restype = None
     lib.fl_b200_seqpar_destroy.restype = None
     lib.fl_b200_plan_destroy.restype = None
+    lib.fl_b200_gguf_close.restype = None
+    lib.fl_b200_gguf_kv_i.restype = C.c_int64
+    lib.fl_b200_gguf_kv_f.restype = C.c_double
+    lib.fl_b200_gguf_kv_sarr_count.restype = C.c_int64
     _lib = lib
     return lib
 

@@ -24,4 +24,6 @@ struct fl_b200_ctx {
 namespace flb {
 int set_err(int code, const char *fmt, ...);
 int cuda_err(cudaError_t e, const char *what);
+// Hands device memory to the decoder, which frees it when it is destroyed.
+void decoder_adopt(fl_b200_decoder *d, void *dev);
 } // namespace flb

@@ -91,7 +91,10 @@ struct fl_b200_decoder {
     cudaGraphExec_t exec = nullptr;
     uint32_t launches = 0;
     bool finalized = false;
+    std::vector<void *> owned;              // device memory the decoder frees (tensors uploaded from a model file)
 };
+
+void flb::decoder_adopt(fl_b200_decoder *d, void *dev) { d->owned.push_back(dev); }
 
 // Every kernel of the step after the embedding lookup is launched with
 // programmatic dependent launch: its preamble (barrier set-up, weight prefetch
@@ -107,6 +110,21 @@ enum : uint32_t { K_MATVEC = 1u, K_ATTN = 2u, K_OTHER = 4u, K_COMM = 8u, K_ALL =
 static int enqueue_step(fl_b200_decoder *d, cudaStream_t s, uint32_t *n_launch, uint32_t mask = K_ALL) {
     uint32_t n = 0;   // launches so far
     auto do_matvec = [&](MatvecArgs &a) -> int {
+        // Q8_0 streams only in launches of its own: a group that mixes it with the K-quants goes out one
+        // tensor per launch (each with the group's prologue). The caller counts the last launch.
+        bool q8 = false, kq = false;
+        for (int i = 0; i < a.n_tensors; ++i) (a.t[i].fmt == FL_B200_Q8_0 ? q8 : kq) = true;
+        if (q8 && kq && !a.swiglu) {
+            for (int i = 0; i < a.n_tensors; ++i) {
+                MatvecArgs one = a;
+                one.n_tensors = 1;
+                one.t[0] = a.t[i];
+                if (d->trace && mask == K_ALL) one.trace = d->trace + 4 * (size_t)n;
+                if (int rc = cuda_err(launch_matvec(one, d->ctx->sms, s), "matvec launch")) return rc;
+                if (i + 1 < a.n_tensors) ++n;
+            }
+            return FL_B200_OK;
+        }
         if (d->trace && mask == K_ALL) a.trace = d->trace + 4 * (size_t)n;
         return cuda_err(launch_matvec(a, d->ctx->sms, s), "matvec launch");
     };
@@ -182,7 +200,8 @@ static int enqueue_step(fl_b200_decoder *d, cudaStream_t s, uint32_t *n_launch, 
             a.t[1] = {w[FL_B200_T_UP].w, d->u, nullptr, d->F, w[FL_B200_T_UP].fmt, 0};
             a.x = d->xb; a.wnorm = d->ffn_norm[l]; a.eps = c.eps; a.cols = E;
             a.x_mode = MV_X_RMSNORM; a.status = ctx->status; a.pdl = kPdl;
-            a.swiglu = w[FL_B200_T_GATE].fmt == w[FL_B200_T_UP].fmt ? 1 : 0;
+            // (Q8_0 streams without the fused product: the down projection then takes silu(g) * u on load)
+            a.swiglu = (w[FL_B200_T_GATE].fmt == w[FL_B200_T_UP].fmt && w[FL_B200_T_GATE].fmt != FL_B200_Q8_0) ? 1 : 0;
             a.issue_late = (issue_late() >> 1) & 1;
             take_pending(a);
             if (mask & K_MATVEC) { if (int rc = do_matvec(a)) return rc; ++n; }
@@ -330,6 +349,7 @@ void fl_b200_decoder_destroy(fl_b200_decoder *d) {
     cudaFree(d->xn_final); cudaFree(d->part); cudaFree(d->tickets);
     cudaFree(d->top3); cudaFree(d->rope_table); cudaFree(d->comm); cudaFree(d->comm_state); cudaFree(d->partial);
     cudaFree(d->trace);
+    for (void *p : d->owned) cudaFree(p);
     cudaFreeHost(d->h_pin);
     delete d;
 }
@@ -337,8 +357,8 @@ void fl_b200_decoder_destroy(fl_b200_decoder *d) {
 static int check_weight(const fl_b200_decoder *d, int fmt, const void *w, uint32_t cols) {
     (void)d;
     if (!w) return set_err(FL_B200_ERR_ARG, "decoder: null weight pointer");
-    if (fmt != FL_B200_Q4_K && fmt != FL_B200_Q6_K)
-        return set_err(FL_B200_ERR_ARG, "decoder: weight format %d (the decoder streams Q4_K and Q6_K)", fmt);
+    if (fmt != FL_B200_Q4_K && fmt != FL_B200_Q6_K && fmt != FL_B200_Q8_0)
+        return set_err(FL_B200_ERR_ARG, "decoder: weight format %d (the decoder streams Q4_K, Q6_K and Q8_0)", fmt);
     if (((uintptr_t)w & 15u) != 0) return set_err(FL_B200_ERR_ARG, "decoder: weights must be 16-byte aligned");
     if (cols % 256 || cols < 512) return set_err(FL_B200_ERR_ARG, "decoder: cols %u not a multiple of 256 (>= 512)", cols);
     return FL_B200_OK;
@@ -421,7 +441,7 @@ int fl_b200_decoder_finalize(fl_b200_decoder *d) {
     CK(cudaStreamSynchronize(s));
     if (const char *e = getenv("FLB_TRACE")) {
         if (e[0] == '1' && !d->trace) {
-            d->trace_n = 8 + 6 * d->c.n_layer;
+            d->trace_n = 8 + 10 * d->c.n_layer;   // room for groups that go out one tensor per launch
             CK(cudaMalloc(&d->trace, (size_t)d->trace_n * 4 * sizeof(unsigned long long)));
         }
     }

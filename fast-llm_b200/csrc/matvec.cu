@@ -50,9 +50,9 @@ namespace flb {
 
 namespace {
 
-constexpr int kMaxWarps = 12;         // warps per CTA (each consumes and feeds its own ring). 16 warps with two ring
-constexpr int kMinWarps = 12;         // stages each were measured slower (128-register cap), so the range is one value.
-constexpr int kMaxThreads = kMaxWarps * 32;
+constexpr int kWarps = 12;            // warps per CTA (each consumes and feeds its own ring); 16 warps with two ring
+                                      // stages each were measured slower (they cap the kernel at 128 registers)
+constexpr int kMaxThreads = kWarps * 32;
 constexpr int kRowsPerStage = 4;
 constexpr uint32_t kSeg4 = 8 * 144;   // bytes of one Q4_K segment (8 super-blocks)
 constexpr uint32_t kSeg6 = 8 * 210;   // bytes of one Q6_K segment
@@ -356,7 +356,7 @@ matvec_stream_kernel(const MatvecArgs a, const __grid_constant__ TensorMaps maps
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
     const uint32_t nseg = (a.cols + 2047u) / 2048u;   // the last segment may be partial: the TMA unit fills the rest with zeros
     const uint32_t stage_bytes = use_q8 ? kStage8 : use_q6 ? kStage6 : kStage4;
-    __shared__ float red[kMaxWarps];
+    __shared__ float red[kWarps];
 
     bool indirect = false;
     for (int i = 0; i < a.n_tensors; ++i) indirect = indirect || a.t[i].expert_id != nullptr;
@@ -416,7 +416,7 @@ matvec_stream_kernel(const MatvecArgs a, const __grid_constant__ TensorMaps maps
     // bound; a second round would double it). All global loads of all the blocks are issued first, so
     // the prologue costs one memory round trip; the norm weights are constants and are fetched before
     // the dependency wait.
-    constexpr int kMaxBlk = 3;   // blocks per half-warp: cols <= 3 * 256 * 2 * kMinWarps = 18432
+    constexpr int kMaxBlk = 3;   // blocks per half-warp: cols <= 3 * 256 * 2 * kWarps = 18432
     const uint32_t nblk = a.cols / 256, nblk_pad = nseg * 8;   // blocks nblk .. nblk_pad-1 are zeros
     const uint32_t hw = 2 * warp + (lane >> 4), hl = lane & 15u, nhw = 2 * nw;
     float4 ra[kMaxBlk][4], rb2[kMaxBlk][4];
@@ -722,15 +722,12 @@ bool matvec_is_streaming(int fmt, uint32_t cols) {
     return (fmt == FMT_Q4_K || fmt == FMT_Q6_K || fmt == FMT_Q8_0) && cols >= 512 && cols % 256 == 0;
 }
 
-// Shared memory of a launch and its shape: as many warps as fit with two ring
-// stages each (more warps hide more latency of the issue-bound unpack loop than
-// a third stage does), then as many stages as still fit.
+// Shared memory of a launch and its shape: kWarps rings with as many stages (at most 4) as fit.
 size_t matvec_smem_bytes(uint32_t cols, bool q4, bool q6, int *stages_out, int *warps_out, bool q8) {
     const size_t fixed = smem_fixed_bytes(cols, q4 || q8, q6) + 8 + 128;   // + alignment slack
     const size_t limit = 227 * 1024 - 1024;   // leave room for static shared memory
     const size_t slot = q8 ? kStage8 : q6 ? kStage6 : kStage4;
-    int warps = kMaxWarps;
-    while (warps > kMinWarps && fixed + (size_t)warps * 2 * (8 + slot) > limit) --warps;
+    const int warps = kWarps;
     int stages = 4;
     while (stages > 1 && fixed + (size_t)warps * stages * (8 + slot) > limit) --stages;
     if (stages_out) *stages_out = stages;
@@ -805,7 +802,7 @@ cudaError_t launch_matvec(const MatvecArgs &a, int sms, cudaStream_t stream) {
         if (pitch < row_bytes(t.fmt, a.cols)) return cudaErrorInvalidValue;
         streaming = streaming && matvec_is_streaming(t.fmt, a.cols) && (((uintptr_t)t.w) & 15u) == 0 && (pitch & 15u) == 0;
         if (t.expert_id && (t.rows % kRowsPerStage != 0 || a.swiglu)) streaming = false;
-        streaming = streaming && a.cols <= 6u * 256u * kMinWarps && (((uintptr_t)a.x) & 15u) == 0 &&
+        streaming = streaming && a.cols <= 6u * 256u * kWarps && (((uintptr_t)a.x) & 15u) == 0 &&
                     (((uintptr_t)a.x2) & 15u) == 0 && (((uintptr_t)a.wnorm) & 15u) == 0;
         q4 = q4 || t.fmt == FMT_Q4_K;
         q6 = q6 || t.fmt == FMT_Q6_K;

@@ -32,6 +32,25 @@ class Decoder:
         self._keep = []   # device tensors the decoder points into
         self._peer_maps = []
 
+    @classmethod
+    def from_gguf(cls, ctx, gguf, max_kv, tp=None):
+        """The decoder of a "llama" GGUF file (fast_llm_b200.gguf.Gguf), weights
+        uploaded by the library (DecoderImpl::load, src/model/decoder.cpp:277-321).
+        Not finalized: with tp = (rank, world) run fast_llm_b200.tp.connect first."""
+        self = cls.__new__(cls)
+        self.ctx, self.lib = ctx, ctx.lib
+        self.rank, self.world = tp if tp else (0, 1)
+        c = gguf.llama_cfg(max_kv)
+        self.cfg = {k: getattr(c, k) for k, _ in capi.LlamaCfg._fields_}
+        self.loc = dict(self.cfg)
+        for k in ("n_head", "n_kv_head", "n_ff", "n_vocab"):
+            self.loc[k] = self.cfg[k] // self.world
+        self._keep, self._peer_maps = [], []
+        self._h = C.c_void_p()
+        capi._ck(self.lib.fl_b200_decoder_create_gguf(ctx._h, gguf._h, C.c_uint32(max_kv), C.c_uint32(self.rank),
+                                                      C.c_uint32(self.world), C.byref(self._h)))
+        return self
+
     def close(self):
         if self._h and not self.ctx._h:
             self._h = C.c_void_p()   # the context is gone already (teardown order): nothing left to free safely

@@ -45,12 +45,15 @@ enum {
     FL_B200_ERR_ARG = 1,      /* rejected at the boundary (shape, alignment, null) */
     FL_B200_ERR_CUDA = 2,     /* a CUDA runtime call failed */
     FL_B200_ERR_DEVICE = 3,   /* a kernel reported a status (bounded wait gave up) */
-    FL_B200_ERR_STATE = 4     /* call order (e.g. step before finalize) */
+    FL_B200_ERR_STATE = 4,    /* call order (e.g. step before finalize) */
+    FL_B200_ERR_IO = 5,       /* a model file is missing or cannot be mapped */
+    FL_B200_ERR_FORMAT = 6    /* a model file is malformed or holds what the decoder cannot run */
 };
 
 typedef struct fl_b200_ctx fl_b200_ctx;
 typedef struct fl_b200_decoder fl_b200_decoder;
 typedef struct fl_b200_seqpar fl_b200_seqpar;
+typedef struct fl_b200_gguf fl_b200_gguf;
 
 int fl_b200_abi_version(void);
 const char *fl_b200_last_error(void);
@@ -363,6 +366,75 @@ int fl_b200_decoder_launches_per_step(fl_b200_decoder *dec, uint32_t *n_out);
 /* Weight + KV bytes one step at position `pos` must read (the roofline numerator). */
 int fl_b200_decoder_bytes_per_step(fl_b200_decoder *dec, int32_t pos, uint64_t *weight_bytes,
                                    uint64_t *kv_bytes);
+
+/* ---- GGUF model files: the reader that feeds the decoder (class Gguf,
+ *      src/model/gguf.h:28-79, src/model/gguf.cpp:133-266). Host only: these
+ *      calls need no GPU. Files are mapped read-only and stay mapped until
+ *      fl_b200_gguf_close; tensor payloads are handed out in place. ---- */
+/* ggml tensor type ids as stored in the file (src/model/gguf.h:14-19). */
+enum { FL_B200_GGML_F32 = 0, FL_B200_GGML_F16 = 1, FL_B200_GGML_Q5_0 = 6, FL_B200_GGML_Q8_0 = 8,
+       FL_B200_GGML_Q4_K = 12, FL_B200_GGML_Q6_K = 14, FL_B200_GGML_IQ2_XXS = 16, FL_B200_GGML_IQ3_XXS = 18 };
+typedef struct {
+    int32_t fmt;          /* fastllm::Fmt value (IQ2_XXS = 5, IQ3_XXS = 6 included), -1 for any other type */
+    uint32_t ggml_type;
+    uint32_t n_dims;      /* 1..4 */
+    uint32_t shard;       /* index of the file that holds the payload */
+    uint64_t ne[4];       /* ne[0] = columns (innermost), ne[1] = rows, unused dims = 1 */
+    uint64_t offset;      /* from the start of its shard's data section */
+    uint64_t nbytes;      /* payload size; 0 for a type whose size is unknown */
+    const void *data;     /* host pointer into the mapping */
+} fl_b200_gguf_tensor;
+/* GGUF versions 2 and 3. A name of the form "<stem>-00001-of-000NN.gguf" opens
+ * every shard: metadata comes from the file named, tensors from all of them,
+ * and "split.tensors.count", when present, must match (Gguf::open,
+ * src/model/gguf.cpp:133-159). A missing file returns FL_B200_ERR_IO (the
+ * reference returns false); a truncated or malformed one FL_B200_ERR_FORMAT (the
+ * reference aborts), and so does a payload that runs past the end of its file. */
+int fl_b200_gguf_open(const char *path, fl_b200_gguf **out);
+void fl_b200_gguf_close(fl_b200_gguf *g);
+int fl_b200_gguf_counts(const fl_b200_gguf *g, uint32_t *n_tensors, uint32_t *n_shards, uint32_t *alignment);
+/* Tensor `index` in file order (shards in order); its name goes to name_out
+ * (truncated to cap - 1 characters, always terminated). */
+int fl_b200_gguf_tensor_at(const fl_b200_gguf *g, uint32_t index, char *name_out, size_t cap,
+                           fl_b200_gguf_tensor *info_out);
+/* First tensor of that name (Gguf::find, src/model/gguf.cpp:291-295);
+ * FL_B200_ERR_ARG when there is none. */
+int fl_b200_gguf_find(const fl_b200_gguf *g, const char *name, fl_b200_gguf_tensor *info_out);
+/* Metadata (Gguf::kv_i / kv_f / kv_s / kv_sarr, src/model/gguf.cpp:271-289):
+ * integer and boolean scalars read as int64, floats as double, each falling
+ * back to the other kind and then to `dflt`. kv_s copies the string (or dflt
+ * when the key is absent or not a string; dflt may be null = "") and returns
+ * its full length in len_out. */
+int fl_b200_gguf_has(const fl_b200_gguf *g, const char *key);
+int64_t fl_b200_gguf_kv_i(const fl_b200_gguf *g, const char *key, int64_t dflt);
+double fl_b200_gguf_kv_f(const fl_b200_gguf *g, const char *key, double dflt);
+int fl_b200_gguf_kv_s(const fl_b200_gguf *g, const char *key, const char *dflt, char *out, size_t cap, size_t *len_out);
+/* String arrays (tokenizer.ggml.tokens and the like): the count, or -1 when
+ * the key is absent or not a string array; then item i as kv_s does. */
+int64_t fl_b200_gguf_kv_sarr_count(const fl_b200_gguf *g, const char *key);
+int fl_b200_gguf_kv_sarr_at(const fl_b200_gguf *g, const char *key, uint64_t i, char *out, size_t cap, size_t *len_out);
+/* Hyper-parameters of a "llama" architecture file as the decoder wants them
+ * (what DecoderImpl::load_hparams, src/model/decoder.cpp:208-275, does for the
+ * reference's architecture): "llama.embedding_length", "llama.block_count",
+ * "llama.attention.head_count", "llama.attention.head_count_kv" (default: the
+ * head count), "llama.feed_forward_length",
+ * "llama.attention.layer_norm_rms_epsilon" (1e-5), "llama.rope.freq_base"
+ * (10000), head size from "llama.attention.key_length" (default n_embd /
+ * n_head), vocabulary from token_embd.weight's row count. A file that asks for
+ * RoPE scaling (a "llama.rope.scaling.type" other than "none", or a
+ * rope_freqs.weight tensor) is refused with FL_B200_ERR_FORMAT. */
+int fl_b200_gguf_llama_cfg(const fl_b200_gguf *g, uint32_t max_kv, fl_b200_llama_cfg *cfg_out);
+/* Creates the decoder (rank `rank` of `world`; 0 of 1 = single GPU) of a llama
+ * GGUF and uploads its tensors, each from the mapping straight to device memory
+ * the decoder owns: blk.N.{attn_norm, attn_q, attn_k, attn_v, attn_output,
+ * ffn_norm, ffn_gate, ffn_up, ffn_down}.weight, token_embd.weight,
+ * output_norm.weight, output.weight (token_embd.weight again when the file ties
+ * them); the tensor-parallel slices are cut during the upload (DecoderImpl::load
+ * / load_tensor, src/model/decoder.cpp:185-206, :277-321, map in place instead).
+ * Matrices must be Q4_K, Q6_K or Q8_0, norms F32. Not finalized: call
+ * fl_b200_decoder_finalize (after fl_b200_decoder_set_peers when world > 1). */
+int fl_b200_decoder_create_gguf(fl_b200_ctx *ctx, const fl_b200_gguf *g, uint32_t max_kv, uint32_t rank,
+                                uint32_t world, fl_b200_decoder **out);
 
 #ifdef __cplusplus
 }

@@ -23,7 +23,7 @@ def _free_port():
     return p
 
 
-def _fill(dec, ctx, cfg, rank, world):
+def _fill(dec, ctx, cfg, rank, world, prefill=True):
     """The seeded synthetic model, sliced for (rank, world)."""
     from fast_llm_b200 import capi, synth, tp
     for l in range(cfg["n_layer"]):
@@ -35,6 +35,8 @@ def _fill(dec, ctx, cfg, rank, world):
             dec.set_layer_tensor(l, i, fmt, torch.from_numpy(w).cuda())
         an, fn = synth.llama_norm(cfg, SEED, "attn_norm", l), synth.llama_norm(cfg, SEED, "ffn_norm", l)
         dec.set_layer_norms(l, torch.from_numpy(an).cuda(), torch.from_numpy(fn).cuda())
+        if not prefill:
+            continue
         k, v = synth.llama_kv(cfg, SEED, l, N_PREFILL)
         nkv = cfg["n_kv_head"] // world
         kp, vp = dec.kv_ptrs(l)
@@ -53,7 +55,48 @@ def _fill(dec, ctx, cfg, rank, world):
     torch.cuda.synchronize()
 
 
-def _worker(rank, world, port, q):
+def _write_model_file(path):
+    """The same seeded model as _fill's, as a "llama" GGUF file."""
+    from fast_llm_b200 import gguf, synth
+    layers = []
+    for l in range(SMALL["n_layer"]):
+        L = {n: (synth.Q4_K_M[n], synth.llama_tensor(SMALL, SEED, n, l)) for n in synth.LAYER_TENSORS}
+        L["attn_norm"], L["ffn_norm"] = synth.llama_norm(SMALL, SEED, "attn_norm", l), synth.llama_norm(SMALL, SEED, "ffn_norm", l)
+        layers.append(L)
+    model = dict(layers=layers, tok_embd=(synth.Q4_K_M["tok_embd"], synth.llama_tensor(SMALL, SEED, "tok_embd")),
+                 output=(synth.Q4_K_M["output"], synth.llama_tensor(SMALL, SEED, "output")),
+                 out_norm=synth.llama_norm(SMALL, SEED, "out_norm"))
+    gguf.write_llama_gguf(path, SMALL, model)
+
+
+def _from_file_equals_sliced(rank, world, ctx, dist, path):
+    """The slices the library cuts while it uploads a model file are the slices
+    fast_llm_b200.tp cuts on the host: gathered logits of both decoders, bit for bit."""
+    from fast_llm_b200 import gguf, tp
+    from fast_llm_b200.decoder import Decoder
+    a = Decoder(ctx, SMALL, tp=(rank, world))
+    _fill(a, ctx, SMALL, rank, world, prefill=False)
+    with gguf.Gguf(path) as g:
+        b = Decoder.from_gguf(ctx, g, SMALL["max_kv"], tp=(rank, world))
+    out = []
+    for dec in (a, b):
+        tp.connect(dec, dist)
+        dec.finalize()
+        dist.barrier()
+        toks, tok = [], 5
+        for _ in range(3):
+            tok = dec.step(tok)
+            toks.append(tok)
+        sl = torch.from_numpy(dec.logits())
+        parts = [torch.zeros_like(sl) for _ in range(world)]
+        dist.all_gather(parts, sl)
+        out.append((toks, torch.cat(parts).numpy()))
+        dist.barrier()
+    a.close(); b.close()
+    return out[0][0] == out[1][0] and np.array_equal(out[0][1].view(np.uint32), out[1][1].view(np.uint32))
+
+
+def _worker(rank, world, port, q, model_path=None):
     try:
         import torch.distributed as dist
         os.environ["MASTER_ADDR"] = "127.0.0.1"
@@ -101,6 +144,8 @@ def _worker(rank, world, port, q):
             one.close()
         dist.barrier()
         dec.close()
+        if model_path:
+            res["file_equals_sliced"] = _from_file_equals_sliced(rank, world, ctx, dist, model_path)
         ctx.close()
         dist.destroy_process_group()
         q.put((rank, res))
@@ -109,14 +154,16 @@ def _worker(rank, world, port, q):
         q.put((rank, "ERROR " + traceback.format_exc()))
 
 
-def test_two_rank_decoder_matches_single_gpu():
+def test_two_rank_decoder_matches_single_gpu(tmp_path):
     if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     import torch.multiprocessing as mp
     mpc = mp.get_context("spawn")
     q = mpc.Queue()
     port = _free_port()
-    procs = [mpc.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    model_path = str(tmp_path / "small.gguf")
+    _write_model_file(model_path)
+    procs = [mpc.Process(target=_worker, args=(r, 2, port, q, model_path)) for r in range(2)]
     for p in procs:
         p.start()
     res = dict(q.get(timeout=600) for _ in procs)
@@ -125,6 +172,7 @@ def test_two_rank_decoder_matches_single_gpu():
     for r in (0, 1):
         assert not isinstance(res[r], str), res[r]
         assert res[r]["status"] == 0
+        assert res[r]["file_equals_sliced"]
     a, b, ref = res[0], res[1], res[0]["ref"]
     # every rank holds the same token, margin and (gathered) logits, bit for bit
     assert a["tokens"] == b["tokens"] and a["run"] == b["run"] and a["margin"] == b["margin"]
