@@ -197,14 +197,19 @@ static int check_matvec(int fmt, const void *w, uint32_t rows, uint32_t cols, co
     return FL_B200_OK;
 }
 
-static int matvec_impl(fl_b200_ctx *c, int fmt, const void *w, uint32_t rows, uint32_t cols, const float *x,
-                       uint32_t nx, uint32_t xstride, float *y, uint32_t ystride, int accumulate, uint32_t pitch = 0,
-                       const uint32_t *expert_id = nullptr, uint64_t expert_stride = 0) {
+} // extern "C"
+
+// y[p * ystride + r] (+)= dot(W[r], x + p * xstride) for p < nx on the context's stream (declared in
+// capi_internal.h: the decoder's batch pass uses it too).
+int flb::matmul(fl_b200_ctx *c, int fmt, const void *w, uint32_t rows, uint32_t cols, const float *x,
+                uint32_t nx, uint32_t xstride, float *y, uint32_t ystride, int accumulate, uint32_t pitch,
+                const uint32_t *expert_id, uint64_t expert_stride) {
     if (int rc = check_matvec(fmt, w, rows, cols, x, y)) return rc;
     if (pitch != 0 && pitch < row_bytes(fmt, cols))
         return set_err(FL_B200_ERR_ARG, "matvec: row pitch %u smaller than the packed row (%llu bytes)", pitch,
                        (unsigned long long)row_bytes(fmt, cols));
     if (nx == 0) nx = 1;
+    if (pitch == row_bytes(fmt, cols)) pitch = 0;   // packed rows
     uint32_t first_single = 0;   // columns from here on go through the one-column kernel
     if (nx >= 2 && fmt == FL_B200_Q4_K && pitch == 0 && !expert_id) {
         // verify batches: up to 8 columns per pass over the weights on the tensor-core kernel; a last
@@ -245,26 +250,28 @@ static int matvec_impl(fl_b200_ctx *c, int fmt, const void *w, uint32_t rows, ui
     return FL_B200_OK;
 }
 
+extern "C" {
+
 int fl_b200_matvec_expert(fl_b200_ctx *c, int fmt, const void *w, uint32_t rows, uint32_t cols,
                           const uint32_t *expert_id, uint64_t expert_stride, const float *x, uint32_t nx, uint32_t xstride,
                           float *y, uint32_t ystride) {
     if (!expert_id) return set_err(FL_B200_ERR_ARG, "matvec_expert: null expert id pointer");
-    return matvec_impl(c, fmt, w, rows, cols, x, nx, xstride, y, ystride, 1, 0, expert_id, expert_stride);
+    return flb::matmul(c, fmt, w, rows, cols, x, nx, xstride, y, ystride, 1, 0, expert_id, expert_stride);
 }
 
 int fl_b200_matvec_pitched(fl_b200_ctx *c, int fmt, const void *w, uint32_t rows, uint32_t cols, uint32_t pitch,
                            const float *x, float *y) {
-    return matvec_impl(c, fmt, w, rows, cols, x, 1, 0, y, 0, 0, pitch);
+    return flb::matmul(c, fmt, w, rows, cols, x, 1, 0, y, 0, 0, pitch);
 }
 
 int fl_b200_matvec(fl_b200_ctx *c, int fmt, const void *w, uint32_t rows, uint32_t cols, const float *x,
                    uint32_t nx, uint32_t xstride, float *y, uint32_t ystride) {
-    return matvec_impl(c, fmt, w, rows, cols, x, nx, xstride, y, ystride, 1);
+    return flb::matmul(c, fmt, w, rows, cols, x, nx, xstride, y, ystride, 1);
 }
 
 int fl_b200_matvec_assign(fl_b200_ctx *c, int fmt, const void *w, uint32_t rows, uint32_t cols,
                           const float *x, float *y) {
-    return matvec_impl(c, fmt, w, rows, cols, x, 1, 0, y, 0, 0);
+    return flb::matmul(c, fmt, w, rows, cols, x, 1, 0, y, 0, 0);
 }
 
 static int ensure_stage(fl_b200_ctx *c, size_t bytes) {
@@ -285,7 +292,7 @@ int fl_b200_matvec_host(fl_b200_ctx *c, int fmt, const void *w, uint32_t rows, u
     if (int rc = ensure_stage(c, xb + yb)) return rc;
     float *xd = (float *)c->stage, *yd = (float *)((uint8_t *)c->stage + xb);
     CK(cudaMemcpyAsync(xd, x_host, (size_t)cols * 4, cudaMemcpyHostToDevice, c->stream));
-    if (int rc = matvec_impl(c, fmt, w, rows, cols, xd, 1, 0, yd, 0, 0)) return rc;
+    if (int rc = flb::matmul(c, fmt, w, rows, cols, xd, 1, 0, yd, 0, 0)) return rc;
     CK(cudaMemcpyAsync(y_host, yd, yb, cudaMemcpyDeviceToHost, c->stream));
     CK(cudaStreamSynchronize(c->stream));
     return FL_B200_OK;

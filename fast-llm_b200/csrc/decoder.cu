@@ -92,6 +92,19 @@ struct fl_b200_decoder {
     uint32_t launches = 0;
     bool finalized = false;
     std::vector<void *> owned;              // device memory the decoder frees (tensors uploaded from a model file)
+    // Batch pass (Decoder::step_batch): m <= kMaxBatch tokens at consecutive positions through the model in one
+    // pass; buffers are [kMaxBatch][...] and one CUDA graph per m, all made at the first call.
+    struct Batch {
+        float *x = nullptr, *xn = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *att = nullptr, *g = nullptr, *u = nullptr;
+        float *logits = nullptr, *margin = nullptr, *part = nullptr;
+        int32_t *io = nullptr;              // [0..8) tokens, [8..16) positions, [16..24) greedy next tokens
+        uint32_t *tickets = nullptr;
+        int32_t *h_io = nullptr;            // pinned image of io, then the 8 margins
+        cudaGraph_t graph[FL_B200_MAX_BATCH + 1] = {};
+        cudaGraphExec_t exec[FL_B200_MAX_BATCH + 1] = {};
+        uint32_t last_m = 0;
+        bool ready = false;
+    } b;
 };
 
 void flb::decoder_adopt(fl_b200_decoder *d, void *dev) { d->owned.push_back(dev); }
@@ -350,6 +363,14 @@ void fl_b200_decoder_destroy(fl_b200_decoder *d) {
     cudaFree(d->top3); cudaFree(d->rope_table); cudaFree(d->comm); cudaFree(d->comm_state); cudaFree(d->partial);
     cudaFree(d->trace);
     for (void *p : d->owned) cudaFree(p);
+    for (uint32_t m = 0; m <= FL_B200_MAX_BATCH; ++m) {
+        if (d->b.exec[m]) cudaGraphExecDestroy(d->b.exec[m]);
+        if (d->b.graph[m]) cudaGraphDestroy(d->b.graph[m]);
+    }
+    cudaFree(d->b.x); cudaFree(d->b.xn); cudaFree(d->b.q); cudaFree(d->b.k); cudaFree(d->b.v); cudaFree(d->b.att);
+    cudaFree(d->b.g); cudaFree(d->b.u); cudaFree(d->b.logits); cudaFree(d->b.margin); cudaFree(d->b.part);
+    cudaFree(d->b.io); cudaFree(d->b.tickets);
+    cudaFreeHost(d->b.h_io);
     cudaFreeHost(d->h_pin);
     delete d;
 }
@@ -550,6 +571,129 @@ int fl_b200_decoder_verify(fl_b200_decoder *d, int32_t first_token, const int32_
     *next_token_out = got[acc];
     d->n_past += (int32_t)acc + 1;
     return check_dev_status(d);
+}
+
+// ---- Decoder::step_batch (src/model/decoder.h:64-70): m tokens at positions n_past .. n_past + m - 1 in one
+// pass. Every weight tensor is walked once per pass where the multi-column kernel takes it (Q4_K, up to 8
+// columns) and once per token otherwise; the attention launch covers all m positions, position b attending
+// n_past + b + 1 keys of the one cache (the rows of this pass are appended first). ----
+static int batch_alloc(fl_b200_decoder *d) {
+    if (d->b.ready) return FL_B200_OK;
+    const fl_b200_llama_cfg &c = d->c;
+    const size_t M = FL_B200_MAX_BATCH, E = c.n_embd, QD = (size_t)d->Hq * c.head_dim, KD = (size_t)d->Hkv * c.head_dim;
+    CK(cudaMalloc(&d->b.x, M * E * 4)); CK(cudaMalloc(&d->b.xn, M * E * 4));
+    CK(cudaMalloc(&d->b.q, M * QD * 4)); CK(cudaMalloc(&d->b.k, M * KD * 4)); CK(cudaMalloc(&d->b.v, M * KD * 4));
+    CK(cudaMalloc(&d->b.att, M * QD * 4));
+    CK(cudaMalloc(&d->b.g, M * (size_t)d->F * 4)); CK(cudaMalloc(&d->b.u, M * (size_t)d->F * 4));
+    CK(cudaMalloc(&d->b.logits, M * (size_t)d->V * 4)); CK(cudaMalloc(&d->b.margin, M * 4));
+    size_t part = 0;
+    for (uint32_t m = 1; m <= M; ++m)
+        part = std::max(part, attn_part_floats(d->Hq, m, attn_pick_splits(d->Hkv, m, c.max_kv, d->ctx->sms)));
+    CK(cudaMalloc(&d->b.part, part * sizeof(float)));
+    CK(cudaMalloc(&d->b.io, 24 * sizeof(int32_t)));
+    CK(cudaMalloc(&d->b.tickets, (size_t)d->Hkv * M * sizeof(uint32_t)));
+    CK(cudaMemset(d->b.tickets, 0, (size_t)d->Hkv * M * sizeof(uint32_t)));
+    CK(cudaMallocHost(&d->b.h_io, 32 * sizeof(int32_t)));
+    d->b.ready = true;
+    return FL_B200_OK;
+}
+
+static int enqueue_batch(fl_b200_decoder *d, uint32_t m, cudaStream_t s) {
+    const fl_b200_llama_cfg &c = d->c;
+    fl_b200_ctx *ctx = d->ctx;
+    const uint32_t E = c.n_embd, D = c.head_dim, QD = d->Hq * D, KD = d->Hkv * D, F = d->F, V = d->V;
+    const float theta_scale = powf(c.rope_base, -2.0f / (float)D);
+    auto &b = d->b;
+    const int32_t *tok = b.io, *pos = b.io + 8;
+    int32_t *next = b.io + 16;
+    for (uint32_t i = 0; i < m; ++i)
+        CK(launch_embed(d->tok_embd.fmt, d->tok_embd.w, tok + i, E, b.x + (size_t)i * E, s));
+    for (uint32_t l = 0; l < c.n_layer; ++l) {
+        const Tensor *w = &d->lw[(size_t)l * 7];
+        for (uint32_t i = 0; i < m; ++i)
+            CK(launch_rmsnorm(b.x + (size_t)i * E, d->attn_norm[l], b.xn + (size_t)i * E, c.eps, E, s));
+        if (int rc = matmul(ctx, w[FL_B200_T_WQ].fmt, w[FL_B200_T_WQ].w, QD, E, b.xn, m, E, b.q, QD, 0)) return rc;
+        if (int rc = matmul(ctx, w[FL_B200_T_WK].fmt, w[FL_B200_T_WK].w, KD, E, b.xn, m, E, b.k, KD, 0)) return rc;
+        if (int rc = matmul(ctx, w[FL_B200_T_WV].fmt, w[FL_B200_T_WV].w, KD, E, b.xn, m, E, b.v, KD, 0)) return rc;
+        for (uint32_t i = 0; i < m; ++i) {   // rotate q and k of token i by its own position, append k and v
+            RopeAppendArgs r{};
+            r.q = b.q + (size_t)i * QD; r.k = b.k + (size_t)i * KD; r.v = b.v + (size_t)i * KD;
+            r.kcache = d->kc[l]; r.vcache = d->vc[l]; r.pos = pos + i;
+            r.n_q_head = d->Hq; r.n_kv_head = d->Hkv; r.head_dim = D; r.kv_stride = c.max_kv; r.theta_scale = theta_scale;
+            CK(launch_rope_append(r, s));
+        }
+        {
+            AttnArgs a{};
+            a.q = b.q; a.k = d->kc[l]; a.v = d->vc[l]; a.out = b.att; a.part = b.part; a.tickets = b.tickets;
+            a.pos = pos; a.kv_len = 0; a.kv_len_step = 1; a.shared_kv = 1;
+            a.kv_stride = c.max_kv; a.batch_stride = (uint64_t)d->Hkv * c.max_kv * D;
+            a.n_q_head = d->Hq; a.n_kv_head = d->Hkv; a.batch = m;
+            a.n_splits = attn_pick_splits(d->Hkv, m, c.max_kv, ctx->sms);
+            a.scale = 1.0f / sqrtf((float)D); a.status = ctx->status;
+            CK(attn_make_maps(a));
+            CK(launch_attn_decode(a, s));
+        }
+        // x += Wo att (the residual stays in place)
+        if (int rc = matmul(ctx, w[FL_B200_T_WO].fmt, w[FL_B200_T_WO].w, E, QD, b.att, m, QD, b.x, E, 1, w[FL_B200_T_WO].pitch)) return rc;
+        for (uint32_t i = 0; i < m; ++i)
+            CK(launch_rmsnorm(b.x + (size_t)i * E, d->ffn_norm[l], b.xn + (size_t)i * E, c.eps, E, s));
+        if (int rc = matmul(ctx, w[FL_B200_T_GATE].fmt, w[FL_B200_T_GATE].w, F, E, b.xn, m, E, b.g, F, 0)) return rc;
+        if (int rc = matmul(ctx, w[FL_B200_T_UP].fmt, w[FL_B200_T_UP].w, F, E, b.xn, m, E, b.u, F, 0)) return rc;
+        CK(launch_silu_mul(b.g, b.u, b.g, m * F, s));
+        if (int rc = matmul(ctx, w[FL_B200_T_DOWN].fmt, w[FL_B200_T_DOWN].w, E, F, b.g, m, F, b.x, E, 1, w[FL_B200_T_DOWN].pitch)) return rc;
+    }
+    for (uint32_t i = 0; i < m; ++i)
+        CK(launch_rmsnorm(b.x + (size_t)i * E, d->out_norm, b.xn + (size_t)i * E, c.eps, E, s));
+    if (int rc = matmul(ctx, d->output.fmt, d->output.w, V, E, b.xn, m, E, b.logits, V, 0)) return rc;
+    for (uint32_t i = 0; i < m; ++i)
+        CK(launch_argmax(b.logits + (size_t)i * V, V, next + i, b.margin + i, ctx->argmax_scratch, ctx->argmax_ticket, ctx->sms, s));
+    return FL_B200_OK;
+}
+
+int fl_b200_decoder_step_batch(fl_b200_decoder *d, const int32_t *toks, uint32_t m, int32_t *outs, float *margins) {
+    if (!d || !toks || !outs) return set_err(FL_B200_ERR_ARG, "decoder_step_batch: null");
+    if (!d->finalized) return set_err(FL_B200_ERR_STATE, "decoder_step_batch: finalize first");
+    if (d->tp_size > 1) return set_err(FL_B200_ERR_STATE, "decoder_step_batch: not built for tensor-parallel decoders");
+    if (m == 0 || m > FL_B200_MAX_BATCH) return set_err(FL_B200_ERR_ARG, "decoder_step_batch: m %u outside 1..%d", m, FL_B200_MAX_BATCH);
+    if ((uint64_t)d->n_past + m > d->c.max_kv) return set_err(FL_B200_ERR_STATE, "decoder_step_batch: kv full (%d + %u > %u)", d->n_past, m, d->c.max_kv);
+    for (uint32_t i = 0; i < m; ++i)
+        if (toks[i] < 0 || (uint32_t)toks[i] >= d->c.n_vocab) return set_err(FL_B200_ERR_ARG, "decoder_step_batch: token %d outside the vocabulary", toks[i]);
+    cudaStream_t s = d->ctx->stream;
+    CK(cudaSetDevice(d->ctx->device));
+    if (int rc = batch_alloc(d)) return rc;
+    if (!d->b.exec[m]) {
+        CK(cudaStreamSynchronize(s));
+        CK(cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal));
+        const int rc = enqueue_batch(d, m, s);
+        cudaGraph_t g = nullptr;
+        const cudaError_t e = cudaStreamEndCapture(s, &g);
+        if (rc) { if (g) cudaGraphDestroy(g); return rc; }
+        CK(e);
+        d->b.graph[m] = g;
+        CK(cudaGraphInstantiate(&d->b.exec[m], g, 0));
+    }
+    for (uint32_t i = 0; i < 8; ++i) {
+        d->b.h_io[i] = i < m ? toks[i] : 0;
+        d->b.h_io[8 + i] = d->n_past + (int32_t)i;
+    }
+    CK(cudaMemcpyAsync(d->b.io, d->b.h_io, 16 * sizeof(int32_t), cudaMemcpyHostToDevice, s));
+    CK(cudaGraphLaunch(d->b.exec[m], s));
+    CK(cudaMemcpyAsync(d->b.h_io + 16, d->b.io + 16, 8 * sizeof(int32_t), cudaMemcpyDeviceToHost, s));
+    CK(cudaMemcpyAsync(d->b.h_io + 24, d->b.margin, 8 * sizeof(float), cudaMemcpyDeviceToHost, s));
+    CK(cudaStreamSynchronize(s));
+    for (uint32_t i = 0; i < m; ++i) {
+        outs[i] = d->b.h_io[16 + i];
+        if (margins) memcpy(&margins[i], &d->b.h_io[24 + i], 4);
+    }
+    d->n_past += (int32_t)m;
+    d->b.last_m = m;
+    return check_dev_status(d);
+}
+
+int fl_b200_decoder_batch_logits(fl_b200_decoder *d, uint32_t index, float *out) {
+    if (!d || !out) return set_err(FL_B200_ERR_ARG, "decoder_batch_logits: null");
+    if (!d->b.ready || index >= d->b.last_m) return set_err(FL_B200_ERR_STATE, "decoder_batch_logits: position %u of a pass of %u", index, d->b.last_m);
+    return fl_b200_download(d->ctx, out, d->b.logits + (size_t)index * d->V, (size_t)d->V * 4);
 }
 
 int fl_b200_decoder_logits(fl_b200_decoder *d, float *out) {

@@ -92,7 +92,7 @@ struct AttnArgs {
     float *out;            // [batch][n_q_head][128]
     float *part;           // scratch: [batch][n_q_head][n_splits][132] (context[128], max, sum, pad)
     uint32_t *tickets;     // scratch: [batch][n_kv_head], zero before first use; self-resetting
-    const int32_t *pos;    // device scalar: last valid position (kv_len = *pos + 1); nullptr -> kv_len
+    const int32_t *pos;    // device scalar: last valid position of sequence 0 (kv_len = *pos + 1); nullptr -> kv_len
     uint32_t kv_len;       // used when pos == nullptr
     uint32_t kv_len_step;  // sequence b attends kv_len + b * kv_len_step keys (draft verification: step 1)
     uint32_t shared_kv;    // 1: all sequences read the same cache (batch_stride ignored)

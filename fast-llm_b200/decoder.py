@@ -91,6 +91,20 @@ class Decoder:
         capi._ck(self.lib.fl_b200_decoder_kv(self._h, C.c_uint32(layer), C.byref(k), C.byref(v)))
         return k.value, v.value
 
+    def step_batch(self, tokens):
+        """Decoder::step_batch: feeds len(tokens) <= 8 tokens in one pass; returns
+        (greedy token after each position, its top1 - top2 margin)."""
+        m = len(tokens)
+        toks = (C.c_int32 * m)(*[int(t) for t in tokens])
+        outs, margins = (C.c_int32 * m)(), (C.c_float * m)()
+        capi._ck(self.lib.fl_b200_decoder_step_batch(self._h, toks, C.c_uint32(m), outs, margins))
+        return list(outs), list(margins)
+
+    def batch_logits(self, index):
+        out = np.empty(self.loc["n_vocab"], dtype=np.float32)
+        capi._ck(self.lib.fl_b200_decoder_batch_logits(self._h, C.c_uint32(index), out.ctypes.data_as(C.c_void_p)))
+        return out
+
     def finalize(self):
         capi._ck(self.lib.fl_b200_decoder_finalize(self._h))
 

@@ -341,6 +341,20 @@ int fl_b200_decoder_run(fl_b200_decoder *dec, int32_t first_token, uint32_t n, i
 int fl_b200_decoder_verify(fl_b200_decoder *dec, int32_t first_token, const int32_t *draft_host, uint32_t n_draft,
                            uint32_t *n_accepted_out, int32_t *next_token_out);
 /* After a step: logits (n_vocab floats) and the top1 - top2 margin. */
+/* Decoder::step_batch (src/model/decoder.h:64-70): feeds m <= FL_B200_MAX_BATCH
+ * tokens at positions n_past .. n_past + m - 1 in one pass; outs_host[i] is the
+ * greedy token after position i, margins_host[i] (optional) its top1 - top2
+ * margin (Decoder::last_margins, :73); n_past advances by m, and rewind_to
+ * (fl_b200_decoder_set_n_past) commits or discards the rows as in the
+ * reference. One pass over a tensor serves all m tokens where the multi-column
+ * kernel takes its shape (Q4_K, rows a multiple of 16, columns of 4096); other
+ * tensors are walked once per token. Used for draft verification and for
+ * prompt ingestion in chunks of 8. Single-GPU decoders only. */
+#define FL_B200_MAX_BATCH 8
+int fl_b200_decoder_step_batch(fl_b200_decoder *dec, const int32_t *toks_host, uint32_t m, int32_t *outs_host,
+                               float *margins_host);
+/* Logits of position `index` of the last fl_b200_decoder_step_batch pass. */
+int fl_b200_decoder_batch_logits(fl_b200_decoder *dec, uint32_t index, float *logits_host);
 int fl_b200_decoder_logits(fl_b200_decoder *dec, float *logits_host);
 int fl_b200_decoder_margin(fl_b200_decoder *dec, float *margin_out);
 /* Activations of the last step, for layer-level parity. which: 0 hidden state

@@ -1,0 +1,121 @@
+"""GPU tests of the decoder's batch pass (Decoder::step_batch of the reference:
+m tokens at consecutive positions in one pass) against the same tokens fed one
+by one, and against the CPU oracle's steps."""
+import numpy as np
+import pytest
+
+from fast_llm_b200 import capi, synth
+from fast_llm_b200.decoder import Decoder
+
+pytestmark = pytest.mark.gpu
+torch = pytest.importorskip("torch")
+
+# SMALL: no tensor qualifies for the multi-column kernel (2048 columns); WIDE: wq, wk, wo, gate, up do.
+SMALL = dict(n_layer=2, n_embd=2048, n_head=16, n_kv_head=4, head_dim=128, n_ff=4096, n_vocab=1000, max_kv=96,
+             rope_base=500000.0, eps=1e-5)
+WIDE = dict(n_layer=2, n_embd=4096, n_head=32, n_kv_head=8, head_dim=128, n_ff=4096, n_vocab=1024, max_kv=96,
+            rope_base=500000.0, eps=1e-5)
+TOL = 3e-3
+
+
+def build(ctx, checker, cfg, seed, n_prefill, with_oracle=True):
+    from oracle import pyoracle
+    dec = Decoder(ctx, cfg)
+    orc = pyoracle.LlamaOracle(checker, cfg) if with_oracle else None
+    for l in range(cfg["n_layer"]):
+        for i, name in enumerate(synth.LAYER_TENSORS):
+            w = synth.llama_tensor(cfg, seed, name, l)
+            dec.set_layer_tensor(l, i, synth.Q4_K_M[name], torch.from_numpy(w).cuda())
+            if orc:
+                orc.set_layer_tensor(l, i, synth.Q4_K_M[name], w)
+        an, fn = synth.llama_norm(cfg, seed, "attn_norm", l), synth.llama_norm(cfg, seed, "ffn_norm", l)
+        dec.set_layer_norms(l, torch.from_numpy(an).cuda(), torch.from_numpy(fn).cuda())
+        if orc:
+            orc.set_layer_norms(l, an, fn)
+        if n_prefill:
+            k, v = synth.llama_kv(cfg, seed, l, n_prefill)
+            if orc:
+                orc.seed_kv(l, k, v)
+            for src, dst in zip((k, v), dec.kv_ptrs(l)):
+                full = np.zeros((cfg["n_kv_head"], cfg["max_kv"], cfg["head_dim"]), dtype=np.float16)
+                full[:, :n_prefill] = src
+                capi._ck(ctx.lib.fl_b200_upload(ctx._h, capi.C.c_void_p(dst), capi.C.c_void_p(full.ctypes.data),
+                                                capi.C.c_size_t(full.nbytes)))
+    for which, name in ((capi.G_TOK_EMBD, "tok_embd"), (capi.G_OUTPUT, "output")):
+        w = synth.llama_tensor(cfg, seed, name)
+        dec.set_global(which, synth.Q4_K_M[name], torch.from_numpy(w).cuda())
+        if orc:
+            orc.set_global(which, synth.Q4_K_M[name], w)
+    on = synth.llama_norm(cfg, seed, "out_norm")
+    dec.set_out_norm(torch.from_numpy(on).cuda())
+    if orc:
+        orc.set_out_norm(on)
+        orc.set_n_past(n_prefill)
+    torch.cuda.synchronize()
+    dec.finalize()
+    dec.rewind_to(n_prefill)
+    return dec, orc
+
+
+def rel_err(got, want):
+    return float(np.max(np.abs(got - want)) / (np.sqrt(np.mean(want.astype(np.float64) ** 2)) + 1e-30))
+
+
+@pytest.mark.parametrize("cfg,m", [(SMALL, 5), (WIDE, 8), (WIDE, 3), (WIDE, 1)])
+def test_batch_pass_equals_single_steps_and_oracle(ctx, checker, cfg, m):
+    n_prefill = 37
+    dec, orc = build(ctx, checker, cfg, seed=31, n_prefill=n_prefill)
+    rng = np.random.default_rng(5)
+    toks = [int(t) for t in rng.integers(0, cfg["n_vocab"], m)]
+    outs, margins = dec.step_batch(toks)
+    assert dec.n_past() == n_prefill + m
+    batch_logits = [dec.batch_logits(i) for i in range(m)]
+    # the same tokens one by one from the same start (the pass's cache rows are overwritten before they are read)
+    dec.rewind_to(n_prefill)
+    for i, t in enumerate(toks):
+        nxt = dec.step(t)
+        single = dec.logits()
+        err = rel_err(batch_logits[i], single)
+        assert err < TOL, (i, err)
+        if nxt != outs[i]:
+            assert dec.last_margin() <= 2 * np.max(np.abs(batch_logits[i] - single)), (i, nxt, outs[i])
+        assert abs(margins[i] - dec.last_margin()) <= 4 * np.max(np.abs(batch_logits[i] - single)) + 1e-6
+        want_tok = orc.step(t)
+        want = orc.logits()
+        assert np.all(np.isfinite(batch_logits[i]))
+        # position 0 sees only prefilled keys; later positions read rows whose f16 rounding may differ from the oracle's
+        assert rel_err(batch_logits[i], want) < (TOL if i == 0 else 3 * TOL), (i, rel_err(batch_logits[i], want))
+        if i == 0 and want_tok != outs[0]:
+            assert orc.margin() <= 2 * np.max(np.abs(batch_logits[0] - want))
+    assert ctx.status() == 0
+    dec.close(); orc.close()
+
+
+def test_batch_pass_rules(ctx, checker):
+    dec, _ = build(ctx, checker, SMALL, seed=32, n_prefill=0, with_oracle=False)
+    with pytest.raises(capi.Fl200Error) as e:
+        dec.step_batch([])
+    assert e.value.code == 1
+    with pytest.raises(capi.Fl200Error) as e:
+        dec.step_batch([1] * 9)
+    assert e.value.code == 1
+    with pytest.raises(capi.Fl200Error) as e:
+        dec.step_batch([1, SMALL["n_vocab"]])
+    assert e.value.code == 1
+    dec.rewind_to(SMALL["max_kv"] - 3)
+    with pytest.raises(capi.Fl200Error) as e:
+        dec.step_batch([1, 2, 3, 4])
+    assert e.value.code == 4
+    assert dec.n_past() == SMALL["max_kv"] - 3
+    # prompt ingestion in chunks, then greedy decoding: same tokens as feeding the prompt one by one
+    prompt = [3, 14, 15, 92, 65, 35, 89, 79, 32, 38, 46]
+    dec.rewind_to(0)
+    for i in range(0, len(prompt), 8):
+        outs, _ = dec.step_batch(prompt[i:i + 8])
+    a = [outs[-1]] + [int(t) for t in dec.run(outs[-1], 4)]
+    dec.rewind_to(0)
+    for t in prompt:
+        nxt = dec.step(t)
+    b = [nxt] + [int(t) for t in dec.run(nxt, 4)]
+    assert a == b
+    dec.close()
