@@ -610,16 +610,15 @@ static int enqueue_batch(fl_b200_decoder *d, uint32_t m, cudaStream_t s) {
         CK(launch_embed(d->tok_embd.fmt, d->tok_embd.w, tok + i, E, b.x + (size_t)i * E, s));
     for (uint32_t l = 0; l < c.n_layer; ++l) {
         const Tensor *w = &d->lw[(size_t)l * 7];
-        for (uint32_t i = 0; i < m; ++i)
-            CK(launch_rmsnorm(b.x + (size_t)i * E, d->attn_norm[l], b.xn + (size_t)i * E, c.eps, E, s));
+        CK(launch_rmsnorm(b.x, d->attn_norm[l], b.xn, c.eps, E, s, m, E));
         if (int rc = matmul(ctx, w[FL_B200_T_WQ].fmt, w[FL_B200_T_WQ].w, QD, E, b.xn, m, E, b.q, QD, 0)) return rc;
         if (int rc = matmul(ctx, w[FL_B200_T_WK].fmt, w[FL_B200_T_WK].w, KD, E, b.xn, m, E, b.k, KD, 0)) return rc;
         if (int rc = matmul(ctx, w[FL_B200_T_WV].fmt, w[FL_B200_T_WV].w, KD, E, b.xn, m, E, b.v, KD, 0)) return rc;
-        for (uint32_t i = 0; i < m; ++i) {   // rotate q and k of token i by its own position, append k and v
+        {   // rotate q and k of every token by its own position, append k and v
             RopeAppendArgs r{};
-            r.q = b.q + (size_t)i * QD; r.k = b.k + (size_t)i * KD; r.v = b.v + (size_t)i * KD;
-            r.kcache = d->kc[l]; r.vcache = d->vc[l]; r.pos = pos + i;
+            r.q = b.q; r.k = b.k; r.v = b.v; r.kcache = d->kc[l]; r.vcache = d->vc[l]; r.pos = pos;
             r.n_q_head = d->Hq; r.n_kv_head = d->Hkv; r.head_dim = D; r.kv_stride = c.max_kv; r.theta_scale = theta_scale;
+            r.n_tok = m; r.q_tok_stride = QD; r.kv_tok_stride = KD;
             CK(launch_rope_append(r, s));
         }
         {
@@ -635,15 +634,13 @@ static int enqueue_batch(fl_b200_decoder *d, uint32_t m, cudaStream_t s) {
         }
         // x += Wo att (the residual stays in place)
         if (int rc = matmul(ctx, w[FL_B200_T_WO].fmt, w[FL_B200_T_WO].w, E, QD, b.att, m, QD, b.x, E, 1, w[FL_B200_T_WO].pitch)) return rc;
-        for (uint32_t i = 0; i < m; ++i)
-            CK(launch_rmsnorm(b.x + (size_t)i * E, d->ffn_norm[l], b.xn + (size_t)i * E, c.eps, E, s));
+        CK(launch_rmsnorm(b.x, d->ffn_norm[l], b.xn, c.eps, E, s, m, E));
         if (int rc = matmul(ctx, w[FL_B200_T_GATE].fmt, w[FL_B200_T_GATE].w, F, E, b.xn, m, E, b.g, F, 0)) return rc;
         if (int rc = matmul(ctx, w[FL_B200_T_UP].fmt, w[FL_B200_T_UP].w, F, E, b.xn, m, E, b.u, F, 0)) return rc;
         CK(launch_silu_mul(b.g, b.u, b.g, m * F, s));
         if (int rc = matmul(ctx, w[FL_B200_T_DOWN].fmt, w[FL_B200_T_DOWN].w, E, F, b.g, m, F, b.x, E, 1, w[FL_B200_T_DOWN].pitch)) return rc;
     }
-    for (uint32_t i = 0; i < m; ++i)
-        CK(launch_rmsnorm(b.x + (size_t)i * E, d->out_norm, b.xn + (size_t)i * E, c.eps, E, s));
+    CK(launch_rmsnorm(b.x, d->out_norm, b.xn, c.eps, E, s, m, E));
     if (int rc = matmul(ctx, d->output.fmt, d->output.w, V, E, b.xn, m, E, b.logits, V, 0)) return rc;
     for (uint32_t i = 0; i < m; ++i)
         CK(launch_argmax(b.logits + (size_t)i * V, V, next + i, b.margin + i, ctx->argmax_scratch, ctx->argmax_ticket, ctx->sms, s));

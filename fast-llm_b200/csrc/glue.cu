@@ -13,9 +13,11 @@ namespace {
 // reduction here (the reference sums sequentially); everything after it rounds
 // like the reference: 1/sqrtf(ss/n + eps), then (x*s)*w.
 __global__ void __launch_bounds__(1024) rmsnorm_kernel(const float *__restrict__ x, const float *__restrict__ w,
-                                                       float *__restrict__ y, float eps, uint32_t n) {
+                                                       float *__restrict__ y, float eps, uint32_t n, uint32_t stride) {
     __shared__ float red[32];
     __shared__ float inv;
+    x += (size_t)blockIdx.y * stride;   // one block per vector
+    y += (size_t)blockIdx.y * stride;
     float ss = 0.f;
     for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) ss = fmaf(x[i], x[i], ss);
     ss = warp_sum(ss);
@@ -121,7 +123,8 @@ __global__ void __launch_bounds__(128) rope_append_kernel(const RopeAppendArgs a
     const uint32_t half = a.head_dim / 2;
     const uint32_t t = blockIdx.x * blockDim.x + threadIdx.x;
     const uint32_t n_rot_heads = (a.q ? a.n_q_head : 0) + a.n_kv_head;
-    const uint32_t pos = (uint32_t)*a.pos;
+    const uint32_t tokn = blockIdx.y;   // token of a batch pass (0 in a single step)
+    const uint32_t pos = (uint32_t)a.pos[tokn];
     if (t < n_rot_heads * half) {
         const uint32_t h = t / half, i = t % half;
         float theta = (float)(int32_t)pos;
@@ -129,13 +132,13 @@ __global__ void __launch_bounds__(128) rope_append_kernel(const RopeAppendArgs a
         const float c = cosf(theta), s = sinf(theta);
         const uint32_t nq = a.q ? a.n_q_head : 0;
         if (h < nq) {
-            float *v = a.q + (size_t)h * a.head_dim + 2 * i;
+            float *v = a.q + (size_t)tokn * a.q_tok_stride + (size_t)h * a.head_dim + 2 * i;
             const float x0 = v[0], x1 = v[1];
             v[0] = __fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s));
             v[1] = __fadd_rn(__fmul_rn(x0, s), __fmul_rn(x1, c));
         } else {
             const uint32_t hk = h - nq;
-            const float *v = a.k + (size_t)hk * a.head_dim + 2 * i;
+            const float *v = a.k + (size_t)tokn * a.kv_tok_stride + (size_t)hk * a.head_dim + 2 * i;
             const float x0 = v[0], x1 = v[1];
             __half *dst = a.kcache + ((size_t)hk * a.kv_stride + pos) * a.head_dim + 2 * i;
             dst[0] = __float2half_rn(__fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s)));
@@ -144,7 +147,7 @@ __global__ void __launch_bounds__(128) rope_append_kernel(const RopeAppendArgs a
     } else if (t < (n_rot_heads + a.n_kv_head) * half) {
         const uint32_t u = t - n_rot_heads * half;
         const uint32_t hk = u / half, i = u % half;
-        const float *v = a.v + (size_t)hk * a.head_dim + 2 * i;
+        const float *v = a.v + (size_t)tokn * a.kv_tok_stride + (size_t)hk * a.head_dim + 2 * i;
         __half *dst = a.vcache + ((size_t)hk * a.kv_stride + pos) * a.head_dim + 2 * i;
         dst[0] = __float2half_rn(v[0]);
         dst[1] = __float2half_rn(v[1]);
@@ -230,8 +233,9 @@ __global__ void __launch_bounds__(256) argmax_kernel(const float *__restrict__ l
 } // namespace
 
 cudaError_t launch_rmsnorm(const float *x, const float *wnorm, float *y, float eps, uint32_t n,
-                           cudaStream_t stream) {
-    rmsnorm_kernel<<<1, 1024, 0, stream>>>(x, wnorm, y, eps, n);
+                           cudaStream_t stream, uint32_t rows, uint32_t stride) {
+    if (rows == 0) return cudaErrorInvalidValue;
+    rmsnorm_kernel<<<dim3(1, rows), 1024, 0, stream>>>(x, wnorm, y, eps, n, stride);
     return cudaGetLastError();
 }
 
@@ -263,7 +267,7 @@ cudaError_t launch_rope_append(const RopeAppendArgs &a, cudaStream_t stream) {
     if (a.head_dim == 0 || (a.head_dim & 1u)) return cudaErrorInvalidValue;
     const uint32_t half = a.head_dim / 2;
     const uint32_t n = ((a.q ? a.n_q_head : 0) + 2 * a.n_kv_head) * half;
-    return launch_kernel(rope_append_kernel, dim3((n + 127) / 128), dim3(128), 0, stream, a.pdl != 0, a);
+    return launch_kernel(rope_append_kernel, dim3((n + 127) / 128, a.n_tok ? a.n_tok : 1), dim3(128), 0, stream, a.pdl != 0, a);
 }
 
 cudaError_t launch_rope_table(const int32_t *pos, float theta_scale, uint32_t head_dim, float2 *table, cudaStream_t stream) {

@@ -178,8 +178,9 @@ cudaError_t launch_allreduce_push(const AllReduceArgs &a, cudaStream_t stream, b
 cudaError_t launch_argmax_exchange(const TopExchangeArgs &a, cudaStream_t stream, bool pdl);
 
 // ---- glue.cu ------------------------------------------------------------
+// rows vectors of n floats, `stride` floats apart in x and in y (one weight vector for all).
 cudaError_t launch_rmsnorm(const float *x, const float *wnorm, float *y, float eps, uint32_t n,
-                           cudaStream_t stream);
+                           cudaStream_t stream, uint32_t rows = 1, uint32_t stride = 0);
 cudaError_t launch_add2(const float *a, const float *b, float *y, uint32_t n, cudaStream_t stream);
 // fl_op_router_sel (src/runtime/decode_params.h:234-265): softmax over n_expert logits, top_k by weight.
 cudaError_t launch_router_sel(const float *logits, uint32_t *ids, float *gates, uint32_t n_expert, uint32_t top_k,
@@ -199,6 +200,8 @@ struct RopeAppendArgs {
     uint32_t n_q_head, n_kv_head, head_dim, kv_stride;
     float theta_scale;     // freq_base^(-2/head_dim), computed on the host
     int pdl;
+    // batch pass: n_tok tokens (0 = 1), token i at q + i * q_tok_stride, k / v + i * kv_tok_stride, position pos[i]
+    uint32_t n_tok, q_tok_stride, kv_tok_stride;
 };
 cudaError_t launch_rope_append(const RopeAppendArgs &a, cudaStream_t stream);
 // (cos, sin) of pos * theta_scale^i, i < head_dim / 2, with the angle built by repeated multiplication exactly as
