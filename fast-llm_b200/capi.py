@@ -40,6 +40,10 @@ SYMBOLS = [
     "fl_b200_gguf_open", "fl_b200_gguf_close", "fl_b200_gguf_counts", "fl_b200_gguf_tensor_at", "fl_b200_gguf_find",
     "fl_b200_gguf_has", "fl_b200_gguf_kv_i", "fl_b200_gguf_kv_f", "fl_b200_gguf_kv_s", "fl_b200_gguf_kv_sarr_count",
     "fl_b200_gguf_kv_sarr_at", "fl_b200_gguf_llama_cfg", "fl_b200_decoder_create_gguf",
+    "fl_b200_suffix_create", "fl_b200_suffix_destroy", "fl_b200_suffix_reset", "fl_b200_suffix_push", "fl_b200_suffix_size",
+    "fl_b200_suffix_draft", "fl_b200_spec_cfg_default", "fl_b200_spec_create", "fl_b200_spec_destroy", "fl_b200_spec_choose",
+    "fl_b200_spec_observe", "fl_b200_spec_alpha", "fl_b200_spec_lat_est", "fl_b200_spec_expected_emitted",
+    "fl_b200_decoder_generate_spec",
 ]
 
 
@@ -93,6 +97,12 @@ def load():
     lib.fl_b200_seqpar_destroy.restype = None
     lib.fl_b200_plan_destroy.restype = None
     lib.fl_b200_gguf_close.restype = None
+    for name in ("fl_b200_suffix_destroy", "fl_b200_suffix_reset", "fl_b200_suffix_push", "fl_b200_spec_cfg_default",
+                 "fl_b200_spec_destroy", "fl_b200_spec_observe"):
+        getattr(lib, name).restype = None
+    lib.fl_b200_suffix_size.restype = C.c_uint64
+    for name in ("fl_b200_spec_alpha", "fl_b200_spec_lat_est", "fl_b200_spec_expected_emitted"):
+        getattr(lib, name).restype = C.c_double
     lib.fl_b200_gguf_kv_i.restype = C.c_int64
     lib.fl_b200_gguf_kv_f.restype = C.c_double
     lib.fl_b200_gguf_kv_sarr_count.restype = C.c_int64

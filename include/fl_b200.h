@@ -54,6 +54,8 @@ typedef struct fl_b200_ctx fl_b200_ctx;
 typedef struct fl_b200_decoder fl_b200_decoder;
 typedef struct fl_b200_seqpar fl_b200_seqpar;
 typedef struct fl_b200_gguf fl_b200_gguf;
+typedef struct fl_b200_suffix fl_b200_suffix;
+typedef struct fl_b200_spec fl_b200_spec;
 
 int fl_b200_abi_version(void);
 const char *fl_b200_last_error(void);
@@ -438,6 +440,63 @@ int fl_b200_gguf_kv_sarr_at(const fl_b200_gguf *g, const char *key, uint64_t i, 
  * RoPE scaling (a "llama.rope.scaling.type" other than "none", or a
  * rope_freqs.weight tensor) is refused with FL_B200_ERR_FORMAT. */
 int fl_b200_gguf_llama_cfg(const fl_b200_gguf *g, uint32_t max_kv, fl_b200_llama_cfg *cfg_out);
+/* ---- Speculative decoding around fl_b200_decoder_step_batch (host code). ---- */
+/* Draft source: longest-suffix match over the token stream pushed so far (class
+ * SuffixIndex, src/spec/suffix_index.h:16-114). Every position is indexed by its
+ * trailing 3 tokens; a draft walks at most chain_cap earlier occurrences of the
+ * current tail (most recent first, the tail's own entry included in the count),
+ * keeps the longest match of the whole suffix (ties: the most recent) and, when
+ * it is at least min_match long, proposes the tokens that followed it, up to
+ * n_max and never past the end of the stream. */
+int fl_b200_suffix_create(uint32_t chain_cap, uint32_t min_match, fl_b200_suffix **out);
+void fl_b200_suffix_destroy(fl_b200_suffix *s);
+void fl_b200_suffix_reset(fl_b200_suffix *s);
+void fl_b200_suffix_push(fl_b200_suffix *s, int32_t token);
+uint64_t fl_b200_suffix_size(const fl_b200_suffix *s);
+/* Returns the number of draft tokens written to out (0 = no usable match).
+ * diag_out (optional, 4 values; SuffixIndex::Diag, :41-46): the tail's gram was
+ * indexed, candidates compared, longest match found, entries walked. */
+int fl_b200_suffix_draft(const fl_b200_suffix *s, int32_t n_max, int32_t *out, int32_t *diag_out);
+/* Draft-length controller (class SpecController, src/spec/spec_controller.h:16-107):
+ * choose() = the n in 0..n_max that maximises (1 + a + ... + a^n) / latency(n),
+ * a = running mean of the accepted fraction, latency(n) = running mean per draft
+ * length, unseen lengths seeded from the nearest measured one; n_max before
+ * anything is measured; after probe_iv draftless rounds in a row, probe_n. */
+typedef struct {
+    int32_t n_max;         /* 7 */
+    double alpha0;         /* 0.75 */
+    double alpha_decay;    /* 0.90 */
+    double lat_decay;      /* 0.80 */
+    int32_t probe_iv;      /* 16 */
+    int32_t probe_n;       /* 2 */
+    double seed_slope;     /* 0.15 */
+} fl_b200_spec_cfg;
+void fl_b200_spec_cfg_default(fl_b200_spec_cfg *cfg);
+int fl_b200_spec_create(const fl_b200_spec_cfg *cfg /* null: the defaults */, fl_b200_spec **out);
+void fl_b200_spec_destroy(fl_b200_spec *s);
+int32_t fl_b200_spec_choose(fl_b200_spec *s);
+void fl_b200_spec_observe(fl_b200_spec *s, int32_t n_drafted, int32_t n_accepted, double pass_ms);
+double fl_b200_spec_alpha(const fl_b200_spec *s);
+double fl_b200_spec_lat_est(const fl_b200_spec *s, int32_t n);
+double fl_b200_spec_expected_emitted(const fl_b200_spec *s, int32_t n);
+typedef struct {
+    uint32_t passes, drafted, accepted, emitted;
+    uint32_t n_hist[17];   /* passes by number of drafts */
+    double pass_ms;        /* wall time of all batch passes */
+} fl_b200_spec_stats;
+/* The speculative generation loop of the reference's decode tool
+ * (tools/decode_main.cpp:329-400): writes n_gen tokens to out_tokens_host,
+ * first_token (not yet fed to the model) first. Every round drafts up to
+ * min(spec_max, spec_fixed or the controller's choice) tokens from `idx`,
+ * verifies them in one fl_b200_decoder_step_batch pass, emits the accepted
+ * prefix and takes the model's own token after it; rejected rows of the cache
+ * are dropped by rewinding. spec_fixed < 0: the controller decides and learns
+ * (ctrl required). spec_max <= FL_B200_MAX_BATCH - 1. The reference's margin
+ * gate is not needed: no position of this decoder's batch pass is approximated. */
+int fl_b200_decoder_generate_spec(fl_b200_decoder *dec, int32_t first_token, uint32_t n_gen, int32_t spec_max,
+                                  int32_t spec_fixed, fl_b200_suffix *idx, fl_b200_spec *ctrl,
+                                  int32_t *out_tokens_host, fl_b200_spec_stats *stats_out);
+
 /* Creates the decoder (rank `rank` of `world`; 0 of 1 = single GPU) of a llama
  * GGUF and uploads its tensors, each from the mapping straight to device memory
  * the decoder owns: blk.N.{attn_norm, attn_q, attn_k, attn_v, attn_output,

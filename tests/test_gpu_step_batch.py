@@ -119,3 +119,53 @@ def test_batch_pass_rules(ctx, checker):
     b = [nxt] + [int(t) for t in dec.run(nxt, 4)]
     assert a == b
     dec.close()
+
+
+def test_speculative_generation_equals_greedy(ctx, checker):
+    """The speculative loop emits the greedy sequence whatever the drafts are worth;
+    only the number of passes changes."""
+    from fast_llm_b200 import spec
+    n_prefill, n_gen, first = 20, 40, 5
+    dec, _ = build(ctx, checker, SMALL, seed=33, n_prefill=n_prefill, with_oracle=False)
+    greedy = [first] + [int(t) for t in dec.run(first, n_gen - 1)]
+
+    def gen(index, **kw):
+        dec.rewind_to(n_prefill)
+        toks, st = spec.generate(dec, first, n_gen, index, **kw)
+        assert st.emitted == n_gen and st.accepted <= st.drafted
+        # every pass yields its own token plus the accepted drafts (the last pass may overshoot n_gen)
+        assert sum(st.n_hist) == st.passes and n_gen - 1 <= st.passes + st.accepted <= n_gen - 1 + 7
+        return toks, st
+
+    # an empty history: drafts come only from repetitions of the generated text itself
+    toks, st = gen(spec.SuffixIndex(), spec_fixed=4)
+    assert toks == greedy
+    toks, st = gen(spec.SuffixIndex(), spec_fixed=0)
+    assert toks == greedy and st.drafted == 0 and st.passes == n_gen - 1
+    # the text was seen before: drafts are right, a pass emits several tokens
+    seen = spec.SuffixIndex()
+    for t in greedy:
+        seen.push(t)
+    toks, st = gen(seen, spec_fixed=7)
+    assert toks == greedy
+    assert st.accepted >= 25 and st.passes <= 12, (st.accepted, st.passes)
+    # a misleading history: the same opening, then something else; every draft is rejected at some point
+    wrong = spec.SuffixIndex()
+    for t in greedy[:6] + [(t + 1) % SMALL["n_vocab"] for t in greedy[6:]]:
+        wrong.push(t)
+    toks, st = gen(wrong, spec_fixed=7)
+    assert toks == greedy and st.drafted > 0 and st.accepted < st.drafted
+    # the controller decides the draft length
+    seen2 = spec.SuffixIndex()
+    for t in greedy:
+        seen2.push(t)
+    ctrl = spec.SpecController()
+    toks, st = gen(seen2, ctrl=ctrl)
+    assert toks == greedy and st.accepted > 0
+    assert ctrl.alpha() > 0.75
+    with pytest.raises(capi.Fl200Error):
+        spec.generate(dec, first, 4, seen2, spec_max=8, spec_fixed=1)
+    with pytest.raises(capi.Fl200Error):
+        spec.generate(dec, first, 4, seen2)            # no controller and no fixed length
+    assert ctx.status() == 0
+    dec.close()
