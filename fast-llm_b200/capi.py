@@ -44,6 +44,8 @@ SYMBOLS = [
     "fl_b200_suffix_draft", "fl_b200_spec_cfg_default", "fl_b200_spec_create", "fl_b200_spec_destroy", "fl_b200_spec_choose",
     "fl_b200_spec_observe", "fl_b200_spec_alpha", "fl_b200_spec_lat_est", "fl_b200_spec_expected_emitted",
     "fl_b200_decoder_generate_spec",
+    "fl_b200_moe_create", "fl_b200_moe_destroy", "fl_b200_moe_set_weights", "fl_b200_moe_comm", "fl_b200_moe_set_peers",
+    "fl_b200_moe_forward", "fl_b200_moe_routing",
 ]
 
 
@@ -97,6 +99,7 @@ def load():
     lib.fl_b200_seqpar_destroy.restype = None
     lib.fl_b200_plan_destroy.restype = None
     lib.fl_b200_gguf_close.restype = None
+    lib.fl_b200_moe_destroy.restype = None
     for name in ("fl_b200_suffix_destroy", "fl_b200_suffix_reset", "fl_b200_suffix_push", "fl_b200_spec_cfg_default",
                  "fl_b200_spec_destroy", "fl_b200_spec_observe"):
         getattr(lib, name).restype = None

@@ -1,0 +1,186 @@
+// Mixture-of-experts feed-forward block of the decode graph, single GPU or expert
+// parallel over the GPUs of one box. Per token: router logits (f32 matvec),
+// ROUTER_SEL (fl_op_router_sel, src/runtime/decode_params.h:234-265), the chosen
+// experts' gate / up / down through the expert-indexed matvec (STREAM_DOT_IDX,
+// src/runtime/runtime_internal.h:149-152) with the SiLU product between them, and
+// WMERGE (fl_op_wmerge, :274-295); the reference builds the same chain as tasks
+// (src/model/decoder.cpp:925-1045) and has no multi-GPU form.
+//
+// Expert parallel: rank r of w holds experts [r * n / w, (r + 1) * n / w). The hidden
+// states are replicated, so the dispatch half of the all-to-all moves nothing: every
+// rank routes every token, runs only the slots whose expert it holds (a launch for an
+// expert held elsewhere returns at once and reads no weights), merges them with the
+// other slots' gates set to zero, and the ranks' partial outputs are summed through
+// peer memory by the exchange kernel of the tensor-parallel decoder (rank order, so
+// every rank ends with identical bits). That sum is the combine half.
+#include "capi_internal.h"
+
+using namespace flb;
+
+struct fl_b200_moe {
+    fl_b200_ctx *ctx = nullptr;
+    fl_b200_moe_cfg c{};
+    uint32_t rank = 0, world = 1, n_local = 0, base = 0;
+    const float *router = nullptr;
+    const uint8_t *wg = nullptr, *wu = nullptr, *wd = nullptr;
+    float *logits = nullptr, *gates = nullptr, *mgates = nullptr, *g = nullptr, *u = nullptr, *part = nullptr, *partial = nullptr;
+    uint32_t *ids = nullptr, *lids = nullptr;
+    uint8_t *comm = nullptr;
+    uint8_t *peers[kCommMaxRanks] = {};
+    bool peers_set = false;
+    uint32_t *comm_state = nullptr;
+};
+
+namespace {
+
+// Local expert index and gate of every (token, slot): an expert held by another rank gets the skip mark and gate 0.
+__global__ void ep_mask_kernel(const uint32_t *__restrict__ ids, const float *__restrict__ gates, uint32_t *__restrict__ lids,
+                               float *__restrict__ mgates, uint32_t n, uint32_t base, uint32_t n_local) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const uint32_t e = ids[i];
+    const bool mine = e >= base && e - base < n_local;
+    lids[i] = mine ? e - base : kExpertSkip;
+    mgates[i] = mine ? gates[i] : 0.f;
+}
+
+#define CKM(call)                                                      \
+    do {                                                               \
+        cudaError_t e_ = (call);                                       \
+        if (e_ != cudaSuccess) return cuda_err(e_, #call);             \
+    } while (0)
+
+} // namespace
+
+extern "C" {
+
+int fl_b200_moe_create(fl_b200_ctx *ctx, const fl_b200_moe_cfg *cfg, uint32_t rank, uint32_t world, fl_b200_moe **out) {
+    if (!ctx || !cfg || !out) return set_err(FL_B200_ERR_ARG, "moe_create: null pointer");
+    const fl_b200_moe_cfg &c = *cfg;
+    if (world == 0 || world > kCommMaxRanks || rank >= world) return set_err(FL_B200_ERR_ARG, "moe_create: rank %u of %u", rank, world);
+    if (c.n_expert == 0 || c.n_expert > 256 || c.top_k == 0 || c.top_k > c.n_expert || c.n_expert % world)
+        return set_err(FL_B200_ERR_ARG, "moe_create: %u experts, top %u, %u ranks", c.n_expert, c.top_k, world);
+    if (c.n_embd % 256 || c.n_ff % 256 || c.n_embd < 512 || c.n_ff < 512 || c.max_tokens == 0)
+        return set_err(FL_B200_ERR_ARG, "moe_create: n_embd and n_ff must be multiples of 256 (>= 512), max_tokens > 0");
+    if (world > 1 && (c.n_embd > kCommMaxVec || c.n_embd % (4 * kCommChunks)))
+        return set_err(FL_B200_ERR_ARG, "moe_create: n_embd %u does not fit the exchange buffer", c.n_embd);
+    for (int fmt : {c.fmt_gate_up, c.fmt_down})
+        if (fmt != FL_B200_Q4_K && fmt != FL_B200_Q6_K) return set_err(FL_B200_ERR_ARG, "moe_create: expert format %d (Q4_K or Q6_K)", fmt);
+    CKM(cudaSetDevice(ctx->device));
+    fl_b200_moe *m = new fl_b200_moe();
+    m->ctx = ctx; m->c = c; m->rank = rank; m->world = world;
+    m->n_local = c.n_expert / world;
+    m->base = rank * m->n_local;
+    const size_t T = c.max_tokens, K = c.top_k, E = c.n_embd, F = c.n_ff;
+    auto fail = [&](int rc) { fl_b200_moe_destroy(m); return rc; };
+    auto alloc = [&](void **p, size_t bytes) -> int {
+        if (cudaError_t e = cudaMalloc(p, bytes)) return cuda_err(e, "cudaMalloc (moe)");
+        if (cudaError_t e = cudaMemsetAsync(*p, 0, bytes, ctx->stream)) return cuda_err(e, "cudaMemsetAsync (moe)");
+        return FL_B200_OK;
+    };
+    // zero-filled: a slot that is skipped leaves its buffer as it was, and what is there is then multiplied by gate 0
+    if (int rc = alloc((void **)&m->logits, T * c.n_expert * 4)) return fail(rc);
+    if (int rc = alloc((void **)&m->gates, T * K * 4)) return fail(rc);
+    if (int rc = alloc((void **)&m->mgates, T * K * 4)) return fail(rc);
+    if (int rc = alloc((void **)&m->ids, T * K * 4)) return fail(rc);
+    if (int rc = alloc((void **)&m->lids, T * K * 4)) return fail(rc);
+    if (int rc = alloc((void **)&m->g, F * 4)) return fail(rc);
+    if (int rc = alloc((void **)&m->u, F * 4)) return fail(rc);
+    if (int rc = alloc((void **)&m->part, T * K * E * 4)) return fail(rc);
+    if (world > 1) {
+        if (int rc = alloc((void **)&m->partial, T * E * 4)) return fail(rc);
+        if (int rc = alloc((void **)&m->comm, comm_buffer_bytes())) return fail(rc);
+        if (int rc = alloc((void **)&m->comm_state, 64)) return fail(rc);
+    }
+    CKM(cudaStreamSynchronize(ctx->stream));
+    *out = m;
+    return FL_B200_OK;
+}
+
+void fl_b200_moe_destroy(fl_b200_moe *m) {
+    if (!m) return;
+    cudaSetDevice(m->ctx->device);
+    cudaStreamSynchronize(m->ctx->stream);
+    cudaFree(m->logits); cudaFree(m->gates); cudaFree(m->mgates); cudaFree(m->ids); cudaFree(m->lids); cudaFree(m->g);
+    cudaFree(m->u); cudaFree(m->part); cudaFree(m->partial); cudaFree(m->comm); cudaFree(m->comm_state);
+    delete m;
+}
+
+int fl_b200_moe_set_weights(fl_b200_moe *m, const float *router, const void *gate, const void *up, const void *down) {
+    if (!m || !router || !gate || !up || !down) return set_err(FL_B200_ERR_ARG, "moe_set_weights: null pointer");
+    if (((uintptr_t)gate | (uintptr_t)up | (uintptr_t)down | (uintptr_t)router) & 15u)
+        return set_err(FL_B200_ERR_ARG, "moe_set_weights: tensors must be 16-byte aligned");
+    m->router = router;
+    m->wg = (const uint8_t *)gate; m->wu = (const uint8_t *)up; m->wd = (const uint8_t *)down;
+    return FL_B200_OK;
+}
+
+int fl_b200_moe_comm(fl_b200_moe *m, void **buf, size_t *bytes) {
+    if (!m || !buf || !bytes) return set_err(FL_B200_ERR_ARG, "moe_comm: null");
+    *buf = m->comm;
+    *bytes = m->comm ? comm_buffer_bytes() : 0;
+    return FL_B200_OK;
+}
+
+int fl_b200_moe_set_peers(fl_b200_moe *m, void *const *bufs, uint32_t n) {
+    if (!m || !bufs) return set_err(FL_B200_ERR_ARG, "moe_set_peers: null");
+    if (n != m->world) return set_err(FL_B200_ERR_ARG, "moe_set_peers: %u buffers for %u ranks", n, m->world);
+    for (uint32_t p = 0; p < n; ++p) {
+        if (!bufs[p]) return set_err(FL_B200_ERR_ARG, "moe_set_peers: buffer of rank %u is null", p);
+        m->peers[p] = (uint8_t *)bufs[p];
+    }
+    if (m->world > 1 && m->peers[m->rank] != m->comm) return set_err(FL_B200_ERR_ARG, "moe_set_peers: entry %u must be this rank's own buffer", m->rank);
+    m->peers_set = true;
+    return FL_B200_OK;
+}
+
+int fl_b200_moe_forward(fl_b200_moe *m, const float *x, uint32_t n_tok, float *y) {
+    if (!m || !x || !y) return set_err(FL_B200_ERR_ARG, "moe_forward: null pointer");
+    if (!m->router) return set_err(FL_B200_ERR_STATE, "moe_forward: set the weights first");
+    if (m->world > 1 && !m->peers_set) return set_err(FL_B200_ERR_STATE, "moe_forward: set the peers' exchange buffers first");
+    if (n_tok == 0 || n_tok > m->c.max_tokens) return set_err(FL_B200_ERR_ARG, "moe_forward: %u tokens outside 1..%u", n_tok, m->c.max_tokens);
+    fl_b200_ctx *ctx = m->ctx;
+    cudaStream_t s = ctx->stream;
+    CKM(cudaSetDevice(ctx->device));
+    const fl_b200_moe_cfg &c = m->c;
+    const uint32_t E = c.n_embd, F = c.n_ff, K = c.top_k, NE = c.n_expert;
+    const uint64_t stride_gu = (uint64_t)F * row_bytes(c.fmt_gate_up, E), stride_d = (uint64_t)E * row_bytes(c.fmt_down, F);
+    if (int rc = matmul(ctx, FL_B200_F32, m->router, NE, E, x, n_tok, E, m->logits, NE, 0)) return rc;
+    for (uint32_t t = 0; t < n_tok; ++t)
+        CKM(launch_router_sel(m->logits + (size_t)t * NE, m->ids + (size_t)t * K, m->gates + (size_t)t * K, NE, K, c.norm, c.scale, s));
+    ep_mask_kernel<<<(n_tok * K + 127) / 128, 128, 0, s>>>(m->ids, m->gates, m->lids, m->mgates, n_tok * K, m->base, m->n_local);
+    CKM(cudaGetLastError());
+    for (uint32_t t = 0; t < n_tok; ++t) {
+        const float *xt = x + (size_t)t * E;
+        for (uint32_t k = 0; k < K; ++k) {
+            const uint32_t *lid = m->lids + (size_t)t * K + k;
+            float *part = m->part + ((size_t)t * K + k) * E;
+            if (int rc = matmul(ctx, c.fmt_gate_up, m->wg, F, E, xt, 1, 0, m->g, 0, 0, 0, lid, stride_gu)) return rc;
+            if (int rc = matmul(ctx, c.fmt_gate_up, m->wu, F, E, xt, 1, 0, m->u, 0, 0, 0, lid, stride_gu)) return rc;
+            CKM(launch_silu_mul(m->g, m->u, m->g, F, s));
+            if (int rc = matmul(ctx, c.fmt_down, m->wd, E, F, m->g, 1, 0, part, 0, 0, 0, lid, stride_d)) return rc;
+        }
+        float *dst = (m->world > 1 ? m->partial : y) + (size_t)t * E;
+        CKM(launch_wmerge(m->part + (size_t)t * K * E, m->mgates + (size_t)t * K, nullptr, nullptr, dst, 1.0f, K, E, K, s));
+    }
+    if (m->world > 1) {
+        for (uint32_t t = 0; t < n_tok; ++t) {   // the combine: sum of the ranks' partial outputs, rank order
+            AllReduceArgs r{};
+            for (uint32_t p = 0; p < m->world; ++p) r.peers[p] = m->peers[p];
+            r.in = m->partial + (size_t)t * E; r.resid = nullptr; r.out = y + (size_t)t * E; r.n = E;
+            r.rank = m->rank; r.world = m->world; r.st = CommState{m->comm_state}; r.status = ctx->status;
+            CKM(launch_allreduce_resid(r, s, false));
+        }
+    }
+    return FL_B200_OK;
+}
+
+int fl_b200_moe_routing(fl_b200_moe *m, uint32_t n_tok, uint32_t *ids_host, float *gates_host) {
+    if (!m || n_tok == 0 || n_tok > m->c.max_tokens) return set_err(FL_B200_ERR_ARG, "moe_routing: bad argument");
+    const size_t n = (size_t)n_tok * m->c.top_k;
+    if (ids_host) if (int rc = fl_b200_download(m->ctx, ids_host, m->ids, n * 4)) return rc;
+    if (gates_host) if (int rc = fl_b200_download(m->ctx, gates_host, m->gates, n * 4)) return rc;
+    return FL_B200_OK;
+}
+
+} // extern "C"

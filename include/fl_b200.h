@@ -55,6 +55,7 @@ typedef struct fl_b200_decoder fl_b200_decoder;
 typedef struct fl_b200_seqpar fl_b200_seqpar;
 typedef struct fl_b200_gguf fl_b200_gguf;
 typedef struct fl_b200_suffix fl_b200_suffix;
+typedef struct fl_b200_moe fl_b200_moe;
 typedef struct fl_b200_spec fl_b200_spec;
 
 int fl_b200_abi_version(void);
@@ -440,6 +441,42 @@ int fl_b200_gguf_kv_sarr_at(const fl_b200_gguf *g, const char *key, uint64_t i, 
  * RoPE scaling (a "llama.rope.scaling.type" other than "none", or a
  * rope_freqs.weight tensor) is refused with FL_B200_ERR_FORMAT. */
 int fl_b200_gguf_llama_cfg(const fl_b200_gguf *g, uint32_t max_kv, fl_b200_llama_cfg *cfg_out);
+/* ---- Mixture-of-experts feed-forward block (the MoE configuration: 8 experts,
+ *      top-2), single GPU or expert parallel. The reference builds the chain
+ *      router matvec -> ROUTER_SEL -> STREAM_DOT_IDX x3 with SILU_MUL -> WMERGE
+ *      as tasks (src/model/decoder.cpp:925-1045, src/runtime/decode_params.h:
+ *      234-295) and has no multi-GPU form. ---- */
+typedef struct {
+    uint32_t n_embd, n_ff, n_expert, top_k;
+    uint32_t norm;         /* RouterP::norm: renormalise the chosen weights */
+    float scale;           /* RouterP::scale (expert_weights_scale) */
+    int32_t fmt_gate_up, fmt_down;   /* Q4_K or Q6_K */
+    uint32_t max_tokens;   /* tokens per fl_b200_moe_forward call */
+} fl_b200_moe_cfg;
+/* Rank `rank` of `world` (0 of 1: single GPU) holds experts
+ * [rank * n_expert / world, (rank + 1) * n_expert / world). The hidden states are
+ * replicated over the ranks, so dispatch moves nothing: every rank routes every
+ * token and runs only the slots whose expert it holds; the combine is one sum of
+ * the ranks' partial outputs through peer memory, in rank order (all ranks end
+ * with identical bits). Set-up for world > 1 is the decoder's: export
+ * fl_b200_moe_comm's buffer, open the others', fl_b200_moe_set_peers. */
+int fl_b200_moe_create(fl_b200_ctx *ctx, const fl_b200_moe_cfg *cfg, uint32_t rank, uint32_t world, fl_b200_moe **out);
+void fl_b200_moe_destroy(fl_b200_moe *moe);
+/* router_dev: f32 [n_expert][n_embd], whole on every rank. gate / up: this rank's
+ * experts stacked, [n_local][n_ff rows of n_embd columns]; down: [n_local][n_embd
+ * rows of n_ff columns]; GGUF block layout, 16-byte aligned. The block keeps the
+ * pointers. */
+int fl_b200_moe_set_weights(fl_b200_moe *moe, const float *router_dev, const void *gate_dev, const void *up_dev,
+                            const void *down_dev);
+int fl_b200_moe_comm(fl_b200_moe *moe, void **buf_dev_out, size_t *bytes_out);
+int fl_b200_moe_set_peers(fl_b200_moe *moe, void *const *bufs_dev, uint32_t n);
+/* y[t] = sum over the top_k experts e of token t of weight_e * down_e(silu(gate_e x[t]) * up_e x[t]), t < n_tok;
+ * x_dev, y_dev: [n_tok][n_embd] f32. Enqueued on the context's stream. With
+ * world > 1 all ranks call it with the same x. */
+int fl_b200_moe_forward(fl_b200_moe *moe, const float *x_dev, uint32_t n_tok, float *y_dev);
+/* Expert ids and weights chosen in the last forward call, [n_tok][top_k]. */
+int fl_b200_moe_routing(fl_b200_moe *moe, uint32_t n_tok, uint32_t *ids_host, float *gates_host);
+
 /* ---- Speculative decoding around fl_b200_decoder_step_batch (host code). ---- */
 /* Draft source: longest-suffix match over the token stream pushed so far (class
  * SuffixIndex, src/spec/suffix_index.h:16-114). Every position is indexed by its

@@ -162,3 +162,39 @@ def test_exec_task_moe_kinds(ctx, checker):
     ctx.exec_task(t)
     ctx.sync()
     assert rel_err(y.cpu().numpy(), checker.matvec(capi.Q4_K, w[2 * rows:], rows, cols, x)) <= 1e-3
+
+
+def test_moe_block_vs_oracle(ctx, checker):
+    """The whole block as one call (fl_b200_moe_forward) for several tokens, against the
+    oracle's chain of operators; also what a second call leaves behind in the reused buffers."""
+    from fast_llm_b200.moe import MoeBlock
+    rng = np.random.default_rng(29)
+    E, F, NE, K, T = 4096, 1024, 8, 2, 5
+    wg = synth.q4k_tensor(rng, NE * F, E); wu = synth.q4k_tensor(rng, NE * F, E); wd_ = synth.q6k_tensor(rng, NE * E, F)
+    wr = (rng.standard_normal((NE, E)) * 0.02).astype(np.float32)
+    blk = MoeBlock(ctx, E, F, NE, K, norm=1, scale=1.0, fmt_gate_up=capi.Q4_K, fmt_down=capi.Q6_K, max_tokens=T)
+    blk.set_weights(dev(wr), dev(wg), dev(wu), dev(wd_))
+    for trial in range(2):
+        x = rng.standard_normal((T, E)).astype(np.float32)
+        xd = dev(x); y = torch.zeros((T, E), device="cuda")
+        torch.cuda.synchronize()
+        blk.forward(xd, T, y)
+        ctx.sync()
+        assert ctx.status() == 0
+        ids, gates = blk.routing(T)
+        got = y.cpu().numpy()
+        for t in range(T):
+            logits = checker.matvec(capi.F32, wr.view(np.uint8).reshape(NE, -1), NE, E, x[t])
+            want_ids, want_gates = checker.router_sel(logits, K, 1, 1.0)
+            assert list(ids[t]) == list(want_ids)
+            assert np.allclose(gates[t], want_gates, rtol=1e-5)
+            parts = np.zeros((K, E), dtype=np.float32)
+            for k, e in enumerate(want_ids):
+                g = checker.matvec(capi.Q4_K, wg[e * F:(e + 1) * F], F, E, x[t])
+                u = checker.matvec(capi.Q4_K, wu[e * F:(e + 1) * F], F, E, x[t])
+                parts[k] = checker.matvec(capi.Q6_K, wd_[e * E:(e + 1) * E], E, F, checker.silu_mul(g, u))
+            want = checker.wmerge(parts, np.asarray(want_gates, dtype=np.float32), None, None, 1.0)
+            assert rel_err(got[t], want) <= 2e-3, (trial, t)
+    with pytest.raises(capi.Fl200Error):
+        blk.forward(xd, T + 1, y)
+    blk.close()

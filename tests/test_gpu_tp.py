@@ -254,3 +254,86 @@ def test_sequence_parallel_attention_two_ranks():
         b, err_b = res[1][key]
         assert np.array_equal(a.view(np.uint32), b.view(np.uint32))     # both ranks: identical bits
         assert err_a <= 1e-5 and err_b <= 1e-5, (key, err_a, err_b)      # = one GPU over all keys (f32 reassociation)
+
+
+def _moe_worker(rank, world, port, q_out):
+    try:
+        import torch.distributed as dist
+        os.environ["MASTER_ADDR"] = "127.0.0.1"
+        os.environ["MASTER_PORT"] = str(port)
+        torch.cuda.set_device(rank)
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+        from fast_llm_b200 import capi, synth
+        from fast_llm_b200.moe import MoeBlock, local_experts
+        ctx = capi.Context(rank)
+        E, F, NE, K, T = 4096, 1024, 8, 2, 16
+        rng = np.random.default_rng(41)                     # the same model on every rank
+        wg = synth.q4k_tensor(rng, NE * F, E); wu = synth.q4k_tensor(rng, NE * F, E); wd = synth.q4k_tensor(rng, NE * E, F)
+        wr = (rng.standard_normal((NE, E)) * 0.02).astype(np.float32)
+        x = rng.standard_normal((T, E)).astype(np.float32)
+        dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+        first, n = local_experts(NE, rank, world)
+        blk = MoeBlock(ctx, E, F, NE, K, max_tokens=T, ep=(rank, world))
+        blk.set_weights(dev(wr), dev(wg[first * F:(first + n) * F]), dev(wu[first * F:(first + n) * F]),
+                        dev(wd[first * E:(first + n) * E]))
+        blk.connect(dist)
+        xd = dev(x)
+        res = {"y": []}
+        for n_tok in (T, 3, T):                             # the exchange buffers alternate between calls
+            y = torch.zeros((n_tok, E), device="cuda")
+            torch.cuda.synchronize()
+            dist.barrier()
+            blk.forward(xd, n_tok, y)
+            ctx.sync()
+            res["y"].append(y.cpu().numpy())
+        res["ids"] = blk.routing(T)[0]
+        res["status"] = ctx.status()
+        dist.barrier()
+        if rank == 0:                                       # all experts on one GPU
+            one = MoeBlock(ctx, E, F, NE, K, max_tokens=T)
+            one.set_weights(dev(wr), dev(wg), dev(wu), dev(wd))
+            y = torch.zeros((T, E), device="cuda")
+            torch.cuda.synchronize()
+            one.forward(xd, T, y)
+            ctx.sync()
+            res["ref"] = y.cpu().numpy()
+            res["ref_ids"] = one.routing(T)[0]
+            one.close()
+        dist.barrier()
+        blk.close()
+        ctx.close()
+        dist.destroy_process_group()
+        q_out.put((rank, res))
+    except Exception:
+        import traceback
+        q_out.put((rank, "ERROR " + traceback.format_exc()))
+
+
+def test_two_rank_expert_parallel_moe_matches_single_gpu():
+    """Expert parallelism of the MoE block (4 of the 8 experts per GPU): the ranks'
+    outputs are identical bits and equal the single-GPU block up to the order of one sum."""
+    if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    import torch.multiprocessing as mp
+    mpc = mp.get_context("spawn")
+    q = mpc.Queue()
+    port = _free_port()
+    procs = [mpc.Process(target=_moe_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = dict(q.get(timeout=600) for _ in procs)
+    for p in procs:
+        p.join(timeout=120)
+    for r in (0, 1):
+        assert not isinstance(res[r], str), res[r]
+        assert res[r]["status"] == 0
+    a, b = res[0], res[1]
+    assert np.array_equal(a["ids"], b["ids"]) and np.array_equal(a["ids"], a["ref_ids"])
+    assert len(set(a["ids"].ravel() // 4)) == 2            # both ranks' experts are in use
+    for ya, yb in zip(a["y"], b["y"]):
+        assert np.array_equal(ya.view(np.uint32), yb.view(np.uint32))
+    ref = a["ref"]
+    scale = np.sqrt(np.mean(ref.astype(np.float64) ** 2))
+    assert np.max(np.abs(a["y"][0] - ref)) <= 1e-5 * scale
+    assert np.array_equal(a["y"][0].view(np.uint32), a["y"][2].view(np.uint32))
+    assert np.array_equal(a["y"][1].view(np.uint32), a["y"][0][:3].view(np.uint32))

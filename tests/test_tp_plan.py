@@ -144,3 +144,11 @@ def test_merge_lse_equals_softmax_over_all_keys():
             m = s[sl].max(); e = np.exp(s[sl] - m)
             recs.append((e @ v[sl] / e.sum(), m, e.sum()))
         assert np.allclose(tp.merge_lse(recs), want, rtol=1e-12, atol=1e-12)
+
+
+def test_expert_partition():
+    from fast_llm_b200.moe import local_experts
+    assert [local_experts(8, r, 4) for r in range(4)] == [(0, 2), (2, 2), (4, 2), (6, 2)]
+    assert local_experts(8, 0, 1) == (0, 8) and local_experts(8, 7, 8) == (7, 1)
+    with pytest.raises(ValueError):
+        local_experts(8, 0, 3)
