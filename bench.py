@@ -324,6 +324,22 @@ def measure(tp_mode, args, ctx, cfg, config, dist, gloo, rank, local_rank, world
                 "d2h_bytes_per_step": 4},
         "gpu_launches": launches * steps, "clocks": clocks, "last_token": int(toks[-1]),
     }
+    if not tp_mode and world == 1:
+        # Decoder::step_batch (draft verification / prompt chunks): 8 tokens at consecutive positions in one pass,
+        # timed with device events around the public call (tokens in, greedy tokens and margins out)
+        m, reps = 8, 5
+        dec.rewind_to(N_PREFILL)
+        dec.step_batch(list(range(1, m + 1)))
+        dec.rewind_to(N_PREFILL)
+        dec.step_batch(list(range(1, m + 1)))
+        ctx.timer_start()
+        for _ in range(reps):
+            dec.rewind_to(N_PREFILL)
+            dec.step_batch(list(range(1, m + 1)))
+        bp_ms = ctx.timer_stop() / reps
+        out["batch_pass"] = {"m": m, "ms_per_pass": bp_ms, "positions_per_s": m / (bp_ms * 1e-3),
+                             "single_steps_ms": m * ms_dev / steps,
+                             "note": "Q4_K tensors once per pass (multi-column kernel), Q6_K tensors once per token"}
     if tp_mode:
         out["roofline"]["per_gpu"] = "bytes are this rank's share (1/%d of the weights and KV); fractions are per GPU" % world
         out["roofline"]["exchange"] = {"launches_per_step": cm_n, "ms_per_step": cm_ms, "avg_launch_us": cm_ms * 1e3 / max(cm_n, 1)}

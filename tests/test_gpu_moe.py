@@ -195,6 +195,14 @@ def test_moe_block_vs_oracle(ctx, checker):
                 parts[k] = checker.matvec(capi.Q6_K, wd_[e * E:(e + 1) * E], E, F, checker.silu_mul(g, u))
             want = checker.wmerge(parts, np.asarray(want_gates, dtype=np.float32), None, None, 1.0)
             assert rel_err(got[t], want) <= 2e-3, (trial, t)
+    # a call that repeats the one before it is recorded as a CUDA graph, then replayed: same bits every time
+    first = y.cpu().numpy().copy()
+    for _ in range(3):
+        y.zero_()
+        torch.cuda.synchronize()
+        blk.forward(xd, T, y)
+        ctx.sync()
+        assert np.array_equal(y.cpu().numpy().view(np.uint32), first.view(np.uint32))
     with pytest.raises(capi.Fl200Error):
         blk.forward(xd, T + 1, y)
     blk.close()

@@ -286,6 +286,12 @@ def _moe_worker(rank, world, port, q_out):
             blk.forward(xd, n_tok, y)
             ctx.sync()
             res["y"].append(y.cpu().numpy())
+        for _ in range(3):                                   # recorded as a CUDA graph, then replayed
+            torch.cuda.synchronize()
+            dist.barrier()
+            blk.forward(xd, T, y)
+            ctx.sync()
+            res["y"].append(y.cpu().numpy())
         res["ids"] = blk.routing(T)[0]
         res["status"] = ctx.status()
         dist.barrier()
@@ -337,3 +343,5 @@ def test_two_rank_expert_parallel_moe_matches_single_gpu():
     assert np.max(np.abs(a["y"][0] - ref)) <= 1e-5 * scale
     assert np.array_equal(a["y"][0].view(np.uint32), a["y"][2].view(np.uint32))
     assert np.array_equal(a["y"][1].view(np.uint32), a["y"][0][:3].view(np.uint32))
+    for later in a["y"][3:]:
+        assert np.array_equal(later.view(np.uint32), a["y"][0].view(np.uint32))
