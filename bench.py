@@ -165,7 +165,13 @@ def main():
                          "measurement of the same run under the key \"tp\"")
     ap.add_argument("--layers", type=int, default=32,
                     help="number of layers (32 = the benchmark; fewer = a small case of the same kernels for profiler captures, not a benchmark number)")
+    ap.add_argument("--case", default="decode", choices=["decode", "matmul-nx8", "attn-long"],
+                    help="decode = the benchmark (default). matmul-nx8 = the multi-column Q4_K matmul alone (gate|up shape, 8 "
+                         "columns); attn-long = decode attention alone at 32K / 64K / 128K keys: kernel cases for profiler "
+                         "captures and sweeps, each prints its own JSON line and is not the benchmark number")
     args = ap.parse_args()
+    if args.case != "decode":
+        return kernel_case(args.case, max(1, args.steps), max(3, args.warmup))
     steps, warmup = max(1, args.steps), max(3, args.warmup)
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -229,6 +235,62 @@ def main():
         dist.destroy_process_group()
     if rank == 0:
         print(json.dumps(out))
+
+
+def kernel_case(case, steps, warmup):
+    """One kernel alone on cuda:0, through the C ABI, timed with device events; inputs rotate over
+    more than L2 (126 MB) of distinct weights or keys."""
+    import torch
+    from fast_llm_b200 import capi, synth
+    ctx = capi.Context(0)
+    peak, _ = measured_peaks()
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(1)
+    if case == "matmul-nx8":
+        rows, cols, nx, copies = 28672, 4096, 8, 3
+        w = [synth.device_quant_tensor(capi.Q4_K, rows, cols, gen) for _ in range(copies)]
+        x = torch.randn((nx, cols), device="cuda", generator=gen)
+        y = torch.zeros((nx, rows), device="cuda")
+        torch.cuda.synchronize()
+
+        def run(n):
+            for i in range(n):
+                ctx.matvec(capi.Q4_K, w[i % copies], rows, cols, x, y, nx=nx, xstride=cols, ystride=rows)
+        run(warmup)
+        ctx.sync()
+        ctx.timer_start()
+        run(steps)
+        us = ctx.timer_stop() * 1e3 / steps
+        nbytes = rows * capi.row_bytes(capi.Q4_K, cols)
+        print(json.dumps({"case": case, "kernel": "matvec_q4k_mma_nx_kernel", "rows": rows, "cols": cols, "columns": nx,
+                          "us_per_pass": us, "weight_bytes": nbytes, "achieved_gbs": nbytes / us / 1e3,
+                          "frac_of_measured_hbm": nbytes / us / 1e3 / peak, "status": ctx.status()}))
+        return
+    # attn-long: the long-context configuration (f16 K/V ~ N(0, 1)/sqrt(128), 32 query / 8 KV heads of 128)
+    out = []
+    for kv_len, batch in ((32768, 1), (32768, 4), (65536, 1), (65536, 4), (131072, 1), (131072, 4), (32768, 16), (131072, 16)):
+        nkv, nq, d = 8, 32, 128
+        copies = max(1, int(300e6 // (2 * batch * nkv * kv_len * d * 2)) + 1)   # distinct caches worth more than L2
+        k = [(torch.randn((batch, nkv, kv_len, d), device="cuda", generator=gen) / 128 ** 0.5).half() for _ in range(copies)]
+        v = [(torch.randn((batch, nkv, kv_len, d), device="cuda", generator=gen) / 128 ** 0.5).half() for _ in range(copies)]
+        q = torch.randn((batch, nq, d), device="cuda", generator=gen)
+        o = torch.zeros((batch, nq, d), device="cuda")
+        torch.cuda.synchronize()
+
+        def run(n):
+            for i in range(n):
+                ctx.attn_decode(q, k[i % copies], v[i % copies], nq, nkv, d, kv_len, kv_len, batch, 1.0 / 128 ** 0.5, o)
+        run(warmup)
+        ctx.sync()
+        ctx.timer_start()
+        run(steps)
+        us = ctx.timer_stop() * 1e3 / steps
+        nbytes = 2 * batch * nkv * kv_len * d * 2
+        out.append({"kv_len": kv_len, "batch": batch, "us": us, "kv_bytes": nbytes, "achieved_gbs": nbytes / us / 1e3,
+                    "frac_of_measured_hbm": nbytes / us / 1e3 / peak})
+        del k, v
+        torch.cuda.empty_cache()
+    print(json.dumps({"case": case, "kernel": "attn_decode_kernel", "peak_gbs": peak, "points": out, "status": ctx.status()}))
 
 
 def measure(tp_mode, args, ctx, cfg, config, dist, gloo, rank, local_rank, world, steps, warmup):
