@@ -49,7 +49,7 @@ def measured_peaks():
 
 class ClockSampler:
     """nvidia-smi clocks and throttle reasons, sampled while the timed region runs."""
-    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+    QUERY = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
@@ -63,12 +63,18 @@ class ClockSampler:
         try:
             self.out = open(self.path, "w")
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.device), "--query-gpu=" + self.QUERY,
-                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=self.out,
+                                          "--format=csv,noheader,nounits", "-lms", "50"], stdout=self.out,
                                          stderr=subprocess.DEVNULL)
         except Exception:
             self.proc = None
 
+    def mark(self):
+        """Start of the region whose samples count (nvidia-smi itself is started earlier: it takes a while
+        to come up, longer with one instance per rank)."""
+        self.t0 = time.time()
+
     def stop(self):
+        t1 = time.time()
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
@@ -77,23 +83,30 @@ class ClockSampler:
         except Exception:
             self.proc.kill()
         self.out.close()
-        sm, mx, reasons = [], [], set()
+        import datetime
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        rows = []
         for line in open(self.path):
             f = [x.strip() for x in line.split(",")]
             if len(f) < 9:
                 continue
             try:
-                sm.append(float(f[1])); mx.append(float(f[2]))
+                ts = datetime.datetime.strptime(f[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                rows.append((ts, float(f[1]), float(f[2]), [n for n, v in zip(names, f[5:9]) if v.lower().startswith("active")]))
             except ValueError:
                 continue
-            for name, v in zip(names, f[5:9]):
-                if v.lower().startswith("active"):
-                    reasons.add(name)
-        if not sm:
+        t0 = getattr(self, "t0", 0.0)
+        inside = [r for r in rows if t0 - 0.05 <= r[0] <= t1 + 0.05]
+        window = "timed region"
+        if not inside:   # a region shorter than the sampling period: the nearest samples on either side of it
+            inside = sorted(rows, key=lambda r: min(abs(r[0] - t0), abs(r[0] - t1)))[:2]
+            window = "nearest to the timed region"
+        if not inside:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
-        sm.sort()
-        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+        sm = sorted(r[1] for r in inside)
+        reasons = sorted({n for r in inside for n in r[3]})
+        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": max(r[2] for r in inside), "reasons": reasons,
+                "samples": len(inside), "window": window}
 
 
 def cpu_reference_arm(steps, warmup, threads=None):
@@ -302,6 +315,8 @@ def measure(tp_mode, args, ctx, cfg, config, dist, gloo, rank, local_rank, world
     if world > 1:
         config["parallelism"] = ("tp%d (one sequence; KV heads + matvec rows/columns per GPU, 2 all-reduces per layer through "
                                  "peer memory)" % world) if tp_mode else "replicas x%d (independent sequences, no data-path collective)" % world
+    sampler = ClockSampler(local_rank)
+    sampler.start()   # before the model is built: running by the time the timed region starts
     dec = Decoder(ctx, cfg, tp=(rank, world) if tp_mode else None)
     synth.device_llama(dec, cfg, seed=1234 if tp_mode else 1234 + rank, n_prefill=N_PREFILL)
     if tp_mode:
@@ -323,12 +338,11 @@ def measure(tp_mode, args, ctx, cfg, config, dist, gloo, rank, local_rank, world
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    sampler = ClockSampler(local_rank)
     # ---- value: device-resident feedback loop ----
     dec.rewind_to(N_PREFILL)
     dec.run(1, warmup)
     barrier()
-    sampler.start()
+    sampler.mark()
     ctx.timer_start()
     toks = dec.run(1, steps)
     ms_dev = ctx.timer_stop()
