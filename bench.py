@@ -178,10 +178,11 @@ def main():
                          "measurement of the same run under the key \"tp\"")
     ap.add_argument("--layers", type=int, default=32,
                     help="number of layers (32 = the benchmark; fewer = a small case of the same kernels for profiler captures, not a benchmark number)")
-    ap.add_argument("--case", default="decode", choices=["decode", "matmul-nx8", "attn-long"],
+    ap.add_argument("--case", default="decode", choices=["decode", "matmul-nx8", "attn-long", "moe"],
                     help="decode = the benchmark (default). matmul-nx8 = the multi-column Q4_K matmul alone (gate|up shape, 8 "
-                         "columns); attn-long = decode attention alone at 32K / 64K / 128K keys: kernel cases for profiler "
-                         "captures and sweeps, each prints its own JSON line and is not the benchmark number")
+                         "columns); attn-long = decode attention alone at 32K / 64K / 128K keys; moe = the MoE feed-forward "
+                         "block at the Mixtral shape (8 experts, top-2, 16 tokens; expert parallel under torchrun): kernel "
+                         "cases for profiler captures and sweeps, each prints its own JSON line and is not the benchmark number")
     args = ap.parse_args()
     if args.case != "decode":
         return kernel_case(args.case, max(1, args.steps), max(3, args.warmup))
@@ -279,6 +280,8 @@ def kernel_case(case, steps, warmup):
                           "us_per_pass": us, "weight_bytes": nbytes, "achieved_gbs": nbytes / us / 1e3,
                           "frac_of_measured_hbm": nbytes / us / 1e3 / peak, "status": ctx.status()}))
         return
+    if case == "moe":
+        return moe_case(ctx, steps, warmup, peak)
     # attn-long: the long-context configuration (f16 K/V ~ N(0, 1)/sqrt(128), 32 query / 8 KV heads of 128)
     out = []
     for kv_len, batch in ((32768, 1), (32768, 4), (65536, 1), (65536, 4), (131072, 1), (131072, 4), (32768, 16), (131072, 16)):
@@ -304,6 +307,74 @@ def kernel_case(case, steps, warmup):
         del k, v
         torch.cuda.empty_cache()
     print(json.dumps({"case": case, "kernel": "attn_decode_kernel", "peak_gbs": peak, "points": out, "status": ctx.status()}))
+
+
+def moe_case(ctx0, steps, warmup, peak):
+    """The MoE configuration's feed-forward block: 8 experts of gate / up 14336 x 4096 and down 4096 x 14336
+    (Q4_K), f32 router ~ N(0, 0.02), 16 tokens, top-2 with renormalised weights. One process per GPU under
+    torchrun: expert parallel (8 / N experts per rank), time = max over ranks."""
+    import torch
+    from fast_llm_b200 import capi, synth
+    from fast_llm_b200.moe import MoeBlock, local_experts
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    dist = None
+    ctx = ctx0
+    if world > 1:
+        import torch.distributed as dist
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+        ctx0.close()
+        ctx = capi.Context(local_rank)
+    E, F, NE, K, T = 4096, 14336, 8, 2, 16
+    first, n = local_experts(NE, rank, world)
+    dev = torch.device("cuda", local_rank)
+    gen = torch.Generator(device=dev); gen.manual_seed(3 + rank)
+    rep = torch.Generator(device=dev); rep.manual_seed(99)     # what every rank holds whole
+    wg = synth.device_quant_tensor(capi.Q4_K, n * F, E, gen)
+    wu = synth.device_quant_tensor(capi.Q4_K, n * F, E, gen)
+    wd = synth.device_quant_tensor(capi.Q4_K, n * E, F, gen)
+    wr = torch.randn((NE, E), device=dev, generator=rep) * 0.02
+    x = torch.randn((T, E), device=dev, generator=rep)
+    y = torch.zeros((T, E), device=dev)
+    blk = MoeBlock(ctx, E, F, NE, K, max_tokens=T, ep=(rank, world) if world > 1 else None)
+    blk.set_weights(wr, wg, wu, wd)
+    if world > 1:
+        blk.connect(dist)
+    torch.cuda.synchronize(dev)
+    for _ in range(max(warmup, 3)):   # the third call replays the recorded graph
+        if dist:
+            dist.barrier()
+        blk.forward(x, T, y)
+        ctx.sync()
+    if dist:
+        dist.barrier()
+    ctx.timer_start()
+    for _ in range(steps):
+        blk.forward(x, T, y)
+    ms = ctx.timer_stop() / steps
+    ids = blk.routing(T)[0]
+    mine = int(((ids >= first) & (ids < first + n)).sum())
+    if dist:
+        t = torch.tensor([ms, float(mine)], dtype=torch.float64)
+        parts = [torch.zeros_like(t) for _ in range(world)]
+        dist.all_gather(parts, t)
+        ms = max(float(p[0]) for p in parts)
+        slots = [int(p[1]) for p in parts]
+    else:
+        slots = [mine]
+    status = ctx.status()
+    if rank == 0:
+        slot_bytes = 2 * F * capi.row_bytes(capi.Q4_K, E) + E * capi.row_bytes(capi.Q4_K, F)
+        print(json.dumps({"case": "moe", "n_gpus": world, "tokens": T, "experts": NE, "top_k": K, "ms_per_block": ms,
+                          "tokens_per_s": T / (ms * 1e-3), "slots_per_rank": slots, "bytes_per_slot": slot_bytes,
+                          "busiest_rank_gbs": max(slots) * slot_bytes / ms / 1e6,
+                          "busiest_rank_frac_of_measured_hbm": max(slots) * slot_bytes / ms / 1e6 / peak, "status": status}))
+    if dist:
+        dist.barrier()
+    blk.close()
+    if dist:
+        dist.destroy_process_group()
 
 
 def measure(tp_mode, args, ctx, cfg, config, dist, gloo, rank, local_rank, world, steps, warmup):

@@ -24,7 +24,7 @@ struct MatvecTensor {
                           // tensor is stored with its rows zero-padded to a multiple of 16 bytes.
     // Expert indirection (STREAM_DOT_IDX, fl_idx_w, src/runtime/runtime_internal.h:149-152): the rows used
     // are those of expert *expert_id, expert_rows rows further down per expert (nullptr: none).
-    // *expert_id == kExpertSkip in a one-tensor launch: the kernel returns at once and leaves y as it is (expert
+    // *t[0].expert_id == kExpertSkip: the whole launch returns at once and leaves y as it is (expert
     // parallelism: the expert lives on another GPU). The id is read at kernel entry, so such a launch is not
     // made a programmatic dependent of the kernel that writes the id.
     const uint32_t *expert_id;

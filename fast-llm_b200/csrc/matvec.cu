@@ -351,7 +351,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1)
 matvec_stream_kernel(const MatvecArgs a, const __grid_constant__ TensorMaps maps, const uint32_t total_quads,
                      const int stages, const int use_q4, const int use_q6, const int use_q8) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
-    if (a.n_tensors == 1 && a.t[0].expert_id != nullptr && *a.t[0].expert_id == kExpertSkip) return;   // not this GPU's expert
+    if (a.t[0].expert_id != nullptr && *a.t[0].expert_id == kExpertSkip) return;   // not this GPU's expert (see MatvecTensor)
     const uint32_t nw = blockDim.x >> 5;   // warps of this launch
     const Smem sm = carve(smem_raw, a.cols, use_q4 != 0, use_q6 != 0, stages, nw);   // Q8_0 uses the Q4_K plane layout (use_q4 is set)
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
@@ -694,7 +694,7 @@ __global__ void __launch_bounds__(256) matvec_generic_kernel(const MatvecArgs a,
     griddep_wait();
     const uint32_t lane = threadIdx.x & 31u;
     const uint32_t gw = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, W = (gridDim.x * blockDim.x) >> 5;
-    if (a.n_tensors == 1 && a.t[0].expert_id != nullptr && *a.t[0].expert_id == kExpertSkip) return;   // not this GPU's expert
+    if (a.t[0].expert_id != nullptr && *a.t[0].expert_id == kExpertSkip) return;   // not this GPU's expert (see MatvecTensor)
     for (uint32_t vr = gw; vr < total_rows; vr += W) {
         int ti = 0;
         uint32_t base = 0;

@@ -48,6 +48,24 @@ __global__ void ep_mask_kernel(const uint32_t *__restrict__ ids, const float *__
     mgates[i] = mine ? gates[i] : 0.f;
 }
 
+// Router logits of all tokens in one launch: logits[t][e] = dot(router[e], x[t]); one block per (expert, token).
+__global__ void __launch_bounds__(128) router_logits_kernel(const float *__restrict__ router, const float *__restrict__ x,
+                                                            float *__restrict__ logits, uint32_t n_embd, uint32_t n_expert) {
+    __shared__ float red[4];
+    const uint32_t e = blockIdx.x, t = blockIdx.y;
+    const float4 *w = reinterpret_cast<const float4 *>(router + (size_t)e * n_embd);
+    const float4 *v = reinterpret_cast<const float4 *>(x + (size_t)t * n_embd);
+    float acc = 0.f;
+    for (uint32_t i = threadIdx.x; i < n_embd / 4; i += 128) {
+        const float4 a = w[i], b = v[i];
+        acc = fmaf(a.x, b.x, acc); acc = fmaf(a.y, b.y, acc); acc = fmaf(a.z, b.z, acc); acc = fmaf(a.w, b.w, acc);
+    }
+    acc = warp_sum(acc);
+    if ((threadIdx.x & 31u) == 0) red[threadIdx.x >> 5] = acc;
+    __syncthreads();
+    if (threadIdx.x == 0) logits[(size_t)t * n_expert + e] = (red[0] + red[1]) + (red[2] + red[3]);
+}
+
 #define CKM(call)                                                      \
     do {                                                               \
         cudaError_t e_ = (call);                                       \
@@ -66,6 +84,8 @@ int fl_b200_moe_create(fl_b200_ctx *ctx, const fl_b200_moe_cfg *cfg, uint32_t ra
         return set_err(FL_B200_ERR_ARG, "moe_create: %u experts, top %u, %u ranks", c.n_expert, c.top_k, world);
     if (c.n_embd % 256 || c.n_ff % 256 || c.n_embd < 512 || c.n_ff < 512 || c.max_tokens == 0)
         return set_err(FL_B200_ERR_ARG, "moe_create: n_embd and n_ff must be multiples of 256 (>= 512), max_tokens > 0");
+    if (c.n_embd > 18432 || c.n_ff > 18432)
+        return set_err(FL_B200_ERR_ARG, "moe_create: n_embd / n_ff above 18432 (the streaming matvec's column limit)");
     if (world > 1 && (c.n_embd > kCommMaxVec || c.n_embd % (4 * kCommChunks)))
         return set_err(FL_B200_ERR_ARG, "moe_create: n_embd %u does not fit the exchange buffer", c.n_embd);
     for (int fmt : {c.fmt_gate_up, c.fmt_down})
@@ -181,20 +201,38 @@ static int moe_enqueue(fl_b200_moe *m, const float *x, uint32_t n_tok, float *y)
     const fl_b200_moe_cfg &c = m->c;
     const uint32_t E = c.n_embd, F = c.n_ff, K = c.top_k, NE = c.n_expert;
     const uint64_t stride_gu = (uint64_t)F * row_bytes(c.fmt_gate_up, E), stride_d = (uint64_t)E * row_bytes(c.fmt_down, F);
-    if (int rc = matmul(ctx, FL_B200_F32, m->router, NE, E, x, n_tok, E, m->logits, NE, 0)) return rc;
+    router_logits_kernel<<<dim3(NE, n_tok), 128, 0, s>>>(m->router, x, m->logits, E, NE);
+    CKM(cudaGetLastError());
     for (uint32_t t = 0; t < n_tok; ++t)
         CKM(launch_router_sel(m->logits + (size_t)t * NE, m->ids + (size_t)t * K, m->gates + (size_t)t * K, NE, K, c.norm, c.scale, s));
     ep_mask_kernel<<<(n_tok * K + 127) / 128, 128, 0, s>>>(m->ids, m->gates, m->lids, m->mgates, n_tok * K, m->base, m->n_local);
     CKM(cudaGetLastError());
+    const uint32_t rows_gu = (uint32_t)(stride_gu / row_bytes(c.fmt_gate_up, E)), rows_d = (uint32_t)(stride_d / row_bytes(c.fmt_down, F));
+    const bool down_streams = matvec_is_streaming(c.fmt_down, F) && row_bytes(c.fmt_down, F) % 16 == 0;
     for (uint32_t t = 0; t < n_tok; ++t) {
         const float *xt = x + (size_t)t * E;
         for (uint32_t k = 0; k < K; ++k) {
             const uint32_t *lid = m->lids + (size_t)t * K + k;
-            float *part = m->part + ((size_t)t * K + k) * E;
-            if (int rc = matmul(ctx, c.fmt_gate_up, m->wg, F, E, xt, 1, 0, m->g, 0, 0, 0, lid, stride_gu)) return rc;
-            if (int rc = matmul(ctx, c.fmt_gate_up, m->wu, F, E, xt, 1, 0, m->u, 0, 0, 0, lid, stride_gu)) return rc;
-            CKM(launch_silu_mul(m->g, m->u, m->g, F, s));
-            if (int rc = matmul(ctx, c.fmt_down, m->wd, E, F, m->g, 1, 0, part, 0, 0, 0, lid, stride_d)) return rc;
+            {   // gate and up of the slot's expert in one launch (both tensors carry the same id)
+                MatvecArgs a{};
+                a.n_tensors = 2;
+                a.t[0] = {m->wg, m->g, nullptr, F, c.fmt_gate_up, 0, lid, rows_gu};
+                a.t[1] = {m->wu, m->u, nullptr, F, c.fmt_gate_up, 0, lid, rows_gu};
+                a.x = xt; a.cols = E; a.x_mode = MV_X_PLAIN; a.status = ctx->status;
+                CKM(launch_matvec(a, ctx->sms, s));
+            }
+            {   // down, with silu(g) * u built while the activation is loaded (the streaming kernel's prologue;
+                // rows that are not 16-byte pitched go through the generic kernel after a separate SiLU launch)
+                MatvecArgs a{};
+                a.n_tensors = 1;
+                a.t[0] = {m->wd, m->part + ((size_t)t * K + k) * E, nullptr, E, c.fmt_down, 0, lid, rows_d};
+                a.x = m->g; a.x2 = m->u; a.cols = F; a.x_mode = MV_X_SILU_MUL; a.status = ctx->status;
+                if (!down_streams) {
+                    CKM(launch_silu_mul(m->g, m->u, m->g, F, s));
+                    a.x2 = nullptr; a.x_mode = MV_X_PLAIN;
+                }
+                CKM(launch_matvec(a, ctx->sms, s));
+            }
         }
         float *dst = (m->world > 1 ? m->partial : y) + (size_t)t * E;
         CKM(launch_wmerge(m->part + (size_t)t * K * E, m->mgates + (size_t)t * K, nullptr, nullptr, dst, 1.0f, K, E, K, s));
