@@ -15,6 +15,8 @@
 // every rank ends with identical bits). That sum is the combine half.
 #include "capi_internal.h"
 
+#include <cstdlib>
+
 using namespace flb;
 
 struct fl_b200_moe {
@@ -208,6 +210,8 @@ static int moe_enqueue(fl_b200_moe *m, const float *x, uint32_t n_tok, float *y)
     ep_mask_kernel<<<(n_tok * K + 127) / 128, 128, 0, s>>>(m->ids, m->gates, m->lids, m->mgates, n_tok * K, m->base, m->n_local);
     CKM(cudaGetLastError());
     const uint32_t rows_gu = (uint32_t)(stride_gu / row_bytes(c.fmt_gate_up, E)), rows_d = (uint32_t)(stride_d / row_bytes(c.fmt_down, F));
+    static const int kMoePdl = getenv("FLB_MOE_PDL") ? atoi(getenv("FLB_MOE_PDL")) : 1;
+    bool first_launch = true;
     const bool down_streams = matvec_is_streaming(c.fmt_down, F) && row_bytes(c.fmt_down, F) % 16 == 0;
     for (uint32_t t = 0; t < n_tok; ++t) {
         const float *xt = x + (size_t)t * E;
@@ -219,6 +223,11 @@ static int moe_enqueue(fl_b200_moe *m, const float *x, uint32_t n_tok, float *y)
                 a.t[0] = {m->wg, m->g, nullptr, F, c.fmt_gate_up, 0, lid, rows_gu};
                 a.t[1] = {m->wu, m->u, nullptr, F, c.fmt_gate_up, 0, lid, rows_gu};
                 a.x = xt; a.cols = E; a.x_mode = MV_X_PLAIN; a.status = ctx->status;
+                // Programmatic dependent launch from the second matvec launch on: the first one is an ordinary
+                // dependent of the kernel that wrote the expert ids, and every later launch starts after it did,
+                // so the ids (read at kernel entry, before the dependency wait) are in place for all of them.
+                a.pdl = first_launch ? 0 : kMoePdl;
+                first_launch = false;
                 CKM(launch_matvec(a, ctx->sms, s));
             }
             {   // down, with silu(g) * u built while the activation is loaded (the streaming kernel's prologue;
@@ -227,9 +236,10 @@ static int moe_enqueue(fl_b200_moe *m, const float *x, uint32_t n_tok, float *y)
                 a.n_tensors = 1;
                 a.t[0] = {m->wd, m->part + ((size_t)t * K + k) * E, nullptr, E, c.fmt_down, 0, lid, rows_d};
                 a.x = m->g; a.x2 = m->u; a.cols = F; a.x_mode = MV_X_SILU_MUL; a.status = ctx->status;
+                a.pdl = kMoePdl;
                 if (!down_streams) {
                     CKM(launch_silu_mul(m->g, m->u, m->g, F, s));
-                    a.x2 = nullptr; a.x_mode = MV_X_PLAIN;
+                    a.x2 = nullptr; a.x_mode = MV_X_PLAIN; a.pdl = 0;
                 }
                 CKM(launch_matvec(a, ctx->sms, s));
             }
