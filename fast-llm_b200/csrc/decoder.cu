@@ -97,6 +97,7 @@ struct fl_b200_decoder {
     struct Batch {
         float *x = nullptr, *xn = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *att = nullptr, *g = nullptr, *u = nullptr;
         float *logits = nullptr, *margin = nullptr, *part = nullptr;
+        float *partial = nullptr, *top3 = nullptr;   // tensor parallel: this rank's partial O / down outputs, argmax records
         int32_t *io = nullptr;              // [0..8) tokens, [8..16) positions, [16..24) greedy next tokens
         uint32_t *tickets = nullptr;
         int32_t *h_io = nullptr;            // pinned image of io, then the 8 margins
@@ -369,7 +370,7 @@ void fl_b200_decoder_destroy(fl_b200_decoder *d) {
     }
     cudaFree(d->b.x); cudaFree(d->b.xn); cudaFree(d->b.q); cudaFree(d->b.k); cudaFree(d->b.v); cudaFree(d->b.att);
     cudaFree(d->b.g); cudaFree(d->b.u); cudaFree(d->b.logits); cudaFree(d->b.margin); cudaFree(d->b.part);
-    cudaFree(d->b.io); cudaFree(d->b.tickets);
+    cudaFree(d->b.io); cudaFree(d->b.tickets); cudaFree(d->b.partial); cudaFree(d->b.top3);
     cudaFreeHost(d->b.h_io);
     cudaFreeHost(d->h_pin);
     delete d;
@@ -590,6 +591,10 @@ static int batch_alloc(fl_b200_decoder *d) {
     for (uint32_t m = 1; m <= M; ++m)
         part = std::max(part, attn_part_floats(d->Hq, m, attn_pick_splits(d->Hkv, m, c.max_kv, d->ctx->sms)));
     CK(cudaMalloc(&d->b.part, part * sizeof(float)));
+    if (d->tp_size > 1) {
+        CK(cudaMalloc(&d->b.partial, M * E * 4));
+        CK(cudaMalloc(&d->b.top3, M * 16));
+    }
     CK(cudaMalloc(&d->b.io, 24 * sizeof(int32_t)));
     CK(cudaMalloc(&d->b.tickets, (size_t)d->Hkv * M * sizeof(uint32_t)));
     CK(cudaMemset(d->b.tickets, 0, (size_t)d->Hkv * M * sizeof(uint32_t)));
@@ -604,6 +609,18 @@ static int enqueue_batch(fl_b200_decoder *d, uint32_t m, cudaStream_t s) {
     const uint32_t E = c.n_embd, D = c.head_dim, QD = d->Hq * D, KD = d->Hkv * D, F = d->F, V = d->V;
     const float theta_scale = powf(c.rope_base, -2.0f / (float)D);
     auto &b = d->b;
+    const bool tp = d->tp_size > 1;
+    // x[i] += sum over the ranks of partial[i], token by token, through the decoder's exchange buffers (rank order)
+    auto sum_ranks = [&]() -> int {
+        for (uint32_t i = 0; i < m; ++i) {
+            AllReduceArgs r{};
+            for (uint32_t p = 0; p < d->tp_size; ++p) r.peers[p] = d->peers[p];
+            r.in = b.partial + (size_t)i * E; r.resid = b.x + (size_t)i * E; r.out = b.x + (size_t)i * E; r.n = E;
+            r.rank = d->tp_rank; r.world = d->tp_size; r.st = CommState{d->comm_state}; r.status = ctx->status;
+            CK(launch_allreduce_resid(r, s, false));
+        }
+        return FL_B200_OK;
+    };
     const int32_t *tok = b.io, *pos = b.io + 8;
     int32_t *next = b.io + 16;
     for (uint32_t i = 0; i < m; ++i)
@@ -632,25 +649,43 @@ static int enqueue_batch(fl_b200_decoder *d, uint32_t m, cudaStream_t s) {
             CK(attn_make_maps(a));
             CK(launch_attn_decode(a, s));
         }
-        // x += Wo att (the residual stays in place)
-        if (int rc = matmul(ctx, w[FL_B200_T_WO].fmt, w[FL_B200_T_WO].w, E, QD, b.att, m, QD, b.x, E, 1, w[FL_B200_T_WO].pitch)) return rc;
+        // x += Wo att (the residual stays in place); tensor parallel: the ranks' partial products are summed per token
+        if (!tp) {
+            if (int rc = matmul(ctx, w[FL_B200_T_WO].fmt, w[FL_B200_T_WO].w, E, QD, b.att, m, QD, b.x, E, 1, w[FL_B200_T_WO].pitch)) return rc;
+        } else {
+            if (int rc = matmul(ctx, w[FL_B200_T_WO].fmt, w[FL_B200_T_WO].w, E, QD, b.att, m, QD, b.partial, E, 0, w[FL_B200_T_WO].pitch)) return rc;
+            if (int rc = sum_ranks()) return rc;
+        }
         CK(launch_rmsnorm(b.x, d->ffn_norm[l], b.xn, c.eps, E, s, m, E));
         if (int rc = matmul(ctx, w[FL_B200_T_GATE].fmt, w[FL_B200_T_GATE].w, F, E, b.xn, m, E, b.g, F, 0)) return rc;
         if (int rc = matmul(ctx, w[FL_B200_T_UP].fmt, w[FL_B200_T_UP].w, F, E, b.xn, m, E, b.u, F, 0)) return rc;
         CK(launch_silu_mul(b.g, b.u, b.g, m * F, s));
-        if (int rc = matmul(ctx, w[FL_B200_T_DOWN].fmt, w[FL_B200_T_DOWN].w, E, F, b.g, m, F, b.x, E, 1, w[FL_B200_T_DOWN].pitch)) return rc;
+        if (!tp) {
+            if (int rc = matmul(ctx, w[FL_B200_T_DOWN].fmt, w[FL_B200_T_DOWN].w, E, F, b.g, m, F, b.x, E, 1, w[FL_B200_T_DOWN].pitch)) return rc;
+        } else {
+            if (int rc = matmul(ctx, w[FL_B200_T_DOWN].fmt, w[FL_B200_T_DOWN].w, E, F, b.g, m, F, b.partial, E, 0, w[FL_B200_T_DOWN].pitch)) return rc;
+            if (int rc = sum_ranks()) return rc;
+        }
     }
     CK(launch_rmsnorm(b.x, d->out_norm, b.xn, c.eps, E, s, m, E));
     if (int rc = matmul(ctx, d->output.fmt, d->output.w, V, E, b.xn, m, E, b.logits, V, 0)) return rc;
-    for (uint32_t i = 0; i < m; ++i)
-        CK(launch_argmax(b.logits + (size_t)i * V, V, next + i, b.margin + i, ctx->argmax_scratch, ctx->argmax_ticket, ctx->sms, s));
+    for (uint32_t i = 0; i < m; ++i) {
+        CK(launch_argmax(b.logits + (size_t)i * V, V, next + i, b.margin + i, ctx->argmax_scratch, ctx->argmax_ticket, ctx->sms, s,
+                         false, tp ? b.top3 + 4 * i : nullptr));
+        if (tp) {   // merge the ranks' (best, index, runner-up) of this position: the same token on every rank
+            TopExchangeArgs x{};
+            for (uint32_t p = 0; p < d->tp_size; ++p) x.peers[p] = d->peers[p];
+            x.top3 = b.top3 + 4 * i; x.index_base = d->tp_rank * V; x.out_idx = next + i; x.out_margin = b.margin + i;
+            x.rank = d->tp_rank; x.world = d->tp_size; x.st = CommState{d->comm_state}; x.status = ctx->status;
+            CK(launch_argmax_exchange(x, s, false));
+        }
+    }
     return FL_B200_OK;
 }
 
 int fl_b200_decoder_step_batch(fl_b200_decoder *d, const int32_t *toks, uint32_t m, int32_t *outs, float *margins) {
     if (!d || !toks || !outs) return set_err(FL_B200_ERR_ARG, "decoder_step_batch: null");
     if (!d->finalized) return set_err(FL_B200_ERR_STATE, "decoder_step_batch: finalize first");
-    if (d->tp_size > 1) return set_err(FL_B200_ERR_STATE, "decoder_step_batch: not built for tensor-parallel decoders");
     if (m == 0 || m > FL_B200_MAX_BATCH) return set_err(FL_B200_ERR_ARG, "decoder_step_batch: m %u outside 1..%d", m, FL_B200_MAX_BATCH);
     if ((uint64_t)d->n_past + m > d->c.max_kv) return set_err(FL_B200_ERR_STATE, "decoder_step_batch: kv full (%d + %u > %u)", d->n_past, m, d->c.max_kv);
     for (uint32_t i = 0; i < m; ++i)

@@ -352,7 +352,10 @@ int fl_b200_decoder_verify(fl_b200_decoder *dec, int32_t first_token, const int3
  * reference. One pass over a tensor serves all m tokens where the multi-column
  * kernel takes its shape (Q4_K, rows a multiple of 16, columns of 4096); other
  * tensors are walked once per token. Used for draft verification and for
- * prompt ingestion in chunks of 8. Single-GPU decoders only. */
+ * prompt ingestion in chunks of 8. On a tensor-parallel decoder all ranks make
+ * the same call; the partial O / down outputs and the argmax records are
+ * exchanged per token, and fl_b200_decoder_batch_logits returns this rank's
+ * slice. */
 #define FL_B200_MAX_BATCH 8
 int fl_b200_decoder_step_batch(fl_b200_decoder *dec, const int32_t *toks_host, uint32_t m, int32_t *outs_host,
                                float *margins_host);

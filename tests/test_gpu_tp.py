@@ -13,6 +13,7 @@ pytestmark = pytest.mark.gpu
 SMALL = dict(n_layer=2, n_embd=2048, n_head=16, n_kv_head=4, head_dim=128, n_ff=4096, n_vocab=1000, max_kv=96,
              rope_base=500000.0, eps=1e-5)
 N_PREFILL, STEPS, SEED = 40, 6, 3
+BATCH_TOKS = [11, 500, 7, 999, 123]
 
 
 def _free_port():
@@ -126,6 +127,14 @@ def _worker(rank, world, port, q, model_path=None):
         dec.rewind_to(N_PREFILL)
         dist.barrier()
         res["run"] = [int(t) for t in dec.run(11, STEPS)]
+        # the batch pass (Decoder::step_batch) on the tensor-parallel decoder: 5 tokens in one pass
+        dec.rewind_to(N_PREFILL)
+        dist.barrier()
+        outs, margins = dec.step_batch(BATCH_TOKS)
+        sl = torch.from_numpy(dec.batch_logits(len(BATCH_TOKS) - 1))
+        parts = [torch.zeros_like(sl) for _ in range(world)]
+        dist.all_gather(parts, sl)
+        res["batch"] = (outs, margins, torch.cat(parts).numpy())
         res["status"] = ctx.status()
         dist.barrier()
         if rank == 0:   # the same model on one GPU
@@ -140,6 +149,9 @@ def _worker(rank, world, port, q, model_path=None):
                 ref["tokens"].append(tok)
                 ref["logits"].append(one.logits())
                 ref["margin"].append(one.last_margin())
+            one.rewind_to(N_PREFILL)
+            o1, m1 = one.step_batch(BATCH_TOKS)
+            ref["batch"] = (o1, m1, one.batch_logits(len(BATCH_TOKS) - 1))
             res["ref"] = ref
             one.close()
         dist.barrier()
@@ -179,6 +191,14 @@ def test_two_rank_decoder_matches_single_gpu(tmp_path):
     assert a["run"] == a["tokens"]
     for la, lb in zip(a["logits"], b["logits"]):
         assert np.array_equal(la.view(np.uint32), lb.view(np.uint32))
+    # the batch pass: identical on both ranks, and equal to the single-GPU pass up to the summation order
+    (oa, ma, la), (ob, mb, lb), (o1, m1, l1) = a["batch"], b["batch"], ref["batch"]
+    assert oa == ob and ma == mb and np.array_equal(la.view(np.uint32), lb.view(np.uint32))
+    err = float(np.max(np.abs(la - l1)) / np.sqrt(np.mean(l1.astype(np.float64) ** 2)))
+    assert err < 3e-3, err
+    for i in range(len(BATCH_TOKS)):
+        if oa[i] != o1[i]:
+            assert m1[i] <= 4 * float(np.max(np.abs(la - l1))), (i, oa[i], o1[i], m1[i])
     # against one GPU: only the summation order of O and down changes
     for s in range(STEPS):
         want, got = ref["logits"][s], a["logits"][s]
