@@ -203,7 +203,7 @@ static int check_matvec(int fmt, const void *w, uint32_t rows, uint32_t cols, co
 // capi_internal.h: the decoder's batch pass uses it too).
 int flb::matmul(fl_b200_ctx *c, int fmt, const void *w, uint32_t rows, uint32_t cols, const float *x,
                 uint32_t nx, uint32_t xstride, float *y, uint32_t ystride, int accumulate, uint32_t pitch,
-                const uint32_t *expert_id, uint64_t expert_stride) {
+                const uint32_t *expert_id, uint64_t expert_stride, int pdl) {
     if (int rc = check_matvec(fmt, w, rows, cols, x, y)) return rc;
     if (pitch != 0 && pitch < row_bytes(fmt, cols))
         return set_err(FL_B200_ERR_ARG, "matvec: row pitch %u smaller than the packed row (%llu bytes)", pitch,
@@ -245,6 +245,7 @@ int flb::matmul(fl_b200_ctx *c, int fmt, const void *w, uint32_t rows, uint32_t 
         a.x_mode = MV_X_PLAIN;
         a.accumulate = accumulate;
         a.status = c->status;
+        a.pdl = pdl;
         if (int rc = cuda_err(launch_matvec(a, c->sms, c->stream), "matvec launch")) return rc;
     }
     return FL_B200_OK;

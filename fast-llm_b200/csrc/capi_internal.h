@@ -25,10 +25,11 @@ namespace flb {
 int set_err(int code, const char *fmt, ...);
 int cuda_err(cudaError_t e, const char *what);
 // y[p * ystride + r] (+)= dot(W[r], x + p * xstride), p < nx, enqueued on the context's stream: up to 8
-// columns per pass over the weights where the multi-column kernel takes the shape, one column per pass otherwise.
+// columns per pass over the weights where the multi-column kernel takes the shape, one column per pass otherwise
+// (pdl: those one-column launches are programmatic dependents of the launch before them).
 int matmul(fl_b200_ctx *c, int fmt, const void *w, uint32_t rows, uint32_t cols, const float *x, uint32_t nx,
            uint32_t xstride, float *y, uint32_t ystride, int accumulate, uint32_t pitch = 0,
-           const uint32_t *expert_id = nullptr, uint64_t expert_stride = 0);
+           const uint32_t *expert_id = nullptr, uint64_t expert_stride = 0, int pdl = 0);
 // Hands device memory to the decoder, which frees it when it is destroyed.
 void decoder_adopt(fl_b200_decoder *d, void *dev);
 } // namespace flb

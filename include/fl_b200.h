@@ -351,7 +351,8 @@ int fl_b200_decoder_verify(fl_b200_decoder *dec, int32_t first_token, const int3
  * (fl_b200_decoder_set_n_past) commits or discards the rows as in the
  * reference. One pass over a tensor serves all m tokens where the multi-column
  * kernel takes its shape (Q4_K, rows a multiple of 16, columns of 4096); other
- * tensors are walked once per token. Used for draft verification and for
+ * tensors are walked once per token; passes of fewer than 4 tokens run as
+ * teacher-forced single steps on the device. Used for draft verification and for
  * prompt ingestion in chunks of 8. On a tensor-parallel decoder all ranks make
  * the same call; the partial O / down outputs and the argmax records are
  * exchanged per token, and fl_b200_decoder_batch_logits returns this rank's
