@@ -256,8 +256,10 @@ def kernel_case(case, steps, warmup):
     more than L2 (126 MB) of distinct weights or keys."""
     import torch
     from fast_llm_b200 import capi, synth
-    ctx = capi.Context(0)
     peak, _ = measured_peaks()
+    if case == "moe":
+        return moe_case(steps, warmup, peak)
+    ctx = capi.Context(0)
     gen = torch.Generator(device="cuda")
     gen.manual_seed(1)
     if case == "matmul-nx8":
@@ -280,8 +282,6 @@ def kernel_case(case, steps, warmup):
                           "us_per_pass": us, "weight_bytes": nbytes, "achieved_gbs": nbytes / us / 1e3,
                           "frac_of_measured_hbm": nbytes / us / 1e3 / peak, "status": ctx.status()}))
         return
-    if case == "moe":
-        return moe_case(ctx, steps, warmup, peak)
     # attn-long: the long-context configuration (f16 K/V ~ N(0, 1)/sqrt(128), 32 query / 8 KV heads of 128)
     out = []
     for kv_len, batch in ((32768, 1), (32768, 4), (65536, 1), (65536, 4), (131072, 1), (131072, 4), (32768, 16), (131072, 16)):
@@ -309,7 +309,7 @@ def kernel_case(case, steps, warmup):
     print(json.dumps({"case": case, "kernel": "attn_decode_kernel", "peak_gbs": peak, "points": out, "status": ctx.status()}))
 
 
-def moe_case(ctx0, steps, warmup, peak):
+def moe_case(steps, warmup, peak):
     """The MoE configuration's feed-forward block: 8 experts of gate / up 14336 x 4096 and down 4096 x 14336
     (Q4_K), f32 router ~ N(0, 0.02), 16 tokens, top-2 with renormalised weights. One process per GPU under
     torchrun: expert parallel (8 / N experts per rank), time = max over ranks."""
@@ -319,13 +319,11 @@ def moe_case(ctx0, steps, warmup, peak):
     rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     dist = None
-    ctx = ctx0
+    torch.cuda.set_device(local_rank)
     if world > 1:
         import torch.distributed as dist
-        torch.cuda.set_device(local_rank)
         dist.init_process_group("gloo", rank=rank, world_size=world)
-        ctx0.close()
-        ctx = capi.Context(local_rank)
+    ctx = capi.Context(local_rank)
     E, F, NE, K, T = 4096, 14336, 8, 2, 16
     first, n = local_experts(NE, rank, world)
     dev = torch.device("cuda", local_rank)
