@@ -407,13 +407,22 @@ def measure(tp_mode, args, ctx, cfg, config, dist, gloo, rank, local_rank, world
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
+    def run_steps(first, n):
+        """n greedy steps on the device, in calls of at most 4096 (the decoder's token history)."""
+        out, t = [], first
+        while n > 0:
+            k = min(n, 4096)
+            out += [int(x) for x in dec.run(t, k)]
+            t, n = out[-1], n - k
+        return out
+
     # ---- value: device-resident feedback loop ----
     dec.rewind_to(N_PREFILL)
-    dec.run(1, warmup)
+    run_steps(1, warmup)
     barrier()
     sampler.mark()
     ctx.timer_start()
-    toks = dec.run(1, steps)
+    toks = run_steps(1, steps)
     ms_dev = ctx.timer_stop()
     barrier()
     ms_dev = max_over_ranks(ms_dev)
