@@ -135,6 +135,9 @@ def _worker(rank, world, port, q, model_path=None):
         parts = [torch.zeros_like(sl) for _ in range(world)]
         dist.all_gather(parts, sl)
         res["batch"] = (outs, margins, torch.cat(parts).numpy())
+        dec.rewind_to(N_PREFILL)                             # a short pass runs as teacher-forced single steps
+        dist.barrier()
+        res["batch2"] = dec.step_batch(BATCH_TOKS[:2])
         res["status"] = ctx.status()
         dist.barrier()
         if rank == 0:   # the same model on one GPU
@@ -199,6 +202,10 @@ def test_two_rank_decoder_matches_single_gpu(tmp_path):
     for i in range(len(BATCH_TOKS)):
         if oa[i] != o1[i]:
             assert m1[i] <= 4 * float(np.max(np.abs(la - l1))), (i, oa[i], o1[i], m1[i])
+    assert a["batch2"] == b["batch2"]
+    for i in range(2):   # the same two positions through the other path: same token unless the margin is tiny
+        if a["batch2"][0][i] != oa[i]:
+            assert ma[i] <= 1e-3, (i, a["batch2"][0][i], oa[i], ma[i])
     # against one GPU: only the summation order of O and down changes
     for s in range(STEPS):
         want, got = ref["logits"][s], a["logits"][s]
