@@ -56,6 +56,8 @@ struct MatvecArgs {
                           // before the dependency wait (for launches whose CTAs only become resident when the previous
                           // kernel's CTAs leave, so that nothing is gained by requesting early)
     unsigned long long *trace;   // optional 4-entry timeline record of this launch (diagnostics)
+    int expert_ids_ready;        // 1: the expert ids were complete before the previous kernel started, so the first
+                                 // weight stages are requested before the dependency wait, as for a plain tensor
     // Tensor parallel: the activation is the sum of the ranks' partial vectors that an exchange launch
     // (launch_allreduce_push) is delivering into this rank's exchange buffer, plus a residual:
     // x = xr_resid + sum_r recv[r]. The kernel waits (bounded) for the ranks' flags of the epoch the

@@ -361,6 +361,7 @@ matvec_stream_kernel(const MatvecArgs a, const __grid_constant__ TensorMaps maps
 
     bool indirect = false;
     for (int i = 0; i < a.n_tensors; ++i) indirect = indirect || a.t[i].expert_id != nullptr;
+    indirect = indirect && !a.expert_ids_ready;   // ids written before the previous kernel started are read like constants
     uint64_t *bars = sm.bars + warp * stages;
     const uint32_t ring = smem_u32(sm.ring) + warp * stages * stage_bytes;   // shared address
     if (lane == 0)

@@ -227,6 +227,7 @@ static int moe_enqueue(fl_b200_moe *m, const float *x, uint32_t n_tok, float *y)
                 // dependent of the kernel that wrote the expert ids, and every later launch starts after it did,
                 // so the ids (read at kernel entry, before the dependency wait) are in place for all of them.
                 a.pdl = first_launch ? 0 : kMoePdl;
+                a.expert_ids_ready = first_launch ? 0 : 1;
                 first_launch = false;
                 CKM(launch_matvec(a, ctx->sms, s));
             }
@@ -237,6 +238,7 @@ static int moe_enqueue(fl_b200_moe *m, const float *x, uint32_t n_tok, float *y)
                 a.t[0] = {m->wd, m->part + ((size_t)t * K + k) * E, nullptr, E, c.fmt_down, 0, lid, rows_d};
                 a.x = m->g; a.x2 = m->u; a.cols = F; a.x_mode = MV_X_SILU_MUL; a.status = ctx->status;
                 a.pdl = kMoePdl;
+                a.expert_ids_ready = 1;
                 if (!down_streams) {
                     CKM(launch_silu_mul(m->g, m->u, m->g, F, s));
                     a.x2 = nullptr; a.x_mode = MV_X_PLAIN; a.pdl = 0;
