@@ -346,10 +346,17 @@ __device__ __forceinline__ QuadRef locate_quad(const MatvecArgs &a, uint32_t qua
 
 // XR: the activation is the sum of the ranks' partial vectors arriving in the exchange buffer (tensor
 // parallel); a separate instantiation so that the single-GPU kernel does not pay for it in registers.
-template <bool XR>
+// Q8: a launch of Q8_0 tensors (never mixed with the K-quants) has an instantiation of its own. All K-quant
+// launches of a decode step share ONE kernel body on purpose: the step alternates between launch shapes every
+// few microseconds, and instruction fetch is a visible part of these short kernels. Measured on the 8B-shape
+// step: taking the Q8_0 unpack code out of the shared body gave +2 % (452 -> 461 tokens/s), while one
+// instantiation per format combination, each smaller still, lost 13 % (395 tokens/s) because consecutive
+// launches then no longer ran the same code.
+template <bool XR, bool Q8>
 __global__ void __launch_bounds__(kMaxThreads, 1)
 matvec_stream_kernel(const MatvecArgs a, const __grid_constant__ TensorMaps maps, const uint32_t total_quads,
-                     const int stages, const int use_q4, const int use_q6, const int use_q8) {
+                     const int stages, const int use_q4, const int use_q6) {
+    constexpr bool use_q8 = Q8;   // use_q4 is set for Q8_0 launches: they use the Q4_K plane layout
     extern __shared__ __align__(128) uint8_t smem_raw[];
     if (a.t[0].expert_id != nullptr && *a.t[0].expert_id == kExpertSkip) return;   // not this GPU's expert (see MatvecTensor)
     const uint32_t nw = blockDim.x >> 5;   // warps of this launch
@@ -585,7 +592,7 @@ matvec_stream_kernel(const MatvecArgs a, const __grid_constant__ TensorMaps maps
         if (seg == 0) cur = locate_quad(a, quad);
         const float xs = sm.xs[seg * 8 + sbi];
         const uint32_t st = ring + slot * stage_bytes;
-        if (use_q8) {
+        if constexpr (use_q8) {
             const XSlots xq = load_slots(q4_addr, seg, lane);
             if (!mbar_wait_bounded(&bars[slot], parity, a.status)) return;
             const uint32_t base = st + (lane >> 4) * (kRowsPerStage * kHalf8) + (lane & 15u) * 68u;
@@ -752,9 +759,13 @@ cudaError_t matvec_init(void) {
         if (qres != cudaDriverEntryPointSuccess || !fn) return cudaErrorNotSupported;
         g_encode = (EncodeTiledFn)fn;
     }
-    cudaError_t e = cudaFuncSetAttribute(matvec_stream_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024 - 1024);
-    if (e != cudaSuccess) return e;
-    return cudaFuncSetAttribute(matvec_stream_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024 - 1024);
+    const void *kernels[] = {(const void *)matvec_stream_kernel<false, false>, (const void *)matvec_stream_kernel<true, false>,
+                             (const void *)matvec_stream_kernel<false, true>};
+    for (const void *k : kernels) {
+        const cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024 - 1024);
+        if (e != cudaSuccess) return e;
+    }
+    return cudaSuccess;
 }
 
 // The packed tensor as [rows][row_bytes / 8] 8-byte elements, box = 4 rows x one segment.
@@ -831,11 +842,15 @@ cudaError_t launch_matvec(const MatvecArgs &a, int sms, cudaStream_t stream) {
                 const cudaError_t e = encode_map(&maps.m[i], a.t[i], a.cols, a.swiglu ? 2 : kRowsPerStage);
                 if (e != cudaSuccess) return e;
             }
+            if (a.xr_buf && q8) return cudaErrorInvalidValue;   // the exchange prologue is not instantiated for Q8_0
+            if (q8)
+                return launch_kernel(matvec_stream_kernel<false, true>, dim3(grid), dim3(warps * 32), smem, stream, a.pdl != 0, a,
+                                     maps, total_quads, stages, 1, 0);
             if (a.xr_buf)
-                return launch_kernel(matvec_stream_kernel<true>, dim3(grid), dim3(warps * 32), smem, stream, a.pdl != 0, a, maps,
-                                     total_quads, stages, (q4 || q8) ? 1 : 0, q6 ? 1 : 0, q8 ? 1 : 0);
-            return launch_kernel(matvec_stream_kernel<false>, dim3(grid), dim3(warps * 32), smem, stream, a.pdl != 0, a, maps,
-                                 total_quads, stages, (q4 || q8) ? 1 : 0, q6 ? 1 : 0, q8 ? 1 : 0);
+                return launch_kernel(matvec_stream_kernel<true, false>, dim3(grid), dim3(warps * 32), smem, stream, a.pdl != 0, a,
+                                     maps, total_quads, stages, q4 ? 1 : 0, q6 ? 1 : 0);
+            return launch_kernel(matvec_stream_kernel<false, false>, dim3(grid), dim3(warps * 32), smem, stream, a.pdl != 0, a,
+                                 maps, total_quads, stages, q4 ? 1 : 0, q6 ? 1 : 0);
         }
     }
     if (a.x_mode != MV_X_PLAIN || a.xr_buf) return cudaErrorInvalidValue;   // prologues exist only in the streaming kernel
