@@ -602,16 +602,28 @@ matvec_stream_kernel(const MatvecArgs a, const __grid_constant__ TensorMaps maps
             const XSlots xq = load_slots(q4_addr, seg, lane);
             const float2 sx = reinterpret_cast<const float2 *>(sm.s4)[seg * 32 + lane];
             if (!mbar_wait_bounded(&bars[slot], parity, a.status)) return;
-#pragma unroll
-            for (int r = 0; r < kRowsPerStage; ++r)
-                acc[r] = fmaf(xs, q4k_quarter(st + r * kSeg4 + sbi * 144, qt, xq, sx), acc[r]);
+            // Two rows per trip of a rolled loop, not four unrolled: the smaller body measured +0.9 % on the whole
+            // step (instruction fetch). The accumulator pairs swap places each trip so that they stay in registers.
+#pragma unroll 1
+            for (int h = 0; h < 2; ++h) {
+                const uint32_t rs = st + (2 * h) * kSeg4 + sbi * 144;
+                acc[0] = fmaf(xs, q4k_quarter(rs, qt, xq, sx), acc[0]);
+                acc[1] = fmaf(xs, q4k_quarter(rs + kSeg4, qt, xq, sx), acc[1]);
+                const float t0 = acc[0], t1 = acc[1];
+                acc[0] = acc[2]; acc[1] = acc[3]; acc[2] = t0; acc[3] = t1;
+            }
         } else {
             const XSlots xq = load_slots(q6_addr, seg, lane);
             const float4 sx = reinterpret_cast<const float4 *>(sm.s6)[seg * 32 + lane];
             if (!mbar_wait_bounded(&bars[slot], parity, a.status)) return;
-#pragma unroll
-            for (int r = 0; r < kRowsPerStage; ++r)
-                acc[r] = fmaf(xs, q6k_quarter(st + r * kSeg6, sbi, qt, xq, sx), acc[r]);
+#pragma unroll 1
+            for (int h = 0; h < 2; ++h) {
+                const uint32_t rs = st + (2 * h) * kSeg6;
+                acc[0] = fmaf(xs, q6k_quarter(rs, sbi, qt, xq, sx), acc[0]);
+                acc[1] = fmaf(xs, q6k_quarter(rs + kSeg6, sbi, qt, xq, sx), acc[1]);
+                const float t0 = acc[0], t1 = acc[1];
+                acc[0] = acc[2]; acc[1] = acc[3]; acc[2] = t0; acc[3] = t1;
+            }
         }
         __syncwarp();
         if (lane == 0 && p_i < my_stages) {
