@@ -56,10 +56,10 @@ class ClockSampler:
     def __init__(self, device):
         self.device = device
         self.proc = None
-        self.path = os.path.join(ROOT, "gpurun_out", "clocks_rank%d.csv" % device)
+        import tempfile
+        self.path = os.path.join(tempfile.gettempdir(), "fl_b200_bench_clocks_%d_rank%d.csv" % (os.getpid(), device))
 
     def start(self):
-        os.makedirs(os.path.dirname(self.path), exist_ok=True)
         try:
             self.out = open(self.path, "w")
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.device), "--query-gpu=" + self.QUERY,
@@ -120,7 +120,8 @@ def cpu_reference_arm(steps, warmup, threads=None):
     kind = "reference" if pyoracle.Oracle.available("reference") else "port"
     orc = pyoracle.Oracle(kind)
     cores = threads or os.cpu_count() or 1
-    os.environ.setdefault("OMP_NUM_THREADS", str(cores))
+    # set, not setdefault: torchrun exports OMP_NUM_THREADS=1 to its ranks, which would time this arm on one thread
+    os.environ["OMP_NUM_THREADS"] = str(cores)
     full = dict(synth.LLAMA3_8B)
 
     def build(n_layer):

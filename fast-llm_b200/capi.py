@@ -24,7 +24,7 @@ G_TOK_EMBD, G_OUTPUT = 0, 1
 # library exports each of them).
 SYMBOLS = [
     "fl_b200_abi_version", "fl_b200_last_error", "fl_b200_create", "fl_b200_destroy", "fl_b200_sync",
-    "fl_b200_device_status", "fl_b200_sm_count", "fl_b200_stream", "fl_b200_malloc", "fl_b200_free",
+    "fl_b200_device_status", "fl_b200_sm_count", "fl_b200_set_wait_limit", "fl_b200_stream", "fl_b200_malloc", "fl_b200_free",
     "fl_b200_upload", "fl_b200_download", "fl_b200_memset", "fl_b200_ipc_export", "fl_b200_ipc_open", "fl_b200_ipc_close", "fl_b200_timer_start", "fl_b200_timer_stop",
     "fl_b200_dequant", "fl_b200_matvec", "fl_b200_matvec_assign", "fl_b200_matvec_expert", "fl_b200_matvec_pitched", "fl_b200_matvec_host",
     "fl_b200_attn_decode", "fl_b200_attn_decode_lse", "fl_b200_seqpar_create", "fl_b200_seqpar_destroy",
@@ -159,6 +159,10 @@ class Context:
 
     def sm_count(self):
         return self.lib.fl_b200_sm_count(self._h)
+
+    def set_wait_limit(self, nanoseconds):
+        """Limit of the exchange kernels' waits for another rank (0 = one second)."""
+        _ck(self.lib.fl_b200_set_wait_limit(self._h, C.c_uint64(nanoseconds)))
 
     def stream(self):
         return self.lib.fl_b200_stream(self._h)

@@ -419,15 +419,21 @@ cudaError_t launch_attn_decode_static(AttnArgs a, int device, cudaStream_t strea
     const size_t records = (size_t)a.n_q_head * a.batch * a.n_splits;
     if (records_needed) *records_needed = records;
     if (device < 0 || device >= kMaxDevices) return cudaErrorInvalidDevice;
+    if (a.n_splits == 0 || a.n_splits > 64) return cudaErrorInvalidValue;   // the combine gives each lane two splits
     if (records > kStaticMaxRecords || (uint64_t)a.n_kv_head * a.batch > kStaticMaxTickets)
         return cudaErrorMemoryAllocation;   // the caller turns this into its size message
-    if (!g_static_ptr[device]) {
-        float *ptr = nullptr;
+    // cudaGetSymbolAddress answers for the device that is current on this thread: the address is only
+    // cached under `device` when that is the current one.
+    int cur = -1;
+    cudaError_t e0 = cudaGetDevice(&cur);
+    if (e0 != cudaSuccess) return e0;
+    if (cur != device) return cudaErrorInvalidDevice;
+    float *ptr = __atomic_load_n(&g_static_ptr[device], __ATOMIC_ACQUIRE);
+    if (!ptr) {
         const cudaError_t e = cudaGetSymbolAddress((void **)&ptr, g_attn_static_scratch);
         if (e != cudaSuccess) return e;
-        g_static_ptr[device] = ptr;
+        __atomic_store_n(&g_static_ptr[device], ptr, __ATOMIC_RELEASE);   // every thread stores the same value
     }
-    float *ptr = g_static_ptr[device];
     a.part = ptr;
     a.tickets = reinterpret_cast<uint32_t *>(ptr + kStaticPartFloats);
     cudaError_t e = cudaMemsetAsync(a.tickets, 0, (size_t)a.n_kv_head * a.batch * sizeof(uint32_t), stream);

@@ -37,6 +37,17 @@ using namespace flb;
         if (e_ != cudaSuccess) return cuda_err(e_, #call);             \
     } while (0)
 
+int flb::grow_attn_part(fl_b200_ctx *c, size_t bytes) {
+    if (c->attn_part_cap >= bytes) return FL_B200_OK;
+    CK(cudaSetDevice(c->device));
+    float *p = nullptr;
+    CK(cudaMalloc(&p, bytes));
+    if (c->attn_part) c->retired.push_back(c->attn_part);   // a captured plan may still write through it
+    c->attn_part = p;
+    c->attn_part_cap = bytes;
+    return FL_B200_OK;
+}
+
 extern "C" {
 
 int fl_b200_abi_version(void) { return FL_B200_ABI_VERSION; }
@@ -72,6 +83,7 @@ int fl_b200_create(int device, fl_b200_ctx **out) {
     CK(cudaMalloc(&c->argmax_scratch, (size_t)3 * 1024 * sizeof(float)));
     CK(cudaMalloc(&c->small, 64));
     CK(matvec_init());
+    CK(matvec_tc_init());
     CK(attn_init());
     *out = c;
     return FL_B200_OK;
@@ -82,6 +94,7 @@ void fl_b200_destroy(fl_b200_ctx *c) {
     cudaSetDevice(c->device);
     cudaStreamSynchronize(c->stream);
     cudaFree(c->attn_part);
+    for (void *p : c->retired) cudaFree(p);
     cudaFree(c->attn_tickets);
     cudaFree(c->argmax_scratch);
     cudaFree(c->small);
@@ -104,6 +117,12 @@ int fl_b200_device_status(fl_b200_ctx *c, uint32_t *out) {
     CK(cudaStreamSynchronize(c->stream));
     if (v != 0) CK(cudaMemsetAsync(c->status, 0, 4, c->stream));
     if (out) *out = v;
+    return FL_B200_OK;
+}
+
+int fl_b200_set_wait_limit(fl_b200_ctx *c, uint64_t nanoseconds) {
+    if (!c) return set_err(FL_B200_ERR_ARG, "set_wait_limit: null context");
+    c->wait_limit_ns = nanoseconds;
     return FL_B200_OK;
 }
 
@@ -332,14 +351,7 @@ static int attn_impl(fl_b200_ctx *c, const float *q, const uint16_t *k, const ui
     a.scale = scale;
     a.status = c->status;
     const size_t need = attn_part_floats(n_q, batch, a.n_splits) * sizeof(float);
-    if (c->attn_part_cap < need) {
-        CK(cudaStreamSynchronize(c->stream));
-        cudaFree(c->attn_part);
-        c->attn_part = nullptr;
-        c->attn_part_cap = 0;
-        CK(cudaMalloc(&c->attn_part, need));
-        c->attn_part_cap = need;
-    }
+    if (int rc = grow_attn_part(c, need)) return rc;
     a.part = c->attn_part;
     a.tickets = c->attn_tickets;
     if (int rc = cuda_err(attn_make_maps(a), "attn tensor maps")) return rc;
@@ -368,6 +380,9 @@ int fl_b200_attn_decode_static(fl_b200_ctx *c, const float *q, const uint16_t *k
         return set_err(FL_B200_ERR_ARG, "attn_decode_static: kv_len %u outside 1..kv_stride %u", kv_len, kv_stride);
     if (((uintptr_t)k & 15u) || ((uintptr_t)v & 15u) || ((uintptr_t)q & 15u))
         return set_err(FL_B200_ERR_ARG, "attn_decode_static: q, k, v must be 16-byte aligned");
+    // The scratch array's address is looked up for the CURRENT device: make the context's device current
+    // first (a process that holds contexts on several devices may call with another one current).
+    CK(cudaSetDevice(c->device));
     AttnArgs a{};
     a.q = q;
     a.k = (const __half *)k;
@@ -471,7 +486,7 @@ int fl_b200_seqpar_combine(fl_b200_seqpar *h, const float *out_local, const floa
     for (uint32_t p = 0; p < h->world; ++p) a.peers[p] = h->peers[p];
     a.out_local = out_local; a.lse_local = reinterpret_cast<const float2 *>(lse_local); a.out = out;
     a.n = n; a.max_records = h->max_records; a.rank = h->rank; a.world = h->world;
-    a.epoch = h->epoch; a.status = h->ctx->status;
+    a.epoch = h->epoch; a.status = h->ctx->status; a.wait_ns = h->ctx->wait_limit_ns;
     return cuda_err(launch_lse_combine(a, h->ctx->stream), "lse combine launch");
 }
 
@@ -704,13 +719,7 @@ int fl_b200_plan_create(fl_b200_ctx *c, const fl_b200_task *tasks, uint32_t n, f
                 return set_err(FL_B200_ERR_ARG, "plan_create: task %u: attention shape %u/%u x %u is not built", i, p.n_q_head, p.n_kv_head, p.head_dim);
             const uint32_t splits = attn_pick_splits(p.n_kv_head, 1, p.kv_stride, c->sms);
             const size_t need = attn_part_floats(p.n_q_head, 1, splits) * sizeof(float);
-            if (c->attn_part_cap < need) {
-                cudaFree(c->attn_part);
-                c->attn_part = nullptr;
-                c->attn_part_cap = 0;
-                CK(cudaMalloc(&c->attn_part, need));
-                c->attn_part_cap = need;
-            }
+            if (int rc = grow_attn_part(c, need)) return rc;
         }
     // --- launch list: by dependency level; within a level, STREAM_DOT tiles of one tensor merge ---
     std::vector<uint32_t> by_level(order);

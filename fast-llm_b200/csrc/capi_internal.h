@@ -4,6 +4,8 @@
 #include "common.cuh"
 #include "kernels.h"
 
+#include <vector>
+
 struct fl_b200_ctx {
     int device = 0;
     int sms = 0;
@@ -15,14 +17,20 @@ struct fl_b200_ctx {
     uint32_t attn_tickets_cap = 0;
     float *attn_part = nullptr;          // split-KV partials (scratch, grown on demand)
     size_t attn_part_cap = 0;
+    // Scratch buffers that were outgrown. A recorded plan (fl_b200_plan) keeps the address it was
+    // captured with, so an outgrown buffer stays allocated until the context goes.
+    std::vector<void *> retired;
     float *argmax_scratch = nullptr;
     void *small = nullptr;
+    uint64_t wait_limit_ns = 0;          // limit of the exchange kernels' waits for other ranks (0 = one second)
     void *stage = nullptr;               // device staging for the *_host entry points
     size_t stage_cap = 0;
 };
 
 namespace flb {
 int set_err(int code, const char *fmt, ...);
+// Makes c->attn_part at least `bytes` large (never frees a buffer a recorded plan may still use).
+int grow_attn_part(fl_b200_ctx *c, size_t bytes);
 int cuda_err(cudaError_t e, const char *what);
 // y[p * ystride + r] (+)= dot(W[r], x + p * xstride), p < nx, enqueued on the context's stream: up to 8
 // columns per pass over the weights where the multi-column kernel takes the shape, one column per pass otherwise

@@ -78,7 +78,7 @@ __global__ void __launch_bounds__(1024) allreduce_resid_kernel(const AllReduceAr
     __syncthreads();
     if (tid < a.world) {
         st_release_sys(flag_of(a.peers[tid], slot, a.rank, chunk), e);
-        if (!wait_flag(flag_of(a.peers[a.rank], slot, tid, chunk), e, a.status)) ok_s = 0u;
+        if (!wait_flag(flag_of(a.peers[a.rank], slot, tid, chunk), e, a.status, a.wait_ns)) ok_s = 0u;
     }
     __syncthreads();
     if (ok_s) {
@@ -135,7 +135,7 @@ __global__ void __launch_bounds__(32) argmax_exchange_kernel(const TopExchangeAr
         rec.w = 0.f;
         *reinterpret_cast<float4 *>(top_of(a.peers[tid], slot, a.rank)) = rec;
         st_release_sys(tflag_of(a.peers[tid], slot, a.rank), e);
-        ok = wait_flag(tflag_of(a.peers[a.rank], slot, tid), e, a.status);
+        ok = wait_flag(tflag_of(a.peers[a.rank], slot, tid), e, a.status, a.wait_ns);
     }
     ok = __all_sync(0xffffffffu, ok);
     if (ok && tid == 0) {
@@ -181,7 +181,7 @@ __global__ void __launch_bounds__(128) lse_combine_kernel(const LseCombineArgs a
     __syncthreads();
     if (tid < a.world) {
         st_release_sys(flag_of2(a.peers[tid], a.rank), e);
-        if (!wait_flag(flag_of2(a.peers[a.rank], tid), e, a.status)) ok_s = 0u;
+        if (!wait_flag(flag_of2(a.peers[a.rank], tid), e, a.status, a.wait_ns)) ok_s = 0u;
     }
     __syncthreads();
     if (!ok_s) return;

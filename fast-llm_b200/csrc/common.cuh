@@ -152,14 +152,17 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p) {
     asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
 }
-// Spins until *flag == want; false (and ST_PEER_TIMEOUT in the status word) after about a second.
-__device__ __forceinline__ bool wait_flag(const uint32_t *flag, uint32_t want, uint32_t *status) {
+// Spins until *flag == want; false (and ST_PEER_TIMEOUT in the status word) after limit_ns of
+// %globaltimer (0 = the default of one second). The caller returns without touching its output.
+constexpr uint64_t kDefaultWaitNs = 1000000000ull;
+__device__ __forceinline__ bool wait_flag(const uint32_t *flag, uint32_t want, uint32_t *status, uint64_t limit_ns = 0) {
     if (ld_acquire_sys(flag) == want) return true;
+    if (limit_ns == 0) limit_ns = kDefaultWaitNs;
     const uint64_t t0 = globaltimer_ns();
     for (;;) {
         for (int i = 0; i < 32; ++i)
             if (ld_acquire_sys(flag) == want) return true;
-        if (globaltimer_ns() - t0 > 1000000000ull) {
+        if (globaltimer_ns() - t0 > limit_ns) {
             atomicCAS(status, ST_OK, ST_PEER_TIMEOUT);
             return false;
         }

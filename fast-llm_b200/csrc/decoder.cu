@@ -159,7 +159,7 @@ static int enqueue_step(fl_b200_decoder *d, cudaStream_t s, uint32_t *n_launch, 
         AllReduceArgs r{};
         for (uint32_t p = 0; p < d->tp_size; ++p) r.peers[p] = d->peers[p];
         r.in = d->partial; r.resid = resid; r.out = out; r.n = E; r.rank = d->tp_rank; r.world = d->tp_size;
-        r.st = cst; r.status = ctx->status;
+        r.st = cst; r.status = ctx->status; r.wait_ns = ctx->wait_limit_ns;
         if (!fused) return cuda_err(launch_allreduce_resid(r, s, kPdl != 0), "all-reduce launch");
         pend.resid = resid; pend.out = out; pend.on = true;
         return cuda_err(launch_allreduce_push(r, s, kPdl != 0), "all-reduce push launch");
@@ -253,7 +253,7 @@ static int enqueue_step(fl_b200_decoder *d, cudaStream_t s, uint32_t *n_launch, 
         TopExchangeArgs x{};
         for (uint32_t p = 0; p < d->tp_size; ++p) x.peers[p] = d->peers[p];
         x.top3 = d->top3; x.index_base = d->tp_rank * d->V; x.out_idx = d->d_next; x.out_margin = d->d_margin;
-        x.rank = d->tp_rank; x.world = d->tp_size; x.st = cst; x.status = ctx->status;
+        x.rank = d->tp_rank; x.world = d->tp_size; x.st = cst; x.status = ctx->status; x.wait_ns = ctx->wait_limit_ns;
         CK(launch_argmax_exchange(x, s, kPdl != 0)); ++n;
     }
     if (mask == K_ALL) {   // state only advances in the real step
@@ -501,7 +501,14 @@ int fl_b200_decoder_n_past(fl_b200_decoder *d, int32_t *out) {
 static int check_dev_status(fl_b200_decoder *d) {
     uint32_t st = 0;
     if (int rc = fl_b200_device_status(d->ctx, &st)) return rc;
-    if (st != 0) return set_err(FL_B200_ERR_DEVICE, "decoder: a kernel reported status %u (bounded wait gave up)", st);
+    if (st != 0) {
+        // a kernel that gave up may have left its arrival counters non-zero: clear them, so that a caller who
+        // carries on does not get a combine that fires with splits missing
+        cudaMemsetAsync(d->tickets, 0, 256 * sizeof(uint32_t), d->ctx->stream);
+        if (d->b.tickets) cudaMemsetAsync(d->b.tickets, 0, (size_t)d->Hkv * FL_B200_MAX_BATCH * sizeof(uint32_t), d->ctx->stream);
+        cudaMemsetAsync(d->ctx->attn_tickets, 0, d->ctx->attn_tickets_cap * sizeof(uint32_t), d->ctx->stream);
+        return set_err(FL_B200_ERR_DEVICE, "decoder: a kernel reported status %u (bounded wait gave up)", st);
+    }
     return FL_B200_OK;
 }
 
@@ -624,7 +631,7 @@ static int enqueue_batch(fl_b200_decoder *d, uint32_t m, cudaStream_t s) {
             AllReduceArgs r{};
             for (uint32_t p = 0; p < d->tp_size; ++p) r.peers[p] = d->peers[p];
             r.in = b.partial + (size_t)i * E; r.resid = b.x + (size_t)i * E; r.out = b.x + (size_t)i * E; r.n = E;
-            r.rank = d->tp_rank; r.world = d->tp_size; r.st = CommState{d->comm_state}; r.status = ctx->status;
+            r.rank = d->tp_rank; r.world = d->tp_size; r.st = CommState{d->comm_state}; r.status = ctx->status; r.wait_ns = ctx->wait_limit_ns;
             CK(launch_allreduce_resid(r, s, false));
         }
         return FL_B200_OK;
@@ -684,7 +691,7 @@ static int enqueue_batch(fl_b200_decoder *d, uint32_t m, cudaStream_t s) {
             TopExchangeArgs x{};
             for (uint32_t p = 0; p < d->tp_size; ++p) x.peers[p] = d->peers[p];
             x.top3 = b.top3 + 4 * i; x.index_base = d->tp_rank * V; x.out_idx = next + i; x.out_margin = b.margin + i;
-            x.rank = d->tp_rank; x.world = d->tp_size; x.st = CommState{d->comm_state}; x.status = ctx->status;
+            x.rank = d->tp_rank; x.world = d->tp_size; x.st = CommState{d->comm_state}; x.status = ctx->status; x.wait_ns = ctx->wait_limit_ns;
             CK(launch_argmax_exchange(x, s, false));
         }
     }

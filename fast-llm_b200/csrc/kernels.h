@@ -77,6 +77,10 @@ struct MatvecArgs {
 cudaError_t tensor_map_2d(CUtensorMap *m, uint32_t elem_bytes, const void *base, uint64_t dim0, uint64_t rows,
                           uint64_t stride_bytes, uint32_t box0, uint32_t box_rows, bool swizzle128);
 cudaError_t launch_matvec(const MatvecArgs &a, int sms, cudaStream_t stream);
+// Q4_K / Q6_K launches that qualify run on the tensor-core streaming kernel (matvec_tc.cu).
+bool matvec_tc_eligible(const MatvecArgs &a);
+cudaError_t launch_matvec_tc(const MatvecArgs &a, int sms, cudaStream_t stream);
+cudaError_t matvec_tc_init(void);
 // Q4_K launches that qualify run on the integer tensor-core kernel (matvec_mma.cu).
 bool matvec_mma_eligible(const MatvecArgs &a);
 cudaError_t launch_matvec_mma(const MatvecArgs &a, int sms, cudaStream_t stream);
@@ -152,6 +156,7 @@ struct AllReduceArgs {
     uint32_t n, rank, world;
     CommState st;
     uint32_t *status;
+    uint64_t wait_ns;                // limit of the wait for the peers' flags (0 = one second)
 };
 struct TopExchangeArgs {
     uint8_t *peers[kCommMaxRanks];
@@ -162,6 +167,7 @@ struct TopExchangeArgs {
     uint32_t rank, world;
     CommState st;
     uint32_t *status;
+    uint64_t wait_ns;
 };
 // Sequence-parallel attention: every rank attended its slice of the keys and holds, per (sequence,
 // query head) record, the normalised context and (max, sum); the exchange merges the ranks' records.
@@ -173,6 +179,7 @@ struct LseCombineArgs {
     uint32_t n, max_records, rank, world;
     uint32_t *epoch;                 // kLseChunks device counters
     uint32_t *status;
+    uint64_t wait_ns;                // limit of the wait for the peers' flags (0 = one second)
 };
 constexpr uint32_t kLseChunks = 32;
 size_t lse_buffer_bytes(uint32_t max_records);

@@ -1,0 +1,675 @@
+// k-quant dequantize-matvec for single-token decode, tensor-core form (replaces the
+// reference's warp-per-row gdot_q4_K / gdot_q6_K, src/runtime/kernels_gpu.h:65-205,
+// and the STREAM_DOT branch of exec_task_block, src/runtime/gpu_exec.cu:64-140).
+//
+// HBM-bound by design: every packed weight byte crosses HBM -> shared memory once,
+// as bulk copies (cp.async.bulk) issued by a producer warp into a CTA-wide ring and
+// completed on mbarriers. What this kernel changes against the dp4a streaming kernel
+// (matvec.cu) is the arithmetic: there the consume loop was bound by instruction
+// issue (about 2.7 instructions per weight, the integer dot products at half rate).
+// Here
+//   * a unit of work is 16 rows x all columns; a stage is the same 8-super-block
+//     column segment (2048 columns) of the unit's 16 rows, one bulk copy per row;
+//     consumer warp w of a group owns super-block w of the segment for all 16 rows;
+//   * the 4- / 6-bit quants become f16 values with two logic operations per PAIR of
+//     weights (the quant lands in the mantissa of a constant: 64 + q for Q4_K; 1024 + q,
+//     then an exact f16 subtraction of 1056, for Q6_K), directly in the register
+//     layout of the A operand of mma.sync.m16n8k16: lane (g, t) holds rows g and g + 8;
+//   * the activation is kept per 256-column block as x = 2^e * (hi + lo) with hi, lo
+//     f16 (hi the nearest f16 of x / 2^e, lo the nearest f16 of the remainder: 22
+//     significant bits, and the power-of-two block scale keeps a block with one huge
+//     element exact for the small ones too). It is the B operand. Column n of B is
+//     non-zero only for the k-slots of lane column t = n / 2 (n & 1 selects hi / lo), so
+//     that the accumulator a lane reads back, C[g][2t], C[g][2t+1], C[g+8][2t],
+//     C[g+8][2t+1], is the dot product of exactly the 2 x 4 weights the lane unpacked
+//     with their activations: every lane column accumulates its own sub-block, the
+//     6-bit sub-block scales / mins are applied once per super-block in f32, and no
+//     shuffle is needed until a row is complete. Products are exact (11-bit x 11-bit),
+//     sums are f32 in a fixed order: results are reproducible run to run.
+//   * a unit's partial row sums (one per warp) are added in warp order by a finalizer
+//     warp, which also applies the fused epilogues (1/rms, residual, accumulate,
+//     SiLU(gate) * up).
+// Fused prologues as in the dp4a kernel: plain x, RMSNorm(x) * w, SiLU(x) * x2.
+#include "common.cuh"
+#include "kernels.h"
+
+#include <cuda.h>
+#include <cstdlib>
+#include <cstring>
+
+namespace flb {
+
+namespace {
+
+constexpr int kCW = 8;                          // consumer warps per group (one per super-block of a segment)
+constexpr uint32_t kSeg4 = 8 * 144, kSeg6 = 8 * 210;
+// Row pitch of a stage in shared memory. Q4_K: + 16 bytes so that the 128-bit loads of lanes
+// (g, t) and (g + 1, t) fall into different bank groups. Q6_K: the natural 1680 bytes (105 x 16:
+// odd), which together with the per-t rotation of the word order makes the 32-bit loads conflict free.
+constexpr uint32_t kPitch4 = kSeg4 + 16, kPitch6 = kSeg6;
+constexpr uint32_t kSlot4 = 16 * kPitch4, kSlot6 = 16 * kPitch6;
+// 256-column blocks a half-warp of the prologue converts (bounds the column count: see matvec_tc_eligible)
+__host__ __device__ constexpr int max_blk_per_half_warp(int groups) { return groups == 1 ? 4 : 2; }
+
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds16(uint32_t addr) {
+    uint16_t v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ void sts64(uint32_t addr, uint32_t a, uint32_t b) {
+    asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(addr), "r"(a), "r"(b) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// All threads of the prologue (every warp but the producer) meet here.
+__device__ __forceinline__ void prologue_barrier(uint32_t nthreads) {
+    asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
+}
+// D(16x8, f32) += A(16x16, f16, row) * B(16x8, f16, col)
+__device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// byte K of w as a float without the conversion pipe (the byte under 0x4B000000 is 2^23 + byte)
+template <int K>
+__device__ __forceinline__ float u8f(uint32_t w) {
+    return __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7650u | K)) - 8388608.0f;
+}
+__device__ __forceinline__ uint32_t word_of(const uint4 &v, int i) { return i == 0 ? v.x : i == 1 ? v.y : i == 2 ? v.z : v.w; }
+
+// ---- the activation in shared memory ---------------------------------------------------------
+// Per 256-column block 1024 bytes per layout: f16 hi and lo parts in the order the B operand wants.
+// "lane8" = 2 t + h is the slot of the lane (g = 2 t + h, t) that feeds column 2 t + h of B.
+// Q4_K layout: for word j (0..7) of a 32-byte chunk: 128 bytes = 8 lane8 x 16; a lane8's 16 bytes are the
+//   B registers (b0, b1) of the low-nibble MMA (columns 64 c + 4 j + {0, 2, 1, 3}) and of the high-nibble
+//   MMA (columns 64 c + 32 + 4 j + {0, 2, 1, 3}), c = t.
+// Q6_K layout: for step s (0..3; the lane column t works on word (s + t) & 3 of its 16-byte runs):
+//   256 bytes = 2 x (8 lane8 x 16); a lane8's 2 x 16 bytes are (b0, b1) of the four 32-column groups
+//   gq = 0..3 (columns 128 hf + 32 gq + 16 hq + 4 j + {0, 2, 1, 3}, t = 2 hf + hq).
+__device__ __forceinline__ uint32_t x4_off(uint32_t j, uint32_t lane8, uint32_t sub) { return j * 128u + lane8 * 16u + sub * 8u; }
+__device__ __forceinline__ uint32_t x6_off(uint32_t s, uint32_t lane8, uint32_t gq) {
+    return s * 256u + (gq >> 1) * 128u + lane8 * 16u + (gq & 1u) * 8u;
+}
+
+struct TcTensor {
+    const uint8_t *w;
+    float *y;
+    const float *resid;
+    uint32_t rows, pitch, unit0;   // unit0: index of the tensor's first unit in the launch
+    int fmt;
+};
+
+struct TcArgs {
+    TcTensor t[4];
+    int n_tensors;
+    const float *x, *x2, *wnorm;
+    float eps;
+    uint32_t cols;
+    int x_mode, accumulate, swiglu;
+    uint32_t total_units, nslots, slot_bytes;
+    int use_q4, use_q6;
+    uint32_t *status;
+    float *xn_out;
+    unsigned long long *trace;
+};
+
+struct TcSmem {
+    uint64_t *full, *empty;        // [nslots]
+    uint64_t *red_full, *red_empty;   // [2]
+    float *red;                    // [2][groups * 8][16]
+    float *ssq;                    // per-warp sums of squares of the prologue
+    float *xs;                     // [nblk] block scale 2^e
+    float *s4;                     // [nblk][8] sums of the 32-column sub-blocks, in units of the block scale
+    uint8_t *x4, *x6;              // [nblk][1024]
+    uint8_t *ring;
+};
+
+__host__ __device__ inline size_t tc_fixed_bytes(uint32_t cols, bool q4, bool q6, uint32_t nslots, int groups) {
+    const size_t nblk = cols / 256;
+    size_t n = (size_t)nslots * 16 + 32;                  // barriers
+    n += (size_t)2 * groups * kCW * 16 * 4;              // red
+    n += 33 * 4 + 12;                                     // ssq + padding
+    n += nblk * 4;                                        // xs
+    if (q4) n += nblk * 32 + nblk * 1024;
+    if (q6) n += nblk * 1024;
+    return n + 256;                                       // alignment slack
+}
+
+template <int G>
+__device__ __forceinline__ TcSmem tc_carve(uint8_t *base, uint32_t cols, bool q4, bool q6, uint32_t nslots) {
+    TcSmem s;
+    const uint32_t nblk = cols / 256;
+    uint8_t *p = base;
+    s.full = (uint64_t *)p; p += nslots * 8;
+    s.empty = (uint64_t *)p; p += nslots * 8;
+    s.red_full = (uint64_t *)p; p += 16;
+    s.red_empty = (uint64_t *)p; p += 16;
+    s.red = (float *)p; p += 2 * G * kCW * 16 * 4;
+    s.ssq = (float *)p; p += 33 * 4 + 12;
+    s.xs = (float *)p; p += nblk * 4;
+    p = (uint8_t *)(((uintptr_t)p + 15) & ~(uintptr_t)15);
+    s.s4 = nullptr; s.x4 = s.x6 = nullptr;
+    if (q4) { s.s4 = (float *)p; p += nblk * 32; s.x4 = p; p += (size_t)nblk * 1024; }
+    if (q6) { s.x6 = p; p += (size_t)nblk * 1024; }
+    p = (uint8_t *)(((uintptr_t)p + 127) & ~(uintptr_t)127);
+    s.ring = p;
+    return s;
+}
+
+// Which tensor and which first row a unit covers (non-SwiGLU launches).
+__device__ __forceinline__ int unit_tensor(const TcArgs &a, uint32_t u) {
+    int ti = 0;
+#pragma unroll 1
+    for (; ti < a.n_tensors - 1; ++ti)
+        if (u < a.t[ti + 1].unit0) break;
+    return ti;
+}
+
+// ---- per-super-block math ------------------------------------------------------------------
+
+// Q4_K: rows g (r0) and g + 8 (r1) of super-block `blk_addr` offsets; chunk c = t. Returns the two rows'
+// contributions in units of the block's activation scale.
+__device__ __forceinline__ void q4k_block(uint32_t r0, uint32_t r1, uint32_t t, bool has_b, uint32_t xaddr, float2 sx,
+                                          float &out0, float &out1) {
+    const uint4 h0 = lds128(r0), h1 = lds128(r1);
+    const uint4 wa0 = lds128(r0 + 16 + 32 * t), wb0 = lds128(r0 + 32 + 32 * t);
+    const uint4 wa1 = lds128(r1 + 16 + 32 * t), wb1 = lds128(r1 + 32 + 32 * t);
+    float cL[2][4], cH[2][4];
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int k = 0; k < 4; ++k) cL[i][k] = cH[i][k] = 0.f;
+    constexpr uint32_t M = 0x00F000F0u, K = 0x54005400u;   // f16 0x54xx: 64 + (mantissa bits 4..7)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        uint4 bx = make_uint4(0u, 0u, 0u, 0u);
+        if (has_b) bx = lds128(xaddr + j * 128);
+        const uint32_t W0 = j < 4 ? word_of(wa0, j) : word_of(wb0, j - 4);
+        const uint32_t W1 = j < 4 ? word_of(wa1, j) : word_of(wb1, j - 4);
+        // low nibbles (sub-block 2t): bytes 0, 2 -> k-slots 2t, 2t+1; bytes 1, 3 -> k-slots 2t+8, 2t+9
+        mma16816(cL[j & 1], ((W0 << 4) & M) | K, ((W1 << 4) & M) | K, ((W0 >> 4) & M) | K, ((W1 >> 4) & M) | K, bx.x, bx.y);
+        // high nibbles (sub-block 2t+1)
+        mma16816(cH[j & 1], (W0 & M) | K, (W1 & M) | K, ((W0 >> 8) & M) | K, ((W1 >> 8) & M) | K, bx.z, bx.w);
+    }
+    // 6-bit scales / mins of sub-blocks 2t, 2t+1 (packing: fl_q4k_scale_min, src/runtime/quants.h:121-129)
+    const uint32_t sh = 16u * (t & 1u);
+    const float s0 = sx.x, s1 = sx.y;
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const uint4 hdr = r ? h1 : h0;
+        const uint32_t a = hdr.y >> sh, b = hdr.z >> sh, e = hdr.w >> sh;
+        const uint32_t sc_lo = a & 0x3F3Fu, mn_lo = b & 0x3F3Fu;
+        const uint32_t sc_hi = (e & 0x0F0Fu) | ((a >> 2) & 0x3030u);
+        const uint32_t mn_hi = ((e >> 4) & 0x0F0Fu) | ((b >> 2) & 0x3030u);
+        const uint32_t sc = t >= 2 ? sc_hi : sc_lo, mn = t >= 2 ? mn_hi : mn_lo;
+        const float d = h2f_bits((uint16_t)(hdr.x & 0xFFFFu)), dmin = h2f_bits((uint16_t)(hdr.x >> 16));
+        const float tl = (cL[0][2 * r] + cL[1][2 * r]) + (cL[0][2 * r + 1] + cL[1][2 * r + 1]);
+        const float th = (cH[0][2 * r] + cH[1][2 * r]) + (cH[0][2 * r + 1] + cH[1][2 * r + 1]);
+        // the unpacked values are 64 + q: take 64 * (sum of the sub-block's activations) off again
+        const float q = u8f<0>(sc) * fmaf(-64.f, s0, tl) + u8f<1>(sc) * fmaf(-64.f, s1, th);
+        const float m = u8f<0>(mn) * s0 + u8f<1>(mn) * s1;
+        (r ? out1 : out0) = d * q - dmin * m;
+    }
+}
+
+// Q6_K: lane column t = 2 hf + hq works on the 16-byte runs ql[64 hf + 16 hq ..], ql[64 hf + 32 + 16 hq ..],
+// qh[32 hf + 16 hq ..] of rows g and g + 8 (q = nibble | two high bits << 4, value d * sc * (q - 32);
+// fl_dot_row_q6_K, src/runtime/quants.h:194-230). ODD: the block starts 2 bytes past a word boundary.
+template <bool ODD>
+__device__ __forceinline__ void q6k_block(uint32_t r0, uint32_t r1, uint32_t t, bool has_b, uint32_t xaddr, float &out0,
+                                          float &out1) {
+    const uint32_t hf = t >> 1, hq = t & 1u;
+    float c[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int k = 0; k < 4; ++k) c[i][k] = 0.f;
+    const __half2 off = __floats2half2_rn(1056.f, 1056.f);
+    const uint32_t oa = 64 * hf + 16 * hq, oh = 128 + 32 * hf + 16 * hq;   // byte offsets in the block (ODD: r0, r1 are 2 less)
+#pragma unroll
+    for (int s = 0; s < 4; ++s) {
+        const uint32_t js = ((uint32_t)s + t) & 3u;
+        uint4 bA = make_uint4(0u, 0u, 0u, 0u), bB = make_uint4(0u, 0u, 0u, 0u);
+        if (has_b) { bA = lds128(xaddr + s * 256); bB = lds128(xaddr + s * 256 + 128); }
+        uint32_t a_[2][8];   // per row: A registers (k-slots 2t.. , 2t+8..) of the four groups
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            const uint32_t rb = r ? r1 : r0;
+            uint32_t wa, wb, wh;
+            if (ODD) {
+                wa = __byte_perm(lds32(rb + oa + 4 * js), lds32(rb + oa + 4 * js + 4), 0x5432u);
+                wb = __byte_perm(lds32(rb + oa + 32 + 4 * js), lds32(rb + oa + 36 + 4 * js), 0x5432u);
+                wh = __byte_perm(lds32(rb + oh + 4 * js), lds32(rb + oh + 4 * js + 4), 0x5432u);
+            } else {
+                wa = lds32(rb + oa + 4 * js);
+                wb = lds32(rb + oa + 32 + 4 * js);
+                wh = lds32(rb + oh + 4 * js);
+            }
+            uint32_t q[4];
+            q[0] = (wa & 0x0F0F0F0Fu) | ((wh << 4) & 0x30303030u);
+            q[1] = (wb & 0x0F0F0F0Fu) | ((wh << 2) & 0x30303030u);
+            q[2] = ((wa >> 4) & 0x0F0F0F0Fu) | (wh & 0x30303030u);
+            q[3] = ((wb >> 4) & 0x0F0F0F0Fu) | ((wh >> 2) & 0x30303030u);
+#pragma unroll
+            for (int gq = 0; gq < 4; ++gq) {
+                // bytes 0, 2 / 1, 3 under 0x64: f16 1024 + q; minus 1056 is q - 32, exact
+                const uint32_t e02 = __byte_perm(q[gq], 0x64646464u, 0x4240u), e13 = __byte_perm(q[gq], 0x64646464u, 0x4341u);
+                __half2 h02 = *reinterpret_cast<const __half2 *>(&e02), h13 = *reinterpret_cast<const __half2 *>(&e13);
+                h02 = __hsub2(h02, off);
+                h13 = __hsub2(h13, off);
+                a_[r][2 * gq] = *reinterpret_cast<const uint32_t *>(&h02);
+                a_[r][2 * gq + 1] = *reinterpret_cast<const uint32_t *>(&h13);
+            }
+        }
+        mma16816(c[0], a_[0][0], a_[1][0], a_[0][1], a_[1][1], bA.x, bA.y);
+        mma16816(c[1], a_[0][2], a_[1][2], a_[0][3], a_[1][3], bA.z, bA.w);
+        mma16816(c[2], a_[0][4], a_[1][4], a_[0][5], a_[1][5], bB.x, bB.y);
+        mma16816(c[3], a_[0][6], a_[1][6], a_[0][7], a_[1][7], bB.z, bB.w);
+    }
+    // scales: int8 sc[8 hf + 2 gq + hq]; d at byte 208
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const uint32_t rb = r ? r1 : r0;
+        const uint32_t ps = rb + 192 + 8 * hf;
+        uint32_t lo, hi;
+        if (ODD) {
+            const uint32_t s0 = lds32(ps), s1 = lds32(ps + 4), s2 = lds32(ps + 8);
+            lo = __byte_perm(s0, s1, 0x5432u);
+            hi = __byte_perm(s1, s2, 0x5432u);
+        } else {
+            lo = lds32(ps);
+            hi = lds32(ps + 4);
+        }
+        const uint32_t sw = __byte_perm(lo, hi, hq ? 0x7531u : 0x6420u) ^ 0x80808080u;   // s + 128 as unsigned bytes
+        const float d = h2f_bits((uint16_t)lds16(rb + (ODD ? 2u : 0u) + 208));
+        float v = (u8f<0>(sw) - 128.f) * (c[0][2 * r] + c[0][2 * r + 1]);
+        v += (u8f<1>(sw) - 128.f) * (c[1][2 * r] + c[1][2 * r + 1]);
+        v += (u8f<2>(sw) - 128.f) * (c[2][2 * r] + c[2][2 * r + 1]);
+        v += (u8f<3>(sw) - 128.f) * (c[3][2 * r] + c[3][2 * r + 1]);
+        (r ? out1 : out0) = d * v;
+    }
+}
+
+// ---- the kernel ----------------------------------------------------------------------------
+// Warps: G groups of 8 consumer warps (group i takes stages i, i + G, ...), then the producer warp,
+// then the finalizer warp.
+template <int G>
+__global__ void __launch_bounds__((G * kCW + 2) * 32, 1) matvec_tc_kernel(const __grid_constant__ TcArgs a) {
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    constexpr uint32_t kConsumers = G * kCW;
+    constexpr uint32_t kProducer = kConsumers, kFinal = kConsumers + 1;
+    constexpr uint32_t kPrologueThreads = (kConsumers + 1) * 32;
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    const uint32_t nblk = a.cols / 256, nseg = (nblk + 7) / 8;
+    const TcSmem sm = tc_carve<G>(smem_raw, a.cols, a.use_q4 != 0, a.use_q6 != 0, a.nslots);
+    const uint32_t S = a.nslots;
+
+    if (tid == 0) {
+        for (uint32_t s = 0; s < S; ++s) { mbar_init(&sm.full[s], 1); mbar_init(&sm.empty[s], kCW); }
+        for (int i = 0; i < 2; ++i) { mbar_init(&sm.red_full[i], kConsumers); mbar_init(&sm.red_empty[i], 1); }
+        fence_barrier_init();
+        trace_min(a.trace, 0);
+    }
+    __syncthreads();
+    griddep_launch_dependents();
+
+    // units of this CTA: blockIdx.x, + gridDim.x, ...
+    const uint32_t my_units = blockIdx.x < a.total_units ? (a.total_units - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    const uint32_t ring = smem_u32(sm.ring);
+
+    if (warp == kProducer) {
+        // ---- producer: one bulk copy per row and stage; the weights do not depend on the previous kernel ----
+        uint32_t slot = 0, par = 1;   // a fresh barrier passes a wait on parity 1
+        for (uint32_t k = 0; k < my_units; ++k) {
+            const uint32_t u = blockIdx.x + k * gridDim.x;
+            const uint8_t *src = nullptr;
+            uint32_t pitch = 0, fmt;
+            bool valid = false;
+            if (a.swiglu) {
+                const TcTensor &t = a.t[(lane >> 3) & 1u];
+                const uint32_t row = 8 * u + (lane & 7u);
+                fmt = (uint32_t)a.t[0].fmt;
+                valid = lane < 16 && row < t.rows;
+                pitch = t.pitch;
+                src = t.w + (size_t)row * t.pitch;
+            } else {
+                const TcTensor &t = a.t[unit_tensor(a, u)];
+                const uint32_t row = 16 * (u - t.unit0) + lane;
+                fmt = (uint32_t)t.fmt;
+                valid = lane < 16 && row < t.rows;
+                pitch = t.pitch;
+                src = t.w + (size_t)row * t.pitch;
+            }
+            const uint32_t segb = fmt == FMT_Q4_K ? kSeg4 : kSeg6, rp = fmt == FMT_Q4_K ? kPitch4 : kPitch6;
+            const uint32_t nvalid = __popc(__ballot_sync(0xffffffffu, valid));
+            for (uint32_t seg = 0; seg < nseg; ++seg) {
+                const uint32_t off = seg * segb;
+                const uint32_t bytes = min(segb, pitch - off);   // pitch and off are multiples of 16
+                if (!mbar_wait_bounded(&sm.empty[slot], par, a.status)) return;
+                fence_proxy_async_smem();
+                if (lane == 0) mbar_arrive_expect_tx(&sm.full[slot], nvalid * bytes);
+                __syncwarp();
+                if (valid) bulk_g2s_addr(ring + slot * a.slot_bytes + lane * rp, src + off, bytes, &sm.full[slot]);
+                if (++slot == S) { slot = 0; par ^= 1u; }
+            }
+        }
+        return;
+    }
+
+    // ---- prologue (consumers and the finalizer): the activation as f16 (hi, lo) pairs ----
+    {
+        const uint32_t pw = warp < kProducer ? warp : warp - 1;   // 0 .. kConsumers
+        const uint32_t hw = 2 * pw + (lane >> 4), hl = lane & 15u;
+        constexpr uint32_t nhw = 2 * (kConsumers + 1);
+        constexpr int kMaxBlkPerHalfWarp = max_blk_per_half_warp(G);
+        float4 ra[kMaxBlkPerHalfWarp][4], rb[kMaxBlkPerHalfWarp][4];
+#pragma unroll
+        for (int b = 0; b < kMaxBlkPerHalfWarp; ++b)
+#pragma unroll
+            for (int k = 0; k < 4; ++k) ra[b][k] = rb[b][k] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (a.x_mode == MV_X_RMSNORM) {   // the norm weights are constants: fetch them before the dependency wait
+#pragma unroll
+            for (int b = 0; b < kMaxBlkPerHalfWarp; ++b) {
+                const uint32_t blk = hw + b * nhw;
+                if (blk < nblk) {
+                    const float4 *src = reinterpret_cast<const float4 *>(a.wnorm + blk * 256 + hl * 16);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) rb[b][k] = __ldg(src + k);
+                }
+            }
+        }
+        griddep_wait();   // the activation (and y, resid) come from the previous kernel
+        if (tid == 0) trace_min(a.trace, 1);
+#pragma unroll
+        for (int b = 0; b < kMaxBlkPerHalfWarp; ++b) {
+            const uint32_t blk = hw + b * nhw;
+            if (blk < nblk) {
+                const float4 *src = reinterpret_cast<const float4 *>(a.x + blk * 256 + hl * 16);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) ra[b][k] = src[k];
+                if (a.x_mode == MV_X_SILU_MUL) {
+                    const float4 *src2 = reinterpret_cast<const float4 *>(a.x2 + blk * 256 + hl * 16);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) rb[b][k] = src2[k];
+                }
+            }
+        }
+        // RMSNorm: hi / lo are those of x * w; the common factor 1 / rms goes onto the row sums at the end
+        if (a.x_mode == MV_X_RMSNORM) {
+            float ss = 0.f;
+#pragma unroll
+            for (int b = 0; b < kMaxBlkPerHalfWarp; ++b)
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const float4 u = ra[b][k];
+                    ss += (u.x * u.x + u.y * u.y) + (u.z * u.z + u.w * u.w);
+                }
+            ss = warp_sum(ss);
+            if (lane == 0) sm.ssq[pw] = ss;
+        }
+#pragma unroll
+        for (int b = 0; b < kMaxBlkPerHalfWarp; ++b) {
+            const uint32_t blk = hw + b * nhw;
+            if (2 * pw + b * nhw >= nblk) break;   // warp-uniform
+            const bool live = blk < nblk;          // the second half-warp of the last warp may be past the end
+            float v[16];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                v[4 * k] = ra[b][k].x; v[4 * k + 1] = ra[b][k].y; v[4 * k + 2] = ra[b][k].z; v[4 * k + 3] = ra[b][k].w;
+            }
+            if (a.x_mode != MV_X_PLAIN) {
+                float w2[16];
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    w2[4 * k] = rb[b][k].x; w2[4 * k + 1] = rb[b][k].y; w2[4 * k + 2] = rb[b][k].z; w2[4 * k + 3] = rb[b][k].w;
+                }
+#pragma unroll
+                for (int i = 0; i < 16; ++i)
+                    v[i] = a.x_mode == MV_X_RMSNORM ? v[i] * w2[i] : (v[i] / (1.0f + expf(-v[i]))) * w2[i];
+            }
+            float amax = 0.f;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
+#pragma unroll
+            for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));   // over the half-warp
+            // block scale 2^e with amax / 2^e in [2^13, 2^14); e clamped so that both 2^e and 2^-e are normal floats
+            int e = (int)((__float_as_uint(amax) >> 23) & 0xFFu) - 127 - 13;
+            e = amax > 0.f ? max(-126, min(e, 114)) : 0;
+            const float inv_s = __uint_as_float((uint32_t)(127 - e) << 23);
+            uint32_t hi2[8], lo2[8];   // element pairs (i, i + 2) of each group of four: the B operand's k order
+            float sum = 0.f;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                __half hh[4], ll[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float s = v[4 * j + i] * inv_s;
+                    hh[i] = __float2half_rn(s);
+                    const float r = s - __half2float(hh[i]);
+                    ll[i] = __float2half_rn(r);
+                    sum += __half2float(hh[i]) + __half2float(ll[i]);
+                }
+                hi2[2 * j] = (uint32_t)__half_as_ushort(hh[0]) | ((uint32_t)__half_as_ushort(hh[2]) << 16);
+                hi2[2 * j + 1] = (uint32_t)__half_as_ushort(hh[1]) | ((uint32_t)__half_as_ushort(hh[3]) << 16);
+                lo2[2 * j] = (uint32_t)__half_as_ushort(ll[0]) | ((uint32_t)__half_as_ushort(ll[2]) << 16);
+                lo2[2 * j + 1] = (uint32_t)__half_as_ushort(ll[1]) | ((uint32_t)__half_as_ushort(ll[3]) << 16);
+            }
+            const float sum32 = sum + __shfl_xor_sync(0xffffffffu, sum, 1);
+            if (live) {
+                if (a.use_q4) {
+                    // columns 16 hl .. 16 hl + 15: chunk c = hl / 4, sub-block half (hl / 2) & 1, words 4 (hl & 1) + j
+                    const uint32_t c = hl >> 2, sub = (hl >> 1) & 1u, j0 = 4 * (hl & 1u);
+                    const uint32_t base = smem_u32(sm.x4) + blk * 1024u;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        sts64(base + x4_off(j0 + j, 2 * c, sub), hi2[2 * j], hi2[2 * j + 1]);
+                        sts64(base + x4_off(j0 + j, 2 * c + 1, sub), lo2[2 * j], lo2[2 * j + 1]);
+                    }
+                    if ((hl & 1u) == 0) sm.s4[blk * 8 + (hl >> 1)] = sum32;
+                }
+                if (a.use_q6) {
+                    // columns 16 hl ..: half hf = hl / 8, group gq = (hl / 2) & 3, run hq = hl & 1, words j = 0..3
+                    const uint32_t hf = hl >> 3, gq = (hl >> 1) & 3u, hq = hl & 1u, t = 2 * hf + hq;
+                    const uint32_t base = smem_u32(sm.x6) + blk * 1024u;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const uint32_t s = ((uint32_t)j - t) & 3u;
+                        sts64(base + x6_off(s, 2 * t, gq), hi2[2 * j], hi2[2 * j + 1]);
+                        sts64(base + x6_off(s, 2 * t + 1, gq), lo2[2 * j], lo2[2 * j + 1]);
+                    }
+                }
+                if (hl == 0) sm.xs[blk] = __uint_as_float((uint32_t)(127 + e) << 23);
+            }
+        }
+        prologue_barrier(kPrologueThreads);
+        if (a.xn_out != nullptr && blockIdx.x == 0) {   // the activation as f32, for layer-level checks
+            float t = 0.f;
+            for (uint32_t w = 0; w <= kConsumers; ++w) t += sm.ssq[w];
+            const float inv_rms = 1.0f / sqrtf(t / (float)a.cols + a.eps);
+            const uint32_t ptid = pw * 32 + lane;
+            for (uint32_t c = ptid; c < a.cols; c += kPrologueThreads) {
+                float v = a.x[c];
+                if (a.x_mode == MV_X_RMSNORM) v = v * inv_rms * a.wnorm[c];
+                else if (a.x_mode == MV_X_SILU_MUL) v = (v / (1.0f + expf(-v))) * a.x2[c];
+                a.xn_out[c] = v;
+            }
+        }
+        if (tid == 0) trace_max(a.trace, 2);
+    }
+
+    if (warp == kFinal) {
+        // ---- finalizer: adds the warps' partial row sums of a unit in warp order, applies the epilogue ----
+        float inv_rms = 1.f;
+        if (a.x_mode == MV_X_RMSNORM) {
+            float t = 0.f;
+            for (uint32_t w = 0; w <= kConsumers; ++w) t += sm.ssq[w];   // the same order in every CTA
+            inv_rms = 1.0f / sqrtf(t / (float)a.cols + a.eps);
+        }
+        for (uint32_t k = 0; k < my_units; ++k) {
+            const uint32_t u = blockIdx.x + k * gridDim.x, buf = k & 1u;
+            if (!mbar_wait_bounded(&sm.red_full[buf], (k >> 1) & 1u, a.status)) return;
+            float v = 0.f;
+            if (lane < 16) {
+                const float *p = sm.red + buf * kConsumers * 16 + lane;
+#pragma unroll
+                for (uint32_t w = 0; w < kConsumers; ++w) v += p[w * 16];
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sm.red_empty[buf]);
+            v *= inv_rms;
+            if (a.swiglu) {
+                // rows 0..7 = gate rows 8u.., rows 8..15 = up rows: h = silu(gate) * up (fl_op_silu_mul,
+                // src/runtime/decode_params.h:267-272)
+                const float up = __shfl_down_sync(0xffffffffu, v, 8);
+                const uint32_t row = 8 * u + lane;
+                if (lane < 8 && row < a.t[0].rows) a.t[0].y[row] = (v / (1.0f + expf(-v))) * up;
+            } else {
+                const TcTensor &t = a.t[unit_tensor(a, u)];
+                const uint32_t row = 16 * (u - t.unit0) + lane;
+                if (lane < 16 && row < t.rows) {
+                    float o = v;
+                    if (t.resid) o = t.resid[row] + v;
+                    if (a.accumulate) o = t.y[row] + o;
+                    t.y[row] = o;
+                }
+            }
+        }
+        if (lane == 0) trace_max(a.trace, 3);
+        return;
+    }
+
+    // ---- consumers ----
+    {
+        const uint32_t grp = warp / kCW, w = warp % kCW;
+        const uint32_t g = lane >> 2, t = lane & 3u;
+        const bool has_b = (g >> 1) == t;
+        const uint32_t lane8 = 2 * t + (g & 1u);
+        const uint32_t x4 = a.use_q4 ? smem_u32(sm.x4) + lane8 * 16u : 0u, x6 = a.use_q6 ? smem_u32(sm.x6) + lane8 * 16u : 0u;
+        for (uint32_t k = 0; k < my_units; ++k) {
+            const uint32_t u = blockIdx.x + k * gridDim.x;
+            const int fmt = a.swiglu ? a.t[0].fmt : a.t[unit_tensor(a, u)].fmt;
+            float acc0 = 0.f, acc1 = 0.f;
+            // this group's stages of unit k: global stage index it = k * nseg + seg, it % G == grp
+            const uint32_t it0 = k * nseg;
+            uint32_t seg = (grp + G - it0 % G) % G;
+            for (; seg < nseg; seg += G) {
+                const uint32_t it = it0 + seg, slot = it % S, par = (it / S) & 1u;
+                const uint32_t blk = seg * 8 + w;
+                if (!mbar_wait_bounded(&sm.full[slot], par, a.status)) return;
+                if (blk < nblk) {
+                    const float xs = sm.xs[blk];
+                    float o0, o1;
+                    if (fmt == FMT_Q4_K) {
+                        const uint32_t r0 = ring + slot * a.slot_bytes + g * kPitch4 + w * 144u;
+                        const float2 sx = *reinterpret_cast<const float2 *>(sm.s4 + blk * 8 + 2 * t);
+                        q4k_block(r0, r0 + 8 * kPitch4, t, has_b, x4 + blk * 1024u, sx, o0, o1);
+                    } else {
+                        const uint32_t r0 = ring + slot * a.slot_bytes + g * kPitch6 + w * 210u;
+                        if (w & 1u) q6k_block<true>(r0 - 2, r0 + 8 * kPitch6 - 2, t, has_b, x6 + blk * 1024u, o0, o1);
+                        else q6k_block<false>(r0, r0 + 8 * kPitch6, t, has_b, x6 + blk * 1024u, o0, o1);
+                    }
+                    acc0 = fmaf(xs, o0, acc0);
+                    acc1 = fmaf(xs, o1, acc1);
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&sm.empty[slot]);
+            }
+            // the unit's partial sums of rows g and g + 8 over this warp's lane columns
+            acc0 += __shfl_xor_sync(0xffffffffu, acc0, 1);
+            acc1 += __shfl_xor_sync(0xffffffffu, acc1, 1);
+            acc0 += __shfl_xor_sync(0xffffffffu, acc0, 2);
+            acc1 += __shfl_xor_sync(0xffffffffu, acc1, 2);
+            const uint32_t buf = k & 1u;
+            if (!mbar_wait_bounded(&sm.red_empty[buf], ((k >> 1) & 1u) ^ 1u, a.status)) return;
+            if (t == 0) {
+                float *p = sm.red + (buf * kConsumers + warp) * 16;
+                p[g] = acc0;
+                p[g + 8] = acc1;
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sm.red_full[buf]);
+        }
+    }
+}
+
+int tc_groups() {
+    static const int v = getenv("FLB_TC_GROUPS") ? atoi(getenv("FLB_TC_GROUPS")) : 1;
+    return v == 2 ? 2 : 1;
+}
+
+} // namespace
+
+cudaError_t matvec_tc_init(void) {
+    cudaError_t e = cudaFuncSetAttribute(matvec_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024 - 1024);
+    if (e != cudaSuccess) return e;
+    return cudaFuncSetAttribute(matvec_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024 - 1024);
+}
+
+// True when the launch can run on the tensor-core kernel: Q4_K / Q6_K tensors only, whole 256-column
+// blocks, 16-byte aligned rows, no expert indirection and no exchange prologue.
+bool matvec_tc_eligible(const MatvecArgs &a) {
+    static const bool off = getenv("FLB_TC") && getenv("FLB_TC")[0] == '0';
+    if (off || a.xr_buf || a.cols % 256 != 0 || a.cols < 256) return false;
+    if ((((uintptr_t)a.x) & 15u) || (((uintptr_t)a.x2) & 15u) || (((uintptr_t)a.wnorm) & 15u)) return false;
+    const int groups = tc_groups();
+    if (a.cols / 256 > (uint32_t)(max_blk_per_half_warp(groups) * 2 * (groups * kCW + 1))) return false;
+    bool q4 = false, q6 = false;
+    for (int i = 0; i < a.n_tensors; ++i) {
+        const MatvecTensor &t = a.t[i];
+        if (t.fmt != FMT_Q4_K && t.fmt != FMT_Q6_K) return false;
+        if (t.expert_id || t.rows == 0) return false;
+        const uint64_t pitch = t.pitch ? t.pitch : row_bytes(t.fmt, a.cols);
+        if ((pitch & 15u) || (((uintptr_t)t.w) & 15u) || pitch < row_bytes(t.fmt, a.cols)) return false;
+        (t.fmt == FMT_Q4_K ? q4 : q6) = true;
+    }
+    if (a.swiglu && (a.n_tensors != 2 || a.t[0].rows != a.t[1].rows || a.t[0].fmt != a.t[1].fmt || a.accumulate)) return false;
+    const uint32_t slot = q6 ? kSlot6 : kSlot4;
+    return tc_fixed_bytes(a.cols, q4, q6, 2, groups) + 2u * slot <= 227 * 1024 - 1024;
+}
+
+cudaError_t launch_matvec_tc(const MatvecArgs &a, int sms, cudaStream_t stream) {
+    TcArgs k;
+    memset(&k, 0, sizeof(k));
+    const int groups = tc_groups();
+    bool q4 = false, q6 = false;
+    uint32_t units = 0;
+    k.n_tensors = a.n_tensors;
+    for (int i = 0; i < a.n_tensors; ++i) {
+        const MatvecTensor &t = a.t[i];
+        k.t[i].w = t.w; k.t[i].y = t.y; k.t[i].resid = t.resid; k.t[i].rows = t.rows; k.t[i].fmt = t.fmt;
+        k.t[i].pitch = t.pitch ? t.pitch : (uint32_t)row_bytes(t.fmt, a.cols);
+        k.t[i].unit0 = units;
+        units += (t.rows + 15) / 16;
+        (t.fmt == FMT_Q4_K ? q4 : q6) = true;
+    }
+    if (a.swiglu) units = (a.t[0].rows + 7) / 8;
+    k.x = a.x; k.x2 = a.x2; k.wnorm = a.wnorm; k.eps = a.eps; k.cols = a.cols; k.x_mode = a.x_mode;
+    k.accumulate = a.accumulate; k.swiglu = a.swiglu; k.total_units = units;
+    k.use_q4 = q4 ? 1 : 0; k.use_q6 = q6 ? 1 : 0;
+    k.status = a.status; k.xn_out = a.xn_out; k.trace = a.trace;
+    k.slot_bytes = q6 ? kSlot6 : kSlot4;
+    const size_t limit = 227 * 1024 - 1024;
+    uint32_t nslots = 2;
+    while (nslots < 32 && tc_fixed_bytes(a.cols, q4, q6, nslots + 1, groups) + (size_t)(nslots + 1) * k.slot_bytes <= limit) ++nslots;
+    k.nslots = nslots;
+    const size_t smem = tc_fixed_bytes(a.cols, q4, q6, nslots, groups) + (size_t)nslots * k.slot_bytes;
+    const uint32_t grid = units < (uint32_t)sms ? units : (uint32_t)sms;
+    if (groups == 2)
+        return launch_kernel(matvec_tc_kernel<2>, dim3(grid), dim3((2 * kCW + 2) * 32), smem, stream, a.pdl != 0, k);
+    return launch_kernel(matvec_tc_kernel<1>, dim3(grid), dim3((kCW + 2) * 32), smem, stream, a.pdl != 0, k);
+}
+
+} // namespace flb

@@ -254,7 +254,7 @@ static int moe_enqueue(fl_b200_moe *m, const float *x, uint32_t n_tok, float *y)
             AllReduceArgs r{};
             for (uint32_t p = 0; p < m->world; ++p) r.peers[p] = m->peers[p];
             r.in = m->partial + (size_t)t * E; r.resid = nullptr; r.out = y + (size_t)t * E; r.n = E;
-            r.rank = m->rank; r.world = m->world; r.st = CommState{m->comm_state}; r.status = ctx->status;
+            r.rank = m->rank; r.world = m->world; r.st = CommState{m->comm_state}; r.status = ctx->status; r.wait_ns = ctx->wait_limit_ns;
             CKM(launch_allreduce_resid(r, s, false));
         }
     }

@@ -69,6 +69,11 @@ int fl_b200_sync(fl_b200_ctx *ctx);
 /* Reads and clears the device status word (0 = no kernel reported a problem). */
 int fl_b200_device_status(fl_b200_ctx *ctx, uint32_t *status_out);
 int fl_b200_sm_count(fl_b200_ctx *ctx);
+/* Limit, in nanoseconds of the device clock, of the waits of the exchange kernels for another rank's
+ * flag (0 = the default of one second). When it runs out the kernel records status 2 ("peer time-out"),
+ * leaves its output untouched and returns; nothing faults and nothing waits for ever. The reference's
+ * counterpart is the 60 s stall abort of Runtime::run (src/runtime/runtime.cpp:239). */
+int fl_b200_set_wait_limit(fl_b200_ctx *ctx, uint64_t nanoseconds);
 /* cudaStream_t of the context, for callers that enqueue their own work. */
 void *fl_b200_stream(fl_b200_ctx *ctx);
 

@@ -21,7 +21,8 @@ import numpy as np
 HERE = os.path.dirname(os.path.abspath(__file__))
 PORT_LIB = os.path.join(HERE, "liboracle.so")
 REF_LIB = os.path.join(HERE, "_ref", "libflref.so")
-REF_SRC = os.environ.get("FLB_REFERENCE", "/root/reference")
+# the reference checkout: FLB_REFERENCE, else a directory named "reference" beside this repository
+REF_SRC = os.environ.get("FLB_REFERENCE") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
 
 F32, Q8_0, Q5_0, Q4_K, Q6_K = 0, 1, 2, 3, 4
 T_WQ, T_WK, T_WV, T_WO, T_GATE, T_UP, T_DOWN = range(7)

@@ -49,3 +49,25 @@ def test_product_does_not_use_the_oracle():
             if f.endswith((".py", ".cu", ".cuh", ".h", ".cpp")):
                 src = open(os.path.join(dirpath, f)).read()
                 assert "oracle" not in src.lower() or f == "__init__.py", os.path.join(dirpath, f)
+
+
+def test_reference_binding_links(lib):
+    """The reference's runtime.cpp, compiled with its GPU backend switched on, links against the six gpu_*
+    functions of oracle/gpu_exec_b200_check.cpp (forwarding to the C ABI) with no undefined symbol:
+    the signatures are those of src/runtime/runtime_internal.h:288-301. Needs the reference checkout."""
+    import subprocess
+    from oracle import pyoracle
+    if not os.path.isdir(os.path.join(pyoracle.REF_SRC, "src", "runtime")):
+        pytest.skip("reference checkout not present")
+    if not os.path.exists("/usr/local/cuda/include/cuda_runtime.h") and not os.environ.get("CUDA_HOME"):
+        pytest.skip("CUDA headers not present")
+    out = os.path.join(ROOT, "oracle", "_ref", "libfastllm_b200_binding.so")
+    if os.path.exists(out):
+        os.remove(out)
+    res = subprocess.run(["make", "-C", os.path.join(ROOT, "oracle"), "binding", "REF=" + pyoracle.REF_SRC],
+                         stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    assert res.returncode == 0 and os.path.exists(out), res.stdout
+    syms = subprocess.run(["nm", "-D", "--defined-only", out], stdout=subprocess.PIPE, text=True).stdout
+    for name in ("gpu_make_stream", "gpu_start", "gpu_resident_blocks", "gpu_stop_sync", "gpu_calibrate_clock",
+                 "gpu_default_blocks"):
+        assert name in syms, name

@@ -116,6 +116,44 @@ def test_matvec_vs_oracle(ctx, checker, fmt, rows, cols):
     assert np.array_equal(bits(got), bits(gpu_matvec(ctx, fmt, w, rows, cols, x)))
 
 
+@pytest.mark.parametrize("fmt", [capi.Q4_K, capi.Q6_K, capi.Q8_0])
+@pytest.mark.parametrize("case", ["outlier_1e3", "outlier_1e4", "zero_block", "denormal_block", "tiny_vector"])
+def test_matvec_activation_outliers(ctx, checker, fmt, case):
+    """The kernels keep the activation per 256-column block as scaled low-precision parts. Real residual
+    streams hold single elements 1e3 - 1e4 times their neighbours: the small elements of such a block, an
+    all-zero block, a block of denormal-scale values and a vector that is tiny throughout must all stay
+    inside the 1e-3 gate (measured against the rows' own magnitude, not against the outlier)."""
+    rows, cols = 256, 4096
+    rng = np.random.default_rng(1000 + fmt)
+    w = synth.quant_tensor(fmt, rng, rows, cols)
+    x = rng.standard_normal(cols).astype(np.float32)
+    if case.startswith("outlier"):
+        # one huge element inside block 3; its own contribution is removed from both sides below so that the
+        # comparison is about the OTHER elements of the block
+        x[3 * 256 + 77] *= 1e3 if case == "outlier_1e3" else 1e4
+    elif case == "zero_block":
+        x[5 * 256:6 * 256] = 0.0
+        x[9 * 256:10 * 256] = -0.0
+    elif case == "denormal_block":
+        x[7 * 256:8 * 256] = (rng.standard_normal(256) * 1e-40).astype(np.float32)
+    else:
+        x *= np.float32(1e-30)
+    got = gpu_matvec(ctx, fmt, w, rows, cols, x)
+    want = checker.matvec(fmt, w, rows, cols, x)
+    assert np.all(np.isfinite(got))
+    if case.startswith("outlier"):
+        # error budget relative to the product WITHOUT the outlier column
+        x0 = x.copy(); x0[3 * 256 + 77] = 0.0
+        base = checker.matvec(fmt, w, rows, cols, x0)
+        floor = 0.1 * np.sqrt(np.mean(base.astype(np.float64) ** 2))
+        err = np.max(np.abs(got.astype(np.float64) - want) / np.maximum(np.abs(base), floor))
+        # the f32 oracle itself carries 2^-24 of the outlier term: allow that much on top of the gate
+        slack = float(np.max(np.abs(want - base)) * 2.0 ** -23 / floor)
+        assert err <= MATVEC_RTOL + slack, (err, slack)
+    else:
+        assert rel_err(got, want) <= MATVEC_RTOL
+
+
 @pytest.mark.parametrize("fmt,rows,cols,c0,n", [
     (capi.Q6_K, 4096, 14336, 7168, 7168),    # down, rank 1 of 2
     (capi.Q6_K, 512, 14336, 3584 * 3, 3584), # down, rank 3 of 4

@@ -185,3 +185,46 @@ def test_freeze_rules(ctx):
     with pytest.raises(capi.Fl200Error): g.freeze()
     g = Graph(ctx); a = g.add(9, aux=x.data_ptr()); s = g.add(capi.K_SIGNAL); g.edge(a, s)   # ATTN_HEAD (f32 MHA): no device kernel
     with pytest.raises(capi.Fl200Error): g.freeze()
+
+
+def test_plan_survives_growth_of_the_attention_scratch(ctx, checker):
+    """A recorded plan keeps the split-KV scratch address it was captured with. A later attention call that
+    needs more scratch (more sequences) must not free that buffer: the plan is run again and checked."""
+    shared = ctx   # the session's context may have grown its scratch already: use a fresh one
+    ctx = capi.Context(0)
+    rng = np.random.default_rng(5)
+    NH, NKV, D, KV, POS = 8, 2, 128, 256, 200
+    scale = float(1.0 / np.sqrt(D))
+    q = rng.standard_normal((NH, D)).astype(np.float32)
+    kc = (rng.standard_normal((NKV, KV, D)) * 0.1).astype(np.float16)
+    vc = (rng.standard_normal((NKV, KV, D)) * 0.1).astype(np.float16)
+    qd, kcd, vcd = dev(q), dev(kc.view(np.int16)), dev(vc.view(np.int16))
+    out = torch.zeros((NH, D), dtype=torch.float32, device="cuda")
+    posd = torch.tensor([POS], dtype=torch.int32, device="cuda")
+    g = Graph(ctx)
+    t_att = g.add(capi.K_ATTN_GQA_F16, aux=g.param_block(AttnP(qd.data_ptr(), kcd.data_ptr(), vcd.data_ptr(), out.data_ptr(),
+                  posd.data_ptr(), scale, NH, NKV, D, KV)))
+    g.edge(t_att, g.add(capi.K_SIGNAL))
+    g.freeze()
+    want = checker.attn_gqa_f16(q, kc, vc, POS + 1, scale)
+    g.run(); ctx.sync()
+    assert float(np.max(np.abs(out.cpu().numpy() - want))) <= 2e-3
+    # a much larger call on the same context: 16 sequences x 32 heads, long enough for many splits
+    B, NH2, NKV2, KV2 = 16, 32, 8, 4096
+    q2 = torch.randn((B, NH2, D), device="cuda")
+    k2 = (torch.randn((B, NKV2, KV2, D), device="cuda") * 0.1).half()
+    v2 = (torch.randn((B, NKV2, KV2, D), device="cuda") * 0.1).half()
+    o2 = torch.zeros((B, NH2, D), device="cuda")
+    torch.cuda.synchronize()
+    ctx.attn_decode(q2, k2.view(torch.int16), v2.view(torch.int16), NH2, NKV2, D, KV2, KV2, B, scale, o2)
+    ctx.sync()
+    junk = [torch.full((1 << 20,), float("nan"), device="cuda") for _ in range(8)]   # reuse of freed memory would show
+    out.zero_()
+    torch.cuda.synchronize()
+    g.run(); ctx.sync()
+    assert ctx.status() == 0
+    assert float(np.max(np.abs(out.cpu().numpy() - want))) <= 2e-3
+    del junk
+    g.close()
+    ctx.close()
+    assert shared.status() == 0
