@@ -16,9 +16,12 @@ read once. Prints ONE JSON line (rank 0).
   cpu_baseline  the reference's CPU operators on this box's host cores, on a
              bounded sample (2 of the 32 layers + the output head), N=1 only
 
-With --gpus N > 1 (torchrun, one rank per GPU) every rank decodes its own
-sequence on its own replica of the model ("weak": per-GPU work fixed); value is
-the sum over ranks / the slowest rank's time.
+With --gpus N > 1 (torchrun, one rank per GPU) the headline value is the
+tensor-parallel decode of ONE sequence over the N GPUs (KV heads and matvec
+rows / columns per GPU, the partial sums exchanged through peer memory):
+"strong" scaling, total work fixed; the roofline object then gives the
+per-GPU fraction. The same run also times N independent replicas (one sequence
+per GPU, no data-path collective) and reports them under the key "replicas".
 --impl reference times only the CPU arm (rank 0), same metric and config.
 """
 import argparse
@@ -173,10 +176,10 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--parallelism", default="both", choices=["both", "tp", "replicas"],
-                    help="N > 1: replicas = one independent sequence per GPU (weak scaling, the headline value); "
-                         "tp = one sequence, the step split over the GPUs (KV heads, matvec rows / columns, exchange "
-                         "through peer memory; strong scaling); both = replicas as the headline and the tp "
-                         "measurement of the same run under the key \"tp\"")
+                    help="N > 1: tp = one sequence, the step split over the GPUs (KV heads, matvec rows / columns, exchange "
+                         "through peer memory; strong scaling; the headline value); replicas = one independent sequence "
+                         "per GPU (weak scaling); both = tp as the headline and the replica measurement of the same run "
+                         "under the key \"replicas\"")
     ap.add_argument("--layers", type=int, default=32,
                     help="number of layers (32 = the benchmark; fewer = a small case of the same kernels for profiler captures, not a benchmark number)")
     ap.add_argument("--case", default="decode", choices=["decode", "matmul-nx8", "attn-long", "moe"],
@@ -196,7 +199,7 @@ def main():
               "kv_prefill": N_PREFILL,
               "parallelism": "single GPU" if world == 1 else
                              ("tp%d (KV heads + matvec rows/columns per GPU, 2 all-reduces per layer through peer memory)" % world
-                              if args.parallelism == "tp" else "replicas x%d (independent sequences, no data-path collective)" % world),
+                              if args.parallelism != "replicas" else "replicas x%d (independent sequences, no data-path collective)" % world),
               "l2": "each step reads 6.0 GB of distinct weights and KV, far larger than L2; no flush needed"}
 
     if args.impl == "reference":
@@ -230,17 +233,16 @@ def main():
     if steps + warmup + 8 > cfg["max_kv"] - N_PREFILL:
         cfg["max_kv"] = N_PREFILL + steps + warmup + 8
     gloo = dist.new_group(backend="gloo") if world > 1 else None   # IPC handles travel as Python objects
-    modes = ["replicas"] if world == 1 else {"both": ["replicas", "tp"], "tp": ["tp"], "replicas": ["replicas"]}[args.parallelism]
+    modes = ["replicas"] if world == 1 else {"both": ["tp", "replicas"], "tp": ["tp"], "replicas": ["replicas"]}[args.parallelism]
     out = None
     for mode in modes:
         r = measure(mode == "tp", args, ctx, cfg, config, dist, gloo, rank, local_rank, world, steps, warmup)
         if out is None:
             out = r
-        else:   # the tensor-parallel measurement of the same run, beside the headline
-            out["tp"] = {"value": r["value"], "unit": r["unit"], "ms_per_step": r["ms_per_step"], "scaling": "strong",
-                         "parallelism": "tp%d: one sequence; KV heads + matvec rows/columns per GPU, 2 all-reduces per "
-                                        "layer + 1 argmax exchange per step through peer memory" % world,
-                         "e2e": r["e2e"], "roofline": r["roofline"], "gpu_launches": r["gpu_launches"]}
+        else:   # the replica measurement of the same run, beside the headline
+            out["replicas"] = {"value": r["value"], "unit": r["unit"], "ms_per_step": r["ms_per_step"], "scaling": "weak",
+                               "parallelism": "replicas x%d: one independent sequence per GPU, no data-path collective" % world,
+                               "e2e": r["e2e"], "roofline": r["roofline"], "gpu_launches": r["gpu_launches"]}
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         r = cpu_reference_arm(1, 1)
         out["cpu_baseline"] = {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")}

@@ -77,6 +77,7 @@ int fl_b200_create(int device, fl_b200_ctx **out) {
     CK(cudaMalloc(&c->status, 256));
     CK(cudaMemset(c->status, 0, 256));
     c->argmax_ticket = c->status + 1;
+    c->grid_bar = c->status + 16;        // two words of the zeroed 256-byte block
     c->attn_tickets_cap = 1024;
     CK(cudaMalloc(&c->attn_tickets, c->attn_tickets_cap * sizeof(uint32_t)));
     CK(cudaMemset(c->attn_tickets, 0, c->attn_tickets_cap * sizeof(uint32_t)));
@@ -115,7 +116,10 @@ int fl_b200_device_status(fl_b200_ctx *c, uint32_t *out) {
     uint32_t v = 0;
     CK(cudaMemcpyAsync(&v, c->status, 4, cudaMemcpyDeviceToHost, c->stream));
     CK(cudaStreamSynchronize(c->stream));
-    if (v != 0) CK(cudaMemsetAsync(c->status, 0, 4, c->stream));
+    if (v != 0) {
+        CK(cudaMemsetAsync(c->status, 0, 4, c->stream));
+        CK(cudaMemsetAsync(c->grid_bar, 0, 8, c->stream));   // a launch that gave up may have left arrivals behind
+    }
     if (out) *out = v;
     return FL_B200_OK;
 }

@@ -173,19 +173,73 @@ static int enqueue_step(fl_b200_decoder *d, cudaStream_t s, uint32_t *n_launch, 
     const float theta_scale = powf(c.rope_base, -2.0f / (float)D);
     if (mask & K_OTHER) { CK(launch_rope_table(d->d_pos, theta_scale, D, d->rope_table, s)); ++n; }
     if (mask & K_OTHER) { CK(launch_embed(d->tok_embd.fmt, d->tok_embd.w, d->d_token, E, d->xa, s, false)); ++n; }
-    for (uint32_t l = 0; l < c.n_layer; ++l) {
+    // The matvec launches of the step, by builder (the launch order is below).
+    auto mk_qkv = [&](uint32_t l) {   // RMSNorm + Q/K/V
         const Tensor *w = &d->lw[(size_t)l * 7];
-        {   // RMSNorm + Q/K/V
-            MatvecArgs a{};
-            a.n_tensors = 3;
-            a.t[0] = {w[FL_B200_T_WQ].w, d->q, nullptr, QD, w[FL_B200_T_WQ].fmt, 0};
-            a.t[1] = {w[FL_B200_T_WK].w, d->k, nullptr, KD, w[FL_B200_T_WK].fmt, 0};
-            a.t[2] = {w[FL_B200_T_WV].w, d->v, nullptr, KD, w[FL_B200_T_WV].fmt, 0};
-            a.x = d->xa; a.wnorm = d->attn_norm[l]; a.eps = c.eps; a.cols = E;
-            a.x_mode = MV_X_RMSNORM; a.status = ctx->status; a.pdl = kPdl; a.issue_late = issue_late() & 1;
+        MatvecArgs a{};
+        a.n_tensors = 3;
+        a.t[0] = {w[FL_B200_T_WQ].w, d->q, nullptr, QD, w[FL_B200_T_WQ].fmt, 0};
+        a.t[1] = {w[FL_B200_T_WK].w, d->k, nullptr, KD, w[FL_B200_T_WK].fmt, 0};
+        a.t[2] = {w[FL_B200_T_WV].w, d->v, nullptr, KD, w[FL_B200_T_WV].fmt, 0};
+        a.x = d->xa; a.wnorm = d->attn_norm[l]; a.eps = c.eps; a.cols = E;
+        a.x_mode = MV_X_RMSNORM; a.status = ctx->status; a.pdl = kPdl; a.issue_late = issue_late() & 1;
+        return a;
+    };
+    auto mk_o = [&](uint32_t l) {     // O projection + residual: xb = xa + Wo att (tensor parallel: partial sums over this
+        const Tensor *w = &d->lw[(size_t)l * 7];   // rank's columns, then the exchange adds the ranks' partials and the residual)
+        MatvecArgs a{};
+        a.n_tensors = 1;
+        a.t[0] = {w[FL_B200_T_WO].w, tp ? d->partial : d->xb, tp ? nullptr : d->xa, E, w[FL_B200_T_WO].fmt, w[FL_B200_T_WO].pitch};
+        a.x = d->att; a.cols = QD; a.x_mode = MV_X_PLAIN; a.status = ctx->status; a.pdl = kPdl;
+        a.issue_late = (issue_late() >> 4) & 1;
+        return a;
+    };
+    auto mk_gate_up = [&](uint32_t l) {   // RMSNorm + gate / up with the SwiGLU product in the epilogue: g <- silu(gate x) * (up x)
+        const Tensor *w = &d->lw[(size_t)l * 7];
+        MatvecArgs a{};
+        a.n_tensors = 2;
+        a.t[0] = {w[FL_B200_T_GATE].w, d->g, nullptr, d->F, w[FL_B200_T_GATE].fmt, 0};
+        a.t[1] = {w[FL_B200_T_UP].w, d->u, nullptr, d->F, w[FL_B200_T_UP].fmt, 0};
+        a.x = d->xb; a.wnorm = d->ffn_norm[l]; a.eps = c.eps; a.cols = E;
+        a.x_mode = MV_X_RMSNORM; a.status = ctx->status; a.pdl = kPdl;
+        // (Q8_0 streams without the fused product: the down projection then takes silu(g) * u on load)
+        a.swiglu = (w[FL_B200_T_GATE].fmt == w[FL_B200_T_UP].fmt && w[FL_B200_T_GATE].fmt != FL_B200_Q8_0) ? 1 : 0;
+        a.issue_late = (issue_late() >> 1) & 1;
+        return a;
+    };
+    auto mk_down = [&](uint32_t l, bool fused_swiglu) {   // down projection + residual: xa = xb + Wdown h
+        const Tensor *w = &d->lw[(size_t)l * 7];
+        MatvecArgs a{};
+        a.n_tensors = 1;
+        a.t[0] = {w[FL_B200_T_DOWN].w, tp ? d->partial : d->xa, tp ? nullptr : d->xb, E, w[FL_B200_T_DOWN].fmt, w[FL_B200_T_DOWN].pitch};
+        a.x = d->g; a.x2 = d->u; a.cols = d->F; a.status = ctx->status; a.pdl = kPdl;
+        a.x_mode = fused_swiglu ? MV_X_PLAIN : MV_X_SILU_MUL;
+        a.issue_late = (issue_late() >> 2) & 1;
+        return a;
+    };
+    auto mk_head = [&]() {   // output norm + head
+        MatvecArgs a{};
+        a.n_tensors = 1;
+        a.t[0] = {d->output.w, d->logits, nullptr, d->V, d->output.fmt, 0};
+        a.x = d->xa; a.wnorm = d->out_norm; a.eps = c.eps; a.cols = E;
+        a.x_mode = MV_X_RMSNORM; a.status = ctx->status; a.pdl = kPdl; a.xn_out = d->xn_final;
+        a.issue_late = (issue_late() >> 3) & 1;
+        return a;
+    };
+    // One GPU: the four matvecs between two attention launches, O -> gate|up -> down -> the next layer's Q/K/V (or the
+    // head), go out as ONE launch with grid-wide barriers between them (launch_matvec_tc_chain): the weights of the next
+    // matvec stream into shared memory while the current one drains and the next activation is built. FLB_CHAIN=0, a
+    // tensor-parallel decoder (its exchange launches sit between the matvecs) or a shape the chain does not take: one
+    // launch per matvec.
+    static const bool chain_on = !(getenv("FLB_CHAIN") && getenv("FLB_CHAIN")[0] == '0');
+    bool qkv_done = false;   // the Q/K/V of the coming layer already went out with the previous layer's chain
+    for (uint32_t l = 0; l < c.n_layer; ++l) {
+        if (!qkv_done) {
+            MatvecArgs a = mk_qkv(l);
             take_pending(a);
             if (mask & K_MATVEC) { if (int rc = do_matvec(a)) return rc; ++n; }
         }
+        qkv_done = false;
         {   // RoPE on q and k, the f16 append of k and v, and the attention itself: one kernel
             AttnArgs a{};
             a.rope_k = d->k; a.rope_v = d->v; a.k_append = d->kc[l]; a.v_append = d->vc[l];
@@ -198,50 +252,26 @@ static int enqueue_step(fl_b200_decoder *d, cudaStream_t s, uint32_t *n_launch, 
             if (d->trace && mask == K_ALL) a.trace = d->trace + 4 * (size_t)n;
             if (mask & K_ATTN) { CK(attn_make_maps(a)); CK(launch_attn_decode(a, s)); ++n; }
         }
-        {   // O projection + residual: xb = xa + Wo att (tensor parallel: partial sums over this rank's
-            // columns, then the exchange adds the ranks' partials and the residual)
-            MatvecArgs a{};
-            a.n_tensors = 1;
-            a.t[0] = {w[FL_B200_T_WO].w, tp ? d->partial : d->xb, tp ? nullptr : d->xa, E, w[FL_B200_T_WO].fmt,
-                      w[FL_B200_T_WO].pitch};
-            a.x = d->att; a.cols = QD; a.x_mode = MV_X_PLAIN; a.status = ctx->status; a.pdl = kPdl;
-            a.issue_late = (issue_late() >> 4) & 1;
-            if (mask & K_MATVEC) { if (int rc = do_matvec(a)) return rc; ++n; }
-            if (tp && (mask & K_COMM)) { if (int rc = do_allreduce(d->xa, d->xb)) return rc; ++n; }
+        MatvecArgs ao = mk_o(l), ag = mk_gate_up(l);
+        d->fused_swiglu = ag.swiglu != 0;
+        MatvecArgs ad = mk_down(l, d->fused_swiglu);
+        if (chain_on && !tp && (mask & K_MATVEC)) {
+            MatvecArgs ch[4] = {ao, ag, ad, l + 1 < c.n_layer ? mk_qkv(l + 1) : mk_head()};
+            if (d->trace && mask == K_ALL) ch[0].trace = d->trace + 4 * (size_t)n;
+            ch[0].grid_bar = ctx->grid_bar;
+            const cudaError_t e = launch_matvec_tc_chain(ch, 4, ctx->sms, s);
+            if (e == cudaSuccess) { ++n; qkv_done = true; continue; }
+            if (e != cudaErrorNotSupported) return cuda_err(e, "matvec chain launch");
         }
-        {   // RMSNorm + gate / up with the SwiGLU product in the epilogue: g <- silu(gate x) * (up x)
-            MatvecArgs a{};
-            a.n_tensors = 2;
-            a.t[0] = {w[FL_B200_T_GATE].w, d->g, nullptr, d->F, w[FL_B200_T_GATE].fmt, 0};
-            a.t[1] = {w[FL_B200_T_UP].w, d->u, nullptr, d->F, w[FL_B200_T_UP].fmt, 0};
-            a.x = d->xb; a.wnorm = d->ffn_norm[l]; a.eps = c.eps; a.cols = E;
-            a.x_mode = MV_X_RMSNORM; a.status = ctx->status; a.pdl = kPdl;
-            // (Q8_0 streams without the fused product: the down projection then takes silu(g) * u on load)
-            a.swiglu = (w[FL_B200_T_GATE].fmt == w[FL_B200_T_UP].fmt && w[FL_B200_T_GATE].fmt != FL_B200_Q8_0) ? 1 : 0;
-            a.issue_late = (issue_late() >> 1) & 1;
-            take_pending(a);
-            if (mask & K_MATVEC) { if (int rc = do_matvec(a)) return rc; ++n; }
-            d->fused_swiglu = a.swiglu != 0;
-        }
-        {   // down projection + residual: xa = xb + Wdown h
-            MatvecArgs a{};
-            a.n_tensors = 1;
-            a.t[0] = {w[FL_B200_T_DOWN].w, tp ? d->partial : d->xa, tp ? nullptr : d->xb, E, w[FL_B200_T_DOWN].fmt,
-                      w[FL_B200_T_DOWN].pitch};
-            a.x = d->g; a.x2 = d->u; a.cols = d->F; a.status = ctx->status; a.pdl = kPdl;
-            a.x_mode = d->fused_swiglu ? MV_X_PLAIN : MV_X_SILU_MUL;
-            a.issue_late = (issue_late() >> 2) & 1;
-            if (mask & K_MATVEC) { if (int rc = do_matvec(a)) return rc; ++n; }
-            if (tp && (mask & K_COMM)) { if (int rc = do_allreduce(d->xb, d->xa)) return rc; ++n; }
-        }
+        if (mask & K_MATVEC) { if (int rc = do_matvec(ao)) return rc; ++n; }
+        if (tp && (mask & K_COMM)) { if (int rc = do_allreduce(d->xa, d->xb)) return rc; ++n; }
+        take_pending(ag);
+        if (mask & K_MATVEC) { if (int rc = do_matvec(ag)) return rc; ++n; }
+        if (mask & K_MATVEC) { if (int rc = do_matvec(ad)) return rc; ++n; }
+        if (tp && (mask & K_COMM)) { if (int rc = do_allreduce(d->xb, d->xa)) return rc; ++n; }
     }
-    {   // output norm + head
-        MatvecArgs a{};
-        a.n_tensors = 1;
-        a.t[0] = {d->output.w, d->logits, nullptr, d->V, d->output.fmt, 0};
-        a.x = d->xa; a.wnorm = d->out_norm; a.eps = c.eps; a.cols = E;
-        a.x_mode = MV_X_RMSNORM; a.status = ctx->status; a.pdl = kPdl; a.xn_out = d->xn_final;
-        a.issue_late = (issue_late() >> 3) & 1;
+    if (!qkv_done) {
+        MatvecArgs a = mk_head();
         take_pending(a);
         if (mask & K_MATVEC) { if (int rc = do_matvec(a)) return rc; ++n; }
     }

@@ -56,6 +56,8 @@ struct MatvecArgs {
                           // before the dependency wait (for launches whose CTAs only become resident when the previous
                           // kernel's CTAs leave, so that nothing is gained by requesting early)
     unsigned long long *trace;   // optional 4-entry timeline record of this launch (diagnostics)
+    uint32_t *grid_bar;          // chained launches (launch_matvec_tc_chain): two zeroed words of device memory, the
+                                 // state of the grid-wide barrier; one launch at a time may use them
     int expert_ids_ready;        // 1: the expert ids were complete before the previous kernel started, so the first
                                  // weight stages are requested before the dependency wait, as for a plain tensor
     // Tensor parallel: the activation is the sum of the ranks' partial vectors that an exchange launch
@@ -80,6 +82,10 @@ cudaError_t launch_matvec(const MatvecArgs &a, int sms, cudaStream_t stream);
 // Q4_K / Q6_K launches that qualify run on the tensor-core streaming kernel (matvec_tc.cu).
 bool matvec_tc_eligible(const MatvecArgs &a);
 cudaError_t launch_matvec_tc(const MatvecArgs &a, int sms, cudaStream_t stream);
+// n (1..4) matvecs in ONE launch, each consuming what the one before it wrote (O -> gate|up -> down -> next Q/K/V),
+// with grid-wide barriers in between and the weights of the next phase streaming meanwhile. cudaErrorNotSupported
+// when a phase does not qualify: launch them one by one then. args[0].grid_bar names the barrier state.
+cudaError_t launch_matvec_tc_chain(const MatvecArgs *args, int n, int sms, cudaStream_t stream);
 cudaError_t matvec_tc_init(void);
 // Q4_K launches that qualify run on the integer tensor-core kernel (matvec_mma.cu).
 bool matvec_mma_eligible(const MatvecArgs &a);

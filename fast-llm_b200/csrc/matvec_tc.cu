@@ -34,6 +34,7 @@
 #include "kernels.h"
 
 #include <cuda.h>
+#include <algorithm>
 #include <cstdlib>
 #include <cstring>
 
@@ -42,12 +43,12 @@ namespace flb {
 namespace {
 
 constexpr int kCW = 8;                          // consumer warps per group (one per super-block of a segment)
-constexpr uint32_t kSeg4 = 8 * 144, kSeg6 = 8 * 210;
-// Row pitch of a stage in shared memory. Q4_K: + 16 bytes so that the 128-bit loads of lanes
-// (g, t) and (g + 1, t) fall into different bank groups. Q6_K: the natural 1680 bytes (105 x 16:
-// odd), which together with the per-t rotation of the word order makes the 32-bit loads conflict free.
-constexpr uint32_t kPitch4 = kSeg4 + 16, kPitch6 = kSeg6;
-constexpr uint32_t kSlot4 = 16 * kPitch4, kSlot6 = 16 * kPitch6;
+constexpr uint32_t kSeg4 = 8 * 144, kSeg6 = 8 * 210, kSeg8 = 64 * 34;
+// Row pitch of a stage in shared memory: what a 2-D TMA box of 16 rows x one segment gives. Q6_K: 1680 bytes
+// (105 x 16: odd), which together with the per-t rotation of the word order makes the 32-bit loads conflict
+// free. Q4_K: 1152 bytes; the six 128-bit loads of a block see a two-way conflict, which is noise.
+constexpr uint32_t kPitch4 = kSeg4, kPitch6 = kSeg6, kPitch8 = kSeg8 + 16;   // Q8_0 (one bulk copy per row): 548 words = 4 mod 32
+constexpr uint32_t kSlot4 = 16 * kPitch4, kSlot6 = 16 * kPitch6, kSlot8 = 16 * kPitch8;
 // 256-column blocks a half-warp of the prologue converts (bounds the column count: see matvec_tc_eligible)
 __host__ __device__ constexpr int max_blk_per_half_warp(int groups) { return groups == 1 ? 4 : 2; }
 
@@ -72,6 +73,13 @@ __device__ __forceinline__ void sts64(uint32_t addr, uint32_t a, uint32_t b) {
 __device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+// 2-D tiled TMA load into shared memory; x counts 8-byte elements (a multiple of 2: the copy starts 16-byte aligned).
+__device__ __forceinline__ void tma_box(uint32_t dst, const CUtensorMap *map, uint32_t x, uint32_t y, uint64_t *bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+        "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
+        : "memory");
+}
 // All threads of the prologue (every warp but the producer) meet here.
 __device__ __forceinline__ void prologue_barrier(uint32_t nthreads) {
     asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
@@ -82,6 +90,25 @@ __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// (a & b) | c in one instruction; b and c are constants the compiler keeps in registers
+__device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t d;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+// h - off for both halves (exact: the operands are small integers)
+__device__ __forceinline__ uint32_t hsub2_u32(uint32_t h, __half2 off) {
+    const __half2 r = __hsub2(*reinterpret_cast<const __half2 *>(&h), off);
+    return *reinterpret_cast<const uint32_t *>(&r);
+}
+// The common case of a wait: the phase is already complete. The bounded polling loop stays out of line.
+__device__ __noinline__ bool mbar_wait_slow(uint64_t *bar, uint32_t parity, uint32_t *status) {
+    return mbar_wait_bounded(bar, parity, status);
+}
+__device__ __forceinline__ bool mbar_wait_fast(uint64_t *bar, uint32_t parity, uint32_t *status) {
+    if (mbar_try_wait(bar, parity)) return true;
+    return mbar_wait_slow(bar, parity, status);
 }
 // byte K of w as a float without the conversion pipe (the byte under 0x4B000000 is 2^23 + byte)
 template <int K>
@@ -105,6 +132,7 @@ __device__ __forceinline__ uint32_t x6_off(uint32_t s, uint32_t lane8, uint32_t 
 }
 
 struct TcTensor {
+    CUtensorMap map;               // the packed tensor as [rows][pitch / 8] 8-byte elements; box = 16 (SwiGLU: 8) rows x one segment
     const uint8_t *w;
     float *y;
     const float *resid;
@@ -112,17 +140,30 @@ struct TcTensor {
     int fmt;
 };
 
-struct TcArgs {
-    TcTensor t[4];
+// One matvec of a launch. A launch is a sequence of up to four phases that depend on one another
+// (phase p + 1 reads as its activation what phase p wrote): O -> gate|up -> down -> next Q/K/V.
+struct TcPhase {
+    TcTensor t[3];
     int n_tensors;
     const float *x, *x2, *wnorm;
     float eps;
     uint32_t cols;
     int x_mode, accumulate, swiglu;
-    uint32_t total_units, nslots, slot_bytes;
+    uint32_t total_units;
     int use_q4, use_q6;
-    uint32_t *status;
     float *xn_out;
+};
+
+// Grid-wide barrier between the phases of a launch: an arrival counter and a generation number in
+// global memory; the counter returns to zero by itself, so the state serves every launch.
+struct GridBar { uint32_t count, gen; };
+
+struct TcArgs {
+    TcPhase ph[4];
+    int n_phases;
+    uint32_t nslots, slot_bytes, ring_off;   // ring_off: bytes from the start of shared memory to the ring
+    uint32_t *status;
+    GridBar *bar;                            // n_phases > 1
     unsigned long long *trace;
 };
 
@@ -131,25 +172,31 @@ struct TcSmem {
     uint64_t *red_full, *red_empty;   // [2]
     float *red;                    // [2][groups * 8][16]
     float *ssq;                    // per-warp sums of squares of the prologue
+    uint8_t *zero;                 // 16 zero bytes (the B operand of lanes that feed no column)
     float *xs;                     // [nblk] block scale 2^e
     float *s4;                     // [nblk][8] sums of the 32-column sub-blocks, in units of the block scale
     uint8_t *x4, *x6;              // [nblk][1024]
     uint8_t *ring;
 };
 
-__host__ __device__ inline size_t tc_fixed_bytes(uint32_t cols, bool q4, bool q6, uint32_t nslots, int groups) {
-    const size_t nblk = cols / 256;
+// Shared memory in front of the ring: barriers and reduction buffers (the same for every phase), then
+// the activation of the current phase. The ring starts at the same offset in every phase.
+__host__ __device__ inline size_t tc_head_bytes(uint32_t nslots, int groups) {
     size_t n = (size_t)nslots * 16 + 32;                  // barriers
     n += (size_t)2 * groups * kCW * 16 * 4;              // red
-    n += 33 * 4 + 12;                                     // ssq + padding
-    n += nblk * 4;                                        // xs
+    n += 36 * 4 + 16;                                     // ssq, 16 zero bytes
+    return (n + 15) & ~(size_t)15;
+}
+__host__ __device__ inline size_t tc_x_bytes(uint32_t cols, bool q4, bool q6) {
+    const size_t nblk = cols / 256;
+    size_t n = (nblk * 4 + 15) & ~(size_t)15;             // xs
     if (q4) n += nblk * 32 + nblk * 1024;
     if (q6) n += nblk * 1024;
-    return n + 256;                                       // alignment slack
+    return n;
 }
 
 template <int G>
-__device__ __forceinline__ TcSmem tc_carve(uint8_t *base, uint32_t cols, bool q4, bool q6, uint32_t nslots) {
+__device__ __forceinline__ TcSmem tc_carve(uint8_t *base, uint32_t cols, bool q4, bool q6, uint32_t nslots, uint32_t ring_off) {
     TcSmem s;
     const uint32_t nblk = cols / 256;
     uint8_t *p = base;
@@ -158,19 +205,19 @@ __device__ __forceinline__ TcSmem tc_carve(uint8_t *base, uint32_t cols, bool q4
     s.red_full = (uint64_t *)p; p += 16;
     s.red_empty = (uint64_t *)p; p += 16;
     s.red = (float *)p; p += 2 * G * kCW * 16 * 4;
-    s.ssq = (float *)p; p += 33 * 4 + 12;
-    s.xs = (float *)p; p += nblk * 4;
-    p = (uint8_t *)(((uintptr_t)p + 15) & ~(uintptr_t)15);
+    s.ssq = (float *)p; p += 36 * 4;
+    s.zero = p;
+    p = base + tc_head_bytes(nslots, G);
+    s.xs = (float *)p; p += (nblk * 4 + 15) & ~15u;
     s.s4 = nullptr; s.x4 = s.x6 = nullptr;
     if (q4) { s.s4 = (float *)p; p += nblk * 32; s.x4 = p; p += (size_t)nblk * 1024; }
     if (q6) { s.x6 = p; p += (size_t)nblk * 1024; }
-    p = (uint8_t *)(((uintptr_t)p + 127) & ~(uintptr_t)127);
-    s.ring = p;
+    s.ring = base + ring_off;
     return s;
 }
 
 // Which tensor and which first row a unit covers (non-SwiGLU launches).
-__device__ __forceinline__ int unit_tensor(const TcArgs &a, uint32_t u) {
+__device__ __forceinline__ int unit_tensor(const TcPhase &a, uint32_t u) {
     int ti = 0;
 #pragma unroll 1
     for (; ti < a.n_tensors - 1; ++ti)
@@ -180,29 +227,42 @@ __device__ __forceinline__ int unit_tensor(const TcArgs &a, uint32_t u) {
 
 // ---- per-super-block math ------------------------------------------------------------------
 
-// Q4_K: rows g (r0) and g + 8 (r1) of super-block `blk_addr` offsets; chunk c = t. Returns the two rows'
-// contributions in units of the block's activation scale.
-__device__ __forceinline__ void q4k_block(uint32_t r0, uint32_t r1, uint32_t t, bool has_b, uint32_t xaddr, float2 sx,
+// Q4_K: rows g (r0) and g + 8 (r1) of one super-block; chunk c = t. Returns the two rows' contributions in
+// units of the block's activation scale. All shared-memory loads of the block are issued first (they are
+// volatile asm statements, which the compiler keeps in program order), so that their latency overlaps.
+// xaddr: this lane's 16-byte B slot of word 0 (lanes that feed no column of B point at 16 zero bytes and
+// use a stride of 0).
+__device__ __forceinline__ void q4k_block(uint32_t r0, uint32_t r1, uint32_t t, uint32_t xaddr, uint32_t xstride, float2 sx,
                                           float &out0, float &out1) {
+    const uint4 wa0 = lds128(r0 + 16 + 32 * t), wa1 = lds128(r1 + 16 + 32 * t);
+    uint4 bx[8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) bx[j] = lds128(xaddr + j * xstride);
+    const uint4 wb0 = lds128(r0 + 32 + 32 * t), wb1 = lds128(r1 + 32 + 32 * t);
+#pragma unroll
+    for (int j = 4; j < 8; ++j) bx[j] = lds128(xaddr + j * xstride);
     const uint4 h0 = lds128(r0), h1 = lds128(r1);
-    const uint4 wa0 = lds128(r0 + 16 + 32 * t), wb0 = lds128(r0 + 32 + 32 * t);
-    const uint4 wa1 = lds128(r1 + 16 + 32 * t), wb1 = lds128(r1 + 32 + 32 * t);
     float cL[2][4], cH[2][4];
 #pragma unroll
     for (int i = 0; i < 2; ++i)
 #pragma unroll
         for (int k = 0; k < 4; ++k) cL[i][k] = cH[i][k] = 0.f;
-    constexpr uint32_t M = 0x00F000F0u, K = 0x54005400u;   // f16 0x54xx: 64 + (mantissa bits 4..7)
+    // A quant lands in the mantissa of a constant: bits 0..3 under 0x6400 give 1024 + q, bits 4..7 under 0x5400 give
+    // 64 + q; the constant is taken off again exactly (f16 subtraction on the other pipe). Bytes 1 and 3 come
+    // down by one shift. Five logic operations and four subtractions per 8 weights.
+    const uint32_t ML = 0x000F000Fu, KL = 0x64006400u, MH = 0x00F000F0u, KH = 0x54005400u;
+    const __half2 oL = __floats2half2_rn(1024.f, 1024.f), oH = __floats2half2_rn(64.f, 64.f);
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-        uint4 bx = make_uint4(0u, 0u, 0u, 0u);
-        if (has_b) bx = lds128(xaddr + j * 128);
         const uint32_t W0 = j < 4 ? word_of(wa0, j) : word_of(wb0, j - 4);
         const uint32_t W1 = j < 4 ? word_of(wa1, j) : word_of(wb1, j - 4);
+        const uint32_t V0 = W0 >> 8, V1 = W1 >> 8;
         // low nibbles (sub-block 2t): bytes 0, 2 -> k-slots 2t, 2t+1; bytes 1, 3 -> k-slots 2t+8, 2t+9
-        mma16816(cL[j & 1], ((W0 << 4) & M) | K, ((W1 << 4) & M) | K, ((W0 >> 4) & M) | K, ((W1 >> 4) & M) | K, bx.x, bx.y);
+        mma16816(cL[j & 1], hsub2_u32(and_or(W0, ML, KL), oL), hsub2_u32(and_or(W1, ML, KL), oL),
+                 hsub2_u32(and_or(V0, ML, KL), oL), hsub2_u32(and_or(V1, ML, KL), oL), bx[j].x, bx[j].y);
         // high nibbles (sub-block 2t+1)
-        mma16816(cH[j & 1], (W0 & M) | K, (W1 & M) | K, ((W0 >> 8) & M) | K, ((W1 >> 8) & M) | K, bx.z, bx.w);
+        mma16816(cH[j & 1], hsub2_u32(and_or(W0, MH, KH), oH), hsub2_u32(and_or(W1, MH, KH), oH),
+                 hsub2_u32(and_or(V0, MH, KH), oH), hsub2_u32(and_or(V1, MH, KH), oH), bx[j].z, bx[j].w);
     }
     // 6-bit scales / mins of sub-blocks 2t, 2t+1 (packing: fl_q4k_scale_min, src/runtime/quants.h:121-129)
     const uint32_t sh = 16u * (t & 1u);
@@ -218,8 +278,7 @@ __device__ __forceinline__ void q4k_block(uint32_t r0, uint32_t r1, uint32_t t, 
         const float d = h2f_bits((uint16_t)(hdr.x & 0xFFFFu)), dmin = h2f_bits((uint16_t)(hdr.x >> 16));
         const float tl = (cL[0][2 * r] + cL[1][2 * r]) + (cL[0][2 * r + 1] + cL[1][2 * r + 1]);
         const float th = (cH[0][2 * r] + cH[1][2 * r]) + (cH[0][2 * r + 1] + cH[1][2 * r + 1]);
-        // the unpacked values are 64 + q: take 64 * (sum of the sub-block's activations) off again
-        const float q = u8f<0>(sc) * fmaf(-64.f, s0, tl) + u8f<1>(sc) * fmaf(-64.f, s1, th);
+        const float q = u8f<0>(sc) * tl + u8f<1>(sc) * th;
         const float m = u8f<0>(mn) * s0 + u8f<1>(mn) * s1;
         (r ? out1 : out0) = d * q - dmin * m;
     }
@@ -227,59 +286,40 @@ __device__ __forceinline__ void q4k_block(uint32_t r0, uint32_t r1, uint32_t t, 
 
 // Q6_K: lane column t = 2 hf + hq works on the 16-byte runs ql[64 hf + 16 hq ..], ql[64 hf + 32 + 16 hq ..],
 // qh[32 hf + 16 hq ..] of rows g and g + 8 (q = nibble | two high bits << 4, value d * sc * (q - 32);
-// fl_dot_row_q6_K, src/runtime/quants.h:194-230). ODD: the block starts 2 bytes past a word boundary.
+// fl_dot_row_q6_K, src/runtime/quants.h:194-230). ODD: the block starts 2 bytes past a word boundary
+// (r0, r1 are then the word-aligned addresses 2 bytes in front of it). Loads first, as for Q4_K.
 template <bool ODD>
-__device__ __forceinline__ void q6k_block(uint32_t r0, uint32_t r1, uint32_t t, bool has_b, uint32_t xaddr, float &out0,
+__device__ __forceinline__ void q6k_block(uint32_t r0, uint32_t r1, uint32_t t, uint32_t xaddr, uint32_t xstride, float &out0,
                                           float &out1) {
     const uint32_t hf = t >> 1, hq = t & 1u;
-    float c[4][4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i)
-#pragma unroll
-        for (int k = 0; k < 4; ++k) c[i][k] = 0.f;
-    const __half2 off = __floats2half2_rn(1056.f, 1056.f);
-    const uint32_t oa = 64 * hf + 16 * hq, oh = 128 + 32 * hf + 16 * hq;   // byte offsets in the block (ODD: r0, r1 are 2 less)
+    const uint32_t oa = 64 * hf + 16 * hq, oh = 128 + 32 * hf + 16 * hq;   // byte offsets in the block
+    uint32_t wa[2][4], wb[2][4], wh[2][4];
+    uint4 bA[4], bB[4];
 #pragma unroll
     for (int s = 0; s < 4; ++s) {
         const uint32_t js = ((uint32_t)s + t) & 3u;
-        uint4 bA = make_uint4(0u, 0u, 0u, 0u), bB = make_uint4(0u, 0u, 0u, 0u);
-        if (has_b) { bA = lds128(xaddr + s * 256); bB = lds128(xaddr + s * 256 + 128); }
-        uint32_t a_[2][8];   // per row: A registers (k-slots 2t.. , 2t+8..) of the four groups
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
             const uint32_t rb = r ? r1 : r0;
-            uint32_t wa, wb, wh;
             if (ODD) {
-                wa = __byte_perm(lds32(rb + oa + 4 * js), lds32(rb + oa + 4 * js + 4), 0x5432u);
-                wb = __byte_perm(lds32(rb + oa + 32 + 4 * js), lds32(rb + oa + 36 + 4 * js), 0x5432u);
-                wh = __byte_perm(lds32(rb + oh + 4 * js), lds32(rb + oh + 4 * js + 4), 0x5432u);
+                const uint32_t a0 = lds32(rb + oa + 4 * js), a1 = lds32(rb + oa + 4 * js + 4);
+                const uint32_t b0 = lds32(rb + oa + 32 + 4 * js), b1 = lds32(rb + oa + 36 + 4 * js);
+                const uint32_t h0 = lds32(rb + oh + 4 * js), h1 = lds32(rb + oh + 4 * js + 4);
+                wa[r][s] = __byte_perm(a0, a1, 0x5432u);
+                wb[r][s] = __byte_perm(b0, b1, 0x5432u);
+                wh[r][s] = __byte_perm(h0, h1, 0x5432u);
             } else {
-                wa = lds32(rb + oa + 4 * js);
-                wb = lds32(rb + oa + 32 + 4 * js);
-                wh = lds32(rb + oh + 4 * js);
-            }
-            uint32_t q[4];
-            q[0] = (wa & 0x0F0F0F0Fu) | ((wh << 4) & 0x30303030u);
-            q[1] = (wb & 0x0F0F0F0Fu) | ((wh << 2) & 0x30303030u);
-            q[2] = ((wa >> 4) & 0x0F0F0F0Fu) | (wh & 0x30303030u);
-            q[3] = ((wb >> 4) & 0x0F0F0F0Fu) | ((wh >> 2) & 0x30303030u);
-#pragma unroll
-            for (int gq = 0; gq < 4; ++gq) {
-                // bytes 0, 2 / 1, 3 under 0x64: f16 1024 + q; minus 1056 is q - 32, exact
-                const uint32_t e02 = __byte_perm(q[gq], 0x64646464u, 0x4240u), e13 = __byte_perm(q[gq], 0x64646464u, 0x4341u);
-                __half2 h02 = *reinterpret_cast<const __half2 *>(&e02), h13 = *reinterpret_cast<const __half2 *>(&e13);
-                h02 = __hsub2(h02, off);
-                h13 = __hsub2(h13, off);
-                a_[r][2 * gq] = *reinterpret_cast<const uint32_t *>(&h02);
-                a_[r][2 * gq + 1] = *reinterpret_cast<const uint32_t *>(&h13);
+                wa[r][s] = lds32(rb + oa + 4 * js);
+                wb[r][s] = lds32(rb + oa + 32 + 4 * js);
+                wh[r][s] = lds32(rb + oh + 4 * js);
             }
         }
-        mma16816(c[0], a_[0][0], a_[1][0], a_[0][1], a_[1][1], bA.x, bA.y);
-        mma16816(c[1], a_[0][2], a_[1][2], a_[0][3], a_[1][3], bA.z, bA.w);
-        mma16816(c[2], a_[0][4], a_[1][4], a_[0][5], a_[1][5], bB.x, bB.y);
-        mma16816(c[3], a_[0][6], a_[1][6], a_[0][7], a_[1][7], bB.z, bB.w);
+        bA[s] = lds128(xaddr + s * 2 * xstride);
+        bB[s] = lds128(xaddr + s * 2 * xstride + xstride);
     }
     // scales: int8 sc[8 hf + 2 gq + hq]; d at byte 208
+    uint32_t sw[2];
+    float dd[2];
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
         const uint32_t rb = r ? r1 : r0;
@@ -293,19 +333,128 @@ __device__ __forceinline__ void q6k_block(uint32_t r0, uint32_t r1, uint32_t t, 
             lo = lds32(ps);
             hi = lds32(ps + 4);
         }
-        const uint32_t sw = __byte_perm(lo, hi, hq ? 0x7531u : 0x6420u) ^ 0x80808080u;   // s + 128 as unsigned bytes
-        const float d = h2f_bits((uint16_t)lds16(rb + (ODD ? 2u : 0u) + 208));
-        float v = (u8f<0>(sw) - 128.f) * (c[0][2 * r] + c[0][2 * r + 1]);
-        v += (u8f<1>(sw) - 128.f) * (c[1][2 * r] + c[1][2 * r + 1]);
-        v += (u8f<2>(sw) - 128.f) * (c[2][2 * r] + c[2][2 * r + 1]);
-        v += (u8f<3>(sw) - 128.f) * (c[3][2 * r] + c[3][2 * r + 1]);
-        (r ? out1 : out0) = d * v;
+        sw[r] = __byte_perm(lo, hi, hq ? 0x7531u : 0x6420u) ^ 0x80808080u;   // s + 128 as unsigned bytes
+        dd[r] = h2f_bits((uint16_t)lds16(rb + (ODD ? 2u : 0u) + 208));
+    }
+    float c[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int k = 0; k < 4; ++k) c[i][k] = 0.f;
+    const __half2 off = __floats2half2_rn(1056.f, 1056.f);
+#pragma unroll
+    for (int s = 0; s < 4; ++s) {
+        uint32_t a_[2][8];   // per row: A registers (k-slots 2t.. , 2t+8..) of the four groups
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            const uint32_t a = wa[r][s], b = wb[r][s], h = wh[r][s];
+            uint32_t q[4];
+            q[0] = (a & 0x0F0F0F0Fu) | ((h << 4) & 0x30303030u);
+            q[1] = (b & 0x0F0F0F0Fu) | ((h << 2) & 0x30303030u);
+            q[2] = ((a >> 4) & 0x0F0F0F0Fu) | (h & 0x30303030u);
+            q[3] = ((b >> 4) & 0x0F0F0F0Fu) | ((h >> 2) & 0x30303030u);
+#pragma unroll
+            for (int gq = 0; gq < 4; ++gq) {
+                // bytes 0, 2 / 1, 3 under 0x64: f16 1024 + q; minus 1056 is q - 32, exact
+                const uint32_t e02 = __byte_perm(q[gq], 0x64646464u, 0x4240u), e13 = __byte_perm(q[gq], 0x64646464u, 0x4341u);
+                __half2 h02 = *reinterpret_cast<const __half2 *>(&e02), h13 = *reinterpret_cast<const __half2 *>(&e13);
+                h02 = __hsub2(h02, off);
+                h13 = __hsub2(h13, off);
+                a_[r][2 * gq] = *reinterpret_cast<const uint32_t *>(&h02);
+                a_[r][2 * gq + 1] = *reinterpret_cast<const uint32_t *>(&h13);
+            }
+        }
+        mma16816(c[0], a_[0][0], a_[1][0], a_[0][1], a_[1][1], bA[s].x, bA[s].y);
+        mma16816(c[1], a_[0][2], a_[1][2], a_[0][3], a_[1][3], bA[s].z, bA[s].w);
+        mma16816(c[2], a_[0][4], a_[1][4], a_[0][5], a_[1][5], bB[s].x, bB[s].y);
+        mma16816(c[3], a_[0][6], a_[1][6], a_[0][7], a_[1][7], bB[s].z, bB[s].w);
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        float v = (u8f<0>(sw[r]) - 128.f) * (c[0][2 * r] + c[0][2 * r + 1]);
+        v += (u8f<1>(sw[r]) - 128.f) * (c[1][2 * r] + c[1][2 * r + 1]);
+        v += (u8f<2>(sw[r]) - 128.f) * (c[2][2 * r] + c[2][2 * r + 1]);
+        v += (u8f<3>(sw[r]) - 128.f) * (c[3][2 * r] + c[3][2 * r + 1]);
+        (r ? out1 : out0) = dd[r] * v;
+    }
+}
+
+// Q8_0 (blocks of 32 int8 with one f16 d, 34 bytes; fl_dot_row_q8_0, src/runtime/quants.h:132-142): the 256
+// columns of warp w are blocks 8 w .. 8 w + 7 of the segment; lane column t takes blocks 2 t and 2 t + 1, 68 bytes
+// from `r0` / `r1` (4-byte aligned). The first block's quants start 2 bytes into a word and are realigned with
+// byte permutes; the second block's are aligned. An int8 s becomes f16 through (s ^ 0x80) under 0x64: 1024 + 128 + s,
+// minus 1152, exact. The activation uses the Q4_K layout (64 consecutive columns per lane column, words of 4).
+__device__ __forceinline__ void q8_0_block(uint32_t r0, uint32_t r1, uint32_t xaddr, uint32_t xstride, float &out0, float &out1) {
+    uint32_t w0[17], w1[17];
+#pragma unroll
+    for (int i = 0; i < 17; ++i) { w0[i] = lds32(r0 + 4 * i); w1[i] = lds32(r1 + 4 * i); }
+    uint4 bx[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) bx[j] = lds128(xaddr + j * xstride);
+    float cA[2][4], cB[2][4];
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int k = 0; k < 4; ++k) cA[i][k] = cB[i][k] = 0.f;
+    const __half2 off = __floats2half2_rn(1152.f, 1152.f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const uint32_t a0 = __byte_perm(w0[j], w0[j + 1], 0x5432u) ^ 0x80808080u, a1 = __byte_perm(w1[j], w1[j + 1], 0x5432u) ^ 0x80808080u;
+        const uint32_t b0 = w0[9 + j] ^ 0x80808080u, b1 = w1[9 + j] ^ 0x80808080u;
+        mma16816(cA[j & 1], hsub2_u32(__byte_perm(a0, 0x64646464u, 0x4240u), off), hsub2_u32(__byte_perm(a1, 0x64646464u, 0x4240u), off),
+                 hsub2_u32(__byte_perm(a0, 0x64646464u, 0x4341u), off), hsub2_u32(__byte_perm(a1, 0x64646464u, 0x4341u), off), bx[j].x, bx[j].y);
+        mma16816(cB[j & 1], hsub2_u32(__byte_perm(b0, 0x64646464u, 0x4240u), off), hsub2_u32(__byte_perm(b1, 0x64646464u, 0x4240u), off),
+                 hsub2_u32(__byte_perm(b0, 0x64646464u, 0x4341u), off), hsub2_u32(__byte_perm(b1, 0x64646464u, 0x4341u), off), bx[j].z, bx[j].w);
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const uint32_t *w = r ? w1 : w0;
+        const float dA = h2f_bits((uint16_t)(w[0] & 0xFFFFu)), dB = h2f_bits((uint16_t)(w[8] >> 16));
+        const float ta = (cA[0][2 * r] + cA[1][2 * r]) + (cA[0][2 * r + 1] + cA[1][2 * r + 1]);
+        const float tb = (cB[0][2 * r] + cB[1][2 * r]) + (cB[0][2 * r + 1] + cB[1][2 * r + 1]);
+        (r ? out1 : out0) = dA * ta + dB * tb;
+    }
+}
+
+// ---- grid barrier --------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t *p) {
+    uint32_t v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ uint32_t atom_add_release_gpu(uint32_t *p, uint32_t v) {
+    uint32_t old;
+    asm volatile("atom.add.release.gpu.global.u32 %0, [%1], %2;" : "=r"(old) : "l"(p), "r"(v) : "memory");
+    return old;
+}
+// One thread per CTA. All CTAs of the launch are resident (one per SM, grid <= SM count; no kernel that
+// could hold an SM depends on this one), so every arrival comes. The wait is bounded all the same: after
+// about a second it records ST_WAIT_TIMEOUT and gives up.
+__device__ __forceinline__ bool grid_barrier(GridBar *b, uint32_t nblocks, uint32_t *status) {
+    const uint32_t gen = ld_acquire_gpu(&b->gen);          // cannot advance before this CTA has arrived
+    const uint32_t old = atom_add_release_gpu(&b->count, 1u);
+    if (old == nblocks - 1u) {
+        b->count = 0u;                                     // ordered before the release below
+        atom_add_release_gpu(&b->gen, 1u);
+        return true;
+    }
+    if (ld_acquire_gpu(&b->gen) != gen) return true;
+    const uint64_t t0 = globaltimer_ns();
+    for (;;) {
+        for (int i = 0; i < 16; ++i)
+            if (ld_acquire_gpu(&b->gen) != gen) return true;
+        if (globaltimer_ns() - t0 > 1000000000ull) {
+            atomicCAS(status, ST_OK, ST_WAIT_TIMEOUT);
+            return false;
+        }
     }
 }
 
 // ---- the kernel ----------------------------------------------------------------------------
 // Warps: G groups of 8 consumer warps (group i takes stages i, i + G, ...), then the producer warp,
-// then the finalizer warp.
+// then the finalizer warp. A launch runs its phases one after the other with a grid-wide barrier in
+// between; the producer does not take part in the barriers: the weights of the next phase are already
+// streaming into the ring while the current phase drains and the next activation is built.
 template <int G>
 __global__ void __launch_bounds__((G * kCW + 2) * 32, 1) matvec_tc_kernel(const __grid_constant__ TcArgs a) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
@@ -313,296 +462,375 @@ __global__ void __launch_bounds__((G * kCW + 2) * 32, 1) matvec_tc_kernel(const 
     constexpr uint32_t kProducer = kConsumers, kFinal = kConsumers + 1;
     constexpr uint32_t kPrologueThreads = (kConsumers + 1) * 32;
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
-    const uint32_t nblk = a.cols / 256, nseg = (nblk + 7) / 8;
-    const TcSmem sm = tc_carve<G>(smem_raw, a.cols, a.use_q4 != 0, a.use_q6 != 0, a.nslots);
     const uint32_t S = a.nslots;
-
-    if (tid == 0) {
-        for (uint32_t s = 0; s < S; ++s) { mbar_init(&sm.full[s], 1); mbar_init(&sm.empty[s], kCW); }
-        for (int i = 0; i < 2; ++i) { mbar_init(&sm.red_full[i], kConsumers); mbar_init(&sm.red_empty[i], 1); }
-        fence_barrier_init();
-        trace_min(a.trace, 0);
+    {
+        const TcSmem sm = tc_carve<G>(smem_raw, 256, false, false, S, a.ring_off);
+        if (tid == 0) {
+            for (uint32_t s = 0; s < S; ++s) { mbar_init(&sm.full[s], 1); mbar_init(&sm.empty[s], kCW); }
+            for (int i = 0; i < 2; ++i) { mbar_init(&sm.red_full[i], kConsumers); mbar_init(&sm.red_empty[i], 1); }
+            *reinterpret_cast<uint4 *>(sm.zero) = make_uint4(0u, 0u, 0u, 0u);
+            fence_barrier_init();
+            trace_min(a.trace, 0);
+        }
     }
     __syncthreads();
     griddep_launch_dependents();
-
-    // units of this CTA: blockIdx.x, + gridDim.x, ...
-    const uint32_t my_units = blockIdx.x < a.total_units ? (a.total_units - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
-    const uint32_t ring = smem_u32(sm.ring);
+    const uint32_t ring = smem_u32(smem_raw) + a.ring_off;
 
     if (warp == kProducer) {
-        // ---- producer: one bulk copy per row and stage; the weights do not depend on the previous kernel ----
+        // ---- producer: one bulk copy per row and stage; the weights do not depend on any activation ----
+        const TcSmem sm = tc_carve<G>(smem_raw, 256, false, false, S, a.ring_off);
         uint32_t slot = 0, par = 1;   // a fresh barrier passes a wait on parity 1
-        for (uint32_t k = 0; k < my_units; ++k) {
-            const uint32_t u = blockIdx.x + k * gridDim.x;
-            const uint8_t *src = nullptr;
-            uint32_t pitch = 0, fmt;
-            bool valid = false;
-            if (a.swiglu) {
-                const TcTensor &t = a.t[(lane >> 3) & 1u];
-                const uint32_t row = 8 * u + (lane & 7u);
-                fmt = (uint32_t)a.t[0].fmt;
-                valid = lane < 16 && row < t.rows;
-                pitch = t.pitch;
-                src = t.w + (size_t)row * t.pitch;
-            } else {
-                const TcTensor &t = a.t[unit_tensor(a, u)];
-                const uint32_t row = 16 * (u - t.unit0) + lane;
-                fmt = (uint32_t)t.fmt;
-                valid = lane < 16 && row < t.rows;
-                pitch = t.pitch;
-                src = t.w + (size_t)row * t.pitch;
-            }
-            const uint32_t segb = fmt == FMT_Q4_K ? kSeg4 : kSeg6, rp = fmt == FMT_Q4_K ? kPitch4 : kPitch6;
-            const uint32_t nvalid = __popc(__ballot_sync(0xffffffffu, valid));
-            for (uint32_t seg = 0; seg < nseg; ++seg) {
-                const uint32_t off = seg * segb;
-                const uint32_t bytes = min(segb, pitch - off);   // pitch and off are multiples of 16
-                if (!mbar_wait_bounded(&sm.empty[slot], par, a.status)) return;
-                fence_proxy_async_smem();
-                if (lane == 0) mbar_arrive_expect_tx(&sm.full[slot], nvalid * bytes);
-                __syncwarp();
-                if (valid) bulk_g2s_addr(ring + slot * a.slot_bytes + lane * rp, src + off, bytes, &sm.full[slot]);
-                if (++slot == S) { slot = 0; par ^= 1u; }
+#pragma unroll 1
+        for (int p = 0; p < a.n_phases; ++p) {
+            const TcPhase &ph = a.ph[p];
+            const uint32_t nblk = ph.cols / 256, nseg = (nblk + 7) / 8;
+            const uint32_t my_units = blockIdx.x < ph.total_units ? (ph.total_units - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+            for (uint32_t k = 0; k < my_units; ++k) {
+                const uint32_t u = blockIdx.x + k * gridDim.x;
+                const uint8_t *src = nullptr;
+                uint32_t pitch = 0, fmt;
+                bool valid = false;
+                if (ph.swiglu) {
+                    const TcTensor &t = ph.t[(lane >> 3) & 1u];
+                    const uint32_t row = 8 * u + (lane & 7u);
+                    fmt = (uint32_t)ph.t[0].fmt;
+                    valid = lane < 16 && row < t.rows;
+                    pitch = t.pitch;
+                    src = t.w + (size_t)row * t.pitch;
+                } else {
+                    const TcTensor &t = ph.t[unit_tensor(ph, u)];
+                    const uint32_t row = 16 * (u - t.unit0) + lane;
+                    fmt = (uint32_t)t.fmt;
+                    valid = lane < 16 && row < t.rows;
+                    pitch = t.pitch;
+                    src = t.w + (size_t)row * t.pitch;
+                }
+                const uint32_t segb = fmt == FMT_Q4_K ? kSeg4 : fmt == FMT_Q6_K ? kSeg6 : kSeg8;
+                const uint32_t rp = fmt == FMT_Q4_K ? kPitch4 : fmt == FMT_Q6_K ? kPitch6 : kPitch8;
+                const uint32_t nvalid = __popc(__ballot_sync(0xffffffffu, valid));
+                const uint32_t row0 = ph.swiglu ? 8 * u : 16 * (u - ph.t[ph.swiglu ? 0 : unit_tensor(ph, u)].unit0);
+                const int ti = ph.swiglu ? 0 : unit_tensor(ph, u);
+                for (uint32_t seg = 0; seg < nseg; ++seg) {
+                    const uint32_t off = seg * segb;
+                    if (!mbar_wait_bounded(&sm.empty[slot], par, a.status)) return;
+                    fence_proxy_async_smem();
+                    const uint32_t dst = ring + slot * a.slot_bytes;
+                    if (fmt == FMT_Q8_0) {   // one bulk copy per row (a segment is wider than a TMA box may be)
+                        const uint32_t bytes = min(segb, pitch - off);   // pitch and off are multiples of 16
+                        if (lane == 0) mbar_arrive_expect_tx(&sm.full[slot], nvalid * bytes);
+                        __syncwarp();
+                        if (valid) bulk_g2s_addr(dst + lane * rp, src + off, bytes, &sm.full[slot]);
+                    } else if (lane == 0) {
+                        // one box of 16 rows x the segment (SwiGLU: 8 gate rows, then 8 up rows); rows past the end of the
+                        // tensor and blocks past the end of a row arrive as zeros and count as bytes all the same
+                        mbar_arrive_expect_tx(&sm.full[slot], 16 * segb);
+                        if (ph.swiglu) {
+                            tma_box(dst, &ph.t[0].map, off / 8, row0, &sm.full[slot]);
+                            tma_box(dst + 8 * segb, &ph.t[1].map, off / 8, row0, &sm.full[slot]);
+                        } else {
+                            tma_box(dst, &ph.t[ti].map, off / 8, row0, &sm.full[slot]);
+                        }
+                    }
+                    if (++slot == S) { slot = 0; par ^= 1u; }
+                }
             }
         }
         return;
     }
 
-    // ---- prologue (consumers and the finalizer): the activation as f16 (hi, lo) pairs ----
-    {
-        const uint32_t pw = warp < kProducer ? warp : warp - 1;   // 0 .. kConsumers
-        const uint32_t hw = 2 * pw + (lane >> 4), hl = lane & 15u;
-        constexpr uint32_t nhw = 2 * (kConsumers + 1);
-        constexpr int kMaxBlkPerHalfWarp = max_blk_per_half_warp(G);
-        float4 ra[kMaxBlkPerHalfWarp][4], rb[kMaxBlkPerHalfWarp][4];
+    uint32_t it_base = 0;    // stages of this CTA in earlier phases
+    uint32_t kk = 0;         // units of this CTA so far (all phases): selects the reduction buffer
+#pragma unroll 1
+    for (int p = 0; p < a.n_phases; ++p) {
+        const TcPhase &ph = a.ph[p];
+        const uint32_t nblk = ph.cols / 256, nseg = (nblk + 7) / 8;
+        const TcSmem sm = tc_carve<G>(smem_raw, ph.cols, ph.use_q4 != 0, ph.use_q6 != 0, S, a.ring_off);
+        const uint32_t my_units = blockIdx.x < ph.total_units ? (ph.total_units - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+        const bool late = p > 0;   // the activation was written by the previous phase of this launch: read it past L1
+
+        // ---- prologue (consumers and the finalizer): the activation as f16 (hi, lo) pairs ----
+        {
+            const uint32_t pw = warp < kProducer ? warp : warp - 1;   // 0 .. kConsumers
+            const uint32_t hw = 2 * pw + (lane >> 4), hl = lane & 15u;
+            constexpr uint32_t nhw = 2 * (kConsumers + 1);
+            constexpr int kMaxBlkPerHalfWarp = max_blk_per_half_warp(G);
+            float4 ra[kMaxBlkPerHalfWarp][4], rb[kMaxBlkPerHalfWarp][4];
 #pragma unroll
-        for (int b = 0; b < kMaxBlkPerHalfWarp; ++b)
+            for (int b = 0; b < kMaxBlkPerHalfWarp; ++b)
 #pragma unroll
-            for (int k = 0; k < 4; ++k) ra[b][k] = rb[b][k] = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (a.x_mode == MV_X_RMSNORM) {   // the norm weights are constants: fetch them before the dependency wait
+                for (int k = 0; k < 4; ++k) ra[b][k] = rb[b][k] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (ph.x_mode == MV_X_RMSNORM) {   // the norm weights are constants: fetch them before the dependency is met
+#pragma unroll
+                for (int b = 0; b < kMaxBlkPerHalfWarp; ++b) {
+                    const uint32_t blk = hw + b * nhw;
+                    if (blk < nblk) {
+                        const float4 *src = reinterpret_cast<const float4 *>(ph.wnorm + blk * 256 + hl * 16);
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) rb[b][k] = __ldg(src + k);
+                    }
+                }
+            }
+            if (!late) {
+                griddep_wait();   // the activation (and y, resid) come from the previous kernel
+                if (tid == 0) trace_min(a.trace, 1);
+            } else {
+                // every output of the previous phase, from every CTA, has to be visible: the finalizer (which wrote
+                // this CTA's share) meets the other CTAs, then this CTA's warps meet here
+                if (warp == kFinal) {
+                    __threadfence();
+                    __syncwarp();
+                    bool ok = true;
+                    if (lane == 0) ok = grid_barrier(a.bar, gridDim.x, a.status);
+                    ok = __shfl_sync(0xffffffffu, ok, 0);
+                    (void)ok;   // on a time-out the status word is set; the launch runs on with void results
+                }
+                prologue_barrier(kPrologueThreads);
+            }
 #pragma unroll
             for (int b = 0; b < kMaxBlkPerHalfWarp; ++b) {
                 const uint32_t blk = hw + b * nhw;
                 if (blk < nblk) {
-                    const float4 *src = reinterpret_cast<const float4 *>(a.wnorm + blk * 256 + hl * 16);
+                    const float4 *src = reinterpret_cast<const float4 *>(ph.x + blk * 256 + hl * 16);
 #pragma unroll
-                    for (int k = 0; k < 4; ++k) rb[b][k] = __ldg(src + k);
+                    for (int k = 0; k < 4; ++k) ra[b][k] = late ? __ldcg(src + k) : src[k];
+                    if (ph.x_mode == MV_X_SILU_MUL) {
+                        const float4 *src2 = reinterpret_cast<const float4 *>(ph.x2 + blk * 256 + hl * 16);
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) rb[b][k] = late ? __ldcg(src2 + k) : src2[k];
+                    }
                 }
             }
-        }
-        griddep_wait();   // the activation (and y, resid) come from the previous kernel
-        if (tid == 0) trace_min(a.trace, 1);
+            // RMSNorm: hi / lo are those of x * w; the common factor 1 / rms goes onto the row sums at the end
+            if (ph.x_mode == MV_X_RMSNORM) {
+                float ss = 0.f;
 #pragma unroll
-        for (int b = 0; b < kMaxBlkPerHalfWarp; ++b) {
-            const uint32_t blk = hw + b * nhw;
-            if (blk < nblk) {
-                const float4 *src = reinterpret_cast<const float4 *>(a.x + blk * 256 + hl * 16);
+                for (int b = 0; b < kMaxBlkPerHalfWarp; ++b)
 #pragma unroll
-                for (int k = 0; k < 4; ++k) ra[b][k] = src[k];
-                if (a.x_mode == MV_X_SILU_MUL) {
-                    const float4 *src2 = reinterpret_cast<const float4 *>(a.x2 + blk * 256 + hl * 16);
-#pragma unroll
-                    for (int k = 0; k < 4; ++k) rb[b][k] = src2[k];
-                }
+                    for (int k = 0; k < 4; ++k) {
+                        const float4 u = ra[b][k];
+                        ss += (u.x * u.x + u.y * u.y) + (u.z * u.z + u.w * u.w);
+                    }
+                ss = warp_sum(ss);
+                if (lane == 0) sm.ssq[pw] = ss;
             }
-        }
-        // RMSNorm: hi / lo are those of x * w; the common factor 1 / rms goes onto the row sums at the end
-        if (a.x_mode == MV_X_RMSNORM) {
-            float ss = 0.f;
 #pragma unroll
-            for (int b = 0; b < kMaxBlkPerHalfWarp; ++b)
+            for (int b = 0; b < kMaxBlkPerHalfWarp; ++b) {
+                const uint32_t blk = hw + b * nhw;
+                if (2 * pw + b * nhw >= nblk) break;   // warp-uniform
+                const bool live = blk < nblk;          // the second half-warp of the last warp may be past the end
+                float v[16];
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
-                    const float4 u = ra[b][k];
-                    ss += (u.x * u.x + u.y * u.y) + (u.z * u.z + u.w * u.w);
+                    v[4 * k] = ra[b][k].x; v[4 * k + 1] = ra[b][k].y; v[4 * k + 2] = ra[b][k].z; v[4 * k + 3] = ra[b][k].w;
                 }
-            ss = warp_sum(ss);
-            if (lane == 0) sm.ssq[pw] = ss;
-        }
+                if (ph.x_mode != MV_X_PLAIN) {
+                    float w2[16];
 #pragma unroll
-        for (int b = 0; b < kMaxBlkPerHalfWarp; ++b) {
-            const uint32_t blk = hw + b * nhw;
-            if (2 * pw + b * nhw >= nblk) break;   // warp-uniform
-            const bool live = blk < nblk;          // the second half-warp of the last warp may be past the end
-            float v[16];
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                v[4 * k] = ra[b][k].x; v[4 * k + 1] = ra[b][k].y; v[4 * k + 2] = ra[b][k].z; v[4 * k + 3] = ra[b][k].w;
-            }
-            if (a.x_mode != MV_X_PLAIN) {
-                float w2[16];
-#pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    w2[4 * k] = rb[b][k].x; w2[4 * k + 1] = rb[b][k].y; w2[4 * k + 2] = rb[b][k].z; w2[4 * k + 3] = rb[b][k].w;
-                }
-#pragma unroll
-                for (int i = 0; i < 16; ++i)
-                    v[i] = a.x_mode == MV_X_RMSNORM ? v[i] * w2[i] : (v[i] / (1.0f + expf(-v[i]))) * w2[i];
-            }
-            float amax = 0.f;
-#pragma unroll
-            for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
-#pragma unroll
-            for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));   // over the half-warp
-            // block scale 2^e with amax / 2^e in [2^13, 2^14); e clamped so that both 2^e and 2^-e are normal floats
-            int e = (int)((__float_as_uint(amax) >> 23) & 0xFFu) - 127 - 13;
-            e = amax > 0.f ? max(-126, min(e, 114)) : 0;
-            const float inv_s = __uint_as_float((uint32_t)(127 - e) << 23);
-            uint32_t hi2[8], lo2[8];   // element pairs (i, i + 2) of each group of four: the B operand's k order
-            float sum = 0.f;
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                __half hh[4], ll[4];
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const float s = v[4 * j + i] * inv_s;
-                    hh[i] = __float2half_rn(s);
-                    const float r = s - __half2float(hh[i]);
-                    ll[i] = __float2half_rn(r);
-                    sum += __half2float(hh[i]) + __half2float(ll[i]);
-                }
-                hi2[2 * j] = (uint32_t)__half_as_ushort(hh[0]) | ((uint32_t)__half_as_ushort(hh[2]) << 16);
-                hi2[2 * j + 1] = (uint32_t)__half_as_ushort(hh[1]) | ((uint32_t)__half_as_ushort(hh[3]) << 16);
-                lo2[2 * j] = (uint32_t)__half_as_ushort(ll[0]) | ((uint32_t)__half_as_ushort(ll[2]) << 16);
-                lo2[2 * j + 1] = (uint32_t)__half_as_ushort(ll[1]) | ((uint32_t)__half_as_ushort(ll[3]) << 16);
-            }
-            const float sum32 = sum + __shfl_xor_sync(0xffffffffu, sum, 1);
-            if (live) {
-                if (a.use_q4) {
-                    // columns 16 hl .. 16 hl + 15: chunk c = hl / 4, sub-block half (hl / 2) & 1, words 4 (hl & 1) + j
-                    const uint32_t c = hl >> 2, sub = (hl >> 1) & 1u, j0 = 4 * (hl & 1u);
-                    const uint32_t base = smem_u32(sm.x4) + blk * 1024u;
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        sts64(base + x4_off(j0 + j, 2 * c, sub), hi2[2 * j], hi2[2 * j + 1]);
-                        sts64(base + x4_off(j0 + j, 2 * c + 1, sub), lo2[2 * j], lo2[2 * j + 1]);
+                    for (int k = 0; k < 4; ++k) {
+                        w2[4 * k] = rb[b][k].x; w2[4 * k + 1] = rb[b][k].y; w2[4 * k + 2] = rb[b][k].z; w2[4 * k + 3] = rb[b][k].w;
                     }
-                    if ((hl & 1u) == 0) sm.s4[blk * 8 + (hl >> 1)] = sum32;
-                }
-                if (a.use_q6) {
-                    // columns 16 hl ..: half hf = hl / 8, group gq = (hl / 2) & 3, run hq = hl & 1, words j = 0..3
-                    const uint32_t hf = hl >> 3, gq = (hl >> 1) & 3u, hq = hl & 1u, t = 2 * hf + hq;
-                    const uint32_t base = smem_u32(sm.x6) + blk * 1024u;
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const uint32_t s = ((uint32_t)j - t) & 3u;
-                        sts64(base + x6_off(s, 2 * t, gq), hi2[2 * j], hi2[2 * j + 1]);
-                        sts64(base + x6_off(s, 2 * t + 1, gq), lo2[2 * j], lo2[2 * j + 1]);
-                    }
+                    for (int i = 0; i < 16; ++i)
+                        v[i] = ph.x_mode == MV_X_RMSNORM ? v[i] * w2[i] : (v[i] / (1.0f + expf(-v[i]))) * w2[i];
                 }
-                if (hl == 0) sm.xs[blk] = __uint_as_float((uint32_t)(127 + e) << 23);
+                float amax = 0.f;
+#pragma unroll
+                for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
+#pragma unroll
+                for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));   // over the half-warp
+                // block scale 2^e with amax / 2^e in [2^13, 2^14); e clamped so that both 2^e and 2^-e are normal floats
+                int e = (int)((__float_as_uint(amax) >> 23) & 0xFFu) - 127 - 13;
+                e = amax > 0.f ? max(-126, min(e, 114)) : 0;
+                const float inv_s = __uint_as_float((uint32_t)(127 - e) << 23);
+                uint32_t hi2[8], lo2[8];   // element pairs (i, i + 2) of each group of four: the B operand's k order
+                float sum = 0.f;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    __half hh[4], ll[4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const float s = v[4 * j + i] * inv_s;
+                        hh[i] = __float2half_rn(s);
+                        const float r = s - __half2float(hh[i]);
+                        ll[i] = __float2half_rn(r);
+                        sum += __half2float(hh[i]) + __half2float(ll[i]);
+                    }
+                    hi2[2 * j] = (uint32_t)__half_as_ushort(hh[0]) | ((uint32_t)__half_as_ushort(hh[2]) << 16);
+                    hi2[2 * j + 1] = (uint32_t)__half_as_ushort(hh[1]) | ((uint32_t)__half_as_ushort(hh[3]) << 16);
+                    lo2[2 * j] = (uint32_t)__half_as_ushort(ll[0]) | ((uint32_t)__half_as_ushort(ll[2]) << 16);
+                    lo2[2 * j + 1] = (uint32_t)__half_as_ushort(ll[1]) | ((uint32_t)__half_as_ushort(ll[3]) << 16);
+                }
+                const float sum32 = sum + __shfl_xor_sync(0xffffffffu, sum, 1);
+                if (live) {
+                    if (ph.use_q4) {
+                        // columns 16 hl .. 16 hl + 15: chunk c = hl / 4, sub-block half (hl / 2) & 1, words 4 (hl & 1) + j
+                        const uint32_t c = hl >> 2, sub = (hl >> 1) & 1u, j0 = 4 * (hl & 1u);
+                        const uint32_t base = smem_u32(sm.x4) + blk * 1024u;
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            sts64(base + x4_off(j0 + j, 2 * c, sub), hi2[2 * j], hi2[2 * j + 1]);
+                            sts64(base + x4_off(j0 + j, 2 * c + 1, sub), lo2[2 * j], lo2[2 * j + 1]);
+                        }
+                        if ((hl & 1u) == 0) sm.s4[blk * 8 + (hl >> 1)] = sum32;
+                    }
+                    if (ph.use_q6) {
+                        // columns 16 hl ..: half hf = hl / 8, group gq = (hl / 2) & 3, run hq = hl & 1, words j = 0..3
+                        const uint32_t hf = hl >> 3, gq = (hl >> 1) & 3u, hq = hl & 1u, t = 2 * hf + hq;
+                        const uint32_t base = smem_u32(sm.x6) + blk * 1024u;
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const uint32_t s = ((uint32_t)j - t) & 3u;
+                            sts64(base + x6_off(s, 2 * t, gq), hi2[2 * j], hi2[2 * j + 1]);
+                            sts64(base + x6_off(s, 2 * t + 1, gq), lo2[2 * j], lo2[2 * j + 1]);
+                        }
+                    }
+                    if (hl == 0) sm.xs[blk] = __uint_as_float((uint32_t)(127 + e) << 23);
+                }
             }
-        }
-        prologue_barrier(kPrologueThreads);
-        if (a.xn_out != nullptr && blockIdx.x == 0) {   // the activation as f32, for layer-level checks
-            float t = 0.f;
-            for (uint32_t w = 0; w <= kConsumers; ++w) t += sm.ssq[w];
-            const float inv_rms = 1.0f / sqrtf(t / (float)a.cols + a.eps);
-            const uint32_t ptid = pw * 32 + lane;
-            for (uint32_t c = ptid; c < a.cols; c += kPrologueThreads) {
-                float v = a.x[c];
-                if (a.x_mode == MV_X_RMSNORM) v = v * inv_rms * a.wnorm[c];
-                else if (a.x_mode == MV_X_SILU_MUL) v = (v / (1.0f + expf(-v))) * a.x2[c];
-                a.xn_out[c] = v;
+            prologue_barrier(kPrologueThreads);
+            if (ph.xn_out != nullptr && blockIdx.x == 0) {   // the activation as f32, for layer-level checks
+                float t = 0.f;
+                for (uint32_t w = 0; w <= kConsumers; ++w) t += sm.ssq[w];
+                const float inv_rms = 1.0f / sqrtf(t / (float)ph.cols + ph.eps);
+                const uint32_t ptid = pw * 32 + lane;
+                for (uint32_t c = ptid; c < ph.cols; c += kPrologueThreads) {
+                    float v = late ? __ldcg(ph.x + c) : ph.x[c];
+                    if (ph.x_mode == MV_X_RMSNORM) v = v * inv_rms * ph.wnorm[c];
+                    else if (ph.x_mode == MV_X_SILU_MUL) v = (v / (1.0f + expf(-v))) * (late ? __ldcg(ph.x2 + c) : ph.x2[c]);
+                    ph.xn_out[c] = v;
+                }
             }
+            if (tid == 0 && !late) trace_max(a.trace, 2);
         }
-        if (tid == 0) trace_max(a.trace, 2);
-    }
 
-    if (warp == kFinal) {
-        // ---- finalizer: adds the warps' partial row sums of a unit in warp order, applies the epilogue ----
-        float inv_rms = 1.f;
-        if (a.x_mode == MV_X_RMSNORM) {
-            float t = 0.f;
-            for (uint32_t w = 0; w <= kConsumers; ++w) t += sm.ssq[w];   // the same order in every CTA
-            inv_rms = 1.0f / sqrtf(t / (float)a.cols + a.eps);
-        }
-        for (uint32_t k = 0; k < my_units; ++k) {
-            const uint32_t u = blockIdx.x + k * gridDim.x, buf = k & 1u;
-            if (!mbar_wait_bounded(&sm.red_full[buf], (k >> 1) & 1u, a.status)) return;
-            float v = 0.f;
-            if (lane < 16) {
-                const float *p = sm.red + buf * kConsumers * 16 + lane;
+        if (warp == kFinal) {
+            // ---- finalizer: adds the warps' partial row sums of a unit in warp order, applies the epilogue ----
+            float inv_rms = 1.f;
+            if (ph.x_mode == MV_X_RMSNORM) {
+                float t = 0.f;
+                for (uint32_t w = 0; w <= kConsumers; ++w) t += sm.ssq[w];   // the same order in every CTA
+                inv_rms = 1.0f / sqrtf(t / (float)ph.cols + ph.eps);
+            }
+            for (uint32_t k = 0; k < my_units; ++k, ++kk) {
+                const uint32_t u = blockIdx.x + k * gridDim.x, buf = kk & 1u;
+                if (!mbar_wait_bounded(&sm.red_full[buf], (kk >> 1) & 1u, a.status)) return;
+                float v = 0.f;
+                if (lane < 16) {
+                    const float *pp = sm.red + buf * kConsumers * 16 + lane;
 #pragma unroll
-                for (uint32_t w = 0; w < kConsumers; ++w) v += p[w * 16];
-            }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&sm.red_empty[buf]);
-            v *= inv_rms;
-            if (a.swiglu) {
-                // rows 0..7 = gate rows 8u.., rows 8..15 = up rows: h = silu(gate) * up (fl_op_silu_mul,
-                // src/runtime/decode_params.h:267-272)
-                const float up = __shfl_down_sync(0xffffffffu, v, 8);
-                const uint32_t row = 8 * u + lane;
-                if (lane < 8 && row < a.t[0].rows) a.t[0].y[row] = (v / (1.0f + expf(-v))) * up;
-            } else {
-                const TcTensor &t = a.t[unit_tensor(a, u)];
-                const uint32_t row = 16 * (u - t.unit0) + lane;
-                if (lane < 16 && row < t.rows) {
-                    float o = v;
-                    if (t.resid) o = t.resid[row] + v;
-                    if (a.accumulate) o = t.y[row] + o;
-                    t.y[row] = o;
-                }
-            }
-        }
-        if (lane == 0) trace_max(a.trace, 3);
-        return;
-    }
-
-    // ---- consumers ----
-    {
-        const uint32_t grp = warp / kCW, w = warp % kCW;
-        const uint32_t g = lane >> 2, t = lane & 3u;
-        const bool has_b = (g >> 1) == t;
-        const uint32_t lane8 = 2 * t + (g & 1u);
-        const uint32_t x4 = a.use_q4 ? smem_u32(sm.x4) + lane8 * 16u : 0u, x6 = a.use_q6 ? smem_u32(sm.x6) + lane8 * 16u : 0u;
-        for (uint32_t k = 0; k < my_units; ++k) {
-            const uint32_t u = blockIdx.x + k * gridDim.x;
-            const int fmt = a.swiglu ? a.t[0].fmt : a.t[unit_tensor(a, u)].fmt;
-            float acc0 = 0.f, acc1 = 0.f;
-            // this group's stages of unit k: global stage index it = k * nseg + seg, it % G == grp
-            const uint32_t it0 = k * nseg;
-            uint32_t seg = (grp + G - it0 % G) % G;
-            for (; seg < nseg; seg += G) {
-                const uint32_t it = it0 + seg, slot = it % S, par = (it / S) & 1u;
-                const uint32_t blk = seg * 8 + w;
-                if (!mbar_wait_bounded(&sm.full[slot], par, a.status)) return;
-                if (blk < nblk) {
-                    const float xs = sm.xs[blk];
-                    float o0, o1;
-                    if (fmt == FMT_Q4_K) {
-                        const uint32_t r0 = ring + slot * a.slot_bytes + g * kPitch4 + w * 144u;
-                        const float2 sx = *reinterpret_cast<const float2 *>(sm.s4 + blk * 8 + 2 * t);
-                        q4k_block(r0, r0 + 8 * kPitch4, t, has_b, x4 + blk * 1024u, sx, o0, o1);
-                    } else {
-                        const uint32_t r0 = ring + slot * a.slot_bytes + g * kPitch6 + w * 210u;
-                        if (w & 1u) q6k_block<true>(r0 - 2, r0 + 8 * kPitch6 - 2, t, has_b, x6 + blk * 1024u, o0, o1);
-                        else q6k_block<false>(r0, r0 + 8 * kPitch6, t, has_b, x6 + blk * 1024u, o0, o1);
-                    }
-                    acc0 = fmaf(xs, o0, acc0);
-                    acc1 = fmaf(xs, o1, acc1);
+                    for (uint32_t w = 0; w < kConsumers; ++w) v += pp[w * 16];
                 }
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&sm.empty[slot]);
+                if (lane == 0) mbar_arrive(&sm.red_empty[buf]);
+                v *= inv_rms;
+                if (ph.swiglu) {
+                    // rows 0..7 = gate rows 8u.., rows 8..15 = up rows: h = silu(gate) * up (fl_op_silu_mul,
+                    // src/runtime/decode_params.h:267-272)
+                    const float up = __shfl_down_sync(0xffffffffu, v, 8);
+                    const uint32_t row = 8 * u + lane;
+                    if (lane < 8 && row < ph.t[0].rows) ph.t[0].y[row] = (v / (1.0f + expf(-v))) * up;
+                } else {
+                    const TcTensor &t = ph.t[unit_tensor(ph, u)];
+                    const uint32_t row = 16 * (u - t.unit0) + lane;
+                    if (lane < 16 && row < t.rows) {
+                        float o = v;
+                        if (t.resid) o = __ldcg(t.resid + row) + v;
+                        if (ph.accumulate) o = __ldcg(t.y + row) + o;
+                        t.y[row] = o;
+                    }
+                }
             }
-            // the unit's partial sums of rows g and g + 8 over this warp's lane columns
-            acc0 += __shfl_xor_sync(0xffffffffu, acc0, 1);
-            acc1 += __shfl_xor_sync(0xffffffffu, acc1, 1);
-            acc0 += __shfl_xor_sync(0xffffffffu, acc0, 2);
-            acc1 += __shfl_xor_sync(0xffffffffu, acc1, 2);
-            const uint32_t buf = k & 1u;
-            if (!mbar_wait_bounded(&sm.red_empty[buf], ((k >> 1) & 1u) ^ 1u, a.status)) return;
-            if (t == 0) {
-                float *p = sm.red + (buf * kConsumers + warp) * 16;
-                p[g] = acc0;
-                p[g + 8] = acc1;
+        } else {
+            // ---- consumers ----
+            const uint32_t grp = warp / kCW, w = warp % kCW;
+            const uint32_t g = lane >> 2, t = lane & 3u;
+            const bool has_b = (g >> 1) == t;   // this lane feeds column g of the B operand; the others feed zeros
+            const uint32_t lane8 = 2 * t + (g & 1u);
+            const uint32_t zero16 = smem_u32(sm.zero);
+            const uint32_t x4 = ph.use_q4 ? smem_u32(sm.x4) + lane8 * 16u : 0u, x6 = ph.use_q6 ? smem_u32(sm.x6) + lane8 * 16u : 0u;
+            const uint32_t xstride = has_b ? 128u : 0u;
+            for (uint32_t k = 0; k < my_units; ++k, ++kk) {
+                const uint32_t u = blockIdx.x + k * gridDim.x;
+                const int fmt = ph.swiglu ? ph.t[0].fmt : ph.t[unit_tensor(ph, u)].fmt;
+                float acc0 = 0.f, acc1 = 0.f;
+                // this group's stages of unit k: stage index it = it_base + k * nseg + seg over the whole launch, it % G == grp
+                const uint32_t it0 = it_base + k * nseg;
+                uint32_t seg = (grp + G - it0 % G) % G;
+                const uint32_t xb = has_b ? 1024u : 0u;   // lanes that feed zeros stay on the zero slot
+                if (fmt == FMT_Q4_K) {
+                    const uint32_t xa4 = has_b ? x4 : zero16;
+                    for (; seg < nseg; seg += G) {
+                        const uint32_t it = it0 + seg, slot = it % S, par = (it / S) & 1u;
+                        const uint32_t blk = seg * 8 + w;
+                        if (!mbar_wait_fast(&sm.full[slot], par, a.status)) return;
+                        if (blk < nblk) {
+                            const uint32_t r0 = ring + slot * a.slot_bytes + g * kPitch4 + w * 144u;
+                            const float2 sx = *reinterpret_cast<const float2 *>(sm.s4 + blk * 8 + 2 * t);
+                            float o0, o1;
+                            q4k_block(r0, r0 + 8 * kPitch4, t, xa4 + blk * xb, xstride, sx, o0, o1);
+                            const float xs = sm.xs[blk];
+                            acc0 = fmaf(xs, o0, acc0);
+                            acc1 = fmaf(xs, o1, acc1);
+                        }
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&sm.empty[slot]);
+                    }
+                } else if (fmt == FMT_Q8_0) {
+                    const uint32_t xa4 = has_b ? x4 : zero16;
+                    for (; seg < nseg; seg += G) {
+                        const uint32_t it = it0 + seg, slot = it % S, par = (it / S) & 1u;
+                        const uint32_t blk = seg * 8 + w;
+                        if (!mbar_wait_fast(&sm.full[slot], par, a.status)) return;
+                        if (blk < nblk) {
+                            const uint32_t r0 = ring + slot * a.slot_bytes + g * kPitch8 + w * 272u + t * 68u;
+                            float o0, o1;
+                            q8_0_block(r0, r0 + 8 * kPitch8, xa4 + blk * xb, xstride, o0, o1);
+                            const float xs = sm.xs[blk];
+                            acc0 = fmaf(xs, o0, acc0);
+                            acc1 = fmaf(xs, o1, acc1);
+                        }
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&sm.empty[slot]);
+                    }
+                } else {
+                    const uint32_t xa6 = has_b ? x6 : zero16;
+                    for (; seg < nseg; seg += G) {
+                        const uint32_t it = it0 + seg, slot = it % S, par = (it / S) & 1u;
+                        const uint32_t blk = seg * 8 + w;
+                        if (!mbar_wait_fast(&sm.full[slot], par, a.status)) return;
+                        if (blk < nblk) {
+                            const uint32_t r0 = ring + slot * a.slot_bytes + g * kPitch6 + w * 210u;
+                            float o0, o1;
+                            if (w & 1u) q6k_block<true>(r0 - 2, r0 + 8 * kPitch6 - 2, t, xa6 + blk * xb, xstride, o0, o1);
+                            else q6k_block<false>(r0, r0 + 8 * kPitch6, t, xa6 + blk * xb, xstride, o0, o1);
+                            const float xs = sm.xs[blk];
+                            acc0 = fmaf(xs, o0, acc0);
+                            acc1 = fmaf(xs, o1, acc1);
+                        }
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&sm.empty[slot]);
+                    }
+                }
+                // the unit's partial sums of rows g and g + 8 over this warp's lane columns
+                acc0 += __shfl_xor_sync(0xffffffffu, acc0, 1);
+                acc1 += __shfl_xor_sync(0xffffffffu, acc1, 1);
+                acc0 += __shfl_xor_sync(0xffffffffu, acc0, 2);
+                acc1 += __shfl_xor_sync(0xffffffffu, acc1, 2);
+                const uint32_t buf = kk & 1u;
+                if (!mbar_wait_fast(&sm.red_empty[buf], ((kk >> 1) & 1u) ^ 1u, a.status)) return;
+                if (t == 0) {
+                    float *pp = sm.red + (buf * kConsumers + warp) * 16;
+                    pp[g] = acc0;
+                    pp[g + 8] = acc1;
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&sm.red_full[buf]);
             }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&sm.red_full[buf]);
         }
+        it_base += my_units * nseg;
     }
+    if (warp == kFinal && lane == 0) trace_max(a.trace, 3);
 }
 
 int tc_groups() {
@@ -618,58 +846,102 @@ cudaError_t matvec_tc_init(void) {
     return cudaFuncSetAttribute(matvec_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024 - 1024);
 }
 
-// True when the launch can run on the tensor-core kernel: Q4_K / Q6_K tensors only, whole 256-column
+// True when the launch can run on the tensor-core kernel: Q4_K / Q6_K / Q8_0 tensors only, whole 256-column
 // blocks, 16-byte aligned rows, no expert indirection and no exchange prologue.
 bool matvec_tc_eligible(const MatvecArgs &a) {
     static const bool off = getenv("FLB_TC") && getenv("FLB_TC")[0] == '0';
     if (off || a.xr_buf || a.cols % 256 != 0 || a.cols < 256) return false;
+    if (a.n_tensors < 1 || a.n_tensors > 3) return false;
     if ((((uintptr_t)a.x) & 15u) || (((uintptr_t)a.x2) & 15u) || (((uintptr_t)a.wnorm) & 15u)) return false;
     const int groups = tc_groups();
     if (a.cols / 256 > (uint32_t)(max_blk_per_half_warp(groups) * 2 * (groups * kCW + 1))) return false;
-    bool q4 = false, q6 = false;
+    bool q4 = false, q6 = false, q8 = false;
     for (int i = 0; i < a.n_tensors; ++i) {
         const MatvecTensor &t = a.t[i];
-        if (t.fmt != FMT_Q4_K && t.fmt != FMT_Q6_K) return false;
+        if (t.fmt != FMT_Q4_K && t.fmt != FMT_Q6_K && t.fmt != FMT_Q8_0) return false;
         if (t.expert_id || t.rows == 0) return false;
         const uint64_t pitch = t.pitch ? t.pitch : row_bytes(t.fmt, a.cols);
         if ((pitch & 15u) || (((uintptr_t)t.w) & 15u) || pitch < row_bytes(t.fmt, a.cols)) return false;
-        (t.fmt == FMT_Q4_K ? q4 : q6) = true;
+        (t.fmt == FMT_Q6_K ? q6 : q4) = true;   // Q8_0 uses the Q4_K layout of the activation
+        q8 = q8 || t.fmt == FMT_Q8_0;
     }
     if (a.swiglu && (a.n_tensors != 2 || a.t[0].rows != a.t[1].rows || a.t[0].fmt != a.t[1].fmt || a.accumulate)) return false;
-    const uint32_t slot = q6 ? kSlot6 : kSlot4;
-    return tc_fixed_bytes(a.cols, q4, q6, 2, groups) + 2u * slot <= 227 * 1024 - 1024;
+    const uint32_t slot = q8 ? kSlot8 : q6 ? kSlot6 : kSlot4;
+    return tc_head_bytes(2, groups) + tc_x_bytes(a.cols, q4, q6) + 128 + 2u * slot <= 227 * 1024 - 1024;
 }
 
-cudaError_t launch_matvec_tc(const MatvecArgs &a, int sms, cudaStream_t stream) {
+// One launch of n dependent matvecs (phase i + 1 consumes what phase i writes). n = 1: a plain launch.
+// cudaErrorNotSupported when a phase does not qualify or the phases do not fit together; the caller then
+// launches them one by one.
+cudaError_t launch_matvec_tc_chain(const MatvecArgs *args, int n, int sms, cudaStream_t stream) {
+    if (n < 1 || n > 4) return cudaErrorInvalidValue;
     TcArgs k;
     memset(&k, 0, sizeof(k));
     const int groups = tc_groups();
-    bool q4 = false, q6 = false;
-    uint32_t units = 0;
-    k.n_tensors = a.n_tensors;
-    for (int i = 0; i < a.n_tensors; ++i) {
-        const MatvecTensor &t = a.t[i];
-        k.t[i].w = t.w; k.t[i].y = t.y; k.t[i].resid = t.resid; k.t[i].rows = t.rows; k.t[i].fmt = t.fmt;
-        k.t[i].pitch = t.pitch ? t.pitch : (uint32_t)row_bytes(t.fmt, a.cols);
-        k.t[i].unit0 = units;
-        units += (t.rows + 15) / 16;
-        (t.fmt == FMT_Q4_K ? q4 : q6) = true;
+    bool any6 = false, any8 = false;
+    size_t xmax = 0;
+    uint32_t max_units = 0;
+    for (int p = 0; p < n; ++p) {
+        const MatvecArgs &a = args[p];
+        if (!matvec_tc_eligible(a)) return cudaErrorNotSupported;
+        if (p > 0 && (a.trace || a.issue_late)) { /* per-launch diagnostics apply to the first phase only */ }
+        TcPhase &ph = k.ph[p];
+        bool q4 = false, q6 = false;
+        uint32_t units = 0;
+        ph.n_tensors = a.n_tensors;
+        for (int i = 0; i < a.n_tensors; ++i) {
+            const MatvecTensor &t = a.t[i];
+            ph.t[i].w = t.w; ph.t[i].y = t.y; ph.t[i].resid = t.resid; ph.t[i].rows = t.rows; ph.t[i].fmt = t.fmt;
+            ph.t[i].pitch = t.pitch ? t.pitch : (uint32_t)row_bytes(t.fmt, a.cols);
+            ph.t[i].unit0 = units;
+            units += (t.rows + 15) / 16;
+            if (t.fmt != FMT_Q8_0) {
+                const uint32_t segb = t.fmt == FMT_Q4_K ? kSeg4 : kSeg6;
+                const cudaError_t e = tensor_map_2d(&ph.t[i].map, 8, t.w, ph.t[i].pitch / 8, t.rows, ph.t[i].pitch, segb / 8,
+                                                    a.swiglu ? 8 : 16, false);
+                if (e != cudaSuccess) return e;
+            }
+            (t.fmt == FMT_Q6_K ? q6 : q4) = true;
+            any8 = any8 || t.fmt == FMT_Q8_0;
+        }
+        if (a.swiglu) units = (a.t[0].rows + 7) / 8;
+        ph.x = a.x; ph.x2 = a.x2; ph.wnorm = a.wnorm; ph.eps = a.eps; ph.cols = a.cols; ph.x_mode = a.x_mode;
+        ph.accumulate = a.accumulate; ph.swiglu = a.swiglu; ph.total_units = units;
+        ph.use_q4 = q4 ? 1 : 0; ph.use_q6 = q6 ? 1 : 0;
+        ph.xn_out = a.xn_out;
+        any6 = any6 || q6;
+        xmax = std::max(xmax, tc_x_bytes(a.cols, q4, q6));
+        max_units = std::max(max_units, units);
     }
-    if (a.swiglu) units = (a.t[0].rows + 7) / 8;
-    k.x = a.x; k.x2 = a.x2; k.wnorm = a.wnorm; k.eps = a.eps; k.cols = a.cols; k.x_mode = a.x_mode;
-    k.accumulate = a.accumulate; k.swiglu = a.swiglu; k.total_units = units;
-    k.use_q4 = q4 ? 1 : 0; k.use_q6 = q6 ? 1 : 0;
-    k.status = a.status; k.xn_out = a.xn_out; k.trace = a.trace;
-    k.slot_bytes = q6 ? kSlot6 : kSlot4;
+    k.n_phases = n;
+    k.status = args[0].status;
+    k.trace = args[0].trace;
+    k.slot_bytes = any8 ? kSlot8 : any6 ? kSlot6 : kSlot4;
     const size_t limit = 227 * 1024 - 1024;
     uint32_t nslots = 2;
-    while (nslots < 32 && tc_fixed_bytes(a.cols, q4, q6, nslots + 1, groups) + (size_t)(nslots + 1) * k.slot_bytes <= limit) ++nslots;
+    auto total = [&](uint32_t ns) {
+        const size_t ring_off = (tc_head_bytes(ns, groups) + xmax + 127) & ~(size_t)127;
+        return ring_off + (size_t)ns * k.slot_bytes;
+    };
+    if (total(nslots) > limit) return cudaErrorNotSupported;
+    while (nslots < 32 && total(nslots + 1) <= limit) ++nslots;
     k.nslots = nslots;
-    const size_t smem = tc_fixed_bytes(a.cols, q4, q6, nslots, groups) + (size_t)nslots * k.slot_bytes;
-    const uint32_t grid = units < (uint32_t)sms ? units : (uint32_t)sms;
+    k.ring_off = (uint32_t)((tc_head_bytes(nslots, groups) + xmax + 127) & ~(size_t)127);
+    const size_t smem = total(nslots);
+    uint32_t grid = max_units < (uint32_t)sms ? max_units : (uint32_t)sms;
+    if (n > 1) {
+        // the barrier needs every CTA resident: one CTA per SM (the shared memory of a CTA is more than half an SM's)
+        if (smem <= 114 * 1024) return cudaErrorNotSupported;
+        if (!args[0].grid_bar) return cudaErrorInvalidValue;
+        k.bar = reinterpret_cast<GridBar *>(args[0].grid_bar);
+    }
     if (groups == 2)
-        return launch_kernel(matvec_tc_kernel<2>, dim3(grid), dim3((2 * kCW + 2) * 32), smem, stream, a.pdl != 0, k);
-    return launch_kernel(matvec_tc_kernel<1>, dim3(grid), dim3((kCW + 2) * 32), smem, stream, a.pdl != 0, k);
+        return launch_kernel(matvec_tc_kernel<2>, dim3(grid), dim3((2 * kCW + 2) * 32), smem, stream, args[0].pdl != 0, k);
+    return launch_kernel(matvec_tc_kernel<1>, dim3(grid), dim3((kCW + 2) * 32), smem, stream, args[0].pdl != 0, k);
+}
+
+cudaError_t launch_matvec_tc(const MatvecArgs &a, int sms, cudaStream_t stream) {
+    return launch_matvec_tc_chain(&a, 1, sms, stream);
 }
 
 } // namespace flb

@@ -1,6 +1,6 @@
-"""Tensor-parallel decoder on 2 GPUs (one process per GPU) against the same
-model on one GPU: identical greedy tokens, logits within the whole-step
-tolerance. Skipped on boxes with fewer than 2 GPUs."""
+"""Tensor-parallel decoder on 2, 4 and 8 GPUs (one process per GPU) against the
+same model on one GPU: identical greedy tokens, logits within the whole-step
+tolerance. Each case is skipped on boxes with fewer GPUs than it needs."""
 import os
 import socket
 
@@ -12,6 +12,9 @@ pytestmark = pytest.mark.gpu
 
 SMALL = dict(n_layer=2, n_embd=2048, n_head=16, n_kv_head=4, head_dim=128, n_ff=4096, n_vocab=1000, max_kv=96,
              rope_base=500000.0, eps=1e-5)
+# 8 ranks need 8 KV heads and at least 512 columns of O per rank
+WIDE = dict(n_layer=2, n_embd=4096, n_head=32, n_kv_head=8, head_dim=128, n_ff=4096, n_vocab=1000, max_kv=96,
+            rope_base=500000.0, eps=1e-5)
 N_PREFILL, STEPS, SEED = 40, 6, 3
 BATCH_TOKS = [11, 500, 7, 999, 123]
 
@@ -97,7 +100,7 @@ def _from_file_equals_sliced(rank, world, ctx, dist, path):
     return out[0][0] == out[1][0] and np.array_equal(out[0][1].view(np.uint32), out[1][1].view(np.uint32))
 
 
-def _worker(rank, world, port, q, model_path=None):
+def _worker(rank, world, port, q, model_path=None, cfg=None):
     try:
         import torch.distributed as dist
         os.environ["MASTER_ADDR"] = "127.0.0.1"
@@ -106,9 +109,10 @@ def _worker(rank, world, port, q, model_path=None):
         dist.init_process_group("gloo", rank=rank, world_size=world)
         from fast_llm_b200 import capi, tp
         from fast_llm_b200.decoder import Decoder
+        cfg = cfg or SMALL
         ctx = capi.Context(rank)
-        dec = Decoder(ctx, SMALL, tp=(rank, world))
-        _fill(dec, ctx, SMALL, rank, world)
+        dec = Decoder(ctx, cfg, tp=(rank, world))
+        _fill(dec, ctx, cfg, rank, world)
         tp.connect(dec, dist)
         dec.finalize()
         dec.rewind_to(N_PREFILL)
@@ -141,8 +145,8 @@ def _worker(rank, world, port, q, model_path=None):
         res["status"] = ctx.status()
         dist.barrier()
         if rank == 0:   # the same model on one GPU
-            one = Decoder(ctx, SMALL)
-            _fill(one, ctx, SMALL, 0, 1)
+            one = Decoder(ctx, cfg)
+            _fill(one, ctx, cfg, 0, 1)
             one.finalize()
             one.rewind_to(N_PREFILL)
             ref = {"tokens": [], "logits": [], "margin": []}
@@ -169,40 +173,48 @@ def _worker(rank, world, port, q, model_path=None):
         q.put((rank, "ERROR " + traceback.format_exc()))
 
 
-def test_two_rank_decoder_matches_single_gpu(tmp_path):
-    if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
-        pytest.skip("needs 2 GPUs")
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_tensor_parallel_decoder_matches_single_gpu(tmp_path, world):
+    if not torch.cuda.is_available() or torch.cuda.device_count() < world:
+        pytest.skip("needs %d GPUs" % world)
     import torch.multiprocessing as mp
     mpc = mp.get_context("spawn")
     q = mpc.Queue()
     port = _free_port()
-    model_path = str(tmp_path / "small.gguf")
-    _write_model_file(model_path)
-    procs = [mpc.Process(target=_worker, args=(r, 2, port, q, model_path)) for r in range(2)]
+    cfg = SMALL if world <= 4 else WIDE
+    model_path = None
+    if world == 2:   # the slices cut from a model file are checked once
+        model_path = str(tmp_path / "small.gguf")
+        _write_model_file(model_path)
+    procs = [mpc.Process(target=_worker, args=(r, world, port, q, model_path, cfg)) for r in range(world)]
     for p in procs:
         p.start()
-    res = dict(q.get(timeout=600) for _ in procs)
+    res = dict(q.get(timeout=900) for _ in procs)
     for p in procs:
         p.join(timeout=120)
-    for r in (0, 1):
+    for r in range(world):
         assert not isinstance(res[r], str), res[r]
         assert res[r]["status"] == 0
-        assert res[r]["file_equals_sliced"]
-    a, b, ref = res[0], res[1], res[0]["ref"]
+        if model_path:
+            assert res[r]["file_equals_sliced"]
+    a, ref = res[0], res[0]["ref"]
     # every rank holds the same token, margin and (gathered) logits, bit for bit
-    assert a["tokens"] == b["tokens"] and a["run"] == b["run"] and a["margin"] == b["margin"]
+    for r in range(1, world):
+        b = res[r]
+        assert a["tokens"] == b["tokens"] and a["run"] == b["run"] and a["margin"] == b["margin"]
+        for la, lb in zip(a["logits"], b["logits"]):
+            assert np.array_equal(la.view(np.uint32), lb.view(np.uint32))
+        (oa, ma, la), (ob, mb, lb) = a["batch"], b["batch"]
+        assert oa == ob and ma == mb and np.array_equal(la.view(np.uint32), lb.view(np.uint32))
+        assert a["batch2"] == b["batch2"]
     assert a["run"] == a["tokens"]
-    for la, lb in zip(a["logits"], b["logits"]):
-        assert np.array_equal(la.view(np.uint32), lb.view(np.uint32))
-    # the batch pass: identical on both ranks, and equal to the single-GPU pass up to the summation order
-    (oa, ma, la), (ob, mb, lb), (o1, m1, l1) = a["batch"], b["batch"], ref["batch"]
-    assert oa == ob and ma == mb and np.array_equal(la.view(np.uint32), lb.view(np.uint32))
+    # the batch pass equals the single-GPU pass up to the summation order
+    (oa, ma, la), (o1, m1, l1) = a["batch"], ref["batch"]
     err = float(np.max(np.abs(la - l1)) / np.sqrt(np.mean(l1.astype(np.float64) ** 2)))
     assert err < 3e-3, err
     for i in range(len(BATCH_TOKS)):
         if oa[i] != o1[i]:
             assert m1[i] <= 4 * float(np.max(np.abs(la - l1))), (i, oa[i], o1[i], m1[i])
-    assert a["batch2"] == b["batch2"]
     for i in range(2):   # the same two positions through the other path: same token unless the margin is tiny
         if a["batch2"][0][i] != oa[i]:
             assert ma[i] <= 1e-3, (i, a["batch2"][0][i], oa[i], ma[i])
@@ -210,7 +222,7 @@ def test_two_rank_decoder_matches_single_gpu(tmp_path):
     for s in range(STEPS):
         want, got = ref["logits"][s], a["logits"][s]
         err = float(np.max(np.abs(got - want)) / np.sqrt(np.mean(want.astype(np.float64) ** 2)))
-        assert err < 3e-3, (s, err)
+        assert err < 3e-3, (world, s, err)
         if a["tokens"][s] != ref["tokens"][s]:
             assert ref["margin"][s] <= 2 * float(np.max(np.abs(got - want))), (s, a["tokens"][s], ref["tokens"][s])
             break   # the sequences differ from here on
@@ -260,27 +272,30 @@ def _seq_worker(rank, world, port, q_out):
         q_out.put((rank, "ERROR " + traceback.format_exc()))
 
 
-def test_sequence_parallel_attention_two_ranks():
-    if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
-        pytest.skip("needs 2 GPUs")
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_sequence_parallel_attention(world):
+    if not torch.cuda.is_available() or torch.cuda.device_count() < world:
+        pytest.skip("needs %d GPUs" % world)
     import torch.multiprocessing as mp
     mpc = mp.get_context("spawn")
     q = mpc.Queue()
     port = _free_port()
-    procs = [mpc.Process(target=_seq_worker, args=(r, 2, port, q)) for r in range(2)]
+    procs = [mpc.Process(target=_seq_worker, args=(r, world, port, q)) for r in range(world)]
     for p in procs:
         p.start()
     res = dict(q.get(timeout=600) for _ in procs)
     for p in procs:
         p.join(timeout=120)
-    for r in (0, 1):
+    for r in range(world):
         assert not isinstance(res[r], str), res[r]
         assert res[r]["status"] == 0
     for key in ((32768, 1), (4096 + 333, 4)):
         a, err_a = res[0][key]
-        b, err_b = res[1][key]
-        assert np.array_equal(a.view(np.uint32), b.view(np.uint32))     # both ranks: identical bits
-        assert err_a <= 1e-5 and err_b <= 1e-5, (key, err_a, err_b)      # = one GPU over all keys (f32 reassociation)
+        assert err_a <= 1e-5, (key, err_a)                               # = one GPU over all keys (f32 reassociation)
+        for r in range(1, world):
+            b, err_b = res[r][key]
+            assert np.array_equal(a.view(np.uint32), b.view(np.uint32))  # all ranks: identical bits
+            assert err_b <= 1e-5, (key, r, err_b)
 
 
 def _moe_worker(rank, world, port, q_out):
@@ -342,29 +357,33 @@ def _moe_worker(rank, world, port, q_out):
         q_out.put((rank, "ERROR " + traceback.format_exc()))
 
 
-def test_two_rank_expert_parallel_moe_matches_single_gpu():
-    """Expert parallelism of the MoE block (4 of the 8 experts per GPU): the ranks'
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_expert_parallel_moe_matches_single_gpu(world):
+    """Expert parallelism of the MoE block (8 / world of the 8 experts per GPU): the ranks'
     outputs are identical bits and equal the single-GPU block up to the order of one sum."""
-    if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
-        pytest.skip("needs 2 GPUs")
+    if not torch.cuda.is_available() or torch.cuda.device_count() < world:
+        pytest.skip("needs %d GPUs" % world)
     import torch.multiprocessing as mp
     mpc = mp.get_context("spawn")
     q = mpc.Queue()
     port = _free_port()
-    procs = [mpc.Process(target=_moe_worker, args=(r, 2, port, q)) for r in range(2)]
+    procs = [mpc.Process(target=_moe_worker, args=(r, world, port, q)) for r in range(world)]
     for p in procs:
         p.start()
     res = dict(q.get(timeout=600) for _ in procs)
     for p in procs:
         p.join(timeout=120)
-    for r in (0, 1):
+    for r in range(world):
         assert not isinstance(res[r], str), res[r]
         assert res[r]["status"] == 0
-    a, b = res[0], res[1]
-    assert np.array_equal(a["ids"], b["ids"]) and np.array_equal(a["ids"], a["ref_ids"])
-    assert len(set(a["ids"].ravel() // 4)) == 2            # both ranks' experts are in use
-    for ya, yb in zip(a["y"], b["y"]):
-        assert np.array_equal(ya.view(np.uint32), yb.view(np.uint32))
+    a = res[0]
+    assert np.array_equal(a["ids"], a["ref_ids"])
+    assert len(set(a["ids"].ravel() // (8 // world))) >= 2   # more than one rank's experts are in use
+    for r in range(1, world):
+        b = res[r]
+        assert np.array_equal(a["ids"], b["ids"])
+        for ya, yb in zip(a["y"], b["y"]):
+            assert np.array_equal(ya.view(np.uint32), yb.view(np.uint32))
     ref = a["ref"]
     scale = np.sqrt(np.mean(ref.astype(np.float64) ** 2))
     assert np.max(np.abs(a["y"][0] - ref)) <= 1e-5 * scale
