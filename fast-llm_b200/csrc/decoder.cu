@@ -228,10 +228,12 @@ static int enqueue_step(fl_b200_decoder *d, cudaStream_t s, uint32_t *n_launch, 
     };
     // One GPU: the four matvecs between two attention launches, O -> gate|up -> down -> the next layer's Q/K/V (or the
     // head), go out as ONE launch with grid-wide barriers between them (launch_matvec_tc_chain): the weights of the next
-    // matvec stream into shared memory while the current one drains and the next activation is built. FLB_CHAIN=0, a
-    // tensor-parallel decoder (its exchange launches sit between the matvecs) or a shape the chain does not take: one
-    // launch per matvec.
-    static const bool chain_on = !(getenv("FLB_CHAIN") && getenv("FLB_CHAIN")[0] == '0');
+    // matvec stream into shared memory while the current one drains and the next activation is built. Off by default
+    // (FLB_CHAIN=1 switches it on): measured on the 8B-shape step it is SLOWER than one launch per matvec with
+    // programmatic dependent launch (391 against 441 tokens/s): a phase boundary inside the kernel costs about 3 us
+    // more than a kernel boundary. A tensor-parallel decoder (its exchange launches sit between the matvecs) and shapes
+    // the chain does not take always go out as one launch per matvec.
+    static const bool chain_on = getenv("FLB_CHAIN") && getenv("FLB_CHAIN")[0] == '1';
     bool qkv_done = false;   // the Q/K/V of the coming layer already went out with the previous layer's chain
     for (uint32_t l = 0; l < c.n_layer; ++l) {
         if (!qkv_done) {

@@ -78,6 +78,8 @@ struct MatvecArgs {
 // 2-D tiled TMA descriptor over a row-major array (rows x dim0 elements, row pitch stride_bytes).
 cudaError_t tensor_map_2d(CUtensorMap *m, uint32_t elem_bytes, const void *base, uint64_t dim0, uint64_t rows,
                           uint64_t stride_bytes, uint32_t box0, uint32_t box_rows, bool swizzle128);
+cudaError_t tensor_map_lines_swz(CUtensorMap *m, const void *base, uint64_t rows, uint64_t pitch, uint32_t box_lines,
+                                 uint32_t box_rows);   // [rows][pitch / 128][128 bytes], 128-byte swizzle (matvec.cu)
 cudaError_t launch_matvec(const MatvecArgs &a, int sms, cudaStream_t stream);
 // Q4_K / Q6_K launches that qualify run on the tensor-core streaming kernel (matvec_tc.cu).
 bool matvec_tc_eligible(const MatvecArgs &a);

@@ -815,6 +815,27 @@ cudaError_t tensor_map_2d(CUtensorMap *m, uint32_t elem_bytes, const void *base,
     return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
 }
 
+// A row-major byte array of rows whose pitch is a multiple of 128 bytes, seen as [rows][pitch / 128][128 bytes] with
+// the 128-byte swizzle: a box of box_rows x box_lines lines lands in shared memory as lines of 128 bytes whose
+// 16-byte chunks are permuted by the line index (chunk ^ (line & 7)), so that the same chunk of 8 consecutive
+// rows falls into 8 different bank groups whatever the row pitch is.
+cudaError_t tensor_map_lines_swz(CUtensorMap *m, const void *base, uint64_t rows, uint64_t pitch, uint32_t box_lines,
+                                 uint32_t box_rows) {
+    if (!g_encode) {
+        const cudaError_t e = matvec_init();
+        if (e != cudaSuccess) return e;
+    }
+    if (pitch % 128 != 0) return cudaErrorInvalidValue;
+    const cuuint64_t gdim[3] = {16, pitch / 128, rows};      // 8-byte elements per line, lines per row, rows
+    const cuuint64_t gstride[2] = {128, pitch};
+    const cuuint32_t box[3] = {16, box_lines, box_rows};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    const CUresult r = g_encode(m, CU_TENSOR_MAP_DATA_TYPE_UINT64, 3, const_cast<void *>(base), gdim, gstride, box, estr,
+                                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
+}
+
 cudaError_t launch_matvec(const MatvecArgs &a, int sms, cudaStream_t stream) {
     if (a.n_tensors < 1 || a.n_tensors > 4 || a.cols == 0) return cudaErrorInvalidValue;
     if (matvec_tc_eligible(a)) return launch_matvec_tc(a, sms, stream);

@@ -44,11 +44,20 @@ namespace {
 
 constexpr int kCW = 8;                          // consumer warps per group (one per super-block of a segment)
 constexpr uint32_t kSeg4 = 8 * 144, kSeg6 = 8 * 210, kSeg8 = 64 * 34;
-// Row pitch of a stage in shared memory: what a 2-D TMA box of 16 rows x one segment gives. Q6_K: 1680 bytes
-// (105 x 16: odd), which together with the per-t rotation of the word order makes the 32-bit loads conflict
-// free. Q4_K: 1152 bytes; the six 128-bit loads of a block see a two-way conflict, which is noise.
-constexpr uint32_t kPitch4 = kSeg4, kPitch6 = kSeg6, kPitch8 = kSeg8 + 16;   // Q8_0 (one bulk copy per row): 548 words = 4 mod 32
-constexpr uint32_t kSlot4 = 16 * kPitch4, kSlot6 = 16 * kPitch6, kSlot8 = 16 * kPitch8;
+// A stage of Q4_K / Q6_K rows arrives as ONE tiled TMA box (16 rows x the segment): one bulk copy per row was
+// measured to cost the TMA unit about 130 cycles each, which capped the stream at 2.6 TB/s. The row pitch in
+// shared memory is therefore the segment's own size.
+// Q6_K: 1680 bytes (105 x 16: odd), which with the per-t rotation of the word order makes the 32-bit loads
+// conflict free. Q4_K: 1152 = 9 x 128 bytes: plain, the block headers of 8 rows would collide 8-way and the
+// quants 2-way (measured 2.2 x the shared-memory wavefronts). The rows are therefore fetched as lines of 128 bytes
+// with the 128-byte swizzle (tensor_map_lines_swz), which spreads the same 16-byte chunk of 8 consecutive rows
+// over 8 bank groups; the consumer addresses chunk c of line l at l * 128 + ((c ^ (l & 7)) << 4). Rows whose
+// pitch in memory is not a multiple of 128 bytes (columns not a multiple of 2048) fall back to the plain box.
+// Q8_0 (a segment is wider than a box may be): one bulk copy per row, pitch + 16 (548 words = 4 mod 32).
+constexpr uint32_t kPitch4 = kSeg4, kPitch6 = kSeg6, kPitch8 = kSeg8 + 16;
+// ring slots are multiples of 1024 bytes: the swizzle pattern of a Q4_K stage is tied to the address
+constexpr uint32_t slot_round(uint32_t b) { return (b + 1023u) & ~1023u; }
+constexpr uint32_t kSlot4 = slot_round(16 * kPitch4), kSlot6 = slot_round(16 * kPitch6), kSlot8 = slot_round(16 * kPitch8);
 // 256-column blocks a half-warp of the prologue converts (bounds the column count: see matvec_tc_eligible)
 __host__ __device__ constexpr int max_blk_per_half_warp(int groups) { return groups == 1 ? 4 : 2; }
 
@@ -73,11 +82,17 @@ __device__ __forceinline__ void sts64(uint32_t addr, uint32_t a, uint32_t b) {
 __device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
-// 2-D tiled TMA load into shared memory; x counts 8-byte elements (a multiple of 2: the copy starts 16-byte aligned).
-__device__ __forceinline__ void tma_box(uint32_t dst, const CUtensorMap *map, uint32_t x, uint32_t y, uint64_t *bar) {
+// Tiled TMA loads into shared memory (2-D: x counts 8-byte elements, a multiple of 2; 3-D: lines of 128 bytes).
+__device__ __forceinline__ void tma_box2(uint32_t dst, const CUtensorMap *map, uint32_t x, uint32_t y, uint64_t *bar) {
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
         "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
+        : "memory");
+}
+__device__ __forceinline__ void tma_box3(uint32_t dst, const CUtensorMap *map, uint32_t line, uint32_t row, uint64_t *bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(dst),
+        "l"(map), "r"(0), "r"(line), "r"(row), "r"(smem_u32(bar))
         : "memory");
 }
 // All threads of the prologue (every warp but the producer) meet here.
@@ -106,9 +121,12 @@ __device__ __forceinline__ uint32_t hsub2_u32(uint32_t h, __half2 off) {
 __device__ __noinline__ bool mbar_wait_slow(uint64_t *bar, uint32_t parity, uint32_t *status) {
     return mbar_wait_bounded(bar, parity, status);
 }
-__device__ __forceinline__ bool mbar_wait_fast(uint64_t *bar, uint32_t parity, uint32_t *status) {
-    if (mbar_try_wait(bar, parity)) return true;
-    return mbar_wait_slow(bar, parity, status);
+// The form the consumer loops use: no exit out of the loop. `dead` (warp-uniform) is set when a wait ran out;
+// from then on the warp waits for nothing any more (its results are void, the status word says so) and the
+// launch still ends.
+__device__ __forceinline__ void mbar_wait_or_die(uint64_t *bar, uint32_t parity, uint32_t *status, bool &dead) {
+    if (dead || mbar_try_wait(bar, parity)) return;
+    dead = !mbar_wait_slow(bar, parity, status);
 }
 // byte K of w as a float without the conversion pipe (the byte under 0x4B000000 is 2^23 + byte)
 template <int K>
@@ -132,12 +150,12 @@ __device__ __forceinline__ uint32_t x6_off(uint32_t s, uint32_t lane8, uint32_t 
 }
 
 struct TcTensor {
-    CUtensorMap map;               // the packed tensor as [rows][pitch / 8] 8-byte elements; box = 16 (SwiGLU: 8) rows x one segment
+    CUtensorMap map;               // Q4_K / Q6_K: the tiled view a stage's box is cut from
     const uint8_t *w;
     float *y;
     const float *resid;
     uint32_t rows, pitch, unit0;   // unit0: index of the tensor's first unit in the launch
-    int fmt;
+    int fmt, swz;                  // swz: Q4_K rows fetched as swizzled 128-byte lines
 };
 
 // One matvec of a launch. A launch is a sequence of up to four phases that depend on one another
@@ -232,21 +250,25 @@ __device__ __forceinline__ int unit_tensor(const TcPhase &a, uint32_t u) {
 // volatile asm statements, which the compiler keeps in program order), so that their latency overlaps.
 // xaddr: this lane's 16-byte B slot of word 0 (lanes that feed no column of B point at 16 zero bytes and
 // use a stride of 0).
-__device__ __forceinline__ void q4k_block(uint32_t r0, uint32_t r1, uint32_t t, uint32_t xaddr, uint32_t xstride, float2 sx,
-                                          float &out0, float &out1) {
-    const uint4 wa0 = lds128(r0 + 16 + 32 * t), wa1 = lds128(r1 + 16 + 32 * t);
+// Byte offset o of a row as the stage holds it: as it is, or in the swizzled 128-byte lines (see kPitch4).
+__device__ __forceinline__ uint32_t q4_row_off(uint32_t o, uint32_t g, bool swz) {
+    return swz ? (o & ~127u) + ((((o >> 4) ^ (g + (o >> 7))) & 7u) << 4) : o;
+}
+// r0: row g of the stage; row g + 8 is 8 * kPitch4 further (the same swizzle: 72 lines further). oh / oa / ob: offsets
+// of the block's header and of the two 16-byte halves of chunk t in the row (q4_row_off).
+__device__ __forceinline__ void q4k_block(uint32_t r0, uint32_t oh, uint32_t oa, uint32_t ob, uint32_t t, uint32_t xaddr,
+                                          uint32_t xstride, float2 sx, float &out0, float &out1) {
+    const uint32_t r1 = r0 + 8 * kPitch4;
+    const uint4 wa0 = lds128(r0 + oa), wa1 = lds128(r1 + oa);
     uint4 bx[8];
 #pragma unroll
     for (int j = 0; j < 4; ++j) bx[j] = lds128(xaddr + j * xstride);
-    const uint4 wb0 = lds128(r0 + 32 + 32 * t), wb1 = lds128(r1 + 32 + 32 * t);
+    const uint4 wb0 = lds128(r0 + ob), wb1 = lds128(r1 + ob);
 #pragma unroll
     for (int j = 4; j < 8; ++j) bx[j] = lds128(xaddr + j * xstride);
-    const uint4 h0 = lds128(r0), h1 = lds128(r1);
-    float cL[2][4], cH[2][4];
-#pragma unroll
-    for (int i = 0; i < 2; ++i)
-#pragma unroll
-        for (int k = 0; k < 4; ++k) cL[i][k] = cH[i][k] = 0.f;
+    const uint4 h0 = lds128(r0 + oh), h1 = lds128(r1 + oh);
+    // two accumulator chains per nibble kind: a chain of eight dependent tensor-core instructions measured 25 % slower
+    float cL[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}}, cH[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
     // A quant lands in the mantissa of a constant: bits 0..3 under 0x6400 give 1024 + q, bits 4..7 under 0x5400 give
     // 64 + q; the constant is taken off again exactly (f16 subtraction on the other pipe). Bytes 1 and 3 come
     // down by one shift. Five logic operations and four subtractions per 8 weights.
@@ -456,8 +478,8 @@ __device__ __forceinline__ bool grid_barrier(GridBar *b, uint32_t nblocks, uint3
 // between; the producer does not take part in the barriers: the weights of the next phase are already
 // streaming into the ring while the current phase drains and the next activation is built.
 template <int G>
-__global__ void __launch_bounds__((G * kCW + 2) * 32, 1) matvec_tc_kernel(const __grid_constant__ TcArgs a) {
-    extern __shared__ __align__(128) uint8_t smem_raw[];
+__global__ void __launch_bounds__((G * kCW + 2) * 32) matvec_tc_kernel(const __grid_constant__ TcArgs a) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
     constexpr uint32_t kConsumers = G * kCW;
     constexpr uint32_t kProducer = kConsumers, kFinal = kConsumers + 1;
     constexpr uint32_t kPrologueThreads = (kConsumers + 1) * 32;
@@ -509,14 +531,14 @@ __global__ void __launch_bounds__((G * kCW + 2) * 32, 1) matvec_tc_kernel(const 
                 const uint32_t segb = fmt == FMT_Q4_K ? kSeg4 : fmt == FMT_Q6_K ? kSeg6 : kSeg8;
                 const uint32_t rp = fmt == FMT_Q4_K ? kPitch4 : fmt == FMT_Q6_K ? kPitch6 : kPitch8;
                 const uint32_t nvalid = __popc(__ballot_sync(0xffffffffu, valid));
-                const uint32_t row0 = ph.swiglu ? 8 * u : 16 * (u - ph.t[ph.swiglu ? 0 : unit_tensor(ph, u)].unit0);
                 const int ti = ph.swiglu ? 0 : unit_tensor(ph, u);
+                const uint32_t row0 = ph.swiglu ? 8 * u : 16 * (u - ph.t[ti].unit0);
                 for (uint32_t seg = 0; seg < nseg; ++seg) {
                     const uint32_t off = seg * segb;
                     if (!mbar_wait_bounded(&sm.empty[slot], par, a.status)) return;
                     fence_proxy_async_smem();
                     const uint32_t dst = ring + slot * a.slot_bytes;
-                    if (fmt == FMT_Q8_0) {   // one bulk copy per row (a segment is wider than a TMA box may be)
+                    if (fmt == FMT_Q8_0) {   // one bulk copy per row
                         const uint32_t bytes = min(segb, pitch - off);   // pitch and off are multiples of 16
                         if (lane == 0) mbar_arrive_expect_tx(&sm.full[slot], nvalid * bytes);
                         __syncwarp();
@@ -525,11 +547,13 @@ __global__ void __launch_bounds__((G * kCW + 2) * 32, 1) matvec_tc_kernel(const 
                         // one box of 16 rows x the segment (SwiGLU: 8 gate rows, then 8 up rows); rows past the end of the
                         // tensor and blocks past the end of a row arrive as zeros and count as bytes all the same
                         mbar_arrive_expect_tx(&sm.full[slot], 16 * segb);
-                        if (ph.swiglu) {
-                            tma_box(dst, &ph.t[0].map, off / 8, row0, &sm.full[slot]);
-                            tma_box(dst + 8 * segb, &ph.t[1].map, off / 8, row0, &sm.full[slot]);
+                        const TcTensor &t0 = ph.t[ti];
+                        if (t0.swz) {
+                            tma_box3(dst, &t0.map, off / 128, row0, &sm.full[slot]);
+                            if (ph.swiglu) tma_box3(dst + 8 * segb, &ph.t[1].map, off / 128, row0, &sm.full[slot]);
                         } else {
-                            tma_box(dst, &ph.t[ti].map, off / 8, row0, &sm.full[slot]);
+                            tma_box2(dst, &t0.map, off / 8, row0, &sm.full[slot]);
+                            if (ph.swiglu) tma_box2(dst + 8 * segb, &ph.t[1].map, off / 8, row0, &sm.full[slot]);
                         }
                     }
                     if (++slot == S) { slot = 0; par ^= 1u; }
@@ -540,6 +564,9 @@ __global__ void __launch_bounds__((G * kCW + 2) * 32, 1) matvec_tc_kernel(const 
     }
 
     uint32_t it_base = 0;    // stages of this CTA in earlier phases
+    // consumer warps: the next stage of this warp's group (index over the whole launch), its ring slot and parity
+    uint32_t c_it = (warp / kCW) % G, c_slot = c_it % a.nslots, c_par = 0;
+    bool dead = false;       // a bounded wait of this warp ran out
     uint32_t kk = 0;         // units of this CTA so far (all phases): selects the reduction buffer
 #pragma unroll 1
     for (int p = 0; p < a.n_phases; ++p) {
@@ -743,47 +770,49 @@ __global__ void __launch_bounds__((G * kCW + 2) * 32, 1) matvec_tc_kernel(const 
             }
         } else {
             // ---- consumers ----
-            const uint32_t grp = warp / kCW, w = warp % kCW;
+            const uint32_t w = warp % kCW;
             const uint32_t g = lane >> 2, t = lane & 3u;
             const bool has_b = (g >> 1) == t;   // this lane feeds column g of the B operand; the others feed zeros
             const uint32_t lane8 = 2 * t + (g & 1u);
             const uint32_t zero16 = smem_u32(sm.zero);
             const uint32_t x4 = ph.use_q4 ? smem_u32(sm.x4) + lane8 * 16u : 0u, x6 = ph.use_q6 ? smem_u32(sm.x6) + lane8 * 16u : 0u;
             const uint32_t xstride = has_b ? 128u : 0u;
+            const uint32_t xb = has_b ? 1024u : 0u;   // lanes that feed zeros stay on the zero slot
+            const uint32_t xa4 = has_b ? x4 : zero16, xa6 = has_b ? x6 : zero16;
             for (uint32_t k = 0; k < my_units; ++k, ++kk) {
                 const uint32_t u = blockIdx.x + k * gridDim.x;
                 const int fmt = ph.swiglu ? ph.t[0].fmt : ph.t[unit_tensor(ph, u)].fmt;
                 float acc0 = 0.f, acc1 = 0.f;
-                // this group's stages of unit k: stage index it = it_base + k * nseg + seg over the whole launch, it % G == grp
-                const uint32_t it0 = it_base + k * nseg;
-                uint32_t seg = (grp + G - it0 % G) % G;
-                const uint32_t xb = has_b ? 1024u : 0u;   // lanes that feed zeros stay on the zero slot
+                // this group's stages of unit k: those of its stage sequence (grp, grp + G, ... over the whole launch)
+                // that fall into [it_base + k nseg, it_base + (k + 1) nseg)
+                const uint32_t it0 = it_base + k * nseg, it1 = it0 + nseg;
                 if (fmt == FMT_Q4_K) {
-                    const uint32_t xa4 = has_b ? x4 : zero16;
-                    for (; seg < nseg; seg += G) {
-                        const uint32_t it = it0 + seg, slot = it % S, par = (it / S) & 1u;
-                        const uint32_t blk = seg * 8 + w;
-                        if (!mbar_wait_fast(&sm.full[slot], par, a.status)) return;
+                    const bool swz = ph.t[ph.swiglu ? 0 : unit_tensor(ph, u)].swz != 0;
+                    const uint32_t oh = q4_row_off(w * 144u, g, swz), oa = q4_row_off(w * 144u + 16u + 32u * t, g, swz),
+                                   ob = q4_row_off(w * 144u + 32u + 32u * t, g, swz);
+                    for (; c_it < it1; c_it += G) {
+                        const uint32_t blk = (c_it - it0) * 8 + w;
+                        mbar_wait_or_die(&sm.full[c_slot], c_par, a.status, dead);
                         if (blk < nblk) {
-                            const uint32_t r0 = ring + slot * a.slot_bytes + g * kPitch4 + w * 144u;
+                            const uint32_t r0 = ring + c_slot * a.slot_bytes + g * kPitch4;
                             const float2 sx = *reinterpret_cast<const float2 *>(sm.s4 + blk * 8 + 2 * t);
                             float o0, o1;
-                            q4k_block(r0, r0 + 8 * kPitch4, t, xa4 + blk * xb, xstride, sx, o0, o1);
+                            q4k_block(r0, oh, oa, ob, t, xa4 + blk * xb, xstride, sx, o0, o1);
                             const float xs = sm.xs[blk];
                             acc0 = fmaf(xs, o0, acc0);
                             acc1 = fmaf(xs, o1, acc1);
                         }
                         __syncwarp();
-                        if (lane == 0) mbar_arrive(&sm.empty[slot]);
+                        if (lane == 0) mbar_arrive(&sm.empty[c_slot]);
+                        c_slot += G;
+                        if (c_slot >= S) { c_slot -= S; c_par ^= 1u; }
                     }
                 } else if (fmt == FMT_Q8_0) {
-                    const uint32_t xa4 = has_b ? x4 : zero16;
-                    for (; seg < nseg; seg += G) {
-                        const uint32_t it = it0 + seg, slot = it % S, par = (it / S) & 1u;
-                        const uint32_t blk = seg * 8 + w;
-                        if (!mbar_wait_fast(&sm.full[slot], par, a.status)) return;
+                    for (; c_it < it1; c_it += G) {
+                        const uint32_t blk = (c_it - it0) * 8 + w;
+                        mbar_wait_or_die(&sm.full[c_slot], c_par, a.status, dead);
                         if (blk < nblk) {
-                            const uint32_t r0 = ring + slot * a.slot_bytes + g * kPitch8 + w * 272u + t * 68u;
+                            const uint32_t r0 = ring + c_slot * a.slot_bytes + g * kPitch8 + w * 272u + t * 68u;
                             float o0, o1;
                             q8_0_block(r0, r0 + 8 * kPitch8, xa4 + blk * xb, xstride, o0, o1);
                             const float xs = sm.xs[blk];
@@ -791,16 +820,16 @@ __global__ void __launch_bounds__((G * kCW + 2) * 32, 1) matvec_tc_kernel(const 
                             acc1 = fmaf(xs, o1, acc1);
                         }
                         __syncwarp();
-                        if (lane == 0) mbar_arrive(&sm.empty[slot]);
+                        if (lane == 0) mbar_arrive(&sm.empty[c_slot]);
+                        c_slot += G;
+                        if (c_slot >= S) { c_slot -= S; c_par ^= 1u; }
                     }
                 } else {
-                    const uint32_t xa6 = has_b ? x6 : zero16;
-                    for (; seg < nseg; seg += G) {
-                        const uint32_t it = it0 + seg, slot = it % S, par = (it / S) & 1u;
-                        const uint32_t blk = seg * 8 + w;
-                        if (!mbar_wait_fast(&sm.full[slot], par, a.status)) return;
+                    for (; c_it < it1; c_it += G) {
+                        const uint32_t blk = (c_it - it0) * 8 + w;
+                        mbar_wait_or_die(&sm.full[c_slot], c_par, a.status, dead);
                         if (blk < nblk) {
-                            const uint32_t r0 = ring + slot * a.slot_bytes + g * kPitch6 + w * 210u;
+                            const uint32_t r0 = ring + c_slot * a.slot_bytes + g * kPitch6 + w * 210u;
                             float o0, o1;
                             if (w & 1u) q6k_block<true>(r0 - 2, r0 + 8 * kPitch6 - 2, t, xa6 + blk * xb, xstride, o0, o1);
                             else q6k_block<false>(r0, r0 + 8 * kPitch6, t, xa6 + blk * xb, xstride, o0, o1);
@@ -809,7 +838,9 @@ __global__ void __launch_bounds__((G * kCW + 2) * 32, 1) matvec_tc_kernel(const 
                             acc1 = fmaf(xs, o1, acc1);
                         }
                         __syncwarp();
-                        if (lane == 0) mbar_arrive(&sm.empty[slot]);
+                        if (lane == 0) mbar_arrive(&sm.empty[c_slot]);
+                        c_slot += G;
+                        if (c_slot >= S) { c_slot -= S; c_par ^= 1u; }
                     }
                 }
                 // the unit's partial sums of rows g and g + 8 over this warp's lane columns
@@ -818,7 +849,7 @@ __global__ void __launch_bounds__((G * kCW + 2) * 32, 1) matvec_tc_kernel(const 
                 acc0 += __shfl_xor_sync(0xffffffffu, acc0, 2);
                 acc1 += __shfl_xor_sync(0xffffffffu, acc1, 2);
                 const uint32_t buf = kk & 1u;
-                if (!mbar_wait_fast(&sm.red_empty[buf], ((kk >> 1) & 1u) ^ 1u, a.status)) return;
+                mbar_wait_or_die(&sm.red_empty[buf], ((kk >> 1) & 1u) ^ 1u, a.status, dead);
                 if (t == 0) {
                     float *pp = sm.red + (buf * kConsumers + warp) * 16;
                     pp[g] = acc0;
@@ -833,9 +864,11 @@ __global__ void __launch_bounds__((G * kCW + 2) * 32, 1) matvec_tc_kernel(const 
     if (warp == kFinal && lane == 0) trace_max(a.trace, 3);
 }
 
+// Consumer groups per CTA: 2 (16 consumer warps, 96 registers each) measured 15 % faster than 1 (8 warps, 168
+// registers) on the 8B-shape step; FLB_TC_GROUPS=1 selects the other instantiation for comparison.
 int tc_groups() {
-    static const int v = getenv("FLB_TC_GROUPS") ? atoi(getenv("FLB_TC_GROUPS")) : 1;
-    return v == 2 ? 2 : 1;
+    static const int v = getenv("FLB_TC_GROUPS") ? atoi(getenv("FLB_TC_GROUPS")) : 2;
+    return v == 1 ? 1 : 2;
 }
 
 } // namespace
@@ -867,7 +900,7 @@ bool matvec_tc_eligible(const MatvecArgs &a) {
     }
     if (a.swiglu && (a.n_tensors != 2 || a.t[0].rows != a.t[1].rows || a.t[0].fmt != a.t[1].fmt || a.accumulate)) return false;
     const uint32_t slot = q8 ? kSlot8 : q6 ? kSlot6 : kSlot4;
-    return tc_head_bytes(2, groups) + tc_x_bytes(a.cols, q4, q6) + 128 + 2u * slot <= 227 * 1024 - 1024;
+    return tc_head_bytes(2, groups) + tc_x_bytes(a.cols, q4, q6) + 1024 + 2u * slot <= 227 * 1024 - 1024;
 }
 
 // One launch of n dependent matvecs (phase i + 1 consumes what phase i writes). n = 1: a plain launch.
@@ -895,13 +928,15 @@ cudaError_t launch_matvec_tc_chain(const MatvecArgs *args, int n, int sms, cudaS
             ph.t[i].pitch = t.pitch ? t.pitch : (uint32_t)row_bytes(t.fmt, a.cols);
             ph.t[i].unit0 = units;
             units += (t.rows + 15) / 16;
-            if (t.fmt != FMT_Q8_0) {
-                const uint32_t segb = t.fmt == FMT_Q4_K ? kSeg4 : kSeg6;
-                const cudaError_t e = tensor_map_2d(&ph.t[i].map, 8, t.w, ph.t[i].pitch / 8, t.rows, ph.t[i].pitch, segb / 8,
-                                                    a.swiglu ? 8 : 16, false);
+            if (t.fmt != FMT_Q8_0) {   // the tiled view the stages' boxes are cut from (16 rows; SwiGLU: 8 + 8)
+                const uint32_t segb = t.fmt == FMT_Q4_K ? kSeg4 : kSeg6, brows = a.swiglu ? 8 : 16;
+                ph.t[i].swz = (t.fmt == FMT_Q4_K && ph.t[i].pitch % 128 == 0) ? 1 : 0;
+                const cudaError_t e = ph.t[i].swz ? tensor_map_lines_swz(&ph.t[i].map, t.w, t.rows, ph.t[i].pitch, segb / 128, brows)
+                                                  : tensor_map_2d(&ph.t[i].map, 8, t.w, ph.t[i].pitch / 8, t.rows, ph.t[i].pitch,
+                                                                  segb / 8, brows, false);
                 if (e != cudaSuccess) return e;
             }
-            (t.fmt == FMT_Q6_K ? q6 : q4) = true;
+            (t.fmt == FMT_Q6_K ? q6 : q4) = true;   // Q8_0 uses the Q4_K layout of the activation
             any8 = any8 || t.fmt == FMT_Q8_0;
         }
         if (a.swiglu) units = (a.t[0].rows + 7) / 8;
@@ -920,13 +955,13 @@ cudaError_t launch_matvec_tc_chain(const MatvecArgs *args, int n, int sms, cudaS
     const size_t limit = 227 * 1024 - 1024;
     uint32_t nslots = 2;
     auto total = [&](uint32_t ns) {
-        const size_t ring_off = (tc_head_bytes(ns, groups) + xmax + 127) & ~(size_t)127;
+        const size_t ring_off = (tc_head_bytes(ns, groups) + xmax + 1023) & ~(size_t)1023;   // the swizzle pattern repeats every 1024 bytes
         return ring_off + (size_t)ns * k.slot_bytes;
     };
     if (total(nslots) > limit) return cudaErrorNotSupported;
     while (nslots < 32 && total(nslots + 1) <= limit) ++nslots;
     k.nslots = nslots;
-    k.ring_off = (uint32_t)((tc_head_bytes(nslots, groups) + xmax + 127) & ~(size_t)127);
+    k.ring_off = (uint32_t)((tc_head_bytes(nslots, groups) + xmax + 1023) & ~(size_t)1023);
     const size_t smem = total(nslots);
     uint32_t grid = max_units < (uint32_t)sms ? max_units : (uint32_t)sms;
     if (n > 1) {
