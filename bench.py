@@ -262,6 +262,8 @@ def kernel_case(case, steps, warmup):
     peak, _ = measured_peaks()
     if case == "moe":
         return moe_case(steps, warmup, peak)
+    if case == "attn-long" and int(os.environ.get("WORLD_SIZE", "1")) > 1:
+        return attn_long_multi(steps, warmup, peak, int(os.environ.get("RANK", "0")), int(os.environ["WORLD_SIZE"]))
     ctx = capi.Context(0)
     gen = torch.Generator(device="cuda")
     gen.manual_seed(1)
@@ -310,6 +312,86 @@ def kernel_case(case, steps, warmup):
         del k, v
         torch.cuda.empty_cache()
     print(json.dumps({"case": case, "kernel": "attn_decode_kernel", "peak_gbs": peak, "points": out, "status": ctx.status()}))
+
+
+def attn_long_multi(steps, warmup, peak, rank, world):
+    """The long-context configuration over the GPUs of one box (torchrun, one rank per GPU), both partitions:
+    "heads": rank r owns 8 / world KV heads with their query heads over ALL keys: no exchange at all;
+    "seq":   every rank owns all heads over a contiguous 1 / world of the keys and the ranks' (context, max, sum)
+             records are merged through peer memory (fl_b200_seqpar_combine).
+    Per point: time of the slowest rank (device events), this rank-set's per-GPU rate, and for "seq" the merge alone."""
+    import torch
+    import torch.distributed as dist
+    from fast_llm_b200 import capi, tp
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    ctx = capi.Context(local_rank)
+    dev = torch.device("cuda", local_rank)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(5 + rank)
+    nkv, nq, d = 8, 32, 128
+    scale = 1.0 / 128 ** 0.5
+    sp = tp.SeqParallel(ctx, dist, max_records=nq * 16)
+    points = []
+
+    def timed(fn):
+        for _ in range(warmup):
+            fn()
+        ctx.sync()
+        dist.barrier()
+        ctx.timer_start()
+        for _ in range(steps):
+            fn()
+        ms = ctx.timer_stop() / steps
+        t = torch.tensor([ms], dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item()) * 1e3   # us, slowest rank
+
+    for kv_len, batch in ((32768, 1), (32768, 4), (32768, 16), (65536, 1), (65536, 4), (65536, 16), (131072, 1), (131072, 4), (131072, 16)):
+        total = 2 * batch * nkv * kv_len * d * 2
+        pt = {"kv_len": kv_len, "batch": batch, "kv_bytes_total": total}
+        # ---- KV heads over the ranks (up to 8 ranks): nothing to exchange ----
+        if nkv % world == 0:
+            hk = nkv // world
+            k = (torch.randn((batch, hk, kv_len, d), device=dev, generator=gen) * scale).half()
+            v = (torch.randn((batch, hk, kv_len, d), device=dev, generator=gen) * scale).half()
+            q = torch.randn((batch, 4 * hk, d), device=dev, generator=gen)
+            o = torch.zeros((batch, 4 * hk, d), device=dev)
+            torch.cuda.synchronize(dev)
+            us = timed(lambda: ctx.attn_decode(q, k, v, 4 * hk, hk, d, kv_len, kv_len, batch, scale, o))
+            pt["heads"] = {"us": us, "per_gpu_gbs": total / world / us / 1e3, "per_gpu_frac_of_measured_hbm": total / world / us / 1e3 / peak,
+                           "exchange": "none"}
+            del k, v
+        # ---- the keys over the ranks: every rank all heads, 1 / world of the positions, then the merge ----
+        lo, hi = kv_len * rank // world, kv_len * (rank + 1) // world
+        k = (torch.randn((batch, nkv, hi - lo, d), device=dev, generator=gen) * scale).half()
+        v = (torch.randn((batch, nkv, hi - lo, d), device=dev, generator=gen) * scale).half()
+        q = torch.randn((batch, nq, d), device=dev, generator=gen)
+        ol = torch.zeros((batch, nq, d), device=dev)
+        lse = torch.zeros((batch, nq, 2), device=dev)
+        o = torch.zeros((batch, nq, d), device=dev)
+        torch.cuda.synchronize(dev)
+
+        def both():
+            ctx.attn_decode_lse(q, k, v, nq, nkv, d, hi - lo, hi - lo, batch, scale, ol, lse)
+            sp.combine(ol, lse, batch * nq, o)
+        us = timed(both)
+        us_attn = timed(lambda: ctx.attn_decode_lse(q, k, v, nq, nkv, d, hi - lo, hi - lo, batch, scale, ol, lse))
+        pt["seq"] = {"us": us, "us_attention_alone": us_attn, "us_merge": us - us_attn, "per_gpu_gbs": total / world / us / 1e3,
+                     "per_gpu_frac_of_measured_hbm": total / world / us / 1e3 / peak,
+                     "exchange": "%d records of 130 floats to every rank" % (batch * nq)}
+        points.append(pt)
+        del k, v
+        torch.cuda.empty_cache()
+    status = ctx.status()
+    dist.barrier()
+    sp.close()
+    if rank == 0:
+        print(json.dumps({"case": "attn-long", "n_gpus": world, "kernel": "attn_decode_kernel + lse_combine_kernel", "peak_gbs": peak,
+                          "points": points, "status": status}))
+    ctx.close()
+    dist.destroy_process_group()
 
 
 def moe_case(steps, warmup, peak):

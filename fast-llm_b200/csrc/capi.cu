@@ -85,6 +85,8 @@ int fl_b200_create(int device, fl_b200_ctx **out) {
     CK(cudaMalloc(&c->small, 64));
     CK(matvec_init());
     CK(matvec_tc_init());
+    CK(matmul_tc_nx_init());
+    CK(cudaMalloc(&c->xq, matmul_tc_nx_scratch_bytes(18432, 8)));   // the widest activation the kernels take, 8 columns
     CK(attn_init());
     *out = c;
     return FL_B200_OK;
@@ -95,6 +97,7 @@ void fl_b200_destroy(fl_b200_ctx *c) {
     cudaSetDevice(c->device);
     cudaStreamSynchronize(c->stream);
     cudaFree(c->attn_part);
+    cudaFree(c->xq);
     for (void *p : c->retired) cudaFree(p);
     cudaFree(c->attn_tickets);
     cudaFree(c->argmax_scratch);
@@ -234,7 +237,19 @@ int flb::matmul(fl_b200_ctx *c, int fmt, const void *w, uint32_t rows, uint32_t 
     if (nx == 0) nx = 1;
     if (pitch == row_bytes(fmt, cols)) pitch = 0;   // packed rows
     uint32_t first_single = 0;   // columns from here on go through the one-column kernel
-    if (nx >= 2 && fmt == FL_B200_Q4_K && pitch == 0 && !expert_id) {
+    if (nx >= 2 && (fmt == FL_B200_Q4_K || fmt == FL_B200_Q6_K) && !expert_id && cols <= 18432) {
+        // verify batches, prompt chunks: up to 8 columns per pass over the weights on the tensor cores, either format
+        for (uint32_t p0 = 0; p0 < nx; p0 += 8) {
+            const uint32_t nt = nx - p0 < 8 ? nx - p0 : 8;
+            if (nt < 2 && p0 > 0) break;   // a last single column goes to the one-column kernel
+            const cudaError_t e = launch_matmul_tc_nx(fmt, w, rows, cols, pitch, x + (size_t)p0 * xstride, nt, xstride,
+                                                      y + (size_t)p0 * ystride, ystride, accumulate, c->xq, c->status, c->sms, c->stream);
+            if (e == cudaErrorNotSupported) break;   // the shape does not qualify (same answer for every chunk)
+            if (e != cudaSuccess) return cuda_err(e, "multi-column matmul launch");
+            first_single = p0 + nt;
+        }
+    }
+    if (first_single == 0 && nx >= 2 && fmt == FL_B200_Q4_K && pitch == 0 && !expert_id) {
         // verify batches: up to 8 columns per pass over the weights on the tensor-core kernel; a last
         // chunk of one column is left to the one-column kernel
         for (uint32_t p0 = 0; p0 + 2 <= nx; p0 += 8) {

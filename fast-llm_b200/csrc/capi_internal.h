@@ -22,6 +22,7 @@ struct fl_b200_ctx {
     std::vector<void *> retired;
     float *argmax_scratch = nullptr;
     void *small = nullptr;
+    uint8_t *xq = nullptr;               // converted activations of the multi-column matmul (fixed size, see fl_b200_create)
     uint32_t *grid_bar = nullptr;        // barrier state of the chained matvec launches (two words, zero between launches)
     uint64_t wait_limit_ns = 0;          // limit of the exchange kernels' waits for other ranks (0 = one second)
     void *stage = nullptr;               // device staging for the *_host entry points

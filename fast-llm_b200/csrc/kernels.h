@@ -89,6 +89,14 @@ cudaError_t launch_matvec_tc(const MatvecArgs &a, int sms, cudaStream_t stream);
 // when a phase does not qualify: launch them one by one then. args[0].grid_bar names the barrier state.
 cudaError_t launch_matvec_tc_chain(const MatvecArgs *args, int n, int sms, cudaStream_t stream);
 cudaError_t matvec_tc_init(void);
+// Several activation columns (P <= 8) in one pass over a Q4_K / Q6_K tensor on the tensor cores (matvec_tc_nx.cu):
+// y[p * ystride + r] (+)= dot(W[r], x + p * xstride). xq: device scratch of matmul_tc_nx_scratch_bytes(cols, P) bytes
+// that holds the converted activations during the call. cudaErrorNotSupported when the shape does not qualify.
+cudaError_t launch_matmul_tc_nx(int fmt, const void *w, uint32_t rows, uint32_t cols, uint32_t pitch, const float *x, uint32_t P,
+                                uint32_t xstride, float *y, uint32_t ystride, int accumulate, uint8_t *xq, uint32_t *status,
+                                int sms, cudaStream_t stream);
+size_t matmul_tc_nx_scratch_bytes(uint32_t cols, uint32_t P);
+cudaError_t matmul_tc_nx_init(void);
 // Q4_K launches that qualify run on the integer tensor-core kernel (matvec_mma.cu).
 bool matvec_mma_eligible(const MatvecArgs &a);
 cudaError_t launch_matvec_mma(const MatvecArgs &a, int sms, cudaStream_t stream);

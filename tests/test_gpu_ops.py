@@ -468,3 +468,51 @@ def test_exec_task_stream_dot(ctx, checker):
     t.w_bytes += 1                    # freeze() rule: w_bytes must equal rows * row_bytes
     with pytest.raises(capi.Fl200Error):
         ctx.exec_task(t)
+
+
+@pytest.mark.parametrize("fmt,rows,cols,nx", [
+    (capi.Q6_K, 1024, 4096, 2), (capi.Q6_K, 1024, 4096, 4), (capi.Q6_K, 4096, 4096, 8), (capi.Q6_K, 320, 4096, 9),
+    (capi.Q6_K, 512, 14336, 8),      # rows of ffn_down: the columns span several resident chunks of the activation
+    (capi.Q6_K, 100, 14336, 5), (capi.Q6_K, 37, 6144, 3),
+    (capi.Q4_K, 256, 14336, 8), (capi.Q4_K, 37, 2048, 3), (capi.Q4_K, 1029, 4096, 6), (capi.Q4_K, 64, 768, 2),
+])
+def test_stream_dot_multi_column_both_formats(ctx, checker, fmt, rows, cols, nx):
+    """Task::nx > 1 on Q6_K as well as Q4_K tensors (draft verification, prompt chunks): all columns in one pass over
+    the weights (up to 8 at a time); every column equals the reference's STREAM_DOT of that column, accumulate and
+    assign-after-zero alike; ragged row counts, column counts that are not a multiple of 2048, strides with gaps."""
+    rng = np.random.default_rng(7 * rows + cols + nx + fmt)
+    w = synth.quant_tensor(fmt, rng, rows, cols)
+    xstride, ystride = cols + 64, rows + 16
+    x = rng.standard_normal((nx, xstride)).astype(np.float32)
+    x[:, cols:] = np.nan                                   # the gap between columns is never read
+    x[1] *= 1000.0                                         # columns with very different scales
+    x[0, 300] *= 1e3                                       # and one outlier inside a block
+    y0 = rng.standard_normal((nx, ystride)).astype(np.float32)
+    want = y0.copy()
+    deq = checker.dequant(fmt, w, rows, cols).astype(np.float64)
+    for p in range(nx):
+        want[p, :rows] += checker.matvec(fmt, w, rows, cols, x[p, :cols].copy())
+    wd, xd, yd = dev(w), dev(x), dev(y0)
+    torch.cuda.synchronize()
+    ctx.matvec(fmt, wd, rows, cols, xd, yd, nx=nx, xstride=xstride, ystride=ystride)
+    ctx.sync()
+    assert ctx.status() == 0
+    got = yd.cpu().numpy()
+    assert np.array_equal(got[:, rows:], y0[:, rows:])     # nothing outside the rows is touched
+    for p in range(nx):
+        if p == 0:   # the outlier column: against the exact product (the f32 oracle rounds at the outlier's magnitude)
+            ref = y0[p, :rows] + deq @ x[p, :cols].astype(np.float64)
+            x0 = x[p, :cols].astype(np.float64); x0[300] = 0.0
+            base = deq @ x0
+            floor = 0.1 * np.sqrt(np.mean(base ** 2))
+            err = float(np.max(np.abs(got[p, :rows] - ref) / np.maximum(np.abs(base), floor)))
+            slack = float(np.max(np.abs(ref)) * 2.0 ** -22 / floor)
+            assert err <= MATVEC_RTOL + slack, (p, err, slack)
+        else:
+            assert rel_err(got[p, :rows] - y0[p, :rows], want[p, :rows] - y0[p, :rows]) <= MATVEC_RTOL, p
+    # run-to-run reproducible
+    yd2 = dev(y0)
+    torch.cuda.synchronize()
+    ctx.matvec(fmt, wd, rows, cols, xd, yd2, nx=nx, xstride=xstride, ystride=ystride)
+    ctx.sync()
+    assert np.array_equal(bits(yd2.cpu().numpy()), bits(got))
