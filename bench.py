@@ -438,21 +438,25 @@ def moe_case(steps, warmup, peak):
     ms = ctx.timer_stop() / steps
     ids = blk.routing(T)[0]
     mine = int(((ids >= first) & (ids < first + n)).sum())
+    distinct = len({int(e) for e in ids.ravel() if first <= int(e) < first + n})   # experts of this rank that were walked
     if dist:
-        t = torch.tensor([ms, float(mine)], dtype=torch.float64)
+        t = torch.tensor([ms, float(mine), float(distinct)], dtype=torch.float64)
         parts = [torch.zeros_like(t) for _ in range(world)]
         dist.all_gather(parts, t)
         ms = max(float(p[0]) for p in parts)
         slots = [int(p[1]) for p in parts]
+        experts = [int(p[2]) for p in parts]
     else:
-        slots = [mine]
+        slots, experts = [mine], [distinct]
     status = ctx.status()
     if rank == 0:
-        slot_bytes = 2 * F * capi.row_bytes(capi.Q4_K, E) + E * capi.row_bytes(capi.Q4_K, F)
+        expert_bytes = 2 * F * capi.row_bytes(capi.Q4_K, E) + E * capi.row_bytes(capi.Q4_K, F)
+        # algorithmic bytes: every DISTINCT expert a rank holds and somebody chose is read once per block
         print(json.dumps({"case": "moe", "n_gpus": world, "tokens": T, "experts": NE, "top_k": K, "ms_per_block": ms,
-                          "tokens_per_s": T / (ms * 1e-3), "slots_per_rank": slots, "bytes_per_slot": slot_bytes,
-                          "busiest_rank_gbs": max(slots) * slot_bytes / ms / 1e6,
-                          "busiest_rank_frac_of_measured_hbm": max(slots) * slot_bytes / ms / 1e6 / peak, "status": status}))
+                          "tokens_per_s": T / (ms * 1e-3), "slots_per_rank": slots, "distinct_experts_per_rank": experts,
+                          "bytes_per_expert": expert_bytes,
+                          "busiest_rank_gbs": max(experts) * expert_bytes / ms / 1e6,
+                          "busiest_rank_frac_of_measured_hbm": max(experts) * expert_bytes / ms / 1e6 / peak, "status": status}))
     if dist:
         dist.barrier()
     blk.close()

@@ -242,8 +242,11 @@ int flb::matmul(fl_b200_ctx *c, int fmt, const void *w, uint32_t rows, uint32_t 
         for (uint32_t p0 = 0; p0 < nx; p0 += 8) {
             const uint32_t nt = nx - p0 < 8 ? nx - p0 : 8;
             if (nt < 2 && p0 > 0) break;   // a last single column goes to the one-column kernel
-            const cudaError_t e = launch_matmul_tc_nx(fmt, w, rows, cols, pitch, x + (size_t)p0 * xstride, nt, xstride,
-                                                      y + (size_t)p0 * ystride, ystride, accumulate, c->xq, c->status, c->sms, c->stream);
+            NxCall nc{};
+            nc.fmt = fmt; nc.w = w; nc.rows = rows; nc.cols = cols; nc.pitch = pitch;
+            nc.x = x + (size_t)p0 * xstride; nc.P = nt; nc.xstride = xstride;
+            nc.y = y + (size_t)p0 * ystride; nc.ystride = ystride; nc.accumulate = accumulate;
+            const cudaError_t e = launch_matmul_tc_nx(nc, c->xq, c->status, c->sms, c->stream);
             if (e == cudaErrorNotSupported) break;   // the shape does not qualify (same answer for every chunk)
             if (e != cudaSuccess) return cuda_err(e, "multi-column matmul launch");
             first_single = p0 + nt;
@@ -541,7 +544,7 @@ int fl_b200_router_sel(fl_b200_ctx *c, const float *logits, uint32_t *ids, float
     if (!c || !logits || !ids || !gates) return set_err(FL_B200_ERR_ARG, "router_sel: null pointer");
     if (n_expert == 0 || n_expert > 256 || top_k == 0 || top_k > n_expert)
         return set_err(FL_B200_ERR_ARG, "router_sel: %u experts (1..256), top_k %u", n_expert, top_k);
-    return cuda_err(launch_router_sel(logits, ids, gates, n_expert, top_k, norm, scale, c->stream), "router_sel launch");
+    return cuda_err(launch_router_sel(logits, ids, gates, 1, n_expert, top_k, norm, scale, c->stream), "router_sel launch");
 }
 
 int fl_b200_wmerge(fl_b200_ctx *c, const float *parts, const float *gates, const float *add1, const float *add2,

@@ -40,40 +40,68 @@ __global__ void add2_kernel(const float *__restrict__ a, const float *__restrict
     if (i < n) y[i] = __fadd_rn(a[i], b[i]);
 }
 
-// fl_op_router_sel, decode_params.h:234-265: one thread follows the reference's
-// sequential algorithm literally (same order of sums, IEEE divisions, ties to
-// the lower index); n_expert <= 256 like the reference's stack array.
-__global__ void router_sel_kernel(const float *__restrict__ logits, uint32_t *ids, float *gates, uint32_t n_expert,
-                                  uint32_t top_k, uint32_t norm, float scale) {
-    if (threadIdx.x != 0 || blockIdx.x != 0) return;
+// Expert selection of the MoE router (fl_op_router_sel, src/runtime/decode_params.h:234-265): softmax over the
+// expert logits of a token, the top_k largest weights (ties go to the lower index), optionally renormalised
+// over the chosen ones. One warp per token, every token of the block in one launch. What the warp does in
+// parallel: the maximum, the exponentials, the divisions and each round's arg-max. What stays sequential,
+// because f32 sums depend on their order and the results have to equal the reference's bit for bit: the sum of
+// the exponentials (ascending expert index, one lane) and the sum of the chosen weights (selection order).
+// With expert parallelism (lids != nullptr) the kernel also writes, per (token, slot), the index of the expert
+// among this rank's experts [base, base + n_local) or the skip mark, and the gate or 0.
+constexpr int kRouterWarps = 4;
+__global__ void __launch_bounds__(kRouterWarps * 32) router_sel_kernel(const float *__restrict__ logits, uint32_t *ids, float *gates,
+                                                                     uint32_t *lids, float *mgates, uint32_t n_tok,
+                                                                     uint32_t n_expert, uint32_t top_k, uint32_t norm, float scale,
+                                                                     uint32_t base, uint32_t n_local) {
+    __shared__ float w_s[kRouterWarps][256], g_s[kRouterWarps][256];
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    const uint32_t tok = blockIdx.x * kRouterWarps + warp;
+    if (tok >= n_tok) return;
+    const float *l = logits + (size_t)tok * n_expert;
+    float *w = w_s[warp], *gk = g_s[warp];
     float mx = -1e30f;
-    for (uint32_t i = 0; i < n_expert; ++i)
-        if (logits[i] > mx) mx = logits[i];
-    float w[256];
+    for (uint32_t i = lane; i < n_expert; i += 32) mx = fmaxf(mx, l[i]);
+    mx = warp_max(mx);
+    for (uint32_t i = lane; i < n_expert; i += 32) w[i] = expf(__fsub_rn(l[i], mx));
+    __syncwarp();
     float sum = 0.f;
-    for (uint32_t i = 0; i < n_expert; ++i) {
-        w[i] = expf(__fsub_rn(logits[i], mx));
-        sum = __fadd_rn(sum, w[i]);
-    }
-    for (uint32_t i = 0; i < n_expert; ++i) w[i] = __fdiv_rn(w[i], sum);
+    if (lane == 0)
+        for (uint32_t i = 0; i < n_expert; ++i) sum = __fadd_rn(sum, w[i]);
+    sum = __shfl_sync(0xffffffffu, sum, 0);
+    for (uint32_t i = lane; i < n_expert; i += 32) w[i] = __fdiv_rn(w[i], sum);
+    __syncwarp();
     float tsum = 0.f;
     for (uint32_t k = 0; k < top_k; ++k) {
-        uint32_t best = 0;
+        // the largest weight not chosen yet; a chosen entry is overwritten with -2, below the starting value -1
         float bw = -1.f;
-        for (uint32_t i = 0; i < n_expert; ++i) {
-            bool taken = false;
-            for (uint32_t k2 = 0; k2 < k; ++k2)
-                if (ids[k2] == i) { taken = true; break; }
-            if (!taken && w[i] > bw) { bw = w[i]; best = i; }
+        uint32_t best = 0;
+        for (uint32_t i = lane; i < n_expert; i += 32)
+            if (w[i] > bw) { bw = w[i]; best = i; }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ow = __shfl_xor_sync(0xffffffffu, bw, o);
+            const uint32_t ob = __shfl_xor_sync(0xffffffffu, best, o);
+            if (ow > bw || (ow == bw && ob < best)) { bw = ow; best = ob; }
         }
-        ids[k] = best;
-        gates[k] = bw;
-        tsum = __fadd_rn(tsum, bw);
+        tsum = __fadd_rn(tsum, bw);   // every lane keeps the same running sum, in selection order
+        if (lane == 0) {
+            ids[(size_t)tok * top_k + k] = best;
+            gk[k] = bw;
+            if (bw >= 0.f) w[best] = -2.f;
+        }
+        __syncwarp();
     }
-    for (uint32_t k = 0; k < top_k; ++k) {
-        float g = gates[k];
+    for (uint32_t k = lane; k < top_k; k += 32) {
+        float g = gk[k];
         if (norm) g = __fdiv_rn(g, tsum);
-        gates[k] = __fmul_rn(g, scale);
+        g = __fmul_rn(g, scale);
+        gates[(size_t)tok * top_k + k] = g;
+        if (lids) {
+            const uint32_t e = ids[(size_t)tok * top_k + k];
+            const bool mine = e >= base && e - base < n_local;
+            lids[(size_t)tok * top_k + k] = mine ? e - base : kExpertSkip;
+            mgates[(size_t)tok * top_k + k] = mine ? g : 0.f;
+        }
     }
 }
 
@@ -100,6 +128,43 @@ __global__ void wmerge_kernel(const float *__restrict__ parts, const float *__re
     if (add1) acc = __fadd_rn(acc, add1[i]);
     if (add2) acc = __fadd_rn(acc, add2[i]);
     y[i] = acc;
+}
+
+// y[t][i] = sum_q (gates[t][q] * parts[t][q][i]), the arithmetic of fl_op_wmerge (decode_params.h:274-295) without its
+// residual terms, for every token of a block in one launch. grid (ceil(n / 256), n_tok).
+__global__ void wmerge_tokens_kernel(const float *__restrict__ parts, const float *__restrict__ gates, float *__restrict__ y,
+                                     uint32_t n_parts, uint32_t n) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x, t = blockIdx.y;
+    if (i >= n) return;
+    float acc = 0.f;
+    for (uint32_t q = 0; q < n_parts; ++q)
+        acc = __fadd_rn(acc, __fmul_rn(gates[(size_t)t * n_parts + q], parts[((size_t)t * n_parts + q) * n + i]));
+    y[(size_t)t * n + i] = __fmul_rn(acc, 1.0f);
+}
+
+// One warp: a stable counting sort of the pairs by local expert.
+__global__ void __launch_bounds__(32) group_by_expert_kernel(const uint32_t *__restrict__ lids, uint32_t n_pairs, uint32_t top_k,
+                                                             uint32_t n_local, uint32_t cap, uint32_t *__restrict__ cnt,
+                                                             uint32_t *__restrict__ tok_list, uint32_t *__restrict__ pair_list) {
+    const uint32_t lane = threadIdx.x;
+    for (uint32_t e = lane; e < n_local; e += 32) cnt[e] = 0;
+    __syncwarp();
+    for (uint32_t b = 0; b < n_pairs; b += 32) {
+        const uint32_t pair = b + lane;
+        const uint32_t e = pair < n_pairs ? lids[pair] : 0xFFFFFFFFu;
+        for (uint32_t x = 0; x < n_local; ++x) {
+            const uint32_t mask = __ballot_sync(0xffffffffu, e == x);
+            if (mask == 0) continue;
+            const uint32_t base = cnt[x];
+            if (e == x) {
+                const uint32_t pos = base + __popc(mask & ((1u << lane) - 1u));
+                if (pos < cap) { tok_list[(size_t)x * cap + pos] = pair / top_k; pair_list[(size_t)x * cap + pos] = pair; }
+            }
+            __syncwarp();
+            if (lane == 0) cnt[x] = min(base + __popc(mask), cap);
+            __syncwarp();
+        }
+    }
 }
 
 // fl_op_silu_mul, decode_params.h:267-272: (g / (1 + expf(-g))) * u
@@ -244,10 +309,13 @@ cudaError_t launch_add2(const float *a, const float *b, float *y, uint32_t n, cu
     return cudaGetLastError();
 }
 
-cudaError_t launch_router_sel(const float *logits, uint32_t *ids, float *gates, uint32_t n_expert, uint32_t top_k,
-                              uint32_t norm, float scale, cudaStream_t stream) {
-    if (n_expert == 0 || n_expert > 256 || top_k == 0 || top_k > n_expert) return cudaErrorInvalidValue;
-    router_sel_kernel<<<1, 32, 0, stream>>>(logits, ids, gates, n_expert, top_k, norm, scale);
+cudaError_t launch_router_sel(const float *logits, uint32_t *ids, float *gates, uint32_t n_tok, uint32_t n_expert, uint32_t top_k,
+                              uint32_t norm, float scale, cudaStream_t stream, uint32_t *lids, float *mgates, uint32_t base,
+                              uint32_t n_local) {
+    if (n_tok == 0 || n_expert == 0 || n_expert > 256 || top_k == 0 || top_k > n_expert) return cudaErrorInvalidValue;
+    if ((lids == nullptr) != (mgates == nullptr)) return cudaErrorInvalidValue;
+    router_sel_kernel<<<(n_tok + kRouterWarps - 1) / kRouterWarps, kRouterWarps * 32, 0, stream>>>(
+        logits, ids, gates, lids, mgates, n_tok, n_expert, top_k, norm, scale, base, n_local);
     return cudaGetLastError();
 }
 
@@ -255,6 +323,20 @@ cudaError_t launch_wmerge(const float *parts, const float *gates, const float *a
                           float scale, uint32_t n_parts, uint32_t n, uint32_t n_full, cudaStream_t stream) {
     if (n == 0 || n_parts == 0) return cudaErrorInvalidValue;
     wmerge_kernel<<<(n + 255) / 256, 256, 0, stream>>>(parts, gates, add1, add2, y, scale, n_parts, n, n_full);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_wmerge_tokens(const float *parts, const float *gates, float *y, uint32_t n_parts, uint32_t n, uint32_t n_tok,
+                                 cudaStream_t stream) {
+    if (n == 0 || n_parts == 0 || n_tok == 0) return cudaErrorInvalidValue;
+    wmerge_tokens_kernel<<<dim3((n + 255) / 256, n_tok), 256, 0, stream>>>(parts, gates, y, n_parts, n);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_group_by_expert(const uint32_t *lids, uint32_t n_pairs, uint32_t top_k, uint32_t n_local, uint32_t cap,
+                                   uint32_t *cnt, uint32_t *tok_list, uint32_t *pair_list, cudaStream_t stream) {
+    if (n_pairs == 0 || top_k == 0 || n_local == 0 || cap == 0) return cudaErrorInvalidValue;
+    group_by_expert_kernel<<<1, 32, 0, stream>>>(lids, n_pairs, top_k, n_local, cap, cnt, tok_list, pair_list);
     return cudaGetLastError();
 }
 

@@ -92,9 +92,23 @@ cudaError_t matvec_tc_init(void);
 // Several activation columns (P <= 8) in one pass over a Q4_K / Q6_K tensor on the tensor cores (matvec_tc_nx.cu):
 // y[p * ystride + r] (+)= dot(W[r], x + p * xstride). xq: device scratch of matmul_tc_nx_scratch_bytes(cols, P) bytes
 // that holds the converted activations during the call. cudaErrorNotSupported when the shape does not qualify.
-cudaError_t launch_matmul_tc_nx(int fmt, const void *w, uint32_t rows, uint32_t cols, uint32_t pitch, const float *x, uint32_t P,
-                                uint32_t xstride, float *y, uint32_t ystride, int accumulate, uint8_t *xq, uint32_t *status,
-                                int sms, cudaStream_t stream);
+struct NxCall {
+    int fmt;
+    const void *w;           // rows x cols, GGUF block layout
+    uint32_t rows, cols, pitch;   // pitch 0 = packed rows
+    const float *x;          // columns: rows of x, xstride floats apart
+    const float *x2;         // optional: the column is SiLU(x) * x2 (same stride)
+    uint32_t P, xstride;     // columns of this call (<= 8)
+    float *y;                // output row blocks, ystride floats apart
+    uint32_t ystride;
+    int accumulate;
+    int skip_convert;        // 1: xq already holds exactly these columns in this format's layout (the call before used them)
+    // Device-side column list (mixture of experts): column p is row col_idx[col_off + p] of x and goes to output row
+    // block out_idx[col_off + p]; only columns col_off + p < *cnt exist. All nullptr: column p = row p -> row block p.
+    const uint32_t *cnt, *col_idx, *out_idx;
+    uint32_t col_off;
+};
+cudaError_t launch_matmul_tc_nx(const NxCall &c, uint8_t *xq, uint32_t *status, int sms, cudaStream_t stream);
 size_t matmul_tc_nx_scratch_bytes(uint32_t cols, uint32_t P);
 cudaError_t matmul_tc_nx_init(void);
 // Q4_K launches that qualify run on the integer tensor-core kernel (matvec_mma.cu).
@@ -211,12 +225,25 @@ cudaError_t launch_argmax_exchange(const TopExchangeArgs &a, cudaStream_t stream
 cudaError_t launch_rmsnorm(const float *x, const float *wnorm, float *y, float eps, uint32_t n,
                            cudaStream_t stream, uint32_t rows = 1, uint32_t stride = 0);
 cudaError_t launch_add2(const float *a, const float *b, float *y, uint32_t n, cudaStream_t stream);
-// fl_op_router_sel (src/runtime/decode_params.h:234-265): softmax over n_expert logits, top_k by weight.
-cudaError_t launch_router_sel(const float *logits, uint32_t *ids, float *gates, uint32_t n_expert, uint32_t top_k,
-                              uint32_t norm, float scale, cudaStream_t stream);
+// fl_op_router_sel (src/runtime/decode_params.h:234-265) for n_tok tokens in one launch (one warp per token):
+// softmax over n_expert logits, top_k by weight; logits [n_tok][n_expert], ids / gates [n_tok][top_k]. Expert
+// parallel (lids, mgates != nullptr): also the expert's index among this rank's experts [base, base + n_local)
+// or the skip mark, and the gate or 0.
+cudaError_t launch_router_sel(const float *logits, uint32_t *ids, float *gates, uint32_t n_tok, uint32_t n_expert, uint32_t top_k,
+                              uint32_t norm, float scale, cudaStream_t stream, uint32_t *lids = nullptr,
+                              float *mgates = nullptr, uint32_t base = 0, uint32_t n_local = 0);
+// The (token, slot) pairs of a block, grouped by the local expert they chose (a stable counting sort: within an
+// expert the pairs stay in ascending order): cnt[e] pairs for expert e, their tokens in tok_list[e * cap + i] and
+// their pair indices (token * top_k + slot) in pair_list[e * cap + i]. lids: local expert of every pair or kExpertSkip.
+cudaError_t launch_group_by_expert(const uint32_t *lids, uint32_t n_pairs, uint32_t top_k, uint32_t n_local, uint32_t cap,
+                                   uint32_t *cnt, uint32_t *tok_list, uint32_t *pair_list, cudaStream_t stream);
 // fl_op_wmerge (src/runtime/decode_params.h:274-295).
 cudaError_t launch_wmerge(const float *parts, const float *gates, const float *add1, const float *add2, float *y,
                           float scale, uint32_t n_parts, uint32_t n, uint32_t n_full, cudaStream_t stream);
+// fl_op_wmerge for n_tok tokens in one launch: y[t] = sum_q gates[t][q] * parts[t][q] (products and sums rounded in
+// the reference's order; no residual terms).
+cudaError_t launch_wmerge_tokens(const float *parts, const float *gates, float *y, uint32_t n_parts, uint32_t n, uint32_t n_tok,
+                                 cudaStream_t stream);
 cudaError_t launch_silu_mul(const float *gate, const float *up, float *h, uint32_t n, cudaStream_t stream);
 // RoPE (adjacent pairs) on q in place and on k, then store k and v as f16 at
 // row *pos of a cache laid out [n_kv_head][kv_stride][head_dim].

@@ -21,6 +21,10 @@
 //     the units' running sums in shared memory.
 // Every weight byte still crosses HBM once per pass, whatever P is; a pass over 8 tokens costs about what a
 // single-column pass costs.
+// For the experts of a mixture-of-experts block the columns of a call are a device-side list: the number of
+// valid columns is read from device memory (a call with none returns at once and reads no weights), the
+// conversion gathers the listed tokens (optionally as SiLU(x) * x2, the input of a down projection) and the
+// finalizer scatters the results to the listed output rows.
 #include "common.cuh"
 #include "kernels.h"
 
@@ -34,9 +38,14 @@ namespace {
 
 constexpr int kCW = 8;
 constexpr uint32_t kSeg4 = 8 * 144, kSeg6 = 8 * 210;
-constexpr uint32_t kPitch4 = kSeg4 + 16;   // 292 words = 4 mod 32: the 32-bit loads of lanes (g, t) are conflict free
-constexpr uint32_t kPitch6 = kSeg6;        // 420 words = 4 mod 32 as it is
-constexpr uint32_t kSlot4 = 16 * kPitch4, kSlot6 = 16 * kPitch6;
+// A stage arrives as one tiled TMA box of 16 rows x the segment, so the row pitch in shared memory is the segment's
+// size. Q6_K: 420 words = 4 mod 32: the 32-bit loads of lanes (g, t) are conflict free as they are. Q4_K: 288 words =
+// 0 mod 32: the rows are fetched as lines of 128 bytes with the 128-byte swizzle (tensor_map_lines_swz), which
+// spreads the same 16-byte chunk of 8 consecutive rows over 8 bank groups; rows whose pitch in memory is not a
+// multiple of 128 bytes (columns not a multiple of 2048) use the plain box and pay the conflicts.
+constexpr uint32_t kPitch4 = kSeg4, kPitch6 = kSeg6;
+constexpr uint32_t slot_round(uint32_t b) { return (b + 1023u) & ~1023u; }   // the swizzle pattern is tied to the address
+constexpr uint32_t kSlot4 = slot_round(16 * kPitch4), kSlot6 = slot_round(16 * kPitch6);
 constexpr uint32_t kFragBytes = 4096;                    // B fragments of one (block, token group)
 constexpr uint32_t kXqBlk = kFragBytes + 128 + 16;       // + sub-block sums [4 tokens][8] + block scales [4]
 constexpr uint32_t kMaxChunkBlks = 16;                   // blocks of activation resident at a time, at most
@@ -64,6 +73,22 @@ __device__ __forceinline__ float ldsf(uint32_t addr) {
 }
 __device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tma_box2(uint32_t dst, const CUtensorMap *map, uint32_t x, uint32_t y, uint64_t *bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+        "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
+        : "memory");
+}
+__device__ __forceinline__ void tma_box3(uint32_t dst, const CUtensorMap *map, uint32_t line, uint32_t row, uint64_t *bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(dst),
+        "l"(map), "r"(0), "r"(line), "r"(row), "r"(smem_u32(bar))
+        : "memory");
+}
+// Byte offset o of a Q4_K row as the stage holds it: as it is, or in the swizzled 128-byte lines.
+__device__ __forceinline__ uint32_t q4_row_off(uint32_t o, uint32_t g, bool swz) {
+    return swz ? (o & ~127u) + ((((o >> 4) ^ (g + (o >> 7))) & 7u) << 4) + (o & 15u) : o;
 }
 __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                          uint32_t b1) {
@@ -101,17 +126,36 @@ __device__ __forceinline__ void mbar_wait_or_die(uint64_t *bar, uint32_t parity,
 // image: (m / 2) * 512 + lane * 16 + (m & 1) * 8, so that a lane's 128-bit load fetches two combos and a warp's
 // load is one contiguous 512 bytes.
 // grid (nblk, ntg), 64 threads: half-warp p' converts the block's 256 columns of token 4 tg + p'.
-__global__ void __launch_bounds__(64) act_convert_nx_kernel(const float *__restrict__ x, uint32_t xstride, uint32_t P, int fmt,
-                                                            uint8_t *__restrict__ xq, uint32_t ntg) {
+// Column p of the call is row col_idx[col_off + p] of x (col_idx == nullptr: row p); columns at or past *cnt - col_off
+// (cnt == nullptr: P) are zeros. x2 != nullptr: the value is SiLU(x) * x2 (fl_op_silu_mul, src/runtime/decode_params.h:267-272).
+__global__ void __launch_bounds__(64) act_convert_nx_kernel(const float *__restrict__ x, const float *__restrict__ x2, uint32_t xstride,
+                                                            uint32_t P, int fmt, uint8_t *__restrict__ xq, uint32_t ntg,
+                                                            const uint32_t *__restrict__ cnt, uint32_t col_off,
+                                                            const uint32_t *__restrict__ col_idx) {
     const uint32_t blk = blockIdx.x, tg = blockIdx.y;
     const uint32_t pp = threadIdx.x >> 4, hl = threadIdx.x & 15u, p = 4 * tg + pp;
+    uint32_t n_valid = P;
+    if (cnt) { const uint32_t c = *cnt; n_valid = c > col_off ? min(c - col_off, P) : 0u; }
+    if (n_valid == 0) return;   // the matmul of this call returns at entry too
     float v[16];
-    if (p < P) {
-        const float4 *src = reinterpret_cast<const float4 *>(x + (size_t)p * xstride + blk * 256 + hl * 16);
+    if (p < n_valid) {
+        const size_t row = col_idx ? col_idx[col_off + p] : p;
+        const float4 *src = reinterpret_cast<const float4 *>(x + row * xstride + blk * 256 + hl * 16);
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
             const float4 u = src[k];
             v[4 * k] = u.x; v[4 * k + 1] = u.y; v[4 * k + 2] = u.z; v[4 * k + 3] = u.w;
+        }
+        if (x2) {
+            const float4 *src2 = reinterpret_cast<const float4 *>(x2 + row * xstride + blk * 256 + hl * 16);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const float4 u = src2[k];
+                v[4 * k] = (v[4 * k] / (1.0f + expf(-v[4 * k]))) * u.x;
+                v[4 * k + 1] = (v[4 * k + 1] / (1.0f + expf(-v[4 * k + 1]))) * u.y;
+                v[4 * k + 2] = (v[4 * k + 2] / (1.0f + expf(-v[4 * k + 2]))) * u.z;
+                v[4 * k + 3] = (v[4 * k + 3] / (1.0f + expf(-v[4 * k + 3]))) * u.w;
+            }
         }
     } else {
 #pragma unroll
@@ -155,6 +199,10 @@ __global__ void __launch_bounds__(64) act_convert_nx_kernel(const float *__restr
 }
 
 struct NxArgs {
+    CUtensorMap map;               // the tiled view a stage's box is cut from
+    const uint32_t *cnt;           // optional: number of listed columns on the device
+    const uint32_t *out_idx;       // optional: output row block (in units of ystride) of listed column col_off + p
+    uint32_t col_off, swz;
     const uint8_t *w;
     const uint8_t *xq;
     float *y;
@@ -172,18 +220,22 @@ __host__ __device__ inline size_t nx_head_bytes(uint32_t nslots, int groups) {
 
 // ---- per-block math: rows g (r0) and g + 8 (r1), tokens t and t + 4 -----------------------------------------
 // out[row][tg] in units of the tokens' block scales.
+// r0: row g of the stage (row g + 8 is 8 pitches further: the same swizzle, 72 lines on); ow[c][i]: offset in the row
+// of word 4 i + t of chunk c of this warp's block, oh: of the block's header (q4_row_off).
 template <int NTG>
-__device__ __forceinline__ void q4k_block_nx(uint32_t r0, uint32_t r1, uint32_t t, uint32_t xaddr, uint32_t lane, float (&out)[2][NTG]) {
-    // words 4 i + t of chunk c (i = 0, 1): 16 bytes into the chunk's 32; all loads first
+__device__ __forceinline__ void q4k_block_nx(uint32_t r0, const uint32_t (&ow)[4][2], uint32_t oh, uint32_t t, uint32_t xaddr,
+                                             uint32_t lane, float (&out)[2][NTG]) {
+    const uint32_t r1 = r0 + 8 * kPitch4;
+    // all loads first
     uint32_t w0[4][2], w1[4][2];
 #pragma unroll
     for (int c = 0; c < 4; ++c)
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
-            w0[c][i] = lds32(r0 + 16 + 32 * c + 16 * i + 4 * t);
-            w1[c][i] = lds32(r1 + 16 + 32 * c + 16 * i + 4 * t);
+            w0[c][i] = lds32(r0 + ow[c][i]);
+            w1[c][i] = lds32(r1 + ow[c][i]);
         }
-    const uint4 h0 = lds128(r0), h1 = lds128(r1);
+    const uint4 h0 = lds128(r0 + oh), h1 = lds128(r1 + oh);
     float sums[NTG][8];   // sub-block sums of token t (+ 4 tg)
 #pragma unroll
     for (int tg = 0; tg < NTG; ++tg) {
@@ -350,11 +402,11 @@ __device__ __forceinline__ void q6k_block_nx(uint32_t r0, uint32_t r1, uint32_t 
         for (int tg = 0; tg < NTG; ++tg) out[r][tg] = dd[r] * acc[r][tg];
 }
 
-// Warps: 8 consumers, the producer, the finalizer.
-template <int NTG>
-__global__ void __launch_bounds__((kCW + 2) * 32) matmul_tc_nx_kernel(const __grid_constant__ NxArgs a) {
-    extern __shared__ __align__(128) uint8_t smem_raw[];
-    constexpr uint32_t kProducer = kCW, kFinal = kCW + 1;
+// Warps: G groups of 8 consumers (group i takes stages i, i + G, ... of the CTA's stage sequence), the producer, the finalizer.
+template <int NTG, int G>
+__global__ void __launch_bounds__((G * kCW + 2) * 32) matmul_tc_nx_kernel(const __grid_constant__ NxArgs a) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    constexpr uint32_t kConsumers = G * kCW, kProducer = kConsumers, kFinal = kConsumers + 1;
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
     const uint32_t S = a.nslots;
     uint64_t *full = (uint64_t *)smem_raw, *empty = full + S;
@@ -365,16 +417,19 @@ __global__ void __launch_bounds__((kCW + 2) * 32) matmul_tc_nx_kernel(const __gr
     const uint32_t nchunk = (nblk + kChunkBlks - 1) / kChunkBlks;
     const uint32_t units = (a.rows + 15) / 16;
     const uint32_t my_units = blockIdx.x < units ? (units - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    uint32_t n_valid = a.P;   // listed columns of this call
+    if (a.cnt) { const uint32_t c = *a.cnt; n_valid = c > a.col_off ? min(c - a.col_off, a.P) : 0u; }
+    if (n_valid == 0) return;   // nothing routed here: no weights are read
     if (tid == 0) {
         for (uint32_t s = 0; s < S; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], kCW); }
-        for (int i = 0; i < 2; ++i) { mbar_init(&red_full[i], kCW); mbar_init(&red_empty[i], 1); }
+        for (int i = 0; i < 2; ++i) { mbar_init(&red_full[i], kConsumers); mbar_init(&red_empty[i], 1); }
         mbar_init(x_full, 1);
-        mbar_init(x_empty, kCW);
+        mbar_init(x_empty, kConsumers);
         fence_barrier_init();
     }
     __syncthreads();
     const uint32_t ring = smem_u32(smem_raw) + a.ring_off, xs_addr = smem_u32(smem_raw) + a.x_off;
-    const uint32_t segb = a.fmt == FMT_Q4_K ? kSeg4 : kSeg6, rp = a.fmt == FMT_Q4_K ? kPitch4 : kPitch6;
+    const uint32_t segb = a.fmt == FMT_Q4_K ? kSeg4 : kSeg6;
 
     if (warp == kProducer) {
         uint32_t slot = 0, par = 1;
@@ -390,18 +445,17 @@ __global__ void __launch_bounds__((kCW + 2) * 32) matmul_tc_nx_kernel(const __gr
             const uint32_t seg0 = ch * (kChunkBlks / 8), seg1 = min(seg0 + kChunkBlks / 8, nseg);
             for (uint32_t k = 0; k < my_units; ++k) {
                 const uint32_t u = blockIdx.x + k * gridDim.x;
-                const uint32_t row = 16 * u + lane;
-                const bool valid = lane < 16 && row < a.rows;
-                const uint8_t *src = a.w + (size_t)row * a.pitch;
-                const uint32_t nvalid = __popc(__ballot_sync(0xffffffffu, valid));
                 for (uint32_t seg = seg0; seg < seg1; ++seg) {
                     const uint32_t off = seg * segb;
-                    const uint32_t bytes = min(segb, a.pitch - off);   // pitch and off are multiples of 16
                     if (!mbar_wait_bounded(&empty[slot], par, a.status)) return;
                     fence_proxy_async_smem();
-                    if (lane == 0) mbar_arrive_expect_tx(&full[slot], nvalid * bytes);
-                    __syncwarp();
-                    if (valid) bulk_g2s_addr(ring + slot * a.slot_bytes + lane * rp, src + off, bytes, &full[slot]);
+                    if (lane == 0) {
+                        // one box of 16 rows x the segment; rows past the end of the tensor and blocks past the end of a
+                        // row arrive as zeros and count as bytes all the same
+                        mbar_arrive_expect_tx(&full[slot], 16 * segb);
+                        if (a.swz) tma_box3(ring + slot * a.slot_bytes, &a.map, off / 128, 16 * u, &full[slot]);
+                        else tma_box2(ring + slot * a.slot_bytes, &a.map, off / 8, 16 * u, &full[slot]);
+                    }
                     if (++slot == S) { slot = 0; par ^= 1u; }
                 }
             }
@@ -419,8 +473,8 @@ __global__ void __launch_bounds__((kCW + 2) * 32) matmul_tc_nx_kernel(const __gr
                 if (!mbar_wait_bounded(&red_full[buf], (kk >> 1) & 1u, a.status)) return;
                 float v[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-                for (uint32_t w = 0; w < kCW; ++w) {
-                    const float4 p = *reinterpret_cast<const float4 *>(red + (buf * kCW + w) * 128 + lane * 4);
+                for (uint32_t w = 0; w < kConsumers; ++w) {
+                    const float4 p = *reinterpret_cast<const float4 *>(red + (buf * kConsumers + w) * 128 + lane * 4);
                     v[0] += p.x; v[1] += p.y; v[2] += p.z; v[3] += p.w;
                 }
                 __syncwarp();
@@ -433,8 +487,9 @@ __global__ void __launch_bounds__((kCW + 2) * 32) matmul_tc_nx_kernel(const __gr
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     const uint32_t o = lane * 4 + i, row = 16 * u + (o >> 3), tok = o & 7u;
-                    if (row < a.rows && tok < a.P) {
-                        float *dst = a.y + (size_t)tok * a.ystride + row;
+                    if (row < a.rows && tok < n_valid) {
+                        const size_t orow = a.out_idx ? a.out_idx[a.col_off + tok] : tok;
+                        float *dst = a.y + orow * a.ystride + row;
                         *dst = a.accumulate ? *dst + v[i] : v[i];
                     }
                 }
@@ -445,8 +500,15 @@ __global__ void __launch_bounds__((kCW + 2) * 32) matmul_tc_nx_kernel(const __gr
 
     // ---- consumers ----
     {
-        const uint32_t w = warp, g = lane >> 2, t = lane & 3u;
-        uint32_t c_slot = 0, c_par = 0, kk = 0;
+        const uint32_t w = warp % kCW, g = lane >> 2, t = lane & 3u;
+        uint32_t ow[4][2];
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+            for (int i = 0; i < 2; ++i) ow[c][i] = q4_row_off(w * 144u + 16u + 32u * c + 16u * i + 4u * t, g, a.swz != 0);
+        const uint32_t oh = q4_row_off(w * 144u, g, a.swz != 0);
+        // this group's next stage (index over the CTA's whole stage sequence), its ring slot and parity
+        uint32_t c_it = warp / kCW, c_slot = c_it % S, c_par = 0, kk = 0, it0 = 0;
         bool dead = false;
         for (uint32_t ch = 0; ch < nchunk; ++ch) {
             const uint32_t seg0 = ch * (kChunkBlks / 8), seg1 = min(seg0 + kChunkBlks / 8, nseg);
@@ -457,15 +519,16 @@ __global__ void __launch_bounds__((kCW + 2) * 32) matmul_tc_nx_kernel(const __gr
                 for (int r = 0; r < 2; ++r)
 #pragma unroll
                     for (int tg = 0; tg < NTG; ++tg) acc[r][tg] = 0.f;
-                for (uint32_t seg = seg0; seg < seg1; ++seg) {
-                    const uint32_t blk = seg * 8 + w;
+                const uint32_t it1 = it0 + (seg1 - seg0);
+                for (; c_it < it1; c_it += G) {
+                    const uint32_t blk = (seg0 + (c_it - it0)) * 8 + w;
                     mbar_wait_or_die(&full[c_slot], c_par, a.status, dead);
                     if (blk < nblk) {
                         const uint32_t xaddr = xs_addr + (blk - ch * kChunkBlks) * (NTG * kXqBlk);
                         float o[2][NTG];
                         if (a.fmt == FMT_Q4_K) {
-                            const uint32_t r0 = ring + c_slot * a.slot_bytes + g * kPitch4 + w * 144u;
-                            q4k_block_nx<NTG>(r0, r0 + 8 * kPitch4, t, xaddr, lane, o);
+                            const uint32_t r0 = ring + c_slot * a.slot_bytes + g * kPitch4;
+                            q4k_block_nx<NTG>(r0, ow, oh, t, xaddr, lane, o);
                         } else {
                             const uint32_t r0 = ring + c_slot * a.slot_bytes + g * kPitch6 + w * 210u;
                             if (w & 1u) q6k_block_nx<NTG, true>(r0 - 2, r0 + 8 * kPitch6 - 2, t, xaddr, lane, o);
@@ -480,12 +543,14 @@ __global__ void __launch_bounds__((kCW + 2) * 32) matmul_tc_nx_kernel(const __gr
                     }
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&empty[c_slot]);
-                    if (++c_slot == S) { c_slot = 0; c_par ^= 1u; }
+                    c_slot += G;
+                    if (c_slot >= S) { c_slot -= S; c_par ^= 1u; }
                 }
+                it0 = it1;
                 // this warp's share of the unit: rows g, g + 8 x tokens t, t + 4 (complete over the warp's columns)
                 const uint32_t buf = kk & 1u;
                 mbar_wait_or_die(&red_empty[buf], ((kk >> 1) & 1u) ^ 1u, a.status, dead);
-                float *pp = red + (buf * kCW + w) * 128;
+                float *pp = red + (buf * kConsumers + warp) * 128;
 #pragma unroll
                 for (int tg = 0; tg < NTG; ++tg) {
                     pp[g * 8 + 4 * tg + t] = acc[0][tg];
@@ -503,10 +568,20 @@ __global__ void __launch_bounds__((kCW + 2) * 32) matmul_tc_nx_kernel(const __gr
 
 } // namespace
 
+// Consumer groups per CTA (FLB_NX_GROUPS=1 selects the single-group instantiation for comparison).
+static int nx_groups() {
+    static const int v = getenv("FLB_NX_GROUPS") ? atoi(getenv("FLB_NX_GROUPS")) : 2;
+    return v == 1 ? 1 : 2;
+}
+
 cudaError_t matmul_tc_nx_init(void) {
-    cudaError_t e = cudaFuncSetAttribute(matmul_tc_nx_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024 - 1024);
-    if (e != cudaSuccess) return e;
-    return cudaFuncSetAttribute(matmul_tc_nx_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024 - 1024);
+    const void *ks[] = {(const void *)matmul_tc_nx_kernel<1, 1>, (const void *)matmul_tc_nx_kernel<2, 1>,
+                        (const void *)matmul_tc_nx_kernel<1, 2>, (const void *)matmul_tc_nx_kernel<2, 2>};
+    for (const void *k : ks) {
+        const cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024 - 1024);
+        if (e != cudaSuccess) return e;
+    }
+    return cudaSuccess;
 }
 
 // Bytes of device scratch the converted activations of one call need (cols <= 18432, up to 8 columns).
@@ -514,16 +589,17 @@ size_t matmul_tc_nx_scratch_bytes(uint32_t cols, uint32_t P) {
     return (size_t)(cols / 256) * ((P + 3) / 4) * kXqBlk;
 }
 
-// Y[p][r] (+)= dot(W[r], X[p]), 2 <= P <= 8 (1 works too), Q4_K or Q6_K, cols a multiple of 256, rows 16-byte
-// pitched. xq: scratch of matmul_tc_nx_scratch_bytes(cols, P). cudaErrorNotSupported for other shapes.
-cudaError_t launch_matmul_tc_nx(int fmt, const void *w, uint32_t rows, uint32_t cols, uint32_t pitch, const float *x, uint32_t P,
-                                uint32_t xstride, float *y, uint32_t ystride, int accumulate, uint8_t *xq, uint32_t *status,
-                                int sms, cudaStream_t stream) {
+// Y[c.out row of column p][r] (+)= dot(W[r], column p), P <= 8 columns, Q4_K or Q6_K, cols a multiple of 256, rows
+// 16-byte pitched. xq: scratch of matmul_tc_nx_scratch_bytes(cols, P). cudaErrorNotSupported for other shapes.
+cudaError_t launch_matmul_tc_nx(const NxCall &c, uint8_t *xq, uint32_t *status, int sms, cudaStream_t stream) {
     static const bool off = getenv("FLB_TC_NX") && getenv("FLB_TC_NX")[0] == '0';
+    const int fmt = c.fmt;
+    const uint32_t rows = c.rows, cols = c.cols, P = c.P;
     if (off || (fmt != FMT_Q4_K && fmt != FMT_Q6_K) || cols % 256 != 0 || cols < 256 || P == 0 || P > 8 || rows == 0) return cudaErrorNotSupported;
     const uint32_t rb = (uint32_t)row_bytes(fmt, cols);
-    if (pitch == 0) pitch = rb;
-    if ((pitch & 15u) || pitch < rb || (((uintptr_t)w) & 15u) || (((uintptr_t)x) & 15u) || (xstride & 3u) || !xq) return cudaErrorNotSupported;
+    const uint32_t pitch = c.pitch ? c.pitch : rb;
+    if ((pitch & 15u) || pitch < rb || (((uintptr_t)c.w) & 15u) || (((uintptr_t)c.x) & 15u) || (((uintptr_t)c.x2) & 15u) || (c.xstride & 3u) || !xq)
+        return cudaErrorNotSupported;
     const uint32_t nblk = cols / 256, ntg = (P + 3) / 4;
     const uint32_t units = (rows + 15) / 16;
     const uint32_t grid = units < (uint32_t)sms ? units : (uint32_t)sms;
@@ -532,21 +608,30 @@ cudaError_t launch_matmul_tc_nx(int fmt, const void *w, uint32_t rows, uint32_t 
     const uint32_t nchunk = (nblk + kChunkBlks - 1) / kChunkBlks;
     const uint32_t my_units_max = (units + grid - 1) / grid;
     if (nchunk > 1 && my_units_max > kMaxChunkUnits) return cudaErrorNotSupported;
-    act_convert_nx_kernel<<<dim3(nblk, ntg), 64, 0, stream>>>(x, xstride, P, fmt, xq, ntg);
-    cudaError_t e = cudaGetLastError();
-    if (e != cudaSuccess) return e;
     NxArgs k;
     memset(&k, 0, sizeof(k));
-    k.w = (const uint8_t *)w; k.xq = xq; k.y = y; k.rows = rows; k.pitch = pitch; k.cols = cols; k.ystride = ystride; k.P = P; k.ntg = ntg;
-    k.fmt = fmt; k.accumulate = accumulate; k.status = status; k.chunk_blks = kChunkBlks;
+    const uint32_t segb = fmt == FMT_Q4_K ? kSeg4 : kSeg6;
+    k.swz = (fmt == FMT_Q4_K && pitch % 128 == 0) ? 1 : 0;
+    cudaError_t e = k.swz ? tensor_map_lines_swz(&k.map, c.w, rows, pitch, segb / 128, 16)
+                          : tensor_map_2d(&k.map, 8, c.w, pitch / 8, rows, pitch, segb / 8, 16, false);
+    if (e != cudaSuccess) return e;
+    if (!c.skip_convert) {
+        act_convert_nx_kernel<<<dim3(nblk, ntg), 64, 0, stream>>>(c.x, c.x2, c.xstride, P, fmt, xq, ntg, c.cnt, c.col_off, c.col_idx);
+        e = cudaGetLastError();
+        if (e != cudaSuccess) return e;
+    }
+    k.w = (const uint8_t *)c.w; k.xq = xq; k.y = c.y; k.rows = rows; k.pitch = pitch; k.cols = cols; k.ystride = c.ystride; k.P = P; k.ntg = ntg;
+    k.fmt = fmt; k.accumulate = c.accumulate; k.status = status; k.chunk_blks = kChunkBlks;
+    k.cnt = c.cnt; k.col_off = c.col_off; k.out_idx = c.out_idx;
     k.slot_bytes = fmt == FMT_Q4_K ? kSlot4 : kSlot6;
     const size_t limit = 227 * 1024 - 1024;
+    const int groups = nx_groups();
     const size_t xbytes = (size_t)std::min(nblk, kChunkBlks) * ntg * kXqBlk;
     const size_t uacc = nchunk > 1 ? (size_t)my_units_max * 128 * 4 : 0;
     auto layout = [&](uint32_t ns, size_t &x_off, size_t &uacc_off, size_t &ring_off) {
-        x_off = nx_head_bytes(ns, 1);
+        x_off = nx_head_bytes(ns, groups);
         uacc_off = (x_off + xbytes + 15) & ~(size_t)15;
-        ring_off = (uacc_off + uacc + 127) & ~(size_t)127;
+        ring_off = (uacc_off + uacc + 1023) & ~(size_t)1023;
         return ring_off + (size_t)ns * k.slot_bytes;
     };
     size_t xo, uo, ro;
@@ -555,8 +640,13 @@ cudaError_t launch_matmul_tc_nx(int fmt, const void *w, uint32_t rows, uint32_t 
     while (nslots < 32 && layout(nslots + 1, xo, uo, ro) <= limit) ++nslots;
     const size_t smem = layout(nslots, xo, uo, ro);
     k.nslots = nslots; k.x_off = (uint32_t)xo; k.uacc_off = (uint32_t)uo; k.ring_off = (uint32_t)ro;
-    if (ntg == 1) return launch_kernel(matmul_tc_nx_kernel<1>, dim3(grid), dim3((kCW + 2) * 32), smem, stream, false, k);
-    return launch_kernel(matmul_tc_nx_kernel<2>, dim3(grid), dim3((kCW + 2) * 32), smem, stream, false, k);
+    const dim3 block((groups * kCW + 2) * 32);
+    if (groups == 2) {
+        if (ntg == 1) return launch_kernel(matmul_tc_nx_kernel<1, 2>, dim3(grid), block, smem, stream, false, k);
+        return launch_kernel(matmul_tc_nx_kernel<2, 2>, dim3(grid), block, smem, stream, false, k);
+    }
+    if (ntg == 1) return launch_kernel(matmul_tc_nx_kernel<1, 1>, dim3(grid), block, smem, stream, false, k);
+    return launch_kernel(matmul_tc_nx_kernel<2, 1>, dim3(grid), block, smem, stream, false, k);
 }
 
 } // namespace flb

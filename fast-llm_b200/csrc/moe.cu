@@ -6,12 +6,17 @@
 // WMERGE (fl_op_wmerge, :274-295); the reference builds the same chain as tasks
 // (src/model/decoder.cpp:925-1045) and has no multi-GPU form.
 //
-// Expert parallel: rank r of w holds experts [r * n / w, (r + 1) * n / w). The hidden
-// states are replicated, so the dispatch half of the all-to-all moves nothing: every
-// rank routes every token, runs only the slots whose expert it holds (a launch for an
-// expert held elsewhere returns at once and reads no weights), merges them with the
-// other slots' gates set to zero, and the ranks' partial outputs are summed through
-// peer memory by the exchange kernel of the tensor-parallel decoder (rank order, so
+// The tokens of a block are grouped by expert on the device (a stable counting sort of the (token, slot)
+// pairs), and each of this rank's experts is walked ONCE per block: gate, up and down run as multi-column
+// matmuls (matvec_tc_nx.cu) over the tokens that chose the expert, up to 8 per pass, with the token list
+// and its length read on the device (an expert nobody chose costs launches that return at entry, no
+// weight traffic). The reference describes the same grouping for its task graph ("one tile set per
+// DISTINCT expert serving every position that routed to it", src/model/decoder.cpp:927-930).
+//
+// Expert parallel: rank r of w holds experts [r * n / w, (r + 1) * n / w). The hidden states are
+// replicated, so the dispatch half of the all-to-all moves nothing: every rank routes every token, runs
+// only its own experts, merges with the other slots' gates set to zero, and the ranks' partial outputs
+// are summed through peer memory by the exchange kernel of the tensor-parallel decoder (rank order, so
 // every rank ends with identical bits). That sum is the combine half.
 #include "capi_internal.h"
 
@@ -27,6 +32,7 @@ struct fl_b200_moe {
     const uint8_t *wg = nullptr, *wu = nullptr, *wd = nullptr;
     float *logits = nullptr, *gates = nullptr, *mgates = nullptr, *g = nullptr, *u = nullptr, *part = nullptr, *partial = nullptr;
     uint32_t *ids = nullptr, *lids = nullptr;
+    uint32_t *cnt = nullptr, *tok_list = nullptr, *pair_list = nullptr;   // the pairs grouped by local expert (launch_group_by_expert)
     uint8_t *comm = nullptr;
     uint8_t *peers[kCommMaxRanks] = {};
     bool peers_set = false;
@@ -38,17 +44,6 @@ struct fl_b200_moe {
 };
 
 namespace {
-
-// Local expert index and gate of every (token, slot): an expert held by another rank gets the skip mark and gate 0.
-__global__ void ep_mask_kernel(const uint32_t *__restrict__ ids, const float *__restrict__ gates, uint32_t *__restrict__ lids,
-                               float *__restrict__ mgates, uint32_t n, uint32_t base, uint32_t n_local) {
-    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= n) return;
-    const uint32_t e = ids[i];
-    const bool mine = e >= base && e - base < n_local;
-    lids[i] = mine ? e - base : kExpertSkip;
-    mgates[i] = mine ? gates[i] : 0.f;
-}
 
 // Router logits of all tokens in one launch: logits[t][e] = dot(router[e], x[t]); one block per (expert, token).
 __global__ void __launch_bounds__(128) router_logits_kernel(const float *__restrict__ router, const float *__restrict__ x,
@@ -110,8 +105,11 @@ int fl_b200_moe_create(fl_b200_ctx *ctx, const fl_b200_moe_cfg *cfg, uint32_t ra
     if (int rc = alloc((void **)&m->mgates, T * K * 4)) return fail(rc);
     if (int rc = alloc((void **)&m->ids, T * K * 4)) return fail(rc);
     if (int rc = alloc((void **)&m->lids, T * K * 4)) return fail(rc);
-    if (int rc = alloc((void **)&m->g, F * 4)) return fail(rc);
-    if (int rc = alloc((void **)&m->u, F * 4)) return fail(rc);
+    if (int rc = alloc((void **)&m->g, T * K * F * 4)) return fail(rc);   // gate / up outputs, one row per (token, slot) pair
+    if (int rc = alloc((void **)&m->u, T * K * F * 4)) return fail(rc);
+    if (int rc = alloc((void **)&m->cnt, (size_t)m->n_local * 4)) return fail(rc);
+    if (int rc = alloc((void **)&m->tok_list, (size_t)m->n_local * T * 4)) return fail(rc);
+    if (int rc = alloc((void **)&m->pair_list, (size_t)m->n_local * T * 4)) return fail(rc);
     if (int rc = alloc((void **)&m->part, T * K * E * 4)) return fail(rc);
     if (world > 1) {
         if (int rc = alloc((void **)&m->partial, T * E * 4)) return fail(rc);
@@ -128,6 +126,7 @@ void fl_b200_moe_destroy(fl_b200_moe *m) {
     cudaSetDevice(m->ctx->device);
     cudaStreamSynchronize(m->ctx->stream);
     cudaFree(m->logits); cudaFree(m->gates); cudaFree(m->mgates); cudaFree(m->ids); cudaFree(m->lids); cudaFree(m->g);
+    cudaFree(m->cnt); cudaFree(m->tok_list); cudaFree(m->pair_list);
     cudaFree(m->u); cudaFree(m->part); cudaFree(m->partial); cudaFree(m->comm); cudaFree(m->comm_state);
     if (m->rec.exec) cudaGraphExecDestroy(m->rec.exec);
     if (m->rec.graph) cudaGraphDestroy(m->rec.graph);
@@ -197,7 +196,9 @@ int fl_b200_moe_forward(fl_b200_moe *m, const float *x, uint32_t n_tok, float *y
 
 } // extern "C"
 
-static int moe_enqueue(fl_b200_moe *m, const float *x, uint32_t n_tok, float *y) {
+// One gate | up launch and one down launch per (token, slot) through the expert-indexed one-column matvec: the form
+// for shapes the multi-column matmul does not take (rows that are not 16-byte pitched, e.g. Q6_K with 1024 columns).
+static int moe_enqueue_per_slot(fl_b200_moe *m, const float *x, uint32_t n_tok, float *y) {
     fl_b200_ctx *ctx = m->ctx;
     cudaStream_t s = ctx->stream;
     const fl_b200_moe_cfg &c = m->c;
@@ -205,10 +206,7 @@ static int moe_enqueue(fl_b200_moe *m, const float *x, uint32_t n_tok, float *y)
     const uint64_t stride_gu = (uint64_t)F * row_bytes(c.fmt_gate_up, E), stride_d = (uint64_t)E * row_bytes(c.fmt_down, F);
     router_logits_kernel<<<dim3(NE, n_tok), 128, 0, s>>>(m->router, x, m->logits, E, NE);
     CKM(cudaGetLastError());
-    for (uint32_t t = 0; t < n_tok; ++t)
-        CKM(launch_router_sel(m->logits + (size_t)t * NE, m->ids + (size_t)t * K, m->gates + (size_t)t * K, NE, K, c.norm, c.scale, s));
-    ep_mask_kernel<<<(n_tok * K + 127) / 128, 128, 0, s>>>(m->ids, m->gates, m->lids, m->mgates, n_tok * K, m->base, m->n_local);
-    CKM(cudaGetLastError());
+    CKM(launch_router_sel(m->logits, m->ids, m->gates, n_tok, NE, K, c.norm, c.scale, s, m->lids, m->mgates, m->base, m->n_local));
     const uint32_t rows_gu = (uint32_t)(stride_gu / row_bytes(c.fmt_gate_up, E)), rows_d = (uint32_t)(stride_d / row_bytes(c.fmt_down, F));
     static const int kMoePdl = getenv("FLB_MOE_PDL") ? atoi(getenv("FLB_MOE_PDL")) : 1;
     bool first_launch = true;
@@ -249,6 +247,58 @@ static int moe_enqueue(fl_b200_moe *m, const float *x, uint32_t n_tok, float *y)
         float *dst = (m->world > 1 ? m->partial : y) + (size_t)t * E;
         CKM(launch_wmerge(m->part + (size_t)t * K * E, m->mgates + (size_t)t * K, nullptr, nullptr, dst, 1.0f, K, E, K, s));
     }
+    if (m->world > 1) {
+        for (uint32_t t = 0; t < n_tok; ++t) {   // the combine: sum of the ranks' partial outputs, rank order
+            AllReduceArgs r{};
+            for (uint32_t p = 0; p < m->world; ++p) r.peers[p] = m->peers[p];
+            r.in = m->partial + (size_t)t * E; r.resid = nullptr; r.out = y + (size_t)t * E; r.n = E;
+            r.rank = m->rank; r.world = m->world; r.st = CommState{m->comm_state}; r.status = ctx->status; r.wait_ns = ctx->wait_limit_ns;
+            CKM(launch_allreduce_resid(r, s, false));
+        }
+    }
+    return FL_B200_OK;
+}
+
+static int moe_enqueue(fl_b200_moe *m, const float *x, uint32_t n_tok, float *y) {
+    fl_b200_ctx *ctx = m->ctx;
+    cudaStream_t s = ctx->stream;
+    const fl_b200_moe_cfg &c = m->c;
+    const uint32_t E = c.n_embd, F = c.n_ff, K = c.top_k, NE = c.n_expert, T = c.max_tokens;
+    const uint64_t stride_gu = (uint64_t)F * row_bytes(c.fmt_gate_up, E), stride_d = (uint64_t)E * row_bytes(c.fmt_down, F);
+    if (row_bytes(c.fmt_gate_up, E) % 16 != 0 || row_bytes(c.fmt_down, F) % 16 != 0)
+        return moe_enqueue_per_slot(m, x, n_tok, y);
+    router_logits_kernel<<<dim3(NE, n_tok), 128, 0, s>>>(m->router, x, m->logits, E, NE);
+    CKM(cudaGetLastError());
+    CKM(launch_router_sel(m->logits, m->ids, m->gates, n_tok, NE, K, c.norm, c.scale, s, m->lids, m->mgates, m->base, m->n_local));
+    CKM(launch_group_by_expert(m->lids, n_tok * K, K, m->n_local, T, m->cnt, m->tok_list, m->pair_list, s));
+    // Every local expert once: the tokens that chose it, 8 columns per pass. The lists live on the device, so the
+    // launch sequence is the same for every routing (and can be replayed as a graph); a pass without columns
+    // returns at entry.
+    for (uint32_t e = 0; e < m->n_local; ++e) {
+        const uint32_t *cnt = m->cnt + e, *toks = m->tok_list + (size_t)e * T, *pairs = m->pair_list + (size_t)e * T;
+        for (uint32_t off = 0; off < n_tok; off += 8) {
+            const uint32_t P = n_tok - off < 8 ? n_tok - off : 8;
+            NxCall g{};
+            g.fmt = c.fmt_gate_up; g.w = m->wg + (uint64_t)e * stride_gu; g.rows = F; g.cols = E;
+            g.x = x; g.P = P; g.xstride = E; g.y = m->g; g.ystride = F;
+            g.cnt = cnt; g.col_idx = toks; g.out_idx = pairs; g.col_off = off;
+            cudaError_t er = launch_matmul_tc_nx(g, ctx->xq, ctx->status, ctx->sms, s);
+            if (er == cudaErrorNotSupported) return set_err(FL_B200_ERR_ARG, "moe_forward: shape not taken by the multi-column matmul");
+            CKM(er);
+            NxCall u = g;
+            u.w = m->wu + (uint64_t)e * stride_gu; u.y = m->u; u.skip_convert = 1;   // the same columns, already converted
+            CKM(launch_matmul_tc_nx(u, ctx->xq, ctx->status, ctx->sms, s));
+            NxCall d{};   // down: the column of pair p is silu(g[p]) * u[p], built while it is converted
+            d.fmt = c.fmt_down; d.w = m->wd + (uint64_t)e * stride_d; d.rows = E; d.cols = F;
+            d.x = m->g; d.x2 = m->u; d.P = P; d.xstride = F; d.y = m->part; d.ystride = E;
+            d.cnt = cnt; d.col_idx = pairs; d.out_idx = pairs; d.col_off = off;
+            er = launch_matmul_tc_nx(d, ctx->xq, ctx->status, ctx->sms, s);
+            if (er == cudaErrorNotSupported) return set_err(FL_B200_ERR_ARG, "moe_forward: shape not taken by the multi-column matmul");
+            CKM(er);
+        }
+    }
+    // WMERGE of every token: y[t] = sum_k gate[t][k] * part[t][k] (slots of experts held elsewhere carry gate 0)
+    CKM(launch_wmerge_tokens(m->part, m->mgates, m->world > 1 ? m->partial : y, K, E, n_tok, s));
     if (m->world > 1) {
         for (uint32_t t = 0; t < n_tok; ++t) {   // the combine: sum of the ranks' partial outputs, rank order
             AllReduceArgs r{};
