@@ -283,7 +283,7 @@ def kernel_case(case, steps, warmup):
         run(steps)
         us = ctx.timer_stop() * 1e3 / steps
         nbytes = rows * capi.row_bytes(capi.Q4_K, cols)
-        print(json.dumps({"case": case, "kernel": "matvec_q4k_mma_nx_kernel", "rows": rows, "cols": cols, "columns": nx,
+        print(json.dumps({"case": case, "kernel": "matmul_tc_nx_kernel", "rows": rows, "cols": cols, "columns": nx,
                           "us_per_pass": us, "weight_bytes": nbytes, "achieved_gbs": nbytes / us / 1e3,
                           "frac_of_measured_hbm": nbytes / us / 1e3 / peak, "status": ctx.status()}))
         return
@@ -549,7 +549,7 @@ def measure(tp_mode, args, ctx, cfg, config, dist, gloo, rank, local_rank, world
         "steps": steps, "warmup": warmup, "ms_per_step": ms_dev / steps, "higher_is_better": True,
         "scaling": "strong" if tp_mode else "weak", "vs_baseline": None, "dtype": "f32 activations / accumulation over Q4_K,Q6_K weights and f16 KV",
         "data": "synthetic", "config": config,
-        "roofline": {"bound": "hbm", "kernel": "matvec_stream_kernel", "achieved": achieved, "peak": peak,
+        "roofline": {"bound": "hbm", "kernel": "matvec_tc_kernel", "achieved": achieved, "peak": peak,
                      "peak_source": "MEASURED_PEAKS.json hbm_gbs" if peak_kind == "measured" else "fallback 6.65 TB/s",
                      "unit": "GB/s", "frac": achieved / peak,
                      # dram__bytes_read.sum + dram__bytes_write.sum of the four matvec launch shapes in one ncu

@@ -229,7 +229,7 @@ static int check_matvec(int fmt, const void *w, uint32_t rows, uint32_t cols, co
 // capi_internal.h: the decoder's batch pass uses it too).
 int flb::matmul(fl_b200_ctx *c, int fmt, const void *w, uint32_t rows, uint32_t cols, const float *x,
                 uint32_t nx, uint32_t xstride, float *y, uint32_t ystride, int accumulate, uint32_t pitch,
-                const uint32_t *expert_id, uint64_t expert_stride, int pdl) {
+                const uint32_t *expert_id, uint64_t expert_stride, int pdl, const float *x2, int same_columns) {
     if (int rc = check_matvec(fmt, w, rows, cols, x, y)) return rc;
     if (pitch != 0 && pitch < row_bytes(fmt, cols))
         return set_err(FL_B200_ERR_ARG, "matvec: row pitch %u smaller than the packed row (%llu bytes)", pitch,
@@ -245,20 +245,10 @@ int flb::matmul(fl_b200_ctx *c, int fmt, const void *w, uint32_t rows, uint32_t 
             NxCall nc{};
             nc.fmt = fmt; nc.w = w; nc.rows = rows; nc.cols = cols; nc.pitch = pitch;
             nc.x = x + (size_t)p0 * xstride; nc.P = nt; nc.xstride = xstride;
+            if (x2) nc.x2 = x2 + (size_t)p0 * xstride;
+            nc.skip_convert = (same_columns && nx <= 8) ? 1 : 0;   // with more than 8 columns the scratch holds the last chunk only
             nc.y = y + (size_t)p0 * ystride; nc.ystride = ystride; nc.accumulate = accumulate;
             const cudaError_t e = launch_matmul_tc_nx(nc, c->xq, c->status, c->sms, c->stream);
-            if (e == cudaErrorNotSupported) break;   // the shape does not qualify (same answer for every chunk)
-            if (e != cudaSuccess) return cuda_err(e, "multi-column matmul launch");
-            first_single = p0 + nt;
-        }
-    }
-    if (first_single == 0 && nx >= 2 && fmt == FL_B200_Q4_K && pitch == 0 && !expert_id) {
-        // verify batches: up to 8 columns per pass over the weights on the tensor-core kernel; a last
-        // chunk of one column is left to the one-column kernel
-        for (uint32_t p0 = 0; p0 + 2 <= nx; p0 += 8) {
-            const uint32_t nt = nx - p0 < 8 ? nx - p0 : 8;
-            const cudaError_t e = launch_matmul_q4k_nx(w, rows, cols, x + (size_t)p0 * xstride, nt, xstride, y + (size_t)p0 * ystride,
-                                                       ystride, accumulate, c->status, c->sms, c->stream);
             if (e == cudaErrorNotSupported) break;   // the shape does not qualify (same answer for every chunk)
             if (e != cudaSuccess) return cuda_err(e, "multi-column matmul launch");
             first_single = p0 + nt;
@@ -284,6 +274,7 @@ int flb::matmul(fl_b200_ctx *c, int fmt, const void *w, uint32_t rows, uint32_t 
         a.x = x + (size_t)p * xstride;
         a.cols = cols;
         a.x_mode = MV_X_PLAIN;
+        if (x2) { a.x2 = x2 + (size_t)p * xstride; a.x_mode = MV_X_SILU_MUL; }
         a.accumulate = accumulate;
         a.status = c->status;
         a.pdl = pdl;

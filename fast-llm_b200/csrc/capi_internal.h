@@ -39,7 +39,11 @@ int cuda_err(cudaError_t e, const char *what);
 // (pdl: those one-column launches are programmatic dependents of the launch before them).
 int matmul(fl_b200_ctx *c, int fmt, const void *w, uint32_t rows, uint32_t cols, const float *x, uint32_t nx,
            uint32_t xstride, float *y, uint32_t ystride, int accumulate, uint32_t pitch = 0,
-           const uint32_t *expert_id = nullptr, uint64_t expert_stride = 0, int pdl = 0);
+           const uint32_t *expert_id = nullptr, uint64_t expert_stride = 0, int pdl = 0, const float *x2 = nullptr,
+           int same_columns = 0);
+// x2 != nullptr: column p is SiLU(x_p) * x2_p (fl_op_silu_mul fused into the matmul's activation prologue).
+// same_columns: x, nx and the weight format are those of the matmul call before this one on the same context, so the
+// converted activations of the multi-column kernel are reused (Q/K after Q, up after gate).
 // Hands device memory to the decoder, which frees it when it is destroyed.
 void decoder_adopt(fl_b200_decoder *d, void *dev);
 } // namespace flb

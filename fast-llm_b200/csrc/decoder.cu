@@ -676,8 +676,11 @@ static int enqueue_batch(fl_b200_decoder *d, uint32_t m, cudaStream_t s) {
         const Tensor *w = &d->lw[(size_t)l * 7];
         CK(launch_rmsnorm(b.x, d->attn_norm[l], b.xn, c.eps, E, s, m, E));
         if (int rc = matmul(ctx, w[FL_B200_T_WQ].fmt, w[FL_B200_T_WQ].w, QD, E, b.xn, m, E, b.q, QD, 0, 0, nullptr, 0, kBatchPdl)) return rc;
-        if (int rc = matmul(ctx, w[FL_B200_T_WK].fmt, w[FL_B200_T_WK].w, KD, E, b.xn, m, E, b.k, KD, 0, 0, nullptr, 0, kBatchPdl)) return rc;
-        if (int rc = matmul(ctx, w[FL_B200_T_WV].fmt, w[FL_B200_T_WV].w, KD, E, b.xn, m, E, b.v, KD, 0, 0, nullptr, 0, kBatchPdl)) return rc;
+        // the converted activations of the multi-column kernel are reused while the weight format stays the same
+        if (int rc = matmul(ctx, w[FL_B200_T_WK].fmt, w[FL_B200_T_WK].w, KD, E, b.xn, m, E, b.k, KD, 0, 0, nullptr, 0, kBatchPdl, nullptr,
+                            w[FL_B200_T_WK].fmt == w[FL_B200_T_WQ].fmt)) return rc;
+        if (int rc = matmul(ctx, w[FL_B200_T_WV].fmt, w[FL_B200_T_WV].w, KD, E, b.xn, m, E, b.v, KD, 0, 0, nullptr, 0, kBatchPdl, nullptr,
+                            w[FL_B200_T_WV].fmt == w[FL_B200_T_WK].fmt)) return rc;
         {   // rotate q and k of every token by its own position, append k and v
             RopeAppendArgs r{};
             r.q = b.q; r.k = b.k; r.v = b.v; r.kcache = d->kc[l]; r.vcache = d->vc[l]; r.pos = pos;
@@ -705,12 +708,18 @@ static int enqueue_batch(fl_b200_decoder *d, uint32_t m, cudaStream_t s) {
         }
         CK(launch_rmsnorm(b.x, d->ffn_norm[l], b.xn, c.eps, E, s, m, E));
         if (int rc = matmul(ctx, w[FL_B200_T_GATE].fmt, w[FL_B200_T_GATE].w, F, E, b.xn, m, E, b.g, F, 0, 0, nullptr, 0, kBatchPdl)) return rc;
-        if (int rc = matmul(ctx, w[FL_B200_T_UP].fmt, w[FL_B200_T_UP].w, F, E, b.xn, m, E, b.u, F, 0, 0, nullptr, 0, kBatchPdl)) return rc;
-        CK(launch_silu_mul(b.g, b.u, b.g, m * F, s));
+        if (int rc = matmul(ctx, w[FL_B200_T_UP].fmt, w[FL_B200_T_UP].w, F, E, b.xn, m, E, b.u, F, 0, 0, nullptr, 0, kBatchPdl, nullptr,
+                            w[FL_B200_T_UP].fmt == w[FL_B200_T_GATE].fmt)) return rc;
+        // SiLU(g) * u is built while the down projection's activation is converted (streaming formats); other formats
+        // get the product from a launch of its own
+        const bool fuse_silu = (w[FL_B200_T_DOWN].fmt == FL_B200_Q4_K || w[FL_B200_T_DOWN].fmt == FL_B200_Q6_K || w[FL_B200_T_DOWN].fmt == FL_B200_Q8_0) &&
+                               row_bytes(w[FL_B200_T_DOWN].fmt, F) % 16 == 0;   // rows the streaming kernels take
+        if (!fuse_silu) CK(launch_silu_mul(b.g, b.u, b.g, m * F, s));
+        const float *down_x2 = fuse_silu ? b.u : nullptr;
         if (!tp) {
-            if (int rc = matmul(ctx, w[FL_B200_T_DOWN].fmt, w[FL_B200_T_DOWN].w, E, F, b.g, m, F, b.x, E, 1, w[FL_B200_T_DOWN].pitch, nullptr, 0, kBatchPdl)) return rc;
+            if (int rc = matmul(ctx, w[FL_B200_T_DOWN].fmt, w[FL_B200_T_DOWN].w, E, F, b.g, m, F, b.x, E, 1, w[FL_B200_T_DOWN].pitch, nullptr, 0, kBatchPdl, down_x2)) return rc;
         } else {
-            if (int rc = matmul(ctx, w[FL_B200_T_DOWN].fmt, w[FL_B200_T_DOWN].w, E, F, b.g, m, F, b.partial, E, 0, w[FL_B200_T_DOWN].pitch, nullptr, 0, kBatchPdl)) return rc;
+            if (int rc = matmul(ctx, w[FL_B200_T_DOWN].fmt, w[FL_B200_T_DOWN].w, E, F, b.g, m, F, b.partial, E, 0, w[FL_B200_T_DOWN].pitch, nullptr, 0, kBatchPdl, down_x2)) return rc;
             if (int rc = sum_ranks()) return rc;
         }
     }

@@ -111,13 +111,6 @@ struct NxCall {
 cudaError_t launch_matmul_tc_nx(const NxCall &c, uint8_t *xq, uint32_t *status, int sms, cudaStream_t stream);
 size_t matmul_tc_nx_scratch_bytes(uint32_t cols, uint32_t P);
 cudaError_t matmul_tc_nx_init(void);
-// Q4_K launches that qualify run on the integer tensor-core kernel (matvec_mma.cu).
-bool matvec_mma_eligible(const MatvecArgs &a);
-cudaError_t launch_matvec_mma(const MatvecArgs &a, int sms, cudaStream_t stream);
-// Several activation columns in one pass over a Q4_K tensor (tensor cores); cudaErrorNotSupported when the
-// shape does not qualify.
-cudaError_t launch_matmul_q4k_nx(const void *w, uint32_t rows, uint32_t cols, const float *x, uint32_t nt, uint32_t xstride,
-                                 float *y, uint32_t ystride, int accumulate, uint32_t *status, int sms, cudaStream_t stream);
 // True when launch_matvec would take the streaming kernel for this shape.
 bool matvec_is_streaming(int fmt, uint32_t cols);
 // Dynamic shared memory the streaming kernel needs for (cols, formats used).

@@ -839,7 +839,6 @@ cudaError_t tensor_map_lines_swz(CUtensorMap *m, const void *base, uint64_t rows
 cudaError_t launch_matvec(const MatvecArgs &a, int sms, cudaStream_t stream) {
     if (a.n_tensors < 1 || a.n_tensors > 4 || a.cols == 0) return cudaErrorInvalidValue;
     if (matvec_tc_eligible(a)) return launch_matvec_tc(a, sms, stream);
-    if (matvec_mma_eligible(a)) return launch_matvec_mma(a, sms, stream);
     bool streaming = true, q4 = false, q6 = false, q8 = false;
     uint32_t total_rows = 0, total_quads = 0;
     for (int i = 0; i < a.n_tensors; ++i) {

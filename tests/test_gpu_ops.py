@@ -201,28 +201,6 @@ def test_matvec_column_slice_with_pitch(ctx, checker, fmt, rows, cols, c0, n):
     assert rel_err(acc.astype(np.float32), full) <= MATVEC_RTOL
 
 
-def test_matvec_tensor_core_kernel_opt_in(ctx, checker, monkeypatch):
-    """The experimental mma.sync Q4_K kernel (FLB_MMA=1): same gate as the default kernel, plain and
-    accumulate (STREAM_DOT) forms."""
-    monkeypatch.setenv("FLB_MMA", "1")
-    rng = np.random.default_rng(77)
-    for rows, cols in ((4096, 4096), (48, 8192), (16, 4096)):
-        w = synth.q4k_tensor(rng, rows, cols)
-        x = rng.standard_normal(cols).astype(np.float32)
-        want = checker.matvec(capi.Q4_K, w, rows, cols, x)
-        got = gpu_matvec(ctx, capi.Q4_K, w, rows, cols, x)
-        assert rel_err(got, want) <= MATVEC_RTOL
-        y0 = rng.standard_normal(rows).astype(np.float32)
-        wd, xd, yd = dev(w), dev(x), dev(y0)
-        torch.cuda.synchronize()
-        ctx.matvec(capi.Q4_K, wd, rows, cols, xd, yd)
-        ctx.sync()
-        assert rel_err(yd.cpu().numpy(), y0 + want) <= MATVEC_RTOL
-    monkeypatch.delenv("FLB_MMA")
-    got2 = gpu_matvec(ctx, capi.Q4_K, w, rows, cols, x)     # the default kernel on the same input
-    assert rel_err(got2, got) <= 1e-5
-
-
 def test_matvec_config0_vs_f64_and_golden(ctx, checker):
     c0 = synth.config0(0)
     got = gpu_matvec(ctx, capi.Q4_K, c0["w"], 4096, 4096, c0["x"])
