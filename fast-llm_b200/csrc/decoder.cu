@@ -338,6 +338,8 @@ int fl_b200_decoder_create_tp(fl_b200_ctx *ctx, const fl_b200_llama_cfg *cfg, ui
     d->ffn_norm.assign(c.n_layer, nullptr);
     d->kc.assign(c.n_layer, nullptr);
     d->vc.assign(c.n_layer, nullptr);
+    // every failure from here on destroys d (the KV caches already allocated would otherwise stay for the life of the process)
+    auto alloc = [&]() -> int {
     CK(cudaSetDevice(ctx->device));
     const size_t kvb = (size_t)d->Hkv * c.max_kv * c.head_dim * sizeof(__half);
     for (uint32_t l = 0; l < c.n_layer; ++l) {
@@ -382,6 +384,13 @@ int fl_b200_decoder_create_tp(fl_b200_ctx *ctx, const fl_b200_llama_cfg *cfg, ui
     CK(cudaMemsetAsync(d->tickets, 0, 256 * sizeof(uint32_t), ctx->stream));
     CK(cudaMallocHost(&d->h_pin, 64));
     CK(cudaStreamSynchronize(ctx->stream));
+    return FL_B200_OK;
+    };
+    const int rc = alloc();
+    if (rc != FL_B200_OK) {
+        fl_b200_decoder_destroy(d);
+        return rc;
+    }
     *out = d;
     return FL_B200_OK;
 }
@@ -554,7 +563,9 @@ int fl_b200_decoder_step(fl_b200_decoder *d, int32_t token, int32_t *next_out) {
     d->h_pin[1] = 0;            // next (unused on the way in)
     d->h_pin[2] = d->n_past;
     d->h_pin[3] = 0;            // history counter
-    CK(cudaMemcpyAsync(d->d_token, d->h_pin, 16, cudaMemcpyHostToDevice, s));
+    d->h_pin[4] = 0;
+    d->h_pin[5] = 0;            // teacher forcing off, whatever an earlier failed call left behind
+    CK(cudaMemcpyAsync(d->d_token, d->h_pin, 24, cudaMemcpyHostToDevice, s));
     if (d->trace) trace_init_kernel<<<(d->trace_n * 4 + 255) / 256, 256, 0, s>>>(d->trace, d->trace_n);
     CK(cudaGraphLaunch(d->exec, s));
     CK(cudaMemcpyAsync(d->h_pin + 8, d->d_next, 4, cudaMemcpyDeviceToHost, s));
@@ -575,7 +586,9 @@ int fl_b200_decoder_run(fl_b200_decoder *d, int32_t first_token, uint32_t n, int
     d->h_pin[1] = 0;
     d->h_pin[2] = d->n_past;
     d->h_pin[3] = 0;
-    CK(cudaMemcpyAsync(d->d_token, d->h_pin, 16, cudaMemcpyHostToDevice, s));
+    d->h_pin[4] = 0;
+    d->h_pin[5] = 0;            // teacher forcing off
+    CK(cudaMemcpyAsync(d->d_token, d->h_pin, 24, cudaMemcpyHostToDevice, s));
     for (uint32_t i = 0; i < n; ++i) CK(cudaGraphLaunch(d->exec, s));
     CK(cudaMemcpyAsync(tokens_host, d->d_hist, (size_t)n * 4, cudaMemcpyDeviceToHost, s));
     CK(cudaStreamSynchronize(s));
@@ -847,8 +860,8 @@ int fl_b200_decoder_time_class(fl_b200_decoder *d, uint32_t kernel_class, uint32
     if (kernel_class == 0 || kernel_class > K_ALL || reps == 0) return set_err(FL_B200_ERR_ARG, "decoder_time_class: bad class / reps");
     if ((uint32_t)d->n_past >= d->c.max_kv) return set_err(FL_B200_ERR_STATE, "decoder_time_class: kv full");
     cudaStream_t s = d->ctx->stream;
-    d->h_pin[0] = 0; d->h_pin[1] = 0; d->h_pin[2] = d->n_past; d->h_pin[3] = 0;
-    CK(cudaMemcpyAsync(d->d_token, d->h_pin, 16, cudaMemcpyHostToDevice, s));
+    d->h_pin[0] = 0; d->h_pin[1] = 0; d->h_pin[2] = d->n_past; d->h_pin[3] = 0; d->h_pin[4] = 0; d->h_pin[5] = 0;
+    CK(cudaMemcpyAsync(d->d_token, d->h_pin, 24, cudaMemcpyHostToDevice, s));
     // Bit 4 keeps the mask different from K_ALL, so the advance kernel is left
     // out and the position stays put over the replays.
     const uint32_t m = kernel_class | 16u;

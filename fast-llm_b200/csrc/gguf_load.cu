@@ -12,8 +12,10 @@
 
 #include <cctype>
 #include <cstdio>
+#include <cstdint>
 #include <cstdlib>
 #include <cstring>
+#include <exception>
 #include <fcntl.h>
 #include <map>
 #include <string>
@@ -77,8 +79,11 @@ uint32_t scalar_bytes(uint32_t t) {
     }
 }
 
-// Skips one array value (element type and count follow); arrays may nest.
-bool skip_array(Reader &r, std::vector<std::string> *keep_strings) {
+// Skips one array value (element type and count follow); arrays may nest, up to kMaxArrayDepth levels (a nested
+// level costs 12 bytes of input, so an unbounded depth would let a small file exhaust the stack).
+constexpr int kMaxArrayDepth = 4;
+bool skip_array(Reader &r, std::vector<std::string> *keep_strings, int depth = 0) {
+    if (depth >= kMaxArrayDepth) return false;
     const uint32_t et = r.get<uint32_t>();
     const uint64_t n = r.get<uint64_t>();
     if (et == V_STR) {
@@ -91,7 +96,7 @@ bool skip_array(Reader &r, std::vector<std::string> *keep_strings) {
     }
     if (et == V_ARR) {
         for (uint64_t i = 0; i < n; ++i)
-            if (!skip_array(r, nullptr)) return false;
+            if (!skip_array(r, nullptr, depth + 1)) return false;
         return true;
     }
     const uint32_t sz = scalar_bytes(et);
@@ -209,7 +214,8 @@ int map_file(fl_b200_gguf *g, const std::string &path, bool keep_meta) {
                 Reader look = r;
                 const bool strings = look.get<uint32_t>() == V_STR;
                 if (!skip_array(r, strings ? &meta->string_arrays[key] : nullptr))
-                    return set_err(FL_B200_ERR_FORMAT, "gguf: %s: bad array element type in '%s'", path.c_str(), key.c_str());
+                    return set_err(FL_B200_ERR_FORMAT, "gguf: %s: bad element type or more than %d nested levels in array '%s'",
+                                   path.c_str(), kMaxArrayDepth, key.c_str());
                 break;
             }
             default:
@@ -234,10 +240,19 @@ int map_file(fl_b200_gguf *g, const std::string &path, bool keep_meta) {
             t.type = r.get<uint32_t>();
             t.offset = r.get<uint64_t>();
             const int fmt = fmt_of_ggml(t.type);
-            const uint64_t outer = t.ne[1] * t.ne[2] * t.ne[3];
-            if (fmt >= 0) t.nbytes = any_row_bytes(fmt, t.ne[0]) * outer;
-            else if (t.type == FL_B200_GGML_F16) t.nbytes = 2 * t.ne[0] * outer;
-            else t.nbytes = 0;   // a type without kernels: visible in the listing, payload unusable
+            // sizes with checked arithmetic: a wrapped product could pass the runs-past-the-end check below
+            uint64_t outer = 0, row = 0;
+            bool bad = t.ne[0] > UINT32_MAX;   // row_bytes takes 32-bit column counts
+            bad = bad || __builtin_mul_overflow(t.ne[1], t.ne[2], &outer) || __builtin_mul_overflow(outer, t.ne[3], &outer);
+            if (!bad) {
+                if (fmt >= 0) row = any_row_bytes(fmt, t.ne[0]);
+                else if (t.type == FL_B200_GGML_F16) row = 2 * t.ne[0];
+                // any other type has no kernels: visible in the listing with nbytes 0, payload unusable
+                bad = __builtin_mul_overflow(row, outer, &t.nbytes);
+            }
+            if (bad)
+                return set_err(FL_B200_ERR_FORMAT, "gguf: %s: tensor '%s' has dimensions whose size does not fit 64 bits",
+                               path.c_str(), t.name.c_str());
             t.shard = shard;
             g->tensors.push_back(std::move(t));
         }
@@ -251,6 +266,8 @@ int map_file(fl_b200_gguf *g, const std::string &path, bool keep_meta) {
         }
     } catch (const Truncated &) {
         return set_err(FL_B200_ERR_FORMAT, "gguf: %s: truncated file", path.c_str());
+    } catch (const std::exception &e) {   // bad_alloc / length_error from a string or vector a hostile count asked for
+        return set_err(FL_B200_ERR_FORMAT, "gguf: %s: %s while reading the metadata", path.c_str(), e.what());
     }
     return FL_B200_OK;
 }
@@ -290,10 +307,12 @@ extern "C" {
 int fl_b200_gguf_open(const char *path, fl_b200_gguf **out) {
     if (!path || !out) return set_err(FL_B200_ERR_ARG, "gguf_open: null pointer");
     *out = nullptr;
-    fl_b200_gguf *g = new fl_b200_gguf();
+    fl_b200_gguf *g = nullptr;
+    int rc = FL_B200_OK;
+    try {
+    g = new fl_b200_gguf();
     std::string pattern;
     const int parts = split_pattern(path, &pattern);
-    int rc = FL_B200_OK;
     if (parts <= 1) {
         rc = map_file(g, path, true);
     } else {
@@ -306,6 +325,9 @@ int fl_b200_gguf_open(const char *path, fl_b200_gguf **out) {
         if (rc == FL_B200_OK && want != g->ints.end() && want->second > 0 && (int64_t)g->tensors.size() != want->second)
             rc = set_err(FL_B200_ERR_FORMAT, "gguf: split.tensors.count = %lld but the shards hold %zu tensors",
                          (long long)want->second, g->tensors.size());
+    }
+    } catch (const std::exception &e) {   // nothing may cross the C boundary
+        rc = set_err(FL_B200_ERR_IO, "gguf_open: %s", e.what());
     }
     if (rc != FL_B200_OK) {
         delete g;

@@ -21,6 +21,8 @@ import numpy as np
 HERE = os.path.dirname(os.path.abspath(__file__))
 PORT_LIB = os.path.join(HERE, "liboracle.so")
 REF_LIB = os.path.join(HERE, "_ref", "libflref.so")
+# the same reference sources at -O3 -march=x86-64-v3 (AVX2 + FMA): a timed CPU baseline, never a checker
+REF_O3_LIB = os.path.join(HERE, "_ref", "libflref_o3.so")
 # the reference checkout: FLB_REFERENCE, else a directory named "reference" beside this repository
 REF_SRC = os.environ.get("FLB_REFERENCE") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
 
@@ -33,6 +35,19 @@ def _newer(a, b):
     return os.path.exists(a) and (not os.path.exists(b) or os.path.getmtime(a) > os.path.getmtime(b))
 
 
+def host_has_avx2_fma():
+    """True when this host's cores can run the x86-64-v3 build (libflref_o3.so)."""
+    try:
+        with open("/proc/cpuinfo") as f:
+            for line in f:
+                if line.startswith("flags"):
+                    flags = set(line.split(":", 1)[1].split())
+                    return {"avx2", "fma", "bmi2", "f16c"} <= flags
+    except OSError:
+        pass
+    return False
+
+
 def build(which="all"):
     """Builds what is missing or stale. Returns (port_ok, ref_ok)."""
     srcs = [os.path.join(HERE, f) for f in ("oracle.c", "llama_oracle.c", "flo_ops.h")]
@@ -42,6 +57,9 @@ def build(which="all"):
         shim = [os.path.join(HERE, f) for f in ("ref_shim.cpp", "flo_ops.h", "abi_check.cpp")]
         if any(_newer(s, REF_LIB) for s in shim):
             subprocess.run(["make", "-C", HERE, "ref", "REF=" + REF_SRC], check=True, stdout=subprocess.PIPE,
+                           stderr=subprocess.STDOUT)
+        if any(_newer(s, REF_O3_LIB) for s in shim):
+            subprocess.run(["make", "-C", HERE, "ref_o3", "REF=" + REF_SRC], check=True, stdout=subprocess.PIPE,
                            stderr=subprocess.STDOUT)
     return os.path.exists(PORT_LIB), os.path.exists(REF_LIB)
 
@@ -87,7 +105,8 @@ def _f32(a):
 class Oracle:
     """One of the two oracles, through the shared operator table."""
 
-    def __init__(self, kind="port"):
+    def __init__(self, kind="port", ref_lib=None):
+        """ref_lib: another build of the reference library (REF_O3_LIB) for kind == "reference"."""
         build()
         if not os.path.exists(PORT_LIB):
             raise RuntimeError("oracle/liboracle.so could not be built")
@@ -98,9 +117,10 @@ class Oracle:
             self.ops = self.port.flo_port_ops()
             self.ref = None
         elif kind == "reference":
-            if not os.path.exists(REF_LIB):
-                raise RuntimeError("oracle/_ref/libflref.so is not available (no reference checkout, no prebuilt copy)")
-            self.ref = C.CDLL(REF_LIB)
+            lib = ref_lib or REF_LIB
+            if not os.path.exists(lib):
+                raise RuntimeError("%s is not available (no reference checkout, no prebuilt copy)" % os.path.relpath(lib, HERE))
+            self.ref = C.CDLL(lib)
             self.ref.flref_ops.restype = C.POINTER(Ops)
             self.ops = self.ref.flref_ops()
             self.ref.flref_dot_row.restype = C.c_float

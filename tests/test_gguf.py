@@ -209,6 +209,21 @@ def test_malformed_files_return_a_status(tmp_path):
     bad_type = bytearray()
     bad_type += struct.pack("<IIQQ", 0x46554747, 3, 0, 1) + struct.pack("<Q", 1) + b"k" + struct.pack("<I", 13)
     assert code_of(bytes(bad_type)) == 6                                   # value type 13 does not exist
+    # arrays nested deeper than the reader follows (12 bytes per level: a few MB would otherwise overflow the stack)
+    hdr = struct.pack("<IIQQ", 0x46554747, 3, 0, 1) + struct.pack("<Q", 1) + b"k" + struct.pack("<I", 9)
+    assert code_of(hdr + struct.pack("<IQ", 9, 1) * 400000 + struct.pack("<IQ", 4, 0)) == 6
+    nested_ok = tmp_path / "nested_ok.gguf"                                # three levels are followed
+    nested_ok.write_bytes(hdr + struct.pack("<IQ", 9, 1) * 2 + struct.pack("<IQ", 4, 2) + struct.pack("<II", 7, 8))
+    with gguf.Gguf(nested_ok) as g:
+        assert len(list(g.tensors())) == 0
+    # dimensions whose byte size wraps around 64 bits must not pass the bounds check
+    def one_tensor(ne, ggml_type=12):
+        rec = struct.pack("<Q", 1) + b"t" + struct.pack("<I", len(ne)) + b"".join(struct.pack("<Q", n) for n in ne)
+        return struct.pack("<IIQQ", 0x46554747, 3, 1, 0) + rec + struct.pack("<IQ", ggml_type, 0) + bytes(64)
+    assert code_of(one_tensor([256, 2 ** 32, 2 ** 32])) == 6              # ne[1] * ne[2] wraps to 0
+    assert code_of(one_tensor([256, 2 ** 62, 1, 1])) == 6                 # 144 * 2^62 wraps
+    assert code_of(one_tensor([2 ** 32 + 256, 1])) == 6                   # a row longer than 32 bits of columns
+    assert code_of(one_tensor([256, 2 ** 40])) == 6                       # honest but larger than the file
     p = tmp_path / "odd_align.gguf"
     gguf.write_gguf(p, [], [], alignment=48)
     with pytest.raises(capi.Fl200Error) as e:
