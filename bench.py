@@ -39,7 +39,7 @@ N_PREFILL = 8192
 METRIC = "decode tokens/s at 8B Q4_K_M shape, 1/2/4/8 B200; HBM GB/s % of roofline"
 
 
-NCU_TRAFFIC_RATIO = 1.0095
+NCU_TRAFFIC_RATIO = 1.0079
 TIMED_REGION_MS = 1000.0   # device time the repeated K-step loops add up to, at least
 
 
@@ -224,6 +224,8 @@ def main():
                          "through peer memory; strong scaling; the headline value); replicas = one independent sequence "
                          "per GPU (weak scaling); both = tp as the headline and the replica measurement of the same run "
                          "under the key \"replicas\"")
+    ap.add_argument("--region-ms", type=float, default=TIMED_REGION_MS,
+                    help="device time the repeated K-step loops add up to, at least (0 = one repetition: profiler captures)")
     ap.add_argument("--layers", type=int, default=32,
                     help="number of layers (32 = the benchmark; fewer = a small case of the same kernels for profiler captures, not a benchmark number)")
     ap.add_argument("--case", default="decode", choices=["decode", "matmul-nx8", "attn-long", "moe"],
@@ -562,7 +564,7 @@ def measure(tp_mode, args, ctx, cfg, config, dist, gloo, rank, local_rank, world
             ms = ctx.timer_stop()
             barrier()
             times.append(max_over_ranks(ms))
-            if len(times) >= 15 or (sum(times) >= TIMED_REGION_MS and len(times) % 2 == 1):
+            if len(times) >= 15 or (sum(times) >= args.region_ms and len(times) % 2 == 1):
                 break
         return sorted(times)[len(times) // 2], times, res
 
@@ -611,7 +613,7 @@ def measure(tp_mode, args, ctx, cfg, config, dist, gloo, rank, local_rank, world
                      "peak_source": "MEASURED_PEAKS.json hbm_gbs" if peak_kind == "measured" else "fallback 6.65 TB/s",
                      "unit": "GB/s", "frac": achieved / peak,
                      # dram__bytes_read.sum + dram__bytes_write.sum of the four matvec launch shapes in one ncu
-                     # capture (profiles/matvec_stream_kernel_8b_layer_shapes.md) were 1.0095 x their algorithmic
+                     # capture (profiles/matvec_tc_kernel_8b_layer_shapes.md) were 1.0079 x their algorithmic
                      # bytes; traffic grows in proportion to the weights streamed, so it is scaled to this launch mix
                      "traffic": NCU_TRAFFIC_RATIO * w_bytes / mv_n,
                      "bytes_per_launch": w_bytes / mv_n, "launches_per_step": mv_n, "avg_launch_us": mv_ms * 1e3 / mv_n,

@@ -259,6 +259,16 @@ __device__ __forceinline__ void q4k_block_nx(uint32_t r0, const uint32_t (&ow)[4
     for (int r = 0; r < 2; ++r)
 #pragma unroll
         for (int tg = 0; tg < NTG; ++tg) accq[r][tg] = accm[r][tg] = 0.f;
+    // the mins against the sub-block sums first: the sums' registers are free again before the unpacking starts
+#pragma unroll
+    for (int sb = 0; sb < 8; ++sb)
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            const uint32_t mw = mnw[r][sb >> 2];
+            const float mnf = (sb & 3) == 0 ? u8f<0>(mw) : (sb & 3) == 1 ? u8f<1>(mw) : (sb & 3) == 2 ? u8f<2>(mw) : u8f<3>(mw);
+#pragma unroll
+            for (int tg = 0; tg < NTG; ++tg) accm[r][tg] = fmaf(mnf, sums[tg][sb], accm[r][tg]);
+        }
     const uint32_t ML = 0x000F000Fu, KL = 0x64006400u, MH = 0x00F000F0u, KH = 0x54005400u;
     const __half2 oL = __floats2half2_rn(1024.f, 1024.f), oH = __floats2half2_rn(64.f, 64.f);
 #pragma unroll
@@ -276,13 +286,12 @@ __device__ __forceinline__ void q4k_block_nx(uint32_t r0, const uint32_t (&ow)[4
 #pragma unroll
         for (int sub = 0; sub < 2; ++sub) {
             const int sb = 2 * c + sub;
-            // scale and min of sub-block sb for both rows, as floats
-            float scf[2], mnf[2];
+            // scale of sub-block sb for both rows, as floats
+            float scf[2];
 #pragma unroll
             for (int r = 0; r < 2; ++r) {
-                const uint32_t sw = scw[r][sb >> 2], mw = mnw[r][sb >> 2];
+                const uint32_t sw = scw[r][sb >> 2];
                 scf[r] = (sb & 3) == 0 ? u8f<0>(sw) : (sb & 3) == 1 ? u8f<1>(sw) : (sb & 3) == 2 ? u8f<2>(sw) : u8f<3>(sw);
-                mnf[r] = (sb & 3) == 0 ? u8f<0>(mw) : (sb & 3) == 1 ? u8f<1>(mw) : (sb & 3) == 2 ? u8f<2>(mw) : u8f<3>(mw);
             }
 #pragma unroll
             for (int tg = 0; tg < NTG; ++tg) {
@@ -298,8 +307,6 @@ __device__ __forceinline__ void q4k_block_nx(uint32_t r0, const uint32_t (&ow)[4
                 }
                 accq[0][tg] = fmaf(scf[0], cc[0] + cc[1], accq[0][tg]);
                 accq[1][tg] = fmaf(scf[1], cc[2] + cc[3], accq[1][tg]);
-                accm[0][tg] = fmaf(mnf[0], sums[tg][sb], accm[0][tg]);
-                accm[1][tg] = fmaf(mnf[1], sums[tg][sb], accm[1][tg]);
             }
         }
     }
