@@ -283,6 +283,8 @@ class LlamaOracle:
     def set_layer_norms(self, layer, an, fn):
         an = _f32(an); fn = _f32(fn)
         self._keep += [an, fn]
+        if layer == 0:
+            self._attn_norm0 = an   # the live array the C side reads (one_ulp_move)
         self.p.flo_llama_set_layer_norms(self.h, C.c_uint32(layer), _ptr(an), _ptr(fn))
 
     def set_global(self, which, fmt, w):
@@ -312,6 +314,25 @@ class LlamaOracle:
 
     def logits(self):
         return np.ctypeslib.as_array(self.p.flo_llama_logits(self.h), shape=(self.cfg["n_vocab"],)).copy()
+
+    def one_ulp_move(self, token):
+        """Conditioning of the step just taken (call right after step(token)): the step is repeated with every
+        attn_norm weight of layer 0 one f32 ulp larger, then once more unperturbed (which restores the K/V rows
+        and every tap). Returns max |logits' - logits| / RMS(logits): how far the ORACLE's own result moves for
+        the smallest possible change of one input."""
+        pos = self.n_past() - 1
+        base = self.logits()
+        an = self._attn_norm0
+        keep = an.copy()
+        an[:] = np.nextafter(an, np.float32(4.0))
+        self.set_n_past(pos)
+        self.step(token)
+        moved = self.logits()
+        an[:] = keep
+        self.set_n_past(pos)
+        self.step(token)
+        assert np.array_equal(self.logits(), base)
+        return float(np.max(np.abs(moved - base)) / (np.sqrt(np.mean(base.astype(np.float64) ** 2)) + 1e-30))
 
     def hidden(self):
         return np.ctypeslib.as_array(self.p.flo_llama_hidden(self.h), shape=(self.cfg["n_embd"],)).copy()
