@@ -330,7 +330,8 @@ def kernel_case(case, steps, warmup):
         run(steps)
         us = ctx.timer_stop() * 1e3 / steps
         nbytes = rows * capi.row_bytes(capi.Q4_K, cols)
-        print(json.dumps({"case": case, "kernel": "matmul_tc_nx_kernel", "rows": rows, "cols": cols, "columns": nx,
+        print(json.dumps({"case": case, "kernel": "matmul_umma_kernel (tcgen05, FLB_UMMA=1)" if os.environ.get("FLB_UMMA", "")[:1] == "1" else "matmul_tc_nx_kernel",
+                          "rows": rows, "cols": cols, "columns": nx,
                           "us_per_pass": us, "weight_bytes": nbytes, "achieved_gbs": nbytes / us / 1e3,
                           "frac_of_measured_hbm": nbytes / us / 1e3 / peak, "status": ctx.status()}))
         return

@@ -6,7 +6,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libfl_b200.so")
-SOURCES = ["dequant.cu", "matvec.cu", "matvec_tc.cu", "matvec_tc_nx.cu", "attn.cu", "glue.cu", "comm.cu", "capi.cu", "decoder.cu", "gguf_load.cu", "spec.cu", "moe.cu"]
+SOURCES = ["dequant.cu", "matvec.cu", "matvec_tc.cu", "matvec_tc_nx.cu", "matmul_umma.cu", "attn.cu", "glue.cu", "comm.cu", "capi.cu", "decoder.cu", "gguf_load.cu", "spec.cu", "moe.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-shared",

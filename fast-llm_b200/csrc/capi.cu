@@ -87,6 +87,11 @@ int fl_b200_create(int device, fl_b200_ctx **out) {
     CK(matvec_tc_init());
     CK(matmul_tc_nx_init());
     CK(cudaMalloc(&c->xq, matmul_tc_nx_scratch_bytes(18432, 8)));   // the widest activation the kernels take, 8 columns
+    CK(matmul_umma_init());
+    CK(cudaMalloc(&c->xu, matmul_umma_xu_bytes(18432)));
+    CK(cudaMalloc(&c->um_scratch, matmul_umma_scratch_bytes()));
+    CK(cudaMalloc(&c->um_tickets, matmul_umma_ticket_count() * sizeof(uint32_t)));
+    CK(cudaMemset(c->um_tickets, 0, matmul_umma_ticket_count() * sizeof(uint32_t)));
     CK(attn_init());
     *out = c;
     return FL_B200_OK;
@@ -98,6 +103,7 @@ void fl_b200_destroy(fl_b200_ctx *c) {
     cudaStreamSynchronize(c->stream);
     cudaFree(c->attn_part);
     cudaFree(c->xq);
+    cudaFree(c->xu); cudaFree(c->um_scratch); cudaFree(c->um_tickets);
     for (void *p : c->retired) cudaFree(p);
     cudaFree(c->attn_tickets);
     cudaFree(c->argmax_scratch);
@@ -248,7 +254,12 @@ int flb::matmul(fl_b200_ctx *c, int fmt, const void *w, uint32_t rows, uint32_t 
             if (x2) nc.x2 = x2 + (size_t)p0 * xstride;
             nc.skip_convert = (same_columns && nx <= 8) ? 1 : 0;   // with more than 8 columns the scratch holds the last chunk only
             nc.y = y + (size_t)p0 * ystride; nc.ystride = ystride; nc.accumulate = accumulate;
-            const cudaError_t e = launch_matmul_tc_nx(nc, c->xq, c->status, c->sms, c->stream);
+            // Q4_K: tcgen05 with the accumulator in tensor memory; what it does not take goes to the mma.sync kernel
+            cudaError_t e = launch_matmul_umma(nc, c->xu, c->um_scratch, c->um_tickets, c->status, c->sms, c->stream);
+            if (e == cudaErrorNotSupported) {
+                if (fmt == FL_B200_Q4_K) nc.skip_convert = 0;   // the other kernel's scratch does not hold these columns
+                e = launch_matmul_tc_nx(nc, c->xq, c->status, c->sms, c->stream);
+            }
             if (e == cudaErrorNotSupported) break;   // the shape does not qualify (same answer for every chunk)
             if (e != cudaSuccess) return cuda_err(e, "multi-column matmul launch");
             first_single = p0 + nt;

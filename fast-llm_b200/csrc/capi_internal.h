@@ -23,6 +23,9 @@ struct fl_b200_ctx {
     float *argmax_scratch = nullptr;
     void *small = nullptr;
     uint8_t *xq = nullptr;               // converted activations of the multi-column matmul (fixed size, see fl_b200_create)
+    uint8_t *xu = nullptr;               // the same for the tcgen05 matmul, with its split-K scratch and tickets
+    float *um_scratch = nullptr;
+    uint32_t *um_tickets = nullptr;
     uint32_t *grid_bar = nullptr;        // barrier state of the chained matvec launches (two words, zero between launches)
     uint64_t wait_limit_ns = 0;          // limit of the exchange kernels' waits for other ranks (0 = one second)
     void *stage = nullptr;               // device staging for the *_host entry points

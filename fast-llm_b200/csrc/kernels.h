@@ -111,6 +111,15 @@ struct NxCall {
 cudaError_t launch_matmul_tc_nx(const NxCall &c, uint8_t *xq, uint32_t *status, int sms, cudaStream_t stream);
 size_t matmul_tc_nx_scratch_bytes(uint32_t cols, uint32_t P);
 cudaError_t matmul_tc_nx_init(void);
+// The same call on tcgen05 with the accumulator in tensor memory (matmul_umma.cu; Q4_K). xu: device scratch of
+// matmul_umma_xu_bytes(cols) bytes for the converted activations; scratch / tickets: split-K partial results and their
+// counters (matmul_umma_scratch_bytes() bytes, matmul_umma_ticket_count() zeroed words).
+cudaError_t launch_matmul_umma(const NxCall &c, uint8_t *xu, float *scratch, uint32_t *tickets, uint32_t *status, int sms,
+                               cudaStream_t stream);
+size_t matmul_umma_xu_bytes(uint32_t cols);
+size_t matmul_umma_scratch_bytes(void);
+size_t matmul_umma_ticket_count(void);
+cudaError_t matmul_umma_init(void);
 // True when launch_matvec would take the streaming kernel for this shape.
 bool matvec_is_streaming(int fmt, uint32_t cols);
 // Dynamic shared memory the streaming kernel needs for (cols, formats used).

@@ -455,6 +455,21 @@ def test_exec_task_stream_dot(ctx, checker):
     (capi.Q4_K, 256, 14336, 8), (capi.Q4_K, 37, 2048, 3), (capi.Q4_K, 1029, 4096, 6), (capi.Q4_K, 64, 768, 2),
 ])
 def test_stream_dot_multi_column_both_formats(ctx, checker, fmt, rows, cols, nx):
+    multi_column_case(ctx, checker, fmt, rows, cols, nx)
+
+
+@pytest.mark.parametrize("rows,cols,nx", [
+    (256, 14336, 8),      # two row tiles, the k range split over several work items (partial results through the ticket)
+    (4096, 4096, 8), (1029, 4096, 6), (37, 2048, 3), (64, 768, 2), (300, 14336, 9), (128, 512, 8),
+])
+def test_stream_dot_multi_column_tcgen05(ctx, checker, monkeypatch, rows, cols, nx):
+    """The same contract on the tcgen05 kernel (accumulator in tensor memory, split-K with ordered partial sums), which
+    is off by default: FLB_UMMA=1 is read at every call."""
+    monkeypatch.setenv("FLB_UMMA", "1")
+    multi_column_case(ctx, checker, capi.Q4_K, rows, cols, nx)
+
+
+def multi_column_case(ctx, checker, fmt, rows, cols, nx):
     """Task::nx > 1 on Q6_K as well as Q4_K tensors (draft verification, prompt chunks): all columns in one pass over
     the weights (up to 8 at a time); every column equals the reference's STREAM_DOT of that column, accumulate and
     assign-after-zero alike; ragged row counts, column counts that are not a multiple of 2048, strides with gaps."""
