@@ -254,6 +254,7 @@ int flb::matmul(fl_b200_ctx *c, int fmt, const void *w, uint32_t rows, uint32_t 
             if (x2) nc.x2 = x2 + (size_t)p0 * xstride;
             nc.skip_convert = (same_columns && nx <= 8) ? 1 : 0;   // with more than 8 columns the scratch holds the last chunk only
             nc.y = y + (size_t)p0 * ystride; nc.ystride = ystride; nc.accumulate = accumulate;
+            nc.pdl = pdl;
             // Q4_K: tcgen05 with the accumulator in tensor memory; what it does not take goes to the mma.sync kernel
             cudaError_t e = launch_matmul_umma(nc, c->xu, c->um_scratch, c->um_tickets, c->status, c->sms, c->stream);
             if (e == cudaErrorNotSupported) {

@@ -107,6 +107,7 @@ struct NxCall {
     // block out_idx[col_off + p]; only columns col_off + p < *cnt exist. All nullptr: column p = row p -> row block p.
     const uint32_t *cnt, *col_idx, *out_idx;
     uint32_t col_off;
+    int pdl;                 // the launches of this call are programmatic dependents of the launch before them
 };
 cudaError_t launch_matmul_tc_nx(const NxCall &c, uint8_t *xq, uint32_t *status, int sms, cudaStream_t stream);
 size_t matmul_tc_nx_scratch_bytes(uint32_t cols, uint32_t P);

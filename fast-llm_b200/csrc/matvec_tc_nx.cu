@@ -134,6 +134,10 @@ __global__ void __launch_bounds__(64) act_convert_nx_kernel(const float *__restr
                                                             const uint32_t *__restrict__ col_idx) {
     const uint32_t blk = blockIdx.x, tg = blockIdx.y;
     const uint32_t pp = threadIdx.x >> 4, hl = threadIdx.x & 15u, p = 4 * tg + pp;
+    // launched as a programmatic dependent: the launch itself overlaps the tail of the kernel before, whose output
+    // (x, the column list) is read only after it has completed
+    griddep_launch_dependents();
+    griddep_wait();
     uint32_t n_valid = P;
     if (cnt) { const uint32_t c = *cnt; n_valid = c > col_off ? min(c - col_off, P) : 0u; }
     if (n_valid == 0) return;   // the matmul of this call returns at entry too
@@ -424,6 +428,11 @@ __global__ void __launch_bounds__((G * kCW + 2) * 32) matmul_tc_nx_kernel(const 
     const uint32_t nchunk = (nblk + kChunkBlks - 1) / kChunkBlks;
     const uint32_t units = (a.rows + 15) / 16;
     const uint32_t my_units = blockIdx.x < units ? (units - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    // Launched as a programmatic dependent. With a device-side column list the list decides whether any weight is read at
+    // all, so everything waits for the kernels before; without one the producer starts streaming the weights (constants)
+    // at once and only the finalizer, which fetches the converted activations and touches y, waits.
+    griddep_launch_dependents();
+    if (a.cnt) griddep_wait();
     uint32_t n_valid = a.P;   // listed columns of this call
     if (a.cnt) { const uint32_t c = *a.cnt; n_valid = c > a.col_off ? min(c - a.col_off, a.P) : 0u; }
     if (n_valid == 0) return;   // nothing routed here: no weights are read
@@ -441,14 +450,6 @@ __global__ void __launch_bounds__((G * kCW + 2) * 32) matmul_tc_nx_kernel(const 
     if (warp == kProducer) {
         uint32_t slot = 0, par = 1;
         for (uint32_t ch = 0; ch < nchunk; ++ch) {
-            // the chunk's activation image: one bulk copy per block (lanes in parallel), after the consumers left the last one
-            const uint32_t b0 = ch * kChunkBlks, nb = min(kChunkBlks, nblk - b0);
-            if (!mbar_wait_bounded(x_empty, (ch & 1u) ^ 1u, a.status)) return;
-            fence_proxy_async_smem();
-            const uint32_t blk_bytes = a.ntg * kXqBlk;
-            if (lane == 0) mbar_arrive_expect_tx(x_full, nb * blk_bytes);
-            __syncwarp();
-            if (lane < nb) bulk_g2s_addr(xs_addr + lane * blk_bytes, a.xq + (size_t)(b0 + lane) * blk_bytes, blk_bytes, x_full);
             const uint32_t seg0 = ch * (kChunkBlks / 8), seg1 = min(seg0 + kChunkBlks / 8, nseg);
             for (uint32_t k = 0; k < my_units; ++k) {
                 const uint32_t u = blockIdx.x + k * gridDim.x;
@@ -474,7 +475,17 @@ __global__ void __launch_bounds__((G * kCW + 2) * 32) matmul_tc_nx_kernel(const 
         // ---- finalizer: 16 rows x 8 tokens per unit; lane <-> outputs 4 lane .. 4 lane + 3 (row = o / 8, token = o % 8) ----
         float *uacc = (float *)(smem_raw + a.uacc_off);   // running sums of the units while the chunks go by
         uint32_t kk = 0;
+        if (!a.cnt) griddep_wait();   // the converted activations and y come from the kernels before
         for (uint32_t ch = 0; ch < nchunk; ++ch) {
+            {   // the chunk's activation image: one bulk copy per block (lanes in parallel), after the consumers left the last one
+                const uint32_t b0 = ch * kChunkBlks, nb = min(kChunkBlks, nblk - b0);
+                if (!mbar_wait_bounded(x_empty, (ch & 1u) ^ 1u, a.status)) return;
+                fence_proxy_async_smem();
+                const uint32_t blk_bytes = a.ntg * kXqBlk;
+                if (lane == 0) mbar_arrive_expect_tx(x_full, nb * blk_bytes);
+                __syncwarp();
+                if (lane < nb) bulk_g2s_addr(xs_addr + lane * blk_bytes, a.xq + (size_t)(b0 + lane) * blk_bytes, blk_bytes, x_full);
+            }
             for (uint32_t k = 0; k < my_units; ++k, ++kk) {
                 const uint32_t u = blockIdx.x + k * gridDim.x, buf = kk & 1u;
                 if (!mbar_wait_bounded(&red_full[buf], (kk >> 1) & 1u, a.status)) return;
@@ -623,8 +634,8 @@ cudaError_t launch_matmul_tc_nx(const NxCall &c, uint8_t *xq, uint32_t *status, 
                           : tensor_map_2d(&k.map, 8, c.w, pitch / 8, rows, pitch, segb / 8, 16, false);
     if (e != cudaSuccess) return e;
     if (!c.skip_convert) {
-        act_convert_nx_kernel<<<dim3(nblk, ntg), 64, 0, stream>>>(c.x, c.x2, c.xstride, P, fmt, xq, ntg, c.cnt, c.col_off, c.col_idx);
-        e = cudaGetLastError();
+        e = launch_kernel(act_convert_nx_kernel, dim3(nblk, ntg), dim3(64), 0, stream, c.pdl != 0, c.x, c.x2, c.xstride, P, fmt, xq, ntg,
+                          c.cnt, c.col_off, c.col_idx);
         if (e != cudaSuccess) return e;
     }
     k.w = (const uint8_t *)c.w; k.xq = xq; k.y = c.y; k.rows = rows; k.pitch = pitch; k.cols = cols; k.ystride = c.ystride; k.P = P; k.ntg = ntg;
@@ -648,12 +659,13 @@ cudaError_t launch_matmul_tc_nx(const NxCall &c, uint8_t *xq, uint32_t *status, 
     const size_t smem = layout(nslots, xo, uo, ro);
     k.nslots = nslots; k.x_off = (uint32_t)xo; k.uacc_off = (uint32_t)uo; k.ring_off = (uint32_t)ro;
     const dim3 block((groups * kCW + 2) * 32);
+    const bool pdl = c.pdl != 0;
     if (groups == 2) {
-        if (ntg == 1) return launch_kernel(matmul_tc_nx_kernel<1, 2>, dim3(grid), block, smem, stream, false, k);
-        return launch_kernel(matmul_tc_nx_kernel<2, 2>, dim3(grid), block, smem, stream, false, k);
+        if (ntg == 1) return launch_kernel(matmul_tc_nx_kernel<1, 2>, dim3(grid), block, smem, stream, pdl, k);
+        return launch_kernel(matmul_tc_nx_kernel<2, 2>, dim3(grid), block, smem, stream, pdl, k);
     }
-    if (ntg == 1) return launch_kernel(matmul_tc_nx_kernel<1, 1>, dim3(grid), block, smem, stream, false, k);
-    return launch_kernel(matmul_tc_nx_kernel<2, 1>, dim3(grid), block, smem, stream, false, k);
+    if (ntg == 1) return launch_kernel(matmul_tc_nx_kernel<1, 1>, dim3(grid), block, smem, stream, pdl, k);
+    return launch_kernel(matmul_tc_nx_kernel<2, 1>, dim3(grid), block, smem, stream, pdl, k);
 }
 
 } // namespace flb

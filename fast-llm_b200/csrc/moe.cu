@@ -259,6 +259,9 @@ static int moe_enqueue_per_slot(fl_b200_moe *m, const float *x, uint32_t n_tok, 
     return FL_B200_OK;
 }
 
+// the multi-column launches of the block as programmatic dependents of one another (FLB_MOE_PDL=0: plain launches)
+static const int kMoePdlNx = getenv("FLB_MOE_PDL") ? atoi(getenv("FLB_MOE_PDL")) : 1;
+
 static int moe_enqueue(fl_b200_moe *m, const float *x, uint32_t n_tok, float *y) {
     fl_b200_ctx *ctx = m->ctx;
     cudaStream_t s = ctx->stream;
@@ -282,6 +285,7 @@ static int moe_enqueue(fl_b200_moe *m, const float *x, uint32_t n_tok, float *y)
             g.fmt = c.fmt_gate_up; g.w = m->wg + (uint64_t)e * stride_gu; g.rows = F; g.cols = E;
             g.x = x; g.P = P; g.xstride = E; g.y = m->g; g.ystride = F;
             g.cnt = cnt; g.col_idx = toks; g.out_idx = pairs; g.col_off = off;
+            g.pdl = kMoePdlNx;
             cudaError_t er = launch_matmul_tc_nx(g, ctx->xq, ctx->status, ctx->sms, s);
             if (er == cudaErrorNotSupported) return set_err(FL_B200_ERR_ARG, "moe_forward: shape not taken by the multi-column matmul");
             CKM(er);
@@ -292,6 +296,7 @@ static int moe_enqueue(fl_b200_moe *m, const float *x, uint32_t n_tok, float *y)
             d.fmt = c.fmt_down; d.w = m->wd + (uint64_t)e * stride_d; d.rows = E; d.cols = F;
             d.x = m->g; d.x2 = m->u; d.P = P; d.xstride = F; d.y = m->part; d.ystride = E;
             d.cnt = cnt; d.col_idx = pairs; d.out_idx = pairs; d.col_off = off;
+            d.pdl = kMoePdlNx;
             er = launch_matmul_tc_nx(d, ctx->xq, ctx->status, ctx->sms, s);
             if (er == cudaErrorNotSupported) return set_err(FL_B200_ERR_ARG, "moe_forward: shape not taken by the multi-column matmul");
             CKM(er);
