@@ -170,11 +170,11 @@ def cpu_reference_arm(steps, warmup, threads=None):
 
 
 def cpu_pool_fast_arms(cores):
-    """The stronger CPU arms, as extra keys of cpu_baseline: the reference's own worker pool (Runtime,
-    gpu_enabled = false) with fast_kernels on (include/fastllm/fastllm.h:198), timed on the STREAM_DOT tiles of
-    one layer's seven tensors and of the output head; tokens/s = 1 / (32 t_layer + t_head). Attention, norms and
-    the other operators are left out, so the figure is an upper bound of what that pool decodes. Once with the
-    reference's own flags (-O2) and once with -O3 -march=x86-64-v3 (its AVX2 kernels), when the host has AVX2."""
+    """The other CPU arms, as extra keys of cpu_baseline: the reference's run_serial on one core and its own worker
+    pool (Runtime, gpu_enabled = false) with fast_kernels off (canonical) and on (include/fastllm/fastllm.h:198),
+    timed on the STREAM_DOT tiles of one layer's seven tensors and of the output head; tokens/s = 1 / (32 t_layer +
+    t_head). Attention, norms and the other operators are left out, so the figures are upper bounds of what these
+    decode. The fast pool once more at -O3 -march=x86-64-v3 (its AVX2 kernels), when the host has AVX2."""
     import numpy as np
     from fast_llm_b200 import synth
     from oracle import pyoracle
@@ -186,17 +186,21 @@ def cpu_pool_fast_arms(cores):
     head = (synth.Q4_K_M["output"], synth.llama_tensor(cfg, 0, "output"), (cfg["n_vocab"], cfg["n_embd"]))
     rng = np.random.default_rng(7)
     out = {}
-    libs = [("pool_fast_kernels", None, "-O2 -ffp-contract=off (the reference's flags)")]
+    # (key, library, build flags, threads (0 = run_serial on one core), fast_kernels, repetitions)
+    ref_flags = "-O2 -ffp-contract=off (the reference's flags)"
+    libs = [("run_serial_1_core", None, ref_flags, 0, False, 1),
+            ("pool_canonical", None, ref_flags, cores, False, 3),
+            ("pool_fast_kernels", None, ref_flags, cores, True, 3)]
     if os.path.exists(pyoracle.REF_O3_LIB) and pyoracle.host_has_avx2_fma():
-        libs.append(("pool_fast_kernels_o3_avx2", pyoracle.REF_O3_LIB, "-O3 -march=x86-64-v3 (AVX2 + FMA kernels)"))
-    for key, lib, flags in libs:
+        libs.append(("pool_fast_kernels_o3_avx2", pyoracle.REF_O3_LIB, "-O3 -march=x86-64-v3 (AVX2 + FMA kernels)", cores, True, 3))
+    for key, lib, flags, threads, fast, reps in libs:
         orc = pyoracle.Oracle("reference", ref_lib=lib)
 
         def t_of(fmt, w, shape):
             x = rng.standard_normal(shape[1]).astype(np.float32)
             best = None
-            for _ in range(3):
-                _, ns = orc.ref_stream_dot_tasks(fmt, w, shape[0], shape[1], x, cores, fast=True)
+            for _ in range(reps):
+                _, ns = orc.ref_stream_dot_tasks(fmt, w, shape[0], shape[1], x, threads, fast=fast)
                 best = ns if best is None else min(best, ns)
             return best * 1e-9
 
@@ -204,10 +208,10 @@ def cpu_pool_fast_arms(cores):
         t_head = t_of(*head)
         orc.ref_pool_shutdown()
         t_tok = 32.0 * t_layer + t_head
-        out[key] = {"value": 1.0 / t_tok, "unit": "tokens/s", "cores": cores, "kind": "reference", "build": flags,
+        out[key] = {"value": 1.0 / t_tok, "unit": "tokens/s", "cores": threads if threads > 0 else 1, "kind": "reference", "build": flags,
                     "sample": "STREAM_DOT tiles (192 rows) of one layer's seven tensors and of the output head through the "
-                              "reference's Runtime pool with fast_kernels on, best of 3 each, scaled to 32 layers; attention "
-                              "and the small operators left out (an upper bound)",
+                              "reference's %s, best of %d each, scaled to 32 layers; attention and the small operators left out "
+                              "(an upper bound)" % ("run_serial" if threads <= 0 else "Runtime pool with fast_kernels %s" % ("on" if fast else "off"), reps),
                     "ms_per_token": t_tok * 1e3}
     return out
 
