@@ -232,10 +232,11 @@ def main():
                     help="device time the repeated K-step loops add up to, at least (0 = one repetition: profiler captures)")
     ap.add_argument("--layers", type=int, default=32,
                     help="number of layers (32 = the benchmark; fewer = a small case of the same kernels for profiler captures, not a benchmark number)")
-    ap.add_argument("--case", default="decode", choices=["decode", "matmul-nx8", "attn-long", "moe"],
+    ap.add_argument("--case", default="decode", choices=["decode", "matmul-nx8", "attn-long", "moe", "moe-decode"],
                     help="decode = the benchmark (default). matmul-nx8 = the multi-column Q4_K matmul alone (gate|up shape, 8 "
                          "columns); attn-long = decode attention alone at 32K / 64K / 128K keys; moe = the MoE feed-forward "
-                         "block at the Mixtral shape (8 experts, top-2, 16 tokens; expert parallel under torchrun): kernel "
+                         "block at the Mixtral shape (8 experts, top-2, 16 tokens; expert parallel under torchrun); moe-decode = greedy "
+                         "decode of a whole synthetic Mixtral-8x7B-shape model (32 layers, 8 experts, top-2) on one GPU: kernel "
                          "cases for profiler captures and sweeps, each prints its own JSON line and is not the benchmark number")
     args = ap.parse_args()
     if args.case != "decode":
@@ -313,6 +314,8 @@ def kernel_case(case, steps, warmup):
     peak, _ = measured_peaks()
     if case == "moe":
         return moe_case(steps, warmup, peak)
+    if case == "moe-decode":
+        return moe_decode_case(steps, warmup, peak)
     if case == "attn-long" and int(os.environ.get("WORLD_SIZE", "1")) > 1:
         return attn_long_multi(steps, warmup, peak, int(os.environ.get("RANK", "0")), int(os.environ["WORLD_SIZE"]))
     ctx = capi.Context(0)
@@ -514,6 +517,57 @@ def moe_case(steps, warmup, peak):
     blk.close()
     if dist:
         dist.destroy_process_group()
+
+
+def moe_decode_case(steps, warmup, peak):
+    """Greedy decode of a synthetic Mixtral-8x7B-shape model on one GPU: 32 layers of the 8B shape's attention (hidden
+    4096, 32 / 8 heads) with the feed-forward block of every layer replaced by 8 experts (gate / up 14336 x 4096, down
+    4096 x 14336, Q4_K), top-2 routing with renormalised weights, f32 router ~ N(0, 0.02); vocabulary 32000; 4096
+    prefilled positions. Per token the step reads the attention tensors, the routers and 2 experts per layer."""
+    import torch
+    from fast_llm_b200 import capi, synth
+    from fast_llm_b200.decoder import Decoder
+    from fast_llm_b200.moe import MoeBlock
+    ctx = capi.Context(0)
+    n_prefill = 4096
+    cfg = dict(synth.LLAMA3_8B, n_vocab=32000, max_kv=n_prefill + steps + warmup + 64)
+    E, F, NE, K = cfg["n_embd"], cfg["n_ff"], 8, 2
+    dec = Decoder(ctx, cfg)
+    layers = range(cfg["n_layer"])
+    synth.device_llama(dec, cfg, seed=77, n_prefill=n_prefill, skip_ffn=set(layers))
+    dev = torch.device("cuda", 0)
+    gen = torch.Generator(device=dev); gen.manual_seed(5)
+    blocks = []
+    for l in layers:
+        blk = MoeBlock(ctx, E, F, NE, K, max_tokens=8)
+        blk.set_weights(torch.randn((NE, E), device=dev, generator=gen) * 0.02,
+                        synth.device_quant_tensor(capi.Q4_K, NE * F, E, gen), synth.device_quant_tensor(capi.Q4_K, NE * F, E, gen),
+                        synth.device_quant_tensor(capi.Q4_K, NE * E, F, gen))
+        dec.set_layer_moe(l, blk)
+        blocks.append(blk)
+    torch.cuda.synchronize(dev)
+    dec.finalize()
+    dec.rewind_to(n_prefill)
+    last = int(dec.run(1, warmup)[-1])
+    times = []
+    for _ in range(5):
+        dec.rewind_to(n_prefill + warmup)
+        ctx.sync()
+        ctx.timer_start()
+        toks = dec.run(last, steps)
+        times.append(ctx.timer_stop())
+    ms = sorted(times)[len(times) // 2] / steps
+    w_bytes, kv_bytes = dec.bytes_per_step(n_prefill + warmup + steps // 2)
+    print(json.dumps({"case": "moe-decode", "model": "synthetic Mixtral-8x7B shape, Q4_K experts, top-2 of 8, 4096-token prefilled f16 KV",
+                      "tokens_per_s": 1e3 / ms, "ms_per_token": ms, "steps": steps, "repeats": len(times),
+                      "launches_per_step": dec.launches_per_step(), "bytes_per_token": w_bytes + kv_bytes,
+                      "achieved_gbs": (w_bytes + kv_bytes) / ms / 1e6, "frac_of_measured_hbm": (w_bytes + kv_bytes) / ms / 1e6 / peak,
+                      "experts_read_per_token": 32 * K, "device_weight_gb": round((32 * NE * 3 * F * capi.row_bytes(capi.Q4_K, E)) / 1e9, 1),
+                      "last_token": int(toks[-1]), "status": ctx.status()}))
+    dec.close()
+    for b in blocks:
+        b.close()
+    ctx.close()
 
 
 def measure(tp_mode, args, ctx, cfg, config, dist, gloo, rank, local_rank, world, steps, warmup):

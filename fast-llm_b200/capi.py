@@ -32,7 +32,7 @@ SYMBOLS = [
     "fl_b200_silu_mul", "fl_b200_router_sel", "fl_b200_wmerge", "fl_b200_rope_kv_append", "fl_b200_argmax", "fl_b200_exec_task", "fl_b200_plan_create", "fl_b200_plan_run", "fl_b200_plan_info", "fl_b200_plan_destroy",
     "fl_b200_decoder_create", "fl_b200_decoder_create_tp", "fl_b200_decoder_comm", "fl_b200_decoder_set_peers",
     "fl_b200_decoder_destroy", "fl_b200_decoder_set_layer_tensor",
-    "fl_b200_decoder_set_layer_norms", "fl_b200_decoder_set_global", "fl_b200_decoder_set_out_norm",
+    "fl_b200_decoder_set_layer_norms", "fl_b200_decoder_set_layer_moe", "fl_b200_decoder_set_global", "fl_b200_decoder_set_out_norm",
     "fl_b200_decoder_kv", "fl_b200_decoder_finalize", "fl_b200_decoder_set_n_past",
     "fl_b200_decoder_n_past", "fl_b200_decoder_step", "fl_b200_decoder_run", "fl_b200_decoder_verify", "fl_b200_decoder_step_batch", "fl_b200_decoder_batch_logits", "fl_b200_decoder_logits",
     "fl_b200_decoder_margin", "fl_b200_decoder_tap", "fl_b200_decoder_time_class", "fl_b200_decoder_trace", "fl_b200_decoder_launches_per_step",

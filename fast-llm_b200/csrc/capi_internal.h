@@ -49,4 +49,14 @@ int matmul(fl_b200_ctx *c, int fmt, const void *w, uint32_t rows, uint32_t cols,
 // converted activations of the multi-column kernel are reused (Q/K after Q, up after gate).
 // Hands device memory to the decoder, which frees it when it is destroyed.
 void decoder_adopt(fl_b200_decoder *d, void *dev);
+// The MoE block inside a decoder step (moe.cu): y[t] = sum over the selected experts of gate * expert(x[t]) for
+// n_tok <= the block's max_tokens rows of x, enqueued on the block's context's stream (one token: one expert walk per
+// selected expert through the expert-indexed matvec; more: every expert once through the multi-column matmul).
+// *n_launch: launches enqueued.
+int moe_enqueue_tokens(fl_b200_moe *m, const float *x, uint32_t n_tok, float *y, uint32_t *n_launch);
+fl_b200_ctx *moe_ctx(const fl_b200_moe *m);
+const fl_b200_moe_cfg *moe_cfg(const fl_b200_moe *m);
+uint32_t moe_world(const fl_b200_moe *m);
+// Packed weight bytes one token reads in the block: the router and top_k experts.
+uint64_t moe_bytes_per_token(const fl_b200_moe *m);
 } // namespace flb

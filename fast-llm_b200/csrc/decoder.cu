@@ -70,6 +70,7 @@ struct fl_b200_decoder {
     float2 *rope_table = nullptr;           // (cos, sin) of this step's position, shared by all layers
     std::vector<Tensor> lw;                 // n_layer * 7
     std::vector<const float *> attn_norm, ffn_norm;
+    std::vector<fl_b200_moe *> moe;         // per layer: a mixture-of-experts block in place of gate / up / down (or nullptr)
     Tensor tok_embd, output;
     const float *out_norm = nullptr;
     std::vector<__half *> kc, vc;
@@ -254,6 +255,21 @@ static int enqueue_step(fl_b200_decoder *d, cudaStream_t s, uint32_t *n_launch, 
             if (d->trace && mask == K_ALL) a.trace = d->trace + 4 * (size_t)n;
             if (mask & K_ATTN) { CK(attn_make_maps(a)); CK(launch_attn_decode(a, s)); ++n; }
         }
+        if (d->moe[l]) {
+            // Mixture-of-experts layer: xb = xa + Wo att as usual, then xa = xb + MoE(RMSNorm(xb)). The block's own launches
+            // (router, selection, the selected experts through the expert-indexed matvec, merge) are part of the captured
+            // step; the normed vector borrows the head's buffer, the block's output the query buffer (free after attention).
+            MatvecArgs ao = mk_o(l);
+            if (mask & K_MATVEC) { if (int rc = do_matvec(ao)) return rc; ++n; }
+            if (mask & K_MATVEC) {
+                CK(launch_rmsnorm(d->xb, d->ffn_norm[l], d->xn_final, c.eps, E, s));
+                uint32_t nl = 0;
+                if (int rc = moe_enqueue_tokens(d->moe[l], d->xn_final, 1, d->q, &nl)) return rc;
+                CK(launch_add2(d->xb, d->q, d->xa, E, s));
+                n += 2 + nl;
+            }
+            continue;
+        }
         MatvecArgs ao = mk_o(l), ag = mk_gate_up(l);
         d->fused_swiglu = ag.swiglu != 0;
         MatvecArgs ad = mk_down(l, d->fused_swiglu);
@@ -336,6 +352,7 @@ int fl_b200_decoder_create_tp(fl_b200_ctx *ctx, const fl_b200_llama_cfg *cfg, ui
     d->lw.resize((size_t)c.n_layer * 7);
     d->attn_norm.assign(c.n_layer, nullptr);
     d->ffn_norm.assign(c.n_layer, nullptr);
+    d->moe.assign(c.n_layer, nullptr);
     d->kc.assign(c.n_layer, nullptr);
     d->vc.assign(c.n_layer, nullptr);
     // every failure from here on destroys d (the KV caches already allocated would otherwise stay for the life of the process)
@@ -494,11 +511,25 @@ int fl_b200_decoder_set_peers(fl_b200_decoder *d, void *const *bufs, uint32_t n)
     return FL_B200_OK;
 }
 
+int fl_b200_decoder_set_layer_moe(fl_b200_decoder *d, uint32_t layer, fl_b200_moe *moe) {
+    if (!d || !moe) return set_err(FL_B200_ERR_ARG, "decoder_set_layer_moe: null");
+    if (d->finalized) return set_err(FL_B200_ERR_STATE, "decoder_set_layer_moe: the decoder is finalized");
+    if (layer >= d->c.n_layer) return set_err(FL_B200_ERR_ARG, "decoder_set_layer_moe: layer %u of %u", layer, d->c.n_layer);
+    if (d->tp_size > 1 || moe_world(moe) > 1) return set_err(FL_B200_ERR_ARG, "decoder_set_layer_moe: one GPU only");
+    if (moe_ctx(moe) != d->ctx) return set_err(FL_B200_ERR_ARG, "decoder_set_layer_moe: the block belongs to another context");
+    const fl_b200_moe_cfg *mc = moe_cfg(moe);
+    if (mc->n_embd != d->c.n_embd) return set_err(FL_B200_ERR_ARG, "decoder_set_layer_moe: block n_embd %u, model %u", mc->n_embd, d->c.n_embd);
+    if (d->c.n_head * d->c.head_dim < d->c.n_embd) return set_err(FL_B200_ERR_ARG, "decoder_set_layer_moe: the query buffer is narrower than n_embd");
+    d->moe[layer] = moe;
+    return FL_B200_OK;
+}
+
 int fl_b200_decoder_finalize(fl_b200_decoder *d) {
     if (!d) return set_err(FL_B200_ERR_ARG, "decoder_finalize: null");
     if (d->finalized) return FL_B200_OK;
     for (size_t i = 0; i < d->lw.size(); ++i)
-        if (!d->lw[i].w) return set_err(FL_B200_ERR_STATE, "decoder_finalize: layer %zu tensor %zu not set", i / 7, i % 7);
+        if (!d->lw[i].w && !(d->moe[i / 7] && i % 7 >= FL_B200_T_GATE))   // a MoE layer has no gate / up / down of its own
+            return set_err(FL_B200_ERR_STATE, "decoder_finalize: layer %zu tensor %zu not set", i / 7, i % 7);
     for (uint32_t l = 0; l < d->c.n_layer; ++l)
         if (!d->attn_norm[l] || !d->ffn_norm[l]) return set_err(FL_B200_ERR_STATE, "decoder_finalize: norms of layer %u not set", l);
     if (!d->tok_embd.w || !d->output.w || !d->out_norm) return set_err(FL_B200_ERR_STATE, "decoder_finalize: embedding / head / output norm not set");
@@ -508,7 +539,7 @@ int fl_b200_decoder_finalize(fl_b200_decoder *d) {
     CK(cudaStreamSynchronize(s));
     if (const char *e = getenv("FLB_TRACE")) {
         if (e[0] == '1' && !d->trace) {
-            d->trace_n = 8 + 10 * d->c.n_layer;   // room for groups that go out one tensor per launch
+            d->trace_n = 8 + 16 * d->c.n_layer;   // room for groups that go out one tensor per launch
             CK(cudaMalloc(&d->trace, (size_t)d->trace_n * 4 * sizeof(unsigned long long)));
         }
     }
@@ -720,6 +751,11 @@ static int enqueue_batch(fl_b200_decoder *d, uint32_t m, cudaStream_t s) {
             if (int rc = sum_ranks()) return rc;
         }
         CK(launch_rmsnorm(b.x, d->ffn_norm[l], b.xn, c.eps, E, s, m, E));
+        if (d->moe[l]) {   // every expert once for the tokens that chose it, then x += the block's output
+            if (int rc = moe_enqueue_tokens(d->moe[l], b.xn, m, b.q, nullptr)) return rc;
+            CK(launch_add2(b.x, b.q, b.x, m * E, s));
+            continue;
+        }
         if (int rc = matmul(ctx, w[FL_B200_T_GATE].fmt, w[FL_B200_T_GATE].w, F, E, b.xn, m, E, b.g, F, 0, 0, nullptr, 0, kBatchPdl)) return rc;
         if (int rc = matmul(ctx, w[FL_B200_T_UP].fmt, w[FL_B200_T_UP].w, F, E, b.xn, m, E, b.u, F, 0, 0, nullptr, 0, kBatchPdl, nullptr,
                             w[FL_B200_T_UP].fmt == w[FL_B200_T_GATE].fmt)) return rc;
@@ -921,9 +957,10 @@ int fl_b200_decoder_bytes_per_step(fl_b200_decoder *d, int32_t pos, uint64_t *wb
     for (uint32_t l = 0; l < c.n_layer; ++l) {
         const Tensor *t = &d->lw[(size_t)l * 7];
         w += (uint64_t)QD * row_bytes(t[FL_B200_T_WQ].fmt, E) + (uint64_t)KD * row_bytes(t[FL_B200_T_WK].fmt, E) +
-             (uint64_t)KD * row_bytes(t[FL_B200_T_WV].fmt, E) + (uint64_t)E * row_bytes(t[FL_B200_T_WO].fmt, QD) +
-             (uint64_t)d->F * row_bytes(t[FL_B200_T_GATE].fmt, E) + (uint64_t)d->F * row_bytes(t[FL_B200_T_UP].fmt, E) +
-             (uint64_t)E * row_bytes(t[FL_B200_T_DOWN].fmt, d->F);
+             (uint64_t)KD * row_bytes(t[FL_B200_T_WV].fmt, E) + (uint64_t)E * row_bytes(t[FL_B200_T_WO].fmt, QD);
+        if (d->moe[l]) w += moe_bytes_per_token(d->moe[l]);   // the router and the selected experts
+        else w += (uint64_t)d->F * row_bytes(t[FL_B200_T_GATE].fmt, E) + (uint64_t)d->F * row_bytes(t[FL_B200_T_UP].fmt, E) +
+                  (uint64_t)E * row_bytes(t[FL_B200_T_DOWN].fmt, d->F);
         w += 2ull * E * 4;   // the two norm vectors
     }
     w += (uint64_t)d->V * row_bytes(d->output.fmt, E) + (uint64_t)E * 4;

@@ -316,6 +316,27 @@ static int moe_enqueue(fl_b200_moe *m, const float *x, uint32_t n_tok, float *y)
     return FL_B200_OK;
 }
 
+int flb::moe_enqueue_tokens(fl_b200_moe *m, const float *x, uint32_t n_tok, float *y, uint32_t *n_launch) {
+    if (!m || !m->router || !m->wg) return set_err(FL_B200_ERR_STATE, "moe: weights not set");
+    if (n_tok == 0 || n_tok > m->c.max_tokens) return set_err(FL_B200_ERR_ARG, "moe: %u tokens outside 1..%u", n_tok, m->c.max_tokens);
+    const fl_b200_moe_cfg &c = m->c;
+    if (n_tok == 1) {
+        const bool down_streams = matvec_is_streaming(c.fmt_down, c.n_ff) && row_bytes(c.fmt_down, c.n_ff) % 16 == 0;
+        if (n_launch) *n_launch = 2 + c.top_k * (down_streams ? 2u : 3u) + 1 + (m->world > 1 ? 1u : 0u);
+        return moe_enqueue_per_slot(m, x, 1, y);
+    }
+    if (n_launch) *n_launch = 0;   // not counted: the batch pass does not report launches
+    return moe_enqueue(m, x, n_tok, y);
+}
+fl_b200_ctx *flb::moe_ctx(const fl_b200_moe *m) { return m->ctx; }
+const fl_b200_moe_cfg *flb::moe_cfg(const fl_b200_moe *m) { return &m->c; }
+uint32_t flb::moe_world(const fl_b200_moe *m) { return m->world; }
+uint64_t flb::moe_bytes_per_token(const fl_b200_moe *m) {
+    const fl_b200_moe_cfg &c = m->c;
+    return (uint64_t)c.n_expert * c.n_embd * 4 +
+           (uint64_t)c.top_k * (2ull * c.n_ff * row_bytes(c.fmt_gate_up, c.n_embd) + (uint64_t)c.n_embd * row_bytes(c.fmt_down, c.n_ff));
+}
+
 extern "C" {
 
 int fl_b200_moe_routing(fl_b200_moe *m, uint32_t n_tok, uint32_t *ids_host, float *gates_host) {

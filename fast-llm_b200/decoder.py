@@ -78,6 +78,11 @@ class Decoder:
         capi._ck(self.lib.fl_b200_decoder_set_layer_norms(self._h, C.c_uint32(layer), capi._p(attn_norm),
                                                           capi._p(ffn_norm)))
 
+    def set_layer_moe(self, layer, block):
+        """A fast_llm_b200.moe.MoeBlock in place of the layer's gate / up / down (a Mixtral-shape layer)."""
+        self._keep.append(block)
+        capi._ck(self.lib.fl_b200_decoder_set_layer_moe(self._h, C.c_uint32(layer), block._h))
+
     def set_global(self, which, fmt, w):
         self._keep.append(w)
         capi._ck(self.lib.fl_b200_decoder_set_global(self._h, which, fmt, capi._p(w)))

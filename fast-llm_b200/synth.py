@@ -173,12 +173,13 @@ def device_quant_tensor(fmt, rows, cols, gen):
     return w.reshape(rows, -1)
 
 
-def device_llama(dec, cfg, seed, n_prefill, kv_std=0.1, recipe=Q4_K_M):
+def device_llama(dec, cfg, seed, n_prefill, kv_std=0.1, recipe=Q4_K_M, skip_ffn=()):
     """Fills a fast_llm_b200.decoder.Decoder with a synthetic model generated on
     its device and prefills n_prefill KV positions ~ N(0, kv_std). A
     tensor-parallel decoder gets tensors of its share's shapes (drawn directly,
-    not sliced from a whole model: the values are synthetic either way). Returns
-    the list of tensors kept alive."""
+    not sliced from a whole model: the values are synthetic either way). Layers in
+    skip_ffn get no gate / up / down (the caller sets a mixture-of-experts block there).
+    Returns the list of tensors kept alive."""
     import ctypes as C
     import torch
     from . import tp
@@ -191,6 +192,8 @@ def device_llama(dec, cfg, seed, n_prefill, kv_std=0.1, recipe=Q4_K_M):
     shapes = layer_shapes(dec.loc)
     for l in range(cfg["n_layer"]):
         for i, name in enumerate(LAYER_TENSORS):
+            if l in skip_ffn and name in ("gate", "up", "down"):
+                continue
             rows, cols = shapes[name]
             w = device_quant_tensor(recipe[name], rows, cols, gen)
             if name in tp.COL_SPLIT and w.shape[1] % 16:

@@ -324,6 +324,12 @@ int fl_b200_decoder_set_layer_tensor(fl_b200_decoder *dec, uint32_t layer, int w
                                      const void *w_dev);
 int fl_b200_decoder_set_layer_norms(fl_b200_decoder *dec, uint32_t layer, const float *attn_norm_dev,
                                     const float *ffn_norm_dev);
+/* A mixture-of-experts feed-forward block in place of the layer's dense one (a Mixtral-shape layer: the chain the
+ * reference's graph builder emits per MoE layer, src/model/decoder.cpp:925-1045): the layer then needs no gate / up /
+ * down tensor. The block (fl_b200_moe_create on the same context, one GPU, n_embd of the model, its weights set) stays
+ * the caller's; per token it runs router -> top-k -> the selected experts through the expert-indexed matvec -> merge,
+ * inside the decoder's captured step. Before fl_b200_decoder_finalize. */
+int fl_b200_decoder_set_layer_moe(fl_b200_decoder *dec, uint32_t layer, fl_b200_moe *moe);
 int fl_b200_decoder_set_global(fl_b200_decoder *dec, int which, int fmt, const void *w_dev);
 int fl_b200_decoder_set_out_norm(fl_b200_decoder *dec, const float *w_dev);
 /* The decoder owns the KV cache: per layer K and V, each

@@ -44,8 +44,22 @@ enum { G_TOK_EMBD = 0, G_OUTPUT = 1 };
 
 typedef struct { int fmt; const uint8_t *w; } tensor_t;
 
+/* A mixture-of-experts feed-forward block in place of a layer's dense one (the chain the reference's graph builder
+ * emits per MoE layer, src/model/decoder.cpp:925-1045: router matvec -> ROUTER_SEL -> per selected expert gate, up,
+ * SILU_MUL, down through STREAM_DOT_IDX -> WMERGE with the residual). Experts are stacked row-wise in each tensor. */
+typedef struct {
+    uint32_t n_expert, top_k, norm, n_ff;
+    float scale;
+    const float *router;      /* [n_expert][n_embd] f32 */
+    int fmt_gu, fmt_d;
+    const uint8_t *wg, *wu, *wd;
+} moe_t;
+
 typedef struct flo_llama {
     flo_llama_cfg c;
+    moe_t *moe;               /* n_layer; n_expert == 0: dense layer */
+    float *mo_logits, *mo_gates, *mo_parts, *mo_g, *mo_u, *mo_h;
+    uint32_t *mo_ids;
     tensor_t *lw;             /* n_layer * T_PER_LAYER */
     const float **attn_norm;  /* n_layer */
     const float **ffn_norm;   /* n_layer */
@@ -83,7 +97,21 @@ flo_llama *flo_llama_create(const flo_llama_cfg *cfg) {
     m->u = falloc(c->n_ff);    m->h = falloc(c->n_ff);
     m->dn = falloc(c->n_embd); m->logits = falloc(c->n_vocab);
     m->scratch = falloc((size_t)c->n_head * c->max_kv);
+    m->moe = (moe_t *)calloc(c->n_layer, sizeof(moe_t));
     return m;
+}
+
+void flo_llama_set_layer_moe(flo_llama *m, uint32_t layer, uint32_t n_expert, uint32_t top_k, uint32_t norm, float scale,
+                             uint32_t n_ff, const float *router, int fmt_gu, const uint8_t *wg, const uint8_t *wu,
+                             int fmt_d, const uint8_t *wd) {
+    moe_t *e = &m->moe[layer];
+    e->n_expert = n_expert; e->top_k = top_k; e->norm = norm; e->scale = scale; e->n_ff = n_ff;
+    e->router = router; e->fmt_gu = fmt_gu; e->fmt_d = fmt_d; e->wg = wg; e->wu = wu; e->wd = wd;
+    if (!m->mo_logits) {   /* scratch for the widest block the tests build */
+        m->mo_logits = falloc(1024); m->mo_gates = falloc(64); m->mo_ids = (uint32_t *)calloc(64, sizeof(uint32_t));
+        m->mo_parts = falloc((size_t)64 * m->c.n_embd);
+        m->mo_g = falloc(65536); m->mo_u = falloc(65536); m->mo_h = falloc(65536);
+    }
 }
 
 void flo_llama_destroy(flo_llama *m) {
@@ -93,6 +121,7 @@ void flo_llama_destroy(flo_llama *m) {
     free(m->x); free(m->xn); free(m->q); free(m->kvb); free(m->k); free(m->v);
     free(m->att); free(m->o); free(m->x1); free(m->g); free(m->u); free(m->h);
     free(m->dn); free(m->logits); free(m->scratch);
+    free(m->moe); free(m->mo_logits); free(m->mo_gates); free(m->mo_ids); free(m->mo_parts); free(m->mo_g); free(m->mo_u); free(m->mo_h);
     free(m);
 }
 
@@ -232,6 +261,23 @@ int32_t flo_llama_step(flo_llama *m, const flo_ops_t *ops, int32_t token) {
         matvec(ops, w[T_WO], E, H * D, m->att, m->o);
         ops->add2(m->x, m->o, m->x1, E);
         ops->rmsnorm(m->ffn_norm[l], m->x1, m->xn, c->eps, E);
+        if (m->moe[l].n_expert) {
+            const moe_t *e = &m->moe[l];
+            const tensor_t rt = {0 /* F32 */, (const uint8_t *)e->router};
+            matvec(ops, rt, e->n_expert, E, m->xn, m->mo_logits);
+            ops->router_sel(m->mo_logits, m->mo_ids, m->mo_gates, e->n_expert, e->top_k, e->norm, e->scale);
+            const uint64_t sg = (uint64_t)e->n_ff * flo_row_bytes(e->fmt_gu, E), sd = (uint64_t)E * flo_row_bytes(e->fmt_d, e->n_ff);
+            for (uint32_t k = 0; k < e->top_k; ++k) {
+                const uint32_t id = m->mo_ids[k];
+                const tensor_t tg = {e->fmt_gu, e->wg + id * sg}, tu = {e->fmt_gu, e->wu + id * sg}, td = {e->fmt_d, e->wd + id * sd};
+                matvec(ops, tg, e->n_ff, E, m->xn, m->mo_g);
+                matvec(ops, tu, e->n_ff, E, m->xn, m->mo_u);
+                ops->silu_mul(m->mo_g, m->mo_u, m->mo_h, e->n_ff);
+                matvec(ops, td, E, e->n_ff, m->mo_h, m->mo_parts + (size_t)k * E);
+            }
+            ops->wmerge(m->mo_parts, m->mo_gates, m->x1, 0, m->x, 1.0f, e->top_k, E);
+            continue;
+        }
         matvec(ops, w[T_GATE], c->n_ff, E, m->xn, m->g);
         matvec(ops, w[T_UP], c->n_ff, E, m->xn, m->u);
         ops->silu_mul(m->g, m->u, m->h, c->n_ff);
@@ -252,6 +298,9 @@ int32_t flo_llama_step(flo_llama *m, const flo_ops_t *ops, int32_t token) {
     m->margin = bv - sv;
     return (int32_t)best;
 }
+
+/* The expert ids the last mixture-of-experts layer of the last step selected (top_k of them). */
+const uint32_t *flo_llama_moe_ids(const flo_llama *m) { return m->mo_ids; }
 
 /* Taps for layer-level parity checks: the hidden state after the last layer and
  * the final normed vector of the last step. */

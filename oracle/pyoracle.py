@@ -139,6 +139,7 @@ class Oracle:
         p.flo_llama_normed.restype = C.POINTER(C.c_float)
         p.flo_llama_margin.restype = C.c_float
         p.flo_llama_tap.restype = C.POINTER(C.c_float)
+        p.flo_llama_moe_ids.restype = C.POINTER(C.c_uint32)
 
     @staticmethod
     def available(kind):
@@ -286,6 +287,14 @@ class LlamaOracle:
         if layer == 0:
             self._attn_norm0 = an   # the live array the C side reads (one_ulp_move)
         self.p.flo_llama_set_layer_norms(self.h, C.c_uint32(layer), _ptr(an), _ptr(fn))
+
+    def set_layer_moe(self, layer, n_expert, top_k, norm, scale, n_ff, router, fmt_gu, wg, wu, fmt_d, wd):
+        """A mixture-of-experts feed-forward block in place of the layer's dense one (experts stacked row-wise)."""
+        router = _f32(router)
+        wg, wu, wd = (np.ascontiguousarray(a, dtype=np.uint8) for a in (wg, wu, wd))
+        self._keep += [router, wg, wu, wd]
+        self.p.flo_llama_set_layer_moe(self.h, C.c_uint32(layer), C.c_uint32(n_expert), C.c_uint32(top_k), C.c_uint32(norm),
+                                       C.c_float(scale), C.c_uint32(n_ff), _ptr(router), fmt_gu, _ptr(wg), _ptr(wu), fmt_d, _ptr(wd))
 
     def set_global(self, which, fmt, w):
         w = np.ascontiguousarray(w, dtype=np.uint8)

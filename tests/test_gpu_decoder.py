@@ -15,8 +15,9 @@ SMALL = dict(n_layer=2, n_embd=2048, n_head=16, n_kv_head=4, head_dim=128, n_ff=
              rope_base=500000.0, eps=1e-5)
 
 
-def build_pair(ctx, checker, cfg, seed, n_prefill, kv_std=0.1):
-    """The same synthetic model on the GPU decoder and on the CPU oracle."""
+def build_pair(ctx, checker, cfg, seed, n_prefill, kv_std=0.1, finalize=True):
+    """The same synthetic model on the GPU decoder and on the CPU oracle (finalize=False: the caller still changes
+    layers, then finalizes and sets the positions itself)."""
     from oracle import pyoracle
     dec = Decoder(ctx, cfg)
     orc = pyoracle.LlamaOracle(checker, cfg)
@@ -45,6 +46,8 @@ def build_pair(ctx, checker, cfg, seed, n_prefill, kv_std=0.1):
     dec.set_out_norm(torch.from_numpy(on).cuda())
     orc.set_out_norm(on)
     torch.cuda.synchronize()
+    if not finalize:
+        return dec, orc
     dec.finalize()
     dec.rewind_to(n_prefill)
     orc.set_n_past(n_prefill)

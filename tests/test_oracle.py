@@ -231,3 +231,43 @@ def test_port_matches_golden(port):
     assert np.array_equal(bits(port.rmsnorm(g["norm_w"], g["norm_x"], 1e-5)), bits(g["norm_y"]))
     assert np.array_equal(bits(port.silu_mul(g["norm_x"], g["norm_w"])), bits(g["silu_y"]))
     assert np.array_equal(bits(port.rope(g["rope_x"], 4097, 8, 128, 0, 128, 500000.0)), bits(g["rope_y"]))
+
+
+def test_llama_oracle_moe_layer_equals_operator_chain(checker):
+    """The step driver's mixture-of-experts layer (llama_oracle.c) against the same chain written out with the single
+    operators: router matvec -> ROUTER_SEL -> per selected expert gate, up, SILU_MUL, down -> WMERGE with the residual
+    (src/model/decoder.cpp:925-1045). One layer, so the hidden state after the step is the layer's output."""
+    from oracle import pyoracle
+    cfg = dict(n_layer=1, n_embd=512, n_head=4, n_kv_head=1, head_dim=128, n_ff=768, n_vocab=64, max_kv=8,
+               rope_base=10000.0, eps=1e-5)
+    NE, K, F, E = 4, 2, 256, 512
+    rng = np.random.default_rng(41)
+    orc = pyoracle.LlamaOracle(checker, cfg)
+    shapes = synth.layer_shapes(cfg)
+    tensors = {}
+    for i, name in enumerate(synth.LAYER_TENSORS):
+        tensors[name] = synth.quant_tensor(capi.Q4_K, rng, *shapes[name])
+        orc.set_layer_tensor(0, i, capi.Q4_K, tensors[name])
+    an, fn = rng.uniform(0.9, 1.1, E).astype(np.float32), rng.uniform(0.9, 1.1, E).astype(np.float32)
+    orc.set_layer_norms(0, an, fn)
+    emb = synth.quant_tensor(capi.Q6_K, rng, cfg["n_vocab"], E)
+    orc.set_global(pyoracle.G_TOK_EMBD, capi.Q6_K, emb); orc.set_global(pyoracle.G_OUTPUT, capi.Q6_K, emb)
+    orc.set_out_norm(np.ones(E, dtype=np.float32))
+    wr = rng.standard_normal((NE, E)).astype(np.float32)
+    wg = synth.q4k_tensor(rng, NE * F, E); wu = synth.q4k_tensor(rng, NE * F, E); wd = synth.q6k_tensor(rng, NE * E, F)
+    orc.set_layer_moe(0, NE, K, 1, 1.0, F, wr, capi.Q4_K, wg, wu, capi.Q6_K, wd)
+    orc.set_n_past(0)
+    orc.step(5)
+    x1 = orc.tap(5)                                   # residual after attention: the block's input and add1
+    xn = checker.rmsnorm(fn, x1, cfg["eps"])
+    logits = checker.matvec(capi.F32, wr.view(np.uint8).reshape(NE, -1), NE, E, xn)
+    ids, gates = checker.router_sel(logits, K, 1, 1.0)
+    assert list(ids) == [int(i) for i in np.ctypeslib.as_array(orc.p.flo_llama_moe_ids(orc.h), shape=(K,))]
+    parts = np.zeros((K, E), dtype=np.float32)
+    for k, e in enumerate(ids):
+        g = checker.matvec(capi.Q4_K, wg[e * F:(e + 1) * F], F, E, xn)
+        u = checker.matvec(capi.Q4_K, wu[e * F:(e + 1) * F], F, E, xn)
+        parts[k] = checker.matvec(capi.Q6_K, wd[e * E:(e + 1) * E], E, F, checker.silu_mul(g, u))
+    want = checker.wmerge(parts, np.asarray(gates, dtype=np.float32), x1, None, 1.0)
+    assert np.array_equal(orc.hidden().view(np.uint32), want.view(np.uint32))
+    orc.close()
