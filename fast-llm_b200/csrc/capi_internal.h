@@ -53,7 +53,10 @@ void decoder_adopt(fl_b200_decoder *d, void *dev);
 // n_tok <= the block's max_tokens rows of x, enqueued on the block's context's stream (one token: one expert walk per
 // selected expert through the expert-indexed matvec; more: every expert once through the multi-column matmul).
 // *n_launch: launches enqueued.
-int moe_enqueue_tokens(fl_b200_moe *m, const float *x, uint32_t n_tok, float *y, uint32_t *n_launch);
+// wnorm / eps / resid (one token): x is the raw hidden state, RMSNorm(x) * wnorm is taken inside the block's first
+// kernels, and y = resid + the block's output.
+int moe_enqueue_tokens(fl_b200_moe *m, const float *x, uint32_t n_tok, float *y, uint32_t *n_launch, const float *wnorm = nullptr,
+                       float eps = 0.f, const float *resid = nullptr);
 fl_b200_ctx *moe_ctx(const fl_b200_moe *m);
 const fl_b200_moe_cfg *moe_cfg(const fl_b200_moe *m);
 uint32_t moe_world(const fl_b200_moe *m);

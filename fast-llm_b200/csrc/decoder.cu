@@ -258,15 +258,13 @@ static int enqueue_step(fl_b200_decoder *d, cudaStream_t s, uint32_t *n_launch, 
         if (d->moe[l]) {
             // Mixture-of-experts layer: xb = xa + Wo att as usual, then xa = xb + MoE(RMSNorm(xb)). The block's own launches
             // (router, selection, the selected experts through the expert-indexed matvec, merge) are part of the captured
-            // step; the normed vector borrows the head's buffer, the block's output the query buffer (free after attention).
+            // step; the norm is taken inside the router kernel and the gate | up launches, the residual inside the merge.
             MatvecArgs ao = mk_o(l);
             if (mask & K_MATVEC) { if (int rc = do_matvec(ao)) return rc; ++n; }
             if (mask & K_MATVEC) {
-                CK(launch_rmsnorm(d->xb, d->ffn_norm[l], d->xn_final, c.eps, E, s));
                 uint32_t nl = 0;
-                if (int rc = moe_enqueue_tokens(d->moe[l], d->xn_final, 1, d->q, &nl)) return rc;
-                CK(launch_add2(d->xb, d->q, d->xa, E, s));
-                n += 2 + nl;
+                if (int rc = moe_enqueue_tokens(d->moe[l], d->xb, 1, d->xa, &nl, d->ffn_norm[l], c.eps, d->xb)) return rc;
+                n += nl;
             }
             continue;
         }

@@ -46,15 +46,36 @@ struct fl_b200_moe {
 namespace {
 
 // Router logits of all tokens in one launch: logits[t][e] = dot(router[e], x[t]); one block per (expert, token).
+// wnorm != nullptr: x is the raw hidden state and the logits are those of RMSNorm(x) * wnorm (fl_op_rmsnorm,
+// src/runtime/decode_params.h:101-106, fused: every block norms the token itself).
 __global__ void __launch_bounds__(128) router_logits_kernel(const float *__restrict__ router, const float *__restrict__ x,
-                                                            float *__restrict__ logits, uint32_t n_embd, uint32_t n_expert) {
+                                                            float *__restrict__ logits, uint32_t n_embd, uint32_t n_expert,
+                                                            const float *__restrict__ wnorm = nullptr, float eps = 0.f) {
     __shared__ float red[4];
     const uint32_t e = blockIdx.x, t = blockIdx.y;
     const float4 *w = reinterpret_cast<const float4 *>(router + (size_t)e * n_embd);
     const float4 *v = reinterpret_cast<const float4 *>(x + (size_t)t * n_embd);
+    float inv_rms = 1.f;
+    if (wnorm) {
+        float ss = 0.f;
+        for (uint32_t i = threadIdx.x; i < n_embd / 4; i += 128) {
+            const float4 b = v[i];
+            ss += (b.x * b.x + b.y * b.y) + (b.z * b.z + b.w * b.w);
+        }
+        ss = warp_sum(ss);
+        if ((threadIdx.x & 31u) == 0) red[threadIdx.x >> 5] = ss;
+        __syncthreads();
+        inv_rms = 1.0f / sqrtf(((red[0] + red[1]) + (red[2] + red[3])) / (float)n_embd + eps);
+        __syncthreads();
+    }
     float acc = 0.f;
     for (uint32_t i = threadIdx.x; i < n_embd / 4; i += 128) {
-        const float4 a = w[i], b = v[i];
+        const float4 a = w[i];
+        float4 b = v[i];
+        if (wnorm) {
+            const float4 g = reinterpret_cast<const float4 *>(wnorm)[i];
+            b.x = b.x * inv_rms * g.x; b.y = b.y * inv_rms * g.y; b.z = b.z * inv_rms * g.z; b.w = b.w * inv_rms * g.w;
+        }
         acc = fmaf(a.x, b.x, acc); acc = fmaf(a.y, b.y, acc); acc = fmaf(a.z, b.z, acc); acc = fmaf(a.w, b.w, acc);
     }
     acc = warp_sum(acc);
@@ -198,13 +219,16 @@ int fl_b200_moe_forward(fl_b200_moe *m, const float *x, uint32_t n_tok, float *y
 
 // One gate | up launch and one down launch per (token, slot) through the expert-indexed one-column matvec: the form
 // for shapes the multi-column matmul does not take (rows that are not 16-byte pitched, e.g. Q6_K with 1024 columns).
-static int moe_enqueue_per_slot(fl_b200_moe *m, const float *x, uint32_t n_tok, float *y) {
+// wnorm / resid (one token, inside a decoder step): x is the raw hidden state, normed on the fly by the router kernel
+// and by the gate | up launch's prologue, and y = resid + the block's output (the merge's add1 term).
+static int moe_enqueue_per_slot(fl_b200_moe *m, const float *x, uint32_t n_tok, float *y, const float *wnorm = nullptr,
+                                float eps = 0.f, const float *resid = nullptr) {
     fl_b200_ctx *ctx = m->ctx;
     cudaStream_t s = ctx->stream;
     const fl_b200_moe_cfg &c = m->c;
     const uint32_t E = c.n_embd, F = c.n_ff, K = c.top_k, NE = c.n_expert;
     const uint64_t stride_gu = (uint64_t)F * row_bytes(c.fmt_gate_up, E), stride_d = (uint64_t)E * row_bytes(c.fmt_down, F);
-    router_logits_kernel<<<dim3(NE, n_tok), 128, 0, s>>>(m->router, x, m->logits, E, NE);
+    router_logits_kernel<<<dim3(NE, n_tok), 128, 0, s>>>(m->router, x, m->logits, E, NE, wnorm, eps);
     CKM(cudaGetLastError());
     CKM(launch_router_sel(m->logits, m->ids, m->gates, n_tok, NE, K, c.norm, c.scale, s, m->lids, m->mgates, m->base, m->n_local));
     const uint32_t rows_gu = (uint32_t)(stride_gu / row_bytes(c.fmt_gate_up, E)), rows_d = (uint32_t)(stride_d / row_bytes(c.fmt_down, F));
@@ -221,6 +245,7 @@ static int moe_enqueue_per_slot(fl_b200_moe *m, const float *x, uint32_t n_tok, 
                 a.t[0] = {m->wg, m->g, nullptr, F, c.fmt_gate_up, 0, lid, rows_gu};
                 a.t[1] = {m->wu, m->u, nullptr, F, c.fmt_gate_up, 0, lid, rows_gu};
                 a.x = xt; a.cols = E; a.x_mode = MV_X_PLAIN; a.status = ctx->status;
+                if (wnorm) { a.x_mode = MV_X_RMSNORM; a.wnorm = wnorm; a.eps = eps; }
                 // Programmatic dependent launch from the second matvec launch on: the first one is an ordinary
                 // dependent of the kernel that wrote the expert ids, and every later launch starts after it did,
                 // so the ids (read at kernel entry, before the dependency wait) are in place for all of them.
@@ -245,7 +270,7 @@ static int moe_enqueue_per_slot(fl_b200_moe *m, const float *x, uint32_t n_tok, 
             }
         }
         float *dst = (m->world > 1 ? m->partial : y) + (size_t)t * E;
-        CKM(launch_wmerge(m->part + (size_t)t * K * E, m->mgates + (size_t)t * K, nullptr, nullptr, dst, 1.0f, K, E, K, s));
+        CKM(launch_wmerge(m->part + (size_t)t * K * E, m->mgates + (size_t)t * K, m->world > 1 ? nullptr : resid, nullptr, dst, 1.0f, K, E, K, s));
     }
     if (m->world > 1) {
         for (uint32_t t = 0; t < n_tok; ++t) {   // the combine: sum of the ranks' partial outputs, rank order
@@ -316,15 +341,18 @@ static int moe_enqueue(fl_b200_moe *m, const float *x, uint32_t n_tok, float *y)
     return FL_B200_OK;
 }
 
-int flb::moe_enqueue_tokens(fl_b200_moe *m, const float *x, uint32_t n_tok, float *y, uint32_t *n_launch) {
+int flb::moe_enqueue_tokens(fl_b200_moe *m, const float *x, uint32_t n_tok, float *y, uint32_t *n_launch, const float *wnorm,
+                            float eps, const float *resid) {
     if (!m || !m->router || !m->wg) return set_err(FL_B200_ERR_STATE, "moe: weights not set");
     if (n_tok == 0 || n_tok > m->c.max_tokens) return set_err(FL_B200_ERR_ARG, "moe: %u tokens outside 1..%u", n_tok, m->c.max_tokens);
     const fl_b200_moe_cfg &c = m->c;
     if (n_tok == 1) {
         const bool down_streams = matvec_is_streaming(c.fmt_down, c.n_ff) && row_bytes(c.fmt_down, c.n_ff) % 16 == 0;
         if (n_launch) *n_launch = 2 + c.top_k * (down_streams ? 2u : 3u) + 1 + (m->world > 1 ? 1u : 0u);
-        return moe_enqueue_per_slot(m, x, 1, y);
+        if (m->world > 1 && (wnorm || resid)) return set_err(FL_B200_ERR_ARG, "moe: the fused norm / residual form is for one GPU");
+        return moe_enqueue_per_slot(m, x, 1, y, wnorm, eps, resid);
     }
+    if (wnorm || resid) return set_err(FL_B200_ERR_ARG, "moe: the fused norm / residual form takes one token");
     if (n_launch) *n_launch = 0;   // not counted: the batch pass does not report launches
     return moe_enqueue(m, x, n_tok, y);
 }
