@@ -539,7 +539,7 @@ def moe_decode_case(steps, warmup, peak):
     gen = torch.Generator(device=dev); gen.manual_seed(5)
     blocks = []
     for l in layers:
-        blk = MoeBlock(ctx, E, F, NE, K, max_tokens=8)
+        blk = MoeBlock(ctx, E, F, NE, K, max_tokens=16)
         blk.set_weights(torch.randn((NE, E), device=dev, generator=gen) * 0.02,
                         synth.device_quant_tensor(capi.Q4_K, NE * F, E, gen), synth.device_quant_tensor(capi.Q4_K, NE * F, E, gen),
                         synth.device_quant_tensor(capi.Q4_K, NE * E, F, gen))
@@ -558,23 +558,25 @@ def moe_decode_case(steps, warmup, peak):
         times.append(ctx.timer_stop())
     ms = sorted(times)[len(times) // 2] / steps
     w_bytes, kv_bytes = dec.bytes_per_step(n_prefill + warmup + steps // 2)
-    # 8 positions in one batch pass (draft verification / a prompt chunk): every expert is walked once for the
+    # 8 and 16 positions in one batch pass (draft verification / a prompt chunk): every expert is walked once for the
     # positions that chose it (multi-column kernel), the attention tensors once
-    m = 8
-    for _ in range(2):
-        dec.rewind_to(n_prefill)
-        dec.step_batch(list(range(1, m + 1)))
-    ctx.sync()
-    ctx.timer_start()
-    for _ in range(5):
-        dec.rewind_to(n_prefill)
-        dec.step_batch(list(range(1, m + 1)))
-    bp_ms = ctx.timer_stop() / 5
+    passes = {}
+    for m in (8, 16):
+        for _ in range(2):
+            dec.rewind_to(n_prefill)
+            dec.step_batch(list(range(1, m + 1)))
+        ctx.sync()
+        ctx.timer_start()
+        for _ in range(5):
+            dec.rewind_to(n_prefill)
+            dec.step_batch(list(range(1, m + 1)))
+        bp_ms = ctx.timer_stop() / 5
+        passes["m%d" % m] = {"m": m, "ms_per_pass": bp_ms, "positions_per_s": m / (bp_ms * 1e-3), "single_steps_ms": m * ms}
     print(json.dumps({"case": "moe-decode", "model": "synthetic Mixtral-8x7B shape, Q4_K experts, top-2 of 8, 4096-token prefilled f16 KV",
                       "tokens_per_s": 1e3 / ms, "ms_per_token": ms, "steps": steps, "repeats": len(times),
                       "launches_per_step": dec.launches_per_step(), "bytes_per_token": w_bytes + kv_bytes,
                       "achieved_gbs": (w_bytes + kv_bytes) / ms / 1e6, "frac_of_measured_hbm": (w_bytes + kv_bytes) / ms / 1e6 / peak,
-                      "experts_read_per_token": 32 * K, "batch_pass": {"m": m, "ms_per_pass": bp_ms, "positions_per_s": m / (bp_ms * 1e-3), "single_steps_ms": m * ms},
+                      "experts_read_per_token": 32 * K, "batch_pass": passes,
                       "device_weight_gb": round((32 * NE * 3 * F * capi.row_bytes(capi.Q4_K, E)) / 1e9, 1),
                       "last_token": int(toks[-1]), "status": ctx.status()}))
     dec.close()

@@ -683,10 +683,10 @@ static int batch_alloc(fl_b200_decoder *d) {
         CK(cudaMalloc(&d->b.partial, M * E * 4));
         CK(cudaMalloc(&d->b.top3, M * 16));
     }
-    CK(cudaMalloc(&d->b.io, 24 * sizeof(int32_t)));
+    CK(cudaMalloc(&d->b.io, 3 * FL_B200_MAX_BATCH * sizeof(int32_t)));
     CK(cudaMalloc(&d->b.tickets, (size_t)d->Hkv * M * sizeof(uint32_t)));
     CK(cudaMemset(d->b.tickets, 0, (size_t)d->Hkv * M * sizeof(uint32_t)));
-    CK(cudaMallocHost(&d->b.h_io, 32 * sizeof(int32_t)));
+    CK(cudaMallocHost(&d->b.h_io, 4 * FL_B200_MAX_BATCH * sizeof(int32_t)));
     d->b.ready = true;
     return FL_B200_OK;
 }
@@ -710,8 +710,8 @@ static int enqueue_batch(fl_b200_decoder *d, uint32_t m, cudaStream_t s) {
         }
         return FL_B200_OK;
     };
-    const int32_t *tok = b.io, *pos = b.io + 8;
-    int32_t *next = b.io + 16;
+    const int32_t *tok = b.io, *pos = b.io + FL_B200_MAX_BATCH;
+    int32_t *next = b.io + 2 * FL_B200_MAX_BATCH;
     for (uint32_t i = 0; i < m; ++i)
         CK(launch_embed(d->tok_embd.fmt, d->tok_embd.w, tok + i, E, b.x + (size_t)i * E, s));
     for (uint32_t l = 0; l < c.n_layer; ++l) {
@@ -806,13 +806,13 @@ int fl_b200_decoder_step_batch(fl_b200_decoder *d, const int32_t *toks, uint32_t
             CK(cudaGraphLaunch(d->exec, s));
             CK(cudaMemcpyAsync(d->b.logits + (size_t)i * d->V, d->logits, (size_t)d->V * 4, cudaMemcpyDeviceToDevice, s));
         }
-        CK(cudaMemcpyAsync(d->b.h_io + 16, d->d_hist, (size_t)m * 4, cudaMemcpyDeviceToHost, s));
-        CK(cudaMemcpyAsync(d->b.h_io + 24, d->d_margin_hist, (size_t)m * 4, cudaMemcpyDeviceToHost, s));
+        CK(cudaMemcpyAsync(d->b.h_io + 2 * FL_B200_MAX_BATCH, d->d_hist, (size_t)m * 4, cudaMemcpyDeviceToHost, s));
+        CK(cudaMemcpyAsync(d->b.h_io + 3 * FL_B200_MAX_BATCH, d->d_margin_hist, (size_t)m * 4, cudaMemcpyDeviceToHost, s));
         CK(cudaMemsetAsync(d->d_use_forced, 0, 4, s));
         CK(cudaStreamSynchronize(s));
         for (uint32_t i = 0; i < m; ++i) {
-            outs[i] = d->b.h_io[16 + i];
-            if (margins) memcpy(&margins[i], &d->b.h_io[24 + i], 4);
+            outs[i] = d->b.h_io[2 * FL_B200_MAX_BATCH + i];
+            if (margins) memcpy(&margins[i], &d->b.h_io[3 * FL_B200_MAX_BATCH + i], 4);
         }
         d->n_past += (int32_t)m;
         d->b.last_m = m;
@@ -829,18 +829,18 @@ int fl_b200_decoder_step_batch(fl_b200_decoder *d, const int32_t *toks, uint32_t
         d->b.graph[m] = g;
         CK(cudaGraphInstantiate(&d->b.exec[m], g, 0));
     }
-    for (uint32_t i = 0; i < 8; ++i) {
+    for (uint32_t i = 0; i < FL_B200_MAX_BATCH; ++i) {
         d->b.h_io[i] = i < m ? toks[i] : 0;
-        d->b.h_io[8 + i] = d->n_past + (int32_t)i;
+        d->b.h_io[FL_B200_MAX_BATCH + i] = d->n_past + (int32_t)i;
     }
-    CK(cudaMemcpyAsync(d->b.io, d->b.h_io, 16 * sizeof(int32_t), cudaMemcpyHostToDevice, s));
+    CK(cudaMemcpyAsync(d->b.io, d->b.h_io, 2 * FL_B200_MAX_BATCH * sizeof(int32_t), cudaMemcpyHostToDevice, s));
     CK(cudaGraphLaunch(d->b.exec[m], s));
-    CK(cudaMemcpyAsync(d->b.h_io + 16, d->b.io + 16, 8 * sizeof(int32_t), cudaMemcpyDeviceToHost, s));
-    CK(cudaMemcpyAsync(d->b.h_io + 24, d->b.margin, 8 * sizeof(float), cudaMemcpyDeviceToHost, s));
+    CK(cudaMemcpyAsync(d->b.h_io + 2 * FL_B200_MAX_BATCH, d->b.io + 2 * FL_B200_MAX_BATCH, FL_B200_MAX_BATCH * sizeof(int32_t), cudaMemcpyDeviceToHost, s));
+    CK(cudaMemcpyAsync(d->b.h_io + 3 * FL_B200_MAX_BATCH, d->b.margin, FL_B200_MAX_BATCH * sizeof(float), cudaMemcpyDeviceToHost, s));
     CK(cudaStreamSynchronize(s));
     for (uint32_t i = 0; i < m; ++i) {
-        outs[i] = d->b.h_io[16 + i];
-        if (margins) memcpy(&margins[i], &d->b.h_io[24 + i], 4);
+        outs[i] = d->b.h_io[2 * FL_B200_MAX_BATCH + i];
+        if (margins) memcpy(&margins[i], &d->b.h_io[3 * FL_B200_MAX_BATCH + i], 4);
     }
     d->n_past += (int32_t)m;
     d->b.last_m = m;

@@ -360,15 +360,15 @@ int fl_b200_decoder_verify(fl_b200_decoder *dec, int32_t first_token, const int3
  * greedy token after position i, margins_host[i] (optional) its top1 - top2
  * margin (Decoder::last_margins, :73); n_past advances by m, and rewind_to
  * (fl_b200_decoder_set_n_past) commits or discards the rows as in the
- * reference. One pass over a tensor serves all m tokens where the multi-column
- * kernel takes its shape (Q4_K, rows a multiple of 16, columns of 4096); other
+ * reference. One pass over a tensor serves up to 8 tokens where the multi-column
+ * kernel takes its shape (Q4_K and Q6_K; 9 to 16 tokens: two passes); other
  * tensors are walked once per token; passes of fewer than 4 tokens run as
  * teacher-forced single steps on the device. Used for draft verification and for
- * prompt ingestion in chunks of 8. On a tensor-parallel decoder all ranks make
+ * prompt ingestion in chunks. On a tensor-parallel decoder all ranks make
  * the same call; the partial O / down outputs and the argmax records are
  * exchanged per token, and fl_b200_decoder_batch_logits returns this rank's
  * slice. */
-#define FL_B200_MAX_BATCH 8
+#define FL_B200_MAX_BATCH 16
 int fl_b200_decoder_step_batch(fl_b200_decoder *dec, const int32_t *toks_host, uint32_t m, int32_t *outs_host,
                                float *margins_host);
 /* Logits of position `index` of the last fl_b200_decoder_step_batch pass. */
