@@ -124,8 +124,9 @@ def cpu_reference_arm(steps, warmup, threads=None):
     kind = "reference" if pyoracle.Oracle.available("reference") else "port"
     orc = pyoracle.Oracle(kind)
     cores = threads or os.cpu_count() or 1
-    # set, not setdefault: torchrun exports OMP_NUM_THREADS=1 to its ranks, which would time this arm on one thread
+    # torchrun exports OMP_NUM_THREADS=1 to its ranks and the OpenMP runtime has read it by now: set the count directly
     os.environ["OMP_NUM_THREADS"] = str(cores)
+    orc.port.flo_set_threads(cores)
     full = dict(synth.LLAMA3_8B)
 
     def build(n_layer):

@@ -31,6 +31,9 @@
 #include <math.h>
 #include <stdlib.h>
 #include <string.h>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
 
 uint64_t flo_row_bytes(int fmt, uint32_t cols);
 
@@ -297,6 +300,16 @@ int32_t flo_llama_step(flo_llama *m, const flo_ops_t *ops, int32_t token) {
     }
     m->margin = bv - sv;
     return (int32_t)best;
+}
+
+/* Threads of the row / head loops from here on (a launcher may have exported OMP_NUM_THREADS=1 before this library
+ * was loaded: torchrun does). */
+void flo_set_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
 }
 
 /* The expert ids the last mixture-of-experts layer of the last step selected (top_k of them). */
