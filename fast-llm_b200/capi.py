@@ -34,7 +34,7 @@ SYMBOLS = [
     "fl_b200_decoder_destroy", "fl_b200_decoder_set_layer_tensor",
     "fl_b200_decoder_set_layer_norms", "fl_b200_decoder_set_layer_moe", "fl_b200_decoder_set_global", "fl_b200_decoder_set_out_norm",
     "fl_b200_decoder_kv", "fl_b200_decoder_finalize", "fl_b200_decoder_set_n_past",
-    "fl_b200_decoder_n_past", "fl_b200_decoder_step", "fl_b200_decoder_run", "fl_b200_decoder_verify", "fl_b200_decoder_step_batch", "fl_b200_decoder_batch_logits", "fl_b200_decoder_logits",
+    "fl_b200_decoder_n_past", "fl_b200_decoder_step", "fl_b200_decoder_run", "fl_b200_decoder_verify", "fl_b200_decoder_step_batch", "fl_b200_decoder_batch_logits", "fl_b200_decoder_seqs_init", "fl_b200_decoder_seqs_kv", "fl_b200_decoder_seqs_set_pos", "fl_b200_decoder_seqs_pos", "fl_b200_decoder_seqs_step", "fl_b200_decoder_logits",
     "fl_b200_decoder_margin", "fl_b200_decoder_tap", "fl_b200_decoder_time_class", "fl_b200_decoder_trace", "fl_b200_decoder_launches_per_step",
     "fl_b200_decoder_bytes_per_step",
     "fl_b200_gguf_open", "fl_b200_gguf_close", "fl_b200_gguf_counts", "fl_b200_gguf_tensor_at", "fl_b200_gguf_find",

@@ -107,7 +107,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_decode_kernel(const __gr
     if (tid == 0) trace_min(a.trace, 0);
     griddep_launch_dependents();
     // *pos was written at the end of the previous step (or is kv_len - 1 of a single call): stable here.
-    const uint32_t kv_len = (a.pos ? (uint32_t)(*a.pos) + 1u : a.kv_len) + b * a.kv_len_step;
+    const uint32_t kv_len = (a.pos ? (uint32_t)a.pos[b * a.pos_stride] + 1u : a.kv_len) + b * a.kv_len_step;
     const uint32_t tiles_total = (kv_len + kTile - 1) / kTile;
     const uint32_t tps = (tiles_total + a.n_splits - 1) / a.n_splits;
     const uint32_t t0 = split * tps;

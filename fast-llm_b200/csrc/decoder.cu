@@ -109,6 +109,15 @@ struct fl_b200_decoder {
         uint32_t last_m = 0;
         bool ready = false;
     } b;
+    // Independent sequences decoded in lock step (fl_b200_decoder_seqs_*): per layer one cache [n_seq][n_kv_head][max_kv][128]
+    // for K and one for V, a position per sequence, and one CUDA graph of the pass (the batch pass's buffers serve it).
+    struct Seqs {
+        uint32_t n = 0;
+        std::vector<__half *> kc, vc;
+        int32_t pos[FL_B200_MAX_BATCH] = {};
+        cudaGraph_t graph = nullptr;
+        cudaGraphExec_t exec = nullptr;
+    } sq;
 };
 
 void flb::decoder_adopt(fl_b200_decoder *d, void *dev) { d->owned.push_back(dev); }
@@ -418,6 +427,10 @@ void fl_b200_decoder_destroy(fl_b200_decoder *d) {
     if (d->graph) cudaGraphDestroy(d->graph);
     for (auto p : d->kc) cudaFree(p);
     for (auto p : d->vc) cudaFree(p);
+    for (auto p : d->sq.kc) cudaFree(p);
+    for (auto p : d->sq.vc) cudaFree(p);
+    if (d->sq.exec) cudaGraphExecDestroy(d->sq.exec);
+    if (d->sq.graph) cudaGraphDestroy(d->sq.graph);
     cudaFree(d->d_token); cudaFree(d->d_hist); cudaFree(d->d_margin_hist); cudaFree(d->d_forced); cudaFree(d->xa); cudaFree(d->xb); cudaFree(d->q);
     cudaFree(d->k); cudaFree(d->v); cudaFree(d->att); cudaFree(d->g); cudaFree(d->u); cudaFree(d->logits);
     cudaFree(d->xn_final); cudaFree(d->part); cudaFree(d->tickets);
@@ -691,7 +704,9 @@ static int batch_alloc(fl_b200_decoder *d) {
     return FL_B200_OK;
 }
 
-static int enqueue_batch(fl_b200_decoder *d, uint32_t m, cudaStream_t s) {
+// seqs: the m tokens belong to m independent sequences (token i -> sequence i at its own position, its own cache)
+// instead of m consecutive positions of the one sequence.
+static int enqueue_batch(fl_b200_decoder *d, uint32_t m, cudaStream_t s, bool seqs = false) {
     const fl_b200_llama_cfg &c = d->c;
     fl_b200_ctx *ctx = d->ctx;
     const uint32_t E = c.n_embd, D = c.head_dim, QD = d->Hq * D, KD = d->Hkv * D, F = d->F, V = d->V;
@@ -725,15 +740,16 @@ static int enqueue_batch(fl_b200_decoder *d, uint32_t m, cudaStream_t s) {
                             w[FL_B200_T_WV].fmt == w[FL_B200_T_WK].fmt)) return rc;
         {   // rotate q and k of every token by its own position, append k and v
             RopeAppendArgs r{};
-            r.q = b.q; r.k = b.k; r.v = b.v; r.kcache = d->kc[l]; r.vcache = d->vc[l]; r.pos = pos;
+            r.q = b.q; r.k = b.k; r.v = b.v; r.kcache = seqs ? d->sq.kc[l] : d->kc[l]; r.vcache = seqs ? d->sq.vc[l] : d->vc[l]; r.pos = pos;
+            r.seq_elems = seqs ? (uint64_t)d->Hkv * c.max_kv * D : 0;
             r.n_q_head = d->Hq; r.n_kv_head = d->Hkv; r.head_dim = D; r.kv_stride = c.max_kv; r.theta_scale = theta_scale;
             r.n_tok = m; r.q_tok_stride = QD; r.kv_tok_stride = KD;
             CK(launch_rope_append(r, s));
         }
         {
             AttnArgs a{};
-            a.q = b.q; a.k = d->kc[l]; a.v = d->vc[l]; a.out = b.att; a.part = b.part; a.tickets = b.tickets;
-            a.pos = pos; a.kv_len = 0; a.kv_len_step = 1; a.shared_kv = 1;
+            a.q = b.q; a.k = seqs ? d->sq.kc[l] : d->kc[l]; a.v = seqs ? d->sq.vc[l] : d->vc[l]; a.out = b.att; a.part = b.part; a.tickets = b.tickets;
+            a.pos = pos; a.kv_len = 0; a.kv_len_step = seqs ? 0 : 1; a.shared_kv = seqs ? 0 : 1; a.pos_stride = seqs ? 1 : 0;
             a.kv_stride = c.max_kv; a.batch_stride = (uint64_t)d->Hkv * c.max_kv * D;
             a.n_q_head = d->Hq; a.n_kv_head = d->Hkv; a.batch = m;
             a.n_splits = attn_pick_splits(d->Hkv, m, c.max_kv, ctx->sms);
@@ -844,6 +860,91 @@ int fl_b200_decoder_step_batch(fl_b200_decoder *d, const int32_t *toks, uint32_t
     }
     d->n_past += (int32_t)m;
     d->b.last_m = m;
+    return check_dev_status(d);
+}
+
+// ---- independent sequences in lock step: one pass feeds one token to each of n sequences (each with its own cache and
+// position); every tensor is walked once per 8 sequences, the attention runs per sequence over its own keys. ----
+int fl_b200_decoder_seqs_init(fl_b200_decoder *d, uint32_t n_seq) {
+    if (!d) return set_err(FL_B200_ERR_ARG, "decoder_seqs_init: null");
+    if (n_seq < 2 || n_seq > FL_B200_MAX_BATCH) return set_err(FL_B200_ERR_ARG, "decoder_seqs_init: %u sequences outside 2..%d", n_seq, FL_B200_MAX_BATCH);
+    if (d->tp_size > 1) return set_err(FL_B200_ERR_ARG, "decoder_seqs_init: one GPU only");
+    if (d->sq.n) return set_err(FL_B200_ERR_STATE, "decoder_seqs_init: already set up for %u sequences", d->sq.n);
+    const fl_b200_llama_cfg &c = d->c;
+    CK(cudaSetDevice(d->ctx->device));
+    const size_t bytes = (size_t)n_seq * d->Hkv * c.max_kv * c.head_dim * sizeof(__half);
+    d->sq.kc.assign(c.n_layer, nullptr);
+    d->sq.vc.assign(c.n_layer, nullptr);
+    for (uint32_t l = 0; l < c.n_layer; ++l) {
+        CK(cudaMalloc(&d->sq.kc[l], bytes));
+        CK(cudaMalloc(&d->sq.vc[l], bytes));
+        CK(cudaMemsetAsync(d->sq.kc[l], 0, bytes, d->ctx->stream));
+        CK(cudaMemsetAsync(d->sq.vc[l], 0, bytes, d->ctx->stream));
+    }
+    CK(cudaStreamSynchronize(d->ctx->stream));
+    d->sq.n = n_seq;
+    return FL_B200_OK;
+}
+
+int fl_b200_decoder_seqs_kv(fl_b200_decoder *d, uint32_t layer, uint32_t seq, uint16_t **k_out, uint16_t **v_out) {
+    if (!d || !k_out || !v_out) return set_err(FL_B200_ERR_ARG, "decoder_seqs_kv: null");
+    if (layer >= d->c.n_layer || seq >= d->sq.n) return set_err(FL_B200_ERR_ARG, "decoder_seqs_kv: layer %u / sequence %u out of range", layer, seq);
+    const size_t per_seq = (size_t)d->Hkv * d->c.max_kv * d->c.head_dim;
+    *k_out = reinterpret_cast<uint16_t *>(d->sq.kc[layer] + seq * per_seq);
+    *v_out = reinterpret_cast<uint16_t *>(d->sq.vc[layer] + seq * per_seq);
+    return FL_B200_OK;
+}
+
+int fl_b200_decoder_seqs_set_pos(fl_b200_decoder *d, uint32_t seq, int32_t n_past) {
+    if (!d || seq >= d->sq.n || n_past < 0 || (uint32_t)n_past > d->c.max_kv) return set_err(FL_B200_ERR_ARG, "decoder_seqs_set_pos: out of range");
+    d->sq.pos[seq] = n_past;
+    return FL_B200_OK;
+}
+
+int fl_b200_decoder_seqs_pos(fl_b200_decoder *d, uint32_t seq, int32_t *n_past_out) {
+    if (!d || !n_past_out || seq >= d->sq.n) return set_err(FL_B200_ERR_ARG, "decoder_seqs_pos: out of range");
+    *n_past_out = d->sq.pos[seq];
+    return FL_B200_OK;
+}
+
+int fl_b200_decoder_seqs_step(fl_b200_decoder *d, const int32_t *toks, int32_t *outs, float *margins) {
+    if (!d || !toks || !outs) return set_err(FL_B200_ERR_ARG, "decoder_seqs_step: null");
+    if (!d->finalized) return set_err(FL_B200_ERR_STATE, "decoder_seqs_step: finalize first");
+    const uint32_t m = d->sq.n;
+    if (m == 0) return set_err(FL_B200_ERR_STATE, "decoder_seqs_step: fl_b200_decoder_seqs_init first");
+    for (uint32_t i = 0; i < m; ++i) {
+        if (toks[i] < 0 || (uint32_t)toks[i] >= d->c.n_vocab) return set_err(FL_B200_ERR_ARG, "decoder_seqs_step: token %d outside the vocabulary", toks[i]);
+        if ((uint32_t)d->sq.pos[i] >= d->c.max_kv) return set_err(FL_B200_ERR_STATE, "decoder_seqs_step: kv of sequence %u full", i);
+    }
+    cudaStream_t s = d->ctx->stream;
+    CK(cudaSetDevice(d->ctx->device));
+    if (int rc = batch_alloc(d)) return rc;
+    if (!d->sq.exec) {
+        CK(cudaStreamSynchronize(s));
+        CK(cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal));
+        const int rc = enqueue_batch(d, m, s, true);
+        cudaGraph_t g = nullptr;
+        const cudaError_t e = cudaStreamEndCapture(s, &g);
+        if (rc) { if (g) cudaGraphDestroy(g); return rc; }
+        CK(e);
+        d->sq.graph = g;
+        CK(cudaGraphInstantiate(&d->sq.exec, g, 0));
+    }
+    for (uint32_t i = 0; i < FL_B200_MAX_BATCH; ++i) {
+        d->b.h_io[i] = i < m ? toks[i] : 0;
+        d->b.h_io[FL_B200_MAX_BATCH + i] = i < m ? d->sq.pos[i] : 0;
+    }
+    CK(cudaMemcpyAsync(d->b.io, d->b.h_io, 2 * FL_B200_MAX_BATCH * sizeof(int32_t), cudaMemcpyHostToDevice, s));
+    CK(cudaGraphLaunch(d->sq.exec, s));
+    CK(cudaMemcpyAsync(d->b.h_io + 2 * FL_B200_MAX_BATCH, d->b.io + 2 * FL_B200_MAX_BATCH, FL_B200_MAX_BATCH * sizeof(int32_t), cudaMemcpyDeviceToHost, s));
+    CK(cudaMemcpyAsync(d->b.h_io + 3 * FL_B200_MAX_BATCH, d->b.margin, FL_B200_MAX_BATCH * sizeof(float), cudaMemcpyDeviceToHost, s));
+    CK(cudaStreamSynchronize(s));
+    for (uint32_t i = 0; i < m; ++i) {
+        outs[i] = d->b.h_io[2 * FL_B200_MAX_BATCH + i];
+        if (margins) memcpy(&margins[i], &d->b.h_io[3 * FL_B200_MAX_BATCH + i], 4);
+        d->sq.pos[i] += 1;
+    }
+    d->b.last_m = m;   // fl_b200_decoder_batch_logits(i): the logits of sequence i
     return check_dev_status(d);
 }
 

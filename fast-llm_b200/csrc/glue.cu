@@ -205,7 +205,7 @@ __global__ void __launch_bounds__(128) rope_append_kernel(const RopeAppendArgs a
             const uint32_t hk = h - nq;
             const float *v = a.k + (size_t)tokn * a.kv_tok_stride + (size_t)hk * a.head_dim + 2 * i;
             const float x0 = v[0], x1 = v[1];
-            __half *dst = a.kcache + ((size_t)hk * a.kv_stride + pos) * a.head_dim + 2 * i;
+            __half *dst = a.kcache + (size_t)tokn * a.seq_elems + ((size_t)hk * a.kv_stride + pos) * a.head_dim + 2 * i;
             dst[0] = __float2half_rn(__fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s)));
             dst[1] = __float2half_rn(__fadd_rn(__fmul_rn(x0, s), __fmul_rn(x1, c)));
         }
@@ -213,7 +213,7 @@ __global__ void __launch_bounds__(128) rope_append_kernel(const RopeAppendArgs a
         const uint32_t u = t - n_rot_heads * half;
         const uint32_t hk = u / half, i = u % half;
         const float *v = a.v + (size_t)tokn * a.kv_tok_stride + (size_t)hk * a.head_dim + 2 * i;
-        __half *dst = a.vcache + ((size_t)hk * a.kv_stride + pos) * a.head_dim + 2 * i;
+        __half *dst = a.vcache + (size_t)tokn * a.seq_elems + ((size_t)hk * a.kv_stride + pos) * a.head_dim + 2 * i;
         dst[0] = __float2half_rn(v[0]);
         dst[1] = __float2half_rn(v[1]);
     }

@@ -139,6 +139,7 @@ struct AttnArgs {
     uint32_t kv_len;       // used when pos == nullptr
     uint32_t kv_len_step;  // sequence b attends kv_len + b * kv_len_step keys (draft verification: step 1)
     uint32_t shared_kv;    // 1: all sequences read the same cache (batch_stride ignored)
+    uint32_t pos_stride;   // sequence b takes its position from pos[b * pos_stride] (0: all from pos[0]; independent sequences: 1)
     uint32_t kv_stride;    // positions allocated per head
     uint64_t batch_stride; // elements between sequences in k / v
     uint32_t n_q_head, n_kv_head, batch, n_splits;
@@ -261,6 +262,7 @@ struct RopeAppendArgs {
     int pdl;
     // batch pass: n_tok tokens (0 = 1), token i at q + i * q_tok_stride, k / v + i * kv_tok_stride, position pos[i]
     uint32_t n_tok, q_tok_stride, kv_tok_stride;
+    uint64_t seq_elems;    // independent sequences: token i appends to the cache of sequence i, seq_elems halves further (0: one cache)
 };
 cudaError_t launch_rope_append(const RopeAppendArgs &a, cudaStream_t stream);
 // (cos, sin) of pos * theta_scale^i, i < head_dim / 2, with the angle built by repeated multiplication exactly as

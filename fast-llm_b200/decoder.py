@@ -105,6 +105,33 @@ class Decoder:
         capi._ck(self.lib.fl_b200_decoder_step_batch(self._h, toks, C.c_uint32(m), outs, margins))
         return list(outs), list(margins)
 
+    # -- independent sequences in lock step --
+    def seqs_init(self, n_seq):
+        capi._ck(self.lib.fl_b200_decoder_seqs_init(self._h, C.c_uint32(n_seq)))
+        self.n_seq = n_seq
+
+    def seqs_kv_ptrs(self, layer, seq):
+        k, v = C.c_void_p(), C.c_void_p()
+        capi._ck(self.lib.fl_b200_decoder_seqs_kv(self._h, C.c_uint32(layer), C.c_uint32(seq), C.byref(k), C.byref(v)))
+        return k.value, v.value
+
+    def seqs_set_pos(self, seq, n_past):
+        capi._ck(self.lib.fl_b200_decoder_seqs_set_pos(self._h, C.c_uint32(seq), C.c_int32(n_past)))
+
+    def seqs_pos(self, seq):
+        out = C.c_int32()
+        capi._ck(self.lib.fl_b200_decoder_seqs_pos(self._h, C.c_uint32(seq), C.byref(out)))
+        return out.value
+
+    def seqs_step(self, tokens):
+        """One token per sequence; returns (greedy token of every sequence, its top1 - top2 margin)."""
+        m = self.n_seq
+        assert len(tokens) == m
+        toks = (C.c_int32 * m)(*[int(t) for t in tokens])
+        outs, margins = (C.c_int32 * m)(), (C.c_float * m)()
+        capi._ck(self.lib.fl_b200_decoder_seqs_step(self._h, toks, outs, margins))
+        return list(outs), list(margins)
+
     def batch_logits(self, index):
         out = np.empty(self.loc["n_vocab"], dtype=np.float32)
         capi._ck(self.lib.fl_b200_decoder_batch_logits(self._h, C.c_uint32(index), out.ctypes.data_as(C.c_void_p)))

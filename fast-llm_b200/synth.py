@@ -221,3 +221,25 @@ def device_llama(dec, cfg, seed, n_prefill, kv_std=0.1, recipe=Q4_K_M, skip_ffn=
     dec.set_out_norm(on)
     torch.cuda.synchronize(dev)
     return keep
+
+
+def device_seqs(dec, cfg, n_seq, n_prefill, seed=7, kv_std=0.1):
+    """Sets a decoder up for n_seq independent sequences (Decoder.seqs_init) and prefills n_prefill positions of every
+    sequence's cache with f16 ~ N(0, kv_std), generated on the device."""
+    import ctypes as C
+    import torch
+    dev = torch.device("cuda", dec.ctx.device)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(seed)
+    dec.seqs_init(n_seq)
+    nkv = dec.loc["n_kv_head"]
+    for l in range(cfg["n_layer"]):
+        for s in range(n_seq):
+            for ptr in dec.seqs_kv_ptrs(l, s):
+                t = (torch.randn((nkv, n_prefill, cfg["head_dim"]), device=dev, generator=gen) * kv_std).half()
+                full = torch.zeros((nkv, cfg["max_kv"], cfg["head_dim"]), dtype=torch.float16, device=dev)
+                full[:, :n_prefill] = t
+                torch.cuda.synchronize(dev)
+                capi._ck(dec.lib.fl_b200_upload(dec.ctx._h, C.c_void_p(ptr), C.c_void_p(full.data_ptr()), C.c_size_t(full.numel() * 2)))
+    for s in range(n_seq):
+        dec.seqs_set_pos(s, n_prefill)

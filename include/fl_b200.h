@@ -371,6 +371,19 @@ int fl_b200_decoder_verify(fl_b200_decoder *dec, int32_t first_token, const int3
 #define FL_B200_MAX_BATCH 16
 int fl_b200_decoder_step_batch(fl_b200_decoder *dec, const int32_t *toks_host, uint32_t m, int32_t *outs_host,
                                float *margins_host);
+/* Several independent sequences decoded in lock step (nothing in the reference: its decoder holds one sequence): after
+ * fl_b200_decoder_seqs_init(n), 2 <= n <= FL_B200_MAX_BATCH, the decoder owns n more KV caches (per layer
+ * [n][n_kv_head][max_kv][head_dim] f16 for K and for V; fl_b200_decoder_seqs_kv returns sequence seq's part so that a
+ * caller can prefill it) and a position per sequence (fl_b200_decoder_seqs_set_pos = rewind_to of that sequence).
+ * fl_b200_decoder_seqs_step feeds toks_host[i] to sequence i at its own position and returns each sequence's greedy
+ * token (and margin): one pass, every weight tensor walked once per 8 sequences, the attention per sequence over its own
+ * keys; every position advances by one. fl_b200_decoder_batch_logits(i) then returns the logits of sequence i. The
+ * single-sequence calls (step, run, step_batch) keep working on their own cache. One GPU. */
+int fl_b200_decoder_seqs_init(fl_b200_decoder *dec, uint32_t n_seq);
+int fl_b200_decoder_seqs_kv(fl_b200_decoder *dec, uint32_t layer, uint32_t seq, uint16_t **k_dev_out, uint16_t **v_dev_out);
+int fl_b200_decoder_seqs_set_pos(fl_b200_decoder *dec, uint32_t seq, int32_t n_past);
+int fl_b200_decoder_seqs_pos(fl_b200_decoder *dec, uint32_t seq, int32_t *n_past_out);
+int fl_b200_decoder_seqs_step(fl_b200_decoder *dec, const int32_t *toks_host, int32_t *outs_host, float *margins_host);
 /* Logits of position `index` of the last fl_b200_decoder_step_batch pass. */
 int fl_b200_decoder_batch_logits(fl_b200_decoder *dec, uint32_t index, float *logits_host);
 int fl_b200_decoder_logits(fl_b200_decoder *dec, float *logits_host);

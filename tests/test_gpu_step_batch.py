@@ -169,3 +169,64 @@ def test_speculative_generation_equals_greedy(ctx, checker):
         spec.generate(dec, first, 4, seen2)            # no controller and no fixed length
     assert ctx.status() == 0
     dec.close()
+
+
+def _upload_kv(ctx, cfg, ptr, src, n_pos):
+    full = np.zeros((cfg["n_kv_head"], cfg["max_kv"], cfg["head_dim"]), dtype=np.float16)
+    full[:, :n_pos] = src
+    capi._ck(ctx.lib.fl_b200_upload(ctx._h, capi.C.c_void_p(ptr), capi.C.c_void_p(full.ctypes.data), capi.C.c_size_t(full.nbytes)))
+
+
+@pytest.mark.parametrize("cfg,n_seq", [(WIDE, 3), (SMALL, 2), (WIDE, 11)])
+def test_independent_sequences_equal_single_steps_and_oracle(ctx, checker, cfg, n_seq):
+    """n sequences with their own caches, histories of different lengths and their own tokens, one token each per pass:
+    every sequence gets the tokens and logits it gets when it is decoded alone (single steps on the decoder's own
+    cache), and sequence 0 those of the CPU oracle."""
+    dec, orc = build(ctx, checker, cfg, seed=41, n_prefill=0)
+    dec.seqs_init(n_seq)
+    lens = [5 + 7 * s for s in range(n_seq)]
+    kvs = []
+    for s in range(n_seq):
+        per_layer = []
+        for l in range(cfg["n_layer"]):
+            k, v = synth.llama_kv(cfg, 100 + s, l, lens[s])
+            per_layer.append((k, v))
+            for src, dst in zip((k, v), dec.seqs_kv_ptrs(l, s)):
+                _upload_kv(ctx, cfg, dst, src, lens[s])
+        kvs.append(per_layer)
+        dec.seqs_set_pos(s, lens[s])
+    rng = np.random.default_rng(9)
+    n_steps = 4
+    toks = rng.integers(0, cfg["n_vocab"], (n_steps, n_seq))
+    got_tok, got_logits = [], []
+    for st in range(n_steps):
+        outs, margins = dec.seqs_step([int(t) for t in toks[st]])
+        got_tok.append(outs)
+        got_logits.append([dec.batch_logits(s) for s in range(n_seq)])
+    assert [dec.seqs_pos(s) for s in range(n_seq)] == [n + n_steps for n in lens]
+    assert ctx.status() == 0
+    # every sequence alone, on the single-sequence cache, from the same history
+    for s in range(n_seq):
+        for l in range(cfg["n_layer"]):
+            for src, dst in zip(kvs[s][l], dec.kv_ptrs(l)):
+                _upload_kv(ctx, cfg, dst, src, lens[s])
+        dec.rewind_to(lens[s])
+        if s == 0:
+            for l in range(cfg["n_layer"]):
+                orc.seed_kv(l, *kvs[0][l])
+            orc.set_n_past(lens[0])
+        for st in range(n_steps):
+            nxt = dec.step(int(toks[st][s]))
+            single = dec.logits()
+            err = rel_err(got_logits[st][s], single)
+            assert err < TOL, (s, st, err)
+            if nxt != got_tok[st][s]:
+                assert dec.last_margin() <= 2 * np.max(np.abs(got_logits[st][s] - single)), (s, st)
+            if s == 0:
+                want_tok = orc.step(int(toks[st][0]))
+                assert rel_err(got_logits[st][0], orc.logits()) < (TOL if st == 0 else 3 * TOL), (st,)
+                if st == 0 and want_tok != got_tok[0][0]:
+                    assert orc.margin() <= 2 * np.max(np.abs(got_logits[0][0] - orc.logits()))
+    with pytest.raises(capi.Fl200Error):
+        dec.seqs_init(4)                      # already set up
+    dec.close(); orc.close()
