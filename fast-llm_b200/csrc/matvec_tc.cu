@@ -286,17 +286,17 @@ __device__ __forceinline__ void q4k_block(uint32_t r0, uint32_t oh, uint32_t oa,
         mma16816(cH[j & 1], hsub2_u32(and_or(W0, MH, KH), oH), hsub2_u32(and_or(W1, MH, KH), oH),
                  hsub2_u32(and_or(V0, MH, KH), oH), hsub2_u32(and_or(V1, MH, KH), oH), bx[j].z, bx[j].w);
     }
-    // 6-bit scales / mins of sub-blocks 2t, 2t+1 (packing: fl_q4k_scale_min, src/runtime/quants.h:121-129)
+    // 6-bit scales / mins of sub-blocks 2t, 2t+1 (packing: fl_q4k_scale_min, src/runtime/quants.h:121-129). One form
+    // for both kinds of sub-block, the lane's shifts and masks being loop constants: sub-blocks 0..3 are the low six
+    // bits of bytes 0..3 (4..7 for the mins); sub-blocks 4..7 a nibble of bytes 8..11 under the top two bits of those.
     const uint32_t sh = 16u * (t & 1u);
+    const uint32_t shA = t >= 2 ? sh + 2u : sh, mA = t >= 2 ? 0x3030u : 0x3F3Fu, mE = t >= 2 ? 0x0F0Fu : 0u;
     const float s0 = sx.x, s1 = sx.y;
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
         const uint4 hdr = r ? h1 : h0;
-        const uint32_t a = hdr.y >> sh, b = hdr.z >> sh, e = hdr.w >> sh;
-        const uint32_t sc_lo = a & 0x3F3Fu, mn_lo = b & 0x3F3Fu;
-        const uint32_t sc_hi = (e & 0x0F0Fu) | ((a >> 2) & 0x3030u);
-        const uint32_t mn_hi = ((e >> 4) & 0x0F0Fu) | ((b >> 2) & 0x3030u);
-        const uint32_t sc = t >= 2 ? sc_hi : sc_lo, mn = t >= 2 ? mn_hi : mn_lo;
+        const uint32_t sc = ((hdr.y >> shA) & mA) | ((hdr.w >> sh) & mE);
+        const uint32_t mn = ((hdr.z >> shA) & mA) | ((hdr.w >> (sh + 4u)) & mE);
         const float d = h2f_bits((uint16_t)(hdr.x & 0xFFFFu)), dmin = h2f_bits((uint16_t)(hdr.x >> 16));
         const float tl = (cL[0][2 * r] + cL[1][2 * r]) + (cL[0][2 * r + 1] + cL[1][2 * r + 1]);
         const float th = (cH[0][2 * r] + cH[1][2 * r]) + (cH[0][2 * r + 1] + cH[1][2 * r + 1]);
@@ -674,19 +674,20 @@ __global__ void __launch_bounds__((G * kCW + 2) * 32) matvec_tc_kernel(const __g
                 float sum = 0.f;
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    __half hh[4], ll[4];
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const float s = v[4 * j + i] * inv_s;
-                        hh[i] = __float2half_rn(s);
-                        const float r = s - __half2float(hh[i]);
-                        ll[i] = __float2half_rn(r);
-                        sum += __half2float(hh[i]) + __half2float(ll[i]);
-                    }
-                    hi2[2 * j] = (uint32_t)__half_as_ushort(hh[0]) | ((uint32_t)__half_as_ushort(hh[2]) << 16);
-                    hi2[2 * j + 1] = (uint32_t)__half_as_ushort(hh[1]) | ((uint32_t)__half_as_ushort(hh[3]) << 16);
-                    lo2[2 * j] = (uint32_t)__half_as_ushort(ll[0]) | ((uint32_t)__half_as_ushort(ll[2]) << 16);
-                    lo2[2 * j + 1] = (uint32_t)__half_as_ushort(ll[1]) | ((uint32_t)__half_as_ushort(ll[3]) << 16);
+                    // converted two at a time, already as the pairs the operand wants (one conversion instruction per pair)
+                    const float s0 = v[4 * j] * inv_s, s1 = v[4 * j + 1] * inv_s, s2 = v[4 * j + 2] * inv_s, s3 = v[4 * j + 3] * inv_s;
+                    const __half2 h02 = __floats2half2_rn(s0, s2), h13 = __floats2half2_rn(s1, s3);
+                    const float2 f02 = __half22float2(h02), f13 = __half22float2(h13);
+                    const __half2 l02 = __floats2half2_rn(s0 - f02.x, s2 - f02.y), l13 = __floats2half2_rn(s1 - f13.x, s3 - f13.y);
+                    const float2 g02 = __half22float2(l02), g13 = __half22float2(l13);
+                    sum += f02.x + g02.x;   // elements 0, 1, 2, 3 in this order
+                    sum += f13.x + g13.x;
+                    sum += f02.y + g02.y;
+                    sum += f13.y + g13.y;
+                    hi2[2 * j] = *reinterpret_cast<const uint32_t *>(&h02);
+                    hi2[2 * j + 1] = *reinterpret_cast<const uint32_t *>(&h13);
+                    lo2[2 * j] = *reinterpret_cast<const uint32_t *>(&l02);
+                    lo2[2 * j + 1] = *reinterpret_cast<const uint32_t *>(&l13);
                 }
                 const float sum32 = sum + __shfl_xor_sync(0xffffffffu, sum, 1);
                 if (live) {
@@ -779,17 +780,27 @@ __global__ void __launch_bounds__((G * kCW + 2) * 32) matvec_tc_kernel(const __g
             const uint32_t xstride = has_b ? 128u : 0u;
             const uint32_t xb = has_b ? 1024u : 0u;   // lanes that feed zeros stay on the zero slot
             const uint32_t xa4 = has_b ? x4 : zero16, xa6 = has_b ? x6 : zero16;
+            // the tensor of the current unit: its format and the Q4_K offsets change only where a unit enters the next
+            // tensor of the launch (a CTA's units ascend), so they are set there and not once per unit
+            uint32_t ti_end = 0;     // first unit past the current tensor
+            int fmt = 0;
+            uint32_t oh = 0, oa = 0, ob = 0;
             for (uint32_t k = 0; k < my_units; ++k, ++kk) {
                 const uint32_t u = blockIdx.x + k * gridDim.x;
-                const int fmt = ph.swiglu ? ph.t[0].fmt : ph.t[unit_tensor(ph, u)].fmt;
+                if (u >= ti_end) {
+                    const int ti = ph.swiglu ? 0 : unit_tensor(ph, u);
+                    ti_end = (ph.swiglu || ti + 1 >= ph.n_tensors) ? 0xFFFFFFFFu : ph.t[ti + 1].unit0;
+                    fmt = ph.t[ti].fmt;
+                    const bool swz = ph.t[ti].swz != 0;
+                    oh = q4_row_off(w * 144u, g, swz);
+                    oa = q4_row_off(w * 144u + 16u + 32u * t, g, swz);
+                    ob = q4_row_off(w * 144u + 32u + 32u * t, g, swz);
+                }
                 float acc0 = 0.f, acc1 = 0.f;
                 // this group's stages of unit k: those of its stage sequence (grp, grp + G, ... over the whole launch)
                 // that fall into [it_base + k nseg, it_base + (k + 1) nseg)
                 const uint32_t it0 = it_base + k * nseg, it1 = it0 + nseg;
                 if (fmt == FMT_Q4_K) {
-                    const bool swz = ph.t[ph.swiglu ? 0 : unit_tensor(ph, u)].swz != 0;
-                    const uint32_t oh = q4_row_off(w * 144u, g, swz), oa = q4_row_off(w * 144u + 16u + 32u * t, g, swz),
-                                   ob = q4_row_off(w * 144u + 32u + 32u * t, g, swz);
                     for (; c_it < it1; c_it += G) {
                         const uint32_t blk = (c_it - it0) * 8 + w;
                         mbar_wait_or_die(&sm.full[c_slot], c_par, a.status, dead);
