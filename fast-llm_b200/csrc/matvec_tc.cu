@@ -106,6 +106,14 @@ __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
+// D(16x8, s32) += A(16x32, u8, row) * B(32x8, s8, col). Lane (g, t): a0 / a1 = rows g / g + 8, k-slots 4t..4t+3;
+// a2 / a3 = the same rows, k-slots 16+4t..; b0 / b1 = column g, the same two k-slot runs; c as for the f16 form.
+__device__ __forceinline__ void imma16832(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                          uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
 // (a & b) | c in one instruction; b and c are constants the compiler keeps in registers
 __device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t b, uint32_t c) {
     uint32_t d;
@@ -169,6 +177,7 @@ struct TcPhase {
     int x_mode, accumulate, swiglu;
     uint32_t total_units;
     int use_q4, use_q6;
+    int q4_i8;                     // the Q4_K tensors of the phase run on the integer form (see q4k_block_i8)
     float *xn_out;
 };
 
@@ -192,7 +201,8 @@ struct TcSmem {
     float *ssq;                    // per-warp sums of squares of the prologue
     uint8_t *zero;                 // 16 zero bytes (the B operand of lanes that feed no column)
     float *xs;                     // [nblk] block scale 2^e
-    float *s4;                     // [nblk][8] sums of the 32-column sub-blocks, in units of the block scale
+    float *xs8;                    // integer form: [nblk][8] sub-block scales 2^e (odd sub-blocks: 2^e / 16)
+    float *s4;                     // [nblk][8] sums of the 32-column sub-blocks, in units of the block scale (integer form: as they are)
     uint8_t *x4, *x6;              // [nblk][1024]
     uint8_t *ring;
 };
@@ -205,16 +215,17 @@ __host__ __device__ inline size_t tc_head_bytes(uint32_t nslots, int groups) {
     n += 36 * 4 + 16;                                     // ssq, 16 zero bytes
     return (n + 15) & ~(size_t)15;
 }
-__host__ __device__ inline size_t tc_x_bytes(uint32_t cols, bool q4, bool q6) {
+__host__ __device__ inline size_t tc_x_bytes(uint32_t cols, bool q4, bool q6, bool i8) {
     const size_t nblk = cols / 256;
     size_t n = (nblk * 4 + 15) & ~(size_t)15;             // xs
+    if (i8) n += nblk * 32;                               // xs8
     if (q4) n += nblk * 32 + nblk * 1024;
     if (q6) n += nblk * 1024;
     return n;
 }
 
 template <int G>
-__device__ __forceinline__ TcSmem tc_carve(uint8_t *base, uint32_t cols, bool q4, bool q6, uint32_t nslots, uint32_t ring_off) {
+__device__ __forceinline__ TcSmem tc_carve(uint8_t *base, uint32_t cols, bool q4, bool q6, bool i8, uint32_t nslots, uint32_t ring_off) {
     TcSmem s;
     const uint32_t nblk = cols / 256;
     uint8_t *p = base;
@@ -227,6 +238,8 @@ __device__ __forceinline__ TcSmem tc_carve(uint8_t *base, uint32_t cols, bool q4
     s.zero = p;
     p = base + tc_head_bytes(nslots, G);
     s.xs = (float *)p; p += (nblk * 4 + 15) & ~15u;
+    s.xs8 = nullptr;
+    if (i8) { s.xs8 = (float *)p; p += nblk * 32; }
     s.s4 = nullptr; s.x4 = s.x6 = nullptr;
     if (q4) { s.s4 = (float *)p; p += nblk * 32; s.x4 = p; p += (size_t)nblk * 1024; }
     if (q6) { s.x6 = p; p += (size_t)nblk * 1024; }
@@ -303,6 +316,57 @@ __device__ __forceinline__ void q4k_block(uint32_t r0, uint32_t oh, uint32_t oa,
         const float q = u8f<0>(sc) * tl + u8f<1>(sc) * th;
         const float m = u8f<0>(mn) * s0 + u8f<1>(mn) * s1;
         (r ? out1 : out0) = d * q - dmin * m;
+    }
+}
+
+// Q4_K, integer form (the default for Q4_K). The nibbles are used as they are: word & 0x0F0F0F0F is four unsigned
+// 8-bit quants of sub-block 2t, word & 0xF0F0F0F0 four quants of sub-block 2t+1 times 16 (the 1/16 sits in that
+// sub-block's activation scale): one logic operation per four weights, and the products and sums are exact. The
+// activation is fixed point per 32-column sub-block, x = 2^e * n with |n| < 2^30, n cut into four signed 8-bit digits
+// n = D0 2^24 + D1 2^16 + D2 2^8 + D3; digit planes (D0, D1) are the two columns of B that belong to the lane column
+// in the first instruction of a pair, (D2, D3) in the second, so that a lane reads back its own rows' four plane
+// sums: c[0] = {D0, D1 of row g; D0, D1 of row g + 8}, c[1] the same for D2, D3. Word pair (2m, 2m+1) of the chunk
+// is one instruction's k range (8 weights per row). sx: sums of the activation over sub-blocks 2t, 2t+1; xs2: their
+// scales. Results come back in final units (no block scale left to apply).
+__device__ __forceinline__ void q4k_block_i8(uint32_t r0, uint32_t oh, uint32_t oa, uint32_t ob, uint32_t t, uint32_t xaddr,
+                                             uint32_t xstride, float2 sx, float2 xs2, float &out0, float &out1) {
+    const uint32_t r1 = r0 + 8 * kPitch4;
+    const uint4 wa0 = lds128(r0 + oa), wa1 = lds128(r1 + oa);
+    uint4 bx[8];   // slot 2m + h: (b0, b1) of planes 0, 1 and of planes 2, 3 for word pair m, nibble kind h
+#pragma unroll
+    for (int j = 0; j < 4; ++j) bx[j] = lds128(xaddr + j * xstride);
+    const uint4 wb0 = lds128(r0 + ob), wb1 = lds128(r1 + ob);
+#pragma unroll
+    for (int j = 4; j < 8; ++j) bx[j] = lds128(xaddr + j * xstride);
+    const uint4 h0 = lds128(r0 + oh), h1 = lds128(r1 + oh);
+    int cL[2][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}}, cH[2][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}};
+    const uint32_t ML = 0x0F0F0F0Fu, MH = 0xF0F0F0F0u;
+#pragma unroll
+    for (int m = 0; m < 4; ++m) {
+        const uint32_t A0 = m < 2 ? word_of(wa0, 2 * m) : word_of(wb0, 2 * m - 4), B0 = m < 2 ? word_of(wa0, 2 * m + 1) : word_of(wb0, 2 * m - 3);
+        const uint32_t A1 = m < 2 ? word_of(wa1, 2 * m) : word_of(wb1, 2 * m - 4), B1 = m < 2 ? word_of(wa1, 2 * m + 1) : word_of(wb1, 2 * m - 3);
+        const uint32_t l0 = A0 & ML, l1 = A1 & ML, l2 = B0 & ML, l3 = B1 & ML;
+        const uint32_t g0 = A0 & MH, g1 = A1 & MH, g2 = B0 & MH, g3 = B1 & MH;
+        imma16832(cL[0], l0, l1, l2, l3, bx[2 * m].x, bx[2 * m].y);
+        imma16832(cH[0], g0, g1, g2, g3, bx[2 * m + 1].x, bx[2 * m + 1].y);
+        imma16832(cL[1], l0, l1, l2, l3, bx[2 * m].z, bx[2 * m].w);
+        imma16832(cH[1], g0, g1, g2, g3, bx[2 * m + 1].z, bx[2 * m + 1].w);
+    }
+    // 6-bit scales / mins of sub-blocks 2t, 2t+1 (fl_q4k_scale_min, src/runtime/quants.h:121-129), as in q4k_block
+    const uint32_t sh = 16u * (t & 1u);
+    const uint32_t shA = t >= 2 ? sh + 2u : sh, mA = t >= 2 ? 0x3030u : 0x3F3Fu, mE = t >= 2 ? 0x0F0Fu : 0u;
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const uint4 hdr = r ? h1 : h0;
+        const uint32_t sc = ((hdr.y >> shA) & mA) | ((hdr.w >> sh) & mE);
+        const uint32_t mn = ((hdr.z >> shA) & mA) | ((hdr.w >> (sh + 4u)) & mE);
+        const float d = h2f_bits((uint16_t)(hdr.x & 0xFFFFu)), dmin = h2f_bits((uint16_t)(hdr.x >> 16));
+        // the four plane sums of a sub-block as one number: two exact integer steps (|.| < 2^28), then f32
+        const float tl = fmaf((float)(cL[0][2 * r] * 256 + cL[0][2 * r + 1]), 65536.f, (float)(cL[1][2 * r] * 256 + cL[1][2 * r + 1]));
+        const float th = fmaf((float)(cH[0][2 * r] * 256 + cH[0][2 * r + 1]), 65536.f, (float)(cH[1][2 * r] * 256 + cH[1][2 * r + 1]));
+        const float q = u8f<0>(sc) * (xs2.x * tl) + u8f<1>(sc) * (xs2.y * th);   // the sums in the activation's units first
+        const float mm = u8f<0>(mn) * sx.x + u8f<1>(mn) * sx.y;
+        (r ? out1 : out0) = d * q - dmin * mm;
     }
 }
 
@@ -486,7 +550,7 @@ __global__ void __launch_bounds__((G * kCW + 2) * 32) matvec_tc_kernel(const __g
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
     const uint32_t S = a.nslots;
     {
-        const TcSmem sm = tc_carve<G>(smem_raw, 256, false, false, S, a.ring_off);
+        const TcSmem sm = tc_carve<G>(smem_raw, 256, false, false, false, S, a.ring_off);
         if (tid == 0) {
             for (uint32_t s = 0; s < S; ++s) { mbar_init(&sm.full[s], 1); mbar_init(&sm.empty[s], kCW); }
             for (int i = 0; i < 2; ++i) { mbar_init(&sm.red_full[i], kConsumers); mbar_init(&sm.red_empty[i], 1); }
@@ -501,7 +565,7 @@ __global__ void __launch_bounds__((G * kCW + 2) * 32) matvec_tc_kernel(const __g
 
     if (warp == kProducer) {
         // ---- producer: one bulk copy per row and stage; the weights do not depend on any activation ----
-        const TcSmem sm = tc_carve<G>(smem_raw, 256, false, false, S, a.ring_off);
+        const TcSmem sm = tc_carve<G>(smem_raw, 256, false, false, false, S, a.ring_off);
         uint32_t slot = 0, par = 1;   // a fresh barrier passes a wait on parity 1
 #pragma unroll 1
         for (int p = 0; p < a.n_phases; ++p) {
@@ -572,7 +636,7 @@ __global__ void __launch_bounds__((G * kCW + 2) * 32) matvec_tc_kernel(const __g
     for (int p = 0; p < a.n_phases; ++p) {
         const TcPhase &ph = a.ph[p];
         const uint32_t nblk = ph.cols / 256, nseg = (nblk + 7) / 8;
-        const TcSmem sm = tc_carve<G>(smem_raw, ph.cols, ph.use_q4 != 0, ph.use_q6 != 0, S, a.ring_off);
+        const TcSmem sm = tc_carve<G>(smem_raw, ph.cols, ph.use_q4 != 0, ph.use_q6 != 0, ph.q4_i8 != 0, S, a.ring_off);
         const uint32_t my_units = blockIdx.x < ph.total_units ? (ph.total_units - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
         const bool late = p > 0;   // the activation was written by the previous phase of this launch: read it past L1
 
@@ -664,6 +728,47 @@ __global__ void __launch_bounds__((G * kCW + 2) * 32) matvec_tc_kernel(const __g
                 float amax = 0.f;
 #pragma unroll
                 for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
+                if (ph.q4_i8) {
+                    // ---- integer form: fixed point per 32-column sub-block (this lane and its neighbour hl ^ 1) ----
+                    const float am = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+                    int e = (int)((__float_as_uint(am) >> 23) & 0xFFu) - 127 - 29;   // am / 2^e in [2^29, 2^30)
+                    e = am > 0.f ? max(-122, min(e, 98)) : 0;                          // 2^-e and 2^(e - 4) are normal floats
+                    const float inv_s = __uint_as_float((uint32_t)(127 - e) << 23);
+                    float sum = 0.f;
+                    uint32_t V[16];
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        sum += v[i];
+                        // n + 0x808080 has the balanced digits of n, each plus 128, in its low three bytes
+                        V[i] = ((uint32_t)__float2int_rn(v[i] * inv_s) + 0x00808080u) ^ 0x00808080u;
+                    }
+                    const float sum32 = sum + __shfl_xor_sync(0xffffffffu, sum, 1);
+                    uint32_t P[4][4];   // [plane: 0 = most significant digit][group of four elements]
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        const uint32_t t0 = __byte_perm(V[4 * k], V[4 * k + 1], 0x5140u), t1 = __byte_perm(V[4 * k + 2], V[4 * k + 3], 0x5140u);
+                        const uint32_t t2 = __byte_perm(V[4 * k], V[4 * k + 1], 0x7362u), t3 = __byte_perm(V[4 * k + 2], V[4 * k + 3], 0x7362u);
+                        P[3][k] = __byte_perm(t0, t1, 0x5410u);
+                        P[2][k] = __byte_perm(t0, t1, 0x7632u);
+                        P[1][k] = __byte_perm(t2, t3, 0x5410u);
+                        P[0][k] = __byte_perm(t2, t3, 0x7632u);
+                    }
+                    if (live) {
+                        // columns 16 hl ..: chunk c, nibble kind h, elements 16 (hl & 1) .. of the sub-block = word pairs m0, m0 + 1
+                        const uint32_t c = hl >> 2, h = (hl >> 1) & 1u, m0 = 2 * (hl & 1u);
+                        const uint32_t base = smem_u32(sm.x4) + blk * 1024u + h * 128u + c * 32u;
+#pragma unroll
+                        for (int mm = 0; mm < 2; ++mm)
+#pragma unroll
+                            for (int pl = 0; pl < 4; ++pl)
+                                sts64(base + (m0 + mm) * 256u + (pl & 1) * 16u + (pl >> 1) * 8u, P[pl][2 * mm], P[pl][2 * mm + 1]);
+                        if ((hl & 1u) == 0) {
+                            sm.s4[blk * 8 + (hl >> 1)] = sum32;
+                            sm.xs8[blk * 8 + (hl >> 1)] = __uint_as_float((uint32_t)(127 + e - (h ? 4 : 0)) << 23);
+                        }
+                    }
+                    if (!ph.use_q6) continue;   // warp-uniform: no f16 image needed
+                }
 #pragma unroll
                 for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));   // over the half-warp
                 // block scale 2^e with amax / 2^e in [2^13, 2^14); e clamped so that both 2^e and 2^-e are normal floats
@@ -691,7 +796,7 @@ __global__ void __launch_bounds__((G * kCW + 2) * 32) matvec_tc_kernel(const __g
                 }
                 const float sum32 = sum + __shfl_xor_sync(0xffffffffu, sum, 1);
                 if (live) {
-                    if (ph.use_q4) {
+                    if (ph.use_q4 && !ph.q4_i8) {
                         // columns 16 hl .. 16 hl + 15: chunk c = hl / 4, sub-block half (hl / 2) & 1, words 4 (hl & 1) + j
                         const uint32_t c = hl >> 2, sub = (hl >> 1) & 1u, j0 = 4 * (hl & 1u);
                         const uint32_t base = smem_u32(sm.x4) + blk * 1024u;
@@ -800,7 +905,25 @@ __global__ void __launch_bounds__((G * kCW + 2) * 32) matvec_tc_kernel(const __g
                 // this group's stages of unit k: those of its stage sequence (grp, grp + G, ... over the whole launch)
                 // that fall into [it_base + k nseg, it_base + (k + 1) nseg)
                 const uint32_t it0 = it_base + k * nseg, it1 = it0 + nseg;
-                if (fmt == FMT_Q4_K) {
+                if (fmt == FMT_Q4_K && ph.q4_i8) {
+                    for (; c_it < it1; c_it += G) {
+                        const uint32_t blk = (c_it - it0) * 8 + w;
+                        mbar_wait_or_die(&sm.full[c_slot], c_par, a.status, dead);
+                        if (blk < nblk) {
+                            const uint32_t r0 = ring + c_slot * a.slot_bytes + g * kPitch4;
+                            const float2 sx = *reinterpret_cast<const float2 *>(sm.s4 + blk * 8 + 2 * t);
+                            const float2 xs2 = *reinterpret_cast<const float2 *>(sm.xs8 + blk * 8 + 2 * t);
+                            float o0, o1;
+                            q4k_block_i8(r0, oh, oa, ob, t, xa4 + blk * xb, xstride, sx, xs2, o0, o1);
+                            acc0 += o0;
+                            acc1 += o1;
+                        }
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&sm.empty[c_slot]);
+                        c_slot += G;
+                        if (c_slot >= S) { c_slot -= S; c_par ^= 1u; }
+                    }
+                } else if (fmt == FMT_Q4_K) {
                     for (; c_it < it1; c_it += G) {
                         const uint32_t blk = (c_it - it0) * 8 + w;
                         mbar_wait_or_die(&sm.full[c_slot], c_par, a.status, dead);
@@ -892,6 +1015,13 @@ cudaError_t matvec_tc_init(void) {
 
 // True when the launch can run on the tensor-core kernel: Q4_K / Q6_K / Q8_0 tensors only, whole 256-column
 // blocks, 16-byte aligned rows, no expert indirection and no exchange prologue.
+// Q4_K on the integer form (q4k_block_i8) unless FLB_TC_I8=0; a launch that also holds Q8_0 tensors shares the f16
+// image of the activation with them and stays on the f16 form.
+bool tc_q4_i8() {
+    static const bool on = !(getenv("FLB_TC_I8") && getenv("FLB_TC_I8")[0] == '0');
+    return on;
+}
+
 bool matvec_tc_eligible(const MatvecArgs &a) {
     static const bool off = getenv("FLB_TC") && getenv("FLB_TC")[0] == '0';
     if (off || a.xr_buf || a.cols % 256 != 0 || a.cols < 256) return false;
@@ -911,7 +1041,7 @@ bool matvec_tc_eligible(const MatvecArgs &a) {
     }
     if (a.swiglu && (a.n_tensors != 2 || a.t[0].rows != a.t[1].rows || a.t[0].fmt != a.t[1].fmt || a.accumulate)) return false;
     const uint32_t slot = q8 ? kSlot8 : q6 ? kSlot6 : kSlot4;
-    return tc_head_bytes(2, groups) + tc_x_bytes(a.cols, q4, q6) + 1024 + 2u * slot <= 227 * 1024 - 1024;
+    return tc_head_bytes(2, groups) + tc_x_bytes(a.cols, q4, q6, q4 && !q8 && tc_q4_i8()) + 1024 + 2u * slot <= 227 * 1024 - 1024;
 }
 
 // One launch of n dependent matvecs (phase i + 1 consumes what phase i writes). n = 1: a plain launch.
@@ -930,7 +1060,7 @@ cudaError_t launch_matvec_tc_chain(const MatvecArgs *args, int n, int sms, cudaS
         if (!matvec_tc_eligible(a)) return cudaErrorNotSupported;
         if (p > 0 && (a.trace || a.issue_late)) { /* per-launch diagnostics apply to the first phase only */ }
         TcPhase &ph = k.ph[p];
-        bool q4 = false, q6 = false;
+        bool q4 = false, q6 = false, q8 = false;
         uint32_t units = 0;
         ph.n_tensors = a.n_tensors;
         for (int i = 0; i < a.n_tensors; ++i) {
@@ -949,14 +1079,16 @@ cudaError_t launch_matvec_tc_chain(const MatvecArgs *args, int n, int sms, cudaS
             }
             (t.fmt == FMT_Q6_K ? q6 : q4) = true;   // Q8_0 uses the Q4_K layout of the activation
             any8 = any8 || t.fmt == FMT_Q8_0;
+            q8 = q8 || t.fmt == FMT_Q8_0;
         }
         if (a.swiglu) units = (a.t[0].rows + 7) / 8;
         ph.x = a.x; ph.x2 = a.x2; ph.wnorm = a.wnorm; ph.eps = a.eps; ph.cols = a.cols; ph.x_mode = a.x_mode;
         ph.accumulate = a.accumulate; ph.swiglu = a.swiglu; ph.total_units = units;
         ph.use_q4 = q4 ? 1 : 0; ph.use_q6 = q6 ? 1 : 0;
+        ph.q4_i8 = (q4 && !q8 && tc_q4_i8()) ? 1 : 0;
         ph.xn_out = a.xn_out;
         any6 = any6 || q6;
-        xmax = std::max(xmax, tc_x_bytes(a.cols, q4, q6));
+        xmax = std::max(xmax, tc_x_bytes(a.cols, q4, q6, ph.q4_i8 != 0));
         max_units = std::max(max_units, units);
     }
     k.n_phases = n;
