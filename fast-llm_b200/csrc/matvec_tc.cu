@@ -95,6 +95,35 @@ __device__ __forceinline__ void tma_box3(uint32_t dst, const CUtensorMap *map, u
         "l"(map), "r"(0), "r"(line), "r"(row), "r"(smem_u32(bar))
         : "memory");
 }
+// The same with an L2 eviction policy for the lines the copy touches (the weights pass through L2 once).
+__device__ __forceinline__ void tma_box2_hint(uint32_t dst, const CUtensorMap *map, uint32_t x, uint32_t y, uint64_t *bar, uint64_t pol) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, %3}], [%4], %5;" ::"r"(dst),
+        "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar)), "l"(pol)
+        : "memory");
+}
+__device__ __forceinline__ void tma_box3_hint(uint32_t dst, const CUtensorMap *map, uint32_t line, uint32_t row, uint64_t *bar, uint64_t pol) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, %3, %4}], [%5], %6;" ::"r"(dst),
+        "l"(map), "r"(0), "r"(line), "r"(row), "r"(smem_u32(bar)), "l"(pol)
+        : "memory");
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+    uint64_t p;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_last() {
+    uint64_t p;
+    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+// Read-only 16-byte load whose line is kept in L2 in preference to others (small tensors every launch reads again)
+__device__ __forceinline__ float4 ldg_keep(const float4 *p, uint64_t pol) {
+    float4 v;
+    asm volatile("ld.global.nc.L2::cache_hint.v4.f32 {%0, %1, %2, %3}, [%4], %5;" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p), "l"(pol));
+    return v;
+}
 // All threads of the prologue (every warp but the producer) meet here.
 __device__ __forceinline__ void prologue_barrier(uint32_t nthreads) {
     asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
@@ -190,6 +219,7 @@ struct TcArgs {
     int n_phases;
     uint32_t nslots, slot_bytes, ring_off;   // ring_off: bytes from the start of shared memory to the ring
     uint32_t *status;
+    int l2_hints;                            // weights evict-first, norm weights evict-last in L2
     GridBar *bar;                            // n_phases > 1
     unsigned long long *trace;
 };
@@ -567,6 +597,7 @@ __global__ void __launch_bounds__((G * kCW + 2) * 32) matvec_tc_kernel(const __g
         // ---- producer: one bulk copy per row and stage; the weights do not depend on any activation ----
         const TcSmem sm = tc_carve<G>(smem_raw, 256, false, false, false, S, a.ring_off);
         uint32_t slot = 0, par = 1;   // a fresh barrier passes a wait on parity 1
+        const uint64_t pol = a.l2_hints ? l2_policy_evict_first() : 0ull;
 #pragma unroll 1
         for (int p = 0; p < a.n_phases; ++p) {
             const TcPhase &ph = a.ph[p];
@@ -612,9 +643,15 @@ __global__ void __launch_bounds__((G * kCW + 2) * 32) matvec_tc_kernel(const __g
                         // tensor and blocks past the end of a row arrive as zeros and count as bytes all the same
                         mbar_arrive_expect_tx(&sm.full[slot], 16 * segb);
                         const TcTensor &t0 = ph.t[ti];
-                        if (t0.swz) {
+                        if (t0.swz && a.l2_hints) {
+                            tma_box3_hint(dst, &t0.map, off / 128, row0, &sm.full[slot], pol);
+                            if (ph.swiglu) tma_box3_hint(dst + 8 * segb, &ph.t[1].map, off / 128, row0, &sm.full[slot], pol);
+                        } else if (t0.swz) {
                             tma_box3(dst, &t0.map, off / 128, row0, &sm.full[slot]);
                             if (ph.swiglu) tma_box3(dst + 8 * segb, &ph.t[1].map, off / 128, row0, &sm.full[slot]);
+                        } else if (a.l2_hints) {
+                            tma_box2_hint(dst, &t0.map, off / 8, row0, &sm.full[slot], pol);
+                            if (ph.swiglu) tma_box2_hint(dst + 8 * segb, &ph.t[1].map, off / 8, row0, &sm.full[slot], pol);
                         } else {
                             tma_box2(dst, &t0.map, off / 8, row0, &sm.full[slot]);
                             if (ph.swiglu) tma_box2(dst + 8 * segb, &ph.t[1].map, off / 8, row0, &sm.full[slot]);
@@ -652,13 +689,14 @@ __global__ void __launch_bounds__((G * kCW + 2) * 32) matvec_tc_kernel(const __g
 #pragma unroll
                 for (int k = 0; k < 4; ++k) ra[b][k] = rb[b][k] = make_float4(0.f, 0.f, 0.f, 0.f);
             if (ph.x_mode == MV_X_RMSNORM) {   // the norm weights are constants: fetch them before the dependency is met
+                const uint64_t keep = a.l2_hints ? l2_policy_evict_last() : 0ull;
 #pragma unroll
                 for (int b = 0; b < kMaxBlkPerHalfWarp; ++b) {
                     const uint32_t blk = hw + b * nhw;
                     if (blk < nblk) {
                         const float4 *src = reinterpret_cast<const float4 *>(ph.wnorm + blk * 256 + hl * 16);
 #pragma unroll
-                        for (int k = 0; k < 4; ++k) rb[b][k] = __ldg(src + k);
+                        for (int k = 0; k < 4; ++k) rb[b][k] = a.l2_hints ? ldg_keep(src + k, keep) : __ldg(src + k);
                     }
                 }
             }
@@ -721,9 +759,15 @@ __global__ void __launch_bounds__((G * kCW + 2) * 32) matvec_tc_kernel(const __g
                     for (int k = 0; k < 4; ++k) {
                         w2[4 * k] = rb[b][k].x; w2[4 * k + 1] = rb[b][k].y; w2[4 * k + 2] = rb[b][k].z; w2[4 * k + 3] = rb[b][k].w;
                     }
+                    // one branch around each form (a per-element choice made the compiler evaluate the exponential and
+                    // the division in RMSNorm launches too: measured 1.1 us per launch)
+                    if (ph.x_mode == MV_X_RMSNORM) {
 #pragma unroll
-                    for (int i = 0; i < 16; ++i)
-                        v[i] = ph.x_mode == MV_X_RMSNORM ? v[i] * w2[i] : (v[i] / (1.0f + expf(-v[i]))) * w2[i];
+                        for (int i = 0; i < 16; ++i) v[i] *= w2[i];
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) v[i] = (v[i] / (1.0f + expf(-v[i]))) * w2[i];
+                    }
                 }
                 float amax = 0.f;
 #pragma unroll
@@ -1094,6 +1138,8 @@ cudaError_t launch_matvec_tc_chain(const MatvecArgs *args, int n, int sms, cudaS
     k.n_phases = n;
     k.status = args[0].status;
     k.trace = args[0].trace;
+    static const bool hints = !(getenv("FLB_TC_L2HINT") && getenv("FLB_TC_L2HINT")[0] == '0');
+    k.l2_hints = hints ? 1 : 0;
     k.slot_bytes = any8 ? kSlot8 : any6 ? kSlot6 : kSlot4;
     const size_t limit = 227 * 1024 - 1024;
     uint32_t nslots = 2;
