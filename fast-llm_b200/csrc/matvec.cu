@@ -516,13 +516,17 @@ matvec_stream_kernel(const MatvecArgs a, const __grid_constant__ TensorMaps maps
             v[4 * k] = ra[b][k].x; v[4 * k + 1] = ra[b][k].y; v[4 * k + 2] = ra[b][k].z; v[4 * k + 3] = ra[b][k].w;
             w2[4 * k] = rb2[b][k].x; w2[4 * k + 1] = rb2[b][k].y; w2[4 * k + 2] = rb2[b][k].z; w2[4 * k + 3] = rb2[b][k].w;
         }
+        // one branch around each form: chosen per element, the compiler evaluates the exponential in every mode
+        if (a.x_mode == MV_X_RMSNORM) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) v[i] = v[i] * w2[i];
+        } else if (a.x_mode == MV_X_SILU_MUL) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) v[i] = (v[i] / (1.0f + expf(-v[i]))) * w2[i];   // 0 for padding: silu(0) = 0
+        }
         float amax = 0.f;
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-            if (a.x_mode == MV_X_RMSNORM) v[i] = v[i] * w2[i];
-            else if (a.x_mode == MV_X_SILU_MUL) v[i] = (v[i] / (1.0f + expf(-v[i]))) * w2[i];   // 0 for padding: silu(0) = 0
-            amax = fmaxf(amax, fabsf(v[i]));
-        }
+        for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
 #pragma unroll
         for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));   // over the half-warp
         const float s = amax > 0.f ? amax / kFixMax : 1.0f;

@@ -79,6 +79,12 @@ __device__ __forceinline__ uint32_t lds16(uint32_t addr) {
 __device__ __forceinline__ void sts64(uint32_t addr, uint32_t a, uint32_t b) {
     asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(addr), "r"(a), "r"(b) : "memory");
 }
+__device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+__device__ __forceinline__ void sts32(uint32_t addr, uint32_t a) {
+    asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr), "r"(a) : "memory");
+}
 __device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
@@ -206,7 +212,7 @@ struct TcPhase {
     int x_mode, accumulate, swiglu;
     uint32_t total_units;
     int use_q4, use_q6;
-    int q4_i8;                     // the Q4_K tensors of the phase run on the integer form (see q4k_block_i8)
+    int q4_i8;                     // the phase runs on the integer forms (q4k_block_i8, q6k_block_i8): no Q8_0 tensor in it
     float *xn_out;
 };
 
@@ -231,7 +237,9 @@ struct TcSmem {
     float *ssq;                    // per-warp sums of squares of the prologue
     uint8_t *zero;                 // 16 zero bytes (the B operand of lanes that feed no column)
     float *xs;                     // [nblk] block scale 2^e
-    float *xs8;                    // integer form: [nblk][8] sub-block scales 2^e (odd sub-blocks: 2^e / 16)
+    float *xs8;                    // integer form, Q4_K: [nblk][8] sub-block scales 2^e (odd sub-blocks: 2^e / 16)
+    float *xsp;                    // integer form, Q6_K: [nblk][8] sub-block scales 2^e
+    float *s16;                    // integer form, Q6_K: [nblk][4 lane columns][4 groups] sums of the 16-column groups
     float *s4;                     // [nblk][8] sums of the 32-column sub-blocks, in units of the block scale (integer form: as they are)
     uint8_t *x4, *x6;              // [nblk][1024]
     uint8_t *ring;
@@ -248,7 +256,8 @@ __host__ __device__ inline size_t tc_head_bytes(uint32_t nslots, int groups) {
 __host__ __device__ inline size_t tc_x_bytes(uint32_t cols, bool q4, bool q6, bool i8) {
     const size_t nblk = cols / 256;
     size_t n = (nblk * 4 + 15) & ~(size_t)15;             // xs
-    if (i8) n += nblk * 32;                               // xs8
+    if (i8 && q4) n += nblk * 32;                         // xs8
+    if (i8 && q6) n += nblk * 32 + nblk * 64;             // xsp, s16
     if (q4) n += nblk * 32 + nblk * 1024;
     if (q6) n += nblk * 1024;
     return n;
@@ -268,8 +277,9 @@ __device__ __forceinline__ TcSmem tc_carve(uint8_t *base, uint32_t cols, bool q4
     s.zero = p;
     p = base + tc_head_bytes(nslots, G);
     s.xs = (float *)p; p += (nblk * 4 + 15) & ~15u;
-    s.xs8 = nullptr;
-    if (i8) { s.xs8 = (float *)p; p += nblk * 32; }
+    s.xs8 = s.xsp = s.s16 = nullptr;
+    if (i8 && q4) { s.xs8 = (float *)p; p += nblk * 32; }
+    if (i8 && q6) { s.xsp = (float *)p; p += nblk * 32; s.s16 = (float *)p; p += nblk * 64; }
     s.s4 = nullptr; s.x4 = s.x6 = nullptr;
     if (q4) { s.s4 = (float *)p; p += nblk * 32; s.x4 = p; p += (size_t)nblk * 1024; }
     if (q6) { s.x6 = p; p += (size_t)nblk * 1024; }
@@ -495,6 +505,98 @@ __device__ __forceinline__ void q6k_block(uint32_t r0, uint32_t r1, uint32_t t, 
     }
 }
 
+// byte K of w, which holds s + 128, as the float s (the byte under 0x4B000000 is 2^23 + 128 + s)
+template <int K>
+__device__ __forceinline__ float s8f(uint32_t w) {
+    return __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7440u + K)) - 8388736.f;
+}
+
+// Q6_K, integer form: the same loads and the same assembly of the 6-bit quants as q6k_block, but the four bytes
+// q (0 .. 63) of a word are used as they are, as unsigned 8-bit operands of mma.sync m16n8k32; the - 32 of the format
+// comes off through the activation's group sums (sum (q - 32) x = sum q x - 32 sum x). Steps (2 sp, 2 sp + 1) of group gq
+// are one instruction's k range; the activation is the fixed-point form of q4k_block_i8 (scale per 32 columns: the
+// lane column's groups gq = 0..3 have their own sub-blocks), digit planes (D0, D1) in the first instruction of a pair,
+// (D2, D3) in the second. xs4: the scales of the lane's four groups; sx4: the sums of the activation over them.
+template <bool ODD>
+__device__ __forceinline__ void q6k_block_i8(uint32_t r0, uint32_t r1, uint32_t t, uint32_t xaddr, uint32_t xstride, float4 xs4,
+                                             float4 sx4, float &out0, float &out1) {
+    const uint32_t hf = t >> 1, hq = t & 1u;
+    const uint32_t oa = 64 * hf + 16 * hq, oh = 128 + 32 * hf + 16 * hq;   // byte offsets in the block
+    uint32_t wa[2][4], wb[2][4], wh[2][4];
+#pragma unroll
+    for (int s = 0; s < 4; ++s) {
+        const uint32_t js = ((uint32_t)s + t) & 3u;
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            const uint32_t rb = r ? r1 : r0;
+            if (ODD) {
+                const uint32_t a0 = lds32(rb + oa + 4 * js), a1 = lds32(rb + oa + 4 * js + 4);
+                const uint32_t b0 = lds32(rb + oa + 32 + 4 * js), b1 = lds32(rb + oa + 36 + 4 * js);
+                const uint32_t h0 = lds32(rb + oh + 4 * js), h1 = lds32(rb + oh + 4 * js + 4);
+                wa[r][s] = __byte_perm(a0, a1, 0x5432u);
+                wb[r][s] = __byte_perm(b0, b1, 0x5432u);
+                wh[r][s] = __byte_perm(h0, h1, 0x5432u);
+            } else {
+                wa[r][s] = lds32(rb + oa + 4 * js);
+                wb[r][s] = lds32(rb + oa + 32 + 4 * js);
+                wh[r][s] = lds32(rb + oh + 4 * js);
+            }
+        }
+    }
+    uint4 bx[8];   // slot 4 sp + gq
+#pragma unroll
+    for (int q = 0; q < 8; ++q) bx[q] = lds128(xaddr + q * xstride);
+    // scales: int8 sc[8 hf + 2 gq + hq]; d at byte 208
+    uint32_t sw[2];
+    float dd[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const uint32_t rb = r ? r1 : r0;
+        const uint32_t ps = rb + 192 + 8 * hf;
+        uint32_t lo, hi;
+        if (ODD) {
+            const uint32_t s0 = lds32(ps), s1 = lds32(ps + 4), s2 = lds32(ps + 8);
+            lo = __byte_perm(s0, s1, 0x5432u);
+            hi = __byte_perm(s1, s2, 0x5432u);
+        } else {
+            lo = lds32(ps);
+            hi = lds32(ps + 4);
+        }
+        sw[r] = __byte_perm(lo, hi, hq ? 0x7531u : 0x6420u) ^ 0x80808080u;   // s + 128 as unsigned bytes
+        dd[r] = h2f_bits((uint16_t)lds16(rb + (ODD ? 2u : 0u) + 208));
+    }
+    const float xs_[4] = {xs4.x, xs4.y, xs4.z, xs4.w};
+    const float m32[4] = {-32.f * sx4.x, -32.f * sx4.y, -32.f * sx4.z, -32.f * sx4.w};
+    float v[2] = {0.f, 0.f};
+#pragma unroll
+    for (int gq = 0; gq < 4; ++gq) {
+        uint32_t q[2][4];   // [row][step]
+#pragma unroll
+        for (int r = 0; r < 2; ++r)
+#pragma unroll
+            for (int s = 0; s < 4; ++s) {
+                const uint32_t a = wa[r][s], b = wb[r][s], h = wh[r][s];
+                q[r][s] = gq == 0   ? (a & 0x0F0F0F0Fu) | ((h << 4) & 0x30303030u)
+                          : gq == 1 ? (b & 0x0F0F0F0Fu) | ((h << 2) & 0x30303030u)
+                          : gq == 2 ? ((a >> 4) & 0x0F0F0F0Fu) | (h & 0x30303030u)
+                                    : ((b >> 4) & 0x0F0F0F0Fu) | ((h >> 2) & 0x30303030u);
+            }
+        int c0[4] = {0, 0, 0, 0}, c1[4] = {0, 0, 0, 0};
+        imma16832(c0, q[0][0], q[1][0], q[0][1], q[1][1], bx[gq].x, bx[gq].y);
+        imma16832(c1, q[0][0], q[1][0], q[0][1], q[1][1], bx[gq].z, bx[gq].w);
+        imma16832(c0, q[0][2], q[1][2], q[0][3], q[1][3], bx[4 + gq].x, bx[4 + gq].y);
+        imma16832(c1, q[0][2], q[1][2], q[0][3], q[1][3], bx[4 + gq].z, bx[4 + gq].w);
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            const float f = fmaf((float)(c0[2 * r] * 256 + c0[2 * r + 1]), 65536.f, (float)(c1[2 * r] * 256 + c1[2 * r + 1]));
+            const float sc = gq == 0 ? s8f<0>(sw[r]) : gq == 1 ? s8f<1>(sw[r]) : gq == 2 ? s8f<2>(sw[r]) : s8f<3>(sw[r]);
+            v[r] = fmaf(sc, fmaf(xs_[gq], f, m32[gq]), v[r]);
+        }
+    }
+    out0 = dd[0] * v[0];
+    out1 = dd[1] * v[1];
+}
+
 // Q8_0 (blocks of 32 int8 with one f16 d, 34 bytes; fl_dot_row_q8_0, src/runtime/quants.h:132-142): the 256
 // columns of warp w are blocks 8 w .. 8 w + 7 of the segment; lane column t takes blocks 2 t and 2 t + 1, 68 bytes
 // from `r0` / `r1` (4-byte aligned). The first block's quants start 2 bytes into a word and are realigned with
@@ -571,7 +673,11 @@ __device__ __forceinline__ bool grid_barrier(GridBar *b, uint32_t nblocks, uint3
 // then the finalizer warp. A launch runs its phases one after the other with a grid-wide barrier in
 // between; the producer does not take part in the barriers: the weights of the next phase are already
 // streaming into the ring while the current phase drains and the next activation is built.
-template <int G>
+// F: 0 = every format and form, decided per phase at run time (f16 forms, Q8_0, several phases); 1 / 2 / 3 = one phase
+// on the integer forms holding Q4_K tensors only / Q6_K only / both: what a decode step launches. The specialised
+// instances carry only their own code (the whole kernel is some 7000 instructions, and a launch that has to fetch its
+// path out of that from L2 starts later) and get their own register allocation.
+template <int G, int F>
 __global__ void __launch_bounds__((G * kCW + 2) * 32) matvec_tc_kernel(const __grid_constant__ TcArgs a) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     constexpr uint32_t kConsumers = G * kCW;
@@ -673,7 +779,8 @@ __global__ void __launch_bounds__((G * kCW + 2) * 32) matvec_tc_kernel(const __g
     for (int p = 0; p < a.n_phases; ++p) {
         const TcPhase &ph = a.ph[p];
         const uint32_t nblk = ph.cols / 256, nseg = (nblk + 7) / 8;
-        const TcSmem sm = tc_carve<G>(smem_raw, ph.cols, ph.use_q4 != 0, ph.use_q6 != 0, ph.q4_i8 != 0, S, a.ring_off);
+        const bool I8 = F ? true : ph.q4_i8 != 0, UQ4 = F ? (F & 1) != 0 : ph.use_q4 != 0, UQ6 = F ? (F & 2) != 0 : ph.use_q6 != 0;
+        const TcSmem sm = tc_carve<G>(smem_raw, ph.cols, UQ4, UQ6, I8, S, a.ring_off);
         const uint32_t my_units = blockIdx.x < ph.total_units ? (ph.total_units - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
         const bool late = p > 0;   // the activation was written by the previous phase of this launch: read it past L1
 
@@ -772,7 +879,7 @@ __global__ void __launch_bounds__((G * kCW + 2) * 32) matvec_tc_kernel(const __g
                 float amax = 0.f;
 #pragma unroll
                 for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
-                if (ph.q4_i8) {
+                if (I8) {
                     // ---- integer form: fixed point per 32-column sub-block (this lane and its neighbour hl ^ 1) ----
                     const float am = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
                     int e = (int)((__float_as_uint(am) >> 23) & 0xFFu) - 127 - 29;   // am / 2^e in [2^29, 2^30)
@@ -797,7 +904,7 @@ __global__ void __launch_bounds__((G * kCW + 2) * 32) matvec_tc_kernel(const __g
                         P[1][k] = __byte_perm(t2, t3, 0x5410u);
                         P[0][k] = __byte_perm(t2, t3, 0x7632u);
                     }
-                    if (live) {
+                    if (live && UQ4) {
                         // columns 16 hl ..: chunk c, nibble kind h, elements 16 (hl & 1) .. of the sub-block = word pairs m0, m0 + 1
                         const uint32_t c = hl >> 2, h = (hl >> 1) & 1u, m0 = 2 * (hl & 1u);
                         const uint32_t base = smem_u32(sm.x4) + blk * 1024u + h * 128u + c * 32u;
@@ -811,7 +918,25 @@ __global__ void __launch_bounds__((G * kCW + 2) * 32) matvec_tc_kernel(const __g
                             sm.xs8[blk * 8 + (hl >> 1)] = __uint_as_float((uint32_t)(127 + e - (h ? 4 : 0)) << 23);
                         }
                     }
-                    if (!ph.use_q6) continue;   // warp-uniform: no f16 image needed
+                    if (live && UQ6) {
+                        // Q6_K: these 16 columns are one scale group (half hf, group gq, run hq) of lane column t = 2 hf + hq;
+                        // word js of the run is the lane column's step s = (js - t) & 3: register s & 1 of slot (s / 2, gq)
+                        const uint32_t hf = hl >> 3, gq = (hl >> 1) & 3u, hq = hl & 1u, t = 2 * hf + hq;
+                        const uint32_t base = smem_u32(sm.x6) + blk * 1024u + gq * 128u + t * 32u;
+                        // words (hq, hq + 1) of the run are steps (2 sp, 2 sp + 1) of slot sp = hf, words (hq + 2, hq + 3) those
+                        // of slot hf ^ 1: one select per word for the odd lane columns, the slot by address
+#pragma unroll
+                        for (int q = 0; q < 2; ++q)
+#pragma unroll
+                            for (int pp = 0; pp < 2; ++pp) {
+                                const uint32_t a0 = hq ? P[pp][2 * q + 1] : P[pp][2 * q], a1 = hq ? P[pp][(2 * q + 2) & 3] : P[pp][2 * q + 1];
+                                const uint32_t a2 = hq ? P[pp + 2][2 * q + 1] : P[pp + 2][2 * q], a3 = hq ? P[pp + 2][(2 * q + 2) & 3] : P[pp + 2][2 * q + 1];
+                                sts128(base + ((uint32_t)q ^ hf) * 512u + pp * 16u, a0, a1, a2, a3);
+                            }
+                        sm.s16[blk * 16 + t * 4 + gq] = sum;
+                        if (hq == 0) sm.xsp[blk * 8 + (hl >> 1)] = __uint_as_float((uint32_t)(127 + e) << 23);
+                    }
+                    continue;   // warp-uniform: the f16 images belong to the other form
                 }
 #pragma unroll
                 for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));   // over the half-warp
@@ -840,7 +965,7 @@ __global__ void __launch_bounds__((G * kCW + 2) * 32) matvec_tc_kernel(const __g
                 }
                 const float sum32 = sum + __shfl_xor_sync(0xffffffffu, sum, 1);
                 if (live) {
-                    if (ph.use_q4 && !ph.q4_i8) {
+                    if (F == 0 && UQ4 && !I8) {
                         // columns 16 hl .. 16 hl + 15: chunk c = hl / 4, sub-block half (hl / 2) & 1, words 4 (hl & 1) + j
                         const uint32_t c = hl >> 2, sub = (hl >> 1) & 1u, j0 = 4 * (hl & 1u);
                         const uint32_t base = smem_u32(sm.x4) + blk * 1024u;
@@ -851,7 +976,7 @@ __global__ void __launch_bounds__((G * kCW + 2) * 32) matvec_tc_kernel(const __g
                         }
                         if ((hl & 1u) == 0) sm.s4[blk * 8 + (hl >> 1)] = sum32;
                     }
-                    if (ph.use_q6) {
+                    if (F == 0 && UQ6) {
                         // columns 16 hl ..: half hf = hl / 8, group gq = (hl / 2) & 3, run hq = hl & 1, words j = 0..3
                         const uint32_t hf = hl >> 3, gq = (hl >> 1) & 3u, hq = hl & 1u, t = 2 * hf + hq;
                         const uint32_t base = smem_u32(sm.x6) + blk * 1024u;
@@ -925,7 +1050,7 @@ __global__ void __launch_bounds__((G * kCW + 2) * 32) matvec_tc_kernel(const __g
             const bool has_b = (g >> 1) == t;   // this lane feeds column g of the B operand; the others feed zeros
             const uint32_t lane8 = 2 * t + (g & 1u);
             const uint32_t zero16 = smem_u32(sm.zero);
-            const uint32_t x4 = ph.use_q4 ? smem_u32(sm.x4) + lane8 * 16u : 0u, x6 = ph.use_q6 ? smem_u32(sm.x6) + lane8 * 16u : 0u;
+            const uint32_t x4 = UQ4 ? smem_u32(sm.x4) + lane8 * 16u : 0u, x6 = UQ6 ? smem_u32(sm.x6) + lane8 * 16u : 0u;
             const uint32_t xstride = has_b ? 128u : 0u;
             const uint32_t xb = has_b ? 1024u : 0u;   // lanes that feed zeros stay on the zero slot
             const uint32_t xa4 = has_b ? x4 : zero16, xa6 = has_b ? x6 : zero16;
@@ -949,7 +1074,8 @@ __global__ void __launch_bounds__((G * kCW + 2) * 32) matvec_tc_kernel(const __g
                 // this group's stages of unit k: those of its stage sequence (grp, grp + G, ... over the whole launch)
                 // that fall into [it_base + k nseg, it_base + (k + 1) nseg)
                 const uint32_t it0 = it_base + k * nseg, it1 = it0 + nseg;
-                if (fmt == FMT_Q4_K && ph.q4_i8) {
+                const bool is4 = F == 1 ? true : F == 2 ? false : fmt == FMT_Q4_K;
+                if (is4 && I8) {
                     for (; c_it < it1; c_it += G) {
                         const uint32_t blk = (c_it - it0) * 8 + w;
                         mbar_wait_or_die(&sm.full[c_slot], c_par, a.status, dead);
@@ -967,7 +1093,7 @@ __global__ void __launch_bounds__((G * kCW + 2) * 32) matvec_tc_kernel(const __g
                         c_slot += G;
                         if (c_slot >= S) { c_slot -= S; c_par ^= 1u; }
                     }
-                } else if (fmt == FMT_Q4_K) {
+                } else if (F == 0 && fmt == FMT_Q4_K) {
                     for (; c_it < it1; c_it += G) {
                         const uint32_t blk = (c_it - it0) * 8 + w;
                         mbar_wait_or_die(&sm.full[c_slot], c_par, a.status, dead);
@@ -985,7 +1111,7 @@ __global__ void __launch_bounds__((G * kCW + 2) * 32) matvec_tc_kernel(const __g
                         c_slot += G;
                         if (c_slot >= S) { c_slot -= S; c_par ^= 1u; }
                     }
-                } else if (fmt == FMT_Q8_0) {
+                } else if (F == 0 && fmt == FMT_Q8_0) {
                     for (; c_it < it1; c_it += G) {
                         const uint32_t blk = (c_it - it0) * 8 + w;
                         mbar_wait_or_die(&sm.full[c_slot], c_par, a.status, dead);
@@ -1002,7 +1128,26 @@ __global__ void __launch_bounds__((G * kCW + 2) * 32) matvec_tc_kernel(const __g
                         c_slot += G;
                         if (c_slot >= S) { c_slot -= S; c_par ^= 1u; }
                     }
-                } else {
+                } else if (I8) {
+                    for (; c_it < it1; c_it += G) {
+                        const uint32_t blk = (c_it - it0) * 8 + w;
+                        mbar_wait_or_die(&sm.full[c_slot], c_par, a.status, dead);
+                        if (blk < nblk) {
+                            const uint32_t r0 = ring + c_slot * a.slot_bytes + g * kPitch6 + w * 210u;
+                            const float4 xs4 = *reinterpret_cast<const float4 *>(sm.xsp + blk * 8 + 4 * (t >> 1));
+                            const float4 sx4 = *reinterpret_cast<const float4 *>(sm.s16 + blk * 16 + 4 * t);
+                            float o0, o1;
+                            if (w & 1u) q6k_block_i8<true>(r0 - 2, r0 + 8 * kPitch6 - 2, t, xa6 + blk * xb, xstride, xs4, sx4, o0, o1);
+                            else q6k_block_i8<false>(r0, r0 + 8 * kPitch6, t, xa6 + blk * xb, xstride, xs4, sx4, o0, o1);
+                            acc0 += o0;
+                            acc1 += o1;
+                        }
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&sm.empty[c_slot]);
+                        c_slot += G;
+                        if (c_slot >= S) { c_slot -= S; c_par ^= 1u; }
+                    }
+                } else if (F == 0) {
                     for (; c_it < it1; c_it += G) {
                         const uint32_t blk = (c_it - it0) * 8 + w;
                         mbar_wait_or_die(&sm.full[c_slot], c_par, a.status, dead);
@@ -1052,15 +1197,19 @@ int tc_groups() {
 } // namespace
 
 cudaError_t matvec_tc_init(void) {
-    cudaError_t e = cudaFuncSetAttribute(matvec_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024 - 1024);
-    if (e != cudaSuccess) return e;
-    return cudaFuncSetAttribute(matvec_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024 - 1024);
+    const int smem = 227 * 1024 - 1024;
+    cudaError_t e = cudaFuncSetAttribute(matvec_tc_kernel<1, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(matvec_tc_kernel<2, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(matvec_tc_kernel<2, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(matvec_tc_kernel<2, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(matvec_tc_kernel<2, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    return e;
 }
 
 // True when the launch can run on the tensor-core kernel: Q4_K / Q6_K / Q8_0 tensors only, whole 256-column
 // blocks, 16-byte aligned rows, no expert indirection and no exchange prologue.
-// Q4_K on the integer form (q4k_block_i8) unless FLB_TC_I8=0; a launch that also holds Q8_0 tensors shares the f16
-// image of the activation with them and stays on the f16 form.
+// Q4_K and Q6_K on the integer forms (q4k_block_i8, q6k_block_i8) unless FLB_TC_I8=0; a launch that holds a Q8_0
+// tensor stays on the f16 forms (Q8_0 reads the f16 image of the activation).
 bool tc_q4_i8() {
     static const bool on = !(getenv("FLB_TC_I8") && getenv("FLB_TC_I8")[0] == '0');
     return on;
@@ -1085,7 +1234,7 @@ bool matvec_tc_eligible(const MatvecArgs &a) {
     }
     if (a.swiglu && (a.n_tensors != 2 || a.t[0].rows != a.t[1].rows || a.t[0].fmt != a.t[1].fmt || a.accumulate)) return false;
     const uint32_t slot = q8 ? kSlot8 : q6 ? kSlot6 : kSlot4;
-    return tc_head_bytes(2, groups) + tc_x_bytes(a.cols, q4, q6, q4 && !q8 && tc_q4_i8()) + 1024 + 2u * slot <= 227 * 1024 - 1024;
+    return tc_head_bytes(2, groups) + tc_x_bytes(a.cols, q4, q6, !q8 && tc_q4_i8()) + 1024 + 2u * slot <= 227 * 1024 - 1024;
 }
 
 // One launch of n dependent matvecs (phase i + 1 consumes what phase i writes). n = 1: a plain launch.
@@ -1129,7 +1278,7 @@ cudaError_t launch_matvec_tc_chain(const MatvecArgs *args, int n, int sms, cudaS
         ph.x = a.x; ph.x2 = a.x2; ph.wnorm = a.wnorm; ph.eps = a.eps; ph.cols = a.cols; ph.x_mode = a.x_mode;
         ph.accumulate = a.accumulate; ph.swiglu = a.swiglu; ph.total_units = units;
         ph.use_q4 = q4 ? 1 : 0; ph.use_q6 = q6 ? 1 : 0;
-        ph.q4_i8 = (q4 && !q8 && tc_q4_i8()) ? 1 : 0;
+        ph.q4_i8 = (!q8 && tc_q4_i8()) ? 1 : 0;
         ph.xn_out = a.xn_out;
         any6 = any6 || q6;
         xmax = std::max(xmax, tc_x_bytes(a.cols, q4, q6, ph.q4_i8 != 0));
@@ -1159,9 +1308,18 @@ cudaError_t launch_matvec_tc_chain(const MatvecArgs *args, int n, int sms, cudaS
         if (!args[0].grid_bar) return cudaErrorInvalidValue;
         k.bar = reinterpret_cast<GridBar *>(args[0].grid_bar);
     }
-    if (groups == 2)
-        return launch_kernel(matvec_tc_kernel<2>, dim3(grid), dim3((2 * kCW + 2) * 32), smem, stream, args[0].pdl != 0, k);
-    return launch_kernel(matvec_tc_kernel<1>, dim3(grid), dim3((kCW + 2) * 32), smem, stream, args[0].pdl != 0, k);
+    if (groups == 2) {
+        const dim3 block((2 * kCW + 2) * 32);
+        const bool pdl = args[0].pdl != 0;
+        static const bool generic = getenv("FLB_TC_GENERIC") && getenv("FLB_TC_GENERIC")[0] == '1';   // A/B: the run-time form for every launch
+        const TcPhase &p0 = k.ph[0];
+        const int f = (n == 1 && p0.q4_i8 && !generic) ? (p0.use_q4 ? 1 : 0) | (p0.use_q6 ? 2 : 0) : 0;
+        if (f == 1) return launch_kernel(matvec_tc_kernel<2, 1>, dim3(grid), block, smem, stream, pdl, k);
+        if (f == 2) return launch_kernel(matvec_tc_kernel<2, 2>, dim3(grid), block, smem, stream, pdl, k);
+        if (f == 3) return launch_kernel(matvec_tc_kernel<2, 3>, dim3(grid), block, smem, stream, pdl, k);
+        return launch_kernel(matvec_tc_kernel<2, 0>, dim3(grid), block, smem, stream, pdl, k);
+    }
+    return launch_kernel(matvec_tc_kernel<1, 0>, dim3(grid), dim3((kCW + 2) * 32), smem, stream, args[0].pdl != 0, k);
 }
 
 cudaError_t launch_matvec_tc(const MatvecArgs &a, int sms, cudaStream_t stream) {
