@@ -677,7 +677,9 @@ __device__ __forceinline__ bool grid_barrier(GridBar *b, uint32_t nblocks, uint3
 // on the integer forms holding Q4_K tensors only / Q6_K only / both: what a decode step launches. The specialised
 // instances carry only their own code (the whole kernel is some 7000 instructions, and a launch that has to fetch its
 // path out of that from L2 starts later) and get their own register allocation.
-template <int G, int F>
+// R: 256-column blocks a half-warp of the prologue converts (F != 0: 1 up to 34 blocks = 8704 columns, else 2; the
+// specialised instances also leave out the SiLU prologue, the second copy of the activation and several phases).
+template <int G, int F, int R>
 __global__ void __launch_bounds__((G * kCW + 2) * 32) matvec_tc_kernel(const __grid_constant__ TcArgs a) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     constexpr uint32_t kConsumers = G * kCW;
@@ -739,7 +741,7 @@ __global__ void __launch_bounds__((G * kCW + 2) * 32) matvec_tc_kernel(const __g
                     if (!mbar_wait_bounded(&sm.empty[slot], par, a.status)) return;
                     fence_proxy_async_smem();
                     const uint32_t dst = ring + slot * a.slot_bytes;
-                    if (fmt == FMT_Q8_0) {   // one bulk copy per row
+                    if (F == 0 && fmt == FMT_Q8_0) {   // one bulk copy per row
                         const uint32_t bytes = min(segb, pitch - off);   // pitch and off are multiples of 16
                         if (lane == 0) mbar_arrive_expect_tx(&sm.full[slot], nvalid * bytes);
                         __syncwarp();
@@ -782,14 +784,14 @@ __global__ void __launch_bounds__((G * kCW + 2) * 32) matvec_tc_kernel(const __g
         const bool I8 = F ? true : ph.q4_i8 != 0, UQ4 = F ? (F & 1) != 0 : ph.use_q4 != 0, UQ6 = F ? (F & 2) != 0 : ph.use_q6 != 0;
         const TcSmem sm = tc_carve<G>(smem_raw, ph.cols, UQ4, UQ6, I8, S, a.ring_off);
         const uint32_t my_units = blockIdx.x < ph.total_units ? (ph.total_units - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
-        const bool late = p > 0;   // the activation was written by the previous phase of this launch: read it past L1
+        const bool late = F == 0 && p > 0;   // the activation was written by the previous phase of this launch: read it past L1
 
         // ---- prologue (consumers and the finalizer): the activation as f16 (hi, lo) pairs ----
         {
             const uint32_t pw = warp < kProducer ? warp : warp - 1;   // 0 .. kConsumers
             const uint32_t hw = 2 * pw + (lane >> 4), hl = lane & 15u;
             constexpr uint32_t nhw = 2 * (kConsumers + 1);
-            constexpr int kMaxBlkPerHalfWarp = max_blk_per_half_warp(G);
+            constexpr int kMaxBlkPerHalfWarp = F ? R : max_blk_per_half_warp(G);
             float4 ra[kMaxBlkPerHalfWarp][4], rb[kMaxBlkPerHalfWarp][4];
 #pragma unroll
             for (int b = 0; b < kMaxBlkPerHalfWarp; ++b)
@@ -830,7 +832,7 @@ __global__ void __launch_bounds__((G * kCW + 2) * 32) matvec_tc_kernel(const __g
                     const float4 *src = reinterpret_cast<const float4 *>(ph.x + blk * 256 + hl * 16);
 #pragma unroll
                     for (int k = 0; k < 4; ++k) ra[b][k] = late ? __ldcg(src + k) : src[k];
-                    if (ph.x_mode == MV_X_SILU_MUL) {
+                    if (F == 0 && ph.x_mode == MV_X_SILU_MUL) {
                         const float4 *src2 = reinterpret_cast<const float4 *>(ph.x2 + blk * 256 + hl * 16);
 #pragma unroll
                         for (int k = 0; k < 4; ++k) rb[b][k] = late ? __ldcg(src2 + k) : src2[k];
@@ -868,7 +870,7 @@ __global__ void __launch_bounds__((G * kCW + 2) * 32) matvec_tc_kernel(const __g
                     }
                     // one branch around each form (a per-element choice made the compiler evaluate the exponential and
                     // the division in RMSNorm launches too: measured 1.1 us per launch)
-                    if (ph.x_mode == MV_X_RMSNORM) {
+                    if (F != 0 || ph.x_mode == MV_X_RMSNORM) {
 #pragma unroll
                         for (int i = 0; i < 16; ++i) v[i] *= w2[i];
                     } else {
@@ -991,7 +993,7 @@ __global__ void __launch_bounds__((G * kCW + 2) * 32) matvec_tc_kernel(const __g
                 }
             }
             prologue_barrier(kPrologueThreads);
-            if (ph.xn_out != nullptr && blockIdx.x == 0) {   // the activation as f32, for layer-level checks
+            if (F == 0 && ph.xn_out != nullptr && blockIdx.x == 0) {   // the activation as f32, for layer-level checks
                 float t = 0.f;
                 for (uint32_t w = 0; w <= kConsumers; ++w) t += sm.ssq[w];
                 const float inv_rms = 1.0f / sqrtf(t / (float)ph.cols + ph.eps);
@@ -1076,6 +1078,7 @@ __global__ void __launch_bounds__((G * kCW + 2) * 32) matvec_tc_kernel(const __g
                 const uint32_t it0 = it_base + k * nseg, it1 = it0 + nseg;
                 const bool is4 = F == 1 ? true : F == 2 ? false : fmt == FMT_Q4_K;
                 if (is4 && I8) {
+#pragma unroll 1
                     for (; c_it < it1; c_it += G) {
                         const uint32_t blk = (c_it - it0) * 8 + w;
                         mbar_wait_or_die(&sm.full[c_slot], c_par, a.status, dead);
@@ -1094,6 +1097,7 @@ __global__ void __launch_bounds__((G * kCW + 2) * 32) matvec_tc_kernel(const __g
                         if (c_slot >= S) { c_slot -= S; c_par ^= 1u; }
                     }
                 } else if (F == 0 && fmt == FMT_Q4_K) {
+#pragma unroll 1
                     for (; c_it < it1; c_it += G) {
                         const uint32_t blk = (c_it - it0) * 8 + w;
                         mbar_wait_or_die(&sm.full[c_slot], c_par, a.status, dead);
@@ -1112,6 +1116,7 @@ __global__ void __launch_bounds__((G * kCW + 2) * 32) matvec_tc_kernel(const __g
                         if (c_slot >= S) { c_slot -= S; c_par ^= 1u; }
                     }
                 } else if (F == 0 && fmt == FMT_Q8_0) {
+#pragma unroll 1
                     for (; c_it < it1; c_it += G) {
                         const uint32_t blk = (c_it - it0) * 8 + w;
                         mbar_wait_or_die(&sm.full[c_slot], c_par, a.status, dead);
@@ -1129,6 +1134,7 @@ __global__ void __launch_bounds__((G * kCW + 2) * 32) matvec_tc_kernel(const __g
                         if (c_slot >= S) { c_slot -= S; c_par ^= 1u; }
                     }
                 } else if (I8) {
+#pragma unroll 1
                     for (; c_it < it1; c_it += G) {
                         const uint32_t blk = (c_it - it0) * 8 + w;
                         mbar_wait_or_die(&sm.full[c_slot], c_par, a.status, dead);
@@ -1148,6 +1154,7 @@ __global__ void __launch_bounds__((G * kCW + 2) * 32) matvec_tc_kernel(const __g
                         if (c_slot >= S) { c_slot -= S; c_par ^= 1u; }
                     }
                 } else if (F == 0) {
+#pragma unroll 1
                     for (; c_it < it1; c_it += G) {
                         const uint32_t blk = (c_it - it0) * 8 + w;
                         mbar_wait_or_die(&sm.full[c_slot], c_par, a.status, dead);
@@ -1198,11 +1205,13 @@ int tc_groups() {
 
 cudaError_t matvec_tc_init(void) {
     const int smem = 227 * 1024 - 1024;
-    cudaError_t e = cudaFuncSetAttribute(matvec_tc_kernel<1, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(matvec_tc_kernel<2, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(matvec_tc_kernel<2, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(matvec_tc_kernel<2, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(matvec_tc_kernel<2, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaError_t e = cudaFuncSetAttribute(matvec_tc_kernel<1, 0, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(matvec_tc_kernel<2, 0, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(matvec_tc_kernel<2, 1, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(matvec_tc_kernel<2, 3, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(matvec_tc_kernel<2, 1, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(matvec_tc_kernel<2, 2, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(matvec_tc_kernel<2, 3, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     return e;
 }
 
@@ -1313,13 +1322,20 @@ cudaError_t launch_matvec_tc_chain(const MatvecArgs *args, int n, int sms, cudaS
         const bool pdl = args[0].pdl != 0;
         static const bool generic = getenv("FLB_TC_GENERIC") && getenv("FLB_TC_GENERIC")[0] == '1';   // A/B: the run-time form for every launch
         const TcPhase &p0 = k.ph[0];
-        const int f = (n == 1 && p0.q4_i8 && !generic) ? (p0.use_q4 ? 1 : 0) | (p0.use_q6 ? 2 : 0) : 0;
-        if (f == 1) return launch_kernel(matvec_tc_kernel<2, 1>, dim3(grid), block, smem, stream, pdl, k);
-        if (f == 2) return launch_kernel(matvec_tc_kernel<2, 2>, dim3(grid), block, smem, stream, pdl, k);
-        if (f == 3) return launch_kernel(matvec_tc_kernel<2, 3>, dim3(grid), block, smem, stream, pdl, k);
-        return launch_kernel(matvec_tc_kernel<2, 0>, dim3(grid), block, smem, stream, pdl, k);
+        // the specialised instances: one phase, integer forms, plain or RMSNorm prologue, no copy of the activation asked for
+        const bool special = n == 1 && p0.q4_i8 && !generic && p0.x_mode != MV_X_SILU_MUL && p0.xn_out == nullptr;
+        const int f = special ? (p0.use_q4 ? 1 : 0) | (p0.use_q6 ? 2 : 0) : 0;
+        const bool one = p0.cols / 256 <= 2u * (2 * kCW + 1);   // every half-warp of the prologue converts at most one block
+        if (f == 1) return one ? launch_kernel(matvec_tc_kernel<2, 1, 1>, dim3(grid), block, smem, stream, pdl, k)
+                               : launch_kernel(matvec_tc_kernel<2, 1, 2>, dim3(grid), block, smem, stream, pdl, k);
+        // Q6_K only: the two-block instance for every width (the one-block instance spills in its consume loop: with 18
+        // warps a thread can have 96 registers, five warps share a quarter of the register file)
+        if (f == 2) return launch_kernel(matvec_tc_kernel<2, 2, 2>, dim3(grid), block, smem, stream, pdl, k);
+        if (f == 3) return one ? launch_kernel(matvec_tc_kernel<2, 3, 1>, dim3(grid), block, smem, stream, pdl, k)
+                               : launch_kernel(matvec_tc_kernel<2, 3, 2>, dim3(grid), block, smem, stream, pdl, k);
+        return launch_kernel(matvec_tc_kernel<2, 0, 0>, dim3(grid), block, smem, stream, pdl, k);
     }
-    return launch_kernel(matvec_tc_kernel<1, 0>, dim3(grid), dim3((kCW + 2) * 32), smem, stream, args[0].pdl != 0, k);
+    return launch_kernel(matvec_tc_kernel<1, 0, 0>, dim3(grid), dim3((kCW + 2) * 32), smem, stream, args[0].pdl != 0, k);
 }
 
 cudaError_t launch_matvec_tc(const MatvecArgs &a, int sms, cudaStream_t stream) {
