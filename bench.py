@@ -39,7 +39,7 @@ N_PREFILL = 8192
 METRIC = "decode tokens/s at 8B Q4_K_M shape, 1/2/4/8 B200; HBM GB/s % of roofline"
 
 
-NCU_TRAFFIC_RATIO = 1.0079
+NCU_TRAFFIC_RATIO = 1.0057
 TIMED_REGION_MS = 1000.0   # device time the repeated K-step loops add up to, at least
 
 

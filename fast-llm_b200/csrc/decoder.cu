@@ -232,7 +232,7 @@ static int enqueue_step(fl_b200_decoder *d, cudaStream_t s, uint32_t *n_launch, 
         a.n_tensors = 1;
         a.t[0] = {d->output.w, d->logits, nullptr, d->V, d->output.fmt, 0};
         a.x = d->xa; a.wnorm = d->out_norm; a.eps = c.eps; a.cols = E;
-        a.x_mode = MV_X_RMSNORM; a.status = ctx->status; a.pdl = kPdl; a.xn_out = d->xn_final;
+        a.x_mode = MV_X_RMSNORM; a.status = ctx->status; a.pdl = kPdl;   // the normed vector itself: computed when the tap is read
         a.issue_late = (issue_late() >> 3) & 1;
         return a;
     };
@@ -972,7 +972,11 @@ int fl_b200_decoder_tap(fl_b200_decoder *d, int which, float *out) {
     size_t n = 0;
     switch (which) {
     case 0: src = d->xa; n = c.n_embd; break;        // hidden state after the last layer
-    case 1: src = d->xn_final; n = c.n_embd; break;  // final normed vector
+    case 1:                                          // final normed vector: made here from the hidden state (the head's
+        src = d->xn_final; n = c.n_embd;             // launch takes the norm inside its prologue and keeps no copy)
+        if (cudaError_t e = launch_rmsnorm(d->xa, d->out_norm, d->xn_final, c.eps, c.n_embd, d->ctx->stream, 1, c.n_embd); e != cudaSuccess)
+            return set_err(FL_B200_ERR_CUDA, "decoder_tap: %s", cudaGetErrorString(e));
+        break;
     case 2: src = d->q; n = QD; break;               // last layer: q (before RoPE: the attention kernel rotates it)
     case 3: src = d->v; n = KD; break;               // last layer: v
     case 4: src = d->att; n = QD; break;             // last layer: attention output

@@ -117,6 +117,7 @@ def test_small_model_teacher_forced(ctx, checker):
         assert abs(dec.last_margin() - orc.margin()) <= 4 * np.max(np.abs(got - want)) + 1e-6
         hid = dec.tap(0)
         assert logits_close(hid, orc.hidden()) < HIDDEN_TOL
+        assert logits_close(dec.tap(1), orc.normed()) < HIDDEN_TOL     # the final norm, made from the hidden state on request
         force_kv(ctx, dec, orc, SMALL, 40 + step)
         tok = want_tok          # teacher forcing: both sides see the oracle's token and cache
     assert dec.n_past() == 48 and orc.n_past() == 48
