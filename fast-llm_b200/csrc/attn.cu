@@ -326,24 +326,31 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_decode_kernel(const __gr
         const float m1 = lane + 32 < S ? __ldcg(part + (uint64_t)(lane + 32) * kPartStride + kD) : -INFINITY;
         const float l0 = lane < S ? __ldcg(part + (uint64_t)lane * kPartStride + kD + 1) : 0.f;
         const float l1 = lane + 32 < S ? __ldcg(part + (uint64_t)(lane + 32) * kPartStride + kD + 1) : 0.f;
+        // The contexts of up to kCombineChunk splits are requested before anything waits for the maxima: the tail of a
+        // launch is a chain of L2 round trips (ticket, maxima, contexts), and with 16 loads in flight the contexts of
+        // 37 splits alone were three of them.
+        constexpr int kCombineChunk = 40;
+        float4 ov[kCombineChunk];
+#pragma unroll
+        for (int j = 0; j < kCombineChunk; ++j)
+            ov[j] = (uint32_t)j < S ? __ldcg(reinterpret_cast<const float4 *>(part + (uint64_t)j * kPartStride) + lane)
+                                    : make_float4(0.f, 0.f, 0.f, 0.f);
         const float mx = warp_max(fmaxf(m0, m1));
         const float w0 = m0 == -INFINITY ? 0.f : expf(m0 - mx);
         const float w1 = m1 == -INFINITY ? 0.f : expf(m1 - mx);
         const float L = warp_sum(l0 * w0 + l1 * w1);
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (uint32_t s0 = 0; s0 < S; s0 += 16) {
-            float4 ov[16];
 #pragma unroll
-            for (int j = 0; j < 16; ++j)
-                ov[j] = s0 + j < S ? __ldcg(reinterpret_cast<const float4 *>(part + (uint64_t)(s0 + j) * kPartStride) + lane)
-                                   : make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-                const uint32_t s = s0 + j;
-                const float w = __shfl_sync(0xffffffffu, s < 32 ? w0 : w1, s & 31u);
-                acc.x = fmaf(ov[j].x, w, acc.x); acc.y = fmaf(ov[j].y, w, acc.y);
-                acc.z = fmaf(ov[j].z, w, acc.z); acc.w = fmaf(ov[j].w, w, acc.w);
-            }
+        for (int j = 0; j < kCombineChunk; ++j) {
+            const float w = __shfl_sync(0xffffffffu, j < 32 ? w0 : w1, j & 31);
+            acc.x = fmaf(ov[j].x, w, acc.x); acc.y = fmaf(ov[j].y, w, acc.y);
+            acc.z = fmaf(ov[j].z, w, acc.z); acc.w = fmaf(ov[j].w, w, acc.w);
+        }
+        for (uint32_t s = kCombineChunk; s < S; ++s) {   // more splits than one chunk: the rest one by one, in split order
+            const float4 o = __ldcg(reinterpret_cast<const float4 *>(part + (uint64_t)s * kPartStride) + lane);
+            const float w = __shfl_sync(0xffffffffu, s < 32 ? w0 : w1, s & 31u);
+            acc.x = fmaf(o.x, w, acc.x); acc.y = fmaf(o.y, w, acc.y);
+            acc.z = fmaf(o.z, w, acc.z); acc.w = fmaf(o.w, w, acc.w);
         }
         const float inv = 1.0f / L;
         acc.x *= inv; acc.y *= inv; acc.z *= inv; acc.w *= inv;

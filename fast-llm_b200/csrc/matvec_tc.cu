@@ -3,33 +3,39 @@
 // and the STREAM_DOT branch of exec_task_block, src/runtime/gpu_exec.cu:64-140).
 //
 // HBM-bound by design: every packed weight byte crosses HBM -> shared memory once,
-// as bulk copies (cp.async.bulk) issued by a producer warp into a CTA-wide ring and
-// completed on mbarriers. What this kernel changes against the dp4a streaming kernel
-// (matvec.cu) is the arithmetic: there the consume loop was bound by instruction
-// issue (about 2.7 instructions per weight, the integer dot products at half rate).
-// Here
+// as tiled TMA boxes issued by a producer warp into a CTA-wide ring and completed on
+// mbarriers. What this kernel changes against the dp4a streaming kernel (matvec.cu) is
+// the arithmetic: there the consume loop was bound by instruction issue (about 2.7
+// instructions per weight, the integer dot products at half rate). Here
 //   * a unit of work is 16 rows x all columns; a stage is the same 8-super-block
-//     column segment (2048 columns) of the unit's 16 rows, one bulk copy per row;
+//     column segment (2048 columns) of the unit's 16 rows, one box per stage;
 //     consumer warp w of a group owns super-block w of the segment for all 16 rows;
-//   * the 4- / 6-bit quants become f16 values with two logic operations per PAIR of
-//     weights (the quant lands in the mantissa of a constant: 64 + q for Q4_K; 1024 + q,
-//     then an exact f16 subtraction of 1056, for Q6_K), directly in the register
-//     layout of the A operand of mma.sync.m16n8k16: lane (g, t) holds rows g and g + 8;
-//   * the activation is kept per 256-column block as x = 2^e * (hi + lo) with hi, lo
-//     f16 (hi the nearest f16 of x / 2^e, lo the nearest f16 of the remainder: 22
-//     significant bits, and the power-of-two block scale keeps a block with one huge
-//     element exact for the small ones too). It is the B operand. Column n of B is
-//     non-zero only for the k-slots of lane column t = n / 2 (n & 1 selects hi / lo), so
-//     that the accumulator a lane reads back, C[g][2t], C[g][2t+1], C[g+8][2t],
-//     C[g+8][2t+1], is the dot product of exactly the 2 x 4 weights the lane unpacked
-//     with their activations: every lane column accumulates its own sub-block, the
-//     6-bit sub-block scales / mins are applied once per super-block in f32, and no
-//     shuffle is needed until a row is complete. Products are exact (11-bit x 11-bit),
-//     sums are f32 in a fixed order: results are reproducible run to run.
+//   * the products run on the tensor cores through mma.sync, lane (g, t) holding rows
+//     g and g + 8 and the k-slots of lane column t. Column n of the B operand is
+//     non-zero only for the k-slots of lane column t = n / 2, so that the accumulator
+//     a lane reads back, C[g][2t], C[g][2t+1], C[g+8][2t], C[g+8][2t+1], is the dot
+//     product of exactly the weights the lane unpacked with their activations: every
+//     lane column accumulates its own sub-block, the sub-block scales / mins are
+//     applied once per super-block in f32, and no shuffle is needed until a row is
+//     complete;
+//   * integer forms (the default for Q4_K and Q6_K; q4k_block_i8, q6k_block_i8): the
+//     quants go in as they are, as unsigned 8-bit operands of m16n8k32 (a masked word
+//     is four weights: one logic operation per four weights for Q4_K), the activation
+//     as fixed point per 32-column sub-block, x = 2^e n with |n| < 2^30, cut into four
+//     signed 8-bit digit planes that are the two B columns of a lane column in two
+//     instructions. Products and sums are exact integers; one huge element costs the
+//     other 31 of its sub-block at most the digits it pushes out of 30 bits;
+//   * f16 forms (FLB_TC_I8=0, and every launch that holds a Q8_0 tensor): the quants
+//     become f16 values with two logic operations per PAIR of weights (the quant lands
+//     in the mantissa of a constant that an exact f16 subtraction takes off again), the
+//     activation per 256-column block as x = 2^e (hi + lo) with hi, lo f16: 22 bits;
+//   * sums are taken in a fixed order: results are reproducible run to run;
 //   * a unit's partial row sums (one per warp) are added in warp order by a finalizer
 //     warp, which also applies the fused epilogues (1/rms, residual, accumulate,
 //     SiLU(gate) * up).
 // Fused prologues as in the dp4a kernel: plain x, RMSNorm(x) * w, SiLU(x) * x2.
+// The kernel is instantiated once per format set of a decode launch (template F) beside
+// the form that decides everything at run time: see matvec_tc_kernel.
 #include "common.cuh"
 #include "kernels.h"
 
