@@ -703,7 +703,7 @@ def measure(tp_mode, args, ctx, cfg, config, dist, gloo, rank, local_rank, world
         "steps": steps, "warmup": warmup, "ms_per_step": ms_dev / steps, "higher_is_better": True,
         "repeats": {"n": len(reps_dev), "ms_per_repeat": [round(x, 3) for x in reps_dev], "reported": "median",
                     "e2e_n": len(reps_e2e), "e2e_ms_per_repeat": [round(x, 3) for x in reps_e2e]},
-        "scaling": "strong" if tp_mode else "weak", "vs_baseline": None, "dtype": "f32 activations / accumulation over Q4_K,Q6_K weights and f16 KV",
+        "scaling": "strong" if tp_mode else "weak", "vs_baseline": None, "dtype": "s32 sums of u8 x s8 products (Q4_K / Q6_K quants x 30-bit fixed-point activation digits), f32 scales and row sums; f16 KV with f32 attention",
         "data": "synthetic", "config": config,
         "roofline": {"bound": "hbm", "kernel": "matvec_tc_kernel", "achieved": achieved, "peak": peak,
                      "peak_source": "MEASURED_PEAKS.json hbm_gbs" if peak_kind == "measured" else "fallback 6.65 TB/s",
